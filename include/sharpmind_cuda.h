@@ -1,0 +1,187 @@
+/*
+ * sharpmind_cuda.h -- C ABI of libsharpmind_cuda.so, a CUDA (sm_100a) backend for SharpMind's
+ * quantized vec-dot / matmul hot path (GGUF Q8_0, Q4_K, Q6_K) and the fp32 ops the decoder
+ * runs around it.
+ *
+ * Every entry point takes plain pointers and sizes, returns an smc_status (0 = ok) unless
+ * stated otherwise, and never falls back to a CPU implementation.  Each declaration cites the
+ * SharpMind interface it stands in for (paths relative to the SharpMind repository root).
+ *
+ * Conventions kept from the reference:
+ *   - a weight matrix is [N = outFeatures rows, K = inFeatures], row-major by output row, in
+ *     GGUF block layout; `rawWeights` is always the whole tensor;
+ *   - Q8_0 rows are padded to whole 32-element blocks per row; K-quants are addressed on the
+ *     flat tensor (row r starts at element r*K of the 256-element block stream);
+ *   - activations are [M, K] fp32 row-major, outputs [M, N] fp32 row-major;
+ *   - dtype uses SharpMind's QuantDType numbering (QuantDType.cs:2-18).
+ *
+ * Pointers named d_* are device pointers; `stream` is a cudaStream_t passed as void*.
+ * A context may be used from several host threads; calls on one context are serialised.
+ */
+#ifndef SHARPMIND_CUDA_H
+#define SHARPMIND_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define SMC_API __declspec(dllexport)
+#else
+#define SMC_API __attribute__((visibility("default")))
+#endif
+
+typedef struct smc_ctx smc_ctx;
+typedef struct smc_weight smc_weight;
+typedef struct smc_q8act smc_q8act;
+typedef struct smc_model smc_model;
+
+typedef enum smc_status {
+    SMC_OK = 0,
+    SMC_E_INVALID = 1,        /* null pointer, negative size, unknown enum value */
+    SMC_E_UNSUPPORTED = 2,    /* dtype / shape / mode combination this build has no kernel for */
+    SMC_E_SIZE_MISMATCH = 3,  /* byte count != GetRawTensorByteCount; mirrors the reference's guard */
+    SMC_E_CUDA = 4,           /* a CUDA runtime call failed; see smc_last_error */
+    SMC_E_NOT_REGISTERED = 5, /* host weight pointer unknown to smc_weight_lookup */
+    SMC_E_NO_DEVICE = 6,
+    SMC_E_RANGE = 7           /* token id, position or column out of range */
+} smc_status;
+
+/* QuantDType values (SharpMind.Core/Quantization/QuantDType.cs:2-18) */
+enum { SMC_Q8_0 = 8, SMC_Q4_K = 12, SMC_Q6_K = 14 };
+
+/* How a quantized matmul treats its activations. */
+enum {
+    SMC_ACT_F32 = 0,  /* fp32 activations x dequantised weights, fp32 accumulate (reference semantics) */
+    SMC_ACT_Q8 = 1,   /* activations quantised to Q8_0 blocks on device, exact int32 block dots */
+    SMC_REF_ORDER = 2 /* fp32 activations, the scalar tier's own operation order and fp64 running
+                         sum: bit-identical to VecDot*_Scalar; any K; needs the raw layout kept */
+};
+
+/* smc_weight_register flags */
+enum {
+    SMC_W_REPACK = 1,   /* build the coalescing-friendly device layout used by the fast kernels */
+    SMC_W_KEEP_RAW = 2  /* also keep the GGUF-layout copy (needed by SMC_REF_ORDER and smc_vecdot_*) */
+};
+
+/* ---- library / context ------------------------------------------------------------------ */
+SMC_API int smc_version(void);
+SMC_API int smc_device_count(int *count);
+/* Creates a context on `device` (streams, scratch). Replaces the per-call accelerator set-up of
+ * SharpMind.GPU/GPUActivationKernels.cs:15-21. */
+SMC_API int smc_init(int device, smc_ctx **out);
+SMC_API void smc_destroy(smc_ctx *ctx);
+/* Text of the last failure on this context (valid until the next failing call). */
+SMC_API const char *smc_last_error(smc_ctx *ctx);
+/* QuantizationOps.GetRawTensorByteCount for a [N, K] tensor (QuantizationOps.cs:15-72); -1 if dtype unknown. */
+SMC_API int64_t smc_raw_tensor_bytes(int dtype, int64_t N, int64_t K);
+/* Blocks until everything queued on the context's own stream has finished. */
+SMC_API int smc_synchronize(smc_ctx *ctx);
+
+/* ---- weights: uploaded once ---------------------------------------------------------------
+ * InferenceLinearLayer.SetRawWeight (SharpMind.Model/Layers/InferenceLinearLayer.cs:200-221)
+ * validates the byte count on arrival; registration does the same and returns
+ * SMC_E_SIZE_MISMATCH.  The library copies the bytes; the caller keeps ownership of host_raw. */
+SMC_API int smc_weight_register(smc_ctx *ctx, const void *host_raw, size_t bytes, int dtype, int N, int K,
+                                int flags, smc_weight **out);
+/* Same, the GGUF-layout bytes already being in device memory (copied, not adopted). */
+SMC_API int smc_weight_register_dev(smc_ctx *ctx, const void *d_raw, size_t bytes, int dtype, int N, int K,
+                                    int flags, smc_weight **out);
+/* Finds the registration made from this host pointer, so that slots that only receive
+ * `byte* rawWeights` (QuantizedMatMulFn, QuantizationOps.cs:9) can reach the device copy. */
+SMC_API int smc_weight_lookup(smc_ctx *ctx, const void *host_raw, smc_weight **out);
+SMC_API int smc_weight_release(smc_ctx *ctx, smc_weight *w);
+SMC_API int smc_weight_shape(const smc_weight *w, int *dtype, int *N, int *K);
+
+/* ---- slot-shaped entry points: host pointers in, host results out, synchronous -------------
+ * QuantizedMatMulFn(float* input, byte* rawWeights, float* output, int M, int K, int N)
+ * (QuantizationOps.cs:9; the `linear` slot InferenceLinearLayer.cs:146 and the `logit` slot
+ * LogitOps.cs:143).  host_raw must have been registered. */
+SMC_API int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, float *output, int M,
+                             int K, int N, int dtype, int mode);
+/* VecDotFn(float* input, byte* rawWeights, int col, int inFeatures) (QuantizationOps.cs:8,176-202). */
+SMC_API int smc_vecdot_host(smc_ctx *ctx, const float *input, const void *host_raw, int col, int K,
+                            int dtype, float *result);
+/* ApplyGate(gate, up, dst) = SwiGLU (ActivationOps.cs:52-62, ActivationKernels.cs:194-201). */
+SMC_API int smc_swiglu_host(smc_ctx *ctx, const float *gate, const float *up, float *dst, int n);
+/* ApplyPointwise(src, dst) = SiLU (ActivationOps.cs:36-46, ActivationKernels.cs:161-168). */
+SMC_API int smc_silu_host(smc_ctx *ctx, const float *src, float *dst, int n);
+/* ApplySoftmaxRow(src, dst) (ActivationOps.cs:68-72, ActivationKernels.cs:316-348). */
+SMC_API int smc_softmax_row_host(smc_ctx *ctx, const float *src, float *dst, int n);
+/* ApplyRMSNormRow(src, weight, dst, rmsInv) (ActivationOps.cs:78-86, NormKernels.cs:13-33). */
+SMC_API int smc_rmsnorm_row_host(smc_ctx *ctx, const float *src, const float *weight, float *dst, int n,
+                                 float rms_inv);
+/* ScaledDotProduct(q, k, v, o, seqLen, kvLen, headDim, scale, causal, qStride, oStride, alibiSlope)
+ * (AttentionLayer.cs:239-258; flash form AttentionKernels.cs:409-475). k and v are [kvLen, headDim]. */
+SMC_API int smc_sdpa_host(smc_ctx *ctx, const float *q, const float *k, const float *v, float *o, int seqLen,
+                          int kvLen, int headDim, float scale, int causal, int qStride, int oStride,
+                          float alibiSlope);
+
+/* ---- device-resident entry points (asynchronous on `stream`) ------------------------------- */
+/* out[M, N] = in[M, K] x W^T.  QuantizedMatMul*_Parallel_* (e.g. QuantizationKernels.Q8.cs:556-574). */
+SMC_API int smc_qmatmul_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, int mode,
+                            void *stream);
+
+/* Q8_0 activation buffers: the device form of QuantizedKVCache.QuantizeRowQ8_0
+ * (SharpMind.Model/QuantizedKVCache.cs:191-223): d = amax/127 (1 for an all-zero block), stored as
+ * fp16 (round to nearest even), q = round-half-even(x/d). */
+SMC_API int smc_q8act_create(smc_ctx *ctx, int max_rows, int max_k, smc_q8act **out);
+SMC_API int smc_q8act_destroy(smc_ctx *ctx, smc_q8act *a);
+SMC_API int smc_quantize_q8_dev(smc_ctx *ctx, const float *d_x, int M, int K, smc_q8act *a, void *stream);
+/* Copies the quantised rows back to the host: q [M, K] int8, d_bits [M, K/32] fp16 bit patterns. */
+SMC_API int smc_q8act_read(smc_ctx *ctx, const smc_q8act *a, int8_t *q, uint16_t *d_bits);
+/* Matmul on activations already quantised with smc_quantize_q8_dev. */
+SMC_API int smc_qmatmul_q8_dev(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *d_out, void *stream);
+/* Per-32-element-block int32 dot sums of weight rows [col0, col1) with row `m` of `a`:
+ * d_sums[(c - col0) * K/32 + b].  Verification aid for the integer part of SMC_ACT_Q8. */
+SMC_API int smc_block_isums_dev(smc_ctx *ctx, const smc_q8act *a, int m, const smc_weight *w, int col0, int col1,
+                                int32_t *d_sums, void *stream);
+
+/* TensorQuantizer.Quantize (TensorQuantizer.cs:80-144 Q8_0; TensorQuantizer.KQuant.cs:173-225 Q4_K,
+ * :303-376 Q6_K): fp32 values -> GGUF blocks, n a multiple of the block size. */
+SMC_API int smc_quantize_weights_dev(smc_ctx *ctx, int dtype, const float *d_values, int64_t n, void *d_raw,
+                                     void *stream);
+
+/* NormLayer.Forward with RmsNormLayer (NormLayer.cs:42-57, RmsNormLayer.cs:8-20, NormKernels.cs:13-60):
+ * per row rmsInv = 1/sqrt(mean(x^2)+eps), out = x*rmsInv*w.  d_out may alias d_x. */
+SMC_API int smc_rmsnorm_dev(smc_ctx *ctx, const float *d_x, const float *d_w, float *d_out, int rows, int n,
+                            float eps, void *stream);
+/* FfnKernels.Gated's activation loop (Ffn/FfnKernels.cs:52-56): rows of gate/up with row stride `ld`
+ * (ld = 2F and d_up = d_gate + F for the fused gate||up buffer), dst [rows, F] dense. */
+SMC_API int smc_swiglu_dev(smc_ctx *ctx, const float *d_gate, const float *d_up, float *d_dst, int rows, int F,
+                           int ld, void *stream);
+SMC_API int smc_silu_dev(smc_ctx *ctx, const float *d_src, float *d_dst, int64_t n, void *stream);
+/* ActivationOps.Softmax row-wise (ActivationOps.cs:118-132). */
+SMC_API int smc_softmax_dev(smc_ctx *ctx, const float *d_src, float *d_dst, int rows, int n, void *stream);
+/* RoPE table build (SharpMind.Core/Embeddings/RoPE.cs:103-147, no frequency scaling): computed on the
+ * host with the same libm calls as the reference's MathF and uploaded; d_cos/d_sin [maxSeq, ropeDim/2]. */
+SMC_API int smc_rope_tables(smc_ctx *ctx, float theta, int ropeDim, int maxSeq, float *d_cos, float *d_sin);
+/* RoPE.Apply (RoPE.cs:168-259) in place on x [seq, heads, headDim]; neox != 0 pairs (d, d+ropeDim/2). */
+SMC_API int smc_rope_dev(smc_ctx *ctx, float *d_x, int seq, int heads, int headDim, int ropeDim, int posOffset,
+                         const float *d_cos, const float *d_sin, int neox, void *stream);
+/* Tensor<float>.AddInPlace (SharpMind.Core/Tensors/Tensor.cs:328-332): x += y. */
+SMC_API int smc_add_dev(smc_ctx *ctx, float *d_x, const float *d_y, int64_t n, void *stream);
+/* Sampler.Argmax (SharpMind.Inference/Sampler.cs:50-58) per row: first maximum wins. */
+SMC_API int smc_argmax_dev(smc_ctx *ctx, const float *d_logits, int rows, int n, int *d_out, void *stream);
+/* EmbeddingTable.Forward (SharpMind.Core/Embeddings/EmbeddingTable.cs:87-116) gathering rows of a Q8_0
+ * table dequantised as ReadQ8_0_Scalar does (QuantizationKernels.Q8.cs:412-433): out[i] = row tokens[i]. */
+SMC_API int smc_embed_q8_0_dev(smc_ctx *ctx, const smc_weight *table, const int *d_tokens, int count, float *d_out,
+                               void *stream);
+/* One query token per sequence against an fp32 KV cache laid out as KVCache does
+ * (SharpMind.Model/KVCache.cs:13-14,26-36): [batch, kvHeads, maxSeq, headDim]; q and out are
+ * [batch, heads, headDim]; causal with the query at position kvLen-1.  Computes what
+ * ScaledDotProductFlash* computes per (batch, head) (AttentionKernels.cs:315-475). */
+SMC_API int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const float *d_v, float *d_out,
+                                int batch, int heads, int kvHeads, int headDim, int kvLen, int maxSeq, float scale,
+                                void *stream);
+/* KVCache.Update for seqLen == 1 (KVCache.cs:84-150): writes k, v [batch, kvHeads, headDim] at `pos`. */
+SMC_API int smc_kv_append_dev(smc_ctx *ctx, const float *d_k, const float *d_v, float *d_kcache, float *d_vcache,
+                              int batch, int kvHeads, int headDim, int pos, int maxSeq, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHARPMIND_CUDA_H */

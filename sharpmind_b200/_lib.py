@@ -1,0 +1,82 @@
+"""ctypes binding of libsharpmind_cuda.so (the C ABI in include/sharpmind_cuda.h).
+
+The library is the product: if it is missing it is built with nvcc, and if that is impossible the
+import fails loudly.  There is no Python or CPU compute path behind these calls.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+_LIB = None
+
+c_void_p, c_int, c_float, c_size_t, c_int64 = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_int64
+_pp = C.POINTER(c_void_p)
+
+# name -> (restype, argtypes); mirrors include/sharpmind_cuda.h one to one
+SIGNATURES = {
+    "smc_version": (c_int, []),
+    "smc_device_count": (c_int, [C.POINTER(c_int)]),
+    "smc_init": (c_int, [c_int, _pp]),
+    "smc_destroy": (None, [c_void_p]),
+    "smc_last_error": (C.c_char_p, [c_void_p]),
+    "smc_raw_tensor_bytes": (c_int64, [c_int, c_int64, c_int64]),
+    "smc_synchronize": (c_int, [c_void_p]),
+    "smc_weight_register": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, _pp]),
+    "smc_weight_register_dev": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, _pp]),
+    "smc_weight_lookup": (c_int, [c_void_p, c_void_p, _pp]),
+    "smc_weight_release": (c_int, [c_void_p, c_void_p]),
+    "smc_weight_shape": (c_int, [c_void_p, C.POINTER(c_int), C.POINTER(c_int), C.POINTER(c_int)]),
+    "smc_qmatmul_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
+    "smc_vecdot_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, C.POINTER(c_float)]),
+    "smc_swiglu_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int]),
+    "smc_silu_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "smc_softmax_row_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "smc_rmsnorm_row_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float]),
+    "smc_sdpa_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                              c_int, c_int, c_int, c_float]),
+    "smc_qmatmul_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "smc_q8act_create": (c_int, [c_void_p, c_int, c_int, _pp]),
+    "smc_q8act_destroy": (c_int, [c_void_p, c_void_p]),
+    "smc_quantize_q8_dev": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "smc_q8act_read": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "smc_qmatmul_q8_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "smc_block_isums_dev": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "smc_quantize_weights_dev": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+    "smc_rmsnorm_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
+    "smc_swiglu_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "smc_silu_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "smc_softmax_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "smc_rope_tables": (c_int, [c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
+    "smc_rope_dev": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                             c_void_p]),
+    "smc_add_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "smc_argmax_dev": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "smc_embed_q8_0_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "smc_sdpa_decode_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                    c_int, c_int, c_float, c_void_p]),
+    "smc_kv_append_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_int, c_void_p]),
+}
+
+
+def lib_path() -> str:
+    return _build.LIB
+
+
+def load() -> C.CDLL:
+    """Loads (building first if needed) the shared library and types every entry point."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not os.path.exists(_build.LIB):
+        _build.build()
+    lib = C.CDLL(_build.LIB)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means header and library disagree
+        fn.restype = res
+        fn.argtypes = args
+    _LIB = lib
+    return lib

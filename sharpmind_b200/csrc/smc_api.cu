@@ -1,0 +1,500 @@
+// C ABI: context, weight registry, dispatch of the quantized matmul, and the host-pointer
+// ("slot-shaped") entry points that mirror the reference's kernel signatures.
+//
+// The host-pointer calls exist for API fidelity with SharpMind's JigSaw slots, which hand a kernel
+// native host pointers and expect results in host memory on return
+// (QuantizedMatMulFn / VecDotFn, SharpMind.Core/Quantization/QuantizationOps.cs:8-9; ApplyGate etc.,
+// SharpMind.Core/Activations/ActivationOps.cs:36-86).  They stage through pinned memory, run the same
+// device kernels as the *_dev entry points and synchronise.  There is no CPU compute path anywhere.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "smc_common.cuh"
+
+int smc_fail(smc_ctx *ctx, int code, const char *fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->last_error = buf;
+    return code;
+}
+
+namespace {
+
+int ensure_dev(smc_ctx *ctx, float **p, size_t *cap, size_t bytes)
+{
+    if (bytes <= *cap) return SMC_OK;
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *cap = 0;
+    size_t want = bytes + bytes / 4 + 4096;
+    SMC_CUDA(ctx, cudaMalloc(p, want));
+    *cap = want;
+    return SMC_OK;
+}
+
+int ensure_pinned(smc_ctx *ctx, size_t bytes)
+{
+    if (bytes <= ctx->h_pin_cap) return SMC_OK;
+    if (ctx->h_pin) cudaFreeHost(ctx->h_pin);
+    ctx->h_pin = nullptr;
+    ctx->h_pin_cap = 0;
+    size_t want = bytes + bytes / 4 + 4096;
+    SMC_CUDA(ctx, cudaMallocHost(&ctx->h_pin, want));
+    ctx->h_pin_cap = want;
+    return SMC_OK;
+}
+
+// Host -> device through the pinned bounce buffer (pageable source memory would otherwise make the
+// copy synchronous and slow); device -> host likewise.
+int h2d(smc_ctx *ctx, void *dst, const void *src, size_t bytes)
+{
+    int rc = ensure_pinned(ctx, bytes);
+    if (rc) return rc;
+    memcpy(ctx->h_pin, src, bytes);
+    SMC_CUDA(ctx, cudaMemcpyAsync(dst, ctx->h_pin, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    // the bounce buffer is reused by the next copy: wait for this one
+    SMC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SMC_OK;
+}
+
+int d2h(smc_ctx *ctx, void *dst, const void *src, size_t bytes)
+{
+    int rc = ensure_pinned(ctx, bytes);
+    if (rc) return rc;
+    SMC_CUDA(ctx, cudaMemcpyAsync(ctx->h_pin, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    SMC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    memcpy(dst, ctx->h_pin, bytes);
+    return SMC_OK;
+}
+
+bool known_dtype(int dtype) { return dtype == SMC_Q8_0 || dtype == SMC_Q4_K || dtype == SMC_Q6_K; }
+
+void free_weight(smc_weight *w)
+{
+    if (!w) return;
+    cudaFree(w->d_raw);
+    cudaFree(w->q8_qs);
+    cudaFree(w->q8_d);
+    cudaFree(w->q6_ql);
+    cudaFree(w->q6_qh);
+    cudaFree(w->q6_sc);
+    cudaFree(w->q6_d);
+    delete w;
+}
+
+// Shared tail of the two registration entry points: w->d_raw already holds the GGUF bytes.
+int finish_register(smc_ctx *ctx, smc_weight *w)
+{
+    const int K = w->K;
+    const bool shape_ok = (w->dtype == SMC_Q8_0) ? (K % 32 == 0) : (K % 256 == 0);
+    if ((w->flags & SMC_W_REPACK) && shape_ok) {
+        int rc = smc_launch_repack(ctx, w, ctx->stream);
+        if (rc) return rc;
+        SMC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        w->fast = true;
+        // Q4_K computes straight from the GGUF layout; the other formats can drop it
+        if (w->dtype != SMC_Q4_K && !(w->flags & SMC_W_KEEP_RAW)) {
+            cudaFree(w->d_raw);
+            w->d_raw = nullptr;
+        }
+    }
+    return SMC_OK;
+}
+
+int check_register_args(smc_ctx *ctx, const void *src, size_t bytes, int dtype, int N, int K, smc_weight **out)
+{
+    if (!ctx || !src || !out || N <= 0 || K <= 0) return smc_fail(ctx, SMC_E_INVALID, "weight_register: bad arguments");
+    if (!known_dtype(dtype)) return smc_fail(ctx, SMC_E_UNSUPPORTED, "weight_register: dtype %d not supported", dtype);
+    int64_t expect = smc_raw_tensor_bytes(dtype, N, K);
+    if ((int64_t)bytes != expect)
+        return smc_fail(ctx, SMC_E_SIZE_MISMATCH,
+                        "RawQuantizedData size mismatch: dtype=%d, K=%d, N=%d, expected=%lld, actual=%zu", dtype, K, N,
+                        (long long)expect, bytes);
+    return SMC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int smc_version(void) { return 100; }
+
+int smc_device_count(int *count)
+{
+    if (!count) return SMC_E_INVALID;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    *count = (e == cudaSuccess) ? n : 0;
+    return e == cudaSuccess ? SMC_OK : SMC_E_NO_DEVICE;
+}
+
+int64_t smc_raw_tensor_bytes(int dtype, int64_t N, int64_t K)
+{
+    switch (dtype) {
+    case SMC_Q8_0: return N * ((K + 31) / 32) * 34;
+    case SMC_Q4_K: return ((N * K + 255) / 256) * 144;
+    case SMC_Q6_K: return ((N * K + 255) / 256) * 210;
+    default: return -1;
+    }
+}
+
+int smc_init(int device, smc_ctx **out)
+{
+    if (!out) return SMC_E_INVALID;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) return SMC_E_NO_DEVICE;
+    if (device < 0 || device >= n) return SMC_E_INVALID;
+    if (cudaSetDevice(device) != cudaSuccess) return SMC_E_CUDA;
+    smc_ctx *ctx = new smc_ctx();
+    ctx->device = device;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete ctx;
+        return SMC_E_CUDA;
+    }
+    *out = ctx;
+    return SMC_OK;
+}
+
+void smc_destroy(smc_ctx *ctx)
+{
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto &kv : ctx->by_host) free_weight(kv.second);
+    ctx->by_host.clear();
+    cudaFree(ctx->d_stage_in);
+    cudaFree(ctx->d_stage_out);
+    cudaFree(ctx->d_stage_aux);
+    cudaFree(ctx->d_attn_part);
+    if (ctx->h_pin) cudaFreeHost(ctx->h_pin);
+    smc_q8act_free(ctx->act);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+const char *smc_last_error(smc_ctx *ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int smc_synchronize(smc_ctx *ctx)
+{
+    if (!ctx) return SMC_E_INVALID;
+    SMC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SMC_OK;
+}
+
+// ------------------------------------------------------------------------------------------ weights
+int smc_weight_register(smc_ctx *ctx, const void *host_raw, size_t bytes, int dtype, int N, int K, int flags,
+                        smc_weight **out)
+{
+    int rc = check_register_args(ctx, host_raw, bytes, dtype, N, K, out);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    smc_weight *w = new smc_weight();
+    w->dtype = dtype, w->N = N, w->K = K, w->flags = flags, w->raw_bytes = bytes, w->host_key = host_raw;
+    cudaError_t e = cudaMalloc(&w->d_raw, bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(w->d_raw, host_raw, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        free_weight(w);
+        return smc_fail(ctx, SMC_E_CUDA, "weight upload failed: %s", cudaGetErrorString(e));
+    }
+    rc = finish_register(ctx, w);
+    if (rc) {
+        free_weight(w);
+        return rc;
+    }
+    auto it = ctx->by_host.find(host_raw);
+    if (it != ctx->by_host.end()) {  // the same host buffer registered again replaces the old copy
+        free_weight(it->second);
+        ctx->by_host.erase(it);
+    }
+    ctx->by_host[host_raw] = w;
+    *out = w;
+    return SMC_OK;
+}
+
+int smc_weight_register_dev(smc_ctx *ctx, const void *d_raw, size_t bytes, int dtype, int N, int K, int flags,
+                            smc_weight **out)
+{
+    int rc = check_register_args(ctx, d_raw, bytes, dtype, N, K, out);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    smc_weight *w = new smc_weight();
+    w->dtype = dtype, w->N = N, w->K = K, w->flags = flags, w->raw_bytes = bytes, w->host_key = nullptr;
+    cudaError_t e = cudaMalloc(&w->d_raw, bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(w->d_raw, d_raw, bytes, cudaMemcpyDeviceToDevice);
+    if (e != cudaSuccess) {
+        free_weight(w);
+        return smc_fail(ctx, SMC_E_CUDA, "weight copy failed: %s", cudaGetErrorString(e));
+    }
+    rc = finish_register(ctx, w);
+    if (rc) {
+        free_weight(w);
+        return rc;
+    }
+    ctx->by_host[w] = w;  // keyed by itself so that the context owns and frees it
+    *out = w;
+    return SMC_OK;
+}
+
+int smc_weight_lookup(smc_ctx *ctx, const void *host_raw, smc_weight **out)
+{
+    if (!ctx || !host_raw || !out) return smc_fail(ctx, SMC_E_INVALID, "weight_lookup: bad arguments");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    auto it = ctx->by_host.find(host_raw);
+    if (it == ctx->by_host.end())
+        return smc_fail(ctx, SMC_E_NOT_REGISTERED, "no weight was registered from host pointer %p", host_raw);
+    *out = it->second;
+    return SMC_OK;
+}
+
+int smc_weight_release(smc_ctx *ctx, smc_weight *w)
+{
+    if (!ctx || !w) return smc_fail(ctx, SMC_E_INVALID, "weight_release: bad arguments");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    const void *key = w->host_key ? w->host_key : static_cast<const void *>(w);
+    auto it = ctx->by_host.find(key);
+    if (it == ctx->by_host.end() || it->second != w)
+        return smc_fail(ctx, SMC_E_NOT_REGISTERED, "weight %p does not belong to this context", (void *)w);
+    ctx->by_host.erase(it);
+    cudaStreamSynchronize(ctx->stream);
+    free_weight(w);
+    return SMC_OK;
+}
+
+int smc_weight_shape(const smc_weight *w, int *dtype, int *N, int *K)
+{
+    if (!w) return SMC_E_INVALID;
+    if (dtype) *dtype = w->dtype;
+    if (N) *N = w->N;
+    if (K) *K = w->K;
+    return SMC_OK;
+}
+
+// ------------------------------------------------------------------------------------------ matmul
+int smc_q8act_create(smc_ctx *ctx, int max_rows, int max_k, smc_q8act **out)
+{
+    if (!ctx || !out) return smc_fail(ctx, SMC_E_INVALID, "q8act_create: bad arguments");
+    cudaSetDevice(ctx->device);
+    return smc_q8act_alloc(ctx, max_rows, max_k, out);
+}
+
+int smc_q8act_destroy(smc_ctx *ctx, smc_q8act *a)
+{
+    if (!ctx || !a) return smc_fail(ctx, SMC_E_INVALID, "q8act_destroy: bad arguments");
+    smc_q8act_free(a);
+    return SMC_OK;
+}
+
+int smc_quantize_q8_dev(smc_ctx *ctx, const float *d_x, int M, int K, smc_q8act *a, void *stream)
+{
+    if (!ctx || !d_x || !a || M <= 0 || K <= 0) return smc_fail(ctx, SMC_E_INVALID, "quantize_q8: bad arguments");
+    return smc_launch_quantize_q8(ctx, d_x, M, K, a, static_cast<cudaStream_t>(stream));
+}
+
+int smc_q8act_read(smc_ctx *ctx, const smc_q8act *a, int8_t *q, uint16_t *d_bits)
+{
+    if (!ctx || !a || a->M <= 0) return smc_fail(ctx, SMC_E_INVALID, "q8act_read: buffer holds no rows");
+    SMC_CUDA(ctx, cudaDeviceSynchronize());
+    size_t n = (size_t)a->M * a->K;
+    if (q) SMC_CUDA(ctx, cudaMemcpy(q, a->q, n, cudaMemcpyDeviceToHost));
+    if (d_bits) SMC_CUDA(ctx, cudaMemcpy(d_bits, a->dbits, n / 32 * sizeof(uint16_t), cudaMemcpyDeviceToHost));
+    return SMC_OK;
+}
+
+int smc_qmatmul_q8_dev(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *d_out, void *stream)
+{
+    if (!ctx || !a || !w || !d_out) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_q8: bad arguments");
+    if (a->K != w->K) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_q8: activations have K=%d, weight has K=%d", a->K, w->K);
+    if (!w->fast)
+        return smc_fail(ctx, SMC_E_UNSUPPORTED,
+                        "quantised-activation matmul needs a weight registered with SMC_W_REPACK and K %% %d == 0",
+                        w->dtype == SMC_Q8_0 ? 32 : 256);
+    return smc_launch_gemv_q8(ctx, a, w, d_out, static_cast<cudaStream_t>(stream));
+}
+
+static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, int mode,
+                        cudaStream_t s, bool have_lock)
+{
+    switch (mode) {
+    case SMC_REF_ORDER: return smc_launch_gemv_ref(ctx, d_in, w, d_out, M, 0, w->N, s);
+    case SMC_ACT_F32:
+        if (w->fast && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) return smc_launch_gemv_f32(ctx, d_in, w, d_out, M, s);
+        // shapes the vector kernels do not take (ragged K, rows that start inside a block) run in the
+        // reference's own order instead
+        return smc_launch_gemv_ref(ctx, d_in, w, d_out, M, 0, w->N, s);
+    case SMC_ACT_Q8: {
+        if (!w->fast)
+            return smc_fail(ctx, SMC_E_UNSUPPORTED,
+                            "SMC_ACT_Q8 needs a weight registered with SMC_W_REPACK and K %% %d == 0",
+                            w->dtype == SMC_Q8_0 ? 32 : 256);
+        {
+            std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
+            if (!have_lock) lock.lock();
+            if (!ctx->act || ctx->act->max_rows < M || ctx->act->max_k < w->K) {
+                // growing the scratch allocates: make the first call of a new size outside stream capture
+                int rows = ctx->act ? (ctx->act->max_rows > M ? ctx->act->max_rows : M) : (M > 32 ? M : 32);
+                int k = ctx->act ? (ctx->act->max_k > w->K ? ctx->act->max_k : w->K) : w->K;
+                if (ctx->act) {
+                    cudaDeviceSynchronize();
+                    smc_q8act_free(ctx->act);
+                    ctx->act = nullptr;
+                }
+                int rc = smc_q8act_alloc(ctx, rows, k, &ctx->act);
+                if (rc) return rc;
+            }
+        }
+        int rc = smc_launch_quantize_q8(ctx, d_in, M, w->K, ctx->act, s);
+        if (rc) return rc;
+        return smc_launch_gemv_q8(ctx, ctx->act, w, d_out, s);
+    }
+    default: return smc_fail(ctx, SMC_E_INVALID, "qmatmul: unknown mode %d", mode);
+    }
+}
+
+int smc_qmatmul_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, int mode, void *stream)
+{
+    if (!ctx || !d_in || !w || !d_out || M < 0) return smc_fail(ctx, SMC_E_INVALID, "qmatmul: bad arguments");
+    if (M == 0) return SMC_OK;
+    return qmatmul_impl(ctx, d_in, w, d_out, M, mode, static_cast<cudaStream_t>(stream), false);
+}
+
+int smc_block_isums_dev(smc_ctx *ctx, const smc_q8act *a, int m, const smc_weight *w, int col0, int col1,
+                        int32_t *d_sums, void *stream)
+{
+    if (!ctx || !a || !w || !d_sums || m < 0 || m >= a->M || col0 < 0 || col1 > w->N || col0 > col1 || a->K != w->K)
+        return smc_fail(ctx, SMC_E_INVALID, "block_isums: bad arguments");
+    if ((w->dtype == SMC_Q8_0 && w->K % 32) || (w->dtype != SMC_Q8_0 && w->K % 256))
+        return smc_fail(ctx, SMC_E_UNSUPPORTED, "block_isums: K must be a whole number of blocks");
+    return smc_launch_block_isums(ctx, a, m, w, col0, col1, d_sums, static_cast<cudaStream_t>(stream));
+}
+
+int smc_quantize_weights_dev(smc_ctx *ctx, int dtype, const float *d_values, int64_t n, void *d_raw, void *stream)
+{
+    if (!ctx || !d_values || !d_raw) return smc_fail(ctx, SMC_E_INVALID, "quantize_weights: bad arguments");
+    return smc_launch_quantize_weights(ctx, dtype, d_values, n, d_raw, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------------------------------ host slots
+int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, float *output, int M, int K, int N,
+                     int dtype, int mode)
+{
+    if (!ctx || !input || !host_raw || !output || M < 0 || K <= 0 || N <= 0)
+        return smc_fail(ctx, SMC_E_INVALID, "qmatmul_host: bad arguments");
+    smc_weight *w = nullptr;
+    int rc = smc_weight_lookup(ctx, host_raw, &w);
+    if (rc) return rc;
+    if (w->dtype != dtype || w->K != K || w->N != N)
+        return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "qmatmul_host: weight was registered as dtype=%d N=%d K=%d, call says dtype=%d N=%d K=%d",
+                        w->dtype, w->N, w->K, dtype, N, K);
+    if (M == 0) return SMC_OK;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    size_t in_bytes = (size_t)M * K * sizeof(float), out_bytes = (size_t)M * N * sizeof(float);
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_in, &ctx->stage_in_cap, in_bytes))) return rc;
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, out_bytes))) return rc;
+    if ((rc = h2d(ctx, ctx->d_stage_in, input, in_bytes))) return rc;
+    if ((rc = qmatmul_impl(ctx, ctx->d_stage_in, w, ctx->d_stage_out, M, mode, ctx->stream, true))) return rc;
+    return d2h(ctx, output, ctx->d_stage_out, out_bytes);
+}
+
+int smc_vecdot_host(smc_ctx *ctx, const float *input, const void *host_raw, int col, int K, int dtype, float *result)
+{
+    if (!ctx || !input || !host_raw || !result || K <= 0) return smc_fail(ctx, SMC_E_INVALID, "vecdot_host: bad arguments");
+    smc_weight *w = nullptr;
+    int rc = smc_weight_lookup(ctx, host_raw, &w);
+    if (rc) return rc;
+    if (w->dtype != dtype || w->K != K)
+        return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "vecdot_host: weight was registered as dtype=%d K=%d", w->dtype, w->K);
+    if (col < 0 || col >= w->N) return smc_fail(ctx, SMC_E_RANGE, "vecdot_host: col %d outside [0, %d)", col, w->N);
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_in, &ctx->stage_in_cap, (size_t)K * sizeof(float)))) return rc;
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, (size_t)w->N * sizeof(float)))) return rc;
+    if ((rc = h2d(ctx, ctx->d_stage_in, input, (size_t)K * sizeof(float)))) return rc;
+    // a single dot runs in the scalar tier's order: it is what the reference's vec-dot tests pin
+    if ((rc = smc_launch_gemv_ref(ctx, ctx->d_stage_in, w, ctx->d_stage_out, 1, col, col + 1, ctx->stream))) return rc;
+    return d2h(ctx, result, ctx->d_stage_out + col, sizeof(float));
+}
+
+static int unary_host(smc_ctx *ctx, const float *a, const float *b, float *dst, int n, int op, float scalar)
+{
+    if (!ctx || !a || !dst || n < 0) return smc_fail(ctx, SMC_E_INVALID, "bad arguments");
+    if (n == 0) return SMC_OK;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    size_t bytes = (size_t)n * sizeof(float);
+    int rc;
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_in, &ctx->stage_in_cap, bytes))) return rc;
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, bytes))) return rc;
+    if ((rc = h2d(ctx, ctx->d_stage_in, a, bytes))) return rc;
+    if (b) {
+        if ((rc = ensure_dev(ctx, &ctx->d_stage_aux, &ctx->stage_aux_cap, bytes))) return rc;
+        if ((rc = h2d(ctx, ctx->d_stage_aux, b, bytes))) return rc;
+    }
+    switch (op) {
+    case 0: rc = smc_swiglu_dev(ctx, ctx->d_stage_in, ctx->d_stage_aux, ctx->d_stage_out, 1, n, n, ctx->stream); break;
+    case 1: rc = smc_silu_dev(ctx, ctx->d_stage_in, ctx->d_stage_out, n, ctx->stream); break;
+    case 2: rc = smc_softmax_dev(ctx, ctx->d_stage_in, ctx->d_stage_out, 1, n, ctx->stream); break;
+    default: rc = smc_launch_rmsnorm_row(ctx, ctx->d_stage_in, ctx->d_stage_aux, ctx->d_stage_out, n, scalar, ctx->stream); break;
+    }
+    if (rc) return rc;
+    return d2h(ctx, dst, ctx->d_stage_out, bytes);
+}
+
+int smc_swiglu_host(smc_ctx *ctx, const float *gate, const float *up, float *dst, int n)
+{
+    if (!up) return smc_fail(ctx, SMC_E_INVALID, "swiglu_host: bad arguments");
+    return unary_host(ctx, gate, up, dst, n, 0, 0.f);
+}
+int smc_silu_host(smc_ctx *ctx, const float *src, float *dst, int n) { return unary_host(ctx, src, nullptr, dst, n, 1, 0.f); }
+int smc_softmax_row_host(smc_ctx *ctx, const float *src, float *dst, int n)
+{
+    if (n == 0) return smc_fail(ctx, SMC_E_INVALID, "softmax_row_host: empty row");
+    return unary_host(ctx, src, nullptr, dst, n, 2, 0.f);
+}
+int smc_rmsnorm_row_host(smc_ctx *ctx, const float *src, const float *weight, float *dst, int n, float rms_inv)
+{
+    if (!weight) return smc_fail(ctx, SMC_E_INVALID, "rmsnorm_row_host: bad arguments");
+    return unary_host(ctx, src, weight, dst, n, 3, rms_inv);
+}
+
+int smc_sdpa_host(smc_ctx *ctx, const float *q, const float *k, const float *v, float *o, int seqLen, int kvLen,
+                  int headDim, float scale, int causal, int qStride, int oStride, float alibiSlope)
+{
+    if (!ctx || !q || !k || !v || !o || seqLen < 0 || kvLen < 0 || headDim <= 0 || qStride < headDim || oStride < headDim)
+        return smc_fail(ctx, SMC_E_INVALID, "sdpa_host: bad arguments");
+    if (headDim > 256)  // AttentionKernels.cs:225-227 throws ArgumentOutOfRangeException
+        return smc_fail(ctx, SMC_E_RANGE, "headDim %d exceeds FlashMaxHeadDim 256", headDim);
+    if (seqLen == 0) return SMC_OK;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    size_t qn = (size_t)(seqLen - 1) * qStride + headDim, on = (size_t)(seqLen - 1) * oStride + headDim;
+    size_t kvn = (size_t)kvLen * headDim;
+    int rc;
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_in, &ctx->stage_in_cap, qn * sizeof(float)))) return rc;
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, on * sizeof(float)))) return rc;
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_aux, &ctx->stage_aux_cap, (2 * kvn + 4) * sizeof(float)))) return rc;
+    if ((rc = h2d(ctx, ctx->d_stage_in, q, qn * sizeof(float)))) return rc;
+    if (kvn) {
+        if ((rc = h2d(ctx, ctx->d_stage_aux, k, kvn * sizeof(float)))) return rc;
+        if ((rc = h2d(ctx, ctx->d_stage_aux + kvn, v, kvn * sizeof(float)))) return rc;
+    }
+    // rows of o between the headDim-wide outputs belong to the caller: fetch, overwrite, return
+    if (oStride != headDim)
+        if ((rc = h2d(ctx, ctx->d_stage_out, o, on * sizeof(float)))) return rc;
+    if ((rc = smc_launch_sdpa_tile(ctx, ctx->d_stage_in, ctx->d_stage_aux, ctx->d_stage_aux + kvn, ctx->d_stage_out,
+                                   seqLen, kvLen, headDim, scale, causal, qStride, oStride, alibiSlope, ctx->stream)))
+        return rc;
+    return d2h(ctx, o, ctx->d_stage_out, on * sizeof(float));
+}
+
+}  // extern "C"

@@ -1,0 +1,319 @@
+// fp32 attention over an fp32 KV cache.
+//
+//  * sdpa_decode_split_kernel + sdpa_merge_kernel: one query token per sequence (decode).  The cache
+//    sweep is the only traffic that matters (2 * kvLen * headDim * 4 bytes per KV head), so the
+//    key range is split across CTAs to fill the GPU at batch 1, the query heads that share a KV
+//    head are processed together (K and V are read once per group), and eight lanes share a key so
+//    that every load is a coalesced 128-bit access.  Each eight-lane group keeps its own online-
+//    softmax state; states are merged in shared memory per CTA and across CTAs by the merge kernel.
+//  * sdpa_tile_kernel: any seqLen / kvLen / headDim <= 256 / strides / causal / ALiBi, written in the
+//    reference's own order (tiles of 64 keys, sequential fp32 dot, running max and sum), used by the
+//    host-pointer `attention` slot and for head sizes the split kernel does not take.
+//
+// References: ScaledDotProductFlash{Scalar,FMA} SharpMind.Model/Layers/Attention/AttentionKernels.cs:315-475,
+// AttentionLayer.Forward's per-(batch, head) loop AttentionLayer.cs:326-413, KVCache layout and Update
+// SharpMind.Model/KVCache.cs:13-36,84-150.
+#include <math.h>
+
+#include "smc_common.cuh"
+
+namespace {
+
+constexpr int LPK = 8;          // lanes per key
+constexpr int MAXG = 8;         // query heads per KV head handled by one CTA pass
+constexpr int SPLIT_THREADS = 128;
+
+// partial record per (batch, head, split): [m, l, o[headDim]]
+template <int DPL, int G>  // DPL = dims per lane = headDim / 8, G = query heads per KV head
+__global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
+    const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc, float *__restrict__ part,
+    int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits)
+{
+    constexpr int HD = DPL * LPK;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int grp = lane / LPK, sub = lane % LPK;        // 4 key groups per warp
+    const int ngroups = (SPLIT_THREADS / 32) * (32 / LPK);
+    const int gid = warp * (32 / LPK) + grp;
+
+    const int chunk = (kvLen + splits - 1) / splits;
+    const int k0 = split * chunk, k1 = min(kvLen, k0 + chunk);
+
+    const float *kbase = kc + ((size_t)b * kvHeads + kvh) * (size_t)maxSeq * HD;
+    const float *vbase = vc + ((size_t)b * kvHeads + kvh) * (size_t)maxSeq * HD;
+
+    float qr[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float *qp = q + ((size_t)b * heads + (size_t)kvh * G + g) * HD + sub * DPL;
+#pragma unroll
+        for (int d = 0; d < DPL; d += 4) {
+            float4 t = *reinterpret_cast<const float4 *>(qp + d);
+            qr[g][d] = t.x, qr[g][d + 1] = t.y, qr[g][d + 2] = t.z, qr[g][d + 3] = t.w;
+        }
+    }
+    float m[G], l[G], o[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) o[g][d] = 0.f;
+    }
+
+    // every lane group runs the same number of iterations so the shuffles below stay converged
+    const int iters = k1 > k0 ? (k1 - k0 + ngroups - 1) / ngroups : 0;
+    for (int it = 0; it < iters; ++it) {
+        const int j = k0 + it * ngroups + gid;
+        const bool live = j < k1;
+        const int jj = live ? j : k0;
+        float kr[DPL], vr[DPL];
+#pragma unroll
+        for (int d = 0; d < DPL; d += 4) {
+            float4 t = smc_ldg_stream16f(kbase + (size_t)jj * HD + sub * DPL + d);
+            kr[d] = t.x, kr[d + 1] = t.y, kr[d + 2] = t.z, kr[d + 3] = t.w;
+            float4 u = smc_ldg_stream16f(vbase + (size_t)jj * HD + sub * DPL + d);
+            vr[d] = u.x, vr[d + 1] = u.y, vr[d + 2] = u.z, vr[d + 3] = u.w;
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float dot = 0.f;
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) dot = fmaf(qr[g][d], kr[d], dot);
+            dot = smc_group_sum<LPK>(dot);
+            if (live) {
+                float s = dot * scale;
+                float mn = fmaxf(m[g], s);
+                float alpha = expf(m[g] - mn);  // exp(-inf) = 0 on the first key
+                float p = expf(s - mn);
+                l[g] = fmaf(l[g], alpha, p);
+#pragma unroll
+                for (int d = 0; d < DPL; ++d) o[g][d] = fmaf(p, vr[d], o[g][d] * alpha);
+                m[g] = mn;
+            }
+        }
+    }
+
+    // merge the lane groups of the CTA: shared memory holds (m, l) per group and o per group
+    extern __shared__ float sm[];
+    float *sm_m = sm;                                   // [ngroups][G]
+    float *sm_l = sm_m + ngroups * G;                   // [ngroups][G]
+    float *sm_o = sm_l + ngroups * G;                   // [ngroups][G][HD]
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (sub == 0) sm_m[gid * G + g] = m[g], sm_l[gid * G + g] = l[g];
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) sm_o[((size_t)gid * G + g) * HD + sub * DPL + d] = o[g][d];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += SPLIT_THREADS) {
+        int g = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+        for (int r = 0; r < ngroups; ++r) M = fmaxf(M, sm_m[r * G + g]);
+        float L = 0.f, O = 0.f;
+        for (int r = 0; r < ngroups; ++r) {
+            float mr = sm_m[r * G + g];
+            float w = (mr == -INFINITY) ? 0.f : expf(mr - M);
+            L = fmaf(sm_l[r * G + g], w, L);
+            O = fmaf(sm_o[((size_t)r * G + g) * HD + d], w, O);
+        }
+        float *rec = part + (((size_t)b * heads + (size_t)kvh * G + g) * splits + split) * (HD + 2);
+        if (d == 0) rec[0] = M, rec[1] = L;
+        rec[2 + d] = O;
+    }
+}
+
+__global__ void __launch_bounds__(256) sdpa_merge_kernel(const float *__restrict__ part, float *__restrict__ out,
+                                                         int hd, int splits)
+{
+    // grid.x = batch * heads
+    const float *rec = part + (size_t)blockIdx.x * splits * (hd + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, rec[(size_t)s * (hd + 2)]);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float L = 0.f, O = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float *r = rec + (size_t)s * (hd + 2);
+            float w = (r[0] == -INFINITY) ? 0.f : expf(r[0] - M);
+            L = fmaf(r[1], w, L);
+            O = fmaf(r[2 + d], w, O);
+        }
+        out[(size_t)blockIdx.x * hd + d] = L > 0.f ? __fdiv_rn(O, L) : 0.f;
+    }
+}
+
+// Reference-order attention: one CTA per query row, 256 threads, tiles of 64 keys.
+__global__ void __launch_bounds__(256) sdpa_tile_kernel(const float *__restrict__ q, const float *__restrict__ k,
+                                                        const float *__restrict__ v, float *__restrict__ out, int seqLen,
+                                                        int kvLen, int hd, float scale, int causal, int qStride,
+                                                        int oStride, float alibi)
+{
+    __shared__ float tile[64];
+    __shared__ float sq[256];
+    __shared__ float stat[4];  // newMax, scaleOld, newL
+    const int i = blockIdx.x, t = threadIdx.x;
+    const float *qi = q + (size_t)i * qStride;
+    const int queryBase = causal ? kvLen - seqLen : 0;
+    const int absQ = queryBase + i;
+    const int eff = causal ? min(absQ + 1, kvLen) : kvLen;
+    if (t < hd) sq[t] = qi[t];
+    float o = 0.f;
+    float mMax = -INFINITY, lSum = 0.f;  // kept identically by every thread
+    __syncthreads();
+    for (int start = 0; start < eff; start += 64) {
+        const int len = min(64, eff - start);
+        if (t < len) {
+            const float *kj = k + (size_t)(start + t) * hd;
+            float dot = 0.f;
+            for (int d = 0; d < hd; ++d) dot = __fadd_rn(dot, __fmul_rn(sq[d], kj[d]));
+            dot = __fsub_rn(__fmul_rn(dot, scale), __fmul_rn(alibi, (float)(absQ - (start + t))));
+            tile[t] = dot;
+        }
+        __syncthreads();
+        if (t == 0) {
+            float tmax = -INFINITY;
+            for (int j = 0; j < len; ++j) tmax = fmaxf(tmax, tile[j]);
+            float newMax = fmaxf(mMax, tmax);
+            float scaleOld = expf(mMax - newMax);
+            float scaleNew = 0.f;
+            for (int j = 0; j < len; ++j) {
+                tile[j] = expf(tile[j] - newMax);
+                scaleNew = __fadd_rn(scaleNew, tile[j]);
+            }
+            stat[0] = newMax;
+            stat[1] = scaleOld;
+            stat[2] = __fadd_rn(__fmul_rn(scaleOld, lSum), scaleNew);
+        }
+        __syncthreads();
+        mMax = stat[0];
+        lSum = stat[2];
+        if (t < hd) {
+            o = __fmul_rn(o, stat[1]);
+            for (int j = 0; j < len; ++j) o = __fadd_rn(o, __fmul_rn(tile[j], v[(size_t)(start + j) * hd + t]));
+        }
+        __syncthreads();
+    }
+    if (t < hd) out[(size_t)i * oStride + t] = lSum > 0.f ? __fdiv_rn(o, lSum) : 0.f;
+}
+
+__global__ void kv_append_kernel(const float *__restrict__ k, const float *__restrict__ v, float *__restrict__ kc,
+                                 float *__restrict__ vc, int batch, int kvHeads, int hd, int pos, int maxSeq)
+{
+    long long total = (long long)batch * kvHeads * hd;
+    long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= total) return;
+    int d = (int)(t % hd);
+    long long bh = t / hd;  // b * kvHeads + h
+    size_t dst = ((size_t)bh * maxSeq + pos) * hd + d;
+    kc[dst] = k[t];
+    vc[dst] = v[t];
+}
+
+template <int DPL>
+int launch_split_g(smc_ctx *ctx, int G, dim3 grid, size_t smem, cudaStream_t s, const float *q, const float *k,
+                   const float *v, float *part, int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits)
+{
+#define SMC_SPLIT_CASE(GV)                                                                                         \
+    case GV:                                                                                                       \
+        if (smem > 48 * 1024)                                                                                      \
+            cudaFuncSetAttribute(sdpa_decode_split_kernel<DPL, GV>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                 (int)smem);                                                                       \
+        sdpa_decode_split_kernel<DPL, GV><<<grid, SPLIT_THREADS, smem, s>>>(q, k, v, part, heads, kvHeads, kvLen,  \
+                                                                            maxSeq, scale, splits);                \
+        break;
+    switch (G) {
+        SMC_SPLIT_CASE(1)
+        SMC_SPLIT_CASE(2)
+        SMC_SPLIT_CASE(4)
+    default: return smc_fail(ctx, SMC_E_UNSUPPORTED, "sdpa_decode: %d query heads per KV head", G);
+    }
+#undef SMC_SPLIT_CASE
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+}  // namespace
+
+int smc_launch_sdpa_tile(smc_ctx *ctx, const float *q, const float *k, const float *v, float *o, int seqLen, int kvLen,
+                         int hd, float scale, int causal, int qStride, int oStride, float alibi, cudaStream_t s)
+{
+    sdpa_tile_kernel<<<seqLen, 256, 0, s>>>(q, k, v, o, seqLen, kvLen, hd, scale, causal, qStride, oStride, alibi);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+extern "C" {
+
+int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const float *d_v, float *d_out, int batch,
+                        int heads, int kvHeads, int headDim, int kvLen, int maxSeq, float scale, void *stream)
+{
+    if (!ctx || !d_q || !d_k || !d_v || !d_out || batch < 0 || heads <= 0 || kvHeads <= 0 || heads % kvHeads ||
+        headDim <= 0 || kvLen <= 0 || kvLen > maxSeq)
+        return smc_fail(ctx, SMC_E_INVALID, "sdpa_decode: bad arguments");
+    if (headDim > 256) return smc_fail(ctx, SMC_E_RANGE, "sdpa_decode: headDim %d exceeds 256", headDim);
+    if (batch == 0) return SMC_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int G = heads / kvHeads;
+    const bool split_ok = (headDim == 64 || headDim == 128) && (G == 1 || G == 2 || G == 4) &&
+                          ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_k) |
+                            reinterpret_cast<uintptr_t>(d_v)) & 15) == 0;
+    if (!split_ok) {
+        // reference-order kernel, one launch per (batch, head) group is avoided by treating each
+        // (batch, head) as its own single-query problem through grid.y
+        for (int b = 0; b < batch; ++b)
+            for (int h = 0; h < heads; ++h) {
+                const float *kp = d_k + ((size_t)b * kvHeads + h / G) * (size_t)maxSeq * headDim;
+                const float *vp = d_v + ((size_t)b * kvHeads + h / G) * (size_t)maxSeq * headDim;
+                int rc = smc_launch_sdpa_tile(ctx, d_q + ((size_t)b * heads + h) * headDim, kp, vp,
+                                              d_out + ((size_t)b * heads + h) * headDim, 1, kvLen, headDim, scale, 1,
+                                              headDim, headDim, 0.f, s);
+                if (rc) return rc;
+            }
+        return SMC_OK;
+    }
+    int pairs = batch * kvHeads;
+    int splits = (2 * ctx->sm_count + pairs - 1) / pairs;
+    int max_splits = (kvLen + 63) / 64;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    size_t need = (size_t)batch * heads * splits * (headDim + 2) * sizeof(float);
+    if (need > ctx->attn_part_cap) {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (ctx->d_attn_part) cudaFree(ctx->d_attn_part);
+        ctx->d_attn_part = nullptr;
+        ctx->attn_part_cap = 0;
+        SMC_CUDA(ctx, cudaMalloc(&ctx->d_attn_part, need));
+        ctx->attn_part_cap = need;
+    }
+    const int ngroups = (SPLIT_THREADS / 32) * (32 / LPK);
+    size_t smem = ((size_t)ngroups * G * 2 + (size_t)ngroups * G * headDim) * sizeof(float);
+    dim3 grid(splits, kvHeads, batch);
+    int rc;
+    if (headDim == 128)
+        rc = launch_split_g<16>(ctx, G, grid, smem, s, d_q, d_k, d_v, ctx->d_attn_part, heads, kvHeads, kvLen, maxSeq,
+                                scale, splits);
+    else
+        rc = launch_split_g<8>(ctx, G, grid, smem, s, d_q, d_k, d_v, ctx->d_attn_part, heads, kvHeads, kvLen, maxSeq,
+                               scale, splits);
+    if (rc) return rc;
+    sdpa_merge_kernel<<<batch * heads, headDim <= 128 ? 128 : 256, 0, s>>>(ctx->d_attn_part, d_out, headDim, splits);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+int smc_kv_append_dev(smc_ctx *ctx, const float *d_k, const float *d_v, float *d_kcache, float *d_vcache, int batch,
+                      int kvHeads, int headDim, int pos, int maxSeq, void *stream)
+{
+    if (!ctx || !d_k || !d_v || !d_kcache || !d_vcache || batch < 0 || kvHeads <= 0 || headDim <= 0)
+        return smc_fail(ctx, SMC_E_INVALID, "kv_append: bad arguments");
+    if (pos < 0 || pos >= maxSeq)  // KVCache.Update throws on overflow (KVCache.cs:89-91)
+        return smc_fail(ctx, SMC_E_RANGE, "KVCache overflow: position %d + seqLen 1 exceeds capacity %d", pos, maxSeq);
+    long long total = (long long)batch * kvHeads * headDim;
+    if (total == 0) return SMC_OK;
+    kv_append_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        d_k, d_v, d_kcache, d_vcache, batch, kvHeads, headDim, pos, maxSeq);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+}  // extern "C"

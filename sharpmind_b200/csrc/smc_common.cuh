@@ -1,0 +1,189 @@
+// Shared declarations of the CUDA backend: context / weight / activation-buffer objects and the
+// small device helpers every kernel file uses.  Built for sm_100a only, with -fmad=false: every
+// fused multiply-add in this library is written explicitly (fmaf), so that code restating the
+// reference's unfused arithmetic keeps its roundings.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "../../include/sharpmind_cuda.h"
+
+#define SMC_QK 32
+#define SMC_QK_K 256
+
+struct smc_weight {
+    int dtype = 0, N = 0, K = 0, flags = 0;
+    size_t raw_bytes = 0;
+    const void *host_key = nullptr;
+    uint8_t *d_raw = nullptr;  // GGUF layout (compute layout for Q4_K)
+    bool fast = false;         // shape and layout allow the vectorised kernels
+    // Q8_0 planes: quants [N][K] int8 and scales [N][K/32] fp16
+    int8_t *q8_qs = nullptr;
+    __half *q8_d = nullptr;
+    // Q6_K planes, one entry per 256-element block in flat-tensor order
+    uint8_t *q6_ql = nullptr;  // [nblk][128]
+    uint8_t *q6_qh = nullptr;  // [nblk][64]
+    int8_t *q6_sc = nullptr;   // [nblk][16]
+    __half *q6_d = nullptr;    // [nblk]
+};
+
+// Q8_0-quantised activations in structure-of-arrays form.
+struct smc_q8act {
+    int max_rows = 0, max_k = 0;
+    int M = 0, K = 0;          // shape of the rows currently held
+    int8_t *q = nullptr;       // [M][K]
+    float *d = nullptr;        // [M][K/32]  fp16-rounded block scale widened to fp32
+    uint16_t *dbits = nullptr; // [M][K/32]  the fp16 bit pattern itself
+    float *sd = nullptr;       // [M][K/32]  d * sum(q) over the block (Q4_K's min term)
+    int16_t *s16 = nullptr;    // [M][K/16]  sum(q) over each half block (Q6_K's -32 offset)
+};
+
+struct smc_ctx {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;  // used by the host-pointer entry points
+    std::mutex mu;
+    std::string last_error;
+    std::unordered_map<const void *, smc_weight *> by_host;
+    // staging for host-pointer calls (grown on demand)
+    float *d_stage_in = nullptr, *d_stage_out = nullptr, *d_stage_aux = nullptr;
+    size_t stage_in_cap = 0, stage_out_cap = 0, stage_aux_cap = 0;
+    void *h_pin = nullptr;
+    size_t h_pin_cap = 0;
+    // scratch owned by the context
+    smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
+    float *d_attn_part = nullptr;      // split-KV partial results
+    size_t attn_part_cap = 0;
+};
+
+int smc_fail(smc_ctx *ctx, int code, const char *fmt, ...);
+
+#define SMC_CUDA(ctx, call)                                                                     \
+    do {                                                                                        \
+        cudaError_t e_ = (call);                                                                \
+        if (e_ != cudaSuccess)                                                                  \
+            return smc_fail((ctx), SMC_E_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+#define SMC_LAUNCH_CHECK(ctx)                                                                            \
+    do {                                                                                                 \
+        cudaError_t e_ = cudaGetLastError();                                                             \
+        if (e_ != cudaSuccess)                                                                           \
+            return smc_fail((ctx), SMC_E_CUDA, "kernel launch failed: %s (%s:%d)", cudaGetErrorString(e_), \
+                            __FILE__, __LINE__);                                                         \
+    } while (0)
+
+// ---- launchers implemented across the .cu files (all asynchronous on `s`) ----
+int smc_launch_gemv_f32(smc_ctx *, const float *x, const smc_weight *, float *out, int M, cudaStream_t s);
+int smc_launch_gemv_q8(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
+int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,
+                        cudaStream_t s);
+int smc_launch_quantize_q8(smc_ctx *, const float *x, int M, int K, smc_q8act *, cudaStream_t s);
+int smc_launch_block_isums(smc_ctx *, const smc_q8act *, int m, const smc_weight *, int col0, int col1,
+                           int32_t *sums, cudaStream_t s);
+int smc_launch_quantize_weights(smc_ctx *, int dtype, const float *v, int64_t n, void *raw, cudaStream_t s);
+int smc_launch_repack(smc_ctx *, smc_weight *, cudaStream_t s);
+int smc_launch_sdpa_tile(smc_ctx *, const float *q, const float *k, const float *v, float *o, int seqLen, int kvLen,
+                         int hd, float scale, int causal, int qStride, int oStride, float alibi, cudaStream_t s);
+int smc_launch_rmsnorm_row(smc_ctx *, const float *src, const float *w, float *dst, int n, float rms_inv,
+                           cudaStream_t s);
+int smc_q8act_alloc(smc_ctx *, int max_rows, int max_k, smc_q8act **out);
+void smc_q8act_free(smc_q8act *);
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float smc_h2f(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
+
+// 16-byte streaming load: weights are read once, keep them out of L1.
+__device__ __forceinline__ uint4 smc_ldg_stream16(const void *p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float4 smc_ldg_stream16f(const float *p)
+{
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 smc_ldg_stream8(const void *p)
+{
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t smc_ldg_stream4(const void *p)
+{
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint16_t smc_ldg_stream2(const void *p)
+{
+    uint16_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ int smc_dp4a(uint32_t a, uint32_t b, int c)
+{
+    return __dp4a((int)a, (int)b, c);  // signed x signed bytes
+}
+__device__ __forceinline__ int smc_dp4a_us(uint32_t a_unsigned, uint32_t b_signed, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_unsigned), "r"(b_signed), "r"(c));
+    return d;
+}
+
+// Byte j (0..3) of w as an exact float, through the 2^23 mantissa trick: one PRMT and one FADD,
+// both full-rate, instead of a quarter-rate integer-to-float conversion.
+__device__ __forceinline__ float smc_ubyte_to_float(uint32_t w, int j)
+{
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | j)) - 8388608.0f;
+}
+
+template <int LANES>
+__device__ __forceinline__ float smc_group_sum(float v)
+{
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float smc_group_sum_rt(float v, int lanes)
+{
+    for (int o = lanes / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Q4_K / Q5_K 6-bit scale and min of sub-block j (0..7) from the 12 packed bytes held as three
+// little-endian words (GetScaleMinK4_*, QuantizationKernels.cs:177-189).
+__device__ __forceinline__ void smc_k4_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, int &sc, int &mn)
+{
+    // bytes 0..3 = s0, 4..7 = s1, 8..11 = s2
+    if (j < 4) {
+        sc = (s0 >> (8 * j)) & 0x3F;
+        mn = (s1 >> (8 * j)) & 0x3F;
+    } else {
+        int jj = j - 4;
+        uint32_t b8 = (s2 >> (8 * jj)) & 0xFF;   // scales[j + 4]
+        uint32_t lo = (s0 >> (8 * jj)) & 0xFF;   // scales[j - 4]
+        uint32_t mid = (s1 >> (8 * jj)) & 0xFF;  // scales[j]
+        sc = (b8 & 0x0F) | ((lo >> 6) << 4);
+        mn = (b8 >> 4) | ((mid >> 6) << 4);
+    }
+}
+#endif  // __CUDACC__

@@ -1,0 +1,324 @@
+// Quantisers and layout kernels:
+//   * run-time Q8_0 activation quantiser (QuantizedKVCache.QuantizeRowQ8_0,
+//     SharpMind.Model/QuantizedKVCache.cs:191-223) writing the structure-of-arrays form the
+//     integer GEMV kernels read;
+//   * weight quantisers, bit-exact device forms of TensorQuantizer.WriteBlock (Q8_0,
+//     SharpMind.Core/Quantization/TensorQuantizer.cs:80-144), WriteKQ4 and WriteKQ6
+//     (TensorQuantizer.KQuant.cs:173-225, 303-376) -- they make the synthetic weights;
+//   * the upload-time repack of Q8_0 and Q6_K tensors into 16-byte-aligned planes.
+// All arithmetic that decides a code or a scale uses explicit round-to-nearest intrinsics.
+#include "smc_common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------------------- activations -> Q8_0
+// One warp per 32-element block; x [M][K], K % 32 == 0.
+__global__ void __launch_bounds__(256) quantize_q8_kernel(const float *__restrict__ x, int8_t *__restrict__ q,
+                                                          float *__restrict__ d, uint16_t *__restrict__ dbits,
+                                                          float *__restrict__ sd, int16_t *__restrict__ s16,
+                                                          long long nblocks)
+{
+    const int lane = threadIdx.x & 31;
+    long long blk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    for (; blk < nblocks; blk += stride) {
+        float v = x[blk * 32 + lane];
+        float amax = fabsf(v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        float scale = __fdiv_rn(amax, 127.0f);
+        if (amax == 0.0f) scale = 1.0f;
+        int qi = __float2int_rn(__fdiv_rn(v, scale));  // round half to even, like MathF.Round(x)
+        qi = max(-128, min(127, qi));
+        q[blk * 32 + lane] = (int8_t)qi;
+        int s = qi;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        int total = s + __shfl_xor_sync(0xffffffffu, s, 16);
+        if ((lane & 15) == 0) s16[blk * 2 + (lane >> 4)] = (int16_t)s;
+        if (lane == 0) {
+            __half h = __float2half_rn(scale);
+            float df = __half2float(h);
+            d[blk] = df;
+            dbits[blk] = __half_as_ushort(h);
+            sd[blk] = df * (float)total;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------- weights -> Q8_0
+__global__ void __launch_bounds__(256) wq_q8_0_kernel(const float *__restrict__ v, uint8_t *__restrict__ out,
+                                                      long long nblocks)
+{
+    const int lane = threadIdx.x & 31;
+    long long blk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    for (; blk < nblocks; blk += stride) {
+        float x = v[blk * 32 + lane];
+        float amax = fabsf(x);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        uint8_t *o = out + blk * 34;
+        if (amax == 0.0f) {
+            if (lane == 0) o[0] = 0, o[1] = 0;
+            o[2 + lane] = 0;
+            continue;
+        }
+        float d = __fdiv_rn(amax, 127.0f);
+        int qi = (int)roundf(__fdiv_rn(x, d));  // MidpointRounding.AwayFromZero
+        qi = max(-128, min(127, qi));
+        o[2 + lane] = (uint8_t)(int8_t)qi;
+        if (lane == 0) {
+            uint16_t hb = __half_as_ushort(__float2half_rn(d));
+            o[0] = (uint8_t)(hb & 0xFF);
+            o[1] = (uint8_t)(hb >> 8);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------- weights -> Q4_K
+// One warp per 256-element block.  Lane l owns elements 64g + l and 64g + 32 + l (g = 0..3), i.e.
+// both nibbles of byte qs[32g + l]; sub-block 2g holds the first, 2g + 1 the second.
+__global__ void __launch_bounds__(256) wq_q4_K_kernel(const float *__restrict__ v, uint8_t *__restrict__ out,
+                                                      long long nblocks)
+{
+    const int lane = threadIdx.x & 31;
+    long long blk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    for (; blk < nblocks; blk += stride) {
+        const float *p = v + blk * 256;
+        uint8_t *o = out + blk * 144;
+        float e[8];  // e[2g] = element 64g + l (sub-block 2g), e[2g+1] = 64g + 32 + l (sub-block 2g+1)
+        float amax = 0.f;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            e[2 * g] = p[64 * g + lane];
+            e[2 * g + 1] = p[64 * g + 32 + lane];
+            amax = fmaxf(amax, fmaxf(fabsf(e[2 * g]), fabsf(e[2 * g + 1])));
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+        if (amax == 0.0f) {
+            // all-zero block encodes as 144 zero bytes
+            for (int i = lane; i < 144; i += 32) o[i] = 0;
+            continue;
+        }
+        float step = __fdiv_rn(amax, 63.0f);
+        int sc[8], mn[8];
+        uint32_t code[8];
+#pragma unroll
+        for (int sb = 0; sb < 8; ++sb) {
+            float gmn = e[sb], gmx = e[sb];
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) {
+                gmn = fminf(gmn, __shfl_xor_sync(0xffffffffu, gmn, s));
+                gmx = fmaxf(gmx, __shfl_xor_sync(0xffffffffu, gmx, s));
+            }
+            float range = __fsub_rn(gmx, gmn);
+            mn[sb] = max(0, min(63, (int)roundf(__fdiv_rn(-gmn, step))));
+            if (range <= 0.0f) {
+                sc[sb] = 0;
+                code[sb] = 0;
+                continue;
+            }
+            sc[sb] = max(1, min(63, (int)roundf(__fdiv_rn(range, __fmul_rn(15.0f, step)))));
+            float scF = __fmul_rn((float)sc[sb], step);
+            float num = __fadd_rn(e[sb], __fmul_rn((float)mn[sb], step));
+            code[sb] = (uint32_t)max(0, min(15, (int)roundf(__fdiv_rn(num, scF))));
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) o[16 + 32 * g + lane] = (uint8_t)(code[2 * g] | (code[2 * g + 1] << 4));
+        if (lane == 0) {
+            uint16_t hb = __half_as_ushort(__float2half_rn(step));
+            o[0] = o[2] = (uint8_t)(hb & 0xFF);
+            o[1] = o[3] = (uint8_t)(hb >> 8);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                o[4 + j] = (uint8_t)((sc[j] & 0x3F) | ((sc[4 + j] >> 4) << 6));
+                o[8 + j] = (uint8_t)((mn[j] & 0x3F) | ((mn[4 + j] >> 4) << 6));
+                o[12 + j] = (uint8_t)((sc[4 + j] & 0x0F) | ((mn[4 + j] & 0x0F) << 4));
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------- weights -> Q6_K
+// One warp per block.  Lane l owns elements 128h + 32c + l (h = 0..1, c = 0..3): bytes ql[64h + l]
+// (c = 0 low, c = 2 high nibble), ql[64h + 32 + l] (c = 1 low, c = 3 high) and qh[32h + l].
+__global__ void __launch_bounds__(256) wq_q6_K_kernel(const float *__restrict__ v, uint8_t *__restrict__ out,
+                                                      long long nblocks)
+{
+    const int lane = threadIdx.x & 31;
+    long long blk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    for (; blk < nblocks; blk += stride) {
+        const float *p = v + blk * 256;
+        uint8_t *o = out + blk * 210;
+        float e[8];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            e[i] = p[32 * i + lane];  // i = 4h + c
+            amax = fmaxf(amax, fabsf(e[i]));
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+        if (amax == 0.0f) {
+            for (int i = lane; i < 210; i += 32) o[i] = 0;
+            continue;
+        }
+        float d = __fdiv_rn(amax, 4064.0f);
+        int code[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            // group = 16 consecutive elements = lanes (l & 16) .. +15 of column i
+            float gmx = fabsf(e[i]);
+#pragma unroll
+            for (int s = 8; s > 0; s >>= 1) gmx = fmaxf(gmx, __shfl_xor_sync(0xffffffffu, gmx, s));
+            int scale = gmx == 0.0f ? 0 : max(1, min(127, (int)roundf(__fdiv_rn(gmx, __fmul_rn(32.0f, d)))));
+            if ((lane & 15) == 0) o[192 + 2 * i + (lane >> 4)] = (uint8_t)(int8_t)scale;
+            float scf = __fmul_rn(d, (float)scale);
+            code[i] = gmx == 0.0f ? 32 : max(0, min(63, (int)roundf(__fdiv_rn(e[i], scf)) + 32));
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int *c = code + 4 * h;
+            o[64 * h + lane] = (uint8_t)((c[0] & 0x0F) | ((c[2] & 0x0F) << 4));
+            o[64 * h + 32 + lane] = (uint8_t)((c[1] & 0x0F) | ((c[3] & 0x0F) << 4));
+            o[128 + 32 * h + lane] =
+                (uint8_t)(((c[0] >> 4) & 3) | (((c[1] >> 4) & 3) << 2) | (((c[2] >> 4) & 3) << 4) | (((c[3] >> 4) & 3) << 6));
+        }
+        if (lane == 0) {
+            uint16_t hb = __half_as_ushort(__float2half_rn(d));
+            o[208] = (uint8_t)(hb & 0xFF);
+            o[209] = (uint8_t)(hb >> 8);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------- repack
+__global__ void repack_q8_0_kernel(const uint8_t *__restrict__ raw, int8_t *__restrict__ qs, __half *__restrict__ d,
+                                   long long nblocks)
+{
+    long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; t < nblocks * 32; t += stride) {
+        long long blk = t >> 5;
+        int i = (int)(t & 31);
+        const uint8_t *b = raw + blk * 34;
+        qs[t] = (int8_t)b[2 + i];
+        if (i == 0) d[blk] = __ushort_as_half((uint16_t)(b[0] | (b[1] << 8)));
+    }
+}
+
+__global__ void repack_q6_K_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ ql, uint8_t *__restrict__ qh,
+                                   int8_t *__restrict__ sc, __half *__restrict__ d, long long nblocks)
+{
+    long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; t < nblocks * 128; t += stride) {
+        long long blk = t >> 7;
+        int i = (int)(t & 127);
+        const uint8_t *b = raw + blk * 210;
+        ql[t] = b[i];
+        if (i < 64) qh[blk * 64 + i] = b[128 + i];
+        if (i < 16) sc[blk * 16 + i] = (int8_t)b[192 + i];
+        if (i == 0) d[blk] = __ushort_as_half((uint16_t)(b[208] | (b[209] << 8)));
+    }
+}
+
+int grid_for(long long work_items, int per_cta, int cap)
+{
+    long long g = (work_items + per_cta - 1) / per_cta;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+}  // namespace
+
+int smc_q8act_alloc(smc_ctx *ctx, int max_rows, int max_k, smc_q8act **out)
+{
+    if (max_rows <= 0 || max_k <= 0 || max_k % 32) return smc_fail(ctx, SMC_E_INVALID, "q8act: bad capacity %d x %d", max_rows, max_k);
+    smc_q8act *a = new smc_q8act();
+    a->max_rows = max_rows;
+    a->max_k = max_k;
+    size_t n = (size_t)max_rows * max_k, nb = n / 32;
+    cudaError_t e = cudaMalloc(&a->q, n);
+    if (e == cudaSuccess) e = cudaMalloc(&a->d, nb * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&a->dbits, nb * sizeof(uint16_t));
+    if (e == cudaSuccess) e = cudaMalloc(&a->sd, nb * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&a->s16, nb * 2 * sizeof(int16_t));
+    if (e != cudaSuccess) {
+        smc_q8act_free(a);
+        return smc_fail(ctx, SMC_E_CUDA, "q8act allocation failed: %s", cudaGetErrorString(e));
+    }
+    *out = a;
+    return SMC_OK;
+}
+
+void smc_q8act_free(smc_q8act *a)
+{
+    if (!a) return;
+    cudaFree(a->q);
+    cudaFree(a->d);
+    cudaFree(a->dbits);
+    cudaFree(a->sd);
+    cudaFree(a->s16);
+    delete a;
+}
+
+int smc_launch_quantize_q8(smc_ctx *ctx, const float *x, int M, int K, smc_q8act *a, cudaStream_t s)
+{
+    if (K % 32) return smc_fail(ctx, SMC_E_UNSUPPORTED, "Q8 activations need K %% 32 == 0 (K = %d)", K);
+    if (M > a->max_rows || K > a->max_k || (size_t)M * K > (size_t)a->max_rows * a->max_k)
+        return smc_fail(ctx, SMC_E_INVALID, "q8act buffer %d x %d too small for %d x %d", a->max_rows, a->max_k, M, K);
+    a->M = M;
+    a->K = K;
+    long long nblocks = (long long)M * K / 32;
+    quantize_q8_kernel<<<grid_for(nblocks, 8, ctx->sm_count * 8), 256, 0, s>>>(x, a->q, a->d, a->dbits, a->sd, a->s16,
+                                                                               nblocks);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+int smc_launch_quantize_weights(smc_ctx *ctx, int dtype, const float *v, int64_t n, void *raw, cudaStream_t s)
+{
+    const int be = dtype == SMC_Q8_0 ? 32 : 256;
+    if (dtype != SMC_Q8_0 && dtype != SMC_Q4_K && dtype != SMC_Q6_K)
+        return smc_fail(ctx, SMC_E_UNSUPPORTED, "no quantiser for dtype %d", dtype);
+    if (n < 0 || n % be)
+        return smc_fail(ctx, SMC_E_INVALID, "cannot quantise %lld values: length must be a multiple of %d", (long long)n, be);
+    if (n == 0) return SMC_OK;
+    long long nblocks = n / be;
+    int grid = grid_for(nblocks, 8, ctx->sm_count * 16);
+    uint8_t *o = static_cast<uint8_t *>(raw);
+    if (dtype == SMC_Q8_0) wq_q8_0_kernel<<<grid, 256, 0, s>>>(v, o, nblocks);
+    else if (dtype == SMC_Q4_K) wq_q4_K_kernel<<<grid, 256, 0, s>>>(v, o, nblocks);
+    else wq_q6_K_kernel<<<grid, 256, 0, s>>>(v, o, nblocks);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+// Builds the planes of `w` from w->d_raw.  Planes are allocated here; d_raw is left to the caller.
+int smc_launch_repack(smc_ctx *ctx, smc_weight *w, cudaStream_t s)
+{
+    if (w->dtype == SMC_Q8_0) {
+        long long nblocks = (long long)w->N * (w->K / 32);
+        SMC_CUDA(ctx, cudaMalloc(&w->q8_qs, (size_t)nblocks * 32));
+        SMC_CUDA(ctx, cudaMalloc(&w->q8_d, (size_t)nblocks * sizeof(__half)));
+        repack_q8_0_kernel<<<grid_for(nblocks * 32, 256, ctx->sm_count * 16), 256, 0, s>>>(w->d_raw, w->q8_qs, w->q8_d,
+                                                                                          nblocks);
+        SMC_LAUNCH_CHECK(ctx);
+    } else if (w->dtype == SMC_Q6_K) {
+        long long nblocks = (long long)w->N * w->K / 256;
+        SMC_CUDA(ctx, cudaMalloc(&w->q6_ql, (size_t)nblocks * 128));
+        SMC_CUDA(ctx, cudaMalloc(&w->q6_qh, (size_t)nblocks * 64));
+        SMC_CUDA(ctx, cudaMalloc(&w->q6_sc, (size_t)nblocks * 16));
+        SMC_CUDA(ctx, cudaMalloc(&w->q6_d, (size_t)nblocks * sizeof(__half)));
+        repack_q6_K_kernel<<<grid_for(nblocks * 128, 256, ctx->sm_count * 16), 256, 0, s>>>(
+            w->d_raw, w->q6_ql, w->q6_qh, w->q6_sc, w->q6_d, nblocks);
+        SMC_LAUNCH_CHECK(ctx);
+    }
+    return SMC_OK;
+}

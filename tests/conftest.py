@@ -18,3 +18,23 @@ def oracle():
 
     sm_oracle.build()
     return sm_oracle
+
+
+@pytest.fixture(scope="session")
+def cuda():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device and the compiled library; none is visible")
+    from sharpmind_b200 import ops
+
+    ctx = ops.CudaContext(0)
+    yield ctx
+    ctx.close()
+
+
+@pytest.fixture(scope="session")
+def dev(cuda):
+    from sharpmind_b200 import ops
+
+    return ops.DeviceOps(cuda)

@@ -1,0 +1,204 @@
+"""Parity of the fp32 ops around the matmuls with the CPU oracle, through the C ABI.
+
+Bars: norms / softmax / SiLU-gate within 1e-5 relative; RoPE, residual add, argmax, embedding gather
+and the weight quantisers bit-exact (same operations, same roundings).
+"""
+import numpy as np
+import pytest
+
+from sharpmind_b200 import synth
+from tests.gpu_util import Q4_K, Q6_K, Q8_0, bits, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_ok(got, want, tol=1e-5, floor=1e-30):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return np.all(np.abs(got - want) <= tol * np.maximum(np.abs(want), floor) + 1e-37)
+
+
+# ---------------------------------------------------------------- weight quantisers (bit exact)
+@pytest.mark.parametrize("dtype", [Q8_0, Q4_K, Q6_K])
+def test_weight_quantisers_match_oracle_bytes(oracle, dev, dtype):
+    w = synth.normal("gpuq", f"w{dtype}", (64, 1024), 0.02)
+    w[3, :256] = 0.0            # an all-zero block
+    w[5, 256:288] = 0.0123      # a flat 32-element sub-block (Q4_K leaves its codes at zero)
+    w[7, 512:528] = 0.0         # an all-zero 16-group inside a live block (Q6_K code 32)
+    w[9, :] = synth.uniform("gpuq", f"u{dtype}", (1024,))
+    got = dev.quantize_weights(dtype, to_dev(w)).cpu().numpy()
+    want = oracle.quantize(dtype, w)
+    assert got.size == want.size
+    assert np.array_equal(got, want), np.flatnonzero(got != want)[:10]
+
+
+def test_weight_quantiser_rejects_ragged_length(dev):
+    import torch
+
+    from sharpmind_b200 import ops
+
+    with pytest.raises(ops.InvalidOperationException):
+        dev.quantize_weights(Q4_K, torch.zeros(300, device="cuda"))
+    with pytest.raises(ops.InvalidOperationException):
+        dev.quantize_weights(Q8_0, torch.zeros(40, device="cuda"))
+
+
+# ---------------------------------------------------------------- RMSNorm
+@pytest.mark.parametrize("rows,n", [(64, 4096), (1, 1024), (24, 128), (5, 100), (3, 2), (2, 5000), (1, 14336)])
+def test_rmsnorm(oracle, dev, rows, n):
+    x = synth.normal("gpue", f"rx{rows}_{n}", (rows, n))
+    w = synth.normal("gpue", f"rw{n}", (n,), 0.1, 1.0)
+    want = oracle.rmsnorm(x, w, 1e-6)
+    got = dev.rmsnorm(to_dev(x), to_dev(w), 1e-6).cpu().numpy()
+    assert rel_ok(got, want)
+    xd = to_dev(x)  # in place, as the final norm runs
+    dev.rmsnorm(xd, to_dev(w), 1e-6, out=xd)
+    assert np.array_equal(bits(xd.cpu().numpy()), bits(got))
+
+
+def test_rmsnorm_reference_unit_cases(dev):
+    # ActivationTests.cs: RMSNorm_UnitWeights_NormalisesInput / RMSNorm_WeightScales
+    r = dev.rmsnorm(to_dev(np.array([[3, 4]], np.float32)), to_dev(np.ones(2, np.float32)), 0.0).cpu().numpy()
+    assert abs(np.sqrt(np.mean(r * r)) - 1) < 1e-4
+    r = dev.rmsnorm(to_dev(np.ones((1, 4), np.float32)), to_dev(np.full(4, 2, np.float32)), 0.0).cpu().numpy()
+    assert np.allclose(r, 2, atol=1e-4)
+
+
+def test_rmsnorm_row_slot(oracle, cuda):
+    from sharpmind_b200.ops import ActivationOps
+
+    a = ActivationOps(cuda)
+    src = synth.normal("gpue", "rrs", (333,))
+    w = synth.normal("gpue", "rrw", (333,), 0.1, 1.0)
+    inv = oracle.rmsnorm_param(src, 1e-6)
+    dst = np.zeros(333, np.float32)
+    a.ApplyRMSNormRow(src, w, dst, inv)
+    assert np.array_equal(bits(dst), bits(oracle.rmsnorm_row(src, w, inv)))
+
+
+# ---------------------------------------------------------------- SwiGLU / SiLU
+@pytest.mark.parametrize("rows,F", [(64, 14336), (1, 3072), (3, 37)])
+def test_swiglu(oracle, dev, rows, F):
+    gu = synth.normal("gpue", f"gu{rows}_{F}", (rows, 2 * F))
+    want = oracle.swiglu(np.ascontiguousarray(gu[:, :F]), np.ascontiguousarray(gu[:, F:]))
+    got = dev.swiglu_fused(to_dev(gu), F).cpu().numpy()
+    assert rel_ok(got, want, floor=1e-6)
+    got2 = dev.swiglu(to_dev(np.ascontiguousarray(gu[:, :F])), to_dev(np.ascontiguousarray(gu[:, F:]))).cpu().numpy()
+    assert np.array_equal(bits(got2), bits(got))
+
+
+def test_silu_and_slots(oracle, cuda, dev):
+    from sharpmind_b200.ops import ActivationOps
+
+    x = synth.normal("gpue", "silu", (1000,), 3.0)
+    want = oracle.silu(x)
+    assert rel_ok(dev.silu(to_dev(x)).cpu().numpy(), want, floor=1e-6)
+    a = ActivationOps(cuda)
+    dst = np.zeros(1000, np.float32)
+    a.ApplyPointwise(x, dst)
+    assert rel_ok(dst, want, floor=1e-6)
+    assert dev.silu(to_dev(np.zeros(4, np.float32))).cpu().numpy().tolist() == [0, 0, 0, 0]
+    u = synth.normal("gpue", "silu_u", (1000,))
+    a.ApplyGate(x, u, dst)
+    assert rel_ok(dst, oracle.swiglu(x, u), floor=1e-6)
+
+
+# ---------------------------------------------------------------- softmax
+@pytest.mark.parametrize("rows,n", [(64, 128256), (3, 1000), (2, 7), (1, 151936), (4, 4096)])
+def test_softmax(oracle, dev, rows, n):
+    x = synth.normal("gpue", f"sm{rows}_{n}", (rows, n), 2.0)
+    got = dev.softmax(to_dev(x)).cpu().numpy()
+    if rows * n > 2_000_000:
+        check = [0, rows // 2, rows - 1]
+    else:
+        check = range(rows)
+    for r in check:
+        want = oracle.softmax_rows(x[r])
+        assert rel_ok(got[r], want, tol=1e-5, floor=1e-12), r
+    assert np.allclose(got.sum(axis=1, dtype=np.float64), 1.0, atol=1e-5)
+
+
+def test_softmax_reference_properties(cuda, dev):
+    from sharpmind_b200.ops import ActivationOps
+
+    r = dev.softmax(to_dev(np.array([[1000, 1001, 1002]], np.float32))).cpu().numpy()
+    assert abs(r.sum() - 1) < 1e-4 and not np.isnan(r).any()
+    r = dev.softmax(to_dev(np.array([[1, 2, 3, 4]], np.float32))).cpu().numpy()[0]
+    assert abs(r.sum() - 1) < 1e-5 and np.all(np.diff(r) > 0)
+    a = ActivationOps(cuda)
+    out = a.Softmax(np.array([[1, 2, 3], [4, 5, 6]], np.float32))
+    assert np.allclose(out.sum(axis=1), 1, atol=1e-5)
+
+
+# ---------------------------------------------------------------- RoPE (bit exact: same tables, same ops)
+@pytest.mark.parametrize("neox", [False, True])
+def test_rope_llama3_shape(oracle, dev, neox):
+    seq, heads, hd, theta = 64, 32, 128, 500000.0
+    x = synth.normal("gpue", f"rope{neox}", (seq, heads, hd))
+    cos, sin = oracle.rope_tables(theta, hd, 128)
+    dcos, dsin = dev.rope_tables(theta, hd, 128)
+    assert np.array_equal(bits(dcos.cpu().numpy()), bits(cos)) and np.array_equal(bits(dsin.cpu().numpy()), bits(sin))
+    for off in (0, 17):
+        want = oracle.rope_apply(x, off, cos, sin, neox)
+        got = dev.rope(to_dev(x), off, dcos, dsin, neox).cpu().numpy()
+        assert np.array_equal(bits(got), bits(want))
+
+
+def test_rope_reference_unit_cases(dev):
+    # RoPETests.cs:44-79, RoPEConventionTests.cs:34-67
+    from sharpmind_b200 import ops
+
+    cos, sin = dev.rope_tables(10000.0, 4, 8)
+    x = dev.rope(to_dev(np.array([[[1, 2, 3, 4]]], np.float32)), 1, cos, sin, False).cpu().numpy()[0, 0]
+    th2 = float(np.float32(10000.0) ** np.float32(-0.5))
+    want = [np.cos(1.0) - 2 * np.sin(1.0), 2 * np.cos(1.0) + np.sin(1.0),
+            3 * np.cos(th2) - 4 * np.sin(th2), 4 * np.cos(th2) + 3 * np.sin(th2)]
+    assert np.allclose(x, want, atol=5e-6)
+    x = dev.rope(to_dev(np.array([[[1, 2, 3, 4]]], np.float32)), 1, cos, sin, True).cpu().numpy()[0, 0]
+    c0, s0, c1, s1 = np.cos(1.0), np.sin(1.0), np.cos(th2), np.sin(th2)
+    assert np.allclose(x, [c0 - 3 * s0, 2 * c1 - 4 * s1, 3 * c0 + s0, 4 * c1 + 2 * s1], atol=5e-5)
+    x = dev.rope(to_dev(np.array([[[1, 2, 3, 4]]], np.float32)), 0, cos, sin, True).cpu().numpy()[0, 0]
+    assert x.tolist() == [1, 2, 3, 4]
+    with pytest.raises(ops.ArgumentOutOfRangeException):  # Apply_ExceedsMaxSeqLen_Throws
+        dev.rope(to_dev(np.ones((5, 1, 4), np.float32)), 4, cos, sin, False)
+
+
+# ---------------------------------------------------------------- add / argmax / embedding
+def test_residual_add(oracle, dev):
+    for n in (64 * 4096, 1024, 7):
+        a = synth.normal("gpue", f"adda{n}", (n,))
+        b = synth.normal("gpue", f"addb{n}", (n,))
+        got = dev.add_(to_dev(a), to_dev(b)).cpu().numpy()
+        assert np.array_equal(bits(got), bits(oracle.add(a, b)))
+
+
+def test_argmax_first_maximum_wins(oracle, dev):
+    x = synth.normal("gpue", "am", (5, 151936))
+    x[1, 77] = x[1, 150000] = 99.0     # tie: the lower index must win
+    x[2, 0] = 50.0
+    x[3, 151935] = 50.0
+    got = dev.argmax(to_dev(x)).cpu().numpy()
+    assert got.tolist() == [oracle.argmax(x[r]) for r in range(5)]
+    assert got[1] == 77
+    assert dev.argmax(to_dev(np.array([[1, 5, 5, 2]], np.float32))).cpu().numpy().tolist() == [1]
+
+
+def test_embedding_gather_is_the_dequantised_row(oracle, cuda, dev):
+    vocab, H = 1000, 1024
+    raw = oracle.quantize(Q8_0, synth.normal("gpue", "emb", (vocab, H), 0.02))
+    table = oracle.dequantize(Q8_0, raw, vocab * H).reshape(vocab, H)
+    tok = np.array([0, 999, 17, 17, 512], np.int32)
+    for repack in (True, False):
+        w = cuda.register(raw, Q8_0, vocab, H, repack=repack)
+        got = dev.embed(w, to_dev(tok)).cpu().numpy()
+        assert np.array_equal(bits(got), bits(table[tok]))
+        cuda.release(w)
+
+
+def test_empty_inputs_are_no_ops(dev):
+    import torch
+
+    e = torch.zeros((0, 128), device="cuda")
+    w = torch.ones(128, device="cuda")
+    assert dev.rmsnorm(e, w, 1e-6).shape == (0, 128)
+    assert dev.softmax(e).shape == (0, 128)
+    assert dev.silu(e).shape == (0, 128)

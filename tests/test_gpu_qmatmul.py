@@ -1,0 +1,245 @@
+"""Parity of the CUDA quantized matmul (through the C ABI) with the CPU oracle.
+
+Bars: SMC_REF_ORDER is bit-exact with the scalar tier; SMC_ACT_F32 is within 1e-5*||w||*||x|| per
+output; SMC_ACT_Q8 has bit-exact activation quants, fp16 scales and per-block int32 sums, and fp32
+outputs within 1e-5*||w||*||x_hat|| of the oracle fed the dequantised activations.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from sharpmind_b200 import synth
+from tests.gpu_util import Q4_K, Q6_K, Q8_0, bits, row_norm_bound, to_dev
+from tests.test_oracle_pins import _random_raw
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "vecdot_golden.npz")
+
+
+def make_weight(oracle, dtype, n, k, name):
+    w = synth.normal("gpu", name, (n, k), 0.02)
+    return oracle.quantize(dtype, w)
+
+
+SHAPES = [
+    (Q8_0, 3072, 1024),   # Qwen3-0.6B FFN-up: the reference's own CPU-runnable case
+    (Q8_0, 96, 3072), (Q8_0, 40, 64), (Q8_0, 17, 32),
+    (Q4_K, 256, 4096), (Q4_K, 33, 256), (Q4_K, 64, 1024),
+    (Q6_K, 64, 14336), (Q6_K, 33, 256), (Q6_K, 128, 1024),
+]
+
+
+@pytest.mark.parametrize("dtype,n,k", SHAPES)
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 32])
+def test_qmatmul_modes_against_oracle(oracle, cuda, dev, dtype, n, k, m):
+    from sharpmind_b200.ops import Mode, Q8Act
+
+    if m > 3 and n * k > 2_000_000:
+        pytest.skip("oracle time: large shapes are checked at small M")
+    raw = make_weight(oracle, dtype, n, k, f"w{dtype}_{n}_{k}")
+    x = synth.normal("gpu", f"x{dtype}_{n}_{k}_{m}", (m, k))
+    w = cuda.register(raw, dtype, n, k)
+    try:
+        want = oracle.qmatmul(dtype, x, raw, m, k, n)
+        xd = to_dev(x)
+        # reference order: bit exact
+        got = dev.qmatmul(xd, w, Mode.REF_ORDER).cpu().numpy()
+        assert np.array_equal(bits(got), bits(want))
+        # fp32 activations
+        got = dev.qmatmul(xd, w, Mode.ACT_F32).cpu().numpy()
+        bound = row_norm_bound(oracle, dtype, raw, n, k, x)
+        assert np.all(np.abs(got.astype(np.float64) - want) <= bound), np.max(np.abs(got - want) / bound)
+        # quantised activations
+        act = Q8Act(cuda, max(m, 1), k)
+        dev.quantize_q8(xd, act, k)
+        q, dbits = act.read()
+        xq = oracle.quantize_rows_q8_0(x, m, k)
+        oq, od = oracle.split_q8_rows(xq)
+        assert np.array_equal(q, oq) and np.array_equal(dbits, od)
+        sums = dev.block_isums(act, m - 1, w, 0, min(n, 8)).cpu().numpy()
+        for c in range(min(n, 8)):
+            assert np.array_equal(sums[c], oracle.block_isums(dtype, raw, xq[m - 1], c, k))
+        xhat = np.stack([oracle.dequantize(Q8_0, xq[r], k) for r in range(m)])
+        want_q = oracle.qmatmul(dtype, xhat, raw, m, k, n)
+        got_q = dev.qmatmul_q8(act, w).cpu().numpy()
+        bound_q = row_norm_bound(oracle, dtype, raw, n, k, xhat)
+        assert np.all(np.abs(got_q.astype(np.float64) - want_q) <= bound_q), np.max(np.abs(got_q - want_q) / bound_q)
+        # the one-call form (quantise + matmul on the context's scratch) gives the same bits
+        got_q2 = dev.qmatmul(xd, w, Mode.ACT_Q8).cpu().numpy()
+        assert np.array_equal(bits(got_q2), bits(got_q))
+        act.close()
+    finally:
+        cuda.release(w)
+
+
+def test_results_do_not_depend_on_batch_size(oracle, cuda, dev):
+    """Row r of an M-row call equals the M = 1 call on that row (both fast modes, all formats)."""
+    from sharpmind_b200.ops import Mode
+
+    for dtype, n, k in ((Q8_0, 512, 1024), (Q4_K, 256, 4096), (Q6_K, 64, 14336)):
+        raw = make_weight(oracle, dtype, n, k, f"bs{dtype}")
+        w = cuda.register(raw, dtype, n, k)
+        x = to_dev(synth.normal("gpu", f"bsx{dtype}", (32, k)))
+        for mode in (Mode.ACT_F32, Mode.ACT_Q8):
+            full = dev.qmatmul(x, w, mode).cpu().numpy()
+            for r in (0, 7, 31):
+                one = dev.qmatmul(x[r:r + 1].contiguous(), w, mode).cpu().numpy()
+                assert np.array_equal(bits(one[0]), bits(full[r])), (dtype, mode, r)
+        cuda.release(w)
+
+
+@pytest.mark.parametrize("k", [8, 15, 20, 32, 33, 40, 63, 64, 96, 137, 896])
+def test_q8_0_block_tails_with_poisoned_padding(oracle, cuda, dev, k):
+    # Q8BlockTailTests.cs:25-97: partial last blocks; anything read past K would pick up 1e6
+    from sharpmind_b200.ops import Mode
+
+    n = 3
+    raw = _random_raw(Q8_0, oracle.raw_bytes(Q8_0, n, k), f"tail{k}")
+    x = np.full((2, k + 64), 1e6, np.float32)
+    x[:, :k] = synth.uniform("gpu", f"tailx{k}", (2, k))
+    xin = np.ascontiguousarray(x[:, :k])
+    w = cuda.register(raw, Q8_0, n, k)
+    want = oracle.qmatmul(Q8_0, xin, raw, 2, k, n)
+    for mode in (Mode.REF_ORDER, Mode.ACT_F32):
+        got = dev.qmatmul(to_dev(xin), w, mode).cpu().numpy()
+        if mode == Mode.REF_ORDER or k % 32:
+            assert np.array_equal(bits(got), bits(want))
+        else:
+            assert np.all(np.abs(got - want) <= 1e-4 * np.maximum(1.0, np.abs(want)))
+    cuda.release(w)
+
+
+@pytest.mark.parametrize("dtype", [Q4_K, Q6_K])
+@pytest.mark.parametrize("n,k", [(8, 96), (8, 160), (4, 320), (6, 1024)])
+def test_kquant_rows_that_start_inside_a_block(oracle, cuda, dev, dtype, n, k):
+    """Flat-tensor addressing (startBlock / colBlockStart): rows need not start on a block boundary."""
+    from sharpmind_b200.ops import Mode
+
+    nbytes = oracle.raw_bytes(dtype, n, k)
+    raw = _random_raw(dtype, nbytes + 256, f"rag{dtype}_{n}_{k}")[:nbytes].copy()
+    x = synth.uniform("gpu", f"ragx{dtype}_{n}_{k}", (2, k))
+    w = cuda.register(raw, dtype, n, k)
+    want = oracle.qmatmul(dtype, x, raw, 2, k, n)
+    for mode in (Mode.REF_ORDER, Mode.ACT_F32):
+        got = dev.qmatmul(to_dev(x), w, mode).cpu().numpy()
+        if k % 256:
+            assert np.array_equal(bits(got), bits(want)), mode
+        else:
+            assert np.allclose(got, want, rtol=0, atol=1e-3 * np.abs(want).max())
+    cuda.release(w)
+
+
+def test_golden_vectors_through_the_c_abi(oracle, cuda):
+    """Outputs recorded from the reference's own compiled C, reproduced bit for bit by the CUDA path."""
+    from sharpmind_b200.ops import QuantizationOps
+
+    q = QuantizationOps(cuda)
+    gold = np.load(GOLDEN)
+    for key in gold.files:
+        if not key.startswith("out_"):
+            continue
+        _, dtype, n, k = key.split("_")
+        dtype, n, k = int(dtype), int(n), int(k)
+        nbytes = oracle.raw_bytes(dtype, n, k)
+        raw = _random_raw(dtype, nbytes + 256, f"gold{dtype}_{n}_{k}")[:nbytes].copy()
+        x = synth.uniform("pins", f"goldx{dtype}_{n}_{k}", (k,))
+        w = cuda.register(raw, dtype, n, k)
+        fn = {Q8_0: q.VecDotQ8_0, Q4_K: q.VecDotQ4K, Q6_K: q.VecDotQ6K}[dtype]
+        got = np.array([fn(x, raw, c, k) for c in range(n)], np.float32)
+        assert np.array_equal(bits(got), bits(gold[key])), key
+        cuda.release(w)
+
+
+def test_known_answer_blocks_through_the_c_abi(cuda):
+    # VecDotTests.cs:87-172
+    from sharpmind_b200.ops import QuantizationOps
+
+    q = QuantizationOps(cuda)
+    b8 = np.zeros(34, np.uint8); b8[1], b8[2] = 0x40, 0x03
+    b4 = np.zeros(144, np.uint8); b4[1], b4[4], b4[16] = 0x3C, 0x11, 0x01
+    b6 = np.zeros(210, np.uint8); b6[209] = 0x3C
+    for raw, dtype, fn, want in ((b8, Q8_0, q.VecDotQ8_0, 6.0), (b4, Q4_K, q.VecDotQ4K, 17.0), (b6, Q6_K, q.VecDotQ6K, 0.0)):
+        w = cuda.register(raw, dtype, 1, 1)
+        assert fn(np.array([1.0], np.float32), raw, 0, 1) == want
+        cuda.release(w)
+
+
+def test_host_slot_equals_device_path_and_guards(oracle, cuda, dev):
+    from sharpmind_b200 import ops
+
+    n, k, m = 192, 1024, 3
+    raw = make_weight(oracle, Q8_0, n, k, "slot")
+    x = synth.normal("gpu", "slotx", (m, k))
+    w = cuda.register(raw, Q8_0, n, k)
+    for mode in (ops.Mode.ACT_F32, ops.Mode.ACT_Q8, ops.Mode.REF_ORDER):
+        q = ops.QuantizationOps(cuda, mode)
+        out = np.zeros((m, n), np.float32)
+        q.QuantizedMatMulQ8_0(x, raw, out, m, k, n)
+        ref = dev.qmatmul(to_dev(x), w, mode).cpu().numpy()
+        assert np.array_equal(bits(out), bits(ref))
+    q = ops.QuantizationOps(cuda)
+    out = np.zeros((m, n), np.float32)
+    with pytest.raises(ops.InvalidOperationException):  # shape does not match the registration
+        q.QuantizedMatMulQ8_0(x, raw, np.zeros((m, n - 32), np.float32), m, k, n - 32)
+    with pytest.raises(ops.InvalidOperationException):  # never registered
+        q.QuantizedMatMulQ8_0(x, raw.copy(), out, m, k, n)
+    with pytest.raises(ops.InvalidOperationException):  # byte count guard on arrival
+        cuda.register(raw[:-34], Q8_0, n, k)
+    with pytest.raises(ops.ArgumentOutOfRangeException):
+        q.VecDotQ8_0(x[0], raw, n, k)
+    cuda.release(w)
+    w2 = cuda.register(raw, Q8_0, n, k, repack=False)
+    with pytest.raises(ops.NotSupportedException):
+        dev.qmatmul(to_dev(x), w2, ops.Mode.ACT_Q8)
+    cuda.release(w2)
+    # M = 0 is a no-op
+    w3 = cuda.register(raw, Q8_0, n, k)
+    assert dev.qmatmul(to_dev(np.zeros((0, k), np.float32)), w3).shape == (0, n)
+    cuda.release(w3)
+
+
+def test_repeated_launches_are_bit_identical(oracle, cuda, dev):
+    """Race check: the same launch repeated gives the same bits."""
+    from sharpmind_b200.ops import Mode
+
+    raw = make_weight(oracle, Q4_K, 512, 4096, "race")
+    w = cuda.register(raw, Q4_K, 512, 4096)
+    x = to_dev(synth.normal("gpu", "racex", (4, 4096)))
+    for mode in (Mode.ACT_F32, Mode.ACT_Q8):
+        first = dev.qmatmul(x, w, mode).cpu().numpy()
+        for _ in range(5):
+            assert np.array_equal(bits(dev.qmatmul(x, w, mode).cpu().numpy()), bits(first))
+    cuda.release(w)
+
+
+def test_llama8b_ffn_shapes_sampled_rows_and_linearity(oracle, cuda, dev):
+    """Full-size Llama-3-8B FFN matrices: weights quantised on device, sampled rows against the
+    oracle, and linearity (W(a*x + y) = a*Wx + Wy) as the size-independent property."""
+    import torch
+
+    from sharpmind_b200.ops import Mode
+
+    for dtype, n, k in ((Q4_K, 14336, 4096), (Q6_K, 4096, 14336)):
+        g = torch.Generator(device="cuda").manual_seed(1234 + dtype)
+        wf = torch.randn((n, k), generator=g, device="cuda", dtype=torch.float32) * 0.02
+        raw_d = dev.quantize_weights(dtype, wf)
+        raw = raw_d.cpu().numpy()
+        del wf
+        w = cuda.register(raw, dtype, n, k, keep_raw=False)
+        x = synth.normal("gpu", f"full{dtype}", (2, k))
+        rows = [0, 1, n // 2, n - 1]
+        for mode in (Mode.ACT_F32,):
+            got = dev.qmatmul(to_dev(x), w, mode).cpu().numpy()
+            for r in rows:
+                want = oracle.qmatmul(dtype, x, raw, 2, k, n, cols=(r, r + 1))[:, r]
+                wrow = oracle.dequantize(dtype, raw[r * (len(raw) // n):(r + 1) * (len(raw) // n)], k)
+                tol = 1e-5 * np.linalg.norm(wrow) * np.linalg.norm(x, axis=1)
+                assert np.all(np.abs(got[:, r] - want) <= tol)
+        a = np.float32(0.5)
+        xs = to_dev(np.stack([x[0], x[1], a * x[0] + x[1]]))
+        y = dev.qmatmul(xs, w, Mode.ACT_F32).cpu().numpy().astype(np.float64)
+        scale = np.abs(y).max()
+        assert np.max(np.abs(a * y[0] + y[1] - y[2])) <= 2e-5 * scale
+        cuda.release(w)
