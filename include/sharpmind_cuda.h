@@ -78,6 +78,10 @@ SMC_API void smc_destroy(smc_ctx *ctx);
 SMC_API const char *smc_last_error(smc_ctx *ctx);
 /* QuantizationOps.GetRawTensorByteCount for a [N, K] tensor (QuantizationOps.cs:15-72); -1 if dtype unknown. */
 SMC_API int64_t smc_raw_tensor_bytes(int dtype, int64_t N, int64_t K);
+/* Waits for the device, then reports whether any kernel of this context gave up a bounded wait since
+ * the last call (0 = none; the flag is cleared).  No counterpart in the reference: its kernels are
+ * synchronous CPU code (QuantizationKernels.cs), so it has no asynchronous failures to surface. */
+SMC_API int smc_device_status(smc_ctx *ctx, int *status);
 /* Blocks until everything queued on the context's own stream has finished. */
 SMC_API int smc_synchronize(smc_ctx *ctx);
 

@@ -24,6 +24,7 @@ SIGNATURES = {
     "smc_last_error": (C.c_char_p, [c_void_p]),
     "smc_raw_tensor_bytes": (c_int64, [c_int, c_int64, c_int64]),
     "smc_synchronize": (c_int, [c_void_p]),
+    "smc_device_status": (c_int, [c_void_p, C.POINTER(c_int)]),
     "smc_weight_register": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, _pp]),
     "smc_weight_register_dev": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_int, _pp]),
     "smc_weight_lookup": (c_int, [c_void_p, c_void_p, _pp]),

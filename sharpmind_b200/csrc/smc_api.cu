@@ -8,6 +8,7 @@
 // device kernels as the *_dev entry points and synchronise.  There is no CPU compute path anywhere.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "smc_common.cuh"
@@ -159,6 +160,13 @@ int smc_init(int device, smc_ctx **out)
         delete ctx;
         return SMC_E_CUDA;
     }
+    if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess) {
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return SMC_E_CUDA;
+    }
+    const char *impl = getenv("SMC_GEMV");
+    ctx->use_tma = !(impl && strcmp(impl, "stream") == 0);
     *out = ctx;
     return SMC_OK;
 }
@@ -174,6 +182,7 @@ void smc_destroy(smc_ctx *ctx)
     cudaFree(ctx->d_stage_out);
     cudaFree(ctx->d_stage_aux);
     cudaFree(ctx->d_attn_part);
+    cudaFree(ctx->d_status);
     if (ctx->h_pin) cudaFreeHost(ctx->h_pin);
     smc_q8act_free(ctx->act);
     cudaStreamDestroy(ctx->stream);
@@ -181,6 +190,18 @@ void smc_destroy(smc_ctx *ctx)
 }
 
 const char *smc_last_error(smc_ctx *ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int smc_device_status(smc_ctx *ctx, int *status)
+{
+    if (!ctx || !status) return smc_fail(ctx, SMC_E_INVALID, "device_status: bad arguments");
+    SMC_CUDA(ctx, cudaDeviceSynchronize());
+    SMC_CUDA(ctx, cudaMemcpy(status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status) {
+        SMC_CUDA(ctx, cudaMemset(ctx->d_status, 0, sizeof(int)));
+        return smc_fail(ctx, SMC_E_CUDA, "a kernel gave up a bounded wait (status %d): its outputs are invalid", *status);
+    }
+    return SMC_OK;
+}
 
 int smc_synchronize(smc_ctx *ctx)
 {

@@ -58,6 +58,8 @@ struct smc_ctx {
     size_t h_pin_cap = 0;
     // scratch owned by the context
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
+    int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
+    bool use_tma = true;               // SMC_GEMV=stream in the environment selects the register-prefetch kernels
     float *d_attn_part = nullptr;      // split-KV partial results
     size_t attn_part_cap = 0;
 };
@@ -82,6 +84,10 @@ int smc_fail(smc_ctx *ctx, int code, const char *fmt, ...);
 // ---- launchers implemented across the .cu files (all asynchronous on `s`) ----
 int smc_launch_gemv_f32(smc_ctx *, const float *x, const smc_weight *, float *out, int M, cudaStream_t s);
 int smc_launch_gemv_q8(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
+bool smc_tma_supported(const smc_weight *, int M);
+int smc_launch_gemv_tma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
+bool smc_stream_supported(const smc_weight *, int M);
+int smc_launch_gemv_stream(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,
                         cudaStream_t s);
 int smc_launch_quantize_q8(smc_ctx *, const float *x, int M, int K, smc_q8act *, cudaStream_t s);

@@ -319,8 +319,8 @@ extern "C" {
 int smc_rmsnorm_dev(smc_ctx *ctx, const float *d_x, const float *d_w, float *d_out, int rows, int n, float eps,
                     void *stream)
 {
+    if (ctx && rows == 0) return SMC_OK;  // an empty tensor has no data pointer to check
     if (!ctx || !d_x || !d_w || !d_out || rows < 0 || n <= 0) return smc_fail(ctx, SMC_E_INVALID, "rmsnorm: bad arguments");
-    if (rows == 0) return SMC_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     bool aligned = ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_out) |
                      reinterpret_cast<uintptr_t>(d_w)) & 15) == 0;
@@ -352,8 +352,8 @@ int smc_swiglu_dev(smc_ctx *ctx, const float *d_gate, const float *d_up, float *
 
 int smc_silu_dev(smc_ctx *ctx, const float *d_src, float *d_dst, int64_t n, void *stream)
 {
+    if (ctx && n == 0) return SMC_OK;
     if (!ctx || !d_src || !d_dst || n < 0) return smc_fail(ctx, SMC_E_INVALID, "silu: bad arguments");
-    if (n == 0) return SMC_OK;
     silu_kernel<<<ew_grid(n, ctx->sm_count * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(d_src, d_dst, n);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
@@ -361,8 +361,8 @@ int smc_silu_dev(smc_ctx *ctx, const float *d_src, float *d_dst, int64_t n, void
 
 int smc_softmax_dev(smc_ctx *ctx, const float *d_src, float *d_dst, int rows, int n, void *stream)
 {
+    if (ctx && rows == 0) return SMC_OK;
     if (!ctx || !d_src || !d_dst || rows < 0 || n <= 0) return smc_fail(ctx, SMC_E_INVALID, "softmax: bad arguments");
-    if (rows == 0) return SMC_OK;
     int vec = ((n & 3) == 0 && ((reinterpret_cast<uintptr_t>(d_src) | reinterpret_cast<uintptr_t>(d_dst)) & 15) == 0) ? 1 : 0;
     int threads = n >= 8192 ? 1024 : (n >= 1024 ? 256 : 64);
     softmax_kernel<<<rows, threads, 0, static_cast<cudaStream_t>(stream)>>>(d_src, d_dst, n, vec);

@@ -414,8 +414,13 @@ __device__ float ref_vecdot_q4_K(const float *x, const uint8_t *raw, int col, in
     return (float)sum;
 }
 
-__device__ float ref_vecdot_q6_K(const float *x, const uint8_t *raw, int col, int K)
+// `avail` = floats readable from x: when a row ends inside a 128-element half the reference's loop
+// still reads the l+64 / l+96 partners, up to 96 floats past the row (into the next input row, or
+// past the tensor for the last row).  Reads inside the activation tensor are reproduced; reads past
+// its end return 0 instead of touching memory the caller never handed over.
+__device__ float ref_vecdot_q6_K(const float *x, const uint8_t *raw, int col, int K, long long avail)
 {
+    auto X = [&](int i) { return i < avail ? x[i] : 0.0f; };
     long long flat = (long long)col * K;
     long long startBlock = flat / 256;
     int cbs = (int)(flat % 256);
@@ -443,16 +448,16 @@ __device__ float ref_vecdot_q6_K(const float *x, const uint8_t *raw, int col, in
                 int lim = b * 256 + end - cbs;
                 float w1 = __fmul_rn(__fmul_rn(d, (float)psc[is + 0]), (float)(q1 - 32));
                 if (i2 >= lim) {
-                    if (i1 < lim) sum += (double)__fmul_rn(x[i1], w1);
+                    if (i1 < lim) sum += (double)__fmul_rn(X(i1), w1);
                     break;
                 }
                 float w2 = __fmul_rn(__fmul_rn(d, (float)psc[is + 2]), (float)(q2 - 32));
                 float w3 = __fmul_rn(__fmul_rn(d, (float)psc[is + 4]), (float)(q3 - 32));
                 float w4 = __fmul_rn(__fmul_rn(d, (float)psc[is + 6]), (float)(q4 - 32));
-                sum += (double)__fmul_rn(x[i1], w1);
-                sum += (double)__fmul_rn(x[i2], w2);
-                sum += (double)__fmul_rn(x[i1 + 64], w3);
-                sum += (double)__fmul_rn(x[i1 + 96], w4);
+                sum += (double)__fmul_rn(X(i1), w1);
+                sum += (double)__fmul_rn(X(i2), w2);
+                sum += (double)__fmul_rn(X(i1 + 64), w3);
+                sum += (double)__fmul_rn(X(i1 + 96), w4);
             }
         }
     }
@@ -470,7 +475,7 @@ __global__ void gemv_ref_kernel(const float *__restrict__ x, const uint8_t *__re
     float r;
     if (dtype == SMC_Q8_0) r = ref_vecdot_q8_0(xr, raw, col, K);
     else if (dtype == SMC_Q4_K) r = ref_vecdot_q4_K(xr, raw, col, K);
-    else r = ref_vecdot_q6_K(xr, raw, col, K);
+    else r = ref_vecdot_q6_K(xr, raw, col, K, (long long)(M - m) * K);
     out[(size_t)m * N + col] = r;
 }
 
@@ -525,6 +530,8 @@ int smc_launch_gemv_f32(smc_ctx *ctx, const float *x, const smc_weight *w, float
 
 int smc_launch_gemv_q8(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *out, cudaStream_t s)
 {
+    if (ctx->use_tma && smc_tma_supported(w, a->M)) return smc_launch_gemv_tma(ctx, a, w, out, s);
+    if (smc_stream_supported(w, a->M)) return smc_launch_gemv_stream(ctx, a, w, out, s);
     ActPtrs ap{};
     ap.q = a->q;
     ap.d = a->d;

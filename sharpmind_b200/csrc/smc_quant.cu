@@ -69,9 +69,8 @@ __global__ void __launch_bounds__(256) wq_q8_0_kernel(const float *__restrict__ 
         qi = max(-128, min(127, qi));
         o[2 + lane] = (uint8_t)(int8_t)qi;
         if (lane == 0) {
-            uint16_t hb = __half_as_ushort(__float2half_rn(d));
-            o[0] = (uint8_t)(hb & 0xFF);
-            o[1] = (uint8_t)(hb >> 8);
+            // block offsets are even, so the scale goes out as one 16-bit store
+            *reinterpret_cast<uint16_t *>(o) = __half_as_ushort(__float2half_rn(d));
         }
     }
 }
@@ -130,8 +129,8 @@ __global__ void __launch_bounds__(256) wq_q4_K_kernel(const float *__restrict__ 
         for (int g = 0; g < 4; ++g) o[16 + 32 * g + lane] = (uint8_t)(code[2 * g] | (code[2 * g + 1] << 4));
         if (lane == 0) {
             uint16_t hb = __half_as_ushort(__float2half_rn(step));
-            o[0] = o[2] = (uint8_t)(hb & 0xFF);
-            o[1] = o[3] = (uint8_t)(hb >> 8);
+            reinterpret_cast<uint16_t *>(o)[0] = hb;  // d
+            reinterpret_cast<uint16_t *>(o)[1] = hb;  // dmin
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 o[4 + j] = (uint8_t)((sc[j] & 0x3F) | ((sc[4 + j] >> 4) << 6));
@@ -189,9 +188,7 @@ __global__ void __launch_bounds__(256) wq_q6_K_kernel(const float *__restrict__ 
                 (uint8_t)(((c[0] >> 4) & 3) | (((c[1] >> 4) & 3) << 2) | (((c[2] >> 4) & 3) << 4) | (((c[3] >> 4) & 3) << 6));
         }
         if (lane == 0) {
-            uint16_t hb = __half_as_ushort(__float2half_rn(d));
-            o[208] = (uint8_t)(hb & 0xFF);
-            o[209] = (uint8_t)(hb >> 8);
+            *reinterpret_cast<uint16_t *>(o + 208) = __half_as_ushort(__float2half_rn(d));
         }
     }
 }

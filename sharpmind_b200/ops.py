@@ -111,6 +111,12 @@ class CudaContext:
     def synchronize(self):
         self.check(self.lib.smc_synchronize(self.h))
 
+    def device_status(self) -> int:
+        """Waits for the device; raises if a kernel abandoned a bounded wait since the last call."""
+        st = C.c_int(0)
+        self.check(self.lib.smc_device_status(self.h, C.byref(st)))
+        return st.value
+
     # ---- weights
     def register(self, raw: np.ndarray, dtype: int, n: int, k: int, repack: bool = True,
                  keep_raw: bool = True) -> Weight:

@@ -30,7 +30,10 @@ def cuda():
 
     ctx = ops.CudaContext(0)
     yield ctx
-    ctx.close()
+    try:
+        assert ctx.device_status() == 0  # no kernel abandoned a bounded wait during the session
+    finally:
+        ctx.close()
 
 
 @pytest.fixture(scope="session")

@@ -111,9 +111,16 @@ def test_softmax(oracle, dev, rows, n):
         check = [0, rows // 2, rows - 1]
     else:
         check = range(rows)
+    # The scalar reference adds n exponentials one after another in fp32, so its own normaliser
+    # carries about sqrt(n) * 2^-24 of rounding noise (1.2e-5 at n = 128256).  The CUDA kernel is
+    # held to 1e-5 against the exact (fp64) softmax, and to 1e-5 plus that noise against the oracle.
+    noise = np.sqrt(n) * 2.0 ** -24
     for r in check:
         want = oracle.softmax_rows(x[r])
-        assert rel_ok(got[r], want, tol=1e-5, floor=1e-12), r
+        assert rel_ok(got[r], want, tol=1e-5 + noise, floor=1e-12), r
+        z = x[r].astype(np.float64)
+        e = np.exp(z - z.max())
+        assert rel_ok(got[r], e / e.sum(), tol=1e-5, floor=1e-12), r
     assert np.allclose(got.sum(axis=1, dtype=np.float64), 1.0, atol=1e-5)
 
 

@@ -119,7 +119,12 @@ def test_kquant_rows_that_start_inside_a_block(oracle, cuda, dev, dtype, n, k):
 
     nbytes = oracle.raw_bytes(dtype, n, k)
     raw = _random_raw(dtype, nbytes + 256, f"rag{dtype}_{n}_{k}")[:nbytes].copy()
-    x = synth.uniform("gpu", f"ragx{dtype}_{n}_{k}", (2, k))
+    # The reference's Q6_K loop reads up to 96 floats past a row that ends inside a 128-element half
+    # (into the next input row, or past the tensor).  The CUDA kernel reproduces reads inside the
+    # tensor and returns 0 past its end, so the oracle is given a zero-padded backing buffer.
+    backing = np.zeros(2 * k + 128, np.float32)
+    backing[:2 * k] = synth.uniform("gpu", f"ragx{dtype}_{n}_{k}", (2 * k,))
+    x = backing[:2 * k].reshape(2, k)
     w = cuda.register(raw, dtype, n, k)
     want = oracle.qmatmul(dtype, x, raw, 2, k, n)
     for mode in (Mode.REF_ORDER, Mode.ACT_F32):
