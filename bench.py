@@ -291,7 +291,7 @@ def run_ours(args):
                     ev.record()
                     with torch.cuda.stream(comm_stream):
                         comm_stream.wait_event(ev)
-                        dist.all_gather_into_tensor(gathered[mi], outs[mi])
+                        dist.all_gather_into_tensor(gathered[mi].view(world * M, -1), outs[mi])
                     # the next launch that overwrites outs[mi] must wait for this gather
                     done = torch.cuda.Event()
                     done.record(comm_stream)

@@ -5,19 +5,28 @@
 // Q8_0: 32 blocks = 1024 elements).  The bytes of a step are brought into a warp-private ring of
 // shared-memory slots by bulk asynchronous copies (cp.async.bulk global -> shared, completion on an
 // mbarrier) issued by one lane, up to `slots` steps ahead of the math:
-//   * memory-level parallelism is set by shared memory, not by registers (8 slots x 8 warps x
-//     2 CTAs keeps more than 100 KB per SM in flight, against the ~45 KB Little's law asks for);
+//   * memory-level parallelism is set by shared memory, not by registers (6-8 slots x 8 warps x
+//     2-3 CTAs keep more than 100 KB per SM in flight, against the ~45 KB Little's law asks for);
 //   * HBM and L2 see whole contiguous ranges, never half-used sectors;
-//   * the lanes read their unit with conflict-free 128-bit shared loads, and the activation row is
-//     also in shared memory (XOR-swizzled in 16-byte chunks so that the strided reads of eight
-//     lanes fall in eight different bank groups), so the inner loop issues no global loads at all.
+//   * the lanes read their unit with conflict-free 128-bit shared loads, and for M = 1 the
+//     activation row is in shared memory too (16-byte chunks permuted per format so that the
+//     strided reads of eight lanes fall in eight different bank groups): the inner loop issues no
+//     global loads at all.
+// The kernels are bound by instruction issue before they are bound by HBM, so the inner loop is
+// written for a short instruction stream: 32-bit shared addresses and explicit ld.shared, every
+// lane-constant offset hoisted, Q4_K scale / min bytes unpacked with two PRMTs, high nibbles dotted
+// in place (dp4a on w & 0xF0F0F0F0, exact shift by 4 afterwards), independent dp4a chains.
 // A slot is re-armed only after __syncwarp(): every lane has passed its wait and read its data, so
 // no lane can be left waiting on a phase that has already been reused.  Every wait is bounded; on
 // expiry the warp raises a flag in device memory (read back by smc_device_status) and stops.
 //
 // Arithmetic is identical to the other SMC_ACT_Q8 kernels: exact int32 block dots (dp4a), one fp32
 // multiply-add per 32-element block.  Shapes: K % 2048 == 0 (K-quants) / K % 1024 == 0 (Q8_0).
-// References as in smc_gemv.cu.
+// References: VecDotQ4K_* SharpMind.Core/Quantization/QuantizationKernels.Q4.cs:586-747, GetScaleMinK4_*
+// QuantizationKernels.cs:177-189, VecDotQ6K_* QuantizationKernels.Q6.cs:12-235, VecDotQ8_0_*
+// QuantizationKernels.Q8.cs:11-138.
+#include <stdlib.h>
+
 #include "smc_common.cuh"
 
 namespace {
@@ -63,6 +72,32 @@ __device__ __forceinline__ void fence_barrier_init()
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// explicit shared-space loads on 32-bit addresses
+__device__ __forceinline__ uint4 lds128(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16u(uint32_t a)
+{
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+
 __device__ __forceinline__ float warp_sum32(float v)
 {
 #pragma unroll
@@ -81,7 +116,7 @@ struct XPtrs {
 // chunks permuted by Math::swz so that the 128-bit reads of a quarter warp (eight lanes, each format
 // with its own stride pattern) fall in eight different bank groups.
 template <class Math>
-__device__ __forceinline__ void stage_x(const XPtrs &g, int m, int K, uint8_t *sx, bool want_sd, bool want_s16)
+__device__ __forceinline__ void stage_x(const XPtrs &g, int m, int K, uint8_t *sx)
 {
     uint4 *sq = reinterpret_cast<uint4 *>(sx);
     float *sdx = reinterpret_cast<float *>(sx + K);
@@ -91,112 +126,120 @@ __device__ __forceinline__ void stage_x(const XPtrs &g, int m, int K, uint8_t *s
     for (int i = threadIdx.x; i < K / 16; i += blockDim.x) sq[Math::swz(i)] = __ldg(gq + i);
     for (int i = threadIdx.x; i < K / 32; i += blockDim.x) {
         sdx[i] = __ldg(g.d + (size_t)m * (K / 32) + i);
-        if (want_sd) ssd[i] = __ldg(g.sd + (size_t)m * (K / 32) + i);
+        if (Math::SD) ssd[i] = __ldg(g.sd + (size_t)m * (K / 32) + i);
     }
-    if (want_s16)
+    if (Math::S16)
         for (int i = threadIdx.x; i < K / 16; i += blockDim.x) ss16[i] = __ldg(g.s16 + (size_t)m * (K / 16) + i);
 }
 __host__ __device__ inline size_t x_bytes(int K) { return (size_t)K + (size_t)(K / 32) * 8 + (size_t)(K / 16) * 2; }
 
-__device__ __forceinline__ uint4 lds16(const uint8_t *p) { return *reinterpret_cast<const uint4 *>(p); }
-
-__device__ __forceinline__ void warp_rows(int N, int &r0, int &r1)
-{
-    const long long W = (long long)gridDim.x * WARPS;
-    const long long w = (long long)blockIdx.x * WARPS + (threadIdx.x >> 5);
-    r0 = (int)((long long)N * w / W);
-    r1 = (int)((long long)N * (w + 1) / W);
-}
-
-// Description of how one step of a format is fetched: up to four contiguous pieces.
+// Where the weight arrays of a format start (piece sizes and slot offsets are Math constants).
 struct StepSrc {
-    const uint8_t *base[4];  // address of this warp's first step in each weight array
-    uint32_t bytes[4];       // bytes per step in each array (multiples of 16)
-    uint32_t off[4];         // offset of each piece inside a slot
-    int pieces;
-    uint32_t total;
+    const uint8_t *base[4];  // first step of row 0 in each weight array
 };
 
-__device__ __forceinline__ void issue_step(const StepSrc &s, int t, uint32_t slot_addr, uint32_t bar)
+// Fetches stage `g` (SS consecutive steps, contiguous in every weight array) into a slot.  PIECES and
+// the per-piece sizes are compile-time so that the elected lane spends a handful of instructions here.
+template <class Math, int SS>
+__device__ __forceinline__ void issue_stage(const StepSrc &s, long long g, uint32_t slot_addr, uint32_t bar)
 {
-    mbar_expect_tx(bar, s.total);
+    mbar_expect_tx(bar, Math::STEP_BYTES * SS);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-        if (i < s.pieces) bulk_g2s(slot_addr + s.off[i], s.base[i] + (size_t)t * s.bytes[i], s.bytes[i], bar);
+    for (int i = 0; i < Math::PIECES; ++i)
+        bulk_g2s(slot_addr + Math::piece_off(i) * SS, s.base[i] + (size_t)g * (Math::piece_bytes(i) * SS),
+                 Math::piece_bytes(i) * SS, bar);
 }
 
-// ------------------------------------------------------------------------------------------------
-// Format-specific math on one unit held in a shared-memory slot.
-// ------------------------------------------------------------------------------------------------
+// Context handed to the per-format math: where the activations are.
+struct XCtx {
+    uint32_t sx;   // shared address of the staged row (M = 1)
+    int K, m0, M;
+    XPtrs g;       // global buffers (M > 1)
+};
+
+// ------------------------------------------------------------------------------------------------ Q4_K
 struct MathQ4K {
     static constexpr int STEP_ELEMS = 2048;
-    static constexpr uint32_t SLOT = 1152;  // 8 blocks x 144 B
+    static constexpr int PIECES = 1;
+    static constexpr uint32_t STEP_BYTES = 1152;  // 8 blocks x 144 B
+    static __host__ __device__ constexpr uint32_t piece_bytes(int) { return 1152; }
+    static __host__ __device__ constexpr uint32_t piece_off(int) { return 0; }
     static constexpr bool SD = true, S16 = false;
     // a quarter warp reads chunks 16*b + 4*p + j (two blocks b, four p, fixed j)
-    static __device__ __forceinline__ int swz(int c) { return c ^ ((c >> 3) & 7); }
-    int b, p, sh;
+    static __host__ __device__ __forceinline__ int swz(int c) { return c ^ ((c >> 3) & 7); }
+
+    uint32_t blk_off, q_off;   // lane's block and qs bytes inside a slot
+    uint32_t xo[4];            // swizzled byte offsets of the lane's four activation chunks inside a step
+    uint32_t dx_off;           // byte offset of the lane's two block scales inside a step
+    uint32_t selR, selT;       // PRMT selectors of the scale unpack
     bool low;
+    int k_lane;                // element offset of the lane's unit inside a step
+
     __device__ __forceinline__ void init(int lane)
     {
-        b = lane >> 2, p = lane & 3;
-        sh = (p & 1) * 16;
+        const int b = lane >> 2, p = lane & 3, pp = p & 1;
+        blk_off = b * 144;
+        q_off = blk_off + 16 + 32 * p;
+        const int c = 16 * b + 4 * p;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xo[j] = 16 * swz(c + j);  // the permutation never crosses a 128-chunk step
+        dx_off = (8 * b + 2 * p) * 4;
+        selR = (2 * pp) | ((2 * pp + 1) << 4) | ((4 + 2 * pp) << 8) | ((5 + 2 * pp) << 12);
+        selT = (2 * pp) | ((2 * pp + 1) << 4) | ((2 * pp) << 8) | ((2 * pp + 1) << 12);
         low = p < 2;
+        k_lane = b * 256 + 64 * p;
     }
-    template <int MT, bool XS>
-    __device__ __forceinline__ void step(const uint8_t *slot, int part, const XPtrs &xs, const uint8_t *sx, int K, int m0,
-                                         int M, float *acc) const
+
+    template <int MT, bool XS, int SS>
+    __device__ __forceinline__ void step(uint32_t slot, int i, int part, const XCtx &xc, float *acc) const
     {
-        const uint8_t *blk = slot + b * 144;
-        const uint4 hdr = lds16(blk), q0 = lds16(blk + 16 + 32 * p), q1 = lds16(blk + 32 + 32 * p);
-        // scales / mins of sub-blocks 2p (low byte) and 2p+1 (high byte): GetScaleMinK4_* on 16-bit pairs
-        const uint32_t s0 = hdr.y, s1 = hdr.z, s2 = hdr.w;
-        const uint32_t hp = ((low ? s0 : s1) >> sh) & 0xFFFFu;
-        const uint32_t hp2 = ((low ? s1 : s2) >> sh) & 0xFFFFu;
-        const uint32_t hm2 = (s0 >> sh) & 0xFFFFu;
-        const uint32_t sc = low ? (hp & 0x3F3Fu) : ((hp2 & 0x0F0Fu) | ((hm2 >> 2) & 0x3030u));
-        const uint32_t mn = low ? (hp2 & 0x3F3Fu) : (((hp2 >> 4) & 0x0F0Fu) | ((hp >> 2) & 0x3030u));
-        const int sc_lo = sc & 0xFF, sc_hi = sc >> 8;
-        const float mn_lo = (float)(mn & 0xFF), mn_hi = (float)(mn >> 8);
+        slot += i * 1152;
+        const uint4 hdr = lds128(slot + blk_off), q0 = lds128(slot + q_off), q1 = lds128(slot + q_off + 16);
+        // [sc(2p), sc(2p+1), mn(2p), mn(2p+1)] as four bytes (GetScaleMinK4_*): R holds scales[2pp..], scales[4+2pp..];
+        // for sub-blocks >= 4 the low nibbles / high nibbles of T = scales[8+2pp..] are joined with the top two bits of R
+        const uint32_t R = __byte_perm(hdr.y, hdr.z, selR);
+        const uint32_t T = __byte_perm(hdr.w, hdr.w, selT);
+        const uint32_t hi_form = (T & 0x00000F0Fu) | ((T >> 4) & 0x0F0F0000u) | ((R >> 2) & 0x30303030u);
+        const uint32_t sm = low ? (R & 0x3F3F3F3Fu) : hi_form;
+        const int sc_lo = sm & 0xFF, sc_hi = (sm >> 8) & 0xFF;
+        const float mn_lo = (float)((sm >> 16) & 0xFF), mn_hi = (float)(sm >> 24);
         const float d = smc_h2f((uint16_t)(hdr.x & 0xFFFF));
         const float dmin = smc_h2f((uint16_t)(hdr.x >> 16));
         const uint32_t M4 = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u;
-        const int k0 = part * 2048 + b * 256 + 64 * p;
+        const uint32_t l0 = q0.x & M4, l1 = q0.y & M4, l2 = q0.z & M4, l3 = q0.w & M4;
+        const uint32_t l4 = q1.x & M4, l5 = q1.y & M4, l6 = q1.z & M4, l7 = q1.w & M4;
+        const uint32_t h0 = q0.x & MH, h1 = q0.y & MH, h2 = q0.z & MH, h3 = q0.w & MH;
+        const uint32_t h4 = q1.x & MH, h5 = q1.y & MH, h6 = q1.z & MH, h7 = q1.w & MH;
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             uint4 a0, a1, c0, c1;
             float2 dx, sdx;
             if (XS) {
-                const int c = k0 >> 4;
-                a0 = lds16(sx + 16 * swz(c)), a1 = lds16(sx + 16 * swz(c + 1));
-                c0 = lds16(sx + 16 * swz(c + 2)), c1 = lds16(sx + 16 * swz(c + 3));
-                const float *fd = reinterpret_cast<const float *>(sx + K);
-                dx = *reinterpret_cast<const float2 *>(fd + (k0 >> 5));
-                sdx = *reinterpret_cast<const float2 *>(fd + K / 32 + (k0 >> 5));
+                const uint32_t xb = xc.sx + part * 2048;
+                a0 = lds128(xb + xo[0]), a1 = lds128(xb + xo[1]), c0 = lds128(xb + xo[2]), c1 = lds128(xb + xo[3]);
+                const uint32_t db = xc.sx + xc.K + part * 256 + dx_off;
+                const uint2 t0 = lds64(db), t1 = lds64(db + (xc.K >> 3));
+                dx = make_float2(__uint_as_float(t0.x), __uint_as_float(t0.y));
+                sdx = make_float2(__uint_as_float(t1.x), __uint_as_float(t1.y));
             } else {
-                const int mm = min(m0 + m, M - 1);
-                const uint4 *xq = reinterpret_cast<const uint4 *>(xs.q + (size_t)mm * K + k0);
+                const int mm = min(xc.m0 + m, xc.M - 1);
+                const int k0 = part * 2048 + k_lane;
+                const uint4 *xq = reinterpret_cast<const uint4 *>(xc.g.q + (size_t)mm * xc.K + k0);
                 a0 = __ldg(xq), a1 = __ldg(xq + 1), c0 = __ldg(xq + 2), c1 = __ldg(xq + 3);
-                const size_t b32 = (size_t)mm * (K / 32) + (k0 >> 5);
-                dx = __ldg(reinterpret_cast<const float2 *>(xs.d + b32));
-                sdx = __ldg(reinterpret_cast<const float2 *>(xs.sd + b32));
+                const size_t b32 = (size_t)mm * (xc.K / 32) + (k0 >> 5);
+                dx = __ldg(reinterpret_cast<const float2 *>(xc.g.d + b32));
+                sdx = __ldg(reinterpret_cast<const float2 *>(xc.g.sd + b32));
             }
-            int lo = smc_dp4a(q0.x & M4, a0.x, 0);
-            lo = smc_dp4a(q0.y & M4, a0.y, lo);
-            lo = smc_dp4a(q0.z & M4, a0.z, lo);
-            lo = smc_dp4a(q0.w & M4, a0.w, lo);
-            lo = smc_dp4a(q1.x & M4, a1.x, lo);
-            lo = smc_dp4a(q1.y & M4, a1.y, lo);
-            lo = smc_dp4a(q1.z & M4, a1.z, lo);
-            lo = smc_dp4a(q1.w & M4, a1.w, lo);
-            int hi = smc_dp4a_us(q0.x & MH, c0.x, 0);
-            hi = smc_dp4a_us(q0.y & MH, c0.y, hi);
-            hi = smc_dp4a_us(q0.z & MH, c0.z, hi);
-            hi = smc_dp4a_us(q0.w & MH, c0.w, hi);
-            hi = smc_dp4a_us(q1.x & MH, c1.x, hi);
-            hi = smc_dp4a_us(q1.y & MH, c1.y, hi);
-            hi = smc_dp4a_us(q1.z & MH, c1.z, hi);
-            hi = smc_dp4a_us(q1.w & MH, c1.w, hi);
-            hi >>= 4;  // every term carried a factor 16: exact
+            int lo = smc_dp4a(l0, a0.x, 0), lo2 = smc_dp4a(l1, a0.y, 0);
+            lo = smc_dp4a(l2, a0.z, lo), lo2 = smc_dp4a(l3, a0.w, lo2);
+            lo = smc_dp4a(l4, a1.x, lo), lo2 = smc_dp4a(l5, a1.y, lo2);
+            lo = smc_dp4a(l6, a1.z, lo), lo2 = smc_dp4a(l7, a1.w, lo2);
+            int hi = smc_dp4a_us(h0, c0.x, 0), hi2 = smc_dp4a_us(h1, c0.y, 0);
+            hi = smc_dp4a_us(h2, c0.z, hi), hi2 = smc_dp4a_us(h3, c0.w, hi2);
+            hi = smc_dp4a_us(h4, c1.x, hi), hi2 = smc_dp4a_us(h5, c1.y, hi2);
+            hi = smc_dp4a_us(h6, c1.z, hi), hi2 = smc_dp4a_us(h7, c1.w, hi2);
+            lo += lo2;
+            hi = (hi + hi2) >> 4;  // every term carried a factor 16: exact
             const float tsum = fmaf((float)(sc_lo * lo), dx.x, (float)(sc_hi * hi) * dx.y);
             const float msum = fmaf(mn_lo, sdx.x, mn_hi * sdx.y);
             acc[m] = fmaf(d, tsum, acc[m]);
@@ -205,29 +248,49 @@ struct MathQ4K {
     }
 };
 
+// ------------------------------------------------------------------------------------------------ Q6_K
 struct MathQ6K {
     static constexpr int STEP_ELEMS = 2048;
-    static constexpr uint32_t OFF_QH = 1024, OFF_SC = 1536, OFF_D = 1664, SLOT = 1792;
+    static constexpr int PIECES = 4;  // ql, qh, scales, d of 8 blocks
+    static constexpr uint32_t STEP_BYTES = 1680;
+    static __host__ __device__ constexpr uint32_t piece_bytes(int i) { return i == 0 ? 1024 : (i == 1 ? 512 : (i == 2 ? 128 : 16)); }
+    static __host__ __device__ constexpr uint32_t piece_off(int i) { return i == 0 ? 0 : (i == 1 ? 1024 : (i == 2 ? 1536 : 1664)); }
     static constexpr bool SD = false, S16 = true;
     // a quarter warp reads chunks 16*b + 8*h + e + 2*cc (two b, two h, two e, fixed cc)
-    static __device__ __forceinline__ int swz(int c) { return c ^ (((c >> 3) & 3) << 1); }
-    int b, r, h, l0, ssel;
+    static __host__ __device__ __forceinline__ int swz(int c) { return c ^ (((c >> 3) & 3) << 1); }
+
+    uint32_t a_off, h_off, sc_off, d_off;
+    uint32_t xo[4], dx_off, s16_off;
+    int odd, ssel, k_half, l0;
+
     __device__ __forceinline__ void init(int lane)
     {
-        b = lane >> 2, r = lane & 3, h = r >> 1, l0 = 16 * (r & 1);
-        ssel = (r & 1) ? 0 : 16;
+        const int b = lane >> 2, r = lane & 3, h = r >> 1;
+        odd = r & 1;
+        l0 = 16 * odd;
+        a_off = b * 128 + 64 * h + l0;   // offsets inside each piece of one step
+        h_off = b * 64 + 32 * h + l0;
+        sc_off = b * 16 + 8 * h;
+        d_off = 2 * b;
+        const int c = 16 * b + 8 * h + odd;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) xo[cc] = 16 * swz(c + 2 * cc);
+        dx_off = (8 * b + 4 * h) * 4;
+        s16_off = (16 * b + 8 * h) * 2;
+        ssel = odd ? 0 : 16;  // left shift that brings the wanted int16 of a pair to the top
+        k_half = b * 256 + 128 * h;
     }
-    template <int MT, bool XS>
-    __device__ __forceinline__ void step(const uint8_t *slot, int part, const XPtrs &xs, const uint8_t *sx, int K, int m0,
-                                         int M, float *acc) const
+
+    template <int MT, bool XS, int SS>
+    __device__ __forceinline__ void step(uint32_t slot, int i, int part, const XCtx &xc, float *acc) const
     {
-        const uint4 ua = lds16(slot + b * 128 + 64 * h + l0), ub = lds16(slot + b * 128 + 64 * h + 32 + l0);
-        const uint4 uh = lds16(slot + OFF_QH + b * 64 + 32 * h + l0);
-        const uint2 usc = *reinterpret_cast<const uint2 *>(slot + OFF_SC + b * 16 + 8 * h);
-        const float d = smc_h2f(*reinterpret_cast<const uint16_t *>(slot + OFF_D + 2 * b));
+        const uint32_t pa = slot + i * 1024 + a_off;
+        const uint4 ua = lds128(pa), ub = lds128(pa + 32), uh = lds128(slot + SS * 1024 + i * 512 + h_off);
+        const uint2 usc = lds64(slot + SS * 1536 + i * 128 + sc_off);
+        const float d = smc_h2f((uint16_t)lds16u(slot + SS * 1664 + i * 16 + d_off));
         const uint32_t M4 = 0x0F0F0F0Fu, M2 = 0x30303030u;
         const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w}, wh[4] = {uh.x, uh.y, uh.z, uh.w};
-        uint32_t q[4][4];
+        uint32_t q[4][4];  // [column c][word j]: six-bit codes of elements 32c + l0 + 4j .. +3
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             q[0][j] = (wa[j] & M4) | ((wh[j] << 4) & M2);
@@ -235,41 +298,38 @@ struct MathQ6K {
             q[2][j] = ((wa[j] >> 4) & M4) | (wh[j] & M2);
             q[3][j] = ((wb[j] >> 4) & M4) | ((wh[j] >> 2) & M2);
         }
-        const uint32_t sw0 = (r & 1) ? (usc.x >> 8) : usc.x, sw1 = (r & 1) ? (usc.y >> 8) : usc.y;
+        // int8 scales is + {0, 2, 4, 6} with is = l0 / 16: bytes odd, odd+2, odd+4, odd+6 of the half's eight
+        const uint32_t sw0 = odd ? (usc.x >> 8) : usc.x, sw1 = odd ? (usc.y >> 8) : usc.y;
         const int scl[4] = {(int)(int8_t)(sw0 & 0xFF), (int)(int8_t)((sw0 >> 16) & 0xFF), (int)(int8_t)(sw1 & 0xFF),
                             (int)(int8_t)((sw1 >> 16) & 0xFF)};
-        const int kb = part * 2048 + b * 256 + 128 * h;  // start of the 128-half; this lane adds l0
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-            float4 dx;
-            uint4 sw, x[4];
+            uint4 x[4], dxu, sw;
             if (XS) {
-                const int c = (kb + l0) >> 4;
+                const uint32_t xb = xc.sx + part * 2048;
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) x[cc] = lds16(sx + 16 * swz(c + 2 * cc));
-                const float *fd = reinterpret_cast<const float *>(sx + K);
-                dx = *reinterpret_cast<const float4 *>(fd + (kb >> 5));
-                const int16_t *s16 = reinterpret_cast<const int16_t *>(fd + 2 * (K / 32));
-                sw = *reinterpret_cast<const uint4 *>(s16 + (kb >> 4));
+                for (int cc = 0; cc < 4; ++cc) x[cc] = lds128(xb + xo[cc]);
+                dxu = lds128(xc.sx + xc.K + part * 256 + dx_off);
+                sw = lds128(xc.sx + xc.K + (xc.K >> 2) + part * 256 + s16_off);
             } else {
-                const int mm = min(m0 + m, M - 1);
-                const int8_t *xq = xs.q + (size_t)mm * K + kb + l0;
+                const int mm = min(xc.m0 + m, xc.M - 1);
+                const int kb = part * 2048 + k_half;
+                const int8_t *xq = xc.g.q + (size_t)mm * xc.K + kb + l0;
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) x[cc] = __ldg(reinterpret_cast<const uint4 *>(xq + 32 * cc));
-                dx = __ldg(reinterpret_cast<const float4 *>(xs.d + (size_t)mm * (K / 32) + (kb >> 5)));
-                sw = __ldg(reinterpret_cast<const uint4 *>(xs.s16 + (size_t)mm * (K / 16) + (kb >> 4)));
+                dxu = __ldg(reinterpret_cast<const uint4 *>(xc.g.d + (size_t)mm * (xc.K / 32) + (kb >> 5)));
+                sw = __ldg(reinterpret_cast<const uint4 *>(xc.g.s16 + (size_t)mm * (xc.K / 16) + (kb >> 4)));
             }
             const uint32_t sws[4] = {sw.x, sw.y, sw.z, sw.w};
-            const float dxs[4] = {dx.x, dx.y, dx.z, dx.w};
+            const float dxs[4] = {__uint_as_float(dxu.x), __uint_as_float(dxu.y), __uint_as_float(dxu.z),
+                                  __uint_as_float(dxu.w)};
             float rsum = 0.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                int s = smc_dp4a(q[c][0], x[c].x, 0);
-                s = smc_dp4a(q[c][1], x[c].y, s);
-                s = smc_dp4a(q[c][2], x[c].z, s);
-                s = smc_dp4a(q[c][3], x[c].w, s);
+                int s = smc_dp4a(q[c][0], x[c].x, 0), s2 = smc_dp4a(q[c][1], x[c].y, 0);
+                s = smc_dp4a(q[c][2], x[c].z, s), s2 = smc_dp4a(q[c][3], x[c].w, s2);
                 const int sxq = ((int)(sws[c] << ssel)) >> 16;  // sum of the 16 activation quants
-                s -= 32 * sxq;                                   // sum (q - 32) x = sum q x - 32 sum x
+                s = s + s2 - 32 * sxq;                           // sum (q - 32) x = sum q x - 32 sum x
                 rsum = fmaf((float)(scl[c] * s), dxs[c], rsum);
             }
             acc[m] = fmaf(d, rsum, acc[m]);
@@ -277,162 +337,231 @@ struct MathQ6K {
     }
 };
 
+// ------------------------------------------------------------------------------------------------ Q8_0
 struct MathQ8_0 {
     static constexpr int STEP_ELEMS = 1024;
-    static constexpr uint32_t OFF_D = 1024, SLOT = 1152;  // 1024 quants + 32 fp16 scales, padded
+    static constexpr int PIECES = 2;  // 32 blocks of quants, their 32 fp16 scales
+    static constexpr uint32_t STEP_BYTES = 1088;
+    static __host__ __device__ constexpr uint32_t piece_bytes(int i) { return i == 0 ? 1024 : 64; }
+    static __host__ __device__ constexpr uint32_t piece_off(int i) { return i == 0 ? 0 : 1024; }
     static constexpr bool SD = false, S16 = false;
     // lane l reads the two 16-byte halves of block l; lanes 0-3 of a quarter warp take half 0 first and
     // lanes 4-7 half 1 first, which already spreads eight reads over eight bank groups
-    static __device__ __forceinline__ int swz(int c) { return c; }
-    int lane_, sel_;
-    __device__ __forceinline__ void init(int lane) { lane_ = lane, sel_ = (lane >> 2) & 1; }
-    template <int MT, bool XS>
-    __device__ __forceinline__ void step(const uint8_t *slot, int part, const XPtrs &xs, const uint8_t *sx, int K, int m0,
-                                         int M, float *acc) const
+    static __host__ __device__ __forceinline__ int swz(int c) { return c; }
+
+    uint32_t qa_off, qb_off, d_off, dx_off;
+    int sel, k_lane;
+    __device__ __forceinline__ void init(int lane)
     {
-        const int blk = lane_;
-        const uint4 q0 = lds16(slot + 32 * blk + 16 * sel_), q1 = lds16(slot + 32 * blk + 16 * (1 - sel_));
-        const float d = smc_h2f(*reinterpret_cast<const uint16_t *>(slot + OFF_D + 2 * blk));
-        const int k0 = part * 1024 + 32 * blk;
+        sel = (lane >> 2) & 1;
+        qa_off = 32 * lane + 16 * sel;
+        qb_off = 32 * lane + 16 * (1 - sel);
+        d_off = 2 * lane;
+        dx_off = 4 * lane;
+        k_lane = 32 * lane;
+    }
+    template <int MT, bool XS, int SS>
+    __device__ __forceinline__ void step(uint32_t slot, int i, int part, const XCtx &xc, float *acc) const
+    {
+        const uint4 q0 = lds128(slot + i * 1024 + qa_off), q1 = lds128(slot + i * 1024 + qb_off);
+        const float d = smc_h2f((uint16_t)lds16u(slot + SS * 1024 + i * 64 + d_off));
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             uint4 a0, a1;
             float dx;
             if (XS) {
-                const int c = k0 >> 4;
-                a0 = lds16(sx + 16 * (c + sel_)), a1 = lds16(sx + 16 * (c + 1 - sel_));
-                dx = reinterpret_cast<const float *>(sx + K)[k0 >> 5];
+                const uint32_t xb = xc.sx + part * 1024;
+                a0 = lds128(xb + qa_off), a1 = lds128(xb + qb_off);
+                dx = __uint_as_float(lds32(xc.sx + xc.K + part * 128 + dx_off));
             } else {
-                const int mm = min(m0 + m, M - 1);
-                const uint4 *xq = reinterpret_cast<const uint4 *>(xs.q + (size_t)mm * K + k0);
-                a0 = __ldg(xq + sel_), a1 = __ldg(xq + 1 - sel_);
-                dx = __ldg(xs.d + (size_t)mm * (K / 32) + (k0 >> 5));
+                const int mm = min(xc.m0 + m, xc.M - 1);
+                const int k0 = part * 1024 + k_lane;
+                const uint4 *xq = reinterpret_cast<const uint4 *>(xc.g.q + (size_t)mm * xc.K + k0);
+                a0 = __ldg(xq + sel), a1 = __ldg(xq + 1 - sel);
+                dx = __ldg(xc.g.d + (size_t)mm * (xc.K / 32) + (k0 >> 5));
             }
-            int s = smc_dp4a(q0.x, a0.x, 0);
-            s = smc_dp4a(q0.y, a0.y, s);
-            s = smc_dp4a(q0.z, a0.z, s);
-            s = smc_dp4a(q0.w, a0.w, s);
-            s = smc_dp4a(q1.x, a1.x, s);
-            s = smc_dp4a(q1.y, a1.y, s);
-            s = smc_dp4a(q1.z, a1.z, s);
-            s = smc_dp4a(q1.w, a1.w, s);
-            acc[m] = fmaf(d * dx, (float)s, acc[m]);
+            int s = smc_dp4a(q0.x, a0.x, 0), s2 = smc_dp4a(q0.y, a0.y, 0);
+            s = smc_dp4a(q0.z, a0.z, s), s2 = smc_dp4a(q0.w, a0.w, s2);
+            s = smc_dp4a(q1.x, a1.x, s), s2 = smc_dp4a(q1.y, a1.y, s2);
+            s = smc_dp4a(q1.z, a1.z, s), s2 = smc_dp4a(q1.w, a1.w, s2);
+            acc[m] = fmaf(d * dx, (float)(s + s2), acc[m]);
         }
     }
 };
 
 // ------------------------------------------------------------------------------------------------
-template <class Math, int MT>
-__global__ void __launch_bounds__(256, 2) gemv_tma_kernel(StepSrc src_rows, size_t row_stride0, size_t row_stride1,
-                                                          size_t row_stride2, size_t row_stride3, XPtrs xg,
-                                                          float *__restrict__ out, int N, int K, int M, int slots,
-                                                          int *__restrict__ status)
+// Work is handed out in "groups" of whole rows so that a row's partial sums never leave its warp:
+// a stage is SS consecutive steps; when a row is shorter than a stage (spr <= SS) a group is SS/spr
+// rows = one stage, otherwise a group is one row = spr/SS stages.  Warp w of W takes groups
+// w, w + W, w + 2W, ...: at any moment the grid reads one dense window that slides through the matrix.
+template <class Math, int MT, int MINB, int SS>
+__global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs xg, float *__restrict__ out, int N, int K,
+                                                             int M, int slots, int *__restrict__ status)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr bool XS = (MT == 1);
+    constexpr uint32_t SLOT = (Math::STEP_BYTES * SS + 127u) & ~127u;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int m0 = blockIdx.y * MT;
 
-    // shared layout: [x row (MT == 1)] [8 warps x slots x SLOT bytes] [8 warps x slots barriers]
-    const size_t xb = XS ? ((x_bytes(K) + 127) & ~(size_t)127) : 0;
-    uint8_t *ring = smem + xb + (size_t)warp * slots * Math::SLOT;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + xb + (size_t)WARPS * slots * Math::SLOT) + warp * slots;
+    // shared layout: [x row (M = 1)] [8 warps x slots x SLOT bytes] [8 warps x slots barriers]
+    const uint32_t xb = XS ? (uint32_t)((x_bytes(K) + 127) & ~(size_t)127) : 0u;
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t ring = sbase + xb + (uint32_t)(warp * slots) * SLOT;
+    const uint32_t bars = sbase + xb + (uint32_t)(WARPS * slots) * SLOT + (uint32_t)(warp * slots) * 8u;
 
-    int r0, r1;
-    warp_rows(N, r0, r1);
-    const int spr = K / Math::STEP_ELEMS;
-    const int nsteps = (r1 - r0) * spr;
-
-    StepSrc src = src_rows;
-    src.base[0] += (size_t)r0 * row_stride0;
-    src.base[1] += (size_t)r0 * row_stride1;
-    src.base[2] += (size_t)r0 * row_stride2;
-    src.base[3] += (size_t)r0 * row_stride3;
+    const int spr = K / Math::STEP_ELEMS;            // steps per row
+    const int rg = SS >= spr ? SS / spr : 1;         // rows per group
+    const int spg = SS >= spr ? 1 : spr / SS;        // stages per group
+    const int W = gridDim.x * WARPS, w = blockIdx.x * WARPS + warp;
+    const int ngroups = N / rg;
+    const int mine = w < ngroups ? (ngroups - w + W - 1) / W : 0;
+    const int nstages = mine * spg;
 
     if (lane == 0) {
-        for (int s = 0; s < slots; ++s) mbar_init(smem_u32(bars + s), 1);
+        for (int s = 0; s < slots; ++s) mbar_init(bars + 8 * s, 1);
         fence_barrier_init();
     }
     __syncwarp();
+    // producer cursor (lane 0): global index of the next stage to fetch
+    long long pstage = (long long)w * spg;
+    int pin = 0, issued = 0;
+    auto fetch_next = [&](uint32_t saddr, uint32_t bar) {
+        issue_stage<Math, SS>(src, pstage, saddr, bar);
+        ++issued;
+        ++pstage;
+        if (++pin == spg) {
+            pin = 0;
+            pstage += (long long)(W - 1) * spg;
+        }
+    };
     if (lane == 0) {
-        const int pre = nsteps < slots ? nsteps : slots;
-        for (int t = 0; t < pre; ++t) issue_step(src, t, smem_u32(ring + (size_t)t * Math::SLOT), smem_u32(bars + t));
+        const int pre = nstages < slots ? nstages : slots;
+        for (int t = 0; t < pre; ++t) fetch_next(ring + (uint32_t)t * SLOT, bars + 8 * t);
     }
     if (XS) {
-        stage_x<Math>(xg, m0, K, smem, Math::SD, Math::S16);
+        stage_x<Math>(xg, m0, K, smem);
         __syncthreads();
     }
 
     Math math;
     math.init(lane);
+    XCtx xc{sbase, K, m0, M, xg};
     float acc[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m] = 0.f;
 
-    int slot = 0, part = 0, row = r0;
+    int slot = 0, part = 0, row = w * rg, cin = 0;
     uint32_t phase = 0;
-    for (int t = 0; t < nsteps; ++t) {
-        const uint32_t bar = smem_u32(bars + slot);
+    for (int t = 0; t < nstages; ++t) {
+        const uint32_t bar = bars + 8 * slot;
+        const uint32_t saddr = ring + (uint32_t)slot * SLOT;
         if (!mbar_wait(bar, phase)) {
             if (lane == 0) atomicExch(status, 1);
             return;
         }
-        math.template step<MT, XS>(ring + (size_t)slot * Math::SLOT, part, xg, smem, K, m0, M, acc);
+#pragma unroll
+        for (int i = 0; i < SS; ++i) {
+            math.template step<MT, XS, SS>(saddr, i, part, xc, acc);
+            if (++part == spr) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    const float v = warp_sum32(acc[m]);
+                    if (lane == 0 && m0 + m < M) out[(size_t)(m0 + m) * N + row] = v;
+                    acc[m] = 0.f;
+                }
+                part = 0;
+                ++row;
+            }
+        }
         __syncwarp();  // every lane has read the slot: it may be refilled
-        if (lane == 0 && t + slots < nsteps) issue_step(src, t + slots, smem_u32(ring + (size_t)slot * Math::SLOT), bar);
+        if (lane == 0 && issued < nstages) fetch_next(saddr, bar);
         if (++slot == slots) {
             slot = 0;
             phase ^= 1;
         }
-        if (++part == spr) {
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                const float v = warp_sum32(acc[m]);
-                if (lane == 0 && m0 + m < M) out[(size_t)(m0 + m) * N + row] = v;
-                acc[m] = 0.f;
-            }
-            part = 0;
-            ++row;
+        if (++cin == spg) {
+            cin = 0;
+            row += (W - 1) * rg;
         }
     }
 }
 
-int tma_ctas(const smc_ctx *ctx, int N)
+struct Tuning {
+    int slots = 2;        // ring depth per warp, in stages (measured best: 2 x 2 steps, 3 CTAs per SM)
+    int ctas_per_sm = 3;  // resident CTAs the grid is sized for (M = 1)
+    int ss = 2;           // steps per stage (M = 1): 1, 2 or 4
+};
+
+Tuning tuning()
 {
-    const int wmax = ctx->sm_count * 2 * WARPS;
-    int rpw = (N + wmax - 1) / wmax;
-    if (rpw < 1) rpw = 1;
-    int warps = (N + rpw - 1) / rpw;
-    int ctas = (warps + WARPS - 1) / WARPS;
-    return ctas < 1 ? 1 : ctas;
+    static Tuning t = [] {
+        Tuning v;
+        if (const char *e = getenv("SMC_TMA_SLOTS")) v.slots = atoi(e) > 1 ? atoi(e) : v.slots;
+        if (const char *e = getenv("SMC_TMA_CTAS")) v.ctas_per_sm = atoi(e) > 0 ? atoi(e) : v.ctas_per_sm;
+        if (const char *e = getenv("SMC_TMA_SS")) v.ss = atoi(e) > 0 ? atoi(e) : v.ss;
+        return v;
+    }();
+    return t;
+}
+
+template <class Math, int MT, int MINB, int SS>
+void launch_one(smc_ctx *ctx, dim3 grid, size_t smem, cudaStream_t s, const StepSrc &src, const XPtrs &x, float *out, int N,
+                int K, int M, int slots)
+{
+    cudaFuncSetAttribute(gemv_tma_kernel<Math, MT, MINB, SS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gemv_tma_kernel<Math, MT, MINB, SS><<<grid, 256, smem, s>>>(src, x, out, N, K, M, slots, ctx->d_status);
 }
 
 template <class Math>
-int launch_math(smc_ctx *ctx, const StepSrc &src, const size_t *row_stride, const XPtrs &x, float *out, int N, int K,
-                int M, cudaStream_t s)
+int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, int N, int K, int M, cudaStream_t s)
 {
+    const Tuning tn = tuning();
     const int mt = M == 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8));
+    const int spr = K / Math::STEP_ELEMS;
+    // steps per stage: the largest of 4, 2, 1 allowed by the tuning that tiles rows exactly
+    int ss = 1;
+    if (mt == 1)
+        for (int c = 4; c >= 2; c >>= 1) {
+            if (c > tn.ss) continue;
+            const bool tiles = (c >= spr) ? (c % spr == 0 && N % (c / spr) == 0) : (spr % c == 0);
+            if (tiles) {
+                ss = c;
+                break;
+            }
+        }
     const size_t xb = mt == 1 ? ((x_bytes(K) + 127) & ~(size_t)127) : 0;
-    // two CTAs per SM must fit: ~113 KB each
-    const size_t budget = 112 * 1024;
-    int slots = 8;
-    while (slots > 2 && xb + (size_t)WARPS * slots * (Math::SLOT + 8) > budget) --slots;
-    const size_t smem = xb + (size_t)WARPS * slots * (Math::SLOT + 8);
-    if (smem > 220 * 1024) return smc_fail(ctx, SMC_E_UNSUPPORTED, "K = %d needs %zu bytes of shared memory", K, smem);
-    dim3 grid(tma_ctas(ctx, N), (M + mt - 1) / mt);
-#define SMC_TMA_LAUNCH(MTV)                                                                                          \
-    do {                                                                                                             \
-        cudaFuncSetAttribute(gemv_tma_kernel<Math, MTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-        gemv_tma_kernel<Math, MTV><<<grid, 256, smem, s>>>(src, row_stride[0], row_stride[1], row_stride[2],         \
-                                                           row_stride[3], x, out, N, K, M, slots, ctx->d_status);    \
-    } while (0)
-    switch (mt) {
-    case 1: SMC_TMA_LAUNCH(1); break;
-    case 2: SMC_TMA_LAUNCH(2); break;
-    case 4: SMC_TMA_LAUNCH(4); break;
-    default: SMC_TMA_LAUNCH(8); break;
+    const size_t slot_bytes = ((size_t)Math::STEP_BYTES * ss + 127) & ~(size_t)127;
+    int per_sm = mt == 1 ? tn.ctas_per_sm : 2;
+    int slots = tn.slots;
+    // `per_sm` CTAs must fit in the 227 KB of an SM (1 KB per CTA is reserved by the system)
+    auto need = [&](int sl) { return xb + (size_t)WARPS * sl * (slot_bytes + 8); };
+    while (per_sm > 1 && (need(slots) + 1024) * per_sm > 227 * 1024) {
+        if (slots > 3) --slots;
+        else --per_sm;
     }
-#undef SMC_TMA_LAUNCH
+    const size_t smem = need(slots);
+    if (smem > 226 * 1024) return smc_fail(ctx, SMC_E_UNSUPPORTED, "K = %d needs %zu bytes of shared memory", K, smem);
+    const int rg = ss >= spr ? ss / spr : 1;
+    const int ngroups = N / rg;
+    int warps = ctx->sm_count * per_sm * WARPS;
+    if (warps > ngroups) warps = ngroups;
+    dim3 grid((warps + WARPS - 1) / WARPS, (M + mt - 1) / mt);
+    if (mt == 1) {
+        const bool three = per_sm >= 3;
+        if (ss == 4) three ? launch_one<Math, 1, 3, 4>(ctx, grid, smem, s, src, x, out, N, K, M, slots)
+                           : launch_one<Math, 1, 2, 4>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+        else if (ss == 2) three ? launch_one<Math, 1, 3, 2>(ctx, grid, smem, s, src, x, out, N, K, M, slots)
+                                : launch_one<Math, 1, 2, 2>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+        else three ? launch_one<Math, 1, 3, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots)
+                   : launch_one<Math, 1, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+    } else if (mt == 2) {
+        launch_one<Math, 2, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+    } else if (mt == 4) {
+        launch_one<Math, 4, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+    } else {
+        launch_one<Math, 8, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+    }
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
@@ -451,28 +580,18 @@ int smc_launch_gemv_tma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, f
     const int N = w->N, K = w->K, M = a->M;
     XPtrs x{a->q, a->d, a->sd, a->s16};
     StepSrc src{};
-    size_t rs[4] = {0, 0, 0, 0};
     if (w->dtype == SMC_Q4_K) {
-        src.pieces = 1;
-        src.base[0] = w->d_raw, src.bytes[0] = 1152, src.off[0] = 0, src.total = 1152;
-        rs[0] = (size_t)(K / 256) * 144;
-        return launch_math<MathQ4K>(ctx, src, rs, x, out, N, K, M, s);
+        src.base[0] = w->d_raw;
+        return launch_math<MathQ4K>(ctx, src, x, out, N, K, M, s);
     }
     if (w->dtype == SMC_Q6_K) {
-        src.pieces = 4;
-        src.base[0] = w->q6_ql, src.bytes[0] = 1024, src.off[0] = 0;
-        src.base[1] = w->q6_qh, src.bytes[1] = 512, src.off[1] = MathQ6K::OFF_QH;
-        src.base[2] = reinterpret_cast<const uint8_t *>(w->q6_sc), src.bytes[2] = 128, src.off[2] = MathQ6K::OFF_SC;
-        src.base[3] = reinterpret_cast<const uint8_t *>(w->q6_d), src.bytes[3] = 16, src.off[3] = MathQ6K::OFF_D;
-        src.total = 1680;
-        const size_t nb = K / 256;
-        rs[0] = nb * 128, rs[1] = nb * 64, rs[2] = nb * 16, rs[3] = nb * 2;
-        return launch_math<MathQ6K>(ctx, src, rs, x, out, N, K, M, s);
+        src.base[0] = w->q6_ql;
+        src.base[1] = w->q6_qh;
+        src.base[2] = reinterpret_cast<const uint8_t *>(w->q6_sc);
+        src.base[3] = reinterpret_cast<const uint8_t *>(w->q6_d);
+        return launch_math<MathQ6K>(ctx, src, x, out, N, K, M, s);
     }
-    src.pieces = 2;
-    src.base[0] = reinterpret_cast<const uint8_t *>(w->q8_qs), src.bytes[0] = 1024, src.off[0] = 0;
-    src.base[1] = reinterpret_cast<const uint8_t *>(w->q8_d), src.bytes[1] = 64, src.off[1] = MathQ8_0::OFF_D;
-    src.total = 1088;
-    rs[0] = (size_t)K, rs[1] = (size_t)(K / 32) * 2;
-    return launch_math<MathQ8_0>(ctx, src, rs, x, out, N, K, M, s);
+    src.base[0] = reinterpret_cast<const uint8_t *>(w->q8_qs);
+    src.base[1] = reinterpret_cast<const uint8_t *>(w->q8_d);
+    return launch_math<MathQ8_0>(ctx, src, x, out, N, K, M, s);
 }

@@ -86,7 +86,8 @@ class ShardedLinear:
         if self.split.world == 1:
             return local
         gathered = torch.empty((self.split.world, m, self.n_local), dtype=local.dtype, device=local.device)
-        self.dist.all_gather_into_tensor(gathered, local.contiguous())
+        # the flat [G*M, n_local] view is the shape every backend accepts
+        self.dist.all_gather_into_tensor(gathered.view(self.split.world * m, self.n_local), local.contiguous())
         return self.assemble(gathered, out)
 
     def assemble(self, gathered, out=None):
