@@ -357,6 +357,11 @@ static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, fl
             return smc_fail(ctx, SMC_E_UNSUPPORTED,
                             "SMC_ACT_Q8 needs a weight registered with SMC_W_REPACK and K %% %d == 0",
                             w->dtype == SMC_Q8_0 ? 32 : 256);
+        // a single row of moderate length is quantised inside the GEMV kernel while it is staged: one launch,
+        // no scratch.  Longer rows cost every CTA a longer prologue than the separate quantiser launch saves.
+        if (M == 1 && w->K <= 8192 && ctx->use_tma && smc_tma_supported(w, 1) &&
+            (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
+            return smc_launch_gemv_tma_f32in(ctx, d_in, w, d_out, s);
         {
             std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
             if (!have_lock) lock.lock();

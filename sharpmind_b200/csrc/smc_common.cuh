@@ -86,6 +86,8 @@ int smc_launch_gemv_f32(smc_ctx *, const float *x, const smc_weight *, float *ou
 int smc_launch_gemv_q8(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 bool smc_tma_supported(const smc_weight *, int M);
 int smc_launch_gemv_tma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
+int smc_launch_gemv_tma_f32in(smc_ctx *, const float *x, const smc_weight *, float *out, cudaStream_t s);
+int smc_launch_gemv_tma_x(smc_ctx *, const smc_q8act *, const float *xf, const smc_weight *, float *out, cudaStream_t s);
 bool smc_stream_supported(const smc_weight *, int M);
 int smc_launch_gemv_stream(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,

@@ -110,6 +110,7 @@ struct XPtrs {
     const float *d;
     const float *sd;
     const int16_t *s16;
+    const float *xf;  // when set (M = 1): fp32 activations, quantised to Q8_0 while they are staged
 };
 
 // Shared layout of the staged activation row: q | d | sd | s16.  The quants are stored in 16-byte
@@ -130,6 +131,63 @@ __device__ __forceinline__ void stage_x(const XPtrs &g, int m, int K, uint8_t *s
     }
     if (Math::S16)
         for (int i = threadIdx.x; i < K / 16; i += blockDim.x) ss16[i] = __ldg(g.s16 + (size_t)m * (K / 16) + i);
+}
+// Same layout, filled by quantising an fp32 row on the fly: one warp per 32-element block, the rules of
+// QuantizedKVCache.QuantizeRowQ8_0 (d = amax/127, 1 for a zero block, stored through fp16; q = round-half-even(x/d)).
+template <class Math>
+__device__ __forceinline__ void stage_x_quant(const float *x, int K, uint8_t *sx)
+{
+    // Four consecutive lanes share a 32-element block, eight elements each; all loads of a batch are
+    // issued before any arithmetic so the row costs one memory latency, not one per block.
+    float *sdx = reinterpret_cast<float *>(sx + K);
+    float *ssd = sdx + K / 32;
+    int16_t *ss16 = reinterpret_cast<int16_t *>(ssd + K / 32);
+    const int nchunks = K / 8;  // K is a multiple of 1024, so whole warps stay converged
+    constexpr int UB = 4;
+    for (int c0 = threadIdx.x; c0 < nchunks; c0 += UB * blockDim.x) {
+        float4 va[UB], vb[UB];
+#pragma unroll
+        for (int j = 0; j < UB; ++j) {
+            const int c = c0 + j * blockDim.x;
+            if (c < nchunks) {
+                va[j] = __ldg(reinterpret_cast<const float4 *>(x) + 2 * c);
+                vb[j] = __ldg(reinterpret_cast<const float4 *>(x) + 2 * c + 1);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < UB; ++j) {
+            const int c = c0 + j * blockDim.x;
+            if (c < nchunks) {  // uniform per warp: nchunks is a multiple of 128
+                const float v[8] = {va[j].x, va[j].y, va[j].z, va[j].w, vb[j].x, vb[j].y, vb[j].z, vb[j].w};
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                float scale = __fdiv_rn(amax, 127.0f);
+                if (amax == 0.0f) scale = 1.0f;
+                int q[8], s = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    q[i] = max(-128, min(127, __float2int_rn(__fdiv_rn(v[i], scale))));
+                    s += q[i];
+                }
+                uint2 packed;
+                packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+                packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+                *reinterpret_cast<uint2 *>(sx + 16 * Math::swz(c >> 1) + 8 * (c & 1)) = packed;
+                const int s16v = s + __shfl_xor_sync(0xffffffffu, s, 1);
+                const int total = s16v + __shfl_xor_sync(0xffffffffu, s16v, 2);
+                const int blk = c >> 2;
+                if (Math::S16 && (c & 1) == 0) ss16[blk * 2 + ((c >> 1) & 1)] = (int16_t)s16v;
+                if ((c & 3) == 0) {
+                    const float df = __half2float(__float2half_rn(scale));
+                    sdx[blk] = df;
+                    if (Math::SD) ssd[blk] = df * (float)total;
+                }
+            }
+        }
+    }
 }
 __host__ __device__ inline size_t x_bytes(int K) { return (size_t)K + (size_t)(K / 32) * 8 + (size_t)(K / 16) * 2; }
 
@@ -440,7 +498,8 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
         for (int t = 0; t < pre; ++t) fetch_next(ring + (uint32_t)t * SLOT, bars + 8 * t);
     }
     if (XS) {
-        stage_x<Math>(xg, m0, K, smem);
+        if (xg.xf) stage_x_quant<Math>(xg.xf, K, smem);
+        else stage_x<Math>(xg, m0, K, smem);
         __syncthreads();
     }
 
@@ -575,10 +634,24 @@ bool smc_tma_supported(const smc_weight *w, int M)
     return w->K % 2048 == 0 && w->K <= 65536;
 }
 
+// M = 1 with fp32 input: the row is quantised inside the kernel, no scratch buffer is involved.
+int smc_launch_gemv_tma_f32in(smc_ctx *ctx, const float *x, const smc_weight *w, float *out, cudaStream_t s)
+{
+    smc_q8act one{};
+    one.M = 1, one.K = w->K;
+    return smc_launch_gemv_tma_x(ctx, &one, x, w, out, s);
+}
+
 int smc_launch_gemv_tma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *out, cudaStream_t s)
 {
+    return smc_launch_gemv_tma_x(ctx, a, nullptr, w, out, s);
+}
+
+int smc_launch_gemv_tma_x(smc_ctx *ctx, const smc_q8act *a, const float *xf, const smc_weight *w, float *out,
+                          cudaStream_t s)
+{
     const int N = w->N, K = w->K, M = a->M;
-    XPtrs x{a->q, a->d, a->sd, a->s16};
+    XPtrs x{a->q, a->d, a->sd, a->s16, xf};
     StepSrc src{};
     if (w->dtype == SMC_Q4_K) {
         src.base[0] = w->d_raw;
