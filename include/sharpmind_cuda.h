@@ -139,6 +139,19 @@ SMC_API int smc_quantize_q8_dev(smc_ctx *ctx, const float *d_x, int M, int K, sm
 SMC_API int smc_q8act_read(smc_ctx *ctx, const smc_q8act *a, int8_t *q, uint16_t *d_bits);
 /* Matmul on activations already quantised with smc_quantize_q8_dev. */
 SMC_API int smc_qmatmul_q8_dev(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *d_out, void *stream);
+/* The SMC_ACT_Q8 matmul of smc_qmatmul_dev for hosts that must not allocate device memory while they run
+ * (all GPU memory budgeted at start-up, no tolerance for the device-wide synchronisation of cudaMalloc, or
+ * an embedding application that forbids allocation after initialisation).  The quantised activations go
+ * into a fixed buffer inside the library image instead of the context's growable scratch; no allocation
+ * routine is called.  Limit: M * K <= SMC_NOALLOC_MAX_ELEMS activations (SMC_E_RANGE beyond); the buffer
+ * (about 0.75 MB) is resident on every GPU that loads the library until the process exits.  All calls on a
+ * device share it and it keeps the previous call's contents (nothing needs clearing: every entry read is
+ * written first, in stream order); calls that can overlap on one GPU race and must be ordered by the caller.
+ * The first call on a device resolves the buffer's address: make it during set-up, before any stream capture.
+ * This entry point has no counterpart in the reference, whose kernels run on caller-owned host memory. */
+#define SMC_NOALLOC_MAX_ELEMS 524288
+SMC_API int smc_qmatmul_q8_noalloc(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M,
+                                   void *stream);
 /* Per-32-element-block int32 dot sums of weight rows [col0, col1) with row `m` of `a`:
  * d_sums[(c - col0) * K/32 + b].  Verification aid for the integer part of SMC_ACT_Q8. */
 SMC_API int smc_block_isums_dev(smc_ctx *ctx, const smc_q8act *a, int m, const smc_weight *w, int col0, int col1,

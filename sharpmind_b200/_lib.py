@@ -44,6 +44,7 @@ SIGNATURES = {
     "smc_quantize_q8_dev": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "smc_q8act_read": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "smc_qmatmul_q8_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "smc_qmatmul_q8_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "smc_block_isums_dev": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "smc_quantize_weights_dev": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "smc_rmsnorm_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),

@@ -326,6 +326,17 @@ class DeviceOps:
         self.ctx.check(self.lib.smc_qmatmul_q8_dev(self.ctx.h, act.h, w.handle, self._chk(out, t.float32), self._stream()))
         return out
 
+    def qmatmul_q8_noalloc(self, x, w: Weight, out=None):
+        """SMC_ACT_Q8 matmul whose intermediate buffer is a fixed array inside the library: for hosts that
+        may not allocate device memory while serving.  M * K is limited (SMC_NOALLOC_MAX_ELEMS)."""
+        t = self.torch
+        M = x.numel() // w.K
+        if out is None:
+            out = t.empty((M, w.N), dtype=t.float32, device=x.device)
+        self.ctx.check(self.lib.smc_qmatmul_q8_noalloc(self.ctx.h, self._chk(x, t.float32), w.handle,
+                                                       self._chk(out, t.float32), M, self._stream()))
+        return out
+
     def block_isums(self, act: Q8Act, m: int, w: Weight, col0: int, col1: int):
         t = self.torch
         out = t.empty((col1 - col0, w.K // 32), dtype=t.int32, device="cuda")
