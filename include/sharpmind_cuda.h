@@ -198,6 +198,39 @@ SMC_API int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k
 SMC_API int smc_kv_append_dev(smc_ctx *ctx, const float *d_k, const float *d_v, float *d_kcache, float *d_vcache,
                               int batch, int kvHeads, int headDim, int pos, int maxSeq, void *stream);
 
+/* ---- one decode step of a Llama/Qwen-shaped decoder -------------------------------------------
+ * What Transformer.ForwardLastLogits computes for [batch, 1] token ids (SharpMind.Model/Transformer.cs:417-463
+ * -> DecoderArch.Forward Arch/DecoderArch.cs:115-134 -> UnhookedTransformerBlock.Forward
+ * Layers/UnhookedTransformerBlock.cs:12-47 -> AttentionLayer.Forward Layers/Attention/AttentionLayer.cs:260-422,
+ * FfnKernels.Gated Layers/Ffn/FfnKernels.cs:35-59).  Weights are handles registered beforehand; norm vectors are
+ * device pointers; wgu is the fused gate||up matrix [2*ffn, hidden]; lm_head is the Q8_0 [vocab, hidden] table
+ * that also serves as the embedding (tied weights, Transformer.cs:67-73). */
+typedef struct smc_model_desc {
+    int n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_seq;
+    float eps, rope_theta;
+    int neox;     /* RoPE pairing: 1 = (d, d + headDim/2) as for qwen/gemma/phi, 0 = adjacent (AttentionLayer.cs:132-144) */
+    int qk_norm;  /* per-head RMSNorm of Q and K before RoPE (Qwen3, AttentionLayer.cs:284-285) */
+    const smc_weight *const *wq, *const *wk, *const *wv, *const *wo, *const *wgu, *const *wdown; /* [n_layers] */
+    const float *const *norm1, *const *norm2, *const *qnorm, *const *knorm;                        /* [n_layers] */
+    const float *final_norm;
+    const smc_weight *lm_head;
+} smc_model_desc;
+/* Allocates the fp32 KV cache [layer, max_batch, kvHeads, max_seq, headDim] (KVCache.cs:13-14), RoPE tables
+ * and intermediates.  The description's arrays are copied; the weights stay owned by the context. */
+SMC_API int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, smc_model **out);
+SMC_API int smc_model_destroy(smc_ctx *ctx, smc_model *m);
+/* Device pointers of the K and V caches, e.g. to install a prefilled context. */
+SMC_API int smc_model_kv(smc_ctx *ctx, smc_model *m, float **d_k, float **d_v);
+/* Installs a context: d_k / d_v are dense [layers, batch, kvHeads, len, headDim] fp32 and become positions
+ * [0, len) of the cache (what `len` calls of KVCache.Update would have left, KVCache.cs:84-150). */
+SMC_API int smc_model_kv_load(smc_ctx *ctx, smc_model *m, const float *d_k, const float *d_v, int batch, int len,
+                              void *stream);
+/* Runs the step for `batch` lock-step sequences whose new token sits at position `pos` (the cache already
+ * holds positions [0, pos)), writes logits [batch, vocab] and, if d_argmax is not null, the greedy token per
+ * sequence (Sampler.Argmax, Sampler.cs:50-58).  `mode` is one of SMC_ACT_F32 / SMC_ACT_Q8 / SMC_REF_ORDER. */
+SMC_API int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, int pos, int mode,
+                            float *d_logits, int *d_argmax, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

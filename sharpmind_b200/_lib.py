@@ -59,6 +59,11 @@ SIGNATURES = {
     "smc_embed_q8_0_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "smc_sdpa_decode_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_float, c_void_p]),
+    "smc_model_create": (c_int, [c_void_p, c_void_p, c_int, _pp]),
+    "smc_model_destroy": (c_int, [c_void_p, c_void_p]),
+    "smc_model_kv": (c_int, [c_void_p, c_void_p, _pp, _pp]),
+    "smc_model_kv_load": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "smc_decode_step": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "smc_kv_append_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                   c_int, c_void_p]),
 }

@@ -1,0 +1,224 @@
+// One decode step of a Llama/Qwen-shaped decoder, device resident: the order of operations of
+// Transformer.ForwardLastLogits (SharpMind.Model/Transformer.cs:417-463), DecoderArch.Forward
+// (SharpMind.Model/Arch/DecoderArch.cs:115-134), UnhookedTransformerBlock.Forward
+// (SharpMind.Model/Layers/UnhookedTransformerBlock.cs:12-47), AttentionLayer.Forward
+// (SharpMind.Model/Layers/Attention/AttentionLayer.cs:260-422) and FfnKernels.Gated
+// (SharpMind.Model/Layers/Ffn/FfnKernels.cs:35-59), for seqLen = 1 and `batch` lock-step sequences sharing
+// one position (the only batched semantics the reference's KVCache defines, KVCache.cs:21,149).
+// The step is a plain sequence of launches of the kernels in this library on the caller's stream;
+// the KV cache, the RoPE tables and all intermediates are owned by the model object.
+#include <vector>
+
+#include "smc_common.cuh"
+
+struct smc_model {
+    smc_model_desc d{};
+    int max_batch = 0;
+    std::vector<const smc_weight *> wq, wk, wv, wo, wgu, wdown;
+    std::vector<const float *> norm1, norm2, qnorm, knorm;
+    float *kcache = nullptr, *vcache = nullptr;  // [layer][batch][kvHeads][max_seq][head_dim]
+    float *cosT = nullptr, *sinT = nullptr;
+    float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *tmp = nullptr,
+          *gu = nullptr, *act = nullptr;
+    smc_q8act *qa = nullptr, *qb = nullptr;  // quantised activations for batch > 1 (hidden-sized / widest row)
+};
+
+namespace {
+
+void free_model(smc_model *m)
+{
+    if (!m) return;
+    float *bufs[] = {m->kcache, m->vcache, m->cosT, m->sinT, m->x, m->xn, m->q, m->k, m->v, m->att, m->tmp, m->gu, m->act};
+    for (float *p : bufs) cudaFree(p);
+    smc_q8act_free(m->qa);
+    smc_q8act_free(m->qb);
+    delete m;
+}
+
+// y[M, N] = x[M, K] W^T in the requested mode; for SMC_ACT_Q8 with several rows the quantised rows in
+// `pre` (made by the caller from the same x) are reused instead of quantising again.
+int linear(smc_ctx *ctx, const float *x, const smc_weight *w, float *y, int M, int mode, const smc_q8act *pre,
+           cudaStream_t s)
+{
+    if (mode == SMC_ACT_Q8 && pre) return smc_qmatmul_q8_dev(ctx, pre, w, y, s);
+    return smc_qmatmul_dev(ctx, x, w, y, M, mode, s);
+}
+
+// src [layers][batch][kvHeads][len][headDim] dense  ->  cache [layers][max_batch][kvHeads][max_seq][headDim]
+__global__ void kv_load_kernel(const float *__restrict__ src, float *__restrict__ dst, long long total, int batch,
+                               int max_batch, int kvh, int len, int max_seq, int hd)
+{
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+        int d = (int)(t % hd);
+        long long r = t / hd;
+        int p = (int)(r % len);
+        r /= len;
+        int h = (int)(r % kvh);
+        r /= kvh;
+        int b = (int)(r % batch);
+        long long l = r / batch;
+        dst[(((l * max_batch + b) * kvh + h) * max_seq + p) * hd + d] = src[t];
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int smc_model_kv_load(smc_ctx *ctx, smc_model *m, const float *d_k, const float *d_v, int batch, int len, void *stream)
+{
+    if (!ctx || !m || !d_k || !d_v || batch <= 0 || len < 0) return smc_fail(ctx, SMC_E_INVALID, "kv_load: bad arguments");
+    if (batch > m->max_batch || len > m->d.max_seq) return smc_fail(ctx, SMC_E_RANGE, "kv_load: %d x %d exceeds the cache", batch, len);
+    long long total = (long long)m->d.n_layers * batch * m->d.n_kv_heads * len * m->d.head_dim;
+    if (total == 0) return SMC_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int grid = (int)((total + 255) / 256 > ctx->sm_count * 16 ? ctx->sm_count * 16 : (total + 255) / 256);
+    kv_load_kernel<<<grid, 256, 0, s>>>(d_k, m->kcache, total, batch, m->max_batch, m->d.n_kv_heads, len, m->d.max_seq, m->d.head_dim);
+    kv_load_kernel<<<grid, 256, 0, s>>>(d_v, m->vcache, total, batch, m->max_batch, m->d.n_kv_heads, len, m->d.max_seq, m->d.head_dim);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, smc_model **out)
+{
+    if (!ctx || !desc || !out || max_batch <= 0) return smc_fail(ctx, SMC_E_INVALID, "model_create: bad arguments");
+    const smc_model_desc &d = *desc;
+    if (d.n_layers <= 0 || d.hidden <= 0 || d.n_heads <= 0 || d.n_kv_heads <= 0 || d.n_heads % d.n_kv_heads ||
+        d.head_dim <= 0 || (d.head_dim & 1) || d.ffn <= 0 || d.vocab <= 0 || d.max_seq <= 0 || !d.wq || !d.wk || !d.wv ||
+        !d.wo || !d.wgu || !d.wdown || !d.norm1 || !d.norm2 || !d.final_norm || !d.lm_head ||
+        (d.qk_norm && (!d.qnorm || !d.knorm)))
+        return smc_fail(ctx, SMC_E_INVALID, "model_create: incomplete description");
+    if (d.head_dim > 256) return smc_fail(ctx, SMC_E_RANGE, "headDim %d exceeds FlashMaxHeadDim 256", d.head_dim);
+    const int H = d.hidden, qDim = d.n_heads * d.head_dim, kvDim = d.n_kv_heads * d.head_dim, F = d.ffn;
+    auto shape_ok = [&](const smc_weight *w, int n, int k) { return w && w->N == n && w->K == k; };
+    for (int l = 0; l < d.n_layers; ++l) {
+        if (!shape_ok(d.wq[l], qDim, H) || !shape_ok(d.wk[l], kvDim, H) || !shape_ok(d.wv[l], kvDim, H) ||
+            !shape_ok(d.wo[l], H, qDim) || !shape_ok(d.wgu[l], 2 * F, H) || !shape_ok(d.wdown[l], H, F))
+            return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "model_create: layer %d weight shapes do not match the description", l);
+    }
+    if (!shape_ok(d.lm_head, d.vocab, H) || d.lm_head->dtype != SMC_Q8_0)
+        return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "model_create: lm_head / embedding must be a Q8_0 [vocab, hidden] tensor");
+
+    cudaSetDevice(ctx->device);
+    smc_model *m = new smc_model();
+    m->d = d;
+    m->max_batch = max_batch;
+    auto copy_w = [&](std::vector<const smc_weight *> &dst, const smc_weight *const *src) { dst.assign(src, src + d.n_layers); };
+    auto copy_f = [&](std::vector<const float *> &dst, const float *const *src) {
+        if (src) dst.assign(src, src + d.n_layers);
+    };
+    copy_w(m->wq, d.wq), copy_w(m->wk, d.wk), copy_w(m->wv, d.wv), copy_w(m->wo, d.wo), copy_w(m->wgu, d.wgu),
+        copy_w(m->wdown, d.wdown);
+    copy_f(m->norm1, d.norm1), copy_f(m->norm2, d.norm2), copy_f(m->qnorm, d.qnorm), copy_f(m->knorm, d.knorm);
+    const size_t B = (size_t)max_batch;
+    const size_t cache = (size_t)d.n_layers * B * d.n_kv_heads * d.max_seq * d.head_dim;
+    const size_t half = (size_t)d.max_seq * (d.head_dim / 2);
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](float **p, size_t n) {
+        if (e == cudaSuccess) e = cudaMalloc(p, n * sizeof(float));
+    };
+    alloc(&m->kcache, cache), alloc(&m->vcache, cache), alloc(&m->cosT, half), alloc(&m->sinT, half);
+    alloc(&m->x, B * H), alloc(&m->xn, B * H), alloc(&m->q, B * qDim), alloc(&m->k, B * kvDim), alloc(&m->v, B * kvDim);
+    alloc(&m->att, B * qDim), alloc(&m->tmp, B * H), alloc(&m->gu, B * 2 * F), alloc(&m->act, B * F);
+    if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache * sizeof(float));
+    if (e != cudaSuccess) {
+        free_model(m);
+        return smc_fail(ctx, SMC_E_CUDA, "model_create: allocation failed: %s", cudaGetErrorString(e));
+    }
+    int rc = 0;
+    if (H % 32 == 0) rc = smc_q8act_alloc(ctx, max_batch, H, &m->qa);
+    const int wide = qDim > F ? qDim : F;
+    if (!rc && wide % 32 == 0) rc = smc_q8act_alloc(ctx, max_batch, wide, &m->qb);
+    if (rc) {
+        free_model(m);
+        return rc;
+    }
+    rc = smc_rope_tables(ctx, d.rope_theta, d.head_dim, d.max_seq, m->cosT, m->sinT);
+    if (rc) {
+        free_model(m);
+        return rc;
+    }
+    *out = m;
+    return SMC_OK;
+}
+
+int smc_model_destroy(smc_ctx *ctx, smc_model *m)
+{
+    if (!ctx || !m) return smc_fail(ctx, SMC_E_INVALID, "model_destroy: bad arguments");
+    cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
+    free_model(m);
+    return SMC_OK;
+}
+
+int smc_model_kv(smc_ctx *ctx, smc_model *m, float **d_k, float **d_v)
+{
+    if (!ctx || !m || !d_k || !d_v) return smc_fail(ctx, SMC_E_INVALID, "model_kv: bad arguments");
+    *d_k = m->kcache;
+    *d_v = m->vcache;
+    return SMC_OK;
+}
+
+int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, int pos, int mode, float *d_logits,
+                    int *d_argmax, void *stream)
+{
+    if (!ctx || !m || !d_tokens || !d_logits || batch <= 0) return smc_fail(ctx, SMC_E_INVALID, "decode_step: bad arguments");
+    if (batch > m->max_batch) return smc_fail(ctx, SMC_E_RANGE, "decode_step: batch %d exceeds the model's %d", batch, m->max_batch);
+    const smc_model_desc &d = m->d;
+    if (pos < 0 || pos + 1 > d.max_seq)  // KVCache.Update throws on overflow (KVCache.cs:89-91)
+        return smc_fail(ctx, SMC_E_RANGE, "KVCache overflow: position %d + seqLen 1 exceeds capacity %d", pos, d.max_seq);
+    if (mode != SMC_ACT_F32 && mode != SMC_ACT_Q8 && mode != SMC_REF_ORDER)
+        return smc_fail(ctx, SMC_E_INVALID, "decode_step: unknown mode %d", mode);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int H = d.hidden, nh = d.n_heads, nkv = d.n_kv_heads, hd = d.head_dim, F = d.ffn;
+    const int qDim = nh * hd, kvDim = nkv * hd, B = batch;
+    const float scale = 1.0f / sqrtf((float)hd);
+    const size_t layer_stride = (size_t)m->max_batch * nkv * d.max_seq * hd;
+    // several rows in SMC_ACT_Q8: quantise an activation once and feed every matmul that reads it
+    const bool reuse = mode == SMC_ACT_Q8 && B > 1 && m->qa && m->qb;
+    int rc;
+#define SMC_TRY(call)        \
+    do {                     \
+        rc = (call);         \
+        if (rc) return rc;   \
+    } while (0)
+
+    SMC_TRY(smc_embed_q8_0_dev(ctx, d.lm_head, d_tokens, B, m->x, s));
+    for (int l = 0; l < d.n_layers; ++l) {
+        SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm1[l], m->xn, B, H, d.eps, s));
+        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
+        SMC_TRY(linear(ctx, m->xn, m->wq[l], m->q, B, mode, reuse ? m->qa : nullptr, s));
+        SMC_TRY(linear(ctx, m->xn, m->wk[l], m->k, B, mode, reuse ? m->qa : nullptr, s));
+        SMC_TRY(linear(ctx, m->xn, m->wv[l], m->v, B, mode, reuse ? m->qa : nullptr, s));
+        if (d.qk_norm) {
+            SMC_TRY(smc_rmsnorm_dev(ctx, m->q, m->qnorm[l], m->q, B * nh, hd, d.eps, s));
+            SMC_TRY(smc_rmsnorm_dev(ctx, m->k, m->knorm[l], m->k, B * nkv, hd, d.eps, s));
+        }
+        // every sequence is one token at position `pos`: [1, B*heads, headDim] with offset pos
+        SMC_TRY(smc_rope_dev(ctx, m->q, 1, B * nh, hd, hd, pos, m->cosT, m->sinT, d.neox, s));
+        SMC_TRY(smc_rope_dev(ctx, m->k, 1, B * nkv, hd, hd, pos, m->cosT, m->sinT, d.neox, s));
+        float *kc = m->kcache + (size_t)l * layer_stride, *vc = m->vcache + (size_t)l * layer_stride;
+        SMC_TRY(smc_kv_append_dev(ctx, m->k, m->v, kc, vc, B, nkv, hd, pos, d.max_seq, s));
+        SMC_TRY(smc_sdpa_decode_dev(ctx, m->q, kc, vc, m->att, B, nh, nkv, hd, pos + 1, d.max_seq, scale, s));
+        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->att, B, qDim, m->qb, s));
+        SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s));
+        SMC_TRY(smc_add_dev(ctx, m->x, m->tmp, (int64_t)B * H, s));
+        SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm2[l], m->xn, B, H, d.eps, s));
+        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
+        SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, B, mode, reuse ? m->qa : nullptr, s));
+        SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, B, F, 2 * F, s));
+        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->act, B, F, m->qb, s));
+        SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s));
+        SMC_TRY(smc_add_dev(ctx, m->x, m->tmp, (int64_t)B * H, s));
+    }
+    SMC_TRY(smc_rmsnorm_dev(ctx, m->x, d.final_norm, m->x, B, H, d.eps, s));
+    if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->x, B, H, m->qa, s));
+    SMC_TRY(linear(ctx, m->x, d.lm_head, d_logits, B, mode, reuse ? m->qa : nullptr, s));
+    if (d_argmax) SMC_TRY(smc_argmax_dev(ctx, d_logits, B, d.vocab, d_argmax, s));
+#undef SMC_TRY
+    return SMC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,131 @@
+"""Times the device-resident decode step on the Qwen3-0.6B-shaped configuration (Q8_0 weights, fp32 KV).
+
+    python -m sharpmind_b200.profile_decode [--batches 1,8,32] [--ctx 2048] [--steps 64] [--modes q8,f32]
+                                            [--layers 28] [--once]
+
+Weights are seeded normal(0, 0.02) values quantised on the device, the context is `ctx` positions of
+seeded normal K/V installed with kv_load (no prompt is run: the step's cost depends on the context length
+only), and every timed step decodes one token per sequence at position `ctx`.  Two timings are printed per
+(batch, mode): plain launches on a stream, and the same step captured once in a CUDA graph and replayed.
+`--once` runs a single untimed step per case (for a profiler).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+from . import ops, synth
+from .decoder import Decoder
+
+MODES = {"q8": ops.Mode.ACT_Q8, "f32": ops.Mode.ACT_F32}
+
+
+def device_weights(dev: ops.DeviceOps, cfg: dict, seed: int = 1234) -> dict:
+    import torch
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    L, H, hd = cfg["n_layers"], cfg["hidden"], cfg["head_dim"]
+    q_dim, kv_dim, F, V, dt = cfg["n_heads"] * hd, cfg["n_kv_heads"] * hd, cfg["ffn"], cfg["vocab"], cfg["dtype"]
+
+    def mat(n, k):
+        return dev.quantize_weights(dt, torch.randn((n, k), generator=g, device="cuda") * 0.02)
+
+    def vec(n):
+        return torch.randn(n, generator=g, device="cuda") * 0.1 + 1.0
+
+    w = {k: [] for k in ("wq", "wk", "wv", "wo", "wgu", "wdown", "norm1", "norm2", "qnorm", "knorm")}
+    for _ in range(L):
+        w["wq"].append(mat(q_dim, H)), w["wk"].append(mat(kv_dim, H)), w["wv"].append(mat(kv_dim, H))
+        w["wo"].append(mat(H, q_dim)), w["wgu"].append(mat(2 * F, H)), w["wdown"].append(mat(H, F))
+        w["norm1"].append(vec(H)), w["norm2"].append(vec(H)), w["qnorm"].append(vec(hd)), w["knorm"].append(vec(hd))
+    w["final_norm"] = vec(H)
+    w["embedding"] = mat(V, H)
+    return w
+
+
+def step_bytes(cfg: dict, batch: int, ctx: int) -> dict:
+    """Bytes one step has to read: every weight block once, and the K/V rows of the context per sequence."""
+    L, H, hd = cfg["n_layers"], cfg["hidden"], cfg["head_dim"]
+    q_dim, kv_dim, F, V = cfg["n_heads"] * hd, cfg["n_kv_heads"] * hd, cfg["ffn"], cfg["vocab"]
+    per_layer = (q_dim * H + 2 * kv_dim * H + H * q_dim + 2 * F * H + H * F) // 32 * 34
+    weights = L * per_layer + V * H // 32 * 34
+    kv = L * batch * 2 * cfg["n_kv_heads"] * (ctx + 1) * hd * 4
+    return {"weights": weights, "kv": kv}
+
+
+def main():
+    import torch
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batches", default="1,8,32")
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--modes", default="q8,f32")
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--once", action="store_true")
+    a = ap.parse_args()
+    cfg = dict(synth.QWEN3_0_6B)
+    if a.layers:
+        cfg["n_layers"] = a.layers
+    batches = [int(b) for b in a.batches.split(",")]
+    ctx = ops.CudaContext(0)
+    dev = ops.DeviceOps(ctx)
+    w = device_weights(dev, cfg)
+    dec = Decoder(ctx, cfg, w, max_batch=max(batches))
+    g = torch.Generator(device="cuda")
+    g.manual_seed(99)
+    shape = (cfg["n_layers"], max(batches), cfg["n_kv_heads"], a.ctx, cfg["head_dim"])
+    dec.load_kv(torch.randn(shape, generator=g, device="cuda"), torch.randn(shape, generator=g, device="cuda"))
+    torch.cuda.synchronize()
+    for B in batches:
+        tok = torch.randint(0, cfg["vocab"], (B,), generator=g, device="cuda", dtype=torch.int32)
+        logits = torch.empty((B, cfg["vocab"]), device="cuda")
+        nxt = torch.empty(B, dtype=torch.int32, device="cuda")
+        for name in a.modes.split(","):
+            mode = MODES[name]
+            if a.once:
+                dec.step(tok, a.ctx, mode, logits, nxt)
+                torch.cuda.synchronize()
+                continue
+            for _ in range(3):
+                dec.step(tok, a.ctx, mode, logits, nxt)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(a.steps):
+                dec.step(tok, a.ctx, mode, logits, nxt)
+            e1.record()
+            torch.cuda.synchronize()
+            plain_ms = e0.elapsed_time(e1) / a.steps
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                dec.step(tok, a.ctx, mode, logits, nxt)
+                side.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    dec.step(tok, a.ctx, mode, logits, nxt)
+            torch.cuda.synchronize()
+            for _ in range(3):
+                graph.replay()
+            e0.record()
+            for _ in range(a.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            graph_ms = e0.elapsed_time(e1) / a.steps
+            by = step_bytes(cfg, B, a.ctx)
+            print(json.dumps({
+                "batch": B, "mode": name, "ctx": a.ctx, "layers": cfg["n_layers"],
+                "plain_ms_per_step": round(plain_ms, 4), "graph_ms_per_step": round(graph_ms, 4),
+                "tokens_per_s_plain": round(B / plain_ms * 1e3, 1), "tokens_per_s_graph": round(B / graph_ms * 1e3, 1),
+                "weight_MB": round(by["weights"] / 1e6, 1), "kv_MB": round(by["kv"] / 1e6, 1),
+                "GBps_graph": round((by["weights"] + by["kv"]) / graph_ms / 1e6, 1),
+                "device_status": ctx.device_status(),
+            }), flush=True)
+    dec.close()
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()

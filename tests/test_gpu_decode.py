@@ -1,0 +1,131 @@
+"""Device-resident decode step against the oracle's restatement of the decoder forward
+(Transformer.ForwardLastLogits with one new token per sequence, greedy sampling).
+
+The model is a reduced Qwen3-shaped decoder (QK-norm, NEOX RoPE, GQA, SwiGLU, tied Q8_0 LM head) with
+seeded random weights; the bar is top-1 token agreement over a run of greedy steps and logits within
+1e-4 of the logit scale (the sum of ~10 ops per layer each held to 1e-5).
+"""
+import numpy as np
+import pytest
+
+from sharpmind_b200 import ops, synth
+from sharpmind_b200.decoder import Decoder
+from tests.gpu_util import to_dev
+
+pytestmark = pytest.mark.gpu
+
+SMALL = dict(n_layers=3, hidden=256, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=2048,
+             max_seq=64, dtype=8, eps=1e-6, rope_theta=1.0e6, neox=True, qk_norm=True)
+LLAMA_LIKE = dict(n_layers=2, hidden=256, n_heads=8, n_kv_heads=8, head_dim=64, ffn=768, vocab=1024,
+                  max_seq=48, dtype=8, eps=1e-5, rope_theta=1.0e4, neox=False, qk_norm=False)
+
+
+def _weights(oracle, cfg, name):
+    return synth.make_decoder_weights(cfg, name, oracle.quantize)
+
+
+def _greedy(oracle, cuda, cfg, name, batch, steps, mode):
+    import torch
+
+    w = _weights(oracle, cfg, name)
+    ref = oracle.Decoder(cfg, w, batch)
+    dec = Decoder(cuda, cfg, w, max_batch=batch, keep_raw=(mode == ops.Mode.REF_ORDER))
+    tok_ref = synth.token_ids(name, "prompt", (batch,), cfg["vocab"])
+    tok_dev = torch.from_numpy(tok_ref.copy()).cuda()
+    worst, match = 0.0, 0
+    for pos in range(steps):
+        want = ref.step(tok_ref, pos)
+        logits, nxt = dec.step(tok_dev, pos, mode)
+        got = logits.cpu().numpy()
+        scale = np.abs(want).max(axis=1, keepdims=True)
+        worst = max(worst, float(np.max(np.abs(got - want) / scale)))
+        pick = want.argmax(axis=1).astype(np.int32)
+        assert np.array_equal(nxt.cpu().numpy(), got.argmax(axis=1).astype(np.int32))  # device argmax = first max
+        match += int(np.array_equal(nxt.cpu().numpy(), pick))
+        # teacher forcing on the oracle's token keeps both sides on one trajectory
+        tok_ref = pick
+        tok_dev = torch.from_numpy(pick.copy()).cuda()
+    dec.close()
+    return worst, match
+
+
+@pytest.mark.parametrize("cfg,name", [(SMALL, "dec_small"), (LLAMA_LIKE, "dec_llama")])
+@pytest.mark.parametrize("mode", [ops.Mode.ACT_F32, ops.Mode.REF_ORDER])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_decode_matches_oracle_tokens(oracle, cuda, cfg, name, mode, batch):
+    steps = 20
+    worst, match = _greedy(oracle, cuda, cfg, name, batch, steps, mode)
+    assert match == steps, f"top-1 matched on {match}/{steps} steps"
+    assert worst <= 1e-4, worst
+
+
+@pytest.mark.parametrize("batch", [1, 4])
+def test_decode_quantised_activations_track_oracle(oracle, cuda, batch):
+    """ACT_Q8 re-quantises every activation row to Q8_0, so logits move by ~1e-2 of their scale; the
+    greedy token still has to agree wherever the oracle's top-2 margin exceeds that noise."""
+    import torch
+
+    cfg, name, steps = SMALL, "dec_small", 16
+    w = _weights(oracle, cfg, name)
+    ref = oracle.Decoder(cfg, w, batch)
+    dec = Decoder(cuda, cfg, w, max_batch=batch)
+    tok = synth.token_ids(name, "prompt", (batch,), cfg["vocab"])
+    for pos in range(steps):
+        want = ref.step(tok, pos)
+        logits, nxt = dec.step(torch.from_numpy(tok.copy()).cuda(), pos, ops.Mode.ACT_Q8)
+        got = logits.cpu().numpy()
+        scale = np.abs(want).max(axis=1)
+        assert np.all(np.abs(got - want).max(axis=1) <= 0.05 * scale)
+        top2 = np.sort(want, axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 0.1 * scale
+        pick = want.argmax(axis=1).astype(np.int32)
+        assert np.array_equal(nxt.cpu().numpy()[clear], pick[clear])
+        tok = pick
+    dec.close()
+
+
+def test_decode_batch_rows_are_independent(oracle, cuda):
+    """Lock-step sequences do not interact: row b of a batch of 4 equals the same sequence decoded alone."""
+    import torch
+
+    cfg, name = SMALL, "dec_small"
+    w = _weights(oracle, cfg, name)
+    toks = synth.token_ids(name, "rows", (6, 4), cfg["vocab"])
+    both = Decoder(cuda, cfg, w, max_batch=4)
+    outs = [both.step(to_dev(toks[p]), p, ops.Mode.ACT_F32)[0].cpu().numpy() for p in range(6)]
+    both.close()
+    solo = Decoder(cuda, cfg, w, max_batch=1)
+    for p in range(6):
+        got = solo.step(to_dev(toks[p, 2:3]), p, ops.Mode.ACT_F32)[0].cpu().numpy()
+        scale = np.abs(got).max()
+        assert np.max(np.abs(got[0] - outs[p][2])) <= 1e-5 * scale
+    solo.close()
+
+
+def test_decode_kv_load_equals_stepping(oracle, cuda):
+    """A context installed with kv_load gives the same next-token logits as the oracle that stepped through it."""
+    import torch
+
+    cfg, name, batch, ctx_len = SMALL, "dec_small", 2, 9
+    w = _weights(oracle, cfg, name)
+    ref = oracle.Decoder(cfg, w, batch)
+    toks = synth.token_ids(name, "kvload", (ctx_len + 1, batch), cfg["vocab"])
+    for p in range(ctx_len):
+        ref.step(toks[p], p)
+    want = ref.step(toks[ctx_len], ctx_len)
+    dec = Decoder(cuda, cfg, w, max_batch=batch)
+    dec.load_kv(to_dev(ref.kcache[:, :, :, :ctx_len]), to_dev(ref.vcache[:, :, :, :ctx_len]))
+    got = dec.step(to_dev(toks[ctx_len]), ctx_len, ops.Mode.ACT_F32)[0].cpu().numpy()
+    assert np.max(np.abs(got - want)) <= 1e-4 * np.abs(want).max()
+    dec.close()
+
+
+def test_decode_rejects_bad_arguments(oracle, cuda):
+    cfg, name = LLAMA_LIKE, "dec_llama"
+    dec = Decoder(cuda, cfg, _weights(oracle, cfg, name), max_batch=2)
+    tok = to_dev(np.zeros(3, np.int32))
+    with pytest.raises(ops.SharpMindCudaError):
+        dec.step(tok, 0)                       # batch 3 > max_batch 2
+    with pytest.raises(ops.SharpMindCudaError):
+        dec.step(tok[:2], cfg["max_seq"])      # position past the cache (KVCache.Update throws)
+    dec.close()
