@@ -59,6 +59,8 @@ def parse():
     ap.add_argument("--mode", default="q8", choices=["q8", "f32"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: exchange inside the GEMV kernel over peer memory, or a library all-gather per matmul")
     ap.add_argument("--no-extras", action="store_true", help="skip the batch sweep / e2e / cpu baseline")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     return ap.parse_args()
@@ -231,7 +233,7 @@ def run_ours(args):
         dist = None
         torch.cuda.set_device(local)
     from sharpmind_b200 import ops
-    from sharpmind_b200.sharded import RowSplit
+    from sharpmind_b200.sharded import PeerGather, RowSplit
 
     ctx = ops.CudaContext(local)
     dev = ops.DeviceOps(ctx)
@@ -275,11 +277,22 @@ def run_ours(args):
         return xs, acts, outs, gathered
 
     comm_stream = torch.cuda.Stream() if world > 1 else None
+    peer = world > 1 and args.gather == "peer"
+    gathers = {}
+
+    def gather_for(M, mi):
+        # one receive buffer per (batch, matrix): the exchange runs inside the GEMV kernel over peer memory
+        if (M, mi) not in gathers:
+            gathers[(M, mi)] = PeerGather(ctx, split, world * M * weights[0][mi].N, dist)
+        return gathers[(M, mi)]
 
     def step(state, M):
         xs, acts, outs, gathered = state
         for layer in range(L):
             for mi, w in enumerate(weights[layer]):
+                if peer:
+                    gather_for(M, mi).matmul(xs[mi], w, mode)
+                    continue
                 if mode == ops.Mode.ACT_Q8 and M > 1:
                     dev.quantize_q8(xs[mi], acts[mi], w.K)
                     dev.qmatmul_q8(acts[mi], w, out=outs[mi])
@@ -300,13 +313,19 @@ def run_ours(args):
 
     def launches_per_step(M):
         # M = 1 rows up to K = 8192 are quantised inside the GEMV kernel; otherwise a quantiser launch precedes it
-        return L * sum(2 if (mode == ops.Mode.ACT_Q8 and (M > 1 or k > 8192)) else 1 for _, _, _, k in mats)
+        per = sum(2 if (mode == ops.Mode.ACT_Q8 and (M > 1 or k > 8192)) else 1 for _, _, _, k in mats)
+        if peer and not (mode == ops.Mode.ACT_Q8 and M == 1):
+            per += len(mats)  # the exchange is a launch of its own unless it rides in the one-row GEMV's tail
+        return L * per
 
     def timed(M, steps, warmup, use_graph):
         state = make_state(M)
         runner = lambda: step(state, M)  # noqa: E731
         graph = None
-        if use_graph and world == 1:
+        if peer:
+            for mi in range(len(mats)):
+                gather_for(M, mi)  # created (and peers mapped) on every rank before anything is timed or captured
+        if use_graph and (world == 1 or peer):
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
@@ -359,7 +378,9 @@ def run_ours(args):
                    "weight_bytes": sum(raw_bytes(dt, n, k) for _, dt, n, k in mats) * L,
                    "l2": f"{L} distinct layers ({step_bytes / 1e9:.2f} GB per step) >> 126 MB L2",
                    "cuda_graph": graphed,
-                   "parallelism": "single GPU" if world == 1 else f"row-split x{world} + NCCL all-gather"},
+                   "parallelism": "single GPU" if world == 1 else (
+                       f"row-split x{world}, slices exchanged by the GEMV kernel over NVLink peer memory" if peer
+                       else f"row-split x{world} + NCCL all-gather")},
         "pct_of_8TBs_nominal": value / 8000.0 * 100.0 / world,
         "gpu_launches": launches_per_step(M) * args.steps,
         "clocks": clocks,

@@ -231,6 +231,34 @@ SMC_API int smc_model_kv_load(smc_ctx *ctx, smc_model *m, const float *d_k, cons
 SMC_API int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, int pos, int mode,
                             float *d_logits, int *d_argmax, void *stream);
 
+/* ---- row-split matmul across GPUs -----------------------------------------------------------
+ * No reference counterpart: SharpMind runs one device per process (Accelerator selection in
+ * SharpMind.GPU/GPUDevice.cs); these entry points exist for the sharded large-matrix configurations.
+ * One process per GPU holds the rows [rank * N / world, (rank + 1) * N / world) of a matrix as an
+ * ordinary registered weight.  A gather object owns this rank's receive buffer: `world` chunks of
+ * `count` floats, chunk r being rank r's output slice ([M, N_local] row-major).  Peers map each other's
+ * buffers through CUDA IPC: every rank exports a 64-byte handle, the host exchanges them by any means
+ * (one all-gather of bytes at start-up) and calls connect with all of them in rank order.  The exchange
+ * itself moves no data through the host or a collective library: the producing kernel stores its slice
+ * into every peer's buffer over NVLink and returns when every peer's slice has arrived here.
+ * All ranks must issue the same sequence of exchanges on an object; calls on one object must not overlap
+ * (one stream).  A peer that does not show up within 2 s raises smc_device_status (value 2). */
+typedef struct smc_gather smc_gather;
+#define SMC_IPC_HANDLE_BYTES 64
+SMC_API int smc_gather_create(smc_ctx *ctx, int rank, int world, size_t capacity_floats, smc_gather **out);
+SMC_API int smc_gather_export(smc_ctx *ctx, smc_gather *g, unsigned char *handle /* [64] */);
+SMC_API int smc_gather_connect(smc_ctx *ctx, smc_gather *g, const unsigned char *handles /* [world][64] */);
+/* Device address of the receive buffer (chunk r at d_buf + r * count for an exchange of `count` floats). */
+SMC_API int smc_gather_buffer(smc_ctx *ctx, smc_gather *g, float **d_buf);
+/* y_local = x W_local^T written as this rank's chunk, then exchanged; on return of the launch's completion
+ * the buffer holds [world][M][N_local].  Same modes and errors as smc_qmatmul_dev. */
+SMC_API int smc_qmatmul_gather_dev(smc_ctx *ctx, smc_gather *g, const float *d_in, const smc_weight *w_local, int M,
+                                   int mode, void *stream);
+/* Exchange alone: this rank's chunk (count floats at d_buf + rank * count) was written by earlier work on
+ * `stream`. */
+SMC_API int smc_gather_exchange_dev(smc_ctx *ctx, smc_gather *g, size_t count, void *stream);
+SMC_API int smc_gather_destroy(smc_ctx *ctx, smc_gather *g);
+
 #ifdef __cplusplus
 }
 #endif

@@ -342,8 +342,10 @@ int smc_qmatmul_q8_dev(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, fl
     return smc_launch_gemv_q8(ctx, a, w, d_out, static_cast<cudaStream_t>(stream));
 }
 
+// `gd` (row-split across GPUs): when the one-row TMA kernel runs, it also exchanges the output slice with the
+// peers and *fused is set; otherwise the caller launches the exchange after this returns.
 static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, int mode,
-                        cudaStream_t s, bool have_lock)
+                        cudaStream_t s, bool have_lock, const smc_gather_dev *gd = nullptr, bool *fused = nullptr)
 {
     switch (mode) {
     case SMC_REF_ORDER: return smc_launch_gemv_ref(ctx, d_in, w, d_out, M, 0, w->N, s);
@@ -360,8 +362,11 @@ static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, fl
         // a single row of moderate length is quantised inside the GEMV kernel while it is staged: one launch,
         // no scratch.  Longer rows cost every CTA a longer prologue than the separate quantiser launch saves.
         if (M == 1 && w->K <= 8192 && ctx->use_tma && smc_tma_supported(w, 1) &&
-            (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
-            return smc_launch_gemv_tma_f32in(ctx, d_in, w, d_out, s);
+            (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) {
+            if (!gd) return smc_launch_gemv_tma_f32in(ctx, d_in, w, d_out, s);
+            *fused = true;
+            return smc_launch_gemv_tma_gather(ctx, d_in, w, d_out, gd, s);
+        }
         {
             std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
             if (!have_lock) lock.lock();
@@ -380,6 +385,10 @@ static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, fl
         }
         int rc = smc_launch_quantize_q8(ctx, d_in, M, w->K, ctx->act, s);
         if (rc) return rc;
+        if (gd && M == 1 && ctx->use_tma && smc_tma_supported(w, 1)) {
+            *fused = true;
+            return smc_launch_gemv_tma_xg(ctx, ctx->act, nullptr, w, d_out, gd, s);
+        }
         return smc_launch_gemv_q8(ctx, ctx->act, w, d_out, s);
     }
     default: return smc_fail(ctx, SMC_E_INVALID, "qmatmul: unknown mode %d", mode);
@@ -392,6 +401,17 @@ int smc_qmatmul_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, float 
     if (M == 0) return SMC_OK;
     return qmatmul_impl(ctx, d_in, w, d_out, M, mode, static_cast<cudaStream_t>(stream), false);
 }
+
+}  // extern "C"
+
+int smc_qmatmul_dev_gather(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, int mode,
+                           cudaStream_t s, const smc_gather_dev *gd, bool *fused)
+{
+    *fused = false;
+    return qmatmul_impl(ctx, d_in, w, d_out, M, mode, s, false, gd, fused);
+}
+
+extern "C" {
 
 int smc_block_isums_dev(smc_ctx *ctx, const smc_q8act *a, int m, const smc_weight *w, int col0, int col1,
                         int32_t *d_sums, void *stream)

@@ -88,6 +88,14 @@ bool smc_tma_supported(const smc_weight *, int M);
 int smc_launch_gemv_tma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_tma_f32in(smc_ctx *, const float *x, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_tma_x(smc_ctx *, const smc_q8act *, const float *xf, const smc_weight *, float *out, cudaStream_t s);
+struct smc_gather_dev;
+struct smc_gather;
+int smc_launch_gemv_tma_xg(smc_ctx *, const smc_q8act *, const float *xf, const smc_weight *, float *out,
+                           const smc_gather_dev *, cudaStream_t s);
+int smc_launch_gemv_tma_gather(smc_ctx *, const float *x, const smc_weight *, float *out, const smc_gather_dev *,
+                               cudaStream_t s);
+int smc_qmatmul_dev_gather(smc_ctx *, const float *d_in, const smc_weight *, float *d_out, int M, int mode, cudaStream_t s,
+                           const smc_gather_dev *, bool *fused);
 bool smc_stream_supported(const smc_weight *, int M);
 int smc_launch_gemv_stream(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,

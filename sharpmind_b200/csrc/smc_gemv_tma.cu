@@ -28,6 +28,7 @@
 #include <stdlib.h>
 
 #include "smc_common.cuh"
+#include "smc_gather.cuh"
 
 namespace {
 
@@ -454,9 +455,14 @@ struct MathQ8_0 {
 // w, w + W, w + 2W, ...: at any moment the grid reads one dense window that slides through the matrix.
 template <class Math, int MT, int MINB, int SS>
 __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs xg, float *__restrict__ out, int N, int K,
-                                                             int M, int slots, int *__restrict__ status)
+                                                             int M, int slots, int *__restrict__ status,
+                                                             const smc_gather_dev *gd)
 {
     extern __shared__ __align__(128) uint8_t smem[];
+    // row-split across GPUs (one row only): tell the peers that this rank's readers of the previous exchange are done
+    if (gd && blockIdx.x == 0 && threadIdx.x == 32) smc_gather_post_ready(gd);
+    int sending = -1;      // lane 0: whether packets go out, known after the first look at the peers' ready flags
+    unsigned gtag = 0;     // number of the running exchange
     constexpr bool XS = (MT == 1);
     constexpr uint32_t SLOT = (Math::STEP_BYTES * SS + 127u) & ~127u;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -517,7 +523,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
         const uint32_t saddr = ring + (uint32_t)slot * SLOT;
         if (!mbar_wait(bar, phase)) {
             if (lane == 0) atomicExch(status, 1);
-            return;
+            break;
         }
 #pragma unroll
         for (int i = 0; i < SS; ++i) {
@@ -526,7 +532,16 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
                     const float v = warp_sum32(acc[m]);
-                    if (lane == 0 && m0 + m < M) out[(size_t)(m0 + m) * N + row] = v;
+                    if (lane == 0 && m0 + m < M) {
+                        out[(size_t)(m0 + m) * N + row] = v;
+                        if (XS && gd) {  // this rank's chunk starts at rank * N in every peer's buffer
+                            if (sending < 0) {
+                                gtag = smc_gather_tag(gd);
+                                sending = smc_gather_wait_ready(gd, gtag) ? 1 : 0;
+                            }
+                            if (sending) smc_gather_send(gd, (size_t)N, (size_t)row, v, gtag);
+                        }
+                    }
                     acc[m] = 0.f;
                 }
                 part = 0;
@@ -543,6 +558,11 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
             cin = 0;
             row += (W - 1) * rg;
         }
+    }
+    // rows done: unpack this CTA's stripe of the peers' slices as they arrive
+    if (gd) {
+        smc_gather_collect(gd, (size_t)N, blockIdx.x, gridDim.x, smc_gather_tag(gd));
+        smc_gather_done(gd, gridDim.x);
     }
 }
 
@@ -566,14 +586,15 @@ Tuning tuning()
 
 template <class Math, int MT, int MINB, int SS>
 void launch_one(smc_ctx *ctx, dim3 grid, size_t smem, cudaStream_t s, const StepSrc &src, const XPtrs &x, float *out, int N,
-                int K, int M, int slots)
+                int K, int M, int slots, const smc_gather_dev *gd)
 {
     cudaFuncSetAttribute(gemv_tma_kernel<Math, MT, MINB, SS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gemv_tma_kernel<Math, MT, MINB, SS><<<grid, 256, smem, s>>>(src, x, out, N, K, M, slots, ctx->d_status);
+    gemv_tma_kernel<Math, MT, MINB, SS><<<grid, 256, smem, s>>>(src, x, out, N, K, M, slots, ctx->d_status, gd);
 }
 
 template <class Math>
-int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, int N, int K, int M, cudaStream_t s)
+int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, int N, int K, int M, cudaStream_t s,
+                const smc_gather_dev *gd)
 {
     const Tuning tn = tuning();
     const int mt = M == 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8));
@@ -608,18 +629,18 @@ int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, in
     dim3 grid((warps + WARPS - 1) / WARPS, (M + mt - 1) / mt);
     if (mt == 1) {
         const bool three = per_sm >= 3;
-        if (ss == 4) three ? launch_one<Math, 1, 3, 4>(ctx, grid, smem, s, src, x, out, N, K, M, slots)
-                           : launch_one<Math, 1, 2, 4>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
-        else if (ss == 2) three ? launch_one<Math, 1, 3, 2>(ctx, grid, smem, s, src, x, out, N, K, M, slots)
-                                : launch_one<Math, 1, 2, 2>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
-        else three ? launch_one<Math, 1, 3, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots)
-                   : launch_one<Math, 1, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+        if (ss == 4) three ? launch_one<Math, 1, 3, 4>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd)
+                           : launch_one<Math, 1, 2, 4>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
+        else if (ss == 2) three ? launch_one<Math, 1, 3, 2>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd)
+                                : launch_one<Math, 1, 2, 2>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
+        else three ? launch_one<Math, 1, 3, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd)
+                   : launch_one<Math, 1, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
     } else if (mt == 2) {
-        launch_one<Math, 2, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+        launch_one<Math, 2, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
     } else if (mt == 4) {
-        launch_one<Math, 4, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+        launch_one<Math, 4, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
     } else {
-        launch_one<Math, 8, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots);
+        launch_one<Math, 8, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
     }
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
@@ -650,21 +671,36 @@ int smc_launch_gemv_tma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, f
 int smc_launch_gemv_tma_x(smc_ctx *ctx, const smc_q8act *a, const float *xf, const smc_weight *w, float *out,
                           cudaStream_t s)
 {
+    return smc_launch_gemv_tma_xg(ctx, a, xf, w, out, nullptr, s);
+}
+
+// One fp32 row, quantised in the kernel, whose output slice is exchanged with the peers in the kernel's tail.
+int smc_launch_gemv_tma_gather(smc_ctx *ctx, const float *x, const smc_weight *w, float *out, const smc_gather_dev *gd,
+                               cudaStream_t s)
+{
+    smc_q8act one{};
+    one.M = 1, one.K = w->K;
+    return smc_launch_gemv_tma_xg(ctx, &one, x, w, out, gd, s);
+}
+
+int smc_launch_gemv_tma_xg(smc_ctx *ctx, const smc_q8act *a, const float *xf, const smc_weight *w, float *out,
+                           const smc_gather_dev *gd, cudaStream_t s)
+{
     const int N = w->N, K = w->K, M = a->M;
     XPtrs x{a->q, a->d, a->sd, a->s16, xf};
     StepSrc src{};
     if (w->dtype == SMC_Q4_K) {
         src.base[0] = w->d_raw;
-        return launch_math<MathQ4K>(ctx, src, x, out, N, K, M, s);
+        return launch_math<MathQ4K>(ctx, src, x, out, N, K, M, s, gd);
     }
     if (w->dtype == SMC_Q6_K) {
         src.base[0] = w->q6_ql;
         src.base[1] = w->q6_qh;
         src.base[2] = reinterpret_cast<const uint8_t *>(w->q6_sc);
         src.base[3] = reinterpret_cast<const uint8_t *>(w->q6_d);
-        return launch_math<MathQ6K>(ctx, src, x, out, N, K, M, s);
+        return launch_math<MathQ6K>(ctx, src, x, out, N, K, M, s, gd);
     }
     src.base[0] = reinterpret_cast<const uint8_t *>(w->q8_qs);
     src.base[1] = reinterpret_cast<const uint8_t *>(w->q8_d);
-    return launch_math<MathQ8_0>(ctx, src, x, out, N, K, M, s);
+    return launch_math<MathQ8_0>(ctx, src, x, out, N, K, M, s, gd);
 }

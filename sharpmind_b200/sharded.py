@@ -105,3 +105,67 @@ class ShardedLinear:
             out.copy_(res)
             return out
         return res.contiguous() if not res.is_contiguous() else res
+
+
+class PeerGather:
+    """Row-split matmul whose exchange runs inside the producing kernel over peer memory (no collective).
+
+    Wraps the library's gather object: allocates this rank's receive buffer, swaps the CUDA IPC handles with
+    one `all_gather_object` on `dist` (any backend: only 64 bytes per rank travel) and maps the peers.
+    `matmul(x, w_local)` returns a [world, M, N_local] view of the receive buffer, valid until the next
+    exchange on this object; `ShardedLinear.assemble` puts it into the unsplit column order.
+    """
+
+    def __init__(self, ctx, split: RowSplit, capacity_floats: int, dist=None):
+        import ctypes as C
+
+        import torch
+
+        self.ctx, self.split, self.torch, self.C = ctx, split, torch, C
+        self.capacity = int(capacity_floats)
+        h = C.c_void_p()
+        ctx.check(ctx.lib.smc_gather_create(ctx.h, split.rank, split.world, self.capacity, C.byref(h)))
+        self.h = h
+        if split.world > 1:
+            mine = (C.c_ubyte * 64)()
+            ctx.check(ctx.lib.smc_gather_export(ctx.h, self.h, mine))
+            handles = [None] * split.world
+            dist.all_gather_object(handles, bytes(mine))
+            blob = (C.c_ubyte * (64 * split.world)).from_buffer_copy(b"".join(handles))
+            ctx.check(ctx.lib.smc_gather_connect(ctx.h, self.h, blob))
+            dist.barrier()  # nobody starts an exchange before every rank has mapped its peers
+        p = C.c_void_p()
+        ctx.check(ctx.lib.smc_gather_buffer(ctx.h, self.h, C.byref(p)))
+        self._ptr = p.value
+        self._view = None
+
+    def buffer(self):
+        """The whole receive buffer as a flat fp32 CUDA tensor (no copy; owned by the library)."""
+        if self._view is None:
+            t = self.torch
+
+            class _Holder:  # minimal __cuda_array_interface__ provider
+                pass
+
+            hld = _Holder()
+            hld.__cuda_array_interface__ = {"shape": (self.capacity,), "typestr": "<f4", "data": (self._ptr, False),
+                                            "version": 2}
+            self._view = t.as_tensor(hld, device=f"cuda:{self.ctx.device}")
+        return self._view
+
+    def _stream(self):
+        return self.C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+
+    def matmul(self, x, w_local, mode: int):
+        m = x.shape[0] if x.dim() > 1 else 1
+        self.ctx.check(self.ctx.lib.smc_qmatmul_gather_dev(self.ctx.h, self.h, x.data_ptr(), w_local.handle, m,
+                                                           int(mode), self._stream()))
+        return self.buffer()[: self.split.world * m * w_local.N].view(self.split.world, m, w_local.N)
+
+    def exchange(self, count: int):
+        self.ctx.check(self.ctx.lib.smc_gather_exchange_dev(self.ctx.h, self.h, int(count), self._stream()))
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.smc_gather_destroy(self.ctx.h, self.h)
+            self.h = None

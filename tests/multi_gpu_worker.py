@@ -1,0 +1,80 @@
+"""Worker of the multi-GPU parity test: run under torch.distributed.run, one process per GPU.
+
+Every rank quantises the same seeded matrix on its own GPU, keeps its row slice, and checks that the row-split
+matmul with the in-kernel peer exchange reproduces the unsplit matmul of the same library bit for bit (each
+output row is computed by the same kernel arithmetic whichever rank owns it), for the fused one-row path, the
+several-row path, repeated exchanges, two objects in alternation, and a replayed CUDA graph.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from sharpmind_b200 import ops, synth  # noqa: E402
+from sharpmind_b200.sharded import PeerGather, RowSplit, ShardedLinear  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = ops.CudaContext(local)
+    dev = ops.DeviceOps(ctx)
+    split = RowSplit(world, rank)
+    failures = []
+    for dtype, n, k in ((12, 4096, 4096), (14, 2048, 4096), (8, 3072, 1024), (12, 1024, 16384)):
+        wf = torch.from_numpy(synth.normal("multi", f"w{dtype}_{k}", (n, k), 0.02)).cuda()
+        raw = dev.quantize_weights(dtype, wf)
+        full = ctx.register_dev(raw, dtype, n, k)
+        part = ctx.register_dev(split.slice_raw(raw, dtype, n, k).contiguous(), dtype, n // world, k)
+        lin = ShardedLinear(split, n, None, dist)
+        ga = PeerGather(ctx, split, 8 * n, dist)
+        gb = PeerGather(ctx, split, 8 * n, dist)
+        for m in (1, 4, 8):
+            for it in range(6):
+                x = torch.from_numpy(synth.normal("multi", f"x{dtype}_{m}_{it}", (m, k))).cuda()
+                want = dev.qmatmul(x, full, ops.Mode.ACT_Q8)
+                g = ga if it % 2 == 0 else gb
+                got = lin.assemble(g.matmul(x, part, ops.Mode.ACT_Q8))
+                if not torch.equal(got, want):
+                    failures.append(f"dtype {dtype} M {m} iteration {it}: max diff {(got - want).abs().max().item()}")
+        # replayed graph: the exchange counter lives in device memory, so replays stay in step
+        x = torch.from_numpy(synth.normal("multi", f"xg{dtype}", (1, k))).cuda()
+        want = dev.qmatmul(x, full, ops.Mode.ACT_Q8)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            ga.matmul(x, part, ops.Mode.ACT_Q8)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(3):
+                    view = ga.matmul(x, part, ops.Mode.ACT_Q8)
+        torch.cuda.synchronize()
+        dist.barrier()
+        for _ in range(5):
+            graph.replay()
+        torch.cuda.synchronize()
+        if not torch.equal(lin.assemble(view), want):
+            failures.append(f"dtype {dtype}: graph replay differs")
+        dist.barrier()
+        ga.close(), gb.close()
+    status = ctx.device_status()
+    if status:
+        failures.append(f"device status {status}")
+    flag = torch.tensor([len(failures)], device="cuda")
+    dist.all_reduce(flag)
+    if failures:
+        print(f"rank {rank}: " + "; ".join(failures[:5]), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    ctx.close()
+    sys.exit(1 if flag.item() else 0)
+
+
+if __name__ == "__main__":
+    main()
