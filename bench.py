@@ -48,6 +48,12 @@ WORKLOADS = {
 }
 
 
+# DRAM traffic per algorithmic byte of the one-row TMA GEMV, from the ncu captures summarised under profiles/
+# (Q4_K 28672x4096: 66.116 MB read + 0.48 MB written for 66.191 MB algorithmic; Q6_K 4096x14336: 48.23 MB read +
+# 0.1 MB written for 48.243 MB).  Traffic grows with the rows a launch covers, so other shapes scale it.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {Q4_K: (66.116e6 + 0.48e6) / 66191360.0, Q6_K: (48.23e6 + 0.1e6) / 48242688.0}
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -434,7 +440,9 @@ def run_ours(args):
         result["roofline"] = {"bound": "hbm", "kernel": "gemv_tma_kernel<MathQ4K> (gate||up, Q4_K)", "achieved": achieved,
                               "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                               "us_per_launch": us_launch, "algorithmic_bytes_per_launch": kbytes,
-                              "traffic": None}
+                              "traffic": (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get(dt, 0) * kbytes) or None,
+                              "traffic_source": "ncu dram__bytes_read+write of one launch of this kernel on the single-GPU "
+                                                "shape (profiles/gemv_tma_q4k_llama8b_gate_up.md), scaled by rows"}
         # ---- the other matrix, for the record
         xs2 = xs[1]
         if mode == ops.Mode.ACT_Q8 and M > 1:
@@ -491,6 +499,20 @@ def run_ours(args):
                              "h2d_bytes_per_step": sum(4 * M * k for _, _, _, k in mats) * L,
                              "d2h_bytes_per_step": sum(4 * M * n for _, _, n, _ in mats) * L,
                              "api": "smc_qmatmul_host: one synchronous call per matmul, host fp32 in / out"}
+            # ---- the other half of the metric: decode tokens/s of the Qwen3-0.6B-shaped model (configs[3])
+            try:
+                from sharpmind_b200 import synth
+                from sharpmind_b200.profile_decode import time_decode
+
+                rows = time_decode(ctx, dev, dict(synth.QWEN3_0_6B), [1, 32], 2048, 16)
+                result["decode"] = {
+                    "workload": "configs[3] Qwen3-0.6B-shaped decoder, Q8_0 weights, fp32 KV with a 2048-position seeded "
+                                "random context, one greedy token per sequence per step, q8_0 activations, CUDA graph",
+                    "tokens_per_s_batch1": rows[0]["tokens_per_s_graph"], "ms_per_step_batch1": rows[0]["graph_ms_per_step"],
+                    "tokens_per_s_batch32": rows[1]["tokens_per_s_graph"], "ms_per_step_batch32": rows[1]["graph_ms_per_step"],
+                    "GBps_batch1": rows[0]["GBps_graph"], "GBps_batch32": rows[1]["GBps_graph"]}
+            except Exception as exc:
+                result["decode"] = {"error": str(exc)}
             # ---- CPU baseline on the host cores
             try:
                 result["cpu_baseline"], _ = cpu_port_time(args.workload, M, args.cpu_seconds)

@@ -54,9 +54,72 @@ def step_bytes(cfg: dict, batch: int, ctx: int) -> dict:
     return {"weights": weights, "kv": kv}
 
 
-def main():
+def time_decode(ctx, dev, cfg: dict, batches, ctx_len: int, steps: int, modes=("q8",), once: bool = False) -> list:
+    """Builds the model, installs a `ctx_len`-position context and times one-token steps; one dict per case."""
     import torch
 
+    w = device_weights(dev, cfg)
+    dec = Decoder(ctx, cfg, w, max_batch=max(batches))
+    del w
+    g = torch.Generator(device="cuda")
+    g.manual_seed(99)
+    shape = (cfg["n_layers"], max(batches), cfg["n_kv_heads"], ctx_len, cfg["head_dim"])
+    k, v = torch.randn(shape, generator=g, device="cuda"), torch.randn(shape, generator=g, device="cuda")
+    dec.load_kv(k, v)
+    torch.cuda.synchronize()
+    del k, v
+    torch.cuda.empty_cache()
+    rows = []
+    for B in batches:
+        tok = torch.randint(0, cfg["vocab"], (B,), generator=g, device="cuda", dtype=torch.int32)
+        logits = torch.empty((B, cfg["vocab"]), device="cuda")
+        nxt = torch.empty(B, dtype=torch.int32, device="cuda")
+        for name in modes:
+            mode = MODES[name]
+            if once:
+                dec.step(tok, ctx_len, mode, logits, nxt)
+                torch.cuda.synchronize()
+                continue
+            for _ in range(3):
+                dec.step(tok, ctx_len, mode, logits, nxt)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                dec.step(tok, ctx_len, mode, logits, nxt)
+            e1.record()
+            torch.cuda.synchronize()
+            plain_ms = e0.elapsed_time(e1) / steps
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                dec.step(tok, ctx_len, mode, logits, nxt)
+                side.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    dec.step(tok, ctx_len, mode, logits, nxt)
+            torch.cuda.synchronize()
+            for _ in range(3):
+                graph.replay()
+            e0.record()
+            for _ in range(steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            graph_ms = e0.elapsed_time(e1) / steps
+            by = step_bytes(cfg, B, ctx_len)
+            rows.append({
+                "batch": B, "mode": name, "ctx": ctx_len, "layers": cfg["n_layers"],
+                "plain_ms_per_step": round(plain_ms, 4), "graph_ms_per_step": round(graph_ms, 4),
+                "tokens_per_s_plain": round(B / plain_ms * 1e3, 1), "tokens_per_s_graph": round(B / graph_ms * 1e3, 1),
+                "weight_MB": round(by["weights"] / 1e6, 1), "kv_MB": round(by["kv"] / 1e6, 1),
+                "GBps_graph": round((by["weights"] + by["kv"]) / graph_ms / 1e6, 1),
+                "device_status": ctx.device_status(),
+            })
+    dec.close()
+    return rows
+
+
+def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batches", default="1,8,32")
     ap.add_argument("--ctx", type=int, default=2048)
@@ -68,62 +131,11 @@ def main():
     cfg = dict(synth.QWEN3_0_6B)
     if a.layers:
         cfg["n_layers"] = a.layers
-    batches = [int(b) for b in a.batches.split(",")]
     ctx = ops.CudaContext(0)
     dev = ops.DeviceOps(ctx)
-    w = device_weights(dev, cfg)
-    dec = Decoder(ctx, cfg, w, max_batch=max(batches))
-    g = torch.Generator(device="cuda")
-    g.manual_seed(99)
-    shape = (cfg["n_layers"], max(batches), cfg["n_kv_heads"], a.ctx, cfg["head_dim"])
-    dec.load_kv(torch.randn(shape, generator=g, device="cuda"), torch.randn(shape, generator=g, device="cuda"))
-    torch.cuda.synchronize()
-    for B in batches:
-        tok = torch.randint(0, cfg["vocab"], (B,), generator=g, device="cuda", dtype=torch.int32)
-        logits = torch.empty((B, cfg["vocab"]), device="cuda")
-        nxt = torch.empty(B, dtype=torch.int32, device="cuda")
-        for name in a.modes.split(","):
-            mode = MODES[name]
-            if a.once:
-                dec.step(tok, a.ctx, mode, logits, nxt)
-                torch.cuda.synchronize()
-                continue
-            for _ in range(3):
-                dec.step(tok, a.ctx, mode, logits, nxt)
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(a.steps):
-                dec.step(tok, a.ctx, mode, logits, nxt)
-            e1.record()
-            torch.cuda.synchronize()
-            plain_ms = e0.elapsed_time(e1) / a.steps
-            side = torch.cuda.Stream()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(side):
-                dec.step(tok, a.ctx, mode, logits, nxt)
-                side.synchronize()
-                with torch.cuda.graph(graph, stream=side):
-                    dec.step(tok, a.ctx, mode, logits, nxt)
-            torch.cuda.synchronize()
-            for _ in range(3):
-                graph.replay()
-            e0.record()
-            for _ in range(a.steps):
-                graph.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            graph_ms = e0.elapsed_time(e1) / a.steps
-            by = step_bytes(cfg, B, a.ctx)
-            print(json.dumps({
-                "batch": B, "mode": name, "ctx": a.ctx, "layers": cfg["n_layers"],
-                "plain_ms_per_step": round(plain_ms, 4), "graph_ms_per_step": round(graph_ms, 4),
-                "tokens_per_s_plain": round(B / plain_ms * 1e3, 1), "tokens_per_s_graph": round(B / graph_ms * 1e3, 1),
-                "weight_MB": round(by["weights"] / 1e6, 1), "kv_MB": round(by["kv"] / 1e6, 1),
-                "GBps_graph": round((by["weights"] + by["kv"]) / graph_ms / 1e6, 1),
-                "device_status": ctx.device_status(),
-            }), flush=True)
-    dec.close()
+    for row in time_decode(ctx, dev, cfg, [int(b) for b in a.batches.split(",")], a.ctx, a.steps,
+                           tuple(a.modes.split(",")), a.once):
+        print(json.dumps(row), flush=True)
     ctx.close()
 
 
