@@ -137,6 +137,13 @@ SMC_API int smc_q8act_destroy(smc_ctx *ctx, smc_q8act *a);
 SMC_API int smc_quantize_q8_dev(smc_ctx *ctx, const float *d_x, int M, int K, smc_q8act *a, void *stream);
 /* Copies the quantised rows back to the host: q [M, K] int8, d_bits [M, K/32] fp16 bit patterns. */
 SMC_API int smc_q8act_read(smc_ctx *ctx, const smc_q8act *a, int8_t *q, uint16_t *d_bits);
+/* The same product for prefill-sized M on the tensor cores (tcgen05 MMA, accumulators in tensor memory):
+ * Q4_K weights with N % 128 == 0 and K % 256 == 0; the integer part of each weight is exact in fp16 and the
+ * activations travel as an fp16 (hi, lo) pair, so the result meets the bound of SMC_ACT_F32.  This is what
+ * the M > 1 row loop of QuantizedMatMulQ4K_Parallel_* (QuantizationKernels.Q4.cs:1148-1212) becomes when the
+ * whole token batch shares one pass over the weights.  SMC_E_UNSUPPORTED for other formats / shapes.  The
+ * first call of a larger M * K allocates scratch in the context (make it outside stream capture). */
+SMC_API int smc_qmatmul_tc_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, void *stream);
 /* Matmul on activations already quantised with smc_quantize_q8_dev. */
 SMC_API int smc_qmatmul_q8_dev(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *d_out, void *stream);
 /* The SMC_ACT_Q8 matmul of smc_qmatmul_dev for hosts that must not allocate device memory while they run

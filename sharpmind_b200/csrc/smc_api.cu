@@ -182,6 +182,7 @@ void smc_destroy(smc_ctx *ctx)
     cudaFree(ctx->d_stage_out);
     cudaFree(ctx->d_stage_aux);
     cudaFree(ctx->d_attn_part);
+    cudaFree(ctx->d_prefill);
     cudaFree(ctx->d_status);
     if (ctx->h_pin) cudaFreeHost(ctx->h_pin);
     smc_q8act_free(ctx->act);
@@ -412,6 +413,13 @@ int smc_qmatmul_dev_gather(smc_ctx *ctx, const float *d_in, const smc_weight *w,
 }
 
 extern "C" {
+
+int smc_qmatmul_tc_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, void *stream)
+{
+    if (!ctx || !d_in || !w || !d_out || M < 0) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_tc: bad arguments");
+    if (M == 0) return SMC_OK;
+    return smc_launch_prefill_q4k(ctx, d_in, w, d_out, M, static_cast<cudaStream_t>(stream));
+}
 
 int smc_block_isums_dev(smc_ctx *ctx, const smc_q8act *a, int m, const smc_weight *w, int col0, int col1,
                         int32_t *d_sums, void *stream)

@@ -60,6 +60,8 @@ struct smc_ctx {
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
     bool use_tma = true;               // SMC_GEMV=stream in the environment selects the register-prefetch kernels
+    void *d_prefill = nullptr;         // activation image of the tensor-core matmul
+    size_t prefill_cap = 0;
     float *d_attn_part = nullptr;      // split-KV partial results
     size_t attn_part_cap = 0;
 };
@@ -96,6 +98,8 @@ int smc_launch_gemv_tma_gather(smc_ctx *, const float *x, const smc_weight *, fl
                                cudaStream_t s);
 int smc_qmatmul_dev_gather(smc_ctx *, const float *d_in, const smc_weight *, float *d_out, int M, int mode, cudaStream_t s,
                            const smc_gather_dev *, bool *fused);
+bool smc_prefill_supported(const smc_weight *, int M);
+int smc_launch_prefill_q4k(smc_ctx *, const float *x, const smc_weight *, float *out, int M, cudaStream_t s);
 bool smc_stream_supported(const smc_weight *, int M);
 int smc_launch_gemv_stream(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,

@@ -1,0 +1,468 @@
+// Prefill-sized quantised matmul on the 5th-generation tensor cores (tcgen05 + TMEM), Q4_K weights.
+//
+//   out[t, r] = sum_k x[t, k] * w[r, k],   w[r, k] = d_b * (sc_j * q_k) - dmin_b * m_j
+//
+// (block b = k / 256 of row r, sub-block j = (k % 256) / 32; VecDotQ4K, QuantizationKernels.Q4.cs:586-747).
+// The integer part sc_j * q_k <= 63 * 15 is exact in fp16, so the tensor cores multiply exact weights:
+//   acc_d[r, t] = sum_{k in b} (sc_j q_k) * x~[t, k]        16 MMAs of K = 16 per block and activation half
+//   acc_m[r, t] = sum_{j < 8}  m_j * sx~[t, b, j]           one MMA of K = 16 per block
+//   out[t, r]  += s_t * (d_b * acc_d - dmin_b * acc_m)      CUDA cores, once per 256-element block
+// x~ = x / s_t with s_t a power of two that brings the row's largest magnitude to about 2^10, carried as an
+// fp16 pair (hi, lo) so that hi + lo holds 22 significant bits of x~: the result stays inside the fp32 parity
+// bound of the fp32-activation mode.  sx~ is the fp32 sum of x~ over a 32-element sub-block, also as a pair.
+//
+// One CTA computes 128 weight rows x 128 tokens.  Warp roles:
+//   warp 0        lane 0 streams the activation tiles with bulk copies (global -> shared, mbarrier tx count)
+//   warp 1        lane 0 issues tcgen05.mma / tcgen05.commit
+//   warps 2..5    one thread per weight row: reads its 144-byte block, expands the nibbles to fp16 sc*q and
+//                 writes the A operand tile in the tensor cores' canonical K-major layout
+//   warps 6..13   drain: tcgen05.ld of the two accumulators, scaling by d / dmin, fp32 running sums in
+//                 registers (64 tokens per thread), final store
+// Shared memory: 4 stages of {A 16 KB, B_hi 16 KB, B_lo 16 KB} (64 k each) + 2 x {A'' 4 KB, B'' 4 KB} for the
+// min term.  TMEM: all 512 columns = 2 buffers x (acc_d 128 + acc_m 128), so the drain of one block overlaps
+// the MMAs of the next.  Every mbarrier wait is bounded; a wait that runs out raises the context's status
+// word and a CTA-wide abort flag that makes every later wait return at once, so the kernel still ends and
+// frees its TMEM.
+#include <cuda_fp16.h>
+
+#include "smc_common.cuh"
+
+namespace {
+
+constexpr int TM = 128;    // weight rows per CTA (MMA M)
+constexpr int TN = 128;    // tokens per CTA (MMA N)
+constexpr int KS = 64;     // k per stage
+constexpr int NSLOT = 4;   // stages in flight = stages per 256-element block
+constexpr uint32_t A_BYTES = TM * KS * 2;
+constexpr uint32_t B_BYTES = TN * KS * 2;
+constexpr uint32_t SLOT_BYTES = A_BYTES + 2 * B_BYTES;
+constexpr uint32_t AM_BYTES = TM * 16 * 2;
+constexpr uint32_t BM_BYTES = TN * 16 * 2;
+constexpr uint32_t AUX_BYTES = AM_BYTES + BM_BYTES;
+constexpr uint32_t OFF_AUX = NSLOT * SLOT_BYTES;
+constexpr uint32_t OFF_BAR = OFF_AUX + 2 * AUX_BYTES;
+constexpr uint32_t SMEM_BYTES = OFF_BAR + 256;
+constexpr int THREADS = 14 * 32;
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+
+// barrier slots (8 bytes each) inside the last 256 bytes
+enum { BAR_FULL_B = 0, BAR_FULL_A = 4, BAR_EMPTY = 8, BAR_ACC_FULL = 12, BAR_ACC_EMPTY = 14, BAR_COUNT = 16 };
+constexpr uint32_t OFF_TMEM_PTR = OFF_BAR + BAR_COUNT * 8;
+constexpr uint32_t OFF_ABORT = OFF_TMEM_PTR + 4;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  When the limit runs out, or another thread of the CTA already gave up, raises the flags and
+// returns: the caller carries on with whatever is in memory so that the kernel ends in bounded time.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, int *status)
+{
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return;
+        if ((i & 255u) == 255u && *abort_flag) return;
+    }
+    *abort_flag = 1;
+    atomicExch(status, 3);
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], M = 128, N = 128, K = 16, fp16 operands, fp32 accumulate; one thread issues.
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float *v)
+{
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices of 128 contiguous
+// bytes; `lbo` = bytes between the two core matrices along K of one MMA, `sbo` = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo)
+{
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+// Instruction descriptor: fp32 accumulator, fp16 A and B, both K-major, N = 128, M = 128.
+constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+
+// ------------------------------------------------------------------------------ activation image
+// Global layout read by the GEMM kernel with plain bulk copies (already in the shared-memory order):
+//   img  [token tile][stage = k / 64][hi | lo][token / 8][k chunk = (k % 64) / 8][token % 8][k % 8]   fp16
+//   mimg [token tile][block = k / 256][token / 8][2][token % 8][8]                                    fp16
+//        (second index 0: sx~ hi of sub-blocks 0..7, 1: sx~ lo)
+//   scale[token]  fp32 power of two
+__global__ void __launch_bounds__(256) prefill_scale_kernel(const float *__restrict__ x, int M, int K, float *__restrict__ scale)
+{
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    float amax = 0.f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(x[(size_t)t * K + k]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+        float s = 1.0f;
+        if (amax > 0.f && amax < INFINITY) {
+            int e;
+            frexpf(amax, &e);          // amax = f * 2^e, f in [0.5, 1)
+            s = ldexpf(1.0f, e - 10);  // amax / s in [512, 1024)
+        }
+        scale[t] = s;
+    }
+}
+
+__global__ void __launch_bounds__(256) prefill_image_kernel(const float *__restrict__ x, int M, int K,
+                                                            const float *__restrict__ scale, __half *__restrict__ img,
+                                                            __half *__restrict__ mimg)
+{
+    // one CTA per (token tile, 256-element block): 128 tokens x 32 chunks of 8
+    const int nsb = K / 256;
+    const int tt = blockIdx.x / nsb, sb = blockIdx.x % nsb;
+    for (int it = threadIdx.x; it < TN * 32; it += blockDim.x) {
+        const int tl = it >> 5, c = it & 31;  // token in tile, chunk in block
+        const int t = tt * TN + tl;
+        float v[8];
+        float inv = 0.f;
+        if (t < M) {
+            inv = 1.0f / scale[t];  // exact: a power of two
+            const float4 a = *reinterpret_cast<const float4 *>(x + (size_t)t * K + sb * 256 + c * 8);
+            const float4 b = *reinterpret_cast<const float4 *>(x + (size_t)t * K + sb * 256 + c * 8 + 4);
+            v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        }
+        __align__(16) __half hi[8], lo[8];
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float xs = v[i] * inv;
+            hi[i] = __float2half_rn(xs);
+            lo[i] = __float2half_rn(xs - __half2float(hi[i]));
+            sum += xs;
+        }
+        const int stage = sb * 4 + (c >> 3);
+        const size_t base = ((size_t)(tt * (K / KS) + stage) * 2) * (TN * KS) + (size_t)(tl >> 3) * (KS / 8 * 64) +
+                            (size_t)(c & 7) * 64 + (size_t)(tl & 7) * 8;
+        *reinterpret_cast<uint4 *>(img + base) = *reinterpret_cast<const uint4 *>(hi);
+        *reinterpret_cast<uint4 *>(img + base + TN * KS) = *reinterpret_cast<const uint4 *>(lo);
+        // sub-block sums: chunks 4j .. 4j+3 are adjacent lanes
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((c & 3) == 0) {
+            const int j = c >> 2;
+            const __half sh = __float2half_rn(sum);
+            const __half sl = __float2half_rn(sum - __half2float(sh));
+            const size_t mb = (size_t)(tt * nsb + sb) * (TN * 16) + (size_t)(tl >> 3) * 128 + (size_t)(tl & 7) * 8 + j;
+            mimg[mb] = sh;
+            mimg[mb + 64] = sl;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------ nibble expansion
+// Bytes b0 b1 of `w` (selected by `sel`) -> {sc * low nibble(b0), sc * low nibble(b1)} and the same for the
+// high nibbles, as fp16 pairs.  0x6400 | q is the fp16 number 1024 + q; one fused multiply-add with
+// (sc, -1024 sc) gives sc * q with a single rounding of an exactly representable result.  The high nibble
+// sits four bits up (1024 + 16 q), so its multiplier is sc / 16 and its offset -64 sc, both exact.
+__device__ __forceinline__ void expand_pair(uint32_t w, uint32_t sel, __half2 sc_lo, __half2 off_lo, __half2 sc_hi16,
+                                            __half2 off_hi, uint32_t &lo, uint32_t &hi)
+{
+    const uint32_t p = __byte_perm(w, 0u, sel);  // bytes {bA, 0, bB, 0}
+    const uint32_t l = (p & 0x000F000Fu) | 0x64006400u;
+    const uint32_t h = (p & 0x00F000F0u) | 0x64006400u;
+    const __half2 rl = __hfma2(*reinterpret_cast<const __half2 *>(&l), sc_lo, off_lo);
+    const __half2 rh = __hfma2(*reinterpret_cast<const __half2 *>(&h), sc_hi16, off_hi);
+    lo = *reinterpret_cast<const uint32_t *>(&rl);
+    hi = *reinterpret_cast<const uint32_t *>(&rh);
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// ------------------------------------------------------------------------------ the GEMM
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ img, const __half *__restrict__ mimg,
+                   const float *__restrict__ scale, float *__restrict__ out, int N, int K, int M, int ntt, int *status)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rt = blockIdx.x / ntt, tt = blockIdx.x % ntt;
+    const int row0 = rt * TM;
+    const int nsb = K / 256;
+    const size_t row_bytes = (size_t)nsb * 144;
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + OFF_ABORT);
+    auto bar = [&](int i) { return sbase + OFF_BAR + 8u * (uint32_t)i; };
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NSLOT; ++i) {
+            mbar_init(bar(BAR_FULL_B + i), 1);
+            mbar_init(bar(BAR_FULL_A + i), TM);
+            mbar_init(bar(BAR_EMPTY + i), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(BAR_ACC_FULL + i), 1);
+            mbar_init(bar(BAR_ACC_EMPTY + i), 256);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+    }
+    if (warp == 0) {
+        const uint32_t dst = sbase + OFF_TMEM_PTR;
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem + OFF_TMEM_PTR);
+
+    if (warp == 0) {
+        // ---------------- activation tiles: one bulk copy of hi|lo per stage (+ the min-term tile per block)
+        if (lane == 0) {
+            const __half *src = img + (size_t)tt * (K / KS) * 2 * (TN * KS);
+            const __half *msrc = mimg + (size_t)tt * nsb * (TN * 16);
+            for (int sb = 0; sb < nsb; ++sb) {
+                for (int g = 0; g < NSLOT; ++g) {
+                    mbar_wait(bar(BAR_EMPTY + g), (uint32_t)((sb & 1) ^ 1), abort_flag, status);
+                    const uint32_t fb = bar(BAR_FULL_B + g);
+                    mbar_expect_tx(fb, 2 * B_BYTES + (g == 0 ? BM_BYTES : 0u));
+                    bulk_g2s(sbase + (uint32_t)g * SLOT_BYTES + A_BYTES, src + (size_t)(sb * NSLOT + g) * 2 * (TN * KS),
+                             2 * B_BYTES, fb);
+                    if (g == 0)
+                        bulk_g2s(sbase + OFF_AUX + (uint32_t)(sb & 1) * AUX_BYTES + AM_BYTES, msrc + (size_t)sb * (TN * 16),
+                                 BM_BYTES, fb);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue
+        if (lane == 0) {
+            for (int sb = 0; sb < nsb; ++sb) {
+                const int buf = sb & 1;
+                mbar_wait(bar(BAR_ACC_EMPTY + buf), (uint32_t)(((sb >> 1) & 1) ^ 1), abort_flag, status);
+                tc_fence_after();
+                const uint32_t acc_d = tmem_base + (uint32_t)buf * 256u, acc_m = acc_d + 128u;
+                for (int g = 0; g < NSLOT; ++g) {
+                    mbar_wait(bar(BAR_FULL_B + g), (uint32_t)(sb & 1), abort_flag, status);
+                    mbar_wait(bar(BAR_FULL_A + g), (uint32_t)(sb & 1), abort_flag, status);
+                    tc_fence_after();
+                    const uint32_t a0 = sbase + (uint32_t)g * SLOT_BYTES, bh = a0 + A_BYTES, bl = bh + B_BYTES;
+                    if (g == 0) {
+                        const uint32_t aux = sbase + OFF_AUX + (uint32_t)buf * AUX_BYTES;
+                        tc_mma_f16(acc_m, smem_desc(aux, 128, 256), smem_desc(aux + AM_BYTES, 128, 256), IDESC, 0u);
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < KS / 16; ++kk)
+                        tc_mma_f16(acc_d, smem_desc(a0 + kk * 256, 128, 1024), smem_desc(bh + kk * 256, 128, 1024), IDESC,
+                                   (g | kk) != 0 ? 1u : 0u);
+#pragma unroll
+                    for (int kk = 0; kk < KS / 16; ++kk)
+                        tc_mma_f16(acc_d, smem_desc(a0 + kk * 256, 128, 1024), smem_desc(bl + kk * 256, 128, 1024), IDESC, 1u);
+                    tc_commit(bar(BAR_EMPTY + g));  // arrives when the MMAs above have read the stage
+                }
+                tc_commit(bar(BAR_ACC_FULL + buf));
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- weight expansion: thread r owns weight row row0 + r
+        const int r = threadIdx.x - 64;
+        const uint8_t *rowp = raw + (size_t)(row0 + r) * row_bytes;
+        const uint32_t a_row = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 16u;
+        const uint32_t am_row = (uint32_t)(r >> 3) * 256u + (uint32_t)(r & 7) * 16u;
+        uint4 nx[9];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) nx[i] = smc_ldg_stream16(rowp + 16 * i);
+        for (int sb = 0; sb < nsb; ++sb) {
+            uint4 cur[9];
+#pragma unroll
+            for (int i = 0; i < 9; ++i) cur[i] = nx[i];
+            if (sb + 1 < nsb) {
+#pragma unroll
+                for (int i = 0; i < 9; ++i) nx[i] = smc_ldg_stream16(rowp + (size_t)(sb + 1) * 144 + 16 * i);
+            }
+            const uint32_t s0 = cur[0].y, s1 = cur[0].z, s2 = cur[0].w;  // the 12 packed scale / min bytes
+#pragma unroll
+            for (int g = 0; g < NSLOT; ++g) {
+                mbar_wait(bar(BAR_EMPTY + g), (uint32_t)((sb & 1) ^ 1), abort_flag, status);
+                if (g == 0) {
+                    // A'' of the min term: m_0..m_7 in columns 0..7 and again in 8..15
+                    uint32_t mh[4];
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) {
+                        int sc, ma, mb;
+                        smc_k4_scale_min(s0, s1, s2, j, sc, ma);
+                        smc_k4_scale_min(s0, s1, s2, j + 1, sc, mb);
+                        const __half2 hm = __halves2half2(__int2half_rn(ma), __int2half_rn(mb));
+                        mh[j >> 1] = *reinterpret_cast<const uint32_t *>(&hm);
+                    }
+                    const uint32_t am = sbase + OFF_AUX + (uint32_t)(sb & 1) * AUX_BYTES + am_row;
+                    sts128(am, mh[0], mh[1], mh[2], mh[3]);
+                    sts128(am + 128u, mh[0], mh[1], mh[2], mh[3]);
+                }
+                int sca, scb, mn;
+                smc_k4_scale_min(s0, s1, s2, 2 * g, sca, mn);      // low nibbles: sub-block 2g
+                smc_k4_scale_min(s0, s1, s2, 2 * g + 1, scb, mn);  // high nibbles: sub-block 2g + 1
+                const __half2 sc_lo = __half2half2(__int2half_rn(sca));
+                const __half2 off_lo = __half2half2(__int2half_rn(-1024 * sca));
+                const __half2 sc_hi = __half2half2(__float2half_rn((float)scb * 0.0625f));
+                const __half2 off_hi = __half2half2(__int2half_rn(-64 * scb));
+                const uint32_t wq[8] = {cur[1 + 2 * g].x, cur[1 + 2 * g].y, cur[1 + 2 * g].z, cur[1 + 2 * g].w,
+                                        cur[2 + 2 * g].x, cur[2 + 2 * g].y, cur[2 + 2 * g].z, cur[2 + 2 * g].w};
+                const uint32_t a_dst = sbase + (uint32_t)g * SLOT_BYTES + a_row;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {  // bytes 8c .. 8c+7 -> k chunk c (low nibbles) and c + 4 (high nibbles)
+                    uint32_t lo[4], hi[4];
+                    expand_pair(wq[2 * c], 0x4140u, sc_lo, off_lo, sc_hi, off_hi, lo[0], hi[0]);
+                    expand_pair(wq[2 * c], 0x4342u, sc_lo, off_lo, sc_hi, off_hi, lo[1], hi[1]);
+                    expand_pair(wq[2 * c + 1], 0x4140u, sc_lo, off_lo, sc_hi, off_hi, lo[2], hi[2]);
+                    expand_pair(wq[2 * c + 1], 0x4342u, sc_lo, off_lo, sc_hi, off_hi, lo[3], hi[3]);
+                    sts128(a_dst + (uint32_t)c * 128u, lo[0], lo[1], lo[2], lo[3]);
+                    sts128(a_dst + (uint32_t)(c + 4) * 128u, hi[0], hi[1], hi[2], hi[3]);
+                }
+                fence_proxy_async();  // the tensor cores read this tile through the async proxy
+                mbar_arrive(bar(BAR_FULL_A + g));
+            }
+        }
+    } else {
+        // ---------------- drain: thread = (TMEM lane = weight row, 64 of the 128 token columns)
+        const int quarter = warp & 3, half = (warp - 6) >> 2;
+        const int rl = quarter * 32 + lane;
+        const uint8_t *rowp = raw + (size_t)(row0 + rl) * row_bytes;
+        float acc[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        for (int sb = 0; sb < nsb; ++sb) {
+            const int buf = sb & 1;
+            const uint32_t hdr = smc_ldg_stream4(rowp + (size_t)sb * 144);
+            const float d = smc_h2f((uint16_t)(hdr & 0xFFFFu)), ndmin = -smc_h2f((uint16_t)(hdr >> 16));
+            mbar_wait(bar(BAR_ACC_FULL + buf), (uint32_t)((sb >> 1) & 1), abort_flag, status);
+            tc_fence_after();
+            const uint32_t td = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * 256u + (uint32_t)half * 64u;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float vd[16], vm[16];
+                tc_ld16(td + (uint32_t)c * 16u, vd);
+                tc_ld16(td + 128u + (uint32_t)c * 16u, vm);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(ndmin, vm[i], fmaf(d, vd[i], acc[c * 16 + i]));
+            }
+            tc_fence_before();
+            mbar_arrive(bar(BAR_ACC_EMPTY + buf));
+        }
+        const int t0 = tt * TN + half * 64;
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+            if (t0 + j < M) out[(size_t)(t0 + j) * N + row0 + rl] = acc[j] * scale[t0 + j];
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+}  // namespace
+
+bool smc_prefill_supported(const smc_weight *w, int M)
+{
+    return w->dtype == SMC_Q4_K && w->N % TM == 0 && w->K % 256 == 0 && M >= 1 && w->d_raw != nullptr;
+}
+
+// Scratch for the activation image, owned by the context and grown on demand (the first call of a larger
+// shape allocates: make it outside stream capture).
+static int ensure_scratch(smc_ctx *ctx, size_t bytes)
+{
+    if (ctx->prefill_cap >= bytes) return SMC_OK;
+    if (ctx->d_prefill) {
+        cudaDeviceSynchronize();
+        cudaFree(ctx->d_prefill);
+        ctx->d_prefill = nullptr, ctx->prefill_cap = 0;
+    }
+    SMC_CUDA(ctx, cudaMalloc(&ctx->d_prefill, bytes));
+    ctx->prefill_cap = bytes;
+    return SMC_OK;
+}
+
+int smc_launch_prefill_q4k(smc_ctx *ctx, const float *x, const smc_weight *w, float *out, int M, cudaStream_t s)
+{
+    if (!smc_prefill_supported(w, M)) return smc_fail(ctx, SMC_E_UNSUPPORTED, "tensor-core matmul needs Q4_K, N %% 128 == 0, K %% 256 == 0");
+    if (reinterpret_cast<uintptr_t>(x) & 15) return smc_fail(ctx, SMC_E_INVALID, "tensor-core matmul needs 16-byte aligned activations");
+    const int N = w->N, K = w->K, ntt = (M + TN - 1) / TN, nsb = K / 256;
+    const size_t img_halves = (size_t)ntt * TN * K * 2, mimg_halves = (size_t)ntt * nsb * TN * 16;
+    const size_t scale_off = (img_halves + mimg_halves) * sizeof(__half);
+    const size_t bytes = scale_off + (size_t)ntt * TN * sizeof(float);
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        int rc = ensure_scratch(ctx, bytes);
+        if (rc) return rc;
+    }
+    __half *img = reinterpret_cast<__half *>(ctx->d_prefill);
+    __half *mimg = img + img_halves;
+    float *scale = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ctx->d_prefill) + scale_off);
+    prefill_scale_kernel<<<M, 256, 0, s>>>(x, M, K, scale);
+    prefill_image_kernel<<<ntt * nsb, 256, 0, s>>>(x, M, K, scale, img, mimg);
+    static bool attr_set = false;
+    if (!attr_set) {
+        SMC_CUDA(ctx, cudaFuncSetAttribute(prefill_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+        attr_set = true;
+    }
+    prefill_q4k_kernel<<<(N / TM) * ntt, THREADS, SMEM_BYTES, s>>>(w->d_raw, img, mimg, scale, out, N, K, M, ntt, ctx->d_status);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}

@@ -312,6 +312,20 @@ class DeviceOps:
                                                 M, int(mode), self._stream()))
         return out
 
+    def qmatmul_tc(self, x, w: Weight, out=None):
+        """Prefill-sized matmul on the tensor cores (Q4_K, N % 128 == 0, K % 256 == 0)."""
+        t = self.torch
+        M = x.numel() // w.K
+        if x.numel() != M * w.K:
+            raise ArgumentException(f"input of {x.numel()} values is not a multiple of K = {w.K}")
+        if out is None:
+            out = t.empty((M, w.N), dtype=t.float32, device=x.device)
+        if M == 0:
+            return out
+        self.ctx.check(self.lib.smc_qmatmul_tc_dev(self.ctx.h, self._chk(x, t.float32), w.handle,
+                                                   self._chk(out, t.float32), M, self._stream()))
+        return out
+
     def quantize_q8(self, x, act: Q8Act, K: int):
         M = x.numel() // K
         self.ctx.check(self.lib.smc_quantize_q8_dev(self.ctx.h, self._chk(x, self.torch.float32), M, K, act.h,

@@ -1,0 +1,73 @@
+"""Prefill-sized Q4_K matmul on the tensor cores against the oracle's scalar vec-dot (fp32 activations).
+
+Bound: 1e-5 * ||w_row|| * ||x_row|| per output, the same as the fp32-activation GEMV: the tensor-core path
+multiplies exact integer weight parts with an fp16 (hi, lo) split of the activations.
+"""
+import numpy as np
+import pytest
+
+from sharpmind_b200 import ops, synth
+from tests.gpu_util import Q4_K, row_norm_bound, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(oracle, cuda, dev, n, k, m, sigma_x=1.0, tag=""):
+    wf = synth.normal("prefill", f"w{n}x{k}{tag}", (n, k), 0.02)
+    raw = oracle.quantize(Q4_K, wf)
+    x = synth.normal("prefill", f"x{m}x{k}{tag}", (m, k), sigma_x)
+    w = cuda.register(raw, Q4_K, n, k)
+    got = dev.qmatmul_tc(to_dev(x), w).cpu().numpy()
+    assert cuda.device_status() == 0
+    return raw, x, got, w
+
+
+@pytest.mark.parametrize("n,k,m", [
+    (128, 256, 128),     # one tile, one block
+    (128, 1024, 128),    # several blocks: both accumulator buffers, stage reuse
+    (256, 2048, 200),    # two row tiles, ragged token tile
+    (384, 512, 1),       # a single token
+    (128, 4096, 300),    # three token tiles
+])
+def test_tc_matmul_matches_oracle(oracle, cuda, dev, n, k, m):
+    raw, x, got, w = _case(oracle, cuda, dev, n, k, m)
+    want = oracle.qmatmul(Q4_K, x, raw, m, k, n)
+    bound = row_norm_bound(oracle, Q4_K, raw, n, k, x)
+    err = np.abs(got - want)
+    assert np.all(err <= bound), float(np.max(err / bound))
+    cuda.release(w)
+
+
+def test_tc_matmul_scaling_and_zero_rows(oracle, cuda, dev):
+    """Rows of very different magnitude (per-token power-of-two scale) and an all-zero row."""
+    n, k, m = 128, 512, 16
+    wf = synth.normal("prefill", "wz", (n, k), 0.02)
+    raw = oracle.quantize(Q4_K, wf)
+    x = synth.normal("prefill", "xz", (m, k))
+    x[1] *= 1e-6
+    x[2] *= 3e5
+    x[3] = 0.0
+    w = cuda.register(raw, Q4_K, n, k)
+    got = dev.qmatmul_tc(to_dev(x), w).cpu().numpy()
+    want = oracle.qmatmul(Q4_K, x, raw, m, k, n)
+    bound = row_norm_bound(oracle, Q4_K, raw, n, k, x)
+    assert np.all(np.abs(got - want) <= bound + 1e-30)
+    assert np.all(got[3] == 0.0)
+    cuda.release(w)
+
+
+def test_tc_matmul_agrees_with_gemv_path(oracle, cuda, dev):
+    n, k, m = 256, 1024, 64
+    raw, x, got, w = _case(oracle, cuda, dev, n, k, m, tag="g")
+    ref = dev.qmatmul(to_dev(x), w, ops.Mode.ACT_F32).cpu().numpy()
+    bound = 2 * row_norm_bound(oracle, Q4_K, raw, n, k, x)
+    assert np.all(np.abs(got - ref) <= bound)
+    cuda.release(w)
+
+
+def test_tc_matmul_rejects_other_shapes(oracle, cuda, dev):
+    raw = oracle.quantize(Q4_K, synth.normal("prefill", "wr", (64, 256), 0.02))
+    w = cuda.register(raw, Q4_K, 64, 256)
+    with pytest.raises(ops.NotSupportedException):
+        dev.qmatmul_tc(to_dev(synth.normal("prefill", "xr", (4, 256))), w)
+    cuda.release(w)
