@@ -188,6 +188,11 @@ SMC_API int smc_rope_dev(smc_ctx *ctx, float *d_x, int seq, int heads, int headD
                          const float *d_cos, const float *d_sin, int neox, void *stream);
 /* Tensor<float>.AddInPlace (SharpMind.Core/Tensors/Tensor.cs:328-332): x += y. */
 SMC_API int smc_add_dev(smc_ctx *ctx, float *d_x, const float *d_y, int64_t n, void *stream);
+/* The residual add and the norm that follows it in a decoder block as one pass (UnhookedTransformerBlock.Forward,
+ * UnhookedTransformerBlock.cs:12-47: x.AddInPlace(attnOut); normed = norm2.Forward(x)): x += y, out = RMSNorm(x) * w.
+ * Same bits as smc_add_dev followed by smc_rmsnorm_dev. */
+SMC_API int smc_add_rmsnorm_dev(smc_ctx *ctx, float *d_x, const float *d_y, const float *d_w, float *d_out, int rows,
+                                int n, float eps, void *stream);
 /* Sampler.Argmax (SharpMind.Inference/Sampler.cs:50-58) per row: first maximum wins. */
 SMC_API int smc_argmax_dev(smc_ctx *ctx, const float *d_logits, int rows, int n, int *d_out, void *stream);
 /* EmbeddingTable.Forward (SharpMind.Core/Embeddings/EmbeddingTable.cs:87-116) gathering rows of a Q8_0
@@ -237,6 +242,10 @@ SMC_API int smc_model_kv_load(smc_ctx *ctx, smc_model *m, const float *d_k, cons
  * sequence (Sampler.Argmax, Sampler.cs:50-58).  `mode` is one of SMC_ACT_F32 / SMC_ACT_Q8 / SMC_REF_ORDER. */
 SMC_API int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, int pos, int mode,
                             float *d_logits, int *d_argmax, void *stream);
+
+/* A new weight whose rows are the rows of parts[0], parts[1], ... in order (same dtype and K, all registered
+ * with SMC_W_REPACK): how the decoder turns Wq / Wk / Wv into one matmul.  The parts stay valid. */
+SMC_API int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts, int count, smc_weight **out);
 
 /* ---- row-split matmul across GPUs -----------------------------------------------------------
  * No reference counterpart: SharpMind runs one device per process (Accelerator selection in

@@ -11,6 +11,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <type_traits>
+
 #include "smc_common.cuh"
 
 int smc_fail(smc_ctx *ctx, int code, const char *fmt, ...)
@@ -183,6 +185,7 @@ void smc_destroy(smc_ctx *ctx)
     cudaFree(ctx->d_stage_aux);
     cudaFree(ctx->d_attn_part);
     cudaFree(ctx->d_prefill);
+    cudaFree(ctx->d_argmax);
     cudaFree(ctx->d_status);
     if (ctx->h_pin) cudaFreeHost(ctx->h_pin);
     smc_q8act_free(ctx->act);
@@ -413,6 +416,65 @@ int smc_qmatmul_dev_gather(smc_ctx *ctx, const float *d_in, const smc_weight *w,
 }
 
 extern "C" {
+
+int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts, int count, smc_weight **out)
+{
+    if (!ctx || !parts || !out || count <= 0 || !parts[0]) return smc_fail(ctx, SMC_E_INVALID, "weight_concat: bad arguments");
+    const int dtype = parts[0]->dtype, K = parts[0]->K;
+    long long N = 0;
+    bool raw = true;
+    for (int i = 0; i < count; ++i) {
+        const smc_weight *p = parts[i];
+        if (!p || p->dtype != dtype || p->K != K) return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "weight_concat: parts differ in dtype or K");
+        if (!p->fast) return smc_fail(ctx, SMC_E_UNSUPPORTED, "weight_concat: parts must be registered with SMC_W_REPACK");
+        raw = raw && p->d_raw != nullptr;
+        N += p->N;
+    }
+    if (N > INT32_MAX) return smc_fail(ctx, SMC_E_RANGE, "weight_concat: too many rows");
+    SMC_CUDA(ctx, cudaSetDevice(ctx->device));
+    smc_weight *w = new smc_weight();
+    w->dtype = dtype, w->N = (int)N, w->K = K, w->flags = SMC_W_REPACK | (raw ? SMC_W_KEEP_RAW : 0), w->fast = true;
+    w->raw_bytes = (size_t)smc_raw_tensor_bytes(dtype, (int)N, K);
+    cudaError_t e = cudaSuccess;
+    // bytes per row of every array of the compute layout (rows are whole blocks when `fast`)
+    const size_t blk = (size_t)K / 256;
+    auto cat = [&](auto smc_weight::*field, size_t per_row) {
+        using T = std::remove_reference_t<decltype(w->*field)>;
+        if (e != cudaSuccess || per_row == 0) return;
+        uint8_t *dst = nullptr;
+        e = cudaMalloc(&dst, per_row * (size_t)N);
+        if (e != cudaSuccess) return;
+        w->*field = reinterpret_cast<T>(dst);
+        size_t off = 0;
+        for (int i = 0; i < count && e == cudaSuccess; ++i) {
+            const size_t bytes = per_row * (size_t)parts[i]->N;
+            e = cudaMemcpyAsync(dst + off, reinterpret_cast<const uint8_t *>(parts[i]->*field), bytes, cudaMemcpyDeviceToDevice,
+                                ctx->stream);
+            off += bytes;
+        }
+    };
+    if (raw) cat(&smc_weight::d_raw, (size_t)smc_raw_tensor_bytes(dtype, 1, K));
+    if (dtype == SMC_Q8_0) {
+        cat(&smc_weight::q8_qs, (size_t)K);
+        cat(&smc_weight::q8_d, (size_t)K / 32 * 2);
+    } else if (dtype == SMC_Q6_K) {
+        cat(&smc_weight::q6_ql, blk * 128);
+        cat(&smc_weight::q6_qh, blk * 64);
+        cat(&smc_weight::q6_sc, blk * 16);
+        cat(&smc_weight::q6_d, blk * 2);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        free_weight(w);
+        return smc_fail(ctx, SMC_E_CUDA, "weight_concat: %s", cudaGetErrorString(e));
+    }
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        ctx->by_host[static_cast<const void *>(w)] = w;  // no host bytes: the handle is its own key
+    }
+    *out = w;
+    return SMC_OK;
+}
 
 int smc_qmatmul_tc_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, void *stream)
 {

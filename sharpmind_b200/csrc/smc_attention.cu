@@ -123,21 +123,45 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
     }
 }
 
+constexpr int MERGE_MAX_SPLITS = 512;
+
+// Combines the per-split records of one (batch, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M),
+// both sums taken in split order.  The weights are computed once per split by the CTA and shared.
 __global__ void __launch_bounds__(256) sdpa_merge_kernel(const float *__restrict__ part, float *__restrict__ out,
                                                          int hd, int splits)
 {
     // grid.x = batch * heads
+    __shared__ float sw[MERGE_MAX_SPLITS], sl[MERGE_MAX_SPLITS];
+    __shared__ float red[8];
     const float *rec = part + (size_t)blockIdx.x * splits * (hd + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, rec[(size_t)s * (hd + 2)]);
+    float m = -INFINITY;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) m = fmaxf(m, rec[(size_t)s * (hd + 2)]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    float M = red[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) M = fmaxf(M, red[i]);
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        const float *r = rec + (size_t)s * (hd + 2);
+        sw[s] = (r[0] == -INFINITY) ? 0.f : expf(r[0] - M);
+        sl[s] = r[1];
+    }
+    __syncthreads();
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) L = fmaf(sl[s], sw[s], L);
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float L = 0.f, O = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float *r = rec + (size_t)s * (hd + 2);
-            float w = (r[0] == -INFINITY) ? 0.f : expf(r[0] - M);
-            L = fmaf(r[1], w, L);
-            O = fmaf(r[2 + d], w, O);
+        float O = 0.f;
+        int s = 0;
+        for (; s + 4 <= splits; s += 4) {
+            const float a = rec[(size_t)s * (hd + 2) + 2 + d], b = rec[(size_t)(s + 1) * (hd + 2) + 2 + d];
+            const float c = rec[(size_t)(s + 2) * (hd + 2) + 2 + d], e = rec[(size_t)(s + 3) * (hd + 2) + 2 + d];
+            O = fmaf(a, sw[s], O);
+            O = fmaf(b, sw[s + 1], O);
+            O = fmaf(c, sw[s + 2], O);
+            O = fmaf(e, sw[s + 3], O);
         }
+        for (; s < splits; ++s) O = fmaf(rec[(size_t)s * (hd + 2) + 2 + d], sw[s], O);
         out[(size_t)blockIdx.x * hd + d] = L > 0.f ? __fdiv_rn(O, L) : 0.f;
     }
 }
@@ -276,6 +300,7 @@ int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const 
     int max_splits = (kvLen + 63) / 64;
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
+    if (splits > MERGE_MAX_SPLITS) splits = MERGE_MAX_SPLITS;
     size_t need = (size_t)batch * heads * splits * (headDim + 2) * sizeof(float);
     if (need > ctx->attn_part_cap) {
         std::lock_guard<std::mutex> lock(ctx->mu);

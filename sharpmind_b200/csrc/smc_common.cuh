@@ -60,6 +60,8 @@ struct smc_ctx {
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
     bool use_tma = true;               // SMC_GEMV=stream in the environment selects the register-prefetch kernels
+    void *d_argmax = nullptr;          // chunk results and tickets of the argmax
+    int argmax_rows = 0, argmax_chunks = 0;
     void *d_prefill = nullptr;         // activation image of the tensor-core matmul
     size_t prefill_cap = 0;
     float *d_attn_part = nullptr;      // split-KV partial results

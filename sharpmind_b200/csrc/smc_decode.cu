@@ -5,7 +5,9 @@
 // (SharpMind.Model/Layers/Attention/AttentionLayer.cs:260-422) and FfnKernels.Gated
 // (SharpMind.Model/Layers/Ffn/FfnKernels.cs:35-59), for seqLen = 1 and `batch` lock-step sequences sharing
 // one position (the only batched semantics the reference's KVCache defines, KVCache.cs:21,149).
-// The step is a plain sequence of launches of the kernels in this library on the caller's stream;
+// The step is a sequence of launches of the kernels in this library on the caller's stream, with the
+// elementwise work between two matmuls folded into one launch each (joined Q/K/V matmul, then per-head
+// norm + RoPE + cache append in one kernel; residual add + the following RMSNorm in one kernel);
 // the KV cache, the RoPE tables and all intermediates are owned by the model object.
 #include <vector>
 
@@ -15,6 +17,8 @@ struct smc_model {
     smc_model_desc d{};
     int max_batch = 0;
     std::vector<const smc_weight *> wq, wk, wv, wo, wgu, wdown;
+    std::vector<smc_weight *> wqkv;  // rows of Wq, Wk, Wv in one matrix (owned), when the three could be joined
+    float *qkv = nullptr;            // [batch][qDim + 2 kvDim]
     std::vector<const float *> norm1, norm2, qnorm, knorm;
     float *kcache = nullptr, *vcache = nullptr;  // [layer][batch][kvHeads][max_seq][head_dim]
     float *cosT = nullptr, *sinT = nullptr;
@@ -25,11 +29,13 @@ struct smc_model {
 
 namespace {
 
-void free_model(smc_model *m)
+void free_model(smc_ctx *ctx, smc_model *m)
 {
     if (!m) return;
-    float *bufs[] = {m->kcache, m->vcache, m->cosT, m->sinT, m->x, m->xn, m->q, m->k, m->v, m->att, m->tmp, m->gu, m->act};
+    float *bufs[] = {m->kcache, m->vcache, m->cosT, m->sinT, m->x, m->xn, m->q, m->k, m->v, m->att, m->tmp, m->gu, m->act, m->qkv};
     for (float *p : bufs) cudaFree(p);
+    for (smc_weight *w : m->wqkv)
+        if (w) smc_weight_release(ctx, w);
     smc_q8act_free(m->qa);
     smc_q8act_free(m->qb);
     delete m;
@@ -60,6 +66,93 @@ __global__ void kv_load_kernel(const float *__restrict__ src, float *__restrict_
         long long l = r / batch;
         dst[(((l * max_batch + b) * kvh + h) * max_seq + p) * hd + d] = src[t];
     }
+}
+
+// What follows the joined Q/K/V matmul for one new token per sequence, one warp per (sequence, head slot):
+// per-head RMSNorm of Q and K (AttentionLayer.cs:300-318), RoPE at position `pos` (RoPE.Apply, RoPE.cs:168-277),
+// K and V written into the cache at `pos` (KVCache.Update, KVCache.cs:84-150), Q written densely for the
+// attention kernel.  Lane l holds elements l, l + 32, ...: the norm sums in the order of the stand-alone norm
+// kernel and the rotation uses the same unfused products, so the results are the same bits as the separate
+// launches.  headDim % 64 == 0, headDim <= 256.
+template <int EPL>  // elements per lane = headDim / 32
+__global__ void __launch_bounds__(256) qkv_post_kernel(const float *__restrict__ qkv, float *__restrict__ q_out,
+                                                       float *__restrict__ kc, float *__restrict__ vc,
+                                                       const float *__restrict__ qnorm, const float *__restrict__ knorm,
+                                                       const float *__restrict__ cosT, const float *__restrict__ sinT, int batch,
+                                                       int nh, int nkv, int pos, int maxSeq, float eps, int neox)
+{
+    constexpr int HD = EPL * 32, PAIRS = HD / 2;
+    const int lane = threadIdx.x & 31;
+    const int slots = nh + 2 * nkv;
+    const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= batch * slots) return;
+    const int b = wid / slots, slot = wid % slots;
+    const float *src = qkv + (size_t)b * slots * HD + (size_t)slot * HD;
+    float v[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] = src[lane + 32 * j];
+    if (slot >= nh + nkv) {  // V: straight into the cache
+        float *dst = vc + (((size_t)b * nkv + (slot - nh - nkv)) * maxSeq + pos) * HD;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) dst[lane + 32 * j] = v[j];
+        return;
+    }
+    const bool is_q = slot < nh;
+    const float *nw = is_q ? qnorm : knorm;
+    if (nw) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) ss = fmaf(v[j], v[j], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = __fdiv_rn(1.0f, sqrtf(__fdiv_rn(ss, (float)HD) + eps));
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) v[j] = (v[j] * inv) * nw[lane + 32 * j];
+    }
+    const float *ct = cosT + (size_t)pos * PAIRS, *st = sinT + (size_t)pos * PAIRS;
+    if (neox) {  // pairs (i, i + headDim / 2): both halves live in this lane
+#pragma unroll
+        for (int j = 0; j < EPL / 2; ++j) {
+            const int i = lane + 32 * j;
+            const float c = __ldg(ct + i), sn = __ldg(st + i);
+            const float a = v[j], bb = v[j + EPL / 2];
+            v[j] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(bb, sn));
+            v[j + EPL / 2] = __fadd_rn(__fmul_rn(bb, c), __fmul_rn(a, sn));
+        }
+    } else {  // pairs (2i, 2i + 1): the partner sits in the neighbouring lane
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            const int e = lane + 32 * j, i = e >> 1;
+            const float c = __ldg(ct + i), sn = __ldg(st + i);
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+            v[j] = (lane & 1) ? __fadd_rn(__fmul_rn(v[j], c), __fmul_rn(other, sn))
+                              : __fsub_rn(__fmul_rn(v[j], c), __fmul_rn(other, sn));
+        }
+    }
+    float *dst = is_q ? q_out + ((size_t)b * nh + slot) * HD : kc + (((size_t)b * nkv + (slot - nh)) * maxSeq + pos) * HD;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) dst[lane + 32 * j] = v[j];
+}
+
+int launch_qkv_post(smc_ctx *ctx, const smc_model *m, int l, float *kc, float *vc, int B, int pos, cudaStream_t s)
+{
+    const smc_model_desc &d = m->d;
+    const int warps = B * (d.n_heads + 2 * d.n_kv_heads);
+    const dim3 grid((warps + 7) / 8);
+    const float *qn = d.qk_norm ? m->qnorm[l] : nullptr, *kn = d.qk_norm ? m->knorm[l] : nullptr;
+#define SMC_QKV_POST(E)                                                                                                  \
+    qkv_post_kernel<E><<<grid, 256, 0, s>>>(m->qkv, m->q, kc, vc, qn, kn, m->cosT, m->sinT, B, d.n_heads, d.n_kv_heads, \
+                                            pos, d.max_seq, d.eps, d.neox)
+    switch (d.head_dim) {
+    case 64: SMC_QKV_POST(2); break;
+    case 128: SMC_QKV_POST(4); break;
+    case 192: SMC_QKV_POST(6); break;
+    case 256: SMC_QKV_POST(8); break;
+    default: return smc_fail(ctx, SMC_E_UNSUPPORTED, "joined QKV path needs headDim in {64, 128, 192, 256}");
+    }
+#undef SMC_QKV_POST
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
 }
 
 }  // namespace
@@ -121,10 +214,11 @@ int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, sm
     alloc(&m->kcache, cache), alloc(&m->vcache, cache), alloc(&m->cosT, half), alloc(&m->sinT, half);
     alloc(&m->x, B * H), alloc(&m->xn, B * H), alloc(&m->q, B * qDim), alloc(&m->k, B * kvDim), alloc(&m->v, B * kvDim);
     alloc(&m->att, B * qDim), alloc(&m->tmp, B * H), alloc(&m->gu, B * 2 * F), alloc(&m->act, B * F);
+    alloc(&m->qkv, B * (qDim + 2 * kvDim));
     if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache * sizeof(float));
     if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache * sizeof(float));
     if (e != cudaSuccess) {
-        free_model(m);
+        free_model(ctx, m);
         return smc_fail(ctx, SMC_E_CUDA, "model_create: allocation failed: %s", cudaGetErrorString(e));
     }
     int rc = 0;
@@ -132,12 +226,27 @@ int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, sm
     const int wide = qDim > F ? qDim : F;
     if (!rc && wide % 32 == 0) rc = smc_q8act_alloc(ctx, max_batch, wide, &m->qb);
     if (rc) {
-        free_model(m);
+        free_model(ctx, m);
+        return rc;
+    }
+    // one matmul for Q, K and V where the three matrices can be joined (same format, vector layout) and the
+    // head size suits the kernel that follows it
+    m->wqkv.assign(d.n_layers, nullptr);
+    const bool hd_ok = d.head_dim == 64 || d.head_dim == 128 || d.head_dim == 192 || d.head_dim == 256;
+    for (int l = 0; l < d.n_layers && hd_ok && !rc; ++l) {
+        const smc_weight *parts[3] = {m->wq[l], m->wk[l], m->wv[l]};
+        if (!(parts[0]->fast && parts[1]->fast && parts[2]->fast && parts[0]->dtype == parts[1]->dtype &&
+              parts[0]->dtype == parts[2]->dtype))
+            continue;
+        rc = smc_weight_concat_rows(ctx, parts, 3, &m->wqkv[l]);
+    }
+    if (rc) {
+        free_model(ctx, m);
         return rc;
     }
     rc = smc_rope_tables(ctx, d.rope_theta, d.head_dim, d.max_seq, m->cosT, m->sinT);
     if (rc) {
-        free_model(m);
+        free_model(ctx, m);
         return rc;
     }
     *out = m;
@@ -149,7 +258,7 @@ int smc_model_destroy(smc_ctx *ctx, smc_model *m)
     if (!ctx || !m) return smc_fail(ctx, SMC_E_INVALID, "model_destroy: bad arguments");
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
-    free_model(m);
+    free_model(ctx, m);
     return SMC_OK;
 }
 
@@ -186,36 +295,44 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
     } while (0)
 
     SMC_TRY(smc_embed_q8_0_dev(ctx, d.lm_head, d_tokens, B, m->x, s));
+    SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm1[0], m->xn, B, H, d.eps, s));
     for (int l = 0; l < d.n_layers; ++l) {
-        SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm1[l], m->xn, B, H, d.eps, s));
-        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
-        SMC_TRY(linear(ctx, m->xn, m->wq[l], m->q, B, mode, reuse ? m->qa : nullptr, s));
-        SMC_TRY(linear(ctx, m->xn, m->wk[l], m->k, B, mode, reuse ? m->qa : nullptr, s));
-        SMC_TRY(linear(ctx, m->xn, m->wv[l], m->v, B, mode, reuse ? m->qa : nullptr, s));
-        if (d.qk_norm) {
-            SMC_TRY(smc_rmsnorm_dev(ctx, m->q, m->qnorm[l], m->q, B * nh, hd, d.eps, s));
-            SMC_TRY(smc_rmsnorm_dev(ctx, m->k, m->knorm[l], m->k, B * nkv, hd, d.eps, s));
-        }
-        // every sequence is one token at position `pos`: [1, B*heads, headDim] with offset pos
-        SMC_TRY(smc_rope_dev(ctx, m->q, 1, B * nh, hd, hd, pos, m->cosT, m->sinT, d.neox, s));
-        SMC_TRY(smc_rope_dev(ctx, m->k, 1, B * nkv, hd, hd, pos, m->cosT, m->sinT, d.neox, s));
+        // m->xn holds RMSNorm(x) with this layer's first norm (made by the previous layer's tail)
         float *kc = m->kcache + (size_t)l * layer_stride, *vc = m->vcache + (size_t)l * layer_stride;
-        SMC_TRY(smc_kv_append_dev(ctx, m->k, m->v, kc, vc, B, nkv, hd, pos, d.max_seq, s));
+        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
+        // the joined matrix carries no GGUF-layout copy unless its parts kept theirs: reference order needs it
+        const smc_weight *joined = m->wqkv[l];
+        if (joined && (mode != SMC_REF_ORDER || joined->d_raw)) {
+            SMC_TRY(linear(ctx, m->xn, joined, m->qkv, B, mode, reuse ? m->qa : nullptr, s));
+            SMC_TRY(launch_qkv_post(ctx, m, l, kc, vc, B, pos, s));
+        } else {
+            SMC_TRY(linear(ctx, m->xn, m->wq[l], m->q, B, mode, reuse ? m->qa : nullptr, s));
+            SMC_TRY(linear(ctx, m->xn, m->wk[l], m->k, B, mode, reuse ? m->qa : nullptr, s));
+            SMC_TRY(linear(ctx, m->xn, m->wv[l], m->v, B, mode, reuse ? m->qa : nullptr, s));
+            if (d.qk_norm) {
+                SMC_TRY(smc_rmsnorm_dev(ctx, m->q, m->qnorm[l], m->q, B * nh, hd, d.eps, s));
+                SMC_TRY(smc_rmsnorm_dev(ctx, m->k, m->knorm[l], m->k, B * nkv, hd, d.eps, s));
+            }
+            // every sequence is one token at position `pos`: [1, B*heads, headDim] with offset pos
+            SMC_TRY(smc_rope_dev(ctx, m->q, 1, B * nh, hd, hd, pos, m->cosT, m->sinT, d.neox, s));
+            SMC_TRY(smc_rope_dev(ctx, m->k, 1, B * nkv, hd, hd, pos, m->cosT, m->sinT, d.neox, s));
+            SMC_TRY(smc_kv_append_dev(ctx, m->k, m->v, kc, vc, B, nkv, hd, pos, d.max_seq, s));
+        }
         SMC_TRY(smc_sdpa_decode_dev(ctx, m->q, kc, vc, m->att, B, nh, nkv, hd, pos + 1, d.max_seq, scale, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->att, B, qDim, m->qb, s));
         SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s));
-        SMC_TRY(smc_add_dev(ctx, m->x, m->tmp, (int64_t)B * H, s));
-        SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm2[l], m->xn, B, H, d.eps, s));
+        SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, B, H, d.eps, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
         SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, B, mode, reuse ? m->qa : nullptr, s));
         SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, B, F, 2 * F, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->act, B, F, m->qb, s));
         SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s));
-        SMC_TRY(smc_add_dev(ctx, m->x, m->tmp, (int64_t)B * H, s));
+        // residual add, then the next block's first norm (the final norm after the last block)
+        const float *next_norm = l + 1 < d.n_layers ? m->norm1[l + 1] : d.final_norm;
+        SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, B, H, d.eps, s));
     }
-    SMC_TRY(smc_rmsnorm_dev(ctx, m->x, d.final_norm, m->x, B, H, d.eps, s));
-    if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->x, B, H, m->qa, s));
-    SMC_TRY(linear(ctx, m->x, d.lm_head, d_logits, B, mode, reuse ? m->qa : nullptr, s));
+    if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
+    SMC_TRY(linear(ctx, m->xn, d.lm_head, d_logits, B, mode, reuse ? m->qa : nullptr, s));
     if (d_argmax) SMC_TRY(smc_argmax_dev(ctx, d_logits, B, d.vocab, d_argmax, s));
 #undef SMC_TRY
     return SMC_OK;

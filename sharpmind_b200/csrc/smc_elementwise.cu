@@ -113,6 +113,52 @@ __global__ void __launch_bounds__(256) rmsnorm_cta_kernel(const float *x, const 
     }
 }
 
+// x[row] += y[row] (Tensor.AddInPlace), then out[row] = RMSNorm(x[row]) * w: the residual add and the norm that
+// follows it in a decoder block as one pass.  Arithmetic and summation order are those of add_kernel followed by
+// rmsnorm_cta_kernel, so the fused and the separate forms give the same bits.
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float *__restrict__ y, const float *__restrict__ w,
+                                                          float *out, int n, float eps, int vec)
+{
+    __shared__ float red[32];
+    float *p = x + (size_t)blockIdx.x * n;
+    const float *q = y + (size_t)blockIdx.x * n;
+    float *o = out + (size_t)blockIdx.x * n;
+    float ss = 0.f;
+    if (vec) {
+        float4 *p4 = reinterpret_cast<float4 *>(p);
+        const float4 *q4 = reinterpret_cast<const float4 *>(q);
+        for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+            const float4 a = p4[i], b = q4[i];
+            const float4 v = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+            p4[i] = v;
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = p[i] + q[i];
+            p[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = __fdiv_rn(1.0f, sqrtf(__fdiv_rn(ss, (float)n) + eps));
+    // each thread re-reads exactly the elements it wrote above
+    if (vec) {
+        const float4 *p4 = reinterpret_cast<const float4 *>(p);
+        const float4 *w4 = reinterpret_cast<const float4 *>(w);
+        float4 *o4 = reinterpret_cast<float4 *>(o);
+        for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+            const float4 v = p4[i], g = __ldg(w4 + i);
+            o4[i] = make_float4((v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = (p[i] * inv) * w[i];
+    }
+}
+
 __global__ void rmsnorm_row_kernel(const float *__restrict__ src, const float *__restrict__ w, float *__restrict__ dst,
                                    int n, float rms_inv)
 {
@@ -240,41 +286,71 @@ __global__ void __launch_bounds__(256) add_kernel(float *__restrict__ x, const f
     }
 }
 
-__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, int n, int *__restrict__ out)
+// First index of the largest value per row (Sampler.Argmax keeps the first maximum).  A row is cut into
+// chunks scanned by one CTA each; the CTA that finishes a row last combines the chunk results.
+constexpr int ARGMAX_CHUNK = 2048;
+
+__device__ __forceinline__ bool argmax_better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, int n, int chunks, float *part_v,
+                                                     int *part_i, unsigned *tickets, int *__restrict__ out)
 {
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const float *p = logits + (size_t)blockIdx.x * n;
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ int s_last;
+    const int row = blockIdx.y, c = blockIdx.x;
+    const float *p = logits + (size_t)row * n;
+    const int lo = c * ARGMAX_CHUNK, hi = min(n, lo + ARGMAX_CHUNK);
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = p[i];
-        if (v > best || idx == 0x7fffffff) {  // strict > keeps the first maximum of this thread's stride
-            best = v;
-            idx = i;
-        }
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = p[i];
+        if (v > best || idx == 0x7fffffff) best = v, idx = i;  // strict > keeps the first maximum of the stride
     }
-    // reduce (value, index): larger value wins, ties go to the smaller index
-    auto better = [](float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); };
+    auto reduce_warp = [&]() {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (better(ov, oi, best, idx)) best = ov, idx = oi;
-    }
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (argmax_better(ov, oi, best, idx)) best = ov, idx = oi;
+        }
+    };
+    reduce_warp();
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     if (lane == 0) sv[wid] = best, si[wid] = idx;
     __syncthreads();
     if (wid == 0) {
-        best = lane < nw ? sv[lane] : -INFINITY;
-        idx = lane < nw ? si[lane] : 0x7fffffff;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (better(ov, oi, best, idx)) best = ov, idx = oi;
+        best = lane < 8 ? sv[lane] : -INFINITY;
+        idx = lane < 8 ? si[lane] : 0x7fffffff;
+        reduce_warp();
+        if (lane == 0) {
+            part_v[(size_t)row * chunks + c] = best;
+            part_i[(size_t)row * chunks + c] = idx;
+            __threadfence();
+            s_last = atomicAdd(&tickets[row], 1u) == (unsigned)chunks - 1 ? 1 : 0;
         }
-        if (lane == 0) out[blockIdx.x] = idx;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    best = -INFINITY, idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+        const float v = __ldcg(part_v + (size_t)row * chunks + i);
+        const int vi = __ldcg(part_i + (size_t)row * chunks + i);
+        if (argmax_better(v, vi, best, idx)) best = v, idx = vi;
+    }
+    reduce_warp();
+    __syncthreads();
+    if (lane == 0) sv[wid] = best, si[wid] = idx;
+    __syncthreads();
+    if (wid == 0) {
+        best = lane < 8 ? sv[lane] : -INFINITY;
+        idx = lane < 8 ? si[lane] : 0x7fffffff;
+        reduce_warp();
+        if (lane == 0) {
+            out[row] = idx;
+            tickets[row] = 0;
+        }
     }
 }
 
@@ -324,12 +400,32 @@ int smc_rmsnorm_dev(smc_ctx *ctx, const float *d_x, const float *d_w, float *d_o
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     bool aligned = ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_out) |
                      reinterpret_cast<uintptr_t>(d_w)) & 15) == 0;
-    if (n <= 1024) {
-        // short rows (per-head QK norm, hidden 1024): a warp per row
+    if (n <= 256) {
+        // short rows (per-head QK norm): a warp per row
         rmsnorm_warp_kernel<<<(rows + 7) / 8, 256, 0, s>>>(d_x, d_w, d_out, rows, n, eps);
     } else {
         rmsnorm_cta_kernel<<<rows, 256, 0, s>>>(d_x, d_w, d_out, n, eps, (aligned && (n & 3) == 0) ? 1 : 0);
     }
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+int smc_add_rmsnorm_dev(smc_ctx *ctx, float *d_x, const float *d_y, const float *d_w, float *d_out, int rows, int n,
+                        float eps, void *stream)
+{
+    if (ctx && rows == 0) return SMC_OK;
+    if (!ctx || !d_x || !d_y || !d_w || !d_out || rows < 0 || n <= 0)
+        return smc_fail(ctx, SMC_E_INVALID, "add_rmsnorm: bad arguments");
+    if (n <= 256) {  // short rows: the two separate kernels (a warp per row)
+        int rc = smc_add_dev(ctx, d_x, d_y, (int64_t)rows * n, stream);
+        if (rc) return rc;
+        return smc_rmsnorm_dev(ctx, d_x, d_w, d_out, rows, n, eps, stream);
+    }
+    // the vector form needs what both separate kernels need: add_kernel vectorises on the whole tensor
+    const bool aligned = ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_y) |
+                           reinterpret_cast<uintptr_t>(d_out) | reinterpret_cast<uintptr_t>(d_w)) & 15) == 0;
+    add_rmsnorm_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(d_x, d_y, d_w, d_out, n, eps,
+                                                                            (aligned && (n & 3) == 0) ? 1 : 0);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
@@ -421,8 +517,30 @@ int smc_argmax_dev(smc_ctx *ctx, const float *d_logits, int rows, int n, int *d_
 {
     if (!ctx || !d_logits || !d_out || rows < 0 || n <= 0) return smc_fail(ctx, SMC_E_INVALID, "argmax: bad arguments");
     if (rows == 0) return SMC_OK;
-    int threads = n >= 4096 ? 1024 : 256;
-    argmax_kernel<<<rows, threads, 0, static_cast<cudaStream_t>(stream)>>>(d_logits, n, d_out);
+    const int chunks = (n + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+    {
+        // scratch for the chunk results and the per-row tickets, grown on demand (the first call of a larger
+        // shape allocates: make it outside stream capture).  Layout: values [rows x chunks] | indices | tickets.
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (rows > ctx->argmax_rows || chunks > ctx->argmax_chunks) {
+            const int big_rows = rows > ctx->argmax_rows ? rows : ctx->argmax_rows;
+            const int big_chunks = chunks > ctx->argmax_chunks ? chunks : ctx->argmax_chunks;
+            if (ctx->d_argmax) {
+                cudaDeviceSynchronize();
+                cudaFree(ctx->d_argmax);
+                ctx->d_argmax = nullptr, ctx->argmax_rows = ctx->argmax_chunks = 0;
+            }
+            const size_t bytes = (size_t)big_rows * big_chunks * 8 + (size_t)big_rows * 4;
+            SMC_CUDA(ctx, cudaMalloc(&ctx->d_argmax, bytes));
+            SMC_CUDA(ctx, cudaMemset(ctx->d_argmax, 0, bytes));
+            ctx->argmax_rows = big_rows, ctx->argmax_chunks = big_chunks;
+        }
+    }
+    const size_t cap_cells = (size_t)ctx->argmax_rows * ctx->argmax_chunks;
+    float *pv = reinterpret_cast<float *>(ctx->d_argmax);
+    int *pi = reinterpret_cast<int *>(pv + cap_cells);
+    unsigned *tk = reinterpret_cast<unsigned *>(pi + cap_cells);
+    argmax_kernel<<<dim3(chunks, rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(d_logits, n, chunks, pv, pi, tk, d_out);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }

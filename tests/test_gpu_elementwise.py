@@ -209,3 +209,41 @@ def test_empty_inputs_are_no_ops(dev):
     assert dev.rmsnorm(e, w, 1e-6).shape == (0, 128)
     assert dev.softmax(e).shape == (0, 128)
     assert dev.silu(e).shape == (0, 128)
+
+
+@pytest.mark.parametrize("rows,n", [(1, 1024), (3, 4096), (5, 1000), (2, 128), (4, 1026)])
+def test_add_rmsnorm_equals_separate_launches(dev, rows, n):
+    """The fused residual add + RMSNorm gives the bits of smc_add_dev followed by smc_rmsnorm_dev."""
+    import ctypes as C
+
+    import torch
+
+    x = to_dev(synth.normal("gpue", f"arx{rows}_{n}", (rows, n)))
+    y = to_dev(synth.normal("gpue", f"ary{rows}_{n}", (rows, n)))
+    w = to_dev(synth.normal("gpue", f"arw{n}", (n,), 0.1, 1.0))
+    x1 = x.clone()
+    dev.add_(x1, y)
+    want = dev.rmsnorm(x1, w, 1e-6)
+    x2, out = x.clone(), torch.empty_like(x)
+    ctx = dev.ctx
+    ctx.check(ctx.lib.smc_add_rmsnorm_dev(ctx.h, x2.data_ptr(), y.data_ptr(), w.data_ptr(), out.data_ptr(), rows, n,
+                                          C.c_float(1e-6), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    assert torch.equal(x1, x2)
+    assert torch.equal(out, want)
+
+
+def test_argmax_first_maximum_over_chunks(dev):
+    import torch
+
+    logits = to_dev(synth.normal("gpue", "amx", (5, 151936)))
+    logits[1, 70000] = 50.0
+    logits[1, 150000] = 50.0   # a later tie: the first one wins
+    logits[2, 0] = 60.0
+    logits[3, 151935] = 60.0
+    logits[4, :] = -3.0        # all equal: index 0
+    got = dev.argmax(logits).cpu().numpy()
+    want = logits.cpu().numpy().argmax(axis=1)
+    assert got.tolist() == want.tolist()
+    assert got[1] == 70000 and got[4] == 0
+    small = to_dev(synth.normal("gpue", "ams", (7, 100)))
+    assert dev.argmax(small).cpu().numpy().tolist() == small.cpu().numpy().argmax(axis=1).tolist()
