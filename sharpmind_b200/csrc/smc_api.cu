@@ -169,6 +169,7 @@ int smc_init(int device, smc_ctx **out)
     }
     const char *impl = getenv("SMC_GEMV");
     ctx->use_tma = !(impl && strcmp(impl, "stream") == 0);
+    ctx->use_mma = !(impl && strcmp(impl, "dp4a") == 0);
     *out = ctx;
     return SMC_OK;
 }

@@ -59,6 +59,7 @@ struct smc_ctx {
     // scratch owned by the context
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
+    bool use_mma = true;               // SMC_GEMV=dp4a in the environment keeps batches on the dp4a kernels
     bool use_tma = true;               // SMC_GEMV=stream in the environment selects the register-prefetch kernels
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
     int argmax_rows = 0, argmax_chunks = 0;
@@ -102,6 +103,8 @@ int smc_qmatmul_dev_gather(smc_ctx *, const float *d_in, const smc_weight *, flo
                            const smc_gather_dev *, bool *fused);
 bool smc_prefill_supported(const smc_weight *, int M);
 int smc_launch_prefill_q4k(smc_ctx *, const float *x, const smc_weight *, float *out, int M, cudaStream_t s);
+bool smc_mma_supported(const smc_weight *, int M);
+int smc_launch_gemv_mma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 bool smc_stream_supported(const smc_weight *, int M);
 int smc_launch_gemv_stream(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,

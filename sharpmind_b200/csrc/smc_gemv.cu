@@ -530,6 +530,8 @@ int smc_launch_gemv_f32(smc_ctx *ctx, const float *x, const smc_weight *w, float
 
 int smc_launch_gemv_q8(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *out, cudaStream_t s)
 {
+    // two or more rows: per-block integer sums on the int8 tensor-core path (Q8_0, Q4_K)
+    if (ctx->use_mma && smc_mma_supported(w, a->M)) return smc_launch_gemv_mma(ctx, a, w, out, s);
     if (ctx->use_tma && smc_tma_supported(w, a->M)) return smc_launch_gemv_tma(ctx, a, w, out, s);
     if (smc_stream_supported(w, a->M)) return smc_launch_gemv_stream(ctx, a, w, out, s);
     ActPtrs ap{};

@@ -1,0 +1,261 @@
+// Small-batch (2..32 rows, larger batches in passes of 32) quantised-activation matmul on the int8 tensor-core
+// path: out[t, r] = sum_blocks (dw * dx) * isum(block) (- the Q4_K min term), the arithmetic of SMC_ACT_Q8.
+//
+// Why MMA here: with a handful of activation rows the dp4a kernels issue one integer dot per (row, token,
+// 4 bytes) and become instruction-bound long before HBM is busy.  One mma.m16n8k32 (s8 x s8 -> s32) covers
+// 16 weight rows x 8 tokens x one 32-element block, so the per-block integer sums of 32 rows x 32 tokens cost
+// 8 instructions per warp; the per-block scaling (int -> float, dw * dx, fused multiply-add) stays on the
+// CUDA cores and is what remains.  Integer block sums are exact, so they equal the dp4a kernels' sums; each
+// output adds its scaled block sums in k order within a warp's k range and the eight warps of a CTA (which
+// split K) are added in warp order: the result of a row does not depend on the batch size or on the other
+// rows (for any batch >= 2; the one-row kernels use a different summation tree).
+//
+// Layout choices.  A CTA owns 32 weight rows (two m16 tiles) and all tokens; its 8 warps take interleaved
+// k groups and meet in shared memory at the end.  Fragments are loaded straight from global memory as 8-byte
+// words: the dot product does not care about the order of k inside a block, so MMA k index 4*tg + i is bound to
+// byte 8*tg + i and 16 + 4*tg + i to byte 8*tg + 4 + i of the block, for weights and activations alike; a
+// quad of lanes then reads one whole 32-byte sector per row.  Scales are loaded once per lane (lane = row for
+// the weights, lane = token for the activations) and handed round with shuffles.
+#include "smc_common.cuh"
+
+namespace {
+
+constexpr int MMA_ROWS = 32;   // weight rows per CTA
+constexpr int MMA_WARPS = 8;
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+__device__ __forceinline__ uint2 ldg8(const void *p)
+{
+    uint2 v;
+    asm("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));  // not volatile: free to be hoisted
+    return v;
+}
+
+// Adds the eight warps' partial tiles in warp order and stores out[t, r]; red is [8 warps][32 tokens][33].
+template <int NT>
+__device__ __forceinline__ void reduce_and_store(float (*red)[32][33], const float (&acc)[2][NT][4], float *out, int N, int M,
+                                                 int r0, int t0)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) red[warp][8 * t + 2 * tg + (i & 1)][mt * 16 + g + ((i >> 1) << 3)] = acc[mt][t][i];
+    __syncthreads();
+    for (int o = threadIdx.x; o < 32 * 8 * NT; o += blockDim.x) {
+        const int row = o & 31, tok = o >> 5;
+        float s = red[0][tok][row];
+#pragma unroll
+        for (int w = 1; w < MMA_WARPS; ++w) s += red[w][tok][row];
+        if (r0 + row < N && t0 + tok < M) out[(size_t)(t0 + tok) * N + r0 + row] = s;
+    }
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------ Q8_0
+// Planes: quants [N][K] int8, scales [N][K/32] fp16.  K % 128 == 0; a warp works on groups of four blocks.
+template <int NT>
+__global__ void __launch_bounds__(256, 2)
+gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ wd, const int8_t *__restrict__ xq,
+                     const float *__restrict__ xd, float *__restrict__ out, int N, int K, int M)
+{
+    __shared__ float red[MMA_WARPS][32][33];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
+    const int r0 = blockIdx.x * MMA_ROWS;
+    const int nb = K / 32, ngroups = nb / 4;
+    // rows past the end are clamped for loads and masked at the store
+    const int8_t *arow[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) arow[j] = wq + (size_t)min(r0 + (j >> 1) * 16 + g + (j & 1) * 8, N - 1) * K + 8 * tg;
+    const __half *drow = wd + (size_t)min(r0 + lane, N - 1) * nb;
+    for (int t0 = 0; t0 < M; t0 += 8 * NT) {
+        const int8_t *brow[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) brow[t] = xq + (size_t)min(t0 + 8 * t + g, M - 1) * K + 8 * tg;
+        const float *xrow = xd + (size_t)min(t0 + lane, M - 1) * nb;
+        float acc[2][NT][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
+        for (int gi = warp; gi < ngroups; gi += MMA_WARPS) {
+            // all weight bytes of the group are requested before any of them is used: 4 KB in flight per warp
+            uint2 aq[4][4];
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) aq[kb][j] = ldg8(arow[j] + (gi * 4 + kb) * 32);
+            const uint2 dwp = *reinterpret_cast<const uint2 *>(drow + gi * 4);   // this lane's row, 4 blocks
+            const float4 dxp = *reinterpret_cast<const float4 *>(xrow + gi * 4);  // this lane's token, 4 blocks
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                const int koff = (gi * 4 + kb) * 32;
+                uint2 b[NT];
+                const uint2 (&a)[4] = aq[kb];
+#pragma unroll
+                for (int t = 0; t < NT; ++t) b[t] = ldg8(brow[t] + koff);
+                const uint32_t dword = (kb & 2) ? dwp.y : dwp.x;
+                const float dxl = kb == 0 ? dxp.x : kb == 1 ? dxp.y : kb == 2 ? dxp.z : dxp.w;
+                float dw[2][2];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t wv = __shfl_sync(0xffffffffu, dword, (j >> 1) * 16 + g + (j & 1) * 8);
+                    dw[j >> 1][j & 1] = smc_h2f((uint16_t)((kb & 1) ? (wv >> 16) : (wv & 0xFFFFu)));
+                }
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    const float dx0 = __shfl_sync(0xffffffffu, dxl, 8 * t + 2 * tg);
+                    const float dx1 = __shfl_sync(0xffffffffu, dxl, 8 * t + 2 * tg + 1);
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        int c[4];
+                        mma_s8(c, a[2 * mt].x, a[2 * mt + 1].x, a[2 * mt].y, a[2 * mt + 1].y, b[t].x, b[t].y);
+                        acc[mt][t][0] = fmaf((float)c[0], dw[mt][0] * dx0, acc[mt][t][0]);
+                        acc[mt][t][1] = fmaf((float)c[1], dw[mt][0] * dx1, acc[mt][t][1]);
+                        acc[mt][t][2] = fmaf((float)c[2], dw[mt][1] * dx0, acc[mt][t][2]);
+                        acc[mt][t][3] = fmaf((float)c[3], dw[mt][1] * dx1, acc[mt][t][3]);
+                    }
+                }
+            }
+        }
+        reduce_and_store<NT>(red, acc, out, N, M, r0, t0);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ Q4_K
+// GGUF blocks of 144 bytes: d, dmin (fp16), 12 packed scale / min bytes, 128 nibble bytes; the 32 bytes of
+// group gq hold sub-block 2*gq in the low nibbles and 2*gq + 1 in the high ones.  K % 256 == 0; a warp works
+// on whole 256-element blocks.  out += d*sc_j * dx * isum  -  dmin*m_j * (dx * sum(xq))  per sub-block.
+template <int NT>
+__global__ void __launch_bounds__(256, 2)
+gemv_mma_q4_K_kernel(const uint8_t *__restrict__ raw, const int8_t *__restrict__ xq, const float *__restrict__ xd,
+                     const float *__restrict__ xsd, float *__restrict__ out, int N, int K, int M)
+{
+    __shared__ float red[MMA_WARPS][32][33];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
+    const int r0 = blockIdx.x * MMA_ROWS;
+    const int nb = K / 32, nsb = K / 256;
+    const size_t row_bytes = (size_t)nsb * 144;
+    const uint8_t *arow[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) arow[j] = raw + (size_t)min(r0 + (j >> 1) * 16 + g + (j & 1) * 8, N - 1) * row_bytes + 16 + 8 * tg;
+    const uint8_t *hrow = raw + (size_t)min(r0 + lane, N - 1) * row_bytes;
+    for (int t0 = 0; t0 < M; t0 += 8 * NT) {
+        const int8_t *brow[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) brow[t] = xq + (size_t)min(t0 + 8 * t + g, M - 1) * K + 8 * tg;
+        const float *xrow = xd + (size_t)min(t0 + lane, M - 1) * nb;
+        const float *srow = xsd + (size_t)min(t0 + lane, M - 1) * nb;
+        float acc[2][NT][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
+        for (int sb = warp; sb < nsb; sb += MMA_WARPS) {
+            // this lane's row: d * sc_j and dmin * m_j of the eight sub-blocks
+            const uint4 hdr = *reinterpret_cast<const uint4 *>(hrow + (size_t)sb * 144);
+            const float d = smc_h2f((uint16_t)(hdr.x & 0xFFFFu)), dmin = smc_h2f((uint16_t)(hdr.x >> 16));
+            float dsc[8], dmn[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                int sc, mn;
+                smc_k4_scale_min(hdr.y, hdr.z, hdr.w, j, sc, mn);
+                dsc[j] = d * (float)sc;
+                dmn[j] = dmin * (float)mn;
+            }
+            // this lane's token: activation scale and scale * sum(q) of the eight sub-blocks
+            const float4 dxa = *reinterpret_cast<const float4 *>(xrow + sb * 8), dxb = *reinterpret_cast<const float4 *>(xrow + sb * 8 + 4);
+            const float4 sxa = *reinterpret_cast<const float4 *>(srow + sb * 8), sxb = *reinterpret_cast<const float4 *>(srow + sb * 8 + 4);
+            const float dxl[8] = {dxa.x, dxa.y, dxa.z, dxa.w, dxb.x, dxb.y, dxb.z, dxb.w};
+            const float sxl[8] = {sxa.x, sxa.y, sxa.z, sxa.w, sxb.x, sxb.y, sxb.z, sxb.w};
+            uint2 aq[4][4];
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) aq[gq][j] = ldg8(arow[j] + (size_t)sb * 144 + 32 * gq);
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) {
+                const uint2 (&a)[4] = aq[gq];
+#pragma unroll
+                for (int hi = 0; hi < 2; ++hi) {
+                    const int j8 = 2 * gq + hi;  // sub-block
+                    const int koff = (sb * 8 + j8) * 32;
+                    uint2 b[NT];
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) b[t] = ldg8(brow[t] + koff);
+                    float ws[2][2], wm[2][2];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int src = (j >> 1) * 16 + g + (j & 1) * 8;
+                        ws[j >> 1][j & 1] = __shfl_sync(0xffffffffu, dsc[j8], src);
+                        wm[j >> 1][j & 1] = __shfl_sync(0xffffffffu, dmn[j8], src);
+                    }
+                    uint32_t an[4][2];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        an[j][0] = (hi ? (a[j].x >> 4) : a[j].x) & 0x0F0F0F0Fu;
+                        an[j][1] = (hi ? (a[j].y >> 4) : a[j].y) & 0x0F0F0F0Fu;
+                    }
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        const float dx0 = __shfl_sync(0xffffffffu, dxl[j8], 8 * t + 2 * tg);
+                        const float dx1 = __shfl_sync(0xffffffffu, dxl[j8], 8 * t + 2 * tg + 1);
+                        const float sx0 = __shfl_sync(0xffffffffu, sxl[j8], 8 * t + 2 * tg);
+                        const float sx1 = __shfl_sync(0xffffffffu, sxl[j8], 8 * t + 2 * tg + 1);
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt) {
+                            int c[4];
+                            mma_s8(c, an[2 * mt][0], an[2 * mt + 1][0], an[2 * mt][1], an[2 * mt + 1][1], b[t].x, b[t].y);
+                            acc[mt][t][0] = fmaf(-wm[mt][0], sx0, fmaf((float)c[0], ws[mt][0] * dx0, acc[mt][t][0]));
+                            acc[mt][t][1] = fmaf(-wm[mt][0], sx1, fmaf((float)c[1], ws[mt][0] * dx1, acc[mt][t][1]));
+                            acc[mt][t][2] = fmaf(-wm[mt][1], sx0, fmaf((float)c[2], ws[mt][1] * dx0, acc[mt][t][2]));
+                            acc[mt][t][3] = fmaf(-wm[mt][1], sx1, fmaf((float)c[3], ws[mt][1] * dx1, acc[mt][t][3]));
+                        }
+                    }
+                }
+            }
+        }
+        reduce_and_store<NT>(red, acc, out, N, M, r0, t0);
+    }
+}
+
+}  // namespace
+
+bool smc_mma_supported(const smc_weight *w, int M)
+{
+    if (!w->fast || M < 2) return false;
+    if (w->dtype == SMC_Q8_0) return w->K % 128 == 0 && w->q8_qs != nullptr;
+    if (w->dtype == SMC_Q4_K) return w->K % 256 == 0 && w->d_raw != nullptr;
+    return false;
+}
+
+int smc_launch_gemv_mma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *out, cudaStream_t s)
+{
+    const int N = w->N, K = w->K, M = a->M;
+    const dim3 grid((N + MMA_ROWS - 1) / MMA_ROWS);
+    const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+    if (w->dtype == SMC_Q8_0) {
+        if (nt == 1) gemv_mma_q8_0_kernel<1><<<grid, 256, 0, s>>>(w->q8_qs, w->q8_d, a->q, a->d, out, N, K, M);
+        else if (nt == 2) gemv_mma_q8_0_kernel<2><<<grid, 256, 0, s>>>(w->q8_qs, w->q8_d, a->q, a->d, out, N, K, M);
+        else gemv_mma_q8_0_kernel<4><<<grid, 256, 0, s>>>(w->q8_qs, w->q8_d, a->q, a->d, out, N, K, M);
+    } else {
+        if (nt == 1) gemv_mma_q4_K_kernel<1><<<grid, 256, 0, s>>>(w->d_raw, a->q, a->d, a->sd, out, N, K, M);
+        else if (nt == 2) gemv_mma_q4_K_kernel<2><<<grid, 256, 0, s>>>(w->d_raw, a->q, a->d, a->sd, out, N, K, M);
+        else gemv_mma_q4_K_kernel<4><<<grid, 256, 0, s>>>(w->d_raw, a->q, a->d, a->sd, out, N, K, M);
+    }
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
