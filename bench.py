@@ -499,6 +499,29 @@ def run_ours(args):
                              "h2d_bytes_per_step": sum(4 * M * k for _, _, _, k in mats) * L,
                              "d2h_bytes_per_step": sum(4 * M * n for _, _, n, _ in mats) * L,
                              "api": "smc_qmatmul_host: one synchronous call per matmul, host fp32 in / out"}
+            # ---- prefill-sized batch on the tcgen05 tensor-core kernel (512 tokens, the Q4_K gate||up matrices)
+            try:
+                mp = 512
+                xp = torch.from_numpy(np.random.default_rng(5).standard_normal((mp, mats[0][3]), dtype=np.float32)).cuda()
+                op = torch.empty((mp, weights[0][0].N), device="cuda", dtype=torch.float32)
+                dev.qmatmul(xp, weights[0][0], ops.Mode.ACT_F32, out=op)  # first call sizes the scratch
+                torch.cuda.synchronize()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                for layer in range(L):
+                    dev.qmatmul(xp, weights[layer][0], ops.Mode.ACT_F32, out=op)
+                t1.record()
+                torch.cuda.synchronize()
+                msp = t0.elapsed_time(t1) / L
+                tf = 2.0 * mp * weights[0][0].N * mats[0][3] / msp / 1e9
+                tpeak = float(peaks.get("bf16_tflops", 1590.0))
+                result["prefill"] = {"kernel": "prefill_q4k_kernel (tcgen05.mma kind::f16, fp16 integer weights x fp16 hi/lo activations)",
+                                     "M": mp, "N": weights[0][0].N, "K": mats[0][3], "ms_per_matmul": msp, "useful_TFLOPs": tf,
+                                     "tensor_TFLOPs_issued": 2 * tf, "peak_TFLOPs": tpeak, "frac_useful": tf / tpeak,
+                                     "peak_source": "measured bf16 burst (MEASURED_PEAKS.json)" if "bf16_tflops" in peaks else "fallback"}
+                del xp, op
+            except Exception as exc:
+                result["prefill"] = {"error": str(exc)}
             # ---- the other half of the metric: decode tokens/s of the Qwen3-0.6B-shaped model (configs[3])
             try:
                 from sharpmind_b200 import synth

@@ -170,6 +170,7 @@ int smc_init(int device, smc_ctx **out)
     const char *impl = getenv("SMC_GEMV");
     ctx->use_tma = !(impl && strcmp(impl, "stream") == 0);
     ctx->use_mma = !(impl && strcmp(impl, "dp4a") == 0);
+    ctx->use_tc = !(impl && strcmp(impl, "notc") == 0);
     *out = ctx;
     return SMC_OK;
 }
@@ -355,6 +356,9 @@ static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, fl
     switch (mode) {
     case SMC_REF_ORDER: return smc_launch_gemv_ref(ctx, d_in, w, d_out, M, 0, w->N, s);
     case SMC_ACT_F32:
+        // prefill-sized batches of Q4_K run on the tcgen05 tensor cores (same parity bound, see smc_prefill.cu)
+        if (M >= 64 && ctx->use_tc && smc_prefill_supported(w, M) && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
+            return smc_launch_prefill_q4k(ctx, d_in, w, d_out, M, s);
         if (w->fast && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) return smc_launch_gemv_f32(ctx, d_in, w, d_out, M, s);
         // shapes the vector kernels do not take (ragged K, rows that start inside a block) run in the
         // reference's own order instead

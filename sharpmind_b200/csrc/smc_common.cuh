@@ -49,6 +49,7 @@ struct smc_ctx {
     int sm_count = 148;
     cudaStream_t stream = nullptr;  // used by the host-pointer entry points
     std::mutex mu;
+    std::mutex mu_scratch;  // guards the kernels' own scratch buffers (taken with or without `mu` held)
     std::string last_error;
     std::unordered_map<const void *, smc_weight *> by_host;
     // staging for host-pointer calls (grown on demand)
@@ -60,6 +61,7 @@ struct smc_ctx {
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
     bool use_mma = true;               // SMC_GEMV=dp4a in the environment keeps batches on the dp4a kernels
+    bool use_tc = true;                // SMC_GEMV=notc keeps prefill-sized batches off the tcgen05 kernel
     bool use_tma = true;               // SMC_GEMV=stream in the environment selects the register-prefetch kernels
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
     int argmax_rows = 0, argmax_chunks = 0;

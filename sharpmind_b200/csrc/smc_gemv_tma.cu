@@ -453,14 +453,14 @@ struct MathQ8_0 {
 // a stage is SS consecutive steps; when a row is shorter than a stage (spr <= SS) a group is SS/spr
 // rows = one stage, otherwise a group is one row = spr/SS stages.  Warp w of W takes groups
 // w, w + W, w + 2W, ...: at any moment the grid reads one dense window that slides through the matrix.
-template <class Math, int MT, int MINB, int SS>
+template <class Math, int MT, int MINB, int SS, bool GATHER>
 __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs xg, float *__restrict__ out, int N, int K,
                                                              int M, int slots, int *__restrict__ status,
                                                              const smc_gather_dev *gd)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     // row-split across GPUs (one row only): tell the peers that this rank's readers of the previous exchange are done
-    if (gd && blockIdx.x == 0 && threadIdx.x == 32) smc_gather_post_ready(gd);
+    if (GATHER && blockIdx.x == 0 && threadIdx.x == 32) smc_gather_post_ready(gd);
     int sending = -1;      // lane 0: whether packets go out, known after the first look at the peers' ready flags
     unsigned gtag = 0;     // number of the running exchange
     constexpr bool XS = (MT == 1);
@@ -534,7 +534,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
                     const float v = warp_sum32(acc[m]);
                     if (lane == 0 && m0 + m < M) {
                         out[(size_t)(m0 + m) * N + row] = v;
-                        if (XS && gd) {  // this rank's chunk starts at rank * N in every peer's buffer
+                        if (XS && GATHER) {  // this rank's chunk starts at rank * N in every peer's buffer
                             if (sending < 0) {
                                 gtag = smc_gather_tag(gd);
                                 sending = smc_gather_wait_ready(gd, gtag) ? 1 : 0;
@@ -560,7 +560,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
         }
     }
     // rows done: unpack this CTA's stripe of the peers' slices as they arrive
-    if (gd) {
+    if (GATHER) {
         smc_gather_collect(gd, (size_t)N, blockIdx.x, gridDim.x, smc_gather_tag(gd));
         smc_gather_done(gd, gridDim.x);
     }
@@ -588,8 +588,13 @@ template <class Math, int MT, int MINB, int SS>
 void launch_one(smc_ctx *ctx, dim3 grid, size_t smem, cudaStream_t s, const StepSrc &src, const XPtrs &x, float *out, int N,
                 int K, int M, int slots, const smc_gather_dev *gd)
 {
-    cudaFuncSetAttribute(gemv_tma_kernel<Math, MT, MINB, SS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gemv_tma_kernel<Math, MT, MINB, SS><<<grid, 256, smem, s>>>(src, x, out, N, K, M, slots, ctx->d_status, gd);
+    if (MT == 1 && gd) {
+        cudaFuncSetAttribute(gemv_tma_kernel<Math, MT, MINB, SS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        gemv_tma_kernel<Math, MT, MINB, SS, true><<<grid, 256, smem, s>>>(src, x, out, N, K, M, slots, ctx->d_status, gd);
+        return;
+    }
+    cudaFuncSetAttribute(gemv_tma_kernel<Math, MT, MINB, SS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gemv_tma_kernel<Math, MT, MINB, SS, false><<<grid, 256, smem, s>>>(src, x, out, N, K, M, slots, ctx->d_status, nullptr);
 }
 
 template <class Math>

@@ -448,7 +448,7 @@ int smc_launch_prefill_q4k(smc_ctx *ctx, const float *x, const smc_weight *w, fl
     const size_t scale_off = (img_halves + mimg_halves) * sizeof(__half);
     const size_t bytes = scale_off + (size_t)ntt * TN * sizeof(float);
     {
-        std::lock_guard<std::mutex> lock(ctx->mu);
+        std::lock_guard<std::mutex> lock(ctx->mu_scratch);
         int rc = ensure_scratch(ctx, bytes);
         if (rc) return rc;
     }
