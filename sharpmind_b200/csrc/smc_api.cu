@@ -171,6 +171,8 @@ int smc_init(int device, smc_ctx **out)
     ctx->use_tma = !(impl && strcmp(impl, "stream") == 0);
     ctx->use_mma = !(impl && strcmp(impl, "dp4a") == 0);
     ctx->use_tc = !(impl && strcmp(impl, "notc") == 0);
+    const char *pdl = getenv("SMC_PDL");
+    ctx->use_pdl = !(pdl && strcmp(pdl, "0") == 0);
     *out = ctx;
     return SMC_OK;
 }

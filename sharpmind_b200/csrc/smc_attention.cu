@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
     int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits)
 {
     constexpr int HD = DPL * LPK;
+    smc_grid_dep_sync();
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int grp = lane / LPK, sub = lane % LPK;        // 4 key groups per warp
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(256) sdpa_merge_kernel(const float *__restrict
     // grid.x = batch * heads
     __shared__ float sw[MERGE_MAX_SPLITS], sl[MERGE_MAX_SPLITS];
     __shared__ float red[8];
+    smc_grid_dep_sync();
     const float *rec = part + (size_t)blockIdx.x * splits * (hd + 2);
     float m = -INFINITY;
     for (int s = threadIdx.x; s < splits; s += blockDim.x) m = fmaxf(m, rec[(size_t)s * (hd + 2)]);
@@ -242,8 +244,8 @@ int launch_split_g(smc_ctx *ctx, int G, dim3 grid, size_t smem, cudaStream_t s, 
         if (smem > 48 * 1024)                                                                                      \
             cudaFuncSetAttribute(sdpa_decode_split_kernel<DPL, GV>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                  (int)smem);                                                                       \
-        sdpa_decode_split_kernel<DPL, GV><<<grid, SPLIT_THREADS, smem, s>>>(q, k, v, part, heads, kvHeads, kvLen,  \
-                                                                            maxSeq, scale, splits);                \
+        smc_launch_dep(ctx->use_pdl, sdpa_decode_split_kernel<DPL, GV>, grid, dim3(SPLIT_THREADS), smem, s, q, k, v, part, heads, \
+                       kvHeads, kvLen, maxSeq, scale, splits);                \
         break;
     switch (G) {
         SMC_SPLIT_CASE(1)
@@ -321,7 +323,8 @@ int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const 
         rc = launch_split_g<8>(ctx, G, grid, smem, s, d_q, d_k, d_v, ctx->d_attn_part, heads, kvHeads, kvLen, maxSeq,
                                scale, splits);
     if (rc) return rc;
-    sdpa_merge_kernel<<<batch * heads, headDim <= 128 ? 128 : 256, 0, s>>>(ctx->d_attn_part, d_out, headDim, splits);
+    smc_launch_dep(ctx->use_pdl, sdpa_merge_kernel, dim3(batch * heads), dim3(headDim <= 128 ? 128 : 256), 0, s,
+                   (const float *)ctx->d_attn_part, d_out, headDim, splits);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }

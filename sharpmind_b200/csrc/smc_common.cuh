@@ -60,6 +60,7 @@ struct smc_ctx {
     // scratch owned by the context
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
+    bool use_pdl = true;               // SMC_PDL=0 in the environment launches every kernel fully serialised
     bool use_mma = true;               // SMC_GEMV=dp4a in the environment keeps batches on the dp4a kernels
     bool use_tc = true;                // SMC_GEMV=notc keeps prefill-sized batches off the tcgen05 kernel
     bool use_tma = true;               // SMC_GEMV=stream in the environment selects the register-prefetch kernels
@@ -124,6 +125,35 @@ int smc_q8act_alloc(smc_ctx *, int max_rows, int max_k, smc_q8act **out);
 void smc_q8act_free(smc_q8act *);
 
 #ifdef __CUDACC__
+// ---------------------------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------------------------
+// Kernels of a decode step are a few microseconds each, so the gap between two dependent launches costs as much
+// as the kernels.  A kernel launched through smc_launch_dep may be scheduled while its predecessor in the stream
+// is still running; it must call smc_grid_dep_sync() before it touches anything the predecessor wrote or still
+// reads (everything but weights and its own shared memory).  The wait returns when the predecessor has completed
+// and its memory is visible; the trigger that follows lets the next kernel in the stream be scheduled in turn
+// (only once every CTA of this grid is resident or done, so a dependent can never starve its predecessor).
+// Launched the ordinary way, the same kernels run unchanged: both instructions are then no-ops.
+__device__ __forceinline__ void smc_grid_dep_sync()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <class... KArgs, class... Args>
+inline void smc_launch_dep(bool allow_overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                           Args... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = allow_overlap ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---------------------------------------------------------------------------------------------
 // device helpers
 // ---------------------------------------------------------------------------------------------

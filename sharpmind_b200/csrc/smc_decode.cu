@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(const float *__restrict__
                                                        int nh, int nkv, int pos, int maxSeq, float eps, int neox)
 {
     constexpr int HD = EPL * 32, PAIRS = HD / 2;
+    smc_grid_dep_sync();
     const int lane = threadIdx.x & 31;
     const int slots = nh + 2 * nkv;
     const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -140,9 +141,10 @@ int launch_qkv_post(smc_ctx *ctx, const smc_model *m, int l, float *kc, float *v
     const int warps = B * (d.n_heads + 2 * d.n_kv_heads);
     const dim3 grid((warps + 7) / 8);
     const float *qn = d.qk_norm ? m->qnorm[l] : nullptr, *kn = d.qk_norm ? m->knorm[l] : nullptr;
-#define SMC_QKV_POST(E)                                                                                                  \
-    qkv_post_kernel<E><<<grid, 256, 0, s>>>(m->qkv, m->q, kc, vc, qn, kn, m->cosT, m->sinT, B, d.n_heads, d.n_kv_heads, \
-                                            pos, d.max_seq, d.eps, d.neox)
+#define SMC_QKV_POST(E)                                                                                              \
+    smc_launch_dep(ctx->use_pdl, qkv_post_kernel<E>, grid, dim3(256), 0, s, (const float *)m->qkv, m->q, kc, vc, qn, kn, \
+                   (const float *)m->cosT, (const float *)m->sinT, B, d.n_heads, d.n_kv_heads, pos, d.max_seq, d.eps,    \
+                   d.neox)
     switch (d.head_dim) {
     case 64: SMC_QKV_POST(2); break;
     case 128: SMC_QKV_POST(4); break;

@@ -67,6 +67,7 @@ __device__ __forceinline__ float silu_ref(float g)
 __global__ void __launch_bounds__(256) rmsnorm_warp_kernel(const float *x, const float *__restrict__ w, float *out,
                                                            int rows, int n, float eps)
 {
+    smc_grid_dep_sync();
     const int lane = threadIdx.x & 31;
     int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -83,6 +84,7 @@ __global__ void __launch_bounds__(256) rmsnorm_cta_kernel(const float *x, const 
                                                           float eps, int vec)
 {
     __shared__ float red[32];
+    smc_grid_dep_sync();
     const float *p = x + (size_t)blockIdx.x * n;
     float *o = out + (size_t)blockIdx.x * n;
     float ss = 0.f;
@@ -120,6 +122,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
                                                           float *out, int n, float eps, int vec)
 {
     __shared__ float red[32];
+    smc_grid_dep_sync();
     float *p = x + (size_t)blockIdx.x * n;
     const float *q = y + (size_t)blockIdx.x * n;
     float *o = out + (size_t)blockIdx.x * n;
@@ -170,6 +173,7 @@ __global__ void rmsnorm_row_kernel(const float *__restrict__ src, const float *_
 __global__ void __launch_bounds__(256) swiglu_kernel(const float *__restrict__ gate, const float *__restrict__ up,
                                                      float *__restrict__ dst, int rows, int F, int ld, int vec)
 {
+    smc_grid_dep_sync();
     long long total = (long long)rows * F;
     long long stride = (long long)gridDim.x * blockDim.x;
     if (vec) {
@@ -298,6 +302,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
     __shared__ float sv[8];
     __shared__ int si[8];
     __shared__ int s_last;
+    smc_grid_dep_sync();
     const int row = blockIdx.y, c = blockIdx.x;
     const float *p = logits + (size_t)row * n;
     const int lo = c * ARGMAX_CHUNK, hi = min(n, lo + ARGMAX_CHUNK);
@@ -359,6 +364,7 @@ __global__ void __launch_bounds__(256) embed_q8_0_kernel(const int8_t *__restric
                                                          const uint8_t *__restrict__ raw, const int *__restrict__ tokens,
                                                          int K, int vocab, float *__restrict__ out)
 {
+    smc_grid_dep_sync();
     int tok = tokens[blockIdx.x];
     if (tok < 0 || tok >= vocab) {  // out-of-range ids produce NaN rows instead of reading outside the table
         for (int i = threadIdx.x; i < K; i += blockDim.x) out[(size_t)blockIdx.x * K + i] = __int_as_float(0x7fc00000);
@@ -402,9 +408,10 @@ int smc_rmsnorm_dev(smc_ctx *ctx, const float *d_x, const float *d_w, float *d_o
                      reinterpret_cast<uintptr_t>(d_w)) & 15) == 0;
     if (n <= 256) {
         // short rows (per-head QK norm): a warp per row
-        rmsnorm_warp_kernel<<<(rows + 7) / 8, 256, 0, s>>>(d_x, d_w, d_out, rows, n, eps);
+        smc_launch_dep(ctx->use_pdl, rmsnorm_warp_kernel, dim3((rows + 7) / 8), dim3(256), 0, s, d_x, d_w, d_out, rows, n, eps);
     } else {
-        rmsnorm_cta_kernel<<<rows, 256, 0, s>>>(d_x, d_w, d_out, n, eps, (aligned && (n & 3) == 0) ? 1 : 0);
+        smc_launch_dep(ctx->use_pdl, rmsnorm_cta_kernel, dim3(rows), dim3(256), 0, s, d_x, d_w, d_out, n, eps,
+                       (aligned && (n & 3) == 0) ? 1 : 0);
     }
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
@@ -424,8 +431,8 @@ int smc_add_rmsnorm_dev(smc_ctx *ctx, float *d_x, const float *d_y, const float 
     // the vector form needs what both separate kernels need: add_kernel vectorises on the whole tensor
     const bool aligned = ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_y) |
                            reinterpret_cast<uintptr_t>(d_out) | reinterpret_cast<uintptr_t>(d_w)) & 15) == 0;
-    add_rmsnorm_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(d_x, d_y, d_w, d_out, n, eps,
-                                                                            (aligned && (n & 3) == 0) ? 1 : 0);
+    smc_launch_dep(ctx->use_pdl, add_rmsnorm_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), d_x, d_y, d_w, d_out,
+                   n, eps, (aligned && (n & 3) == 0) ? 1 : 0);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
@@ -440,7 +447,8 @@ int smc_swiglu_dev(smc_ctx *ctx, const float *d_gate, const float *d_up, float *
                      reinterpret_cast<uintptr_t>(d_dst)) & 15) == 0;
     int vec = (aligned && ((F | ld) & 3) == 0) ? 1 : 0;
     long long total = (long long)rows * F;
-    swiglu_kernel<<<ew_grid(vec ? total / 4 : total, ctx->sm_count * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    smc_launch_dep(ctx->use_pdl, swiglu_kernel, dim3(ew_grid(vec ? total / 4 : total, ctx->sm_count * 8)), dim3(256), 0,
+                   static_cast<cudaStream_t>(stream), 
         d_gate, d_up, d_dst, rows, F, ld, vec);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
@@ -540,7 +548,8 @@ int smc_argmax_dev(smc_ctx *ctx, const float *d_logits, int rows, int n, int *d_
     float *pv = reinterpret_cast<float *>(ctx->d_argmax);
     int *pi = reinterpret_cast<int *>(pv + cap_cells);
     unsigned *tk = reinterpret_cast<unsigned *>(pi + cap_cells);
-    argmax_kernel<<<dim3(chunks, rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(d_logits, n, chunks, pv, pi, tk, d_out);
+    smc_launch_dep(ctx->use_pdl, argmax_kernel, dim3(chunks, rows), dim3(256), 0, static_cast<cudaStream_t>(stream), d_logits, n, chunks,
+                   pv, pi, tk, d_out);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
@@ -553,7 +562,7 @@ int smc_embed_q8_0_dev(smc_ctx *ctx, const smc_weight *table, const int *d_token
         return smc_fail(ctx, SMC_E_UNSUPPORTED, "embed: table must be Q8_0 with K %% 32 == 0");
     if (!table->q8_qs && !table->d_raw) return smc_fail(ctx, SMC_E_INVALID, "embed: table holds no data");
     if (count == 0) return SMC_OK;
-    embed_q8_0_kernel<<<count, 256, 0, static_cast<cudaStream_t>(stream)>>>(table->q8_qs, table->q8_d, table->d_raw,
+    smc_launch_dep(ctx->use_pdl, embed_q8_0_kernel, dim3(count), dim3(256), 0, static_cast<cudaStream_t>(stream), table->q8_qs, table->q8_d, table->d_raw,
                                                                             d_tokens, table->K, table->N, d_out);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;

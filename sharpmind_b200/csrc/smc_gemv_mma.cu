@@ -69,6 +69,7 @@ gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ w
                      const float *__restrict__ xd, float *__restrict__ out, int N, int K, int M)
 {
     __shared__ float red[MMA_WARPS][32][33];
+    smc_grid_dep_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
     const int r0 = blockIdx.x * MMA_ROWS;
     const int nb = K / 32, ngroups = nb / 4;
@@ -143,6 +144,7 @@ gemv_mma_q4_K_kernel(const uint8_t *__restrict__ raw, const int8_t *__restrict__
                      const float *__restrict__ xsd, float *__restrict__ out, int N, int K, int M)
 {
     __shared__ float red[MMA_WARPS][32][33];
+    smc_grid_dep_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
     const int r0 = blockIdx.x * MMA_ROWS;
     const int nb = K / 32, nsb = K / 256;
@@ -248,13 +250,19 @@ int smc_launch_gemv_mma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, f
     const dim3 grid((N + MMA_ROWS - 1) / MMA_ROWS);
     const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
     if (w->dtype == SMC_Q8_0) {
-        if (nt == 1) gemv_mma_q8_0_kernel<1><<<grid, 256, 0, s>>>(w->q8_qs, w->q8_d, a->q, a->d, out, N, K, M);
-        else if (nt == 2) gemv_mma_q8_0_kernel<2><<<grid, 256, 0, s>>>(w->q8_qs, w->q8_d, a->q, a->d, out, N, K, M);
-        else gemv_mma_q8_0_kernel<4><<<grid, 256, 0, s>>>(w->q8_qs, w->q8_d, a->q, a->d, out, N, K, M);
+        if (nt == 1) smc_launch_dep(ctx->use_pdl, gemv_mma_q8_0_kernel<1>, grid, dim3(256), 0, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
+                           (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
+        else if (nt == 2) smc_launch_dep(ctx->use_pdl, gemv_mma_q8_0_kernel<2>, grid, dim3(256), 0, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
+                           (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
+        else smc_launch_dep(ctx->use_pdl, gemv_mma_q8_0_kernel<4>, grid, dim3(256), 0, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
+                           (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
     } else {
-        if (nt == 1) gemv_mma_q4_K_kernel<1><<<grid, 256, 0, s>>>(w->d_raw, a->q, a->d, a->sd, out, N, K, M);
-        else if (nt == 2) gemv_mma_q4_K_kernel<2><<<grid, 256, 0, s>>>(w->d_raw, a->q, a->d, a->sd, out, N, K, M);
-        else gemv_mma_q4_K_kernel<4><<<grid, 256, 0, s>>>(w->d_raw, a->q, a->d, a->sd, out, N, K, M);
+        if (nt == 1) smc_launch_dep(ctx->use_pdl, gemv_mma_q4_K_kernel<1>, grid, dim3(256), 0, s, (const uint8_t *)w->d_raw, (const int8_t *)a->q,
+                           (const float *)a->d, (const float *)a->sd, out, N, K, M);
+        else if (nt == 2) smc_launch_dep(ctx->use_pdl, gemv_mma_q4_K_kernel<2>, grid, dim3(256), 0, s, (const uint8_t *)w->d_raw, (const int8_t *)a->q,
+                           (const float *)a->d, (const float *)a->sd, out, N, K, M);
+        else smc_launch_dep(ctx->use_pdl, gemv_mma_q4_K_kernel<4>, grid, dim3(256), 0, s, (const uint8_t *)w->d_raw, (const int8_t *)a->q,
+                           (const float *)a->d, (const float *)a->sd, out, N, K, M);
     }
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;

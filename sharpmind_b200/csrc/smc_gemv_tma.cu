@@ -459,8 +459,6 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
                                                              const smc_gather_dev *gd)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    // row-split across GPUs (one row only): tell the peers that this rank's readers of the previous exchange are done
-    if (GATHER && blockIdx.x == 0 && threadIdx.x == 32) smc_gather_post_ready(gd);
     int sending = -1;      // lane 0: whether packets go out, known after the first look at the peers' ready flags
     unsigned gtag = 0;     // number of the running exchange
     constexpr bool XS = (MT == 1);
@@ -503,6 +501,11 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
         const int pre = nstages < slots ? nstages : slots;
         for (int t = 0; t < pre; ++t) fetch_next(ring + (uint32_t)t * SLOT, bars + 8 * t);
     }
+    // The weight stages requested above do not depend on earlier launches; everything below does (activations,
+    // the output buffer, the exchange counters), so this is where a dependent launch waits for its predecessor.
+    smc_grid_dep_sync();
+    // row-split across GPUs (one row only): tell the peers that this rank's readers of the previous exchange are done
+    if (GATHER && blockIdx.x == 0 && threadIdx.x == 32) smc_gather_post_ready(gd);
     if (XS) {
         if (xg.xf) stage_x_quant<Math>(xg.xf, K, smem);
         else stage_x<Math>(xg, m0, K, smem);
@@ -590,11 +593,13 @@ void launch_one(smc_ctx *ctx, dim3 grid, size_t smem, cudaStream_t s, const Step
 {
     if (MT == 1 && gd) {
         cudaFuncSetAttribute(gemv_tma_kernel<Math, MT, MINB, SS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        gemv_tma_kernel<Math, MT, MINB, SS, true><<<grid, 256, smem, s>>>(src, x, out, N, K, M, slots, ctx->d_status, gd);
+        smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, MT, MINB, SS, true>, grid, dim3(256), smem, s, src, x, out, N, K, M, slots,
+                       ctx->d_status, gd);
         return;
     }
     cudaFuncSetAttribute(gemv_tma_kernel<Math, MT, MINB, SS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gemv_tma_kernel<Math, MT, MINB, SS, false><<<grid, 256, smem, s>>>(src, x, out, N, K, M, slots, ctx->d_status, nullptr);
+    smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, MT, MINB, SS, false>, grid, dim3(256), smem, s, src, x, out, N, K, M, slots,
+                   ctx->d_status, (const smc_gather_dev *)nullptr);
 }
 
 template <class Math>

@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(256) quantize_q8_kernel(const float *__restric
                                                           float *__restrict__ sd, int16_t *__restrict__ s16,
                                                           long long nblocks)
 {
+    smc_grid_dep_sync();
     const int lane = threadIdx.x & 31;
     long long blk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
@@ -273,8 +274,8 @@ int smc_launch_quantize_q8(smc_ctx *ctx, const float *x, int M, int K, smc_q8act
     a->M = M;
     a->K = K;
     long long nblocks = (long long)M * K / 32;
-    quantize_q8_kernel<<<grid_for(nblocks, 8, ctx->sm_count * 8), 256, 0, s>>>(x, a->q, a->d, a->dbits, a->sd, a->s16,
-                                                                               nblocks);
+    smc_launch_dep(ctx->use_pdl, quantize_q8_kernel, dim3(grid_for(nblocks, 8, ctx->sm_count * 8)), dim3(256), 0, s, x, a->q, a->d,
+                   a->dbits, a->sd, a->s16, nblocks);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
