@@ -5,25 +5,30 @@
 // (block b = k / 256 of row r, sub-block j = (k % 256) / 32; VecDotQ4K, QuantizationKernels.Q4.cs:586-747).
 // The integer part sc_j * q_k <= 63 * 15 is exact in fp16, so the tensor cores multiply exact weights:
 //   acc_d[r, t] = sum_{k in b} (sc_j q_k) * x~[t, k]        16 MMAs of K = 16 per block and activation half
-//   acc_m[r, t] = sum_{j < 8}  m_j * sx~[t, b, j]           one MMA of K = 16 per block
-//   out[t, r]  += s_t * (d_b * acc_d - dmin_b * acc_m)      CUDA cores, once per 256-element block
+//   acc_m[r, t] = sum_b sum_{j < 8} (dmin_b m_j) * sx~[t, b, j]   two MMAs of K = 16 per block, one accumulator
+//   out[t, r]   = s_t * (sum_b d_b * acc_d(b) - acc_m)      CUDA cores: one FMA per block, one subtraction at the end
 // x~ = x / s_t with s_t a power of two that brings the row's largest magnitude to about 2^10, carried as an
 // fp16 pair (hi, lo) so that hi + lo holds 22 significant bits of x~: the result stays inside the fp32 parity
-// bound of the fp32-activation mode.  sx~ is the fp32 sum of x~ over a 32-element sub-block, also as a pair.
+// bound of the fp32-activation mode.  sx~ is the fp32 sum of x~ over a 32-element sub-block and dmin_b m_j the
+// exact fp32 product (17 significant bits), both also carried as fp16 pairs.
 //
 // One CTA computes 128 weight rows x 128 tokens.  Warp roles:
 //   warp 0        lane 0 streams the activation tiles with bulk copies (global -> shared, mbarrier tx count)
 //   warp 1        lane 0 issues tcgen05.mma / tcgen05.commit
 //   warps 2..5    one thread per weight row: reads its 144-byte block, expands the nibbles to fp16 sc*q and
-//                 writes the A operand tile in the tensor cores' canonical K-major layout
-//   warps 6..13   drain: tcgen05.ld of the two accumulators, scaling by d / dmin, fp32 running sums in
-//                 registers (64 tokens per thread), final store
-// Shared memory: 4 stages of {A 16 KB, B_hi 16 KB, B_lo 16 KB} (64 k each) + 2 x {A'' 4 KB, B'' 4 KB} for the
-// min term.  TMEM: all 512 columns = 2 buffers x (acc_d 128 + acc_m 128), so the drain of one block overlaps
-// the MMAs of the next.  Every mbarrier wait is bounded; a wait that runs out raises the context's status
+//                 stores them with tcgen05.st into its own lane of tensor memory: the A operand never touches
+//                 shared memory (a first version that wrote A tiles to shared memory was bound by shared-memory
+//                 bandwidth: 64 KB of stores and 256 KB of MMA operand reads per block and CTA)
+//   warps 6..13   drain: tcgen05.ld of acc_d, scaling by d_b, fp32 running sums in registers (64 tokens per
+//                 thread), final store
+// Shared memory: 6 stages of {B_hi 16 KB, B_lo 16 KB} (64 k each) + 2 x {A'' 4 KB, B'' 8 KB} for the min term.
+// TMEM (512 columns): acc_d x 2 buffers (the drain of one block overlaps the MMAs of the next), acc_m, and four
+// A stages of 32 columns.  Every mbarrier wait is bounded; a wait that runs out raises the context's status
 // word and a CTA-wide abort flag that makes every later wait return at once, so the kernel still ends and
 // frees its TMEM.
 #include <cuda_fp16.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include "smc_common.cuh"
 
@@ -32,21 +37,34 @@ namespace {
 constexpr int TM = 128;    // weight rows per CTA (MMA M)
 constexpr int TN = 128;    // tokens per CTA (MMA N)
 constexpr int KS = 64;     // k per stage
-constexpr int NSLOT = 4;   // stages in flight = stages per 256-element block
-constexpr uint32_t A_BYTES = TM * KS * 2;
-constexpr uint32_t B_BYTES = TN * KS * 2;
-constexpr uint32_t SLOT_BYTES = A_BYTES + 2 * B_BYTES;
+constexpr int NA = 4;      // A stages in tensor memory = stages per 256-element block
+constexpr int NB = 6;      // B stages in shared memory
+constexpr uint32_t B_BYTES = TN * KS * 2;      // one of hi / lo
+constexpr uint32_t SLOT_BYTES = 2 * B_BYTES;
 constexpr uint32_t AM_BYTES = TM * 16 * 2;
-constexpr uint32_t BM_BYTES = TN * 16 * 2;
+constexpr uint32_t BM_BYTES = 2 * TN * 16 * 2;  // two tiles: [sx_hi | sx_hi] and [sx_lo | sx_lo]
 constexpr uint32_t AUX_BYTES = AM_BYTES + BM_BYTES;
-constexpr uint32_t OFF_AUX = NSLOT * SLOT_BYTES;
+constexpr uint32_t OFF_AUX = NB * SLOT_BYTES;
 constexpr uint32_t OFF_BAR = OFF_AUX + 2 * AUX_BYTES;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 256;
 constexpr int THREADS = 14 * 32;
 constexpr unsigned WAIT_LIMIT = 1u << 22;
+// tensor-memory columns
+constexpr uint32_t COL_ACC_D = 0;    // 2 x 128
+constexpr uint32_t COL_ACC_M = 256;  // 128
+constexpr uint32_t COL_A = 384;      // NA x 32
 
 // barrier slots (8 bytes each) inside the last 256 bytes
-enum { BAR_FULL_B = 0, BAR_FULL_A = 4, BAR_EMPTY = 8, BAR_ACC_FULL = 12, BAR_ACC_EMPTY = 14, BAR_COUNT = 16 };
+enum {
+    BAR_FULL_B = 0,
+    BAR_EMPTY_B = BAR_FULL_B + NB,
+    BAR_FULL_A = BAR_EMPTY_B + NB,
+    BAR_EMPTY_A = BAR_FULL_A + NA,
+    BAR_ACC_FULL = BAR_EMPTY_A + NA,
+    BAR_ACC_EMPTY = BAR_ACC_FULL + 2,
+    BAR_COUNT = BAR_ACC_EMPTY + 2
+};
+static_assert(BAR_COUNT * 8 + 8 <= 256, "barrier area");
 constexpr uint32_t OFF_TMEM_PTR = OFF_BAR + BAR_COUNT * 8;
 constexpr uint32_t OFF_ABORT = OFF_TMEM_PTR + 4;
 
@@ -90,6 +108,25 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     atomicExch(status, 3);
 }
+// One lane polls, the warp follows: 128 or 256 threads polling (and arriving on) one barrier word made the
+// handshakes themselves the slowest part of the pipeline.
+__device__ __forceinline__ void warp_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, int *status)
+{
+    if ((threadIdx.x & 31) == 0) mbar_wait(bar, parity, abort_flag, status);
+    __syncwarp();
+}
+__device__ __forceinline__ void warp_arrive(uint32_t bar)
+{
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+// timing experiments (SMC_PREFILL_DEBUG bit 4096): clocks a role of CTA 0 spends waiting
+#define SMC_TIMED(acc, call)                        \
+    do {                                            \
+        const long long t_ = clock64();             \
+        call;                                       \
+        acc += clock64() - t_;                      \
+    } while (0)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -107,6 +144,27 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint
         : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same with the A operand taken from tensor memory (128 lanes x 8 columns of packed fp16 pairs).
+__device__ __forceinline__ void tc_mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane, written from registers.
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t *r)
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // 16 consecutive fp32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, float *v)
 {
@@ -135,8 +193,8 @@ constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)
 // ------------------------------------------------------------------------------ activation image
 // Global layout read by the GEMM kernel with plain bulk copies (already in the shared-memory order):
 //   img  [token tile][stage = k / 64][hi | lo][token / 8][k chunk = (k % 64) / 8][token % 8][k % 8]   fp16
-//   mimg [token tile][block = k / 256][token / 8][2][token % 8][8]                                    fp16
-//        (second index 0: sx~ hi of sub-blocks 0..7, 1: sx~ lo)
+//   mimg [token tile][block = k / 256][hi | lo][token / 8][2][token % 8][8]                          fp16
+//        (tile hi: sx~ hi of sub-blocks 0..7, twice; tile lo: sx~ lo, twice)
 //   scale[token]  fp32 power of two
 __global__ void __launch_bounds__(256) prefill_scale_kernel(const float *__restrict__ x, int M, int K, float *__restrict__ scale)
 {
@@ -202,9 +260,11 @@ __global__ void __launch_bounds__(256) prefill_image_kernel(const float *__restr
             const int j = c >> 2;
             const __half sh = __float2half_rn(sum);
             const __half sl = __float2half_rn(sum - __half2float(sh));
-            const size_t mb = (size_t)(tt * nsb + sb) * (TN * 16) + (size_t)(tl >> 3) * 128 + (size_t)(tl & 7) * 8 + j;
+            const size_t mb = (size_t)(tt * nsb + sb) * (2 * TN * 16) + (size_t)(tl >> 3) * 128 + (size_t)(tl & 7) * 8 + j;
             mimg[mb] = sh;
-            mimg[mb + 64] = sl;
+            mimg[mb + 64] = sh;
+            mimg[mb + TN * 16] = sl;
+            mimg[mb + TN * 16 + 64] = sl;
         }
     }
 }
@@ -233,27 +293,30 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 // ------------------------------------------------------------------------------ the GEMM
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ img, const __half *__restrict__ mimg,
-                   const float *__restrict__ scale, float *__restrict__ out, int N, int K, int M, int ntt, int *status)
+                   const float *__restrict__ scale, float *__restrict__ out, int N, int K, int M, int ntt, int *status, int dbg)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rt = blockIdx.x / ntt, tt = blockIdx.x % ntt;
     const int row0 = rt * TM;
-    const int nsb = K / 256;
-    const size_t row_bytes = (size_t)nsb * 144;
+    const size_t row_bytes = (size_t)(K / 256) * 144;
+    const int nsb = (dbg & 1024) ? 1 : ((dbg & 2048) ? 8 : K / 256);
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + OFF_ABORT);
     auto bar = [&](int i) { return sbase + OFF_BAR + 8u * (uint32_t)i; };
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NSLOT; ++i) {
+        for (int i = 0; i < NB; ++i) {
             mbar_init(bar(BAR_FULL_B + i), 1);
-            mbar_init(bar(BAR_FULL_A + i), TM);
-            mbar_init(bar(BAR_EMPTY + i), 1);
+            mbar_init(bar(BAR_EMPTY_B + i), 1);
+        }
+        for (int i = 0; i < NA; ++i) {
+            mbar_init(bar(BAR_FULL_A + i), 4);   // one arrival per expansion warp
+            mbar_init(bar(BAR_EMPTY_A + i), 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar(BAR_ACC_FULL + i), 1);
-            mbar_init(bar(BAR_ACC_EMPTY + i), 256);
+            mbar_init(bar(BAR_ACC_EMPTY + i), 8);  // one arrival per drain warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -270,87 +333,139 @@ prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ i
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem + OFF_TMEM_PTR);
 
     if (warp == 0) {
-        // ---------------- activation tiles: one bulk copy of hi|lo per stage (+ the min-term tile per block)
+        // ---------------- activation tiles: one bulk copy of hi|lo per stage (+ the min-term tiles per block)
         if (lane == 0) {
+            long long w0 = 0;
+            const long long tstart = clock64();
             const __half *src = img + (size_t)tt * (K / KS) * 2 * (TN * KS);
-            const __half *msrc = mimg + (size_t)tt * nsb * (TN * 16);
-            for (int sb = 0; sb < nsb; ++sb) {
-                for (int g = 0; g < NSLOT; ++g) {
-                    mbar_wait(bar(BAR_EMPTY + g), (uint32_t)((sb & 1) ^ 1), abort_flag, status);
-                    const uint32_t fb = bar(BAR_FULL_B + g);
-                    mbar_expect_tx(fb, 2 * B_BYTES + (g == 0 ? BM_BYTES : 0u));
-                    bulk_g2s(sbase + (uint32_t)g * SLOT_BYTES + A_BYTES, src + (size_t)(sb * NSLOT + g) * 2 * (TN * KS),
-                             2 * B_BYTES, fb);
-                    if (g == 0)
-                        bulk_g2s(sbase + OFF_AUX + (uint32_t)(sb & 1) * AUX_BYTES + AM_BYTES, msrc + (size_t)sb * (TN * 16),
-                                 BM_BYTES, fb);
+            const __half *msrc = mimg + (size_t)tt * nsb * (2 * TN * 16);
+            for (int t = 0; t < nsb * NA; ++t) {
+                const int sb = t / NA, g = t % NA, slot = t % NB;
+                SMC_TIMED(w0, mbar_wait(bar(BAR_EMPTY_B + slot), (uint32_t)(((t / NB) & 1) ^ 1), abort_flag, status));
+                const uint32_t fb = bar(BAR_FULL_B + slot);
+                if (dbg & 1) {
+                    mbar_arrive(fb);
+                    continue;
                 }
+                mbar_expect_tx(fb, 2 * B_BYTES + (g == 0 ? BM_BYTES : 0u));
+                bulk_g2s(sbase + (uint32_t)slot * SLOT_BYTES, src + (size_t)t * 2 * (TN * KS), 2 * B_BYTES, fb);
+                // the aux buffer sb & 1 was last read by the MMAs of block sb - 2, which completed before the
+                // MMAs whose commit released this B slot were even issued
+                if (g == 0)
+                    bulk_g2s(sbase + OFF_AUX + (uint32_t)(sb & 1) * AUX_BYTES + AM_BYTES, msrc + (size_t)sb * (2 * TN * 16),
+                             BM_BYTES, fb);
             }
+            if ((dbg & 4096) && blockIdx.x == 0) printf("producer: total %lld wait_emptyB %lld\n", clock64() - tstart, w0);
         }
     } else if (warp == 1) {
-        // ---------------- MMA issue
+        // ---------------- MMA issue.  One thread feeds the tensor cores: an MMA of this shape lasts 64 clocks, so
+        // the instructions between two MMAs must stay well below that.  Descriptors are therefore built once and
+        // advanced by adding the 16-byte-unit offset to their low word.
         if (lane == 0) {
+            const uint32_t acc_m = tmem_base + COL_ACC_M;
+            const uint64_t b_desc0 = smem_desc(sbase, 128, 1024);            // stage 0, hi tile, k step 0
+            const uint64_t aux_desc0 = smem_desc(sbase + OFF_AUX, 128, 256);  // aux buffer 0, A''
+            constexpr uint64_t U_SLOT = SLOT_BYTES >> 4, U_LO = B_BYTES >> 4, U_KK = 256 >> 4;
+            constexpr uint64_t U_AUX = AUX_BYTES >> 4, U_BM = AM_BYTES >> 4, U_BM2 = (AM_BYTES + TN * 16 * 2) >> 4;
+            int slot = 0;
+            uint32_t b_phase = 0;
+            long long w0 = 0, w1 = 0, w2 = 0;
+            const long long tstart = clock64();
             for (int sb = 0; sb < nsb; ++sb) {
                 const int buf = sb & 1;
-                mbar_wait(bar(BAR_ACC_EMPTY + buf), (uint32_t)(((sb >> 1) & 1) ^ 1), abort_flag, status);
+                SMC_TIMED(w0, mbar_wait(bar(BAR_ACC_EMPTY + buf), (uint32_t)(((sb >> 1) & 1) ^ 1), abort_flag, status));
                 tc_fence_after();
-                const uint32_t acc_d = tmem_base + (uint32_t)buf * 256u, acc_m = acc_d + 128u;
-                for (int g = 0; g < NSLOT; ++g) {
-                    mbar_wait(bar(BAR_FULL_B + g), (uint32_t)(sb & 1), abort_flag, status);
-                    mbar_wait(bar(BAR_FULL_A + g), (uint32_t)(sb & 1), abort_flag, status);
-                    tc_fence_after();
-                    const uint32_t a0 = sbase + (uint32_t)g * SLOT_BYTES, bh = a0 + A_BYTES, bl = bh + B_BYTES;
+                const uint32_t acc_d = tmem_base + COL_ACC_D + (uint32_t)buf * 128u;
+#pragma unroll
+                for (int g = 0; g < NA; ++g) {
+                    SMC_TIMED(w1, mbar_wait(bar(BAR_FULL_B + slot), b_phase, abort_flag, status));
+                    SMC_TIMED(w2, mbar_wait(bar(BAR_FULL_A + g), (uint32_t)(sb & 1), abort_flag, status));
+                    if (!(dbg & 256)) tc_fence_after();
+                    const uint64_t bh = b_desc0 + (uint64_t)slot * U_SLOT;
+                    const uint32_t a0 = tmem_base + COL_A + (uint32_t)g * 32u;
                     if (g == 0) {
-                        const uint32_t aux = sbase + OFF_AUX + (uint32_t)buf * AUX_BYTES;
-                        tc_mma_f16(acc_m, smem_desc(aux, 128, 256), smem_desc(aux + AM_BYTES, 128, 256), IDESC, 0u);
+                        const uint64_t am = aux_desc0 + (uint64_t)buf * U_AUX;
+                        tc_mma_f16(acc_m, am, am + U_BM, IDESC, sb != 0 ? 1u : 0u);
+                        tc_mma_f16(acc_m, am, am + U_BM2, IDESC, 1u);
                     }
+                    if (!(dbg & 8)) {
 #pragma unroll
-                    for (int kk = 0; kk < KS / 16; ++kk)
-                        tc_mma_f16(acc_d, smem_desc(a0 + kk * 256, 128, 1024), smem_desc(bh + kk * 256, 128, 1024), IDESC,
-                                   (g | kk) != 0 ? 1u : 0u);
+                        for (int kk = 0; kk < KS / 16; ++kk)
+                            tc_mma_f16_ta(acc_d, a0 + kk * 8, bh + kk * U_KK, IDESC, (g | kk) != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < KS / 16; ++kk)
-                        tc_mma_f16(acc_d, smem_desc(a0 + kk * 256, 128, 1024), smem_desc(bl + kk * 256, 128, 1024), IDESC, 1u);
-                    tc_commit(bar(BAR_EMPTY + g));  // arrives when the MMAs above have read the stage
+                        for (int kk = 0; kk < KS / 16; ++kk) tc_mma_f16_ta(acc_d, a0 + kk * 8, bh + U_LO + kk * U_KK, IDESC, 1u);
+                    }
+                    // both arrive when the MMAs above have read their operands
+                    if (dbg & 64) {
+                        mbar_arrive(bar(BAR_EMPTY_B + slot));
+                        mbar_arrive(bar(BAR_EMPTY_A + g));
+                    } else {
+                        tc_commit(bar(BAR_EMPTY_B + slot));
+                        tc_commit(bar(BAR_EMPTY_A + g));
+                    }
+                    if (++slot == NB) slot = 0, b_phase ^= 1;
                 }
-                tc_commit(bar(BAR_ACC_FULL + buf));
+                if (dbg & 64) mbar_arrive(bar(BAR_ACC_FULL + buf));
+                else tc_commit(bar(BAR_ACC_FULL + buf));
             }
+            if ((dbg & 4096) && blockIdx.x == 0)
+                printf("mma: total %lld wait_accempty %lld wait_fullB %lld wait_fullA %lld\n", clock64() - tstart, w0, w1, w2);
         }
     } else if (warp < 6) {
-        // ---------------- weight expansion: thread r owns weight row row0 + r
-        const int r = threadIdx.x - 64;
+        // ---------------- weight expansion: a warp may only touch the TMEM lanes of its quarter (warp % 4)
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
         const uint8_t *rowp = raw + (size_t)(row0 + r) * row_bytes;
-        const uint32_t a_row = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 16u;
         const uint32_t am_row = (uint32_t)(r >> 3) * 256u + (uint32_t)(r & 7) * 16u;
+        const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + COL_A;
         uint4 nx[9];
 #pragma unroll
         for (int i = 0; i < 9; ++i) nx[i] = smc_ldg_stream16(rowp + 16 * i);
+        long long w0 = 0, w_top = 0, w_aux = 0, w_exp = 0, w_st = 0;
+        const long long tstart = clock64();
         for (int sb = 0; sb < nsb; ++sb) {
+            const long long ttop = clock64();
             uint4 cur[9];
 #pragma unroll
             for (int i = 0; i < 9; ++i) cur[i] = nx[i];
-            if (sb + 1 < nsb) {
+            if (sb + 1 < nsb && !(dbg & 16)) {
 #pragma unroll
                 for (int i = 0; i < 9; ++i) nx[i] = smc_ldg_stream16(rowp + (size_t)(sb + 1) * 144 + 16 * i);
             }
             const uint32_t s0 = cur[0].y, s1 = cur[0].z, s2 = cur[0].w;  // the 12 packed scale / min bytes
+            const float dmin = smc_h2f((uint16_t)(cur[0].x >> 16));
+            w_top += clock64() - ttop + (long long)(s0 & 0u);
 #pragma unroll
-            for (int g = 0; g < NSLOT; ++g) {
-                mbar_wait(bar(BAR_EMPTY + g), (uint32_t)((sb & 1) ^ 1), abort_flag, status);
-                if (g == 0) {
-                    // A'' of the min term: m_0..m_7 in columns 0..7 and again in 8..15
-                    uint32_t mh[4];
+            for (int g = 0; g < NA; ++g) {
+                SMC_TIMED(w0, warp_wait(bar(BAR_EMPTY_A + g), (uint32_t)((sb & 1) ^ 1), abort_flag, status));
+                if (!(dbg & 256)) tc_fence_after();
+                const long long taux = clock64();
+                if (g == 0 && !(dbg & 128)) {
+                    // A'' of the min term: dmin * m_j as fp16 pairs, hi in columns 0..7, lo in 8..15
+                    uint32_t mh[4], ml[4];
 #pragma unroll
                     for (int j = 0; j < 8; j += 2) {
                         int sc, ma, mb;
                         smc_k4_scale_min(s0, s1, s2, j, sc, ma);
                         smc_k4_scale_min(s0, s1, s2, j + 1, sc, mb);
-                        const __half2 hm = __halves2half2(__int2half_rn(ma), __int2half_rn(mb));
-                        mh[j >> 1] = *reinterpret_cast<const uint32_t *>(&hm);
+                        const float pa = dmin * (float)ma, pb = dmin * (float)mb;
+                        const __half ha = __float2half_rn(pa), hb = __float2half_rn(pb);
+                        const __half2 hh = __halves2half2(ha, hb);
+                        const __half2 ll = __halves2half2(__float2half_rn(pa - __half2float(ha)), __float2half_rn(pb - __half2float(hb)));
+                        mh[j >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                        ml[j >> 1] = *reinterpret_cast<const uint32_t *>(&ll);
                     }
                     const uint32_t am = sbase + OFF_AUX + (uint32_t)(sb & 1) * AUX_BYTES + am_row;
                     sts128(am, mh[0], mh[1], mh[2], mh[3]);
-                    sts128(am + 128u, mh[0], mh[1], mh[2], mh[3]);
+                    sts128(am + 128u, ml[0], ml[1], ml[2], ml[3]);
+                    fence_proxy_async();  // the tensor cores read this tile through the async proxy
+                }
+                w_aux += clock64() - taux;
+                const long long texp = clock64();
+                if (dbg & 2) {
+                    if (!(dbg & 256)) tc_fence_before();
+                    warp_arrive(bar(BAR_FULL_A + g));
+                    continue;
                 }
                 int sca, scb, mn;
                 smc_k4_scale_min(s0, s1, s2, 2 * g, sca, mn);      // low nibbles: sub-block 2g
@@ -361,52 +476,72 @@ prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ i
                 const __half2 off_hi = __half2half2(__int2half_rn(-64 * scb));
                 const uint32_t wq[8] = {cur[1 + 2 * g].x, cur[1 + 2 * g].y, cur[1 + 2 * g].z, cur[1 + 2 * g].w,
                                         cur[2 + 2 * g].x, cur[2 + 2 * g].y, cur[2 + 2 * g].z, cur[2 + 2 * g].w};
-                const uint32_t a_dst = sbase + (uint32_t)g * SLOT_BYTES + a_row;
+                // column c of the stage holds k = 2c, 2c + 1: columns 0..15 sub-block 2g, 16..31 sub-block 2g + 1
+                uint32_t lo[16], hi[16];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {  // bytes 8c .. 8c+7 -> k chunk c (low nibbles) and c + 4 (high nibbles)
-                    uint32_t lo[4], hi[4];
-                    expand_pair(wq[2 * c], 0x4140u, sc_lo, off_lo, sc_hi, off_hi, lo[0], hi[0]);
-                    expand_pair(wq[2 * c], 0x4342u, sc_lo, off_lo, sc_hi, off_hi, lo[1], hi[1]);
-                    expand_pair(wq[2 * c + 1], 0x4140u, sc_lo, off_lo, sc_hi, off_hi, lo[2], hi[2]);
-                    expand_pair(wq[2 * c + 1], 0x4342u, sc_lo, off_lo, sc_hi, off_hi, lo[3], hi[3]);
-                    sts128(a_dst + (uint32_t)c * 128u, lo[0], lo[1], lo[2], lo[3]);
-                    sts128(a_dst + (uint32_t)(c + 4) * 128u, hi[0], hi[1], hi[2], hi[3]);
+                for (int c = 0; c < 4; ++c) {  // bytes 8c .. 8c+7
+                    expand_pair(wq[2 * c], 0x4140u, sc_lo, off_lo, sc_hi, off_hi, lo[4 * c + 0], hi[4 * c + 0]);
+                    expand_pair(wq[2 * c], 0x4342u, sc_lo, off_lo, sc_hi, off_hi, lo[4 * c + 1], hi[4 * c + 1]);
+                    expand_pair(wq[2 * c + 1], 0x4140u, sc_lo, off_lo, sc_hi, off_hi, lo[4 * c + 2], hi[4 * c + 2]);
+                    expand_pair(wq[2 * c + 1], 0x4342u, sc_lo, off_lo, sc_hi, off_hi, lo[4 * c + 3], hi[4 * c + 3]);
                 }
-                fence_proxy_async();  // the tensor cores read this tile through the async proxy
-                mbar_arrive(bar(BAR_FULL_A + g));
+                const long long tst = clock64() + (long long)(lo[0] & 0u) + (long long)(hi[15] & 0u);
+                w_exp += tst - texp;
+                tc_st16(a_lane + (uint32_t)g * 32u, lo);
+                tc_st16(a_lane + (uint32_t)g * 32u + 16u, hi);
+                tc_wait_st();
+                tc_fence_before();
+                warp_arrive(bar(BAR_FULL_A + g));
+                w_st += clock64() - tst;
             }
         }
+        if ((dbg & 4096) && blockIdx.x == 0 && threadIdx.x == 64) printf("expand: total %lld wait_emptyA %lld top %lld aux %lld expand %lld store %lld\n", clock64() - tstart, w0, w_top, w_aux, w_exp, w_st);
     } else {
         // ---------------- drain: thread = (TMEM lane = weight row, 64 of the 128 token columns)
         const int quarter = warp & 3, half = (warp - 6) >> 2;
         const int rl = quarter * 32 + lane;
         const uint8_t *rowp = raw + (size_t)(row0 + rl) * row_bytes;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)half * 64u;
         float acc[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        long long w0 = 0;
+        const long long tstart = clock64();
         for (int sb = 0; sb < nsb; ++sb) {
             const int buf = sb & 1;
-            const uint32_t hdr = smc_ldg_stream4(rowp + (size_t)sb * 144);
-            const float d = smc_h2f((uint16_t)(hdr & 0xFFFFu)), ndmin = -smc_h2f((uint16_t)(hdr >> 16));
-            mbar_wait(bar(BAR_ACC_FULL + buf), (uint32_t)((sb >> 1) & 1), abort_flag, status);
-            tc_fence_after();
-            const uint32_t td = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * 256u + (uint32_t)half * 64u;
+            const float d = (dbg & (32 | 512)) ? 1.0f : smc_h2f(smc_ldg_stream2(rowp + (size_t)sb * 144));
+            SMC_TIMED(w0, warp_wait(bar(BAR_ACC_FULL + buf), (uint32_t)((sb >> 1) & 1), abort_flag, status));
+            if (!(dbg & 256)) tc_fence_after();
+            const uint32_t td = lane_base + COL_ACC_D + (uint32_t)buf * 128u;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float vd[16], vm[16];
-                tc_ld16(td + (uint32_t)c * 16u, vd);
-                tc_ld16(td + 128u + (uint32_t)c * 16u, vm);
+            for (int c = 0; c < ((dbg & 4) ? 0 : 4); c += 2) {
+                float va[16], vb[16];
+                tc_ld16(td + (uint32_t)c * 16u, va);
+                tc_ld16(td + (uint32_t)(c + 1) * 16u, vb);
                 tc_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(ndmin, vm[i], fmaf(d, vd[i], acc[c * 16 + i]));
+                for (int i = 0; i < 16; ++i) {
+                    acc[c * 16 + i] = fmaf(d, va[i], acc[c * 16 + i]);
+                    acc[(c + 1) * 16 + i] = fmaf(d, vb[i], acc[(c + 1) * 16 + i]);
+                }
             }
-            tc_fence_before();
-            mbar_arrive(bar(BAR_ACC_EMPTY + buf));
+            if (!(dbg & 256)) tc_fence_before();
+            warp_arrive(bar(BAR_ACC_EMPTY + buf));
         }
+        if ((dbg & 4096) && blockIdx.x == 0 && threadIdx.x == 192) printf("drain: total %lld wait_accfull %lld\n", clock64() - tstart, w0);
+        // the commit that completed the last block also covers every min-term MMA
         const int t0 = tt * TN + half * 64;
 #pragma unroll
-        for (int j = 0; j < 64; ++j)
-            if (t0 + j < M) out[(size_t)(t0 + j) * N + row0 + rl] = acc[j] * scale[t0 + j];
+        for (int c = 0; c < 4; ++c) {
+            float vm[16];
+            tc_ld16(lane_base + COL_ACC_M + (uint32_t)c * 16u, vm);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int t = t0 + c * 16 + i;
+                if (t < M) out[(size_t)t * N + row0 + rl] = (acc[c * 16 + i] - vm[i]) * scale[t];
+            }
+        }
     }
 
     tc_fence_before();
@@ -444,7 +579,7 @@ int smc_launch_prefill_q4k(smc_ctx *ctx, const float *x, const smc_weight *w, fl
     if (!smc_prefill_supported(w, M)) return smc_fail(ctx, SMC_E_UNSUPPORTED, "tensor-core matmul needs Q4_K, N %% 128 == 0, K %% 256 == 0");
     if (reinterpret_cast<uintptr_t>(x) & 15) return smc_fail(ctx, SMC_E_INVALID, "tensor-core matmul needs 16-byte aligned activations");
     const int N = w->N, K = w->K, ntt = (M + TN - 1) / TN, nsb = K / 256;
-    const size_t img_halves = (size_t)ntt * TN * K * 2, mimg_halves = (size_t)ntt * nsb * TN * 16;
+    const size_t img_halves = (size_t)ntt * TN * K * 2, mimg_halves = (size_t)ntt * nsb * 2 * TN * 16;
     const size_t scale_off = (img_halves + mimg_halves) * sizeof(__half);
     const size_t bytes = scale_off + (size_t)ntt * TN * sizeof(float);
     {
@@ -462,7 +597,8 @@ int smc_launch_prefill_q4k(smc_ctx *ctx, const float *x, const smc_weight *w, fl
         SMC_CUDA(ctx, cudaFuncSetAttribute(prefill_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
         attr_set = true;
     }
-    prefill_q4k_kernel<<<(N / TM) * ntt, THREADS, SMEM_BYTES, s>>>(w->d_raw, img, mimg, scale, out, N, K, M, ntt, ctx->d_status);
+    static const int dbg = getenv("SMC_PREFILL_DEBUG") ? atoi(getenv("SMC_PREFILL_DEBUG")) : 0;  // timing experiments only
+    prefill_q4k_kernel<<<(N / TM) * ntt, THREADS, SMEM_BYTES, s>>>(w->d_raw, img, mimg, scale, out, N, K, M, ntt, ctx->d_status, dbg);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
