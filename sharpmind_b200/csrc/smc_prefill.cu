@@ -38,17 +38,23 @@ constexpr int TM = 128;    // weight rows per CTA (MMA M)
 constexpr int TN = 128;    // tokens per CTA (MMA N)
 constexpr int KS = 64;     // k per stage
 constexpr int NA = 4;      // A stages in tensor memory = stages per 256-element block
-constexpr int NB = 6;      // B stages in shared memory
+constexpr int NB = 4;      // B stages in shared memory
+constexpr int NW = 4;      // blocks of raw weight bytes in shared memory
 constexpr uint32_t B_BYTES = TN * KS * 2;      // one of hi / lo
 constexpr uint32_t SLOT_BYTES = 2 * B_BYTES;
+constexpr uint32_t W_BYTES = TM * 144;          // one 256-element block of every row of the tile
 constexpr uint32_t AM_BYTES = TM * 16 * 2;
 constexpr uint32_t BM_BYTES = 2 * TN * 16 * 2;  // two tiles: [sx_hi | sx_hi] and [sx_lo | sx_lo]
 constexpr uint32_t AUX_BYTES = AM_BYTES + BM_BYTES;
-constexpr uint32_t OFF_AUX = NB * SLOT_BYTES;
+constexpr uint32_t OFF_W = NB * SLOT_BYTES;
+constexpr uint32_t OFF_AUX = OFF_W + NW * W_BYTES;
 constexpr uint32_t OFF_BAR = OFF_AUX + 2 * AUX_BYTES;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 256;
-constexpr int THREADS = 14 * 32;
+constexpr int EXPAND_WARPS = 8, DRAIN_WARPS = 8;
+constexpr int WARP_EXPAND0 = 2, WARP_DRAIN0 = WARP_EXPAND0 + EXPAND_WARPS;
+constexpr int THREADS = (WARP_DRAIN0 + DRAIN_WARPS) * 32;
 constexpr unsigned WAIT_LIMIT = 1u << 22;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 // tensor-memory columns
 constexpr uint32_t COL_ACC_D = 0;    // 2 x 128
 constexpr uint32_t COL_ACC_M = 256;  // 128
@@ -60,7 +66,9 @@ enum {
     BAR_EMPTY_B = BAR_FULL_B + NB,
     BAR_FULL_A = BAR_EMPTY_B + NB,
     BAR_EMPTY_A = BAR_FULL_A + NA,
-    BAR_ACC_FULL = BAR_EMPTY_A + NA,
+    BAR_FULL_W = BAR_EMPTY_A + NA,
+    BAR_EMPTY_W = BAR_FULL_W + NW,
+    BAR_ACC_FULL = BAR_EMPTY_W + NW,
     BAR_ACC_EMPTY = BAR_ACC_FULL + 2,
     BAR_COUNT = BAR_ACC_EMPTY + 2
 };
@@ -120,13 +128,6 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar)
     __syncwarp();
     if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
 }
-// timing experiments (SMC_PREFILL_DEBUG bit 4096): clocks a role of CTA 0 spends waiting
-#define SMC_TIMED(acc, call)                        \
-    do {                                            \
-        const long long t_ = clock64();             \
-        call;                                       \
-        acc += clock64() - t_;                      \
-    } while (0)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -270,20 +271,18 @@ __global__ void __launch_bounds__(256) prefill_image_kernel(const float *__restr
 }
 
 // ------------------------------------------------------------------------------ nibble expansion
-// Bytes b0 b1 of `w` (selected by `sel`) -> {sc * low nibble(b0), sc * low nibble(b1)} and the same for the
-// high nibbles, as fp16 pairs.  0x6400 | q is the fp16 number 1024 + q; one fused multiply-add with
-// (sc, -1024 sc) gives sc * q with a single rounding of an exactly representable result.  The high nibble
-// sits four bits up (1024 + 16 q), so its multiplier is sc / 16 and its offset -64 sc, both exact.
-__device__ __forceinline__ void expand_pair(uint32_t w, uint32_t sel, __half2 sc_lo, __half2 off_lo, __half2 sc_hi16,
-                                            __half2 off_hi, uint32_t &lo, uint32_t &hi)
+__device__ __forceinline__ uint4 lds128(uint32_t a)
 {
-    const uint32_t p = __byte_perm(w, 0u, sel);  // bytes {bA, 0, bB, 0}
-    const uint32_t l = (p & 0x000F000Fu) | 0x64006400u;
-    const uint32_t h = (p & 0x00F000F0u) | 0x64006400u;
-    const __half2 rl = __hfma2(*reinterpret_cast<const __half2 *>(&l), sc_lo, off_lo);
-    const __half2 rh = __hfma2(*reinterpret_cast<const __half2 *>(&h), sc_hi16, off_hi);
-    lo = *reinterpret_cast<const uint32_t *>(&rl);
-    hi = *reinterpret_cast<const uint32_t *>(&rh);
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+// One nibble plane of bytes bA bB of `w`: {mul * (1024 + nibble << shift) + off} as an fp16 pair.
+__device__ __forceinline__ uint32_t expand_half(uint32_t w, uint32_t sel, uint32_t mask, __half2 mul, __half2 off)
+{
+    const uint32_t p = (__byte_perm(w, 0u, sel) & mask) | 0x64006400u;
+    const __half2 r = __hfma2(*reinterpret_cast<const __half2 *>(&p), mul, off);
+    return *reinterpret_cast<const uint32_t *>(&r);
 }
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
@@ -293,15 +292,15 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 // ------------------------------------------------------------------------------ the GEMM
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ img, const __half *__restrict__ mimg,
-                   const float *__restrict__ scale, float *__restrict__ out, int N, int K, int M, int ntt, int *status, int dbg)
+                   const float *__restrict__ scale, float *__restrict__ out, int N, int K, int M, int ntt, int *status)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rt = blockIdx.x / ntt, tt = blockIdx.x % ntt;
     const int row0 = rt * TM;
-    const size_t row_bytes = (size_t)(K / 256) * 144;
-    const int nsb = (dbg & 1024) ? 1 : ((dbg & 2048) ? 8 : K / 256);
+    const int nsb = K / 256;
+    const size_t row_bytes = (size_t)nsb * 144;
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + OFF_ABORT);
     auto bar = [&](int i) { return sbase + OFF_BAR + 8u * (uint32_t)i; };
 
@@ -311,12 +310,16 @@ prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ i
             mbar_init(bar(BAR_EMPTY_B + i), 1);
         }
         for (int i = 0; i < NA; ++i) {
-            mbar_init(bar(BAR_FULL_A + i), 4);   // one arrival per expansion warp
+            mbar_init(bar(BAR_FULL_A + i), EXPAND_WARPS);  // one arrival per expansion warp
             mbar_init(bar(BAR_EMPTY_A + i), 1);
+        }
+        for (int i = 0; i < NW; ++i) {
+            mbar_init(bar(BAR_FULL_W + i), 1);             // the expect_tx arrival; the 128 row copies add bytes
+            mbar_init(bar(BAR_EMPTY_W + i), EXPAND_WARPS);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar(BAR_ACC_FULL + i), 1);
-            mbar_init(bar(BAR_ACC_EMPTY + i), 8);  // one arrival per drain warp
+            mbar_init(bar(BAR_ACC_EMPTY + i), DRAIN_WARPS);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -335,27 +338,25 @@ prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ i
     if (warp == 0) {
         // ---------------- activation tiles: one bulk copy of hi|lo per stage (+ the min-term tiles per block)
         if (lane == 0) {
-            long long w0 = 0;
-            const long long tstart = clock64();
             const __half *src = img + (size_t)tt * (K / KS) * 2 * (TN * KS);
             const __half *msrc = mimg + (size_t)tt * nsb * (2 * TN * 16);
-            for (int t = 0; t < nsb * NA; ++t) {
-                const int sb = t / NA, g = t % NA, slot = t % NB;
-                SMC_TIMED(w0, mbar_wait(bar(BAR_EMPTY_B + slot), (uint32_t)(((t / NB) & 1) ^ 1), abort_flag, status));
-                const uint32_t fb = bar(BAR_FULL_B + slot);
-                if (dbg & 1) {
-                    mbar_arrive(fb);
-                    continue;
+            int slot = 0;
+            uint32_t phase = 1;  // a fresh barrier passes a wait on the phase before its first
+            for (int sb = 0; sb < nsb; ++sb) {
+#pragma unroll
+                for (int g = 0; g < NA; ++g) {
+                    mbar_wait(bar(BAR_EMPTY_B + slot), phase, abort_flag, status);
+                    const uint32_t fb = bar(BAR_FULL_B + slot);
+                    mbar_expect_tx(fb, 2 * B_BYTES + (g == 0 ? BM_BYTES : 0u));
+                    bulk_g2s(sbase + (uint32_t)slot * SLOT_BYTES, src + (size_t)(sb * NA + g) * 2 * (TN * KS), 2 * B_BYTES, fb);
+                    // the aux buffer sb & 1 was last read by the MMAs of block sb - 2, which completed before the
+                    // MMAs whose commit released this B slot (a stage of block sb - 1) were even issued
+                    if (g == 0)
+                        bulk_g2s(sbase + OFF_AUX + (uint32_t)(sb & 1) * AUX_BYTES + AM_BYTES, msrc + (size_t)sb * (2 * TN * 16),
+                                 BM_BYTES, fb);
+                    if (++slot == NB) slot = 0, phase ^= 1;
                 }
-                mbar_expect_tx(fb, 2 * B_BYTES + (g == 0 ? BM_BYTES : 0u));
-                bulk_g2s(sbase + (uint32_t)slot * SLOT_BYTES, src + (size_t)t * 2 * (TN * KS), 2 * B_BYTES, fb);
-                // the aux buffer sb & 1 was last read by the MMAs of block sb - 2, which completed before the
-                // MMAs whose commit released this B slot were even issued
-                if (g == 0)
-                    bulk_g2s(sbase + OFF_AUX + (uint32_t)(sb & 1) * AUX_BYTES + AM_BYTES, msrc + (size_t)sb * (2 * TN * 16),
-                             BM_BYTES, fb);
             }
-            if ((dbg & 4096) && blockIdx.x == 0) printf("producer: total %lld wait_emptyB %lld\n", clock64() - tstart, w0);
         }
     } else if (warp == 1) {
         // ---------------- MMA issue.  One thread feeds the tensor cores: an MMA of this shape lasts 64 clocks, so
@@ -369,18 +370,16 @@ prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ i
             constexpr uint64_t U_AUX = AUX_BYTES >> 4, U_BM = AM_BYTES >> 4, U_BM2 = (AM_BYTES + TN * 16 * 2) >> 4;
             int slot = 0;
             uint32_t b_phase = 0;
-            long long w0 = 0, w1 = 0, w2 = 0;
-            const long long tstart = clock64();
             for (int sb = 0; sb < nsb; ++sb) {
                 const int buf = sb & 1;
-                SMC_TIMED(w0, mbar_wait(bar(BAR_ACC_EMPTY + buf), (uint32_t)(((sb >> 1) & 1) ^ 1), abort_flag, status));
+                mbar_wait(bar(BAR_ACC_EMPTY + buf), (uint32_t)(((sb >> 1) & 1) ^ 1), abort_flag, status);
                 tc_fence_after();
                 const uint32_t acc_d = tmem_base + COL_ACC_D + (uint32_t)buf * 128u;
 #pragma unroll
                 for (int g = 0; g < NA; ++g) {
-                    SMC_TIMED(w1, mbar_wait(bar(BAR_FULL_B + slot), b_phase, abort_flag, status));
-                    SMC_TIMED(w2, mbar_wait(bar(BAR_FULL_A + g), (uint32_t)(sb & 1), abort_flag, status));
-                    if (!(dbg & 256)) tc_fence_after();
+                    mbar_wait(bar(BAR_FULL_B + slot), b_phase, abort_flag, status);
+                    mbar_wait(bar(BAR_FULL_A + g), (uint32_t)(sb & 1), abort_flag, status);
+                    tc_fence_after();
                     const uint64_t bh = b_desc0 + (uint64_t)slot * U_SLOT;
                     const uint32_t a0 = tmem_base + COL_A + (uint32_t)g * 32u;
                     if (g == 0) {
@@ -388,60 +387,57 @@ prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ i
                         tc_mma_f16(acc_m, am, am + U_BM, IDESC, sb != 0 ? 1u : 0u);
                         tc_mma_f16(acc_m, am, am + U_BM2, IDESC, 1u);
                     }
-                    if (!(dbg & 8)) {
 #pragma unroll
-                        for (int kk = 0; kk < KS / 16; ++kk)
-                            tc_mma_f16_ta(acc_d, a0 + kk * 8, bh + kk * U_KK, IDESC, (g | kk) != 0 ? 1u : 0u);
+                    for (int kk = 0; kk < KS / 16; ++kk)
+                        tc_mma_f16_ta(acc_d, a0 + kk * 8, bh + kk * U_KK, IDESC, (g | kk) != 0 ? 1u : 0u);
 #pragma unroll
-                        for (int kk = 0; kk < KS / 16; ++kk) tc_mma_f16_ta(acc_d, a0 + kk * 8, bh + U_LO + kk * U_KK, IDESC, 1u);
-                    }
+                    for (int kk = 0; kk < KS / 16; ++kk) tc_mma_f16_ta(acc_d, a0 + kk * 8, bh + U_LO + kk * U_KK, IDESC, 1u);
                     // both arrive when the MMAs above have read their operands
-                    if (dbg & 64) {
-                        mbar_arrive(bar(BAR_EMPTY_B + slot));
-                        mbar_arrive(bar(BAR_EMPTY_A + g));
-                    } else {
-                        tc_commit(bar(BAR_EMPTY_B + slot));
-                        tc_commit(bar(BAR_EMPTY_A + g));
-                    }
+                    tc_commit(bar(BAR_EMPTY_B + slot));
+                    tc_commit(bar(BAR_EMPTY_A + g));
                     if (++slot == NB) slot = 0, b_phase ^= 1;
                 }
-                if (dbg & 64) mbar_arrive(bar(BAR_ACC_FULL + buf));
-                else tc_commit(bar(BAR_ACC_FULL + buf));
+                tc_commit(bar(BAR_ACC_FULL + buf));
             }
-            if ((dbg & 4096) && blockIdx.x == 0)
-                printf("mma: total %lld wait_accempty %lld wait_fullB %lld wait_fullA %lld\n", clock64() - tstart, w0, w1, w2);
         }
-    } else if (warp < 6) {
-        // ---------------- weight expansion: a warp may only touch the TMEM lanes of its quarter (warp % 4)
-        const int quarter = warp & 3;
+    } else if (warp < WARP_DRAIN0) {
+        // ---------------- weight expansion.  A warp may only touch the TMEM lanes of its quarter (warp % 4); the
+        // two warps of a quarter split a stage: plane 0 expands the low nibbles (sub-block 2g, columns 0..15),
+        // plane 1 the high nibbles (sub-block 2g + 1, columns 16..31).  The raw 144-byte blocks arrive through a
+        // ring of bulk copies, one copy per row and block, issued NW - 1 blocks ahead by the plane-0 thread of
+        // the row: register prefetch of one block was not enough to cover the latency of these scattered reads.
+        const int quarter = warp & 3, plane = (warp - WARP_EXPAND0) >> 2;
         const int r = quarter * 32 + lane;
         const uint8_t *rowp = raw + (size_t)(row0 + r) * row_bytes;
         const uint32_t am_row = (uint32_t)(r >> 3) * 256u + (uint32_t)(r & 7) * 16u;
-        const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + COL_A;
-        uint4 nx[9];
-#pragma unroll
-        for (int i = 0; i < 9; ++i) nx[i] = smc_ldg_stream16(rowp + 16 * i);
-        long long w0 = 0, w_top = 0, w_aux = 0, w_exp = 0, w_st = 0;
-        const long long tstart = clock64();
+        const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + COL_A + (uint32_t)plane * 16u;
+        const uint32_t w_row = sbase + OFF_W + (uint32_t)r * 144u;
+        auto fetch_block = [&](int p) {  // plane-0 threads: request block p of this thread's row
+            const int ws = p % NW;
+            warp_wait(bar(BAR_EMPTY_W + ws), (uint32_t)(((p / NW) & 1) ^ 1), abort_flag, status);
+            const uint32_t fw = bar(BAR_FULL_W + ws);
+            if (warp == WARP_EXPAND0 && lane == 0) mbar_expect_tx(fw, W_BYTES);
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four plane-0 warps: bytes are expected before any copy lands
+            bulk_g2s(w_row + (uint32_t)ws * W_BYTES, rowp + (size_t)p * 144, 144u, fw);
+        };
+        if (plane == 0)
+            for (int p = 0; p < NW - 1 && p < nsb; ++p) fetch_block(p);
         for (int sb = 0; sb < nsb; ++sb) {
-            const long long ttop = clock64();
+            const int ws = sb % NW;
+            if (plane == 0 && sb + NW - 1 < nsb) fetch_block(sb + NW - 1);
+            warp_wait(bar(BAR_FULL_W + ws), (uint32_t)((sb / NW) & 1), abort_flag, status);
             uint4 cur[9];
 #pragma unroll
-            for (int i = 0; i < 9; ++i) cur[i] = nx[i];
-            if (sb + 1 < nsb && !(dbg & 16)) {
-#pragma unroll
-                for (int i = 0; i < 9; ++i) nx[i] = smc_ldg_stream16(rowp + (size_t)(sb + 1) * 144 + 16 * i);
-            }
+            for (int i = 0; i < 9; ++i) cur[i] = lds128(w_row + (uint32_t)ws * W_BYTES + 16u * i);
+            warp_arrive(bar(BAR_EMPTY_W + ws));  // the bytes are in registers: the slot may be refilled
             const uint32_t s0 = cur[0].y, s1 = cur[0].z, s2 = cur[0].w;  // the 12 packed scale / min bytes
-            const float dmin = smc_h2f((uint16_t)(cur[0].x >> 16));
-            w_top += clock64() - ttop + (long long)(s0 & 0u);
 #pragma unroll
             for (int g = 0; g < NA; ++g) {
-                SMC_TIMED(w0, warp_wait(bar(BAR_EMPTY_A + g), (uint32_t)((sb & 1) ^ 1), abort_flag, status));
-                if (!(dbg & 256)) tc_fence_after();
-                const long long taux = clock64();
-                if (g == 0 && !(dbg & 128)) {
+                warp_wait(bar(BAR_EMPTY_A + g), (uint32_t)((sb & 1) ^ 1), abort_flag, status);
+                tc_fence_after();
+                if (g == 0 && plane == 1) {
                     // A'' of the min term: dmin * m_j as fp16 pairs, hi in columns 0..7, lo in 8..15
+                    const float dmin = smc_h2f((uint16_t)(cur[0].x >> 16));
                     uint32_t mh[4], ml[4];
 #pragma unroll
                     for (int j = 0; j < 8; j += 2) {
@@ -460,75 +456,53 @@ prefill_q4k_kernel(const uint8_t *__restrict__ raw, const __half *__restrict__ i
                     sts128(am + 128u, ml[0], ml[1], ml[2], ml[3]);
                     fence_proxy_async();  // the tensor cores read this tile through the async proxy
                 }
-                w_aux += clock64() - taux;
-                const long long texp = clock64();
-                if (dbg & 2) {
-                    if (!(dbg & 256)) tc_fence_before();
-                    warp_arrive(bar(BAR_FULL_A + g));
-                    continue;
-                }
-                int sca, scb, mn;
-                smc_k4_scale_min(s0, s1, s2, 2 * g, sca, mn);      // low nibbles: sub-block 2g
-                smc_k4_scale_min(s0, s1, s2, 2 * g + 1, scb, mn);  // high nibbles: sub-block 2g + 1
-                const __half2 sc_lo = __half2half2(__int2half_rn(sca));
-                const __half2 off_lo = __half2half2(__int2half_rn(-1024 * sca));
-                const __half2 sc_hi = __half2half2(__float2half_rn((float)scb * 0.0625f));
-                const __half2 off_hi = __half2half2(__int2half_rn(-64 * scb));
+                int sc, mn;
+                smc_k4_scale_min(s0, s1, s2, 2 * g + plane, sc, mn);
+                // low nibble: (1024 + q) * sc - 1024 sc; high nibble: (1024 + 16 q) * sc / 16 - 64 sc; both exact
+                const __half2 mul = plane ? __half2half2(__float2half_rn((float)sc * 0.0625f)) : __half2half2(__int2half_rn(sc));
+                const __half2 off = __half2half2(__int2half_rn((plane ? -64 : -1024) * sc));
+                const uint32_t mask = plane ? 0x00F000F0u : 0x000F000Fu;
                 const uint32_t wq[8] = {cur[1 + 2 * g].x, cur[1 + 2 * g].y, cur[1 + 2 * g].z, cur[1 + 2 * g].w,
                                         cur[2 + 2 * g].x, cur[2 + 2 * g].y, cur[2 + 2 * g].z, cur[2 + 2 * g].w};
-                // column c of the stage holds k = 2c, 2c + 1: columns 0..15 sub-block 2g, 16..31 sub-block 2g + 1
-                uint32_t lo[16], hi[16];
+                // column c of the plane holds elements 2c, 2c + 1 of the sub-block = bytes 2c, 2c + 1 of the group
+                uint32_t col[16];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {  // bytes 8c .. 8c+7
-                    expand_pair(wq[2 * c], 0x4140u, sc_lo, off_lo, sc_hi, off_hi, lo[4 * c + 0], hi[4 * c + 0]);
-                    expand_pair(wq[2 * c], 0x4342u, sc_lo, off_lo, sc_hi, off_hi, lo[4 * c + 1], hi[4 * c + 1]);
-                    expand_pair(wq[2 * c + 1], 0x4140u, sc_lo, off_lo, sc_hi, off_hi, lo[4 * c + 2], hi[4 * c + 2]);
-                    expand_pair(wq[2 * c + 1], 0x4342u, sc_lo, off_lo, sc_hi, off_hi, lo[4 * c + 3], hi[4 * c + 3]);
+                for (int c = 0; c < 8; ++c) {
+                    col[2 * c] = expand_half(wq[c], 0x4140u, mask, mul, off);
+                    col[2 * c + 1] = expand_half(wq[c], 0x4342u, mask, mul, off);
                 }
-                const long long tst = clock64() + (long long)(lo[0] & 0u) + (long long)(hi[15] & 0u);
-                w_exp += tst - texp;
-                tc_st16(a_lane + (uint32_t)g * 32u, lo);
-                tc_st16(a_lane + (uint32_t)g * 32u + 16u, hi);
+                tc_st16(a_lane + (uint32_t)g * 32u, col);
                 tc_wait_st();
                 tc_fence_before();
                 warp_arrive(bar(BAR_FULL_A + g));
-                w_st += clock64() - tst;
             }
         }
-        if ((dbg & 4096) && blockIdx.x == 0 && threadIdx.x == 64) printf("expand: total %lld wait_emptyA %lld top %lld aux %lld expand %lld store %lld\n", clock64() - tstart, w0, w_top, w_aux, w_exp, w_st);
     } else {
         // ---------------- drain: thread = (TMEM lane = weight row, 64 of the 128 token columns)
-        const int quarter = warp & 3, half = (warp - 6) >> 2;
+        const int quarter = warp & 3, half = (warp - WARP_DRAIN0) >> 2;
         const int rl = quarter * 32 + lane;
         const uint8_t *rowp = raw + (size_t)(row0 + rl) * row_bytes;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)half * 64u;
         float acc[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-        long long w0 = 0;
-        const long long tstart = clock64();
         for (int sb = 0; sb < nsb; ++sb) {
             const int buf = sb & 1;
-            const float d = (dbg & (32 | 512)) ? 1.0f : smc_h2f(smc_ldg_stream2(rowp + (size_t)sb * 144));
-            SMC_TIMED(w0, warp_wait(bar(BAR_ACC_FULL + buf), (uint32_t)((sb >> 1) & 1), abort_flag, status));
-            if (!(dbg & 256)) tc_fence_after();
+            const float d = smc_h2f(smc_ldg_stream2(rowp + (size_t)sb * 144));
+            warp_wait(bar(BAR_ACC_FULL + buf), (uint32_t)((sb >> 1) & 1), abort_flag, status);
+            tc_fence_after();
             const uint32_t td = lane_base + COL_ACC_D + (uint32_t)buf * 128u;
 #pragma unroll
-            for (int c = 0; c < ((dbg & 4) ? 0 : 4); c += 2) {
-                float va[16], vb[16];
+            for (int c = 0; c < 4; ++c) {
+                float va[16];
                 tc_ld16(td + (uint32_t)c * 16u, va);
-                tc_ld16(td + (uint32_t)(c + 1) * 16u, vb);
                 tc_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    acc[c * 16 + i] = fmaf(d, va[i], acc[c * 16 + i]);
-                    acc[(c + 1) * 16 + i] = fmaf(d, vb[i], acc[(c + 1) * 16 + i]);
-                }
+                for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(d, va[i], acc[c * 16 + i]);
             }
-            if (!(dbg & 256)) tc_fence_before();
+            tc_fence_before();
             warp_arrive(bar(BAR_ACC_EMPTY + buf));
         }
-        if ((dbg & 4096) && blockIdx.x == 0 && threadIdx.x == 192) printf("drain: total %lld wait_accfull %lld\n", clock64() - tstart, w0);
         // the commit that completed the last block also covers every min-term MMA
         const int t0 = tt * TN + half * 64;
 #pragma unroll
@@ -597,8 +571,7 @@ int smc_launch_prefill_q4k(smc_ctx *ctx, const float *x, const smc_weight *w, fl
         SMC_CUDA(ctx, cudaFuncSetAttribute(prefill_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
         attr_set = true;
     }
-    static const int dbg = getenv("SMC_PREFILL_DEBUG") ? atoi(getenv("SMC_PREFILL_DEBUG")) : 0;  // timing experiments only
-    prefill_q4k_kernel<<<(N / TM) * ntt, THREADS, SMEM_BYTES, s>>>(w->d_raw, img, mimg, scale, out, N, K, M, ntt, ctx->d_status, dbg);
+    prefill_q4k_kernel<<<(N / TM) * ntt, THREADS, SMEM_BYTES, s>>>(w->d_raw, img, mimg, scale, out, N, K, M, ntt, ctx->d_status);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
