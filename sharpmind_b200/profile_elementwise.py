@@ -95,9 +95,9 @@ def main():
             graph.replay()
         e1.record()
         torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (a.reps * ncopies)
-        print(json.dumps({"op": name.replace("64x", f"{R}x"), "us_per_launch": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 3),
-                          "GBps": round(nbytes / us / 1e3, 1), "copies": ncopies}), flush=True)
+        usec = e0.elapsed_time(e1) * 1e3 / (a.reps * ncopies)
+        print(json.dumps({"op": name.replace("64x", f"{R}x"), "us_per_launch": round(usec, 2), "algorithmic_MB": round(nbytes / 1e6, 3),
+                          "GBps": round(nbytes / usec / 1e3, 1), "copies": ncopies}), flush=True)
     ctx.close()
 
 
