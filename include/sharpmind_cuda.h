@@ -243,6 +243,19 @@ SMC_API int smc_model_kv_load(smc_ctx *ctx, smc_model *m, const float *d_k, cons
 SMC_API int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, int pos, int mode,
                             float *d_logits, int *d_argmax, void *stream);
 
+/* One activation row whose elementwise producer rides in the matmul's staging (SMC_ACT_Q8 arithmetic, weights that
+ * the one-row bulk-copy kernel takes: registered with SMC_W_REPACK, K % 1024 == 0 for Q8_0 / K % 2048 == 0 for the
+ * K-quants, K <= 8192; SMC_E_UNSUPPORTED otherwise):
+ *   smc_qmatmul_swiglu_dev   out = (SiLU(gate) * up) W^T      FfnKernels.Gated (FfnKernels.cs:35-59): activation, then down
+ *   smc_qmatmul_addnorm_dev  out = (RMSNorm(x + add) * w) W^T  UnhookedTransformerBlock.Forward (UnhookedTransformerBlock.cs:12-47):
+ *                            residual add, norm, projection; x + add is written to d_sum when that is not null, d_add may
+ *                            be null (plain norm).  The sum of squares is taken in another order than smc_rmsnorm_dev's, so
+ *                            the two agree to rounding, not bit for bit. */
+SMC_API int smc_qmatmul_swiglu_dev(smc_ctx *ctx, const float *d_gate, const float *d_up, const smc_weight *w, float *d_out,
+                                   void *stream);
+SMC_API int smc_qmatmul_addnorm_dev(smc_ctx *ctx, const float *d_x, const float *d_add, const float *d_norm_w, float eps,
+                                    float *d_sum, const smc_weight *w, float *d_out, void *stream);
+
 /* A new weight whose rows are the rows of parts[0], parts[1], ... in order (same dtype and K, all registered
  * with SMC_W_REPACK): how the decoder turns Wq / Wk / Wv into one matmul.  The parts stay valid. */
 SMC_API int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts, int count, smc_weight **out);

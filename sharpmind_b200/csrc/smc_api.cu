@@ -229,7 +229,11 @@ int smc_weight_register(smc_ctx *ctx, const void *host_raw, size_t bytes, int dt
     smc_weight *w = new smc_weight();
     w->dtype = dtype, w->N = N, w->K = K, w->flags = flags, w->raw_bytes = bytes, w->host_key = host_raw;
     cudaError_t e = cudaMalloc(&w->d_raw, bytes);
-    if (e == cudaSuccess) e = cudaMemcpy(w->d_raw, host_raw, bytes, cudaMemcpyHostToDevice);
+    // The copy is ordered on the context's stream, where the repack kernels run: a plain cudaMemcpy from pageable
+    // memory returns once the bytes are staged, with the transfer itself still in flight on the legacy stream, and
+    // the context's stream does not synchronise with that one.
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w->d_raw, host_raw, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
         free_weight(w);
         return smc_fail(ctx, SMC_E_CUDA, "weight upload failed: %s", cudaGetErrorString(e));
@@ -259,7 +263,11 @@ int smc_weight_register_dev(smc_ctx *ctx, const void *d_raw, size_t bytes, int d
     smc_weight *w = new smc_weight();
     w->dtype = dtype, w->N = N, w->K = K, w->flags = flags, w->raw_bytes = bytes, w->host_key = nullptr;
     cudaError_t e = cudaMalloc(&w->d_raw, bytes);
-    if (e == cudaSuccess) e = cudaMemcpy(w->d_raw, d_raw, bytes, cudaMemcpyDeviceToDevice);
+    // whatever produced the bytes (on any stream) has to be finished, and the copy has to be ordered before the
+    // repack kernels on the context's stream
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w->d_raw, d_raw, bytes, cudaMemcpyDeviceToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
         free_weight(w);
         return smc_fail(ctx, SMC_E_CUDA, "weight copy failed: %s", cudaGetErrorString(e));
@@ -423,6 +431,36 @@ int smc_qmatmul_dev_gather(smc_ctx *ctx, const float *d_in, const smc_weight *w,
 }
 
 extern "C" {
+
+static int one_row_fusable(smc_ctx *ctx, const smc_weight *w, const char *what)
+{
+    if (!w->fast || w->K > 8192 || !ctx->use_tma || !smc_tma_supported(w, 1))
+        return smc_fail(ctx, SMC_E_UNSUPPORTED, "%s: the weight is not one the one-row bulk-copy kernel takes (K = %d)", what, w->K);
+    return SMC_OK;
+}
+
+int smc_qmatmul_swiglu_dev(smc_ctx *ctx, const float *d_gate, const float *d_up, const smc_weight *w, float *d_out, void *stream)
+{
+    if (!ctx || !d_gate || !d_up || !w || !d_out) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_swiglu: bad arguments");
+    if ((reinterpret_cast<uintptr_t>(d_gate) | reinterpret_cast<uintptr_t>(d_up)) & 15)
+        return smc_fail(ctx, SMC_E_INVALID, "qmatmul_swiglu: gate and up must be 16-byte aligned");
+    int rc = one_row_fusable(ctx, w, "qmatmul_swiglu");
+    if (rc) return rc;
+    return smc_launch_gemv_tma_swiglu(ctx, d_gate, d_up, w, d_out, static_cast<cudaStream_t>(stream));
+}
+
+int smc_qmatmul_addnorm_dev(smc_ctx *ctx, const float *d_x, const float *d_add, const float *d_norm_w, float eps, float *d_sum,
+                            const smc_weight *w, float *d_out, void *stream)
+{
+    if (!ctx || !d_x || !d_norm_w || !w || !d_out) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_addnorm: bad arguments");
+    if ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_add) | reinterpret_cast<uintptr_t>(d_norm_w) |
+         reinterpret_cast<uintptr_t>(d_sum)) & 15)
+        return smc_fail(ctx, SMC_E_INVALID, "qmatmul_addnorm: operands must be 16-byte aligned");
+    int rc = one_row_fusable(ctx, w, "qmatmul_addnorm");
+    if (rc) return rc;
+    smc_norm_prologue pro{d_add, d_norm_w, d_sum, eps};
+    return smc_launch_gemv_tma_addnorm(ctx, d_x, &pro, w, d_out, static_cast<cudaStream_t>(stream));
+}
 
 int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts, int count, smc_weight **out)
 {

@@ -1,11 +1,12 @@
 // fp32 attention over an fp32 KV cache.
 //
-//  * sdpa_decode_split_kernel + sdpa_merge_kernel: one query token per sequence (decode).  The cache
+//  * sdpa_decode_split_kernel: one query token per sequence (decode).  The cache
 //    sweep is the only traffic that matters (2 * kvLen * headDim * 4 bytes per KV head), so the
 //    key range is split across CTAs to fill the GPU at batch 1, the query heads that share a KV
 //    head are processed together (K and V are read once per group), and eight lanes share a key so
 //    that every load is a coalesced 128-bit access.  Each eight-lane group keeps its own online-
-//    softmax state; states are merged in shared memory per CTA and across CTAs by the merge kernel.
+//    softmax state; states are merged in shared memory per CTA, and the CTA that finishes a (sequence, KV head)
+//    last merges the CTAs' records in split order.
 //  * sdpa_tile_kernel: any seqLen / kvLen / headDim <= 256 / strides / causal / ALiBi, written in the
 //    reference's own order (tiles of 64 keys, sequential fp32 dot, running max and sum), used by the
 //    host-pointer `attention` slot and for head sizes the split kernel does not take.
@@ -23,11 +24,53 @@ constexpr int LPK = 8;          // lanes per key
 constexpr int MAXG = 8;         // query heads per KV head handled by one CTA pass
 constexpr int SPLIT_THREADS = 128;
 
+constexpr int MERGE_MAX_SPLITS = 512;
+
+// Combines the per-split records of one (batch, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M),
+// both sums taken in split order.  The weights are computed once per split by the CTA and shared.  Records are
+// read through L2 (they may have been written by other CTAs of the same launch).  sw / sl hold MERGE_MAX_SPLITS
+// floats each, red 8.
+__device__ __forceinline__ void merge_records(const float *rec, float *out, int hd, int splits, float *sw, float *sl, float *red)
+{
+    float m = -INFINITY;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) m = fmaxf(m, __ldcg(rec + (size_t)s * (hd + 2)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __syncthreads();  // red / sw / sl may still be in use by a previous call
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    float M = red[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) M = fmaxf(M, red[i]);
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        const float *r = rec + (size_t)s * (hd + 2);
+        const float ms = __ldcg(r);
+        sw[s] = (ms == -INFINITY) ? 0.f : expf(ms - M);
+        sl[s] = __ldcg(r + 1);
+    }
+    __syncthreads();
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) L = fmaf(sl[s], sw[s], L);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float O = 0.f;
+        int s = 0;
+        for (; s + 4 <= splits; s += 4) {
+            const float a = __ldcg(rec + (size_t)s * (hd + 2) + 2 + d), b = __ldcg(rec + (size_t)(s + 1) * (hd + 2) + 2 + d);
+            const float c = __ldcg(rec + (size_t)(s + 2) * (hd + 2) + 2 + d), e = __ldcg(rec + (size_t)(s + 3) * (hd + 2) + 2 + d);
+            O = fmaf(a, sw[s], O);
+            O = fmaf(b, sw[s + 1], O);
+            O = fmaf(c, sw[s + 2], O);
+            O = fmaf(e, sw[s + 3], O);
+        }
+        for (; s < splits; ++s) O = fmaf(__ldcg(rec + (size_t)s * (hd + 2) + 2 + d), sw[s], O);
+        out[d] = L > 0.f ? __fdiv_rn(O, L) : 0.f;
+    }
+}
+
 // partial record per (batch, head, split): [m, l, o[headDim]]
 template <int DPL, int G>  // DPL = dims per lane = headDim / 8, G = query heads per KV head
 __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
-    const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc, float *__restrict__ part,
-    int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits)
+    const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc, float *part,
+    int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits, float *__restrict__ out, unsigned *tickets)
 {
     constexpr int HD = DPL * LPK;
     smc_grid_dep_sync();
@@ -122,49 +165,22 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
         if (d == 0) rec[0] = M, rec[1] = L;
         rec[2 + d] = O;
     }
-}
-
-constexpr int MERGE_MAX_SPLITS = 512;
-
-// Combines the per-split records of one (batch, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M),
-// both sums taken in split order.  The weights are computed once per split by the CTA and shared.
-__global__ void __launch_bounds__(256) sdpa_merge_kernel(const float *__restrict__ part, float *__restrict__ out,
-                                                         int hd, int splits)
-{
-    // grid.x = batch * heads
-    __shared__ float sw[MERGE_MAX_SPLITS], sl[MERGE_MAX_SPLITS];
-    __shared__ float red[8];
-    smc_grid_dep_sync();
-    const float *rec = part + (size_t)blockIdx.x * splits * (hd + 2);
-    float m = -INFINITY;
-    for (int s = threadIdx.x; s < splits; s += blockDim.x) m = fmaxf(m, rec[(size_t)s * (hd + 2)]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    // the CTA that finishes a (sequence, KV head) last combines the records of its query heads
+    __shared__ float mw[MERGE_MAX_SPLITS], ml[MERGE_MAX_SPLITS], mred[8];
+    __shared__ int s_last;
     __syncthreads();
-    float M = red[0];
-    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) M = fmaxf(M, red[i]);
-    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
-        const float *r = rec + (size_t)s * (hd + 2);
-        sw[s] = (r[0] == -INFINITY) ? 0.f : expf(r[0] - M);
-        sl[s] = r[1];
+    if (threadIdx.x == 0) {
+        __threadfence();
+        unsigned *tk = tickets + (size_t)b * kvHeads + kvh;
+        s_last = atomicAdd(tk, 1u) == (unsigned)splits - 1 ? 1 : 0;
+        if (s_last) *tk = 0;
     }
     __syncthreads();
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) L = fmaf(sl[s], sw[s], L);
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float O = 0.f;
-        int s = 0;
-        for (; s + 4 <= splits; s += 4) {
-            const float a = rec[(size_t)s * (hd + 2) + 2 + d], b = rec[(size_t)(s + 1) * (hd + 2) + 2 + d];
-            const float c = rec[(size_t)(s + 2) * (hd + 2) + 2 + d], e = rec[(size_t)(s + 3) * (hd + 2) + 2 + d];
-            O = fmaf(a, sw[s], O);
-            O = fmaf(b, sw[s + 1], O);
-            O = fmaf(c, sw[s + 2], O);
-            O = fmaf(e, sw[s + 3], O);
-        }
-        for (; s < splits; ++s) O = fmaf(rec[(size_t)s * (hd + 2) + 2 + d], sw[s], O);
-        out[(size_t)blockIdx.x * hd + d] = L > 0.f ? __fdiv_rn(O, L) : 0.f;
+    if (!s_last) return;
+    __threadfence();
+    for (int g = 0; g < G; ++g) {
+        const size_t head = (size_t)b * heads + (size_t)kvh * G + g;
+        merge_records(part + head * splits * (HD + 2), out + head * HD, HD, splits, mw, ml, mred);
     }
 }
 
@@ -237,7 +253,8 @@ __global__ void kv_append_kernel(const float *__restrict__ k, const float *__res
 
 template <int DPL>
 int launch_split_g(smc_ctx *ctx, int G, dim3 grid, size_t smem, cudaStream_t s, const float *q, const float *k,
-                   const float *v, float *part, int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits)
+                   const float *v, float *part, int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits, float *out,
+                   unsigned *tickets)
 {
 #define SMC_SPLIT_CASE(GV)                                                                                         \
     case GV:                                                                                                       \
@@ -245,7 +262,7 @@ int launch_split_g(smc_ctx *ctx, int G, dim3 grid, size_t smem, cudaStream_t s, 
             cudaFuncSetAttribute(sdpa_decode_split_kernel<DPL, GV>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                  (int)smem);                                                                       \
         smc_launch_dep(ctx->use_pdl, sdpa_decode_split_kernel<DPL, GV>, grid, dim3(SPLIT_THREADS), smem, s, q, k, v, part, heads, \
-                       kvHeads, kvLen, maxSeq, scale, splits);                \
+                       kvHeads, kvLen, maxSeq, scale, splits, out, tickets);                \
         break;
     switch (G) {
         SMC_SPLIT_CASE(1)
@@ -303,29 +320,37 @@ int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const 
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
     if (splits > MERGE_MAX_SPLITS) splits = MERGE_MAX_SPLITS;
-    size_t need = (size_t)batch * heads * splits * (headDim + 2) * sizeof(float);
+    // scratch: a fixed header of tickets (one per (sequence, KV head), zeroed at allocation and left at zero by
+    // every launch), then one record per (sequence, head, split); grown on demand (the first call of a larger
+    // shape allocates: make it outside stream capture)
+    constexpr size_t TICKET_BYTES = 65536 * sizeof(unsigned);
+    if ((size_t)batch * kvHeads > 65536) return smc_fail(ctx, SMC_E_RANGE, "sdpa_decode: more than 65536 (sequence, KV head) pairs");
+    const size_t need = TICKET_BYTES + (size_t)batch * heads * splits * (headDim + 2) * sizeof(float);
     if (need > ctx->attn_part_cap) {
         std::lock_guard<std::mutex> lock(ctx->mu);
-        if (ctx->d_attn_part) cudaFree(ctx->d_attn_part);
+        if (ctx->d_attn_part) {
+            cudaDeviceSynchronize();
+            cudaFree(ctx->d_attn_part);
+        }
         ctx->d_attn_part = nullptr;
         ctx->attn_part_cap = 0;
         SMC_CUDA(ctx, cudaMalloc(&ctx->d_attn_part, need));
+        SMC_CUDA(ctx, cudaMemset(ctx->d_attn_part, 0, TICKET_BYTES));
         ctx->attn_part_cap = need;
     }
+    unsigned *tickets = reinterpret_cast<unsigned *>(ctx->d_attn_part);
+    float *records = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ctx->d_attn_part) + TICKET_BYTES);
     const int ngroups = (SPLIT_THREADS / 32) * (32 / LPK);
     size_t smem = ((size_t)ngroups * G * 2 + (size_t)ngroups * G * headDim) * sizeof(float);
     dim3 grid(splits, kvHeads, batch);
     int rc;
     if (headDim == 128)
-        rc = launch_split_g<16>(ctx, G, grid, smem, s, d_q, d_k, d_v, ctx->d_attn_part, heads, kvHeads, kvLen, maxSeq,
-                                scale, splits);
+        rc = launch_split_g<16>(ctx, G, grid, smem, s, d_q, d_k, d_v, records, heads, kvHeads, kvLen, maxSeq,
+                                scale, splits, d_out, tickets);
     else
-        rc = launch_split_g<8>(ctx, G, grid, smem, s, d_q, d_k, d_v, ctx->d_attn_part, heads, kvHeads, kvLen, maxSeq,
-                               scale, splits);
+        rc = launch_split_g<8>(ctx, G, grid, smem, s, d_q, d_k, d_v, records, heads, kvHeads, kvLen, maxSeq,
+                               scale, splits, d_out, tickets);
     if (rc) return rc;
-    smc_launch_dep(ctx->use_pdl, sdpa_merge_kernel, dim3(batch * heads), dim3(headDim <= 128 ? 128 : 256), 0, s,
-                   (const float *)ctx->d_attn_part, d_out, headDim, splits);
-    SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
 

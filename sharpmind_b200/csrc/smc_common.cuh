@@ -100,6 +100,20 @@ struct smc_gather_dev;
 struct smc_gather;
 int smc_launch_gemv_tma_xg(smc_ctx *, const smc_q8act *, const float *xf, const smc_weight *, float *out,
                            const smc_gather_dev *, cudaStream_t s);
+// Residual add + RMSNorm folded into the staging of a one-row matmul: row = RMSNorm(x + add) * w, x + add -> sum.
+struct smc_norm_prologue {
+    const float *add;  // may be null
+    const float *w;
+    float *sum;        // may be null
+    float eps;
+};
+int smc_launch_gemv_tma_full(smc_ctx *, const smc_q8act *, const float *xf, const float *xu, const smc_norm_prologue *,
+                             const smc_weight *, float *out, const smc_gather_dev *, cudaStream_t s);
+int smc_launch_gemv_tma_addnorm(smc_ctx *, const float *x, const smc_norm_prologue *, const smc_weight *, float *out,
+                                cudaStream_t s);
+int smc_launch_gemv_tma_xgu(smc_ctx *, const smc_q8act *, const float *xf, const float *xu, const smc_weight *, float *out,
+                            const smc_gather_dev *, cudaStream_t s);
+int smc_launch_gemv_tma_swiglu(smc_ctx *, const float *gate, const float *up, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_tma_gather(smc_ctx *, const float *x, const smc_weight *, float *out, const smc_gather_dev *,
                                cudaStream_t s);
 int smc_qmatmul_dev_gather(smc_ctx *, const float *d_in, const smc_weight *, float *d_out, int M, int mode, cudaStream_t s,

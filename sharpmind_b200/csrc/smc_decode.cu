@@ -9,6 +9,7 @@
 // elementwise work between two matmuls folded into one launch each (joined Q/K/V matmul, then per-head
 // norm + RoPE + cache append in one kernel; residual add + the following RMSNorm in one kernel);
 // the KV cache, the RoPE tables and all intermediates are owned by the model object.
+#include <utility>
 #include <vector>
 
 #include "smc_common.cuh"
@@ -19,6 +20,7 @@ struct smc_model {
     std::vector<const smc_weight *> wq, wk, wv, wo, wgu, wdown;
     std::vector<smc_weight *> wqkv;  // rows of Wq, Wk, Wv in one matrix (owned), when the three could be joined
     float *qkv = nullptr;            // [batch][qDim + 2 kvDim]
+    float *x2 = nullptr;             // second residual buffer of the one-sequence path (the stream ping-pongs)
     std::vector<const float *> norm1, norm2, qnorm, knorm;
     float *kcache = nullptr, *vcache = nullptr;  // [layer][batch][kvHeads][max_seq][head_dim]
     float *cosT = nullptr, *sinT = nullptr;
@@ -32,7 +34,7 @@ namespace {
 void free_model(smc_ctx *ctx, smc_model *m)
 {
     if (!m) return;
-    float *bufs[] = {m->kcache, m->vcache, m->cosT, m->sinT, m->x, m->xn, m->q, m->k, m->v, m->att, m->tmp, m->gu, m->act, m->qkv};
+    float *bufs[] = {m->kcache, m->vcache, m->cosT, m->sinT, m->x, m->xn, m->q, m->k, m->v, m->att, m->tmp, m->gu, m->act, m->qkv, m->x2};
     for (float *p : bufs) cudaFree(p);
     for (smc_weight *w : m->wqkv)
         if (w) smc_weight_release(ctx, w);
@@ -217,6 +219,7 @@ int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, sm
     alloc(&m->x, B * H), alloc(&m->xn, B * H), alloc(&m->q, B * qDim), alloc(&m->k, B * kvDim), alloc(&m->v, B * kvDim);
     alloc(&m->att, B * qDim), alloc(&m->tmp, B * H), alloc(&m->gu, B * 2 * F), alloc(&m->act, B * F);
     alloc(&m->qkv, B * (qDim + 2 * kvDim));
+    alloc(&m->x2, (size_t)H);
     if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache * sizeof(float));
     if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache * sizeof(float));
     if (e != cudaSuccess) {
@@ -296,6 +299,36 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
         if (rc) return rc;   \
     } while (0)
 
+    // One sequence with quantised activations: every elementwise step between two matmuls rides in the staging of
+    // the matmul that consumes it (residual add + RMSNorm, SiLU-gate), so a layer is eight launches: joined QKV,
+    // per-head norm + RoPE + append, attention, Wo, gate||up, down (+ the next layer's QKV takes its residual).
+    bool one_row = mode == SMC_ACT_Q8 && B == 1 && H <= 8192 && F <= 8192 && ctx->use_tma && smc_tma_supported(d.lm_head, 1);
+    for (int l = 0; l < d.n_layers && one_row; ++l)
+        one_row = m->wqkv[l] && smc_tma_supported(m->wqkv[l], 1) && smc_tma_supported(m->wgu[l], 1) &&
+                  smc_tma_supported(m->wdown[l], 1);
+    if (one_row) {
+        float *cur = m->x, *other = m->x2;
+        const float *pending = nullptr;  // output of the previous block's down-projection, not yet added to the stream
+        SMC_TRY(smc_embed_q8_0_dev(ctx, d.lm_head, d_tokens, 1, cur, s));
+        for (int l = 0; l < d.n_layers; ++l) {
+            float *kc = m->kcache + (size_t)l * layer_stride, *vc = m->vcache + (size_t)l * layer_stride;
+            smc_norm_prologue p1{pending, m->norm1[l], pending ? other : nullptr, d.eps};
+            SMC_TRY(smc_launch_gemv_tma_addnorm(ctx, cur, &p1, m->wqkv[l], m->qkv, s));
+            if (pending) std::swap(cur, other);
+            SMC_TRY(launch_qkv_post(ctx, m, l, kc, vc, 1, pos, s));
+            SMC_TRY(smc_sdpa_decode_dev(ctx, m->q, kc, vc, m->att, 1, nh, nkv, hd, pos + 1, d.max_seq, scale, s));
+            SMC_TRY(smc_qmatmul_dev(ctx, m->att, m->wo[l], m->tmp, 1, mode, s));
+            smc_norm_prologue p2{m->tmp, m->norm2[l], other, d.eps};
+            SMC_TRY(smc_launch_gemv_tma_addnorm(ctx, cur, &p2, m->wgu[l], m->gu, s));
+            std::swap(cur, other);
+            SMC_TRY(smc_launch_gemv_tma_swiglu(ctx, m->gu, m->gu + F, m->wdown[l], m->tmp, s));
+            pending = m->tmp;
+        }
+        smc_norm_prologue pf{pending, d.final_norm, nullptr, d.eps};
+        SMC_TRY(smc_launch_gemv_tma_addnorm(ctx, cur, &pf, d.lm_head, d_logits, s));
+        if (d_argmax) SMC_TRY(smc_argmax_dev(ctx, d_logits, 1, d.vocab, d_argmax, s));
+        return SMC_OK;
+    }
     SMC_TRY(smc_embed_q8_0_dev(ctx, d.lm_head, d_tokens, B, m->x, s));
     SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm1[0], m->xn, B, H, d.eps, s));
     for (int l = 0; l < d.n_layers; ++l) {
@@ -326,9 +359,14 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, B, H, d.eps, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
         SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, B, mode, reuse ? m->qa : nullptr, s));
-        SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, B, F, 2 * F, s));
-        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->act, B, F, m->qb, s));
-        SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s));
+        if (mode == SMC_ACT_Q8 && B == 1 && F <= 8192 && ctx->use_tma && m->wdown[l]->fast && smc_tma_supported(m->wdown[l], 1)) {
+            // one row: SiLU(gate) * up is formed and quantised while the down-projection stages its activations
+            SMC_TRY(smc_launch_gemv_tma_swiglu(ctx, m->gu, m->gu + F, m->wdown[l], m->tmp, s));
+        } else {
+            SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, B, F, 2 * F, s));
+            if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->act, B, F, m->qb, s));
+            SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s));
+        }
         // residual add, then the next block's first norm (the final norm after the last block)
         const float *next_norm = l + 1 < d.n_layers ? m->norm1[l + 1] : d.final_norm;
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, B, H, d.eps, s));

@@ -495,6 +495,8 @@ int smc_rope_tables(smc_ctx *ctx, float theta, int ropeDim, int maxSeq, float *d
     std::lock_guard<std::mutex> lock(ctx->mu);
     SMC_CUDA(ctx, cudaMemcpy(d_cos, c.data(), c.size() * sizeof(float), cudaMemcpyHostToDevice));
     SMC_CUDA(ctx, cudaMemcpy(d_sin, s.data(), s.size() * sizeof(float), cudaMemcpyHostToDevice));
+    // a copy from pageable memory returns once it is staged; the tables may be read next from any stream
+    SMC_CUDA(ctx, cudaDeviceSynchronize());
     return SMC_OK;
 }
 

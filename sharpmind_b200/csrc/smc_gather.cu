@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(512) gather_exchange_kernel(const smc_gather_d
 int upload_view(smc_ctx *ctx, smc_gather *g)
 {
     SMC_CUDA(ctx, cudaMemcpy(g->d_view, &g->view, sizeof(g->view), cudaMemcpyHostToDevice));
+    SMC_CUDA(ctx, cudaDeviceSynchronize());  // staged copies complete before a kernel on any stream reads the view
     return SMC_OK;
 }
 

@@ -112,6 +112,12 @@ struct XPtrs {
     const float *sd;
     const int16_t *s16;
     const float *xf;  // when set (M = 1): fp32 activations, quantised to Q8_0 while they are staged
+    const float *xu;  // when set too: the staged row is SiLU(xf[i]) * xu[i] (FfnKernels.Gated's activation)
+    // when nw is set: the staged row is RMSNorm(xf + xadd) * nw (xadd may be null), and CTA 0 writes xf + xadd to
+    // xsum: the residual add and the norm of a decoder block folded into the matmul that consumes them
+    const float *xadd, *nw;
+    float *xsum;
+    float eps;
 };
 
 // Shared layout of the staged activation row: q | d | sd | s16.  The quants are stored in 16-byte
@@ -133,16 +139,49 @@ __device__ __forceinline__ void stage_x(const XPtrs &g, int m, int K, uint8_t *s
     if (Math::S16)
         for (int i = threadIdx.x; i < K / 16; i += blockDim.x) ss16[i] = __ldg(g.s16 + (size_t)m * (K / 16) + i);
 }
-// Same layout, filled by quantising an fp32 row on the fly: one warp per 32-element block, the rules of
-// QuantizedKVCache.QuantizeRowQ8_0 (d = amax/127, 1 for a zero block, stored through fp16; q = round-half-even(x/d)).
+// Quantises the eight values of chunk c (lanes 4b .. 4b+3 hold the four chunks of block b) and stores them, their
+// block scale and sums in the staged layout: the rules of QuantizedKVCache.QuantizeRowQ8_0 (d = amax/127, 1 for a
+// zero block, stored through fp16; q = round-half-even(x/d)).
 template <class Math>
-__device__ __forceinline__ void stage_x_quant(const float *x, int K, uint8_t *sx)
+__device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, uint8_t *sx)
 {
-    // Four consecutive lanes share a 32-element block, eight elements each; all loads of a batch are
-    // issued before any arithmetic so the row costs one memory latency, not one per block.
     float *sdx = reinterpret_cast<float *>(sx + K);
     float *ssd = sdx + K / 32;
     int16_t *ss16 = reinterpret_cast<int16_t *>(ssd + K / 32);
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    float scale = __fdiv_rn(amax, 127.0f);
+    if (amax == 0.0f) scale = 1.0f;
+    int q[8], s = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        q[i] = max(-128, min(127, __float2int_rn(__fdiv_rn(v[i], scale))));
+        s += q[i];
+    }
+    uint2 packed;
+    packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+    packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+    *reinterpret_cast<uint2 *>(sx + 16 * Math::swz(c >> 1) + 8 * (c & 1)) = packed;
+    const int s16v = s + __shfl_xor_sync(0xffffffffu, s, 1);
+    const int total = s16v + __shfl_xor_sync(0xffffffffu, s16v, 2);
+    const int blk = c >> 2;
+    if (Math::S16 && (c & 1) == 0) ss16[blk * 2 + ((c >> 1) & 1)] = (int16_t)s16v;
+    if ((c & 3) == 0) {
+        const float df = __half2float(__float2half_rn(scale));
+        sdx[blk] = df;
+        if (Math::SD) ssd[blk] = df * (float)total;
+    }
+}
+
+// Same layout, filled by quantising an fp32 row on the fly.  Four consecutive lanes share a 32-element block,
+// eight elements each; all loads of a batch are issued before any arithmetic so the row costs one memory
+// latency, not one per block.  With `up` the row is SiLU(x) * up in the arithmetic of the stand-alone kernel.
+template <class Math>
+__device__ __forceinline__ void stage_x_quant(const float *x, const float *up, int K, uint8_t *sx)
+{
     const int nchunks = K / 8;  // K is a multiple of 1024, so whole warps stay converged
     constexpr int UB = 4;
     for (int c0 = threadIdx.x; c0 < nchunks; c0 += UB * blockDim.x) {
@@ -159,34 +198,68 @@ __device__ __forceinline__ void stage_x_quant(const float *x, int K, uint8_t *sx
         for (int j = 0; j < UB; ++j) {
             const int c = c0 + j * blockDim.x;
             if (c < nchunks) {  // uniform per warp: nchunks is a multiple of 128
-                const float v[8] = {va[j].x, va[j].y, va[j].z, va[j].w, vb[j].x, vb[j].y, vb[j].z, vb[j].w};
-                float amax = 0.f;
+                float v[8] = {va[j].x, va[j].y, va[j].z, va[j].w, vb[j].x, vb[j].y, vb[j].z, vb[j].w};
+                if (up) {  // g / (1 + exp(-g)) * u
+                    const float4 ua = __ldg(reinterpret_cast<const float4 *>(up) + 2 * c), ub = __ldg(reinterpret_cast<const float4 *>(up) + 2 * c + 1);
+                    const float u[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
 #pragma unroll
-                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                float scale = __fdiv_rn(amax, 127.0f);
-                if (amax == 0.0f) scale = 1.0f;
-                int q[8], s = 0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    q[i] = max(-128, min(127, __float2int_rn(__fdiv_rn(v[i], scale))));
-                    s += q[i];
+                    for (int i = 0; i < 8; ++i) v[i] = __fdiv_rn(v[i], 1.0f + expf(-v[i])) * u[i];
                 }
-                uint2 packed;
-                packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
-                packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
-                *reinterpret_cast<uint2 *>(sx + 16 * Math::swz(c >> 1) + 8 * (c & 1)) = packed;
-                const int s16v = s + __shfl_xor_sync(0xffffffffu, s, 1);
-                const int total = s16v + __shfl_xor_sync(0xffffffffu, s16v, 2);
-                const int blk = c >> 2;
-                if (Math::S16 && (c & 1) == 0) ss16[blk * 2 + ((c >> 1) & 1)] = (int16_t)s16v;
-                if ((c & 3) == 0) {
-                    const float df = __half2float(__float2half_rn(scale));
-                    sdx[blk] = df;
-                    if (Math::SD) ssd[blk] = df * (float)total;
-                }
+                quant_chunk<Math>(v, c, K, sx);
             }
+        }
+    }
+}
+
+// The residual add and the RMSNorm that precede a matmul in a decoder block, done while its activation row is
+// staged: v = x + add (add may be null), xsum = v (written by the CTA that is given a pointer), row = v * rsqrt(mean
+// v^2 + eps) * w, quantised as above.  K <= 8192: a thread keeps its (at most four) chunks in registers between the
+// sum of squares and the scaling.  The sum of squares is taken in a fixed order (thread chunks in order, warp
+// butterfly, warps in order), which is not the order of the stand-alone norm kernel: results agree to rounding.
+template <class Math>
+__device__ __forceinline__ void stage_x_addnorm_quant(const float *x, const float *add, const float *w, float eps, float *xsum,
+                                                      int K, uint8_t *sx)
+{
+    __shared__ float red[8];
+    const int nchunks = K / 8;
+    constexpr int UB = 4;
+    float v[UB][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < UB; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < nchunks) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(x) + 2 * c), b = __ldg(reinterpret_cast<const float4 *>(x) + 2 * c + 1);
+            v[j][0] = a.x, v[j][1] = a.y, v[j][2] = a.z, v[j][3] = a.w, v[j][4] = b.x, v[j][5] = b.y, v[j][6] = b.z, v[j][7] = b.w;
+            if (add) {
+                const float4 p = __ldg(reinterpret_cast<const float4 *>(add) + 2 * c), q = __ldg(reinterpret_cast<const float4 *>(add) + 2 * c + 1);
+                v[j][0] += p.x, v[j][1] += p.y, v[j][2] += p.z, v[j][3] += p.w, v[j][4] += q.x, v[j][5] += q.y, v[j][6] += q.z, v[j][7] += q.w;
+            }
+            if (xsum) {
+                reinterpret_cast<float4 *>(xsum)[2 * c] = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+                reinterpret_cast<float4 *>(xsum)[2 * c + 1] = make_float4(v[j][4], v[j][5], v[j][6], v[j][7]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(v[j][i], v[j][i], ss);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = red[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+    const float inv = __fdiv_rn(1.0f, sqrtf(__fdiv_rn(tot, (float)K) + eps));
+#pragma unroll
+    for (int j = 0; j < UB; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < nchunks) {
+            const float4 g0 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * c), g1 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * c + 1);
+            const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            float r[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[i] = (v[j][i] * inv) * g[i];
+            quant_chunk<Math>(r, c, K, sx);
         }
     }
 }
@@ -507,7 +580,8 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
     // row-split across GPUs (one row only): tell the peers that this rank's readers of the previous exchange are done
     if (GATHER && blockIdx.x == 0 && threadIdx.x == 32) smc_gather_post_ready(gd);
     if (XS) {
-        if (xg.xf) stage_x_quant<Math>(xg.xf, K, smem);
+        if (xg.nw) stage_x_addnorm_quant<Math>(xg.xf, xg.xadd, xg.nw, xg.eps, blockIdx.x == 0 ? xg.xsum : nullptr, K, smem);
+        else if (xg.xf) stage_x_quant<Math>(xg.xf, xg.xu, K, smem);
         else stage_x<Math>(xg, m0, K, smem);
         __syncthreads();
     }
@@ -693,11 +767,41 @@ int smc_launch_gemv_tma_gather(smc_ctx *ctx, const float *x, const smc_weight *w
     return smc_launch_gemv_tma_xg(ctx, &one, x, w, out, gd, s);
 }
 
+// One row whose activation is SiLU(gate) * up, formed and quantised while the row is staged.
+int smc_launch_gemv_tma_swiglu(smc_ctx *ctx, const float *gate, const float *up, const smc_weight *w, float *out, cudaStream_t s)
+{
+    smc_q8act one{};
+    one.M = 1, one.K = w->K;
+    return smc_launch_gemv_tma_xgu(ctx, &one, gate, up, w, out, nullptr, s);
+}
+
 int smc_launch_gemv_tma_xg(smc_ctx *ctx, const smc_q8act *a, const float *xf, const smc_weight *w, float *out,
                            const smc_gather_dev *gd, cudaStream_t s)
 {
+    return smc_launch_gemv_tma_xgu(ctx, a, xf, nullptr, w, out, gd, s);
+}
+
+// One row that is RMSNorm(x + add) * w, formed and quantised while the row is staged; x + add goes to `sum`.
+int smc_launch_gemv_tma_addnorm(smc_ctx *ctx, const float *x, const smc_norm_prologue *pro, const smc_weight *w, float *out,
+                                cudaStream_t s)
+{
+    smc_q8act one{};
+    one.M = 1, one.K = w->K;
+    return smc_launch_gemv_tma_full(ctx, &one, x, nullptr, pro, w, out, nullptr, s);
+}
+
+int smc_launch_gemv_tma_xgu(smc_ctx *ctx, const smc_q8act *a, const float *xf, const float *xu, const smc_weight *w, float *out,
+                            const smc_gather_dev *gd, cudaStream_t s)
+{
+    return smc_launch_gemv_tma_full(ctx, a, xf, xu, nullptr, w, out, gd, s);
+}
+
+int smc_launch_gemv_tma_full(smc_ctx *ctx, const smc_q8act *a, const float *xf, const float *xu, const smc_norm_prologue *pro,
+                             const smc_weight *w, float *out, const smc_gather_dev *gd, cudaStream_t s)
+{
     const int N = w->N, K = w->K, M = a->M;
-    XPtrs x{a->q, a->d, a->sd, a->s16, xf};
+    XPtrs x{a->q, a->d, a->sd, a->s16, xf, xu, nullptr, nullptr, nullptr, 0.f};
+    if (pro) x.xadd = pro->add, x.nw = pro->w, x.xsum = pro->sum, x.eps = pro->eps;
     StepSrc src{};
     if (w->dtype == SMC_Q4_K) {
         src.base[0] = w->d_raw;

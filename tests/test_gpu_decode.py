@@ -129,3 +129,40 @@ def test_decode_rejects_bad_arguments(oracle, cuda):
     with pytest.raises(ops.SharpMindCudaError):
         dec.step(tok[:2], cfg["max_seq"])      # position past the cache (KVCache.Update throws)
     dec.close()
+
+
+WIDE = dict(n_layers=2, hidden=1024, n_heads=8, n_kv_heads=4, head_dim=128, ffn=2048, vocab=2048,
+            max_seq=32, dtype=8, eps=1e-6, rope_theta=1.0e6, neox=True, qk_norm=True)
+
+
+def test_decode_one_sequence_fused_path(oracle, cuda):
+    """Hidden sizes the TMA GEMV takes put a single sequence on the path where the residual add, the RMSNorms and
+    the SiLU-gate ride in the staging of the following matmul: same tolerance as the unfused quantised-activation
+    path, and it agrees with row 0 of a two-sequence step (which runs the separate kernels) on the same tokens."""
+    import torch
+
+    cfg, name, steps = WIDE, "dec_wide", 8
+    w = _weights(oracle, cfg, name)
+    ref = oracle.Decoder(cfg, w, 1)
+    one = Decoder(cuda, cfg, w, max_batch=1)
+    # a host buffer registered twice replaces its first device copy: the second decoder gets its own arrays
+    w2 = {k: ([a.copy() for a in v] if isinstance(v, list) else v.copy()) for k, v in w.items()}
+    two = Decoder(cuda, cfg, w2, max_batch=2)
+    tok = synth.token_ids(name, "prompt", (1,), cfg["vocab"])
+    for pos in range(steps):
+        want = ref.step(tok, pos)
+        t1 = torch.from_numpy(tok.copy()).cuda()
+        l1, n1 = one.step(t1, pos, ops.Mode.ACT_Q8)
+        l2, _ = two.step(torch.cat([t1, t1]), pos, ops.Mode.ACT_Q8)
+        got, pair = l1.cpu().numpy(), l2.cpu().numpy()
+        scale = np.abs(want).max()
+        assert np.abs(got - want).max() <= 0.05 * scale
+        assert np.abs(got[0] - pair[0]).max() <= 2e-3 * scale, float(np.abs(got[0] - pair[0]).max() / scale)
+        top2 = np.sort(want[0])[-2:]
+        pick = want.argmax(axis=1).astype(np.int32)
+        if top2[1] - top2[0] > 0.1 * scale:
+            assert n1.cpu().numpy()[0] == pick[0]
+        tok = pick
+    one.close()
+    two.close()
+    assert cuda.device_status() == 0

@@ -247,3 +247,44 @@ def test_argmax_first_maximum_over_chunks(dev):
     assert got[1] == 70000 and got[4] == 0
     small = to_dev(synth.normal("gpue", "ams", (7, 100)))
     assert dev.argmax(small).cpu().numpy().tolist() == small.cpu().numpy().argmax(axis=1).tolist()
+
+
+@pytest.mark.parametrize("dtype,n,k", [(Q8_0, 1024, 2048), (Q8_0, 256, 3072), (Q4_K, 512, 2048)])
+def test_fused_one_row_matmuls(oracle, cuda, dev, dtype, n, k):
+    """SiLU-gate and residual add + RMSNorm folded into the staging of a one-row matmul, against the separate kernels."""
+    import ctypes as C
+
+    import torch
+
+    from sharpmind_b200.ops import Mode
+
+    raw = oracle.quantize(dtype, synth.normal("gpue", f"fw{dtype}_{n}_{k}", (n, k), 0.02))
+    w = cuda.register(raw, dtype, n, k)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    lib, h = cuda.lib, cuda.h
+    # SwiGLU prologue: same bits as swiglu followed by the quantised-activation matmul
+    gu = to_dev(synth.normal("gpue", f"fgu{k}", (1, 2 * k)))
+    act = dev.swiglu_fused(gu, k)
+    want = dev.qmatmul(act, w, Mode.ACT_Q8)
+    got = torch.empty_like(want)
+    cuda.check(lib.smc_qmatmul_swiglu_dev(h, gu.data_ptr(), gu.data_ptr() + 4 * k, w.handle, got.data_ptr(), st))
+    assert torch.equal(got, want)
+    # add + norm prologue: the stream sum has the bits of the add kernel; the matmul agrees to rounding
+    x = to_dev(synth.normal("gpue", f"fx{k}", (1, k)))
+    y = to_dev(synth.normal("gpue", f"fy{k}", (1, k)))
+    nw = to_dev(synth.normal("gpue", f"fn{k}", (k,), 0.1, 1.0))
+    xs = x.clone()
+    dev.add_(xs, y)
+    want = dev.qmatmul(dev.rmsnorm(xs, nw, 1e-6), w, Mode.ACT_Q8)
+    got, summ = torch.empty_like(want), torch.empty_like(x)
+    cuda.check(lib.smc_qmatmul_addnorm_dev(h, x.data_ptr(), y.data_ptr(), nw.data_ptr(), C.c_float(1e-6), summ.data_ptr(),
+                                           w.handle, got.data_ptr(), st))
+    assert torch.equal(summ, xs)
+    scale = want.abs().max().item()
+    assert (got - want).abs().max().item() <= 2e-2 * scale
+    # without an addend it is the plain norm
+    want = dev.qmatmul(dev.rmsnorm(x, nw, 1e-6), w, Mode.ACT_Q8)
+    cuda.check(lib.smc_qmatmul_addnorm_dev(h, x.data_ptr(), None, nw.data_ptr(), C.c_float(1e-6), None, w.handle,
+                                           got.data_ptr(), st))
+    assert (got - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    cuda.release(w)
