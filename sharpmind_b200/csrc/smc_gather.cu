@@ -42,6 +42,28 @@ __global__ void __launch_bounds__(512) gather_exchange_kernel(const smc_gather_d
     smc_gather_done(g, gridDim.x);
 }
 
+// Exchange of a large chunk: stripes of 16-byte stores straight into every peer's dense area.
+__global__ void __launch_bounds__(512) gather_bulk_kernel(const smc_gather_dev *g, size_t count)
+{
+    __shared__ int s_ok;
+    const unsigned tag = smc_gather_tag(g);
+    if (threadIdx.x == 0) {
+        if (blockIdx.x == 0) smc_gather_post_ready(g);
+        s_ok = smc_gather_wait_ready(g, tag) ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_ok) {
+        const float4 *src = reinterpret_cast<const float4 *>(g->data + (size_t)g->rank * count);
+        const size_t n4 = count / 4, nth = (size_t)gridDim.x * blockDim.x;
+        for (int i = 1; i < g->world; ++i) {
+            const int p = (g->rank + i) % g->world;
+            float4 *dst = reinterpret_cast<float4 *>(g->peer_data[p] + (size_t)g->rank * count);
+            for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < n4; t += nth) dst[t] = __ldcg(src + t);
+        }
+    }
+    smc_gather_finish_bulk(g, gridDim.x, tag);
+}
+
 int upload_view(smc_ctx *ctx, smc_gather *g)
 {
     SMC_CUDA(ctx, cudaMemcpy(g->d_view, &g->view, sizeof(g->view), cudaMemcpyHostToDevice));
@@ -79,6 +101,7 @@ int smc_gather_create(smc_ctx *ctx, int rank, int world, size_t capacity_floats,
     g->view.rank = rank, g->view.world = world, g->view.status = ctx->d_status;
     g->view.ctrl[rank] = reinterpret_cast<smc_gather_ctrl *>(g->base);
     g->view.data = reinterpret_cast<float *>(g->base + SMC_GATHER_CTRL_BYTES);
+    g->view.peer_data[rank] = g->view.data;
     g->view.pkt[rank] = reinterpret_cast<unsigned long long *>(g->base + SMC_GATHER_CTRL_BYTES + g->capacity * sizeof(float));
     g->connected = world == 1;
     int rc = upload_view(ctx, g);
@@ -117,6 +140,7 @@ int smc_gather_connect(smc_ctx *ctx, smc_gather *g, const unsigned char *handles
         g->view.ctrl[p] = reinterpret_cast<smc_gather_ctrl *>(ptr);
         g->view.pkt[p] = reinterpret_cast<unsigned long long *>(static_cast<unsigned char *>(ptr) + SMC_GATHER_CTRL_BYTES +
                                                                 g->capacity * sizeof(float));
+        g->view.peer_data[p] = reinterpret_cast<float *>(static_cast<unsigned char *>(ptr) + SMC_GATHER_CTRL_BYTES);
     }
     int rc = upload_view(ctx, g);
     if (rc) return rc;
@@ -139,6 +163,11 @@ int smc_gather_exchange_dev(smc_ctx *ctx, smc_gather *g, size_t count, void *str
         return smc_fail(ctx, SMC_E_RANGE, "gather_exchange: %zu floats x %d ranks exceed the buffer of %zu", count, g->world,
                         g->capacity);
     if (g->world == 1 || count == 0) return SMC_OK;
+    if (count >= (1u << 18) && (count & 3) == 0) {  // a megabyte or more per rank: bulk stores, one fence, one flag
+        gather_bulk_kernel<<<ctx->sm_count, 512, 0, static_cast<cudaStream_t>(stream)>>>(g->d_view, count);
+        SMC_LAUNCH_CHECK(ctx);
+        return SMC_OK;
+    }
     int ctas = (int)((count + 1023) / 1024);
     if (ctas < 1) ctas = 1;
     if (ctas > ctx->sm_count) ctas = ctx->sm_count;

@@ -29,7 +29,8 @@
 
 // Control block at the start of each rank's allocation (what peers address).
 struct smc_gather_ctrl {
-    unsigned ready[SMC_GATHER_MAX_RANKS];  // ready[r] = e+1: rank r's chunk here may be overwritten for exchange e
+    unsigned ready[SMC_GATHER_MAX_RANKS];    // ready[r] = e+1: rank r's chunk here may be overwritten for exchange e
+    unsigned arrived[SMC_GATHER_MAX_RANKS];  // bulk exchanges: arrived[r] = e+1 once rank r's whole chunk is here
     unsigned ticket;                       // CTAs of the running producer that have finished
     unsigned epoch;                        // exchanges completed by this rank
 };
@@ -38,6 +39,7 @@ struct smc_gather_ctrl {
 struct smc_gather_dev {
     smc_gather_ctrl *ctrl[SMC_GATHER_MAX_RANKS];     // ctrl[r]: rank r's control block as mapped on this device
     unsigned long long *pkt[SMC_GATHER_MAX_RANKS];   // pkt[r]: rank r's packet area as mapped on this device
+    float *peer_data[SMC_GATHER_MAX_RANKS];          // peer_data[r]: rank r's dense data area as mapped on this device
     float *data;                                     // this rank's dense data area
     int rank, world;
     int *status;  // the context's status word
@@ -140,6 +142,53 @@ __device__ __forceinline__ void smc_gather_collect(const smc_gather_dev *g, size
             }
             dst[t] = __uint_as_float((unsigned)pk);
         }
+    }
+}
+
+// Large slices (megabytes) go as plain 16-byte stores into the peers' dense areas instead of packets: half the bytes
+// on the wire, at the price of one system-scope fence and a flag per exchange, which no longer matters at that size.
+__device__ __forceinline__ unsigned smc_ld_acquire_sys(const unsigned *p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void smc_st_release_sys(unsigned *p, unsigned v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Every thread of every CTA, after the CTA's stores into the peers' dense areas.  The CTA that arrives last posts
+// "chunk complete" to every peer, waits for theirs and advances the exchange counter.
+__device__ __forceinline__ void smc_gather_finish_bulk(const smc_gather_dev *g, unsigned total_ctas, unsigned tag)
+{
+    __shared__ unsigned s_last;
+    smc_gather_ctrl *me = g->ctrl[g->rank];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();  // this CTA's stores into peer memory are performed before the ticket is taken
+        s_last = (atomicAdd(&me->ticket, 1u) == total_ctas - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (int p = 0; p < g->world; ++p)
+            if (p != g->rank) smc_st_release_sys(&g->ctrl[p]->arrived[g->rank], tag);
+    }
+    if (threadIdx.x < (unsigned)g->world && (int)threadIdx.x != g->rank) {
+        const unsigned long long t0 = smc_globaltimer();
+        unsigned polls = 0;
+        while ((int)(smc_ld_acquire_sys(&me->arrived[threadIdx.x]) - tag) < 0) {
+            if ((++polls & 63u) == 0 && smc_globaltimer() - t0 > SMC_GATHER_WAIT_NS) {
+                atomicExch(g->status, 2);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        me->ticket = 0;
+        me->epoch = tag;
     }
 }
 

@@ -43,6 +43,22 @@ def main():
                 got = lin.assemble(g.matmul(x, part, ops.Mode.ACT_Q8))
                 if not torch.equal(got, want):
                     failures.append(f"dtype {dtype} M {m} iteration {it}: max diff {(got - want).abs().max().item()}")
+        # a slice of a megabyte or more goes as bulk stores + one flag instead of packets
+        if dtype == 12 and k == 4096:
+            m = 128 * world
+            big = PeerGather(ctx, split, world * m * (n // world), dist)
+            for it in range(3):
+                x = torch.from_numpy(synth.normal("multi", f"xb{it}", (m, k))).cuda()
+                want = dev.qmatmul(x, full, ops.Mode.ACT_Q8)
+                got = lin.assemble(big.matmul(x, part, ops.Mode.ACT_Q8))
+                if not torch.equal(got, want):
+                    failures.append(f"bulk exchange iteration {it}: max diff {(got - want).abs().max().item()}")
+                # alternate with a small (packet) exchange on the same object
+                x1 = torch.from_numpy(synth.normal("multi", f"xs{it}", (1, k))).cuda()
+                if not torch.equal(lin.assemble(big.matmul(x1, part, ops.Mode.ACT_Q8)), dev.qmatmul(x1, full, ops.Mode.ACT_Q8)):
+                    failures.append(f"packet exchange after bulk, iteration {it}")
+            dist.barrier()
+            big.close()
         # replayed graph: the exchange counter lives in device memory, so replays stay in step
         x = torch.from_numpy(synth.normal("multi", f"xg{dtype}", (1, k))).cuda()
         want = dev.qmatmul(x, full, ops.Mode.ACT_Q8)
