@@ -108,6 +108,38 @@ __device__ __forceinline__ bool smc_gather_wait_ready(const smc_gather_dev *g, u
     return true;
 }
 
+// The same for a whole warp: lane p watches peer p, so the flags of all peers cost one round trip instead of one each.
+__device__ __forceinline__ bool smc_gather_wait_ready_warp(const smc_gather_dev *g, unsigned tag)
+{
+    const int lane = threadIdx.x & 31;
+    const smc_gather_ctrl *me = g->ctrl[g->rank];
+    bool ok = true;
+    if (lane < g->world && lane != g->rank) {
+        unsigned long long t0 = 0;
+        unsigned polls = 0;
+        while ((int)(smc_ld_relaxed_sys(&me->ready[lane]) - tag) < 0) {
+            if ((++polls & 63u) == 0) {
+                if (!t0) t0 = smc_globaltimer();
+                else if (smc_globaltimer() - t0 > SMC_GATHER_WAIT_NS) {
+                    atomicExch(g->status, 2);
+                    ok = false;
+                    break;
+                }
+            }
+        }
+    }
+    return __all_sync(0xffffffffu, ok);
+}
+
+// Step 2 for a whole warp that holds `v` in every lane: lane p sends to peer p.
+__device__ __forceinline__ void smc_gather_send_warp(const smc_gather_dev *g, size_t count, size_t idx, float v, unsigned tag)
+{
+    const int lane = threadIdx.x & 31;
+    if (lane < g->world && lane != g->rank)
+        smc_st_relaxed_sys64(g->pkt[lane] + (size_t)g->rank * count + idx,
+                             ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v));
+}
+
 // Step 2: element `idx` of this rank's chunk of `count` floats.
 __device__ __forceinline__ void smc_gather_send(const smc_gather_dev *g, size_t count, size_t idx, float v, unsigned tag)
 {

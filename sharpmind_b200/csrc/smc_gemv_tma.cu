@@ -532,7 +532,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
                                                              const smc_gather_dev *gd)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    int sending = -1;      // lane 0: whether packets go out, known after the first look at the peers' ready flags
+    int sending = -1;      // whether packets go out, known after the first look at the peers' ready flags (warp uniform)
     unsigned gtag = 0;     // number of the running exchange
     constexpr bool XS = (MT == 1);
     constexpr uint32_t SLOT = (Math::STEP_BYTES * SS + 127u) & ~127u;
@@ -606,19 +606,16 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
         for (int i = 0; i < SS; ++i) {
             math.template step<MT, XS, SS>(saddr, i, part, xc, acc);
             if (++part == spr) {
+                if (XS && GATHER && sending < 0) {  // first finished row of this warp: the peers' ready flags, one lane each
+                    gtag = smc_gather_tag(gd);
+                    sending = smc_gather_wait_ready_warp(gd, gtag) ? 1 : 0;
+                }
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
-                    const float v = warp_sum32(acc[m]);
-                    if (lane == 0 && m0 + m < M) {
-                        out[(size_t)(m0 + m) * N + row] = v;
-                        if (XS && GATHER) {  // this rank's chunk starts at rank * N in every peer's buffer
-                            if (sending < 0) {
-                                gtag = smc_gather_tag(gd);
-                                sending = smc_gather_wait_ready(gd, gtag) ? 1 : 0;
-                            }
-                            if (sending) smc_gather_send(gd, (size_t)N, (size_t)row, v, gtag);
-                        }
-                    }
+                    const float v = warp_sum32(acc[m]);  // every lane holds the sum
+                    if (lane == 0 && m0 + m < M) out[(size_t)(m0 + m) * N + row] = v;
+                    // this rank's chunk starts at rank * N in every peer's buffer; lane p sends to peer p
+                    if (XS && GATHER && sending) smc_gather_send_warp(gd, (size_t)N, (size_t)row, v, gtag);
                     acc[m] = 0.f;
                 }
                 part = 0;
