@@ -148,32 +148,33 @@ __device__ __forceinline__ void smc_gather_send(const smc_gather_dev *g, size_t 
         if (p != g->rank) smc_st_relaxed_sys64(g->pkt[p] + (size_t)g->rank * count + idx, pk);
 }
 
-// Step 3: every thread of every CTA, after the CTA's own sends.  CTA `cta` of `total` unpacks its stripe.
+// Step 3: every thread of every CTA, after the CTA's own sends.  CTA `cta` of `total` unpacks its stripe of every
+// peer's chunk; the (peer, element) pairs are spread over the threads so that all peers are polled at once.
 __device__ __forceinline__ void smc_gather_collect(const smc_gather_dev *g, size_t count, unsigned cta, unsigned total,
                                                    unsigned tag)
 {
     const size_t per = (count + total - 1) / total;
     const size_t lo = (size_t)cta * per, hi = lo + per < count ? lo + per : count;
+    if (lo >= hi) return;
+    const size_t span = hi - lo, items = span * (size_t)(g->world - 1);
     bool dead = false;
-    for (int i = 1; i < g->world; ++i) {
-        const int p = (g->rank + i) % g->world;
-        const unsigned long long *src = g->pkt[g->rank] + (size_t)p * count;
-        float *dst = g->data + (size_t)p * count;
-        for (size_t t = lo + threadIdx.x; t < hi; t += blockDim.x) {
-            unsigned long long pk = smc_ld_relaxed_sys64(src + t);
-            if ((unsigned)(pk >> 32) != tag && !dead) {
-                const unsigned long long t0 = smc_globaltimer();
-                unsigned polls = 0;
-                while ((unsigned)((pk = smc_ld_relaxed_sys64(src + t)) >> 32) != tag) {
-                    if ((++polls & 63u) == 0 && smc_globaltimer() - t0 > SMC_GATHER_WAIT_NS) {
-                        dead = true;
-                        atomicExch(g->status, 2);
-                        break;
-                    }
+    for (size_t it = threadIdx.x; it < items; it += blockDim.x) {
+        const int p = (g->rank + 1 + (int)(it / span)) % g->world;
+        const size_t t = lo + it % span;
+        const unsigned long long *src = g->pkt[g->rank] + (size_t)p * count + t;
+        unsigned long long pk = smc_ld_relaxed_sys64(src);
+        if ((unsigned)(pk >> 32) != tag && !dead) {
+            const unsigned long long t0 = smc_globaltimer();
+            unsigned polls = 0;
+            while ((unsigned)((pk = smc_ld_relaxed_sys64(src)) >> 32) != tag) {
+                if ((++polls & 63u) == 0 && smc_globaltimer() - t0 > SMC_GATHER_WAIT_NS) {
+                    dead = true;
+                    atomicExch(g->status, 2);
+                    break;
                 }
             }
-            dst[t] = __uint_as_float((unsigned)pk);
         }
+        g->data[(size_t)p * count + t] = __uint_as_float((unsigned)pk);
     }
 }
 
