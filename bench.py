@@ -324,7 +324,7 @@ def run_ours(args):
             per += len(mats)  # the exchange is a launch of its own unless it rides in the one-row GEMV's tail
         return L * per
 
-    def timed(M, steps, warmup, use_graph):
+    def timed(M, steps, warmup, use_graph, preload_s=0.0):
         state = make_state(M)
         runner = lambda: step(state, M)  # noqa: E731
         graph = None
@@ -345,6 +345,21 @@ def run_ours(args):
         for _ in range(max(warmup, 3)):
             runner()
         torch.cuda.synchronize()
+        # The timed region of a few dozen steps lasts tens of milliseconds, too short for the 200 ms clock sampler:
+        # the same step is replayed (untimed) for `preload_s` first, so that the clocks and throttle reasons that are
+        # sampled are those of the GPU under this very load.  The number of replays is fixed on rank 0 and broadcast.
+        if preload_s > 0:
+            t_one = time.perf_counter()
+            runner()
+            torch.cuda.synchronize()
+            reps = int(min(5000, max(1, preload_s / max(time.perf_counter() - t_one, 1e-5))))
+            if dist is not None:
+                rt = torch.tensor([reps], device="cuda")
+                dist.broadcast(rt, 0)
+                reps = int(rt.item())
+            for _ in range(reps):
+                runner()
+            torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
@@ -368,7 +383,7 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms_step, graphed = timed(M, args.steps, args.warmup, not args.no_graph)
+    ms_step, graphed = timed(M, args.steps, args.warmup, not args.no_graph, preload_s=1.2)
     clocks = sampler.stop() if rank == 0 else None
 
     # whole-job bytes: the full matrices (all ranks' slices) + activations and outputs once
@@ -476,6 +491,60 @@ def run_ours(args):
                     finally:
                         mode = saved
             result["sweep_GBps"] = sweep
+
+            # ---- the 70B-shaped stack of configs[4] on this GPU (12 of its 80 layers: 4.8 GB per step >> L2), batch 1
+            if args.workload == "llama8b":
+                try:
+                    mats70 = matrices("llama70b")
+                    w70 = []
+                    for layer in range(12):
+                        row = []
+                        for mi, (name, dt, n, k) in enumerate(mats70):
+                            g70 = torch.Generator(device="cuda").manual_seed(7_000_003 * layer + 11 * mi + 1)
+                            wf = torch.randn((n, k), generator=g70, device="cuda", dtype=torch.float32) * 0.02
+                            raw_d = dev.quantize_weights(dt, wf)
+                            del wf
+                            row.append(ctx.register_dev(raw_d, dt, n, k, repack=True, keep_raw=False))
+                            del raw_d
+                        w70.append(row)
+                    x70 = [torch.from_numpy(np.random.default_rng(170 + i).standard_normal((1, k), dtype=np.float32)).cuda()
+                           for i, (_, _, _, k) in enumerate(mats70)]
+                    o70 = [torch.empty((1, w.N), device="cuda", dtype=torch.float32) for w in w70[0]]
+
+                    def step70():
+                        for row in w70:
+                            for mi, w in enumerate(row):
+                                dev.qmatmul(x70[mi], w, ops.Mode.ACT_Q8, out=o70[mi])
+
+                    st = torch.cuda.Stream()
+                    st.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(st):
+                        step70()
+                    torch.cuda.current_stream().wait_stream(st)
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        step70()
+                    for _ in range(3):
+                        g.replay()
+                    torch.cuda.synchronize()
+                    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    t0.record()
+                    for _ in range(10):
+                        g.replay()
+                    t1.record()
+                    torch.cuda.synchronize()
+                    ms70 = t0.elapsed_time(t1) / 10
+                    b70 = algorithmic_bytes(mats70, 1) * 12
+                    result["stack70b"] = {"workload": WORKLOADS["llama70b"][3], "layers_timed": 12, "batch": 1,
+                                          "ms_per_12_layers": ms70, "GBps": b70 / (ms70 * 1e-3) / 1e9,
+                                          "frac_of_measured_hbm": b70 / (ms70 * 1e-3) / 1e9 / peak}
+                    for row in w70:
+                        for w in row:
+                            ctx.release(w)
+                    del w70, x70, o70, g
+                except Exception as exc:
+                    result["stack70b"] = {"error": str(exc)}
 
             # ---- end to end through the host-pointer C ABI
             q = ops.QuantizationOps(ctx, mode)
