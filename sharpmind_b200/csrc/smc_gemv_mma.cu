@@ -18,6 +18,8 @@
 // the weights, lane = token for the activations) and handed round with shuffles.
 #include "smc_common.cuh"
 
+#include <type_traits>
+
 namespace {
 
 constexpr int MMA_ROWS = 32;   // weight rows per CTA
@@ -38,8 +40,8 @@ __device__ __forceinline__ uint2 ldg8(const void *p)
     return v;
 }
 
-// Adds the eight warps' partial tiles in warp order and stores out[t, r]; red is [8 warps][32 tokens][33].
-template <int NT>
+// Adds the warps' partial tiles in warp order and stores out[t, r]; red is [NW warps][32 tokens][33].
+template <int NT, int NW = MMA_WARPS>
 __device__ __forceinline__ void reduce_and_store(float (*red)[32][33], const float (&acc)[2][NT][4], float *out, int N, int M,
                                                  int r0, int t0)
 {
@@ -55,7 +57,7 @@ __device__ __forceinline__ void reduce_and_store(float (*red)[32][33], const flo
         const int row = o & 31, tok = o >> 5;
         float s = red[0][tok][row];
 #pragma unroll
-        for (int w = 1; w < MMA_WARPS; ++w) s += red[w][tok][row];
+        for (int w = 1; w < NW; ++w) s += red[w][tok][row];
         if (r0 + row < N && t0 + tok < M) out[(size_t)(t0 + tok) * N + r0 + row] = s;
     }
     __syncthreads();
@@ -234,6 +236,127 @@ gemv_mma_q4_K_kernel(const uint8_t *__restrict__ raw, const int8_t *__restrict__
     }
 }
 
+// ------------------------------------------------------------------------------------------------ Q6_K
+// Planes per 256-element block: ql[128], qh[64], 16 int8 scales, fp16 d.  A scale covers 16 elements, so the unit
+// is mma.m16n8k16: for half h (128 elements) and sixteen `is` a lane reads four bytes of ql[l], ql[32 + l] and
+// qh[l] at l = 16*is + 4*tg of each of its four rows and forms from them the codes of columns c = 0..3 (elements
+// 32c + l .. l + 3 of the half), 32 subtracted bytewise; out += (d * sc[8h + is + 2c]) * dx[4h + c] * isum.
+__device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+__device__ __forceinline__ uint32_t ldg4(const void *p)
+{
+    uint32_t v;
+    asm("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+template <int C>
+__device__ __forceinline__ uint32_t q6_codes(uint32_t wa, uint32_t wb, uint32_t wh)
+{
+    const uint32_t M4 = 0x0F0F0F0Fu, M2 = 0x30303030u;
+    uint32_t q;
+    if (C == 0) q = (wa & M4) | ((wh << 4) & M2);
+    else if (C == 1) q = (wb & M4) | ((wh << 2) & M2);
+    else if (C == 2) q = ((wa >> 4) & M4) | (wh & M2);
+    else q = ((wb >> 4) & M4) | ((wh >> 2) & M2);
+    return __vsub4(q, 0x20202020u);  // codes 0..63 -> -32..31, no byte borrows into its neighbour
+}
+
+template <int NT, int NW>
+__global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1)
+gemv_mma_q6_K_kernel(const uint8_t *__restrict__ ql, const uint8_t *__restrict__ qh, const int8_t *__restrict__ scp,
+                     const __half *__restrict__ dp, const int8_t *__restrict__ xq, const float *__restrict__ xd,
+                     float *__restrict__ out, int N, int K, int M)
+{
+    // NW warps split K: 8 (two CTAs per SM), or 16 in one CTA per SM for rows of 8192 elements and more
+    extern __shared__ __align__(16) float red_dyn[];
+    float (*red)[32][33] = reinterpret_cast<float (*)[32][33]>(red_dyn);
+    smc_grid_dep_sync();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
+    const int r0 = blockIdx.x * MMA_ROWS;
+    const int nb = K / 32, nsb = K / 256;
+    uint32_t rblk[4];  // block indices: a tensor has fewer than 2^32 blocks of 256
+#pragma unroll
+    for (int j = 0; j < 4; ++j) rblk[j] = (uint32_t)min(r0 + (j >> 1) * 16 + g + (j & 1) * 8, N - 1) * (uint32_t)nsb;
+    const uint32_t hblk = (uint32_t)min(r0 + lane, N - 1) * (uint32_t)nsb;
+    for (int t0 = 0; t0 < M; t0 += 8 * NT) {
+        const int8_t *brow[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) brow[t] = xq + (size_t)min(t0 + 8 * t + g, M - 1) * K + 4 * tg;
+        const float *xrow = xd + (size_t)min(t0 + lane, M - 1) * nb;
+        float acc[2][NT][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
+        for (int sb = warp; sb < nsb; sb += NW) {
+            // this lane's row: d * sc of the sixteen sub-blocks
+            const uint4 scw = *reinterpret_cast<const uint4 *>(scp + (size_t)(hblk + sb) * 16);
+            const float d = __half2float(dp[hblk + sb]);
+            // this lane's token: activation scales of the eight 32-element blocks
+            const float4 dxa = *reinterpret_cast<const float4 *>(xrow + sb * 8), dxb = *reinterpret_cast<const float4 *>(xrow + sb * 8 + 4);
+            // up to 16 tokens both halves are unrolled and their loads overlap; beyond, the accumulators need the registers
+#pragma unroll(NT <= 2 ? 2 : 1)
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t scws[2] = {h ? scw.z : scw.x, h ? scw.w : scw.y};
+                const float dxl[4] = {h ? dxb.x : dxa.x, h ? dxb.y : dxa.y, h ? dxb.z : dxa.z, h ? dxb.w : dxa.w};
+#pragma unroll
+                for (int is = 0; is < 2; ++is) {
+                    uint32_t wa[4], wb[4], wh[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint8_t *pl = ql + (size_t)(rblk[j] + sb) * 128 + 64 * h + 16 * is + 4 * tg;
+                        wa[j] = ldg4(pl), wb[j] = ldg4(pl + 32);
+                        wh[j] = ldg4(qh + (size_t)(rblk[j] + sb) * 64 + 32 * h + 16 * is + 4 * tg);
+                    }
+                    auto column = [&](auto cc) {
+                        constexpr int c = decltype(cc)::value;
+                        constexpr int bx = c;
+                        const int si = is + 2 * c;  // scale byte within the half
+                        const int koff = sb * 256 + 128 * h + 32 * c + 16 * is;
+                        uint32_t b[NT], an[4];
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) b[t] = ldg4(brow[t] + koff);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) an[j] = q6_codes<c>(wa[j], wb[j], wh[j]);
+                        const float dsc = d * (float)(int)(int8_t)((scws[si >> 2] >> (8 * (si & 3))) & 0xFF);
+                        float ws[2][2];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            ws[j >> 1][j & 1] = __shfl_sync(0xffffffffu, dsc, (j >> 1) * 16 + g + (j & 1) * 8);
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) {
+                            const float dx0 = __shfl_sync(0xffffffffu, dxl[bx], 8 * t + 2 * tg);
+                            const float dx1 = __shfl_sync(0xffffffffu, dxl[bx], 8 * t + 2 * tg + 1);
+#pragma unroll
+                            for (int mt = 0; mt < 2; ++mt) {
+                                int c4[4];
+                                mma_s8_k16(c4, an[2 * mt], an[2 * mt + 1], b[t]);
+                                acc[mt][t][0] = fmaf((float)c4[0], ws[mt][0] * dx0, acc[mt][t][0]);
+                                acc[mt][t][1] = fmaf((float)c4[1], ws[mt][0] * dx1, acc[mt][t][1]);
+                                acc[mt][t][2] = fmaf((float)c4[2], ws[mt][1] * dx0, acc[mt][t][2]);
+                                acc[mt][t][3] = fmaf((float)c4[3], ws[mt][1] * dx1, acc[mt][t][3]);
+                            }
+                        }
+                    };
+                    column(std::integral_constant<int, 0>{});
+                    column(std::integral_constant<int, 1>{});
+                    column(std::integral_constant<int, 2>{});
+                    column(std::integral_constant<int, 3>{});
+                }
+            }
+        }
+        reduce_and_store<NT, NW>(red, acc, out, N, M, r0, t0);
+    }
+}
+
 }  // namespace
 
 bool smc_mma_supported(const smc_weight *w, int M)
@@ -241,6 +364,7 @@ bool smc_mma_supported(const smc_weight *w, int M)
     if (!w->fast || M < 2) return false;
     if (w->dtype == SMC_Q8_0) return w->K % 128 == 0 && w->q8_qs != nullptr;
     if (w->dtype == SMC_Q4_K) return w->K % 256 == 0 && w->d_raw != nullptr;
+    if (w->dtype == SMC_Q6_K) return w->K % 256 == 0 && w->q6_ql != nullptr;
     return false;
 }
 
@@ -256,6 +380,25 @@ int smc_launch_gemv_mma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, f
                            (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
         else smc_launch_dep(ctx->use_pdl, gemv_mma_q8_0_kernel<4>, grid, dim3(256), 0, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
                            (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
+    } else if (w->dtype == SMC_Q6_K) {
+        // the warp count follows from K alone, so a row's bits depend neither on the batch nor on how the rows are
+        // split across GPUs; long rows are where matrices of few rows (FFN down) need the extra warps per SM
+        const bool wide = K >= 8192;
+        auto go = [&](auto kernel, int nw) {
+            const size_t smem = (size_t)nw * 32 * 33 * sizeof(float);
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            smc_launch_dep(ctx->use_pdl, kernel, grid, dim3(nw * 32), smem, s, (const uint8_t *)w->q6_ql, (const uint8_t *)w->q6_qh,
+                           (const int8_t *)w->q6_sc, (const __half *)w->q6_d, (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
+        };
+        if (wide) {
+            if (nt == 1) go(gemv_mma_q6_K_kernel<1, 16>, 16);
+            else if (nt == 2) go(gemv_mma_q6_K_kernel<2, 16>, 16);
+            else go(gemv_mma_q6_K_kernel<4, 16>, 16);
+        } else {
+            if (nt == 1) go(gemv_mma_q6_K_kernel<1, 8>, 8);
+            else if (nt == 2) go(gemv_mma_q6_K_kernel<2, 8>, 8);
+            else go(gemv_mma_q6_K_kernel<4, 8>, 8);
+        }
     } else {
         if (nt == 1) smc_launch_dep(ctx->use_pdl, gemv_mma_q4_K_kernel<1>, grid, dim3(256), 0, s, (const uint8_t *)w->d_raw, (const int8_t *)a->q,
                            (const float *)a->d, (const float *)a->sd, out, N, K, M);

@@ -1,9 +1,10 @@
 """Small driver for timing / profiling one decode GEMV shape over a few distinct weight matrices.
 
-    python -m sharpmind_b200.profile_gemv {q4k|q6k|q8|lmhead|q4k70} [M] [q8|q8f|f32]
+    python -m sharpmind_b200.profile_gemv {q4k|q6k|q8|lmhead|q4k70|wo|q6k70|wo70} [M] [q8|q8f|f32]
 
 q4k = Llama-3-8B gate||up 28672x4096 Q4_K, q6k = down 4096x14336 Q6_K, q8 = Qwen3-0.6B gate||up 6144x1024 Q8_0,
-lmhead = 151936x1024 Q8_0, q4k70 = Llama-3-70B gate||up 57344x8192 Q4_K.  Modes: q8 = activations quantised by a
+lmhead = 151936x1024 Q8_0, q4k70 = Llama-3-70B gate||up 57344x8192 Q4_K, wo = 8B attention output 4096x4096 Q4_K,
+q6k70 = 70B down 8192x28672 Q6_K, wo70 = 70B attention output 8192x8192 Q4_K.  Modes: q8 = activations quantised by a
 separate launch, q8f = smc_qmatmul_dev(SMC_ACT_Q8) as callers use it (one row is quantised inside the kernel),
 f32 = fp32 activations.  The matrices (more than the 126 MB L2 in total) are cycled inside a CUDA graph and
 timed with CUDA events; under `ncu -k regex:gemv_` the same launches are what gets captured.
@@ -15,7 +16,8 @@ import torch
 from sharpmind_b200 import ops
 
 SHAPES = {"q4k": (12, 28672, 4096, 5), "q6k": (14, 4096, 14336, 5), "q8": (8, 6144, 1024, 40),
-          "lmhead": (8, 151936, 1024, 3), "q4k70": (12, 57344, 8192, 3)}
+          "lmhead": (8, 151936, 1024, 3), "q4k70": (12, 57344, 8192, 3), "wo": (12, 4096, 4096, 20),
+          "q6k70": (14, 8192, 28672, 2), "wo70": (12, 8192, 8192, 5)}
 BLOCK = {8: (32, 34), 12: (256, 144), 14: (256, 210)}
 
 

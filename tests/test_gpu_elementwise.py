@@ -249,7 +249,7 @@ def test_argmax_first_maximum_over_chunks(dev):
     assert dev.argmax(small).cpu().numpy().tolist() == small.cpu().numpy().argmax(axis=1).tolist()
 
 
-@pytest.mark.parametrize("dtype,n,k", [(Q8_0, 1024, 2048), (Q8_0, 256, 3072), (Q4_K, 512, 2048)])
+@pytest.mark.parametrize("dtype,n,k", [(Q8_0, 1024, 2048), (Q8_0, 256, 3072), (Q4_K, 512, 2048), (Q6_K, 600, 8192)])
 def test_fused_one_row_matmuls(oracle, cuda, dev, dtype, n, k):
     """SiLU-gate and residual add + RMSNorm folded into the staging of a one-row matmul, against the separate kernels."""
     import ctypes as C

@@ -98,6 +98,41 @@ def test_results_do_not_depend_on_batch_size(oracle, cuda, dev):
         cuda.release(w)
 
 
+# One row against few long rows: row counts near the number of resident warps (some warps take one row, some two),
+# rows of many steps, and row counts that the warps do not divide.
+LONG_ROW_SHAPES = [
+    (Q4_K, 4096, 4096),    # attention output of an 8B decoder
+    (Q6_K, 4096, 14336),   # FFN down of an 8B decoder
+    (Q4_K, 400, 16384), (Q8_0, 400, 8192),
+    (Q8_0, 1500, 2048), (Q6_K, 1001, 6144),
+]
+
+
+@pytest.mark.parametrize("dtype,n,k", LONG_ROW_SHAPES)
+def test_one_row_long_rows_against_oracle(oracle, cuda, dev, dtype, n, k):
+    from sharpmind_b200.ops import Mode
+
+    raw = make_weight(oracle, dtype, n, k, f"team{dtype}_{n}_{k}")
+    x = synth.normal("gpu", f"teamx{dtype}_{n}_{k}", (1, k))
+    w = cuda.register(raw, dtype, n, k)
+    try:
+        xq = oracle.quantize_rows_q8_0(x, 1, k)
+        xhat = oracle.dequantize(Q8_0, xq[0], k)[None, :]
+        want = oracle.qmatmul(dtype, xhat, raw, 1, k, n)
+        bound = row_norm_bound(oracle, dtype, raw, n, k, xhat)
+        got = dev.qmatmul(to_dev(x), w, Mode.ACT_Q8).cpu().numpy()
+        assert np.all(np.abs(got.astype(np.float64) - want) <= bound), np.max(np.abs(got - want) / bound)
+        # the same row inside a two-row call runs the tensor-core kernel: equal to rounding, not to the bit
+        two = dev.qmatmul(to_dev(np.concatenate([x, x])), w, Mode.ACT_Q8).cpu().numpy()
+        assert np.all(np.abs(two[0].astype(np.float64) - got[0]) <= 2 * bound[0])
+        # repeatable
+        again = dev.qmatmul(to_dev(x), w, Mode.ACT_Q8).cpu().numpy()
+        assert np.array_equal(bits(again), bits(got))
+    finally:
+        cuda.release(w)
+    assert cuda.device_status() == 0
+
+
 @pytest.mark.parametrize("k", [8, 15, 20, 32, 33, 40, 63, 64, 96, 137, 896])
 def test_q8_0_block_tails_with_poisoned_padding(oracle, cuda, dev, k):
     # Q8BlockTailTests.cs:25-97: partial last blocks; anything read past K would pick up 1e6
