@@ -603,8 +603,13 @@ def run_ours(args):
                     "tokens_per_s_batch1": rows[0]["tokens_per_s_graph"], "ms_per_step_batch1": rows[0]["graph_ms_per_step"],
                     "tokens_per_s_batch32": rows[1]["tokens_per_s_graph"], "ms_per_step_batch32": rows[1]["graph_ms_per_step"],
                     "GBps_batch1": rows[0]["GBps_graph"], "GBps_batch32": rows[1]["GBps_graph"]}
+                from sharpmind_b200.profile_decode import time_prompt
+
+                pr = time_prompt(ctx, dev, dict(synth.QWEN3_0_6B), 2048, 512, "q8", 2)
+                result["decode"]["prompt_pass"] = {"what": "ForwardLastLogits over a 2048-token seeded prompt in chunks of 512, one sequence",
+                                                   "ms": pr["ms"], "tokens_per_s": pr["tokens_per_s"]}
             except Exception as exc:
-                result["decode"] = {"error": str(exc)}
+                result.setdefault("decode", {})["error"] = str(exc)
             # ---- CPU baseline on the host cores
             try:
                 result["cpu_baseline"], _ = cpu_port_time(args.workload, M, args.cpu_seconds)

@@ -243,6 +243,17 @@ SMC_API int smc_model_kv_load(smc_ctx *ctx, smc_model *m, const float *d_k, cons
 SMC_API int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, int pos, int mode,
                             float *d_logits, int *d_argmax, void *stream);
 
+/* Transformer.ForwardLastLogits with seqLen > 1 (prompt processing; SharpMind.Model/Transformer.cs, block order
+ * UnhookedTransformerBlock.cs:12-47, causal attention AttentionKernels.cs:315-475 with queryBase = kvLen - seqLen):
+ * `seqLen` consecutive tokens of ONE sequence (cache slot `seq`) at positions pos .. pos + seqLen - 1.  Their K and
+ * V are appended to the cache, every token attends causally to positions 0 .. its own, and d_logits [vocab] /
+ * d_argmax [1] receive the LAST token's logits and greedy pick.  Prompts longer than a caller wants to hold in
+ * scratch are fed in chunks (pos advancing); the first call of a longer chunk grows the activation scratch, so
+ * make it outside stream capture.  Needs the joined Q/K/V path (one weight format per layer, headDim 64 or 128);
+ * SMC_E_UNSUPPORTED otherwise, SMC_E_RANGE past the cache (KVCache.cs:89-91). */
+SMC_API int smc_forward_last_logits(smc_ctx *ctx, smc_model *model, const int *d_tokens, int seqLen, int seq, int pos,
+                                    int mode, float *d_logits, int *d_argmax, void *stream);
+
 /* One activation row whose elementwise producer rides in the matmul's staging (SMC_ACT_Q8 arithmetic, weights that
  * the one-row bulk-copy kernel takes: registered with SMC_W_REPACK, K % 1024 == 0 for Q8_0 / K % 2048 == 0 for the
  * K-quants, K <= 8192; SMC_E_UNSUPPORTED otherwise):

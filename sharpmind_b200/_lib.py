@@ -76,6 +76,7 @@ SIGNATURES = {
     "smc_gather_exchange_dev": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "smc_gather_destroy": (c_int, [c_void_p, c_void_p]),
     "smc_decode_step": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "smc_forward_last_logits": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "smc_kv_append_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                   c_int, c_void_p]),
 }

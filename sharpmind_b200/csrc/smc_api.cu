@@ -65,6 +65,18 @@ int h2d(smc_ctx *ctx, void *dst, const void *src, size_t bytes)
     return SMC_OK;
 }
 
+// Host -> device without the wait, for a call whose next use of the bounce buffer is the result copy queued behind
+// its own kernel on the same stream: `pinned_bytes` (>= bytes) is reserved up front so that the buffer is not
+// reallocated while this copy is in flight.
+int h2d_queued(smc_ctx *ctx, void *dst, const void *src, size_t bytes, size_t pinned_bytes)
+{
+    int rc = ensure_pinned(ctx, pinned_bytes > bytes ? pinned_bytes : bytes);
+    if (rc) return rc;
+    memcpy(ctx->h_pin, src, bytes);
+    SMC_CUDA(ctx, cudaMemcpyAsync(dst, ctx->h_pin, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return SMC_OK;
+}
+
 int d2h(smc_ctx *ctx, void *dst, const void *src, size_t bytes)
 {
     int rc = ensure_pinned(ctx, bytes);
@@ -562,8 +574,12 @@ int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, flo
     size_t in_bytes = (size_t)M * K * sizeof(float), out_bytes = (size_t)M * N * sizeof(float);
     if ((rc = ensure_dev(ctx, &ctx->d_stage_in, &ctx->stage_in_cap, in_bytes))) return rc;
     if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, out_bytes))) return rc;
-    if ((rc = h2d(ctx, ctx->d_stage_in, input, in_bytes))) return rc;
-    if ((rc = qmatmul_impl(ctx, ctx->d_stage_in, w, ctx->d_stage_out, M, mode, ctx->stream, true))) return rc;
+    // one wait per call: input copy, kernels and result copy are ordered by the stream
+    if ((rc = h2d_queued(ctx, ctx->d_stage_in, input, in_bytes, out_bytes))) return rc;
+    if ((rc = qmatmul_impl(ctx, ctx->d_stage_in, w, ctx->d_stage_out, M, mode, ctx->stream, true))) {
+        cudaStreamSynchronize(ctx->stream);
+        return rc;
+    }
     return d2h(ctx, output, ctx->d_stage_out, out_bytes);
 }
 

@@ -275,7 +275,102 @@ int launch_split_g(smc_ctx *ctx, int G, dim3 grid, size_t smem, cudaStream_t s, 
     return SMC_OK;
 }
 
+// Causal attention of T consecutive query tokens of ONE sequence against its fp32 cache (the new tokens' K and V
+// already appended): query t sits at position pos0 + t and sees keys 0 .. pos0 + t.  One warp per query row, eight
+// rows and one head per CTA; K and V go through shared memory in tiles of 32 keys shared by the eight rows (rows
+// padded to HD + 4 floats: a lane's 16-byte reads of its own key row, and all lanes' reads of one value row, are
+// conflict free).  Lane j scores key j of the tile, the running max / sum are per warp, and lane i accumulates
+// output dims 4i .. 4i + 3 (HD = 128) or 2i, 2i + 1 (HD = 64).
+template <int HD>
+__global__ void __launch_bounds__(256) sdpa_prefill_kernel(const float *__restrict__ q, const float *__restrict__ kc,
+                                                           const float *__restrict__ vc, float *__restrict__ out, int T,
+                                                           int nh, int nkv, int pos0, int maxSeq, float scale)
+{
+    constexpr int LD = HD + 4, DPL = HD / 32;
+    __shared__ __align__(16) float sk[32 * LD];
+    __shared__ __align__(16) float sv[32 * LD];
+    __shared__ __align__(16) float sq[8 * HD];
+    smc_grid_dep_sync();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    const int t0 = blockIdx.x * 8, t = t0 + warp;
+    const bool live = t < T;
+    const int my_len = live ? pos0 + t + 1 : 0;
+    const int cta_len = pos0 + min(T, t0 + 8);
+    const float *kbase = kc + (size_t)kvh * maxSeq * HD, *vbase = vc + (size_t)kvh * maxSeq * HD;
+    if (live)
+        for (int d = lane; d < HD; d += 32) sq[warp * HD + d] = q[((size_t)t * nh + h) * HD + d];
+    float o[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    for (int start = 0; start < cta_len; start += 32) {
+        __syncthreads();  // the previous tile has been consumed (and sq is written before the first use)
+        for (int e = threadIdx.x; e < 32 * (HD / 4); e += 256) {
+            const int r = e / (HD / 4), c = e % (HD / 4);
+            float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+            if (start + r < cta_len) {
+                kk = *reinterpret_cast<const float4 *>(kbase + (size_t)(start + r) * HD + 4 * c);
+                vv = *reinterpret_cast<const float4 *>(vbase + (size_t)(start + r) * HD + 4 * c);
+            }
+            *reinterpret_cast<float4 *>(sk + r * LD + 4 * c) = kk;
+            *reinterpret_cast<float4 *>(sv + r * LD + 4 * c) = vv;
+        }
+        __syncthreads();
+        if (start >= my_len) continue;  // warp uniform: this row's causal bound lies before the tile
+        float dot = 0.f;
+#pragma unroll 8
+        for (int c = 0; c < HD / 4; ++c) {
+            const float4 a = *reinterpret_cast<const float4 *>(sq + warp * HD + 4 * c);
+            const float4 b = *reinterpret_cast<const float4 *>(sk + lane * LD + 4 * c);
+            dot = fmaf(a.x, b.x, dot), dot = fmaf(a.y, b.y, dot), dot = fmaf(a.z, b.z, dot), dot = fmaf(a.w, b.w, dot);
+        }
+        const bool valid = start + lane < my_len;
+        const float sc = valid ? dot * scale : -INFINITY;
+        float tmax = sc;
+#pragma unroll
+        for (int x = 16; x > 0; x >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, x));
+        const float nm = fmaxf(m, tmax);  // finite: key `start` is inside the bound
+        const float p = valid ? expf(sc - nm) : 0.f;
+        float ps = p;
+#pragma unroll
+        for (int x = 16; x > 0; x >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, x);
+        const float corr = expf(m - nm);  // exp(-inf) = 0 on the first tile
+        l = fmaf(l, corr, ps);
+        m = nm;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o[i] *= corr;
+        for (int j = 0; j < 32; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            if (DPL == 4) {
+                const float4 vv = *reinterpret_cast<const float4 *>(sv + j * LD + 4 * lane);
+                o[0] = fmaf(pj, vv.x, o[0]), o[1] = fmaf(pj, vv.y, o[1]), o[2] = fmaf(pj, vv.z, o[2]), o[3] = fmaf(pj, vv.w, o[3]);
+            } else {
+                const float2 vv = *reinterpret_cast<const float2 *>(sv + j * LD + 2 * lane);
+                o[0] = fmaf(pj, vv.x, o[0]), o[1] = fmaf(pj, vv.y, o[1]);
+            }
+        }
+    }
+    if (live) {
+        float *dst = out + ((size_t)t * nh + h) * HD + DPL * lane;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) dst[i] = l > 0.f ? o[i] / l : 0.f;
+    }
+}
+
 }  // namespace
+
+int smc_launch_sdpa_prefill(smc_ctx *ctx, const float *q, const float *kc, const float *vc, float *out, int T, int nh, int nkv,
+                            int hd, int pos0, int maxSeq, float scale, cudaStream_t s)
+{
+    if (hd != 64 && hd != 128) return smc_fail(ctx, SMC_E_UNSUPPORTED, "prefill attention needs headDim 64 or 128, got %d", hd);
+    if (nh % nkv) return smc_fail(ctx, SMC_E_INVALID, "prefill attention: heads %d not a multiple of KV heads %d", nh, nkv);
+    const dim3 grid((T + 7) / 8, nh);
+    if (hd == 128) smc_launch_dep(ctx->use_pdl, sdpa_prefill_kernel<128>, grid, dim3(256), 0, s, q, kc, vc, out, T, nh, nkv, pos0, maxSeq, scale);
+    else smc_launch_dep(ctx->use_pdl, sdpa_prefill_kernel<64>, grid, dim3(256), 0, s, q, kc, vc, out, T, nh, nkv, pos0, maxSeq, scale);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
 
 int smc_launch_sdpa_tile(smc_ctx *ctx, const float *q, const float *k, const float *v, float *o, int seqLen, int kvLen,
                          int hd, float scale, int causal, int qStride, int oStride, float alibi, cudaStream_t s)

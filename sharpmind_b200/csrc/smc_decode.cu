@@ -17,6 +17,7 @@
 struct smc_model {
     smc_model_desc d{};
     int max_batch = 0;
+    int rows = 0;  // rows the activation scratch holds: max_batch, or the longest prompt chunk seen so far
     std::vector<const smc_weight *> wq, wk, wv, wo, wgu, wdown;
     std::vector<smc_weight *> wqkv;  // rows of Wq, Wk, Wv in one matrix (owned), when the three could be joined
     float *qkv = nullptr;            // [batch][qDim + 2 kvDim]
@@ -41,6 +42,35 @@ void free_model(smc_ctx *ctx, smc_model *m)
     smc_q8act_free(m->qa);
     smc_q8act_free(m->qb);
     delete m;
+}
+
+// (Re)allocates the per-row activation scratch for `rows` rows; the caches and the tables are not touched.
+int alloc_rows(smc_ctx *ctx, smc_model *m, int rows)
+{
+    const smc_model_desc &d = m->d;
+    const size_t H = d.hidden, qDim = (size_t)d.n_heads * d.head_dim, kvDim = (size_t)d.n_kv_heads * d.head_dim, F = d.ffn;
+    float **bufs[] = {&m->x, &m->xn, &m->q, &m->k, &m->v, &m->att, &m->tmp, &m->gu, &m->act, &m->qkv};
+    const size_t widths[] = {H, H, qDim, kvDim, kvDim, qDim, H, 2 * F, F, qDim + 2 * kvDim};
+    if (m->rows) cudaDeviceSynchronize();  // the buffers being replaced may be in use
+    for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) {
+        cudaFree(*bufs[i]);
+        *bufs[i] = nullptr;
+    }
+    smc_q8act_free(m->qa);
+    smc_q8act_free(m->qb);
+    m->qa = m->qb = nullptr;
+    m->rows = 0;
+    for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) {
+        cudaError_t e = cudaMalloc(bufs[i], (size_t)rows * widths[i] * sizeof(float));
+        if (e != cudaSuccess) return smc_fail(ctx, SMC_E_CUDA, "activation scratch for %d rows: %s", rows, cudaGetErrorString(e));
+    }
+    int rc = 0;
+    if (H % 32 == 0) rc = smc_q8act_alloc(ctx, rows, (int)H, &m->qa);
+    const size_t wide = qDim > F ? qDim : F;
+    if (!rc && wide % 32 == 0) rc = smc_q8act_alloc(ctx, rows, (int)wide, &m->qb);
+    if (rc) return rc;
+    m->rows = rows;
+    return SMC_OK;
 }
 
 // y[M, N] = x[M, K] W^T in the requested mode; for SMC_ACT_Q8 with several rows the quantised rows in
@@ -81,7 +111,7 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(const float *__restrict__
                                                        float *__restrict__ kc, float *__restrict__ vc,
                                                        const float *__restrict__ qnorm, const float *__restrict__ knorm,
                                                        const float *__restrict__ cosT, const float *__restrict__ sinT, int batch,
-                                                       int nh, int nkv, int pos, int maxSeq, float eps, int neox)
+                                                       int nh, int nkv, int pos, int maxSeq, float eps, int neox, int seq0)
 {
     constexpr int HD = EPL * 32, PAIRS = HD / 2;
     smc_grid_dep_sync();
@@ -89,8 +119,11 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(const float *__restrict__
     const int slots = nh + 2 * nkv;
     const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (wid >= batch * slots) return;
-    const int b = wid / slots, slot = wid % slots;
-    const float *src = qkv + (size_t)b * slots * HD + (size_t)slot * HD;
+    const int row = wid / slots, slot = wid % slots;
+    const float *src = qkv + (size_t)row * slots * HD + (size_t)slot * HD;
+    // decode: row r is sequence r at position pos.  Prompt (seq0 >= 0): row r is position pos + r of sequence seq0.
+    const int b = seq0 >= 0 ? seq0 : row;
+    pos += seq0 >= 0 ? row : 0;
     float v[EPL];
 #pragma unroll
     for (int j = 0; j < EPL; ++j) v[j] = src[lane + 32 * j];
@@ -132,12 +165,12 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(const float *__restrict__
                               : __fsub_rn(__fmul_rn(v[j], c), __fmul_rn(other, sn));
         }
     }
-    float *dst = is_q ? q_out + ((size_t)b * nh + slot) * HD : kc + (((size_t)b * nkv + (slot - nh)) * maxSeq + pos) * HD;
+    float *dst = is_q ? q_out + ((size_t)row * nh + slot) * HD : kc + (((size_t)b * nkv + (slot - nh)) * maxSeq + pos) * HD;
 #pragma unroll
     for (int j = 0; j < EPL; ++j) dst[lane + 32 * j] = v[j];
 }
 
-int launch_qkv_post(smc_ctx *ctx, const smc_model *m, int l, float *kc, float *vc, int B, int pos, cudaStream_t s)
+int launch_qkv_post(smc_ctx *ctx, const smc_model *m, int l, float *kc, float *vc, int B, int pos, cudaStream_t s, int seq0 = -1)
 {
     const smc_model_desc &d = m->d;
     const int warps = B * (d.n_heads + 2 * d.n_kv_heads);
@@ -146,7 +179,7 @@ int launch_qkv_post(smc_ctx *ctx, const smc_model *m, int l, float *kc, float *v
 #define SMC_QKV_POST(E)                                                                                              \
     smc_launch_dep(ctx->use_pdl, qkv_post_kernel<E>, grid, dim3(256), 0, s, (const float *)m->qkv, m->q, kc, vc, qn, kn, \
                    (const float *)m->cosT, (const float *)m->sinT, B, d.n_heads, d.n_kv_heads, pos, d.max_seq, d.eps,    \
-                   d.neox)
+                   d.neox, seq0)
     switch (d.head_dim) {
     case 64: SMC_QKV_POST(2); break;
     case 128: SMC_QKV_POST(4); break;
@@ -216,9 +249,6 @@ int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, sm
         if (e == cudaSuccess) e = cudaMalloc(p, n * sizeof(float));
     };
     alloc(&m->kcache, cache), alloc(&m->vcache, cache), alloc(&m->cosT, half), alloc(&m->sinT, half);
-    alloc(&m->x, B * H), alloc(&m->xn, B * H), alloc(&m->q, B * qDim), alloc(&m->k, B * kvDim), alloc(&m->v, B * kvDim);
-    alloc(&m->att, B * qDim), alloc(&m->tmp, B * H), alloc(&m->gu, B * 2 * F), alloc(&m->act, B * F);
-    alloc(&m->qkv, B * (qDim + 2 * kvDim));
     alloc(&m->x2, (size_t)H);
     if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache * sizeof(float));
     if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache * sizeof(float));
@@ -226,10 +256,7 @@ int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, sm
         free_model(ctx, m);
         return smc_fail(ctx, SMC_E_CUDA, "model_create: allocation failed: %s", cudaGetErrorString(e));
     }
-    int rc = 0;
-    if (H % 32 == 0) rc = smc_q8act_alloc(ctx, max_batch, H, &m->qa);
-    const int wide = qDim > F ? qDim : F;
-    if (!rc && wide % 32 == 0) rc = smc_q8act_alloc(ctx, max_batch, wide, &m->qb);
+    int rc = alloc_rows(ctx, m, max_batch);
     if (rc) {
         free_model(ctx, m);
         return rc;
@@ -374,6 +401,57 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
     if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
     SMC_TRY(linear(ctx, m->xn, d.lm_head, d_logits, B, mode, reuse ? m->qa : nullptr, s));
     if (d_argmax) SMC_TRY(smc_argmax_dev(ctx, d_logits, B, d.vocab, d_argmax, s));
+    return SMC_OK;
+}
+
+int smc_forward_last_logits(smc_ctx *ctx, smc_model *m, const int *d_tokens, int seqLen, int seq, int pos, int mode,
+                            float *d_logits, int *d_argmax, void *stream)
+{
+    if (!ctx || !m || !d_tokens || !d_logits || seqLen <= 0) return smc_fail(ctx, SMC_E_INVALID, "forward_last_logits: bad arguments");
+    if (seq < 0 || seq >= m->max_batch) return smc_fail(ctx, SMC_E_RANGE, "forward_last_logits: sequence %d outside [0, %d)", seq, m->max_batch);
+    const smc_model_desc &d = m->d;
+    if (pos < 0 || (long long)pos + seqLen > d.max_seq)  // KVCache.Update throws on overflow (KVCache.cs:89-91)
+        return smc_fail(ctx, SMC_E_RANGE, "KVCache overflow: position %d + seqLen %d exceeds capacity %d", pos, seqLen, d.max_seq);
+    if (mode != SMC_ACT_F32 && mode != SMC_ACT_Q8 && mode != SMC_REF_ORDER)
+        return smc_fail(ctx, SMC_E_INVALID, "forward_last_logits: unknown mode %d", mode);
+    if (d.head_dim != 64 && d.head_dim != 128)
+        return smc_fail(ctx, SMC_E_UNSUPPORTED, "forward_last_logits: headDim %d (64 and 128 are built)", d.head_dim);
+    for (int l = 0; l < d.n_layers; ++l)
+        if (!m->wqkv[l] || (mode == SMC_REF_ORDER && !m->wqkv[l]->d_raw))
+            return smc_fail(ctx, SMC_E_UNSUPPORTED, "forward_last_logits: layer %d has no joined Q/K/V matrix usable in mode %d", l, mode);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int T = seqLen, H = d.hidden, nh = d.n_heads, nkv = d.n_kv_heads, hd = d.head_dim, F = d.ffn, qDim = nh * hd;
+    int rc;
+    if (T > m->rows) {  // first prompt chunk of this length: allocates (keep it outside stream capture)
+        std::lock_guard<std::mutex> lock(ctx->mu_scratch);
+        if ((rc = alloc_rows(ctx, m, T > m->max_batch ? T : m->max_batch))) return rc;
+    }
+    const float scale = 1.0f / sqrtf((float)hd);
+    const size_t layer_stride = (size_t)m->max_batch * nkv * d.max_seq * hd, seq_off = (size_t)seq * nkv * d.max_seq * hd;
+    const bool reuse = mode == SMC_ACT_Q8 && T > 1 && m->qa && m->qb;
+    SMC_TRY(smc_embed_q8_0_dev(ctx, d.lm_head, d_tokens, T, m->x, s));
+    SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm1[0], m->xn, T, H, d.eps, s));
+    for (int l = 0; l < d.n_layers; ++l) {
+        float *kc = m->kcache + (size_t)l * layer_stride, *vc = m->vcache + (size_t)l * layer_stride;
+        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, T, H, m->qa, s));
+        SMC_TRY(linear(ctx, m->xn, m->wqkv[l], m->qkv, T, mode, reuse ? m->qa : nullptr, s));
+        // row t: per-head norm, rotation by position pos + t, K and V appended to sequence `seq`
+        SMC_TRY(launch_qkv_post(ctx, m, l, kc, vc, T, pos, s, seq));
+        SMC_TRY(smc_launch_sdpa_prefill(ctx, m->q, kc + seq_off, vc + seq_off, m->att, T, nh, nkv, hd, pos, d.max_seq, scale, s));
+        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->att, T, qDim, m->qb, s));
+        SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s));
+        SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, T, H, d.eps, s));
+        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, T, H, m->qa, s));
+        SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, T, mode, reuse ? m->qa : nullptr, s));
+        SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, T, F, 2 * F, s));
+        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->act, T, F, m->qb, s));
+        SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s));
+        const float *next_norm = l + 1 < d.n_layers ? m->norm1[l + 1] : d.final_norm;
+        SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, T, H, d.eps, s));
+    }
+    // only the last position's logits are formed (Transformer.ForwardLastLogits)
+    SMC_TRY(smc_qmatmul_dev(ctx, m->xn + (size_t)(T - 1) * H, d.lm_head, d_logits, 1, mode, s));
+    if (d_argmax) SMC_TRY(smc_argmax_dev(ctx, d_logits, 1, d.vocab, d_argmax, s));
 #undef SMC_TRY
     return SMC_OK;
 }

@@ -102,6 +102,23 @@ class Decoder:
                                                     C.c_void_p(t.cuda.current_stream().cuda_stream)))
         return logits, argmax
 
+    def forward_last_logits(self, tokens, pos: int = 0, seq: int = 0, mode: int = ops.Mode.ACT_Q8, chunk: int = 512):
+        """Prompt processing (Transformer.ForwardLastLogits with seqLen > 1): tokens is CUDA int32 [seqLen], one
+        sequence, placed at positions pos .. pos + seqLen - 1 of cache slot `seq`, fed in chunks of `chunk` tokens.
+        Returns (logits [vocab] of the last token, its greedy pick [1])."""
+        t = self.torch
+        n = tokens.numel()
+        logits = t.empty(self.cfg["vocab"], dtype=t.float32, device="cuda")
+        argmax = t.empty(1, dtype=t.int32, device="cuda")
+        if n == 0:
+            raise ValueError("forward_last_logits: empty prompt")
+        for start in range(0, n, chunk):
+            part = tokens[start:start + chunk].contiguous()
+            self.ctx.check(self.ctx.lib.smc_forward_last_logits(self.ctx.h, self.h, part.data_ptr(), part.numel(), seq,
+                                                                pos + start, int(mode), logits.data_ptr(), argmax.data_ptr(),
+                                                                C.c_void_p(t.cuda.current_stream().cuda_stream)))
+        return logits, argmax
+
     def close(self):
         if self.h:
             self.ctx.lib.smc_model_destroy(self.ctx.h, self.h)

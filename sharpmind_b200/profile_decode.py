@@ -119,8 +119,35 @@ def time_decode(ctx, dev, cfg: dict, batches, ctx_len: int, steps: int, modes=("
     return rows
 
 
+def time_prompt(ctx, dev, cfg: dict, n_tokens: int, chunk: int = 512, mode: str = "q8", reps: int = 3) -> dict:
+    """Times ForwardLastLogits over a seeded random prompt of `n_tokens` (one sequence, chunks of `chunk` tokens)."""
+    import torch
+
+    w = device_weights(dev, cfg)
+    dec = Decoder(ctx, cfg, w, max_batch=1)
+    del w
+    g = torch.Generator(device="cuda")
+    g.manual_seed(7)
+    tok = torch.randint(0, cfg["vocab"], (n_tokens,), generator=g, device="cuda", dtype=torch.int32)
+    dec.forward_last_logits(tok, 0, 0, MODES[mode], chunk)  # grows the scratch, warms up
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        dec.forward_last_logits(tok, 0, 0, MODES[mode], chunk)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    row = {"prompt_tokens": n_tokens, "chunk": chunk, "mode": mode, "layers": cfg["n_layers"], "ms": round(ms, 3),
+           "tokens_per_s": round(n_tokens / ms * 1e3, 1), "device_status": ctx.device_status()}
+    dec.close()
+    return row
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--prompt", type=int, default=0, help="time a prompt pass of this many tokens instead of decode steps")
+    ap.add_argument("--chunk", type=int, default=512)
     ap.add_argument("--batches", default="1,8,32")
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=64)
@@ -133,6 +160,11 @@ def main():
         cfg["n_layers"] = a.layers
     ctx = ops.CudaContext(0)
     dev = ops.DeviceOps(ctx)
+    if a.prompt:
+        for name in a.modes.split(","):
+            print(json.dumps(time_prompt(ctx, dev, cfg, a.prompt, a.chunk, name)), flush=True)
+        ctx.close()
+        return
     for row in time_decode(ctx, dev, cfg, [int(b) for b in a.batches.split(",")], a.ctx, a.steps,
                            tuple(a.modes.split(",")), a.once):
         print(json.dumps(row), flush=True)

@@ -166,3 +166,54 @@ def test_decode_one_sequence_fused_path(oracle, cuda):
     one.close()
     two.close()
     assert cuda.device_status() == 0
+
+
+@pytest.mark.parametrize("cfg,name", [(SMALL, "dec_small"), (LLAMA_LIKE, "dec_llama")])
+@pytest.mark.parametrize("mode", [ops.Mode.ACT_F32, ops.Mode.REF_ORDER])
+def test_prompt_in_one_pass_matches_oracle_stepping(oracle, cuda, cfg, name, mode):
+    """ForwardLastLogits over a whole prompt (all tokens in one pass, causal attention among them) gives the logits
+    the oracle reaches token by token, leaves a cache that later decode steps continue from, and chunked feeding
+    (a second sequence slot, chunks of 5) agrees with the one-pass result."""
+    import torch
+
+    n_prompt, n_more = 19, 4
+    w = _weights(oracle, cfg, name)
+    ref = oracle.Decoder(cfg, w, 1)
+    toks = synth.token_ids(name, "prompt_pass", (n_prompt + n_more,), cfg["vocab"])
+    for p in range(n_prompt):
+        want = ref.step(toks[p:p + 1], p)
+    dec = Decoder(cuda, cfg, w, max_batch=2, keep_raw=(mode == ops.Mode.REF_ORDER))
+    logits, pick = dec.forward_last_logits(to_dev(toks[:n_prompt]), 0, 0, mode)
+    got = logits.cpu().numpy()
+    scale = np.abs(want).max()
+    assert np.max(np.abs(got - want[0])) <= 1e-4 * scale, float(np.max(np.abs(got - want[0])) / scale)
+    assert int(pick.cpu()[0]) == int(got.argmax())
+    chunked, _ = dec.forward_last_logits(to_dev(toks[:n_prompt]), 0, 1, mode, chunk=5)
+    assert np.max(np.abs(chunked.cpu().numpy() - got)) <= 1e-5 * scale
+    # decode continues from the cache the prompt pass wrote (both slots hold the same sequence)
+    for p in range(n_prompt, n_prompt + n_more):
+        want = ref.step(toks[p:p + 1], p)
+        pair = to_dev(np.repeat(toks[p:p + 1], 2))
+        out, _ = dec.step(pair, p, mode)
+        out = out.cpu().numpy()
+        for b in range(2):
+            assert np.max(np.abs(out[b] - want[0])) <= 1e-4 * np.abs(want).max()
+    dec.close()
+    assert cuda.device_status() == 0
+
+
+def test_prompt_pass_quantised_activations_and_guards(oracle, cuda):
+    cfg, name = WIDE, "dec_wide"
+    w = _weights(oracle, cfg, name)
+    ref = oracle.Decoder(cfg, w, 1)
+    toks = synth.token_ids(name, "prompt_q8", (12,), cfg["vocab"])
+    for p in range(12):
+        want = ref.step(toks[p:p + 1], p)
+    dec = Decoder(cuda, cfg, w, max_batch=1)
+    got = dec.forward_last_logits(to_dev(toks), 0, 0, ops.Mode.ACT_Q8)[0].cpu().numpy()
+    assert np.max(np.abs(got - want[0])) <= 0.05 * np.abs(want).max()
+    with pytest.raises(ops.SharpMindCudaError):
+        dec.forward_last_logits(to_dev(toks), cfg["max_seq"] - 5, 0)      # runs past the cache
+    with pytest.raises(ops.SharpMindCudaError):
+        dec.forward_last_logits(to_dev(toks), 0, 1)                       # slot 1 of a one-sequence model
+    dec.close()
