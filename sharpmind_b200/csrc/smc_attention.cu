@@ -276,34 +276,41 @@ int launch_split_g(smc_ctx *ctx, int G, dim3 grid, size_t smem, cudaStream_t s, 
 }
 
 // Causal attention of T consecutive query tokens of ONE sequence against its fp32 cache (the new tokens' K and V
-// already appended): query t sits at position pos0 + t and sees keys 0 .. pos0 + t.  One warp per query row, eight
-// rows and one head per CTA; K and V go through shared memory in tiles of 32 keys shared by the eight rows (rows
-// padded to HD + 4 floats: a lane's 16-byte reads of its own key row, and all lanes' reads of one value row, are
-// conflict free).  Lane j scores key j of the tile, the running max / sum are per warp, and lane i accumulates
-// output dims 4i .. 4i + 3 (HD = 128) or 2i, 2i + 1 (HD = 64).
-template <int HD>
+// already appended): query t sits at position pos0 + t and sees keys 0 .. pos0 + t.  A CTA takes one head and
+// 8 * R consecutive query rows, R per warp; K and V go through shared memory in tiles of 32 keys shared by all of
+// them (rows padded to HD + 4 floats: a lane's 16-byte reads of its own key row, and all lanes' reads of one value
+// row, are conflict free).  Lane j scores key j of the tile for each of the warp's R rows from one read of the key
+// (the R query rows are broadcast reads), the running max / sum are per row, and lane i accumulates output dims
+// 4i .. 4i + 3 (HD = 128) or 2i, 2i + 1 (HD = 64) of every row from one read of the value row.
+template <int HD, int R>
 __global__ void __launch_bounds__(256) sdpa_prefill_kernel(const float *__restrict__ q, const float *__restrict__ kc,
                                                            const float *__restrict__ vc, float *__restrict__ out, int T,
                                                            int nh, int nkv, int pos0, int maxSeq, float scale)
 {
-    constexpr int LD = HD + 4, DPL = HD / 32;
-    __shared__ __align__(16) float sk[32 * LD];
-    __shared__ __align__(16) float sv[32 * LD];
-    __shared__ __align__(16) float sq[8 * HD];
+    constexpr int LD = HD + 4, DPL = HD / 32, ROWS = 8 * R;
+    extern __shared__ __align__(16) float sm_att[];
+    float *sk = sm_att, *sv = sk + 32 * LD, *sq = sv + 32 * LD;  // sq [ROWS][HD]
     smc_grid_dep_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y, kvh = h / (nh / nkv);
-    const int t0 = blockIdx.x * 8, t = t0 + warp;
-    const bool live = t < T;
-    const int my_len = live ? pos0 + t + 1 : 0;
-    const int cta_len = pos0 + min(T, t0 + 8);
-    const float *kbase = kc + (size_t)kvh * maxSeq * HD, *vbase = vc + (size_t)kvh * maxSeq * HD;
-    if (live)
-        for (int d = lane; d < HD; d += 32) sq[warp * HD + d] = q[((size_t)t * nh + h) * HD + d];
-    float o[DPL];
+    const int t0 = blockIdx.x * ROWS, tw = t0 + warp * R;  // first row of the CTA, of this warp
+    const int cta_len = pos0 + min(T, t0 + ROWS);
+    int len[R];  // keys row r sees; 0 for rows past the chunk
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    for (int r = 0; r < R; ++r) len[r] = tw + r < T ? pos0 + tw + r + 1 : 0;
+    const int warp_len = tw < T ? pos0 + min(T, tw + R) : 0;
+    const float *kbase = kc + (size_t)kvh * maxSeq * HD, *vbase = vc + (size_t)kvh * maxSeq * HD;
+    for (int e = threadIdx.x; e < ROWS * HD; e += 256) {
+        const int r = e / HD, d = e % HD;
+        sq[e] = t0 + r < T ? q[((size_t)(t0 + r) * nh + h) * HD + d] : 0.f;
+    }
+    float o[R][DPL], m[R], l[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        m[r] = -INFINITY, l[r] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o[r][i] = 0.f;
+    }
     for (int start = 0; start < cta_len; start += 32) {
         __syncthreads();  // the previous tile has been consumed (and sq is written before the first use)
         for (int e = threadIdx.x; e < 32 * (HD / 4); e += 256) {
@@ -317,44 +324,65 @@ __global__ void __launch_bounds__(256) sdpa_prefill_kernel(const float *__restri
             *reinterpret_cast<float4 *>(sv + r * LD + 4 * c) = vv;
         }
         __syncthreads();
-        if (start >= my_len) continue;  // warp uniform: this row's causal bound lies before the tile
-        float dot = 0.f;
-#pragma unroll 8
+        if (start >= warp_len) continue;  // warp uniform: every row's causal bound lies before the tile
+        float dot[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) dot[r] = 0.f;
+#pragma unroll 4
         for (int c = 0; c < HD / 4; ++c) {
-            const float4 a = *reinterpret_cast<const float4 *>(sq + warp * HD + 4 * c);
             const float4 b = *reinterpret_cast<const float4 *>(sk + lane * LD + 4 * c);
-            dot = fmaf(a.x, b.x, dot), dot = fmaf(a.y, b.y, dot), dot = fmaf(a.z, b.z, dot), dot = fmaf(a.w, b.w, dot);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float4 a = *reinterpret_cast<const float4 *>(sq + (warp * R + r) * HD + 4 * c);
+                dot[r] = fmaf(a.x, b.x, dot[r]), dot[r] = fmaf(a.y, b.y, dot[r]);
+                dot[r] = fmaf(a.z, b.z, dot[r]), dot[r] = fmaf(a.w, b.w, dot[r]);
+            }
         }
-        const bool valid = start + lane < my_len;
-        const float sc = valid ? dot * scale : -INFINITY;
-        float tmax = sc;
+        float p[R];
 #pragma unroll
-        for (int x = 16; x > 0; x >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, x));
-        const float nm = fmaxf(m, tmax);  // finite: key `start` is inside the bound
-        const float p = valid ? expf(sc - nm) : 0.f;
-        float ps = p;
+        for (int r = 0; r < R; ++r) {
+            p[r] = 0.f;
+            if (start >= len[r]) continue;  // warp uniform per row
+            const bool valid = start + lane < len[r];
+            const float sc = valid ? dot[r] * scale : -INFINITY;
+            float tmax = sc;
 #pragma unroll
-        for (int x = 16; x > 0; x >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, x);
-        const float corr = expf(m - nm);  // exp(-inf) = 0 on the first tile
-        l = fmaf(l, corr, ps);
-        m = nm;
+            for (int x = 16; x > 0; x >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, x));
+            const float nm = fmaxf(m[r], tmax);  // finite: key `start` is inside the bound
+            p[r] = valid ? expf(sc - nm) : 0.f;
+            float ps = p[r];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) o[i] *= corr;
+            for (int x = 16; x > 0; x >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, x);
+            const float corr = expf(m[r] - nm);  // exp(-inf) = 0 on the first tile
+            l[r] = fmaf(l[r], corr, ps);
+            m[r] = nm;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o[r][i] *= corr;
+        }
+#pragma unroll 4
         for (int j = 0; j < 32; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, p, j);
+            float vv[4];
             if (DPL == 4) {
-                const float4 vv = *reinterpret_cast<const float4 *>(sv + j * LD + 4 * lane);
-                o[0] = fmaf(pj, vv.x, o[0]), o[1] = fmaf(pj, vv.y, o[1]), o[2] = fmaf(pj, vv.z, o[2]), o[3] = fmaf(pj, vv.w, o[3]);
+                const float4 t4 = *reinterpret_cast<const float4 *>(sv + j * LD + 4 * lane);
+                vv[0] = t4.x, vv[1] = t4.y, vv[2] = t4.z, vv[3] = t4.w;
             } else {
-                const float2 vv = *reinterpret_cast<const float2 *>(sv + j * LD + 2 * lane);
-                o[0] = fmaf(pj, vv.x, o[0]), o[1] = fmaf(pj, vv.y, o[1]);
+                const float2 t2 = *reinterpret_cast<const float2 *>(sv + j * LD + 2 * lane);
+                vv[0] = t2.x, vv[1] = t2.y, vv[2] = vv[3] = 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float pj = __shfl_sync(0xffffffffu, p[r], j);
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) o[r][i] = fmaf(pj, vv[i], o[r][i]);
             }
         }
     }
-    if (live) {
-        float *dst = out + ((size_t)t * nh + h) * HD + DPL * lane;
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) dst[i] = l > 0.f ? o[i] / l : 0.f;
+    for (int r = 0; r < R; ++r) {
+        if (tw + r >= T) continue;
+        float *dst = out + ((size_t)(tw + r) * nh + h) * HD + DPL * lane;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) dst[i] = l[r] > 0.f ? o[r][i] / l[r] : 0.f;
     }
 }
 
@@ -365,9 +393,17 @@ int smc_launch_sdpa_prefill(smc_ctx *ctx, const float *q, const float *kc, const
 {
     if (hd != 64 && hd != 128) return smc_fail(ctx, SMC_E_UNSUPPORTED, "prefill attention needs headDim 64 or 128, got %d", hd);
     if (nh % nkv) return smc_fail(ctx, SMC_E_INVALID, "prefill attention: heads %d not a multiple of KV heads %d", nh, nkv);
-    const dim3 grid((T + 7) / 8, nh);
-    if (hd == 128) smc_launch_dep(ctx->use_pdl, sdpa_prefill_kernel<128>, grid, dim3(256), 0, s, q, kc, vc, out, T, nh, nkv, pos0, maxSeq, scale);
-    else smc_launch_dep(ctx->use_pdl, sdpa_prefill_kernel<64>, grid, dim3(256), 0, s, q, kc, vc, out, T, nh, nkv, pos0, maxSeq, scale);
+    // query rows per warp: four, or two while that leaves fewer than three CTAs per SM (a CTA waits on its K/V
+    // tile loads with nothing else to do, so the SM needs other CTAs to run meanwhile)
+    auto go = [&](auto kernel, int R) {
+        const dim3 grid((T + 8 * R - 1) / (8 * R), nh);
+        const size_t smem = ((size_t)2 * 32 * (hd + 4) + (size_t)8 * R * hd) * sizeof(float);
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        smc_launch_dep(ctx->use_pdl, kernel, grid, dim3(256), smem, s, q, kc, vc, out, T, nh, nkv, pos0, maxSeq, scale);
+    };
+    const bool four = (long long)((T + 31) / 32) * nh >= 3LL * ctx->sm_count;
+    if (hd == 128) four ? go(sdpa_prefill_kernel<128, 4>, 4) : go(sdpa_prefill_kernel<128, 2>, 2);
+    else four ? go(sdpa_prefill_kernel<64, 4>, 4) : go(sdpa_prefill_kernel<64, 2>, 2);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
