@@ -853,6 +853,9 @@ typedef struct {
     const uint8_t *lm_head; /* [vocab, hidden] raw; tied models pass the embedding bytes */
     const float *embedding; /* fp32 [vocab, hidden], dequantised table */
     const float *cosT, *sinT;
+    /* formats of the down projection and of the LM head / embedding when they differ from `dtype`
+     * (GGUF files mix formats per tensor); 0 = same as `dtype` */
+    int down_dtype, head_dtype;
 } smo_model;
 
 /* Follows Transformer.ForwardLastLogits (SharpMind.Model/Transformer.cs:417-463),
@@ -918,11 +921,11 @@ SMO_API int smo_decode_step(const smo_model *m, const int *tokens, int batch, in
         smo_qmatmul(m->dtype, xn, m->wgu[L], gu, batch, H, 2 * F);
         for (int b = 0; b < batch; b++)
             smo_swiglu(gu + (size_t)b * 2 * F, gu + (size_t)b * 2 * F + F, act + (size_t)b * F, F);
-        smo_qmatmul(m->dtype, act, m->wdown[L], tmp, batch, F, H);
+        smo_qmatmul(m->down_dtype ? m->down_dtype : m->dtype, act, m->wdown[L], tmp, batch, F, H);
         smo_add_inplace(x, tmp, (int64_t)B * H);
     }
     smo_rmsnorm(x, m->final_norm, x, batch, H, m->eps);
-    smo_qmatmul(m->dtype, x, m->lm_head, logits, batch, H, m->vocab);
+    smo_qmatmul(m->head_dtype ? m->head_dtype : m->dtype, x, m->lm_head, logits, batch, H, m->vocab);
 done:
     free(x); free(xn); free(q); free(k); free(v); free(att); free(tmp); free(gu); free(act);
     return rc;

@@ -375,6 +375,7 @@ class _Model(C.Structure):
         ("qnorm", C.POINTER(C.c_void_p)), ("knorm", C.POINTER(C.c_void_p)),
         ("final_norm", C.c_void_p), ("lm_head", C.c_void_p), ("embedding", C.c_void_p),
         ("cosT", C.c_void_p), ("sinT", C.c_void_p),
+        ("down_dtype", C.c_int), ("head_dtype", C.c_int),
     ]
 
 
@@ -394,7 +395,8 @@ class Decoder:
         self.kcache = np.zeros((L, batch, nkv, ms, hd), dtype=np.float32)
         self.vcache = np.zeros_like(self.kcache)
         self.cos, self.sin = rope_tables(cfg["rope_theta"], hd, ms)
-        self.embedding = dequantize(cfg["dtype"], weights["embedding"], cfg["vocab"] * cfg["hidden"])
+        head_dt = cfg.get("head_dtype", cfg["dtype"])
+        self.embedding = dequantize(head_dt, weights["embedding"], cfg["vocab"] * cfg["hidden"])
         self._keep = []
 
         def arr(name):
@@ -407,6 +409,7 @@ class Decoder:
         m.head_dim, m.ffn, m.vocab, m.max_seq = hd, cfg["ffn"], cfg["vocab"], ms
         m.dtype, m.eps, m.rope_theta = cfg["dtype"], cfg["eps"], cfg["rope_theta"]
         m.neox, m.qk_norm = int(cfg["neox"]), int(cfg["qk_norm"])
+        m.down_dtype, m.head_dtype = cfg.get("down_dtype", 0), cfg.get("head_dtype", 0)
         m.wq, m.wk, m.wv, m.wo = arr("wq"), arr("wk"), arr("wv"), arr("wo")
         m.wgu, m.wdown = arr("wgu"), arr("wdown")
         m.norm1, m.norm2 = arr("norm1"), arr("norm2")

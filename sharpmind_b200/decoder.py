@@ -38,14 +38,16 @@ class Decoder:
         self.w = {}
         self._keep = []
 
-        def reg(raw, n, k):
+        def reg(raw, n, k, fmt=dt):
             if isinstance(raw, np.ndarray):
-                return ctx.register(raw, dt, n, k, repack=True, keep_raw=keep_raw)
-            return ctx.register_dev(raw, dt, n, k, repack=True, keep_raw=keep_raw)
+                return ctx.register(raw, fmt, n, k, repack=True, keep_raw=keep_raw)
+            return ctx.register_dev(raw, fmt, n, k, repack=True, keep_raw=keep_raw)
 
+        # GGUF files mix formats per tensor: the down projection and the embedding may name their own
+        fmts = {"wdown": cfg.get("down_dtype") or dt}
         for name, (n, k) in shapes.items():
-            self.w[name] = [reg(weights[name][i], n, k) for i in range(L)]
-        self.embedding = reg(weights["embedding"], V, H)
+            self.w[name] = [reg(weights[name][i], n, k, fmts.get(name, dt)) for i in range(L)]
+        self.embedding = reg(weights["embedding"], V, H, cfg.get("head_dtype") or dt)
         self.norms = {}
         for name in ("norm1", "norm2", "qnorm", "knorm"):
             self.norms[name] = [self._dev(weights[name][i]) for i in range(L)]

@@ -55,14 +55,15 @@ def make_decoder_weights(cfg: dict, config_name: str, quantize) -> dict:
     caller chooses which quantiser (the CUDA one in the product, a CPU checker in tests).
     Layout per layer follows the reference's linear layers: wq [nH*hd, H], wk/wv [nKV*hd, H],
     wo [H, nH*hd], wgu = gate rows followed by up rows [2F, H], wdown [H, F]; the embedding
-    [vocab, H] doubles as the tied LM head.
+    [vocab, H] doubles as the tied LM head.  cfg["dtype"] is the format of every matrix unless
+    cfg["down_dtype"] / cfg["head_dtype"] name another one for the down projection / the embedding.
     """
     L, H, hd = cfg["n_layers"], cfg["hidden"], cfg["head_dim"]
     q_dim, kv_dim, F, V = cfg["n_heads"] * hd, cfg["n_kv_heads"] * hd, cfg["ffn"], cfg["vocab"]
     dt = cfg["dtype"]
 
-    def mat(name, n, k):
-        return quantize(dt, normal(config_name, name, (n, k), 0.02))
+    def mat(name, n, k, fmt=None):
+        return quantize(fmt or dt, normal(config_name, name, (n, k), 0.02))
 
     w = {k: [] for k in ("wq", "wk", "wv", "wo", "wgu", "wdown", "norm1", "norm2", "qnorm", "knorm")}
     for i in range(L):
@@ -71,11 +72,11 @@ def make_decoder_weights(cfg: dict, config_name: str, quantize) -> dict:
         w["wv"].append(mat(f"l{i}.wv", kv_dim, H))
         w["wo"].append(mat(f"l{i}.wo", H, q_dim))
         w["wgu"].append(mat(f"l{i}.wgu", 2 * F, H))
-        w["wdown"].append(mat(f"l{i}.wdown", H, F))
+        w["wdown"].append(mat(f"l{i}.wdown", H, F, cfg.get("down_dtype")))
         w["norm1"].append(normal(config_name, f"l{i}.norm1", (H,), 0.1, 1.0))
         w["norm2"].append(normal(config_name, f"l{i}.norm2", (H,), 0.1, 1.0))
         w["qnorm"].append(normal(config_name, f"l{i}.qnorm", (hd,), 0.1, 1.0))
         w["knorm"].append(normal(config_name, f"l{i}.knorm", (hd,), 0.1, 1.0))
     w["final_norm"] = normal(config_name, "final_norm", (H,), 0.1, 1.0)
-    w["embedding"] = mat("embedding", V, H)
+    w["embedding"] = mat("embedding", V, H, cfg.get("head_dtype"))
     return w

@@ -217,3 +217,32 @@ def test_prompt_pass_quantised_activations_and_guards(oracle, cuda):
     with pytest.raises(ops.SharpMindCudaError):
         dec.forward_last_logits(to_dev(toks), 0, 1)                       # slot 1 of a one-sequence model
     dec.close()
+
+
+# Formats mixed per tensor as GGUF K-quant files do: Q4_K attention and gate||up, Q6_K down, Q8_0 embedding / LM head.
+MIXED = dict(n_layers=2, hidden=2048, n_heads=16, n_kv_heads=8, head_dim=128, ffn=2048, vocab=1024, max_seq=96,
+             dtype=12, down_dtype=14, head_dtype=8, eps=1e-5, rope_theta=5.0e5, neox=False, qk_norm=False)
+
+
+def test_mixed_format_decoder_prompt_and_decode(oracle, cuda):
+    """K-quant decoder: a 70-token prompt in one pass (fp32 activations: Q4_K matmuls of 64 rows and more run on the
+    tcgen05 kernel), then decode steps in every mode; one sequence with quantised activations takes the path with the
+    norms and the SiLU-gate folded into the one-row Q4_K / Q6_K matmuls."""
+    cfg, name, n_prompt = MIXED, "dec_mixed", 70
+    w = _weights(oracle, cfg, name)
+    ref = oracle.Decoder(cfg, w, 1)
+    toks = synth.token_ids(name, "prompt", (n_prompt + 3,), cfg["vocab"])
+    for p in range(n_prompt):
+        want = ref.step(toks[p:p + 1], p)
+    dec = Decoder(cuda, cfg, w, max_batch=1, keep_raw=True)
+    got = dec.forward_last_logits(to_dev(toks[:n_prompt]), 0, 0, ops.Mode.ACT_F32, chunk=128)[0].cpu().numpy()
+    scale = np.abs(want).max()
+    assert np.max(np.abs(got - want[0])) <= 2e-4 * scale, float(np.max(np.abs(got - want[0])) / scale)
+    assert int(got.argmax()) == int(want[0].argmax())
+    for p, mode, tol in ((n_prompt, ops.Mode.ACT_F32, 2e-4), (n_prompt + 1, ops.Mode.REF_ORDER, 2e-4),
+                         (n_prompt + 2, ops.Mode.ACT_Q8, 0.05)):
+        want = ref.step(toks[p:p + 1], p)
+        out = dec.step(to_dev(toks[p:p + 1]), p, mode)[0].cpu().numpy()
+        assert np.max(np.abs(out[0] - want[0])) <= tol * np.abs(want).max(), (mode, float(np.max(np.abs(out[0] - want[0])) / np.abs(want).max()))
+    dec.close()
+    assert cuda.device_status() == 0
