@@ -1,7 +1,8 @@
-"""Times the device-resident decode step on the Qwen3-0.6B-shaped configuration (Q8_0 weights, fp32 KV).
+"""Times the device-resident decode step on the Qwen3-0.6B-shaped configuration (Q8_0 weights, fp32 KV), or with
+`--model llama8b` on a Llama-3-8B shape with K-quant weights; `--prompt N` times the multi-token prompt pass.
 
     python -m sharpmind_b200.profile_decode [--batches 1,8,32] [--ctx 2048] [--steps 64] [--modes q8,f32]
-                                            [--layers 28] [--once]
+                                            [--layers 28] [--once] [--model qwen3|llama8b] [--prompt N --chunk C]
 
 Weights are seeded normal(0, 0.02) values quantised on the device, the context is `ctx` positions of
 seeded normal K/V installed with kv_load (no prompt is run: the step's cost depends on the context length
@@ -28,8 +29,8 @@ def device_weights(dev: ops.DeviceOps, cfg: dict, seed: int = 1234) -> dict:
     L, H, hd = cfg["n_layers"], cfg["hidden"], cfg["head_dim"]
     q_dim, kv_dim, F, V, dt = cfg["n_heads"] * hd, cfg["n_kv_heads"] * hd, cfg["ffn"], cfg["vocab"], cfg["dtype"]
 
-    def mat(n, k):
-        return dev.quantize_weights(dt, torch.randn((n, k), generator=g, device="cuda") * 0.02)
+    def mat(n, k, fmt=None):
+        return dev.quantize_weights(fmt or dt, torch.randn((n, k), generator=g, device="cuda") * 0.02)
 
     def vec(n):
         return torch.randn(n, generator=g, device="cuda") * 0.1 + 1.0
@@ -37,10 +38,10 @@ def device_weights(dev: ops.DeviceOps, cfg: dict, seed: int = 1234) -> dict:
     w = {k: [] for k in ("wq", "wk", "wv", "wo", "wgu", "wdown", "norm1", "norm2", "qnorm", "knorm")}
     for _ in range(L):
         w["wq"].append(mat(q_dim, H)), w["wk"].append(mat(kv_dim, H)), w["wv"].append(mat(kv_dim, H))
-        w["wo"].append(mat(H, q_dim)), w["wgu"].append(mat(2 * F, H)), w["wdown"].append(mat(H, F))
+        w["wo"].append(mat(H, q_dim)), w["wgu"].append(mat(2 * F, H)), w["wdown"].append(mat(H, F, cfg.get("down_dtype")))
         w["norm1"].append(vec(H)), w["norm2"].append(vec(H)), w["qnorm"].append(vec(hd)), w["knorm"].append(vec(hd))
     w["final_norm"] = vec(H)
-    w["embedding"] = mat(V, H)
+    w["embedding"] = mat(V, H, cfg.get("head_dtype"))
     return w
 
 
@@ -48,8 +49,10 @@ def step_bytes(cfg: dict, batch: int, ctx: int) -> dict:
     """Bytes one step has to read: every weight block once, and the K/V rows of the context per sequence."""
     L, H, hd = cfg["n_layers"], cfg["hidden"], cfg["head_dim"]
     q_dim, kv_dim, F, V = cfg["n_heads"] * hd, cfg["n_kv_heads"] * hd, cfg["ffn"], cfg["vocab"]
-    per_layer = (q_dim * H + 2 * kv_dim * H + H * q_dim + 2 * F * H + H * F) // 32 * 34
-    weights = L * per_layer + V * H // 32 * 34
+    bpe = {8: 34 / 32, 12: 144 / 256, 14: 210 / 256}  # bytes per element of each block format
+    dt = cfg["dtype"]
+    per_layer = (q_dim * H + 2 * kv_dim * H + H * q_dim + 2 * F * H) * bpe[dt] + H * F * bpe[cfg.get("down_dtype") or dt]
+    weights = int(L * per_layer + V * H * bpe[cfg.get("head_dtype") or dt])
     kv = L * batch * 2 * cfg["n_kv_heads"] * (ctx + 1) * hd * 4
     return {"weights": weights, "kv": kv}
 
@@ -154,8 +157,10 @@ def main():
     ap.add_argument("--modes", default="q8,f32")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--once", action="store_true")
+    ap.add_argument("--model", default="qwen3", choices=("qwen3", "llama8b"),
+                    help="qwen3 = Qwen3-0.6B shape, Q8_0; llama8b = Llama-3-8B shape, Q4_K / Q6_K down / Q8_0 head")
     a = ap.parse_args()
-    cfg = dict(synth.QWEN3_0_6B)
+    cfg = dict(synth.QWEN3_0_6B if a.model == "qwen3" else synth.LLAMA3_8B)
     if a.layers:
         cfg["n_layers"] = a.layers
     ctx = ops.CudaContext(0)

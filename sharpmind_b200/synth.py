@@ -48,6 +48,14 @@ QWEN3_0_6B = dict(
 )
 
 
+# Llama-3-8B shape with the formats a Q4_K_M-style GGUF file mixes: Q4_K attention and gate||up, Q6_K down;
+# the embedding / tied LM head is Q8_0 (the decoder's embedding gather reads Q8_0 rows).
+LLAMA3_8B = dict(
+    n_layers=32, hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, vocab=128256,
+    max_seq=2304, dtype=12, down_dtype=14, head_dtype=8, eps=1e-5, rope_theta=5.0e5, neox=False, qk_norm=False,
+)
+
+
 def make_decoder_weights(cfg: dict, config_name: str, quantize) -> dict:
     """Random-init weights of a decoder shaped by `cfg`.
 

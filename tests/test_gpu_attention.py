@@ -26,7 +26,11 @@ def oracle_decode(oracle, q, kc, vc, kv_len, scale):
     (2, 8, 8, 64, 77, 128),
     (2, 8, 2, 128, 1, 64),         # a single key
     (1, 4, 2, 32, 100, 128),       # head size the split kernel does not take: reference-order kernel
-    (1, 14, 2, 64, 300, 512),      # 7 query heads per KV head: reference-order kernel
+    (1, 14, 2, 64, 300, 512),      # 7 query heads per KV head: one head per CTA, seven CTAs share a cached head
+    (2, 32, 8, 128, 500, 512),     # 4 query heads per KV head, few sequences: run as 2 x 2
+    (6, 32, 8, 128, 200, 256),     # 4 per KV head, more sequences
+    (1, 64, 8, 128, 300, 512),     # 8 per KV head (70B-class): 4 x 2
+    (5, 64, 8, 64, 90, 128),       # 8 per KV head, more sequences, head size 64
 ])
 def test_sdpa_decode(oracle, dev, batch, heads, kvh, hd, kv_len, max_seq):
     q = synth.normal("gpua", f"q{batch}_{heads}_{hd}_{kv_len}", (batch, heads, hd))
