@@ -126,6 +126,8 @@ bool smc_stream_supported(const smc_weight *, int M);
 int smc_launch_gemv_stream(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,
                         cudaStream_t s);
+int smc_launch_swiglu_quantize_q8(smc_ctx *ctx, const float *gate, const float *up, int M, int K, int ld, smc_q8act *a,
+                                  cudaStream_t s);
 int smc_launch_quantize_q8(smc_ctx *, const float *x, int M, int K, smc_q8act *, cudaStream_t s);
 int smc_launch_block_isums(smc_ctx *, const smc_q8act *, int m, const smc_weight *, int col0, int col1,
                            int32_t *sums, cudaStream_t s);

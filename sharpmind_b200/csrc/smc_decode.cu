@@ -331,7 +331,8 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
     // per-head norm + RoPE + append, attention, Wo, gate||up, down (+ the next layer's QKV takes its residual).
     // (an FFN wider than 8192 keeps its SiLU-gate as a launch of its own: the down-projection's row is then too
     // long to be worth staging through the gate in every CTA)
-    bool one_row = mode == SMC_ACT_Q8 && B == 1 && H <= 8192 && ctx->use_tma && smc_tma_supported(d.lm_head, 1);
+    bool one_row = mode == SMC_ACT_Q8 && B == 1 && H <= 8192 && ctx->use_tma && smc_tma_supported(d.lm_head, 1) &&
+                   (F <= 8192 || m->qb);
     for (int l = 0; l < d.n_layers && one_row; ++l)
         one_row = m->wqkv[l] && smc_tma_supported(m->wqkv[l], 1) && smc_tma_supported(m->wgu[l], 1) && m->wdown[l]->fast &&
                   (F > 8192 || smc_tma_supported(m->wdown[l], 1));
@@ -353,8 +354,8 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
             if (F <= 8192) {
                 SMC_TRY(smc_launch_gemv_tma_swiglu(ctx, m->gu, m->gu + F, m->wdown[l], m->tmp, s));
             } else {
-                SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, 1, F, 2 * F, s));
-                SMC_TRY(smc_qmatmul_dev(ctx, m->act, m->wdown[l], m->tmp, 1, mode, s));
+                SMC_TRY(smc_launch_swiglu_quantize_q8(ctx, m->gu, m->gu + F, 1, F, 2 * F, m->qb, s));
+                SMC_TRY(smc_qmatmul_q8_dev(ctx, m->qb, m->wdown[l], m->tmp, s));
             }
             pending = m->tmp;
         }
@@ -397,8 +398,11 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
             // one row: SiLU(gate) * up is formed and quantised while the down-projection stages its activations
             SMC_TRY(smc_launch_gemv_tma_swiglu(ctx, m->gu, m->gu + F, m->wdown[l], m->tmp, s));
         } else {
-            SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, B, F, 2 * F, s));
-            if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->act, B, F, m->qb, s));
+            if (reuse) {  // SiLU-gate and quantisation in one pass: the fp32 product is not written out
+                SMC_TRY(smc_launch_swiglu_quantize_q8(ctx, m->gu, m->gu + F, B, F, 2 * F, m->qb, s));
+            } else {
+                SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, B, F, 2 * F, s));
+            }
             SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s));
         }
         // residual add, then the next block's first norm (the final norm after the last block)
@@ -450,8 +454,11 @@ int smc_forward_last_logits(smc_ctx *ctx, smc_model *m, const int *d_tokens, int
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, T, H, d.eps, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, T, H, m->qa, s));
         SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, T, mode, reuse ? m->qa : nullptr, s));
-        SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, T, F, 2 * F, s));
-        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->act, T, F, m->qb, s));
+        if (reuse) {
+            SMC_TRY(smc_launch_swiglu_quantize_q8(ctx, m->gu, m->gu + F, T, F, 2 * F, m->qb, s));
+        } else {
+            SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, T, F, 2 * F, s));
+        }
         SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s));
         const float *next_norm = l + 1 < d.n_layers ? m->norm1[l + 1] : d.final_norm;
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, T, H, d.eps, s));

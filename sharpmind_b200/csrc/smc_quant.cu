@@ -13,7 +13,11 @@ namespace {
 
 // ---------------------------------------------------------------------------- activations -> Q8_0
 // One warp per 32-element block; x [M][K], K % 32 == 0.
-__global__ void __launch_bounds__(256) quantize_q8_kernel(const float *__restrict__ x, int8_t *__restrict__ q,
+// With `up` the quantised value is SiLU(x) * up (x / (1 + exp(-x)) * up in the arithmetic of the stand-alone gate
+// kernel), x and up being rows of `ld` floats of which the first K are used: the FFN's gate step and the
+// quantisation of the down projection's input in one pass, without the fp32 product going through memory.
+__global__ void __launch_bounds__(256) quantize_q8_kernel(const float *__restrict__ x, const float *__restrict__ up, int K, int ld,
+                                                          int8_t *__restrict__ q,
                                                           float *__restrict__ d, uint16_t *__restrict__ dbits,
                                                           float *__restrict__ sd, int16_t *__restrict__ s16,
                                                           long long nblocks)
@@ -22,8 +26,16 @@ __global__ void __launch_bounds__(256) quantize_q8_kernel(const float *__restric
     const int lane = threadIdx.x & 31;
     long long blk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    const int bpr = K / 32;  // blocks per row
     for (; blk < nblocks; blk += stride) {
-        float v = x[blk * 32 + lane];
+        float v;
+        if (up) {
+            const long long at = (blk / bpr) * ld + (blk % bpr) * 32 + lane;
+            const float g = x[at];
+            v = __fdiv_rn(g, 1.0f + expf(-g)) * up[at];
+        } else {
+            v = x[blk * 32 + lane];
+        }
         float amax = fabsf(v);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -274,8 +286,24 @@ int smc_launch_quantize_q8(smc_ctx *ctx, const float *x, int M, int K, smc_q8act
     a->M = M;
     a->K = K;
     long long nblocks = (long long)M * K / 32;
-    smc_launch_dep(ctx->use_pdl, quantize_q8_kernel, dim3(grid_for(nblocks, 8, ctx->sm_count * 8)), dim3(256), 0, s, x, a->q, a->d,
-                   a->dbits, a->sd, a->s16, nblocks);
+    smc_launch_dep(ctx->use_pdl, quantize_q8_kernel, dim3(grid_for(nblocks, 8, ctx->sm_count * 8)), dim3(256), 0, s, x,
+                   (const float *)nullptr, K, K, a->q, a->d, a->dbits, a->sd, a->s16, nblocks);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+// Rows of SiLU(gate) * up, quantised: gate and up are [M] rows of `ld` floats, K of them used.
+int smc_launch_swiglu_quantize_q8(smc_ctx *ctx, const float *gate, const float *up, int M, int K, int ld, smc_q8act *a,
+                                  cudaStream_t s)
+{
+    if (K % 32) return smc_fail(ctx, SMC_E_UNSUPPORTED, "Q8 activations need K %% 32 == 0 (K = %d)", K);
+    if (M > a->max_rows || K > a->max_k || (size_t)M * K > (size_t)a->max_rows * a->max_k)
+        return smc_fail(ctx, SMC_E_INVALID, "q8act buffer %d x %d too small for %d x %d", a->max_rows, a->max_k, M, K);
+    a->M = M;
+    a->K = K;
+    long long nblocks = (long long)M * K / 32;
+    smc_launch_dep(ctx->use_pdl, quantize_q8_kernel, dim3(grid_for(nblocks, 8, ctx->sm_count * 8)), dim3(256), 0, s, gate, up, K, ld,
+                   a->q, a->d, a->dbits, a->sd, a->s16, nblocks);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
