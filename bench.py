@@ -610,6 +610,18 @@ def run_ours(args):
                                                    "ms": pr["ms"], "tokens_per_s": pr["tokens_per_s"]}
             except Exception as exc:
                 result.setdefault("decode", {})["error"] = str(exc)
+            # ---- the same step on a Llama-3-8B shape with K-quant weights (the formats of configs[1] in a whole decoder)
+            try:
+                torch.cuda.empty_cache()
+                rows8 = time_decode(ctx, dev, dict(synth.LLAMA3_8B), [1, 32], 2048, 8)
+                result["decode_llama8b"] = {
+                    "workload": "Llama-3-8B-shaped decoder: Q4_K attention and gate||up, Q6_K down, Q8_0 tied embedding, fp32 KV, "
+                                "2048-position seeded random context, q8_0 activations, CUDA graph",
+                    "tokens_per_s_batch1": rows8[0]["tokens_per_s_graph"], "ms_per_step_batch1": rows8[0]["graph_ms_per_step"],
+                    "tokens_per_s_batch32": rows8[1]["tokens_per_s_graph"], "ms_per_step_batch32": rows8[1]["graph_ms_per_step"],
+                    "GBps_batch1": rows8[0]["GBps_graph"], "GBps_batch32": rows8[1]["GBps_graph"]}
+            except Exception as exc:
+                result["decode_llama8b"] = {"error": str(exc)}
             # ---- CPU baseline on the host cores
             try:
                 result["cpu_baseline"], _ = cpu_port_time(args.workload, M, args.cpu_seconds)
