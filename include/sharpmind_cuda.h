@@ -248,8 +248,9 @@ SMC_API int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int
  * `seqLen` consecutive tokens of ONE sequence (cache slot `seq`) at positions pos .. pos + seqLen - 1.  Their K and
  * V are appended to the cache, every token attends causally to positions 0 .. its own, and d_logits [vocab] /
  * d_argmax [1] receive the LAST token's logits and greedy pick.  Prompts longer than a caller wants to hold in
- * scratch are fed in chunks (pos advancing); the first call of a longer chunk grows the activation scratch, so
- * make it outside stream capture.  Needs the joined Q/K/V path (one weight format per layer, headDim 64 or 128);
+ * scratch are fed in chunks (pos advancing); the first call of a longer chunk grows the activation scratch
+ * (after a device-wide synchronisation), so make it outside stream capture, and re-capture any CUDA graph of
+ * smc_decode_step recorded on this model before that call: it still points at the old buffers.  Needs the joined Q/K/V path (one weight format per layer, headDim 64 or 128);
  * SMC_E_UNSUPPORTED otherwise, SMC_E_RANGE past the cache (KVCache.cs:89-91). */
 SMC_API int smc_forward_last_logits(smc_ctx *ctx, smc_model *model, const int *d_tokens, int seqLen, int seq, int pos,
                                     int mode, float *d_logits, int *d_argmax, void *stream);
