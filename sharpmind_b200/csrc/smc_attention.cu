@@ -24,49 +24,89 @@ constexpr int LPK = 8;          // lanes per key
 constexpr int MAXG = 8;         // query heads per KV head handled by one CTA pass
 constexpr int SPLIT_THREADS = 128;
 
-constexpr int MERGE_MAX_SPLITS = 512;
+constexpr int MERGE_MAX_SPLITS = 128;
 
-// Combines the per-split records of one (batch, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M),
-// both sums taken in split order.  The weights are computed once per split by the CTA and shared.  Records are
-// read through L2 (they may have been written by other CTAs of the same launch).  sw / sl hold MERGE_MAX_SPLITS
-// floats each, red 8.
-__device__ __forceinline__ void merge_records(const float *rec, float *out, int hd, int splits, float *sw, float *sl, float *red)
+// Per (batch, head) the split kernel leaves `splits` partial results laid out for this merge:
+// [splits][4] floats (m, l, -, -) followed by [splits][HD] partial outputs, every row 16-byte aligned.
+__host__ __device__ inline size_t head_record_floats(int splits, int hd) { return (size_t)splits * (hd + 4); }
+
+// Combines the records of the G consecutive heads of one CTA's (sequence, KV head):
+// out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M).  Built for few round trips to L2 (the records were written by
+// other CTAs of the same launch): one for all (m, l) pairs, then every thread streams float4 pieces of the partial
+// outputs of its (head, quarter of the dims, subset of splits) with the loads of a subset in flight together.
+// The subsets (split s belongs to subset s mod P) are added in subset order, each in split order: the result
+// depends on the split count only.  `scratch` (16-byte aligned) holds 3 * G * splits + 3 + (blockDim / (HD / 4)) * HD floats.
+template <int G, int HD>
+__device__ __forceinline__ void merge_heads(const float *rec0, float *out0, int splits, float *scratch)
 {
-    float m = -INFINITY;
-    for (int s = threadIdx.x; s < splits; s += blockDim.x) m = fmaxf(m, __ldcg(rec + (size_t)s * (hd + 2)));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    __syncthreads();  // red / sw / sl may still be in use by a previous call
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
-    __syncthreads();
-    float M = red[0];
-    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) M = fmaxf(M, red[i]);
-    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
-        const float *r = rec + (size_t)s * (hd + 2);
-        const float ms = __ldcg(r);
-        sw[s] = (ms == -INFINITY) ? 0.f : expf(ms - M);
-        sl[s] = __ldcg(r + 1);
+    constexpr int NQ = HD / 4;                   // float4 pieces per head
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    float *sm_m = scratch, *sm_l = sm_m + G * splits, *sm_w = sm_l + G * splits;
+    float *sm_o = scratch + ((3 * G * splits + 3) & ~3);  // float4 rows: 16-byte aligned (scratch itself is)
+    __shared__ float sL[G];
+    const size_t hstride = head_record_floats(splits, HD);
+    for (int i = tid; i < G * splits; i += nthr) {
+        const int g = i / splits, sp = i - g * splits;
+        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(rec0 + g * hstride + 4 * sp));
+        sm_m[i] = ml.x, sm_l[i] = ml.y;
     }
     __syncthreads();
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) L = fmaf(sl[s], sw[s], L);
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float O = 0.f;
-        int s = 0;
-        for (; s + 4 <= splits; s += 4) {
-            const float a = __ldcg(rec + (size_t)s * (hd + 2) + 2 + d), b = __ldcg(rec + (size_t)(s + 1) * (hd + 2) + 2 + d);
-            const float c = __ldcg(rec + (size_t)(s + 2) * (hd + 2) + 2 + d), e = __ldcg(rec + (size_t)(s + 3) * (hd + 2) + 2 + d);
-            O = fmaf(a, sw[s], O);
-            O = fmaf(b, sw[s + 1], O);
-            O = fmaf(c, sw[s + 2], O);
-            O = fmaf(e, sw[s + 3], O);
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int g = warp; g < G; g += nthr >> 5) {  // one warp per head: maximum, weights, then the denominator in split order
+        float m = -INFINITY;
+        for (int sp = lane; sp < splits; sp += 32) m = fmaxf(m, sm_m[g * splits + sp]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        for (int sp = lane; sp < splits; sp += 32) {
+            const float ms = sm_m[g * splits + sp];
+            sm_w[g * splits + sp] = (ms == -INFINITY) ? 0.f : expf(ms - m);
         }
-        for (; s < splits; ++s) O = fmaf(__ldcg(rec + (size_t)s * (hd + 2) + 2 + d), sw[s], O);
-        out[d] = L > 0.f ? __fdiv_rn(O, L) : 0.f;
+        __syncwarp();
+        if (lane == 0) {
+            float L = 0.f;
+            for (int sp = 0; sp < splits; ++sp) L = fmaf(sm_l[g * splits + sp], sm_w[g * splits + sp], L);
+            sL[g] = L;
+        }
+    }
+    __syncthreads();
+    const int groups = nthr / NQ;                // thread groups of one head's width
+    const int P = groups >= G ? groups / G : 1;  // split subsets per head
+    const int gid = tid / NQ, quad = tid - gid * NQ;
+    if (gid < G * P) {  // one (head, subset) per thread
+        const int g = gid % G, part = gid / G;
+        const float *src = rec0 + g * hstride + 4 * (size_t)splits + 4 * quad;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        int sp = part;
+        for (; sp + 3 * P < splits; sp += 4 * P) {
+            const float4 a = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)sp * HD));
+            const float4 b = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)(sp + P) * HD));
+            const float4 c = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)(sp + 2 * P) * HD));
+            const float4 e = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)(sp + 3 * P) * HD));
+            const float wa = sm_w[g * splits + sp], wb = sm_w[g * splits + sp + P], wc = sm_w[g * splits + sp + 2 * P],
+                        we = sm_w[g * splits + sp + 3 * P];
+            acc.x = fmaf(a.x, wa, acc.x), acc.y = fmaf(a.y, wa, acc.y), acc.z = fmaf(a.z, wa, acc.z), acc.w = fmaf(a.w, wa, acc.w);
+            acc.x = fmaf(b.x, wb, acc.x), acc.y = fmaf(b.y, wb, acc.y), acc.z = fmaf(b.z, wb, acc.z), acc.w = fmaf(b.w, wb, acc.w);
+            acc.x = fmaf(c.x, wc, acc.x), acc.y = fmaf(c.y, wc, acc.y), acc.z = fmaf(c.z, wc, acc.z), acc.w = fmaf(c.w, wc, acc.w);
+            acc.x = fmaf(e.x, we, acc.x), acc.y = fmaf(e.y, we, acc.y), acc.z = fmaf(e.z, we, acc.z), acc.w = fmaf(e.w, we, acc.w);
+        }
+        for (; sp < splits; sp += P) {
+            const float4 a = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)sp * HD));
+            const float wa = sm_w[g * splits + sp];
+            acc.x = fmaf(a.x, wa, acc.x), acc.y = fmaf(a.y, wa, acc.y), acc.z = fmaf(a.z, wa, acc.z), acc.w = fmaf(a.w, wa, acc.w);
+        }
+        *reinterpret_cast<float4 *>(sm_o + ((size_t)part * G + g) * HD + 4 * quad) = acc;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += nthr) {
+        const int g = i / HD, d = i - g * HD;
+        float O = sm_o[(size_t)g * HD + d];
+        for (int part = 1; part < P; ++part) O += sm_o[((size_t)part * G + g) * HD + d];
+        const float L = sL[g];
+        out0[(size_t)g * HD + d] = L > 0.f ? __fdiv_rn(O, L) : 0.f;
     }
 }
 
-// partial record per (batch, head, split): [m, l, o[headDim]]
+// partial results per (batch, head): see head_record_floats
 template <int DPL, int G>  // DPL = dims per lane = headDim / 8, G = query heads per KV head
 __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
     const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc, float *part,
@@ -142,7 +182,7 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
     }
 
     // merge the lane groups of the CTA: shared memory holds (m, l) per group and o per group
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     float *sm_m = sm;                                   // [ngroups][G]
     float *sm_l = sm_m + ngroups * G;                   // [ngroups][G]
     float *sm_o = sm_l + ngroups * G;                   // [ngroups][G][HD]
@@ -164,12 +204,11 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
             L = fmaf(sm_l[r * G + g], w, L);
             O = fmaf(sm_o[((size_t)r * G + g) * HD + d], w, O);
         }
-        float *rec = part + (((size_t)b * heads + (size_t)kvh * G + g) * splits + split) * (HD + 2);
-        if (d == 0) rec[0] = M, rec[1] = L;
-        rec[2 + d] = O;
+        float *rec = part + ((size_t)b * heads + (size_t)kvh * G + g) * head_record_floats(splits, HD);
+        if (d == 0) rec[4 * split] = M, rec[4 * split + 1] = L;
+        rec[4 * (size_t)splits + (size_t)split * HD + d] = O;
     }
     // the CTA that finishes a (sequence, KV head) last combines the records of its query heads
-    __shared__ float mw[MERGE_MAX_SPLITS], ml[MERGE_MAX_SPLITS], mred[8];
     __shared__ int s_last;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -181,10 +220,9 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int g = 0; g < G; ++g) {
-        const size_t head = (size_t)b * heads + (size_t)kvh * G + g;
-        merge_records(part + head * splits * (HD + 2), out + head * HD, HD, splits, mw, ml, mred);
-    }
+    // the shared memory of the group merge above is free again (every thread passed the barrier after its last read)
+    const size_t head0 = (size_t)b * heads + (size_t)kvh * G;
+    merge_heads<G, HD>(part + head0 * head_record_floats(splits, HD), out + head0 * HD, splits, sm);
 }
 
 // Reference-order attention: one CTA per query row, 256 threads, tiles of 64 keys.
@@ -470,7 +508,7 @@ int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const 
     // shape allocates: make it outside stream capture)
     constexpr size_t TICKET_BYTES = 65536 * sizeof(unsigned);
     if ((size_t)batch * kvHeads > 65536) return smc_fail(ctx, SMC_E_RANGE, "sdpa_decode: more than 65536 (sequence, KV head) pairs");
-    const size_t need = TICKET_BYTES + (size_t)batch * heads * splits * (headDim + 2) * sizeof(float);
+    const size_t need = TICKET_BYTES + (size_t)batch * heads * head_record_floats(splits, headDim) * sizeof(float);
     if (need > ctx->attn_part_cap) {
         std::lock_guard<std::mutex> lock(ctx->mu);
         if (ctx->d_attn_part) {
