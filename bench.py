@@ -605,8 +605,8 @@ def run_ours(args):
                     "GBps_batch1": rows[0]["GBps_graph"], "GBps_batch32": rows[1]["GBps_graph"]}
                 from sharpmind_b200.profile_decode import time_prompt
 
-                pr = time_prompt(ctx, dev, dict(synth.QWEN3_0_6B), 2048, 512, "q8", 2)
-                result["decode"]["prompt_pass"] = {"what": "ForwardLastLogits over a 2048-token seeded prompt in chunks of 512, one sequence",
+                pr = time_prompt(ctx, dev, dict(synth.QWEN3_0_6B), 2048, 1024, "q8", 2)
+                result["decode"]["prompt_pass"] = {"what": "ForwardLastLogits over a 2048-token seeded prompt in chunks of 1024, one sequence",
                                                    "ms": pr["ms"], "tokens_per_s": pr["tokens_per_s"]}
             except Exception as exc:
                 result.setdefault("decode", {})["error"] = str(exc)

@@ -122,7 +122,7 @@ def time_decode(ctx, dev, cfg: dict, batches, ctx_len: int, steps: int, modes=("
     return rows
 
 
-def time_prompt(ctx, dev, cfg: dict, n_tokens: int, chunk: int = 512, mode: str = "q8", reps: int = 3) -> dict:
+def time_prompt(ctx, dev, cfg: dict, n_tokens: int, chunk: int = 1024, mode: str = "q8", reps: int = 3) -> dict:
     """Times ForwardLastLogits over a seeded random prompt of `n_tokens` (one sequence, chunks of `chunk` tokens)."""
     import torch
 
@@ -150,7 +150,7 @@ def time_prompt(ctx, dev, cfg: dict, n_tokens: int, chunk: int = 512, mode: str 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--prompt", type=int, default=0, help="time a prompt pass of this many tokens instead of decode steps")
-    ap.add_argument("--chunk", type=int, default=512)
+    ap.add_argument("--chunk", type=int, default=1024)
     ap.add_argument("--batches", default="1,8,32")
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=64)
