@@ -16,7 +16,14 @@
  *   - dtype uses SharpMind's QuantDType numbering (QuantDType.cs:2-18).
  *
  * Pointers named d_* are device pointers; `stream` is a cudaStream_t passed as void*.
- * A context may be used from several host threads; calls on one context are serialised.
+ *
+ * Threads and streams.  A context may be used from several host threads.  The host-pointer entry points
+ * (smc_*_host), registration and lookup are serialised by the context.  The device entry points (*_dev) only
+ * queue work on the caller's stream; those that keep intermediate data in buffers owned by the context
+ * (smc_qmatmul_dev with SMC_ACT_Q8 for M > 1 or shapes the one-row kernel does not take, smc_qmatmul_tc_dev,
+ * smc_sdpa_decode_dev, smc_argmax_dev, smc_decode_step, smc_forward_last_logits) reuse those buffers in stream
+ * order: all such calls on one context must go to ONE stream (or be ordered by events).  Work that is to run
+ * concurrently on several streams takes one context per stream.
  */
 #ifndef SHARPMIND_CUDA_H
 #define SHARPMIND_CUDA_H
@@ -74,8 +81,17 @@ SMC_API int smc_device_count(int *count);
  * SharpMind.GPU/GPUActivationKernels.cs:15-21. */
 SMC_API int smc_init(int device, smc_ctx **out);
 SMC_API void smc_destroy(smc_ctx *ctx);
-/* Text of the last failure on this context (valid until the next failing call). */
+/* Text of the last failure on this context (a copy private to the calling thread, valid until that thread's
+ * next call of this function). */
 SMC_API const char *smc_last_error(smc_ctx *ctx);
+/* Per-context switches.  No counterpart in the reference (its tiers are chosen by mapping keys, MappingBuilder.cs).
+ *   "pdl"                   1 (default) / 0: launch kernels with programmatic dependent launch, so that a kernel's
+ *                           weight prefetch overlaps its predecessor's tail, or fully serialised
+ *   "gemv_slots"            ring depth per warp of the one-row matmul kernel, 2..8 (0 = built-in choice)
+ *   "gemv_steps_per_stage"  steps per bulk copy of that kernel: 1, 2 or 4 (0 = built-in choice)
+ *   "gemv_ctas_per_sm"      resident CTAs per SM its grid is sized for, 1..4 (0 = built-in choice)
+ * Results do not depend on any of them.  SMC_E_INVALID for an unknown name. */
+SMC_API int smc_set_option(smc_ctx *ctx, const char *name, int value);
 /* QuantizationOps.GetRawTensorByteCount for a [N, K] tensor (QuantizationOps.cs:15-72); -1 if dtype unknown. */
 SMC_API int64_t smc_raw_tensor_bytes(int dtype, int64_t N, int64_t K);
 /* Waits for the device, then reports whether any kernel of this context gave up a bounded wait since

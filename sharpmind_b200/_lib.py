@@ -22,6 +22,7 @@ SIGNATURES = {
     "smc_init": (c_int, [c_int, _pp]),
     "smc_destroy": (None, [c_void_p]),
     "smc_last_error": (C.c_char_p, [c_void_p]),
+    "smc_set_option": (c_int, [c_void_p, C.c_char_p, c_int]),
     "smc_raw_tensor_bytes": (c_int64, [c_int, c_int64, c_int64]),
     "smc_synchronize": (c_int, [c_void_p]),
     "smc_device_status": (c_int, [c_void_p, C.POINTER(c_int)]),

@@ -22,7 +22,10 @@ int smc_fail(smc_ctx *ctx, int code, const char *fmt, ...)
     va_start(ap, fmt);
     vsnprintf(buf, sizeof(buf), fmt, ap);
     va_end(ap);
-    if (ctx) ctx->last_error = buf;
+    if (ctx) {
+        std::lock_guard<std::mutex> lock(ctx->mu_error);
+        ctx->last_error = buf;
+    }
     return code;
 }
 
@@ -95,10 +98,7 @@ void free_weight(smc_weight *w)
     cudaFree(w->d_raw);
     cudaFree(w->q8_qs);
     cudaFree(w->q8_d);
-    cudaFree(w->q6_ql);
-    cudaFree(w->q6_qh);
-    cudaFree(w->q6_sc);
-    cudaFree(w->q6_d);
+    cudaFree(w->q6u);
     delete w;
 }
 
@@ -179,13 +179,19 @@ int smc_init(int device, smc_ctx **out)
         delete ctx;
         return SMC_E_CUDA;
     }
-    const char *impl = getenv("SMC_GEMV");
-    ctx->use_tma = !(impl && strcmp(impl, "stream") == 0);
-    ctx->use_mma = !(impl && strcmp(impl, "dp4a") == 0);
-    ctx->use_tc = !(impl && strcmp(impl, "notc") == 0);
-    const char *pdl = getenv("SMC_PDL");
-    ctx->use_pdl = !(pdl && strcmp(pdl, "0") == 0);
     *out = ctx;
+    return SMC_OK;
+}
+
+int smc_set_option(smc_ctx *ctx, const char *name, int value)
+{
+    if (!ctx || !name) return smc_fail(ctx, SMC_E_INVALID, "set_option: bad arguments");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (!strcmp(name, "pdl")) ctx->use_pdl = value != 0;
+    else if (!strcmp(name, "gemv_slots")) ctx->tma_slots = value >= 2 && value <= 8 ? value : 0;
+    else if (!strcmp(name, "gemv_steps_per_stage")) ctx->tma_ss = (value == 1 || value == 2 || value == 4) ? value : 0;
+    else if (!strcmp(name, "gemv_ctas_per_sm")) ctx->tma_ctas = value >= 1 && value <= 4 ? value : 0;
+    else return smc_fail(ctx, SMC_E_INVALID, "set_option: unknown option '%s'", name);
     return SMC_OK;
 }
 
@@ -209,7 +215,15 @@ void smc_destroy(smc_ctx *ctx)
     delete ctx;
 }
 
-const char *smc_last_error(smc_ctx *ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+const char *smc_last_error(smc_ctx *ctx)
+{
+    if (!ctx) return "null context";
+    // the text is copied into a per-thread buffer so that a failure on another thread cannot change it under the reader
+    static thread_local std::string copy;
+    std::lock_guard<std::mutex> lock(ctx->mu_error);
+    copy = ctx->last_error;
+    return copy.c_str();
+}
 
 int smc_device_status(smc_ctx *ctx, int *status)
 {
@@ -373,13 +387,13 @@ int smc_qmatmul_q8_dev(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, fl
 // `gd` (row-split across GPUs): when the one-row TMA kernel runs, it also exchanges the output slice with the
 // peers and *fused is set; otherwise the caller launches the exchange after this returns.
 static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, int mode,
-                        cudaStream_t s, bool have_lock, const smc_gather_dev *gd = nullptr, bool *fused = nullptr)
+                        cudaStream_t s, const smc_gather_dev *gd = nullptr, bool *fused = nullptr)
 {
     switch (mode) {
     case SMC_REF_ORDER: return smc_launch_gemv_ref(ctx, d_in, w, d_out, M, 0, w->N, s);
     case SMC_ACT_F32:
         // prefill-sized batches of Q4_K run on the tcgen05 tensor cores (same parity bound, see smc_prefill.cu)
-        if (M >= 64 && ctx->use_tc && smc_prefill_supported(w, M) && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
+        if (M >= 64 && smc_prefill_supported(w, M) && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
             return smc_launch_prefill_q4k(ctx, d_in, w, d_out, M, s);
         if (w->fast && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) return smc_launch_gemv_f32(ctx, d_in, w, d_out, M, s);
         // shapes the vector kernels do not take (ragged K, rows that start inside a block) run in the
@@ -390,33 +404,32 @@ static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, fl
             return smc_fail(ctx, SMC_E_UNSUPPORTED,
                             "SMC_ACT_Q8 needs a weight registered with SMC_W_REPACK and K %% %d == 0",
                             w->dtype == SMC_Q8_0 ? 32 : 256);
-        // a single row of moderate length is quantised inside the GEMV kernel while it is staged: one launch,
-        // no scratch.  Longer rows cost every CTA a longer prologue than the separate quantiser launch saves.
-        if (M == 1 && w->K <= 8192 && ctx->use_tma && smc_tma_supported(w, 1) &&
-            (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) {
+        // a single row is quantised inside the GEMV kernel while it is staged: one launch, no scratch
+        if (M == 1 && smc_tma_supported(w, 1) && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) {
             if (!gd) return smc_launch_gemv_tma_f32in(ctx, d_in, w, d_out, s);
             *fused = true;
             return smc_launch_gemv_tma_gather(ctx, d_in, w, d_out, gd, s);
         }
-        {
-            std::unique_lock<std::mutex> lock(ctx->mu, std::defer_lock);
-            if (!have_lock) lock.lock();
-            if (!ctx->act || ctx->act->max_rows < M || ctx->act->max_k < w->K) {
-                // growing the scratch allocates: make the first call of a new size outside stream capture
-                int rows = ctx->act ? (ctx->act->max_rows > M ? ctx->act->max_rows : M) : (M > 32 ? M : 32);
-                int k = ctx->act ? (ctx->act->max_k > w->K ? ctx->act->max_k : w->K) : w->K;
-                if (ctx->act) {
-                    cudaDeviceSynchronize();
-                    smc_q8act_free(ctx->act);
-                    ctx->act = nullptr;
-                }
-                int rc = smc_q8act_alloc(ctx, rows, k, &ctx->act);
-                if (rc) return rc;
+        // Everything else goes through the context's one scratch buffer of quantised activations.  The lock is held
+        // until both kernels are queued, so host threads cannot interleave their launches or free the buffer under
+        // one another; on the device the buffer is reused in stream order, which is why calls that use it have to
+        // share one stream per context (see the header).
+        std::unique_lock<std::mutex> lock(ctx->mu_scratch);
+        if (!ctx->act || ctx->act->max_rows < M || ctx->act->max_k < w->K) {
+            // growing the scratch allocates: make the first call of a new size outside stream capture
+            int rows = ctx->act ? (ctx->act->max_rows > M ? ctx->act->max_rows : M) : (M > 32 ? M : 32);
+            int k = ctx->act ? (ctx->act->max_k > w->K ? ctx->act->max_k : w->K) : w->K;
+            if (ctx->act) {
+                cudaDeviceSynchronize();
+                smc_q8act_free(ctx->act);
+                ctx->act = nullptr;
             }
+            int rc = smc_q8act_alloc(ctx, rows, k, &ctx->act);
+            if (rc) return rc;
         }
         int rc = smc_launch_quantize_q8(ctx, d_in, M, w->K, ctx->act, s);
         if (rc) return rc;
-        if (gd && M == 1 && ctx->use_tma && smc_tma_supported(w, 1)) {
+        if (gd && M == 1 && smc_tma_supported(w, 1)) {
             *fused = true;
             return smc_launch_gemv_tma_xg(ctx, ctx->act, nullptr, w, d_out, gd, s);
         }
@@ -430,7 +443,7 @@ int smc_qmatmul_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, float 
 {
     if (!ctx || !d_in || !w || !d_out || M < 0) return smc_fail(ctx, SMC_E_INVALID, "qmatmul: bad arguments");
     if (M == 0) return SMC_OK;
-    return qmatmul_impl(ctx, d_in, w, d_out, M, mode, static_cast<cudaStream_t>(stream), false);
+    return qmatmul_impl(ctx, d_in, w, d_out, M, mode, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
@@ -439,14 +452,14 @@ int smc_qmatmul_dev_gather(smc_ctx *ctx, const float *d_in, const smc_weight *w,
                            cudaStream_t s, const smc_gather_dev *gd, bool *fused)
 {
     *fused = false;
-    return qmatmul_impl(ctx, d_in, w, d_out, M, mode, s, false, gd, fused);
+    return qmatmul_impl(ctx, d_in, w, d_out, M, mode, s, gd, fused);
 }
 
 extern "C" {
 
 static int one_row_fusable(smc_ctx *ctx, const smc_weight *w, const char *what)
 {
-    if (!w->fast || w->K > 8192 || !ctx->use_tma || !smc_tma_supported(w, 1))
+    if (!w->fast || w->K > 8192 || !smc_tma_supported(w, 1))
         return smc_fail(ctx, SMC_E_UNSUPPORTED, "%s: the weight is not one the one-row bulk-copy kernel takes (K = %d)", what, w->K);
     return SMC_OK;
 }
@@ -484,6 +497,8 @@ int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts, int cou
         const smc_weight *p = parts[i];
         if (!p || p->dtype != dtype || p->K != K) return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "weight_concat: parts differ in dtype or K");
         if (!p->fast) return smc_fail(ctx, SMC_E_UNSUPPORTED, "weight_concat: parts must be registered with SMC_W_REPACK");
+        if (dtype == SMC_Q6_K && ((long long)p->N * K / 256) % 8 != 0)
+            return smc_fail(ctx, SMC_E_UNSUPPORTED, "weight_concat: a Q6_K part must hold a multiple of 2048 elements");
         raw = raw && p->d_raw != nullptr;
         N += p->N;
     }
@@ -515,10 +530,7 @@ int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts, int cou
         cat(&smc_weight::q8_qs, (size_t)K);
         cat(&smc_weight::q8_d, (size_t)K / 32 * 2);
     } else if (dtype == SMC_Q6_K) {
-        cat(&smc_weight::q6_ql, blk * 128);
-        cat(&smc_weight::q6_qh, blk * 64);
-        cat(&smc_weight::q6_sc, blk * 16);
-        cat(&smc_weight::q6_d, blk * 2);
+        cat(&smc_weight::q6u, blk * (SMC_Q6U_BYTES / 8));  // parts were checked to be whole units
     }
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
@@ -576,7 +588,7 @@ int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, flo
     if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, out_bytes))) return rc;
     // one wait per call: input copy, kernels and result copy are ordered by the stream
     if ((rc = h2d_queued(ctx, ctx->d_stage_in, input, in_bytes, out_bytes))) return rc;
-    if ((rc = qmatmul_impl(ctx, ctx->d_stage_in, w, ctx->d_stage_out, M, mode, ctx->stream, true))) {
+    if ((rc = qmatmul_impl(ctx, ctx->d_stage_in, w, ctx->d_stage_out, M, mode, ctx->stream))) {
         cudaStreamSynchronize(ctx->stream);
         return rc;
     }

@@ -26,12 +26,34 @@ struct smc_weight {
     // Q8_0 planes: quants [N][K] int8 and scales [N][K/32] fp16
     int8_t *q8_qs = nullptr;
     __half *q8_d = nullptr;
-    // Q6_K planes, one entry per 256-element block in flat-tensor order
-    uint8_t *q6_ql = nullptr;  // [nblk][128]
-    uint8_t *q6_qh = nullptr;  // [nblk][64]
-    int8_t *q6_sc = nullptr;   // [nblk][16]
-    __half *q6_d = nullptr;    // [nblk]
+    // Q6_K compute layout: units of eight 256-element blocks in flat-tensor order, SMC_Q6U_BYTES each (see below)
+    uint8_t *q6u = nullptr;
 };
+
+// Q6_K compute layout.  Eight consecutive blocks (2048 elements) form one unit of 1680 bytes, the same byte
+// count as their GGUF form, laid out for the lanes of a warp: "lane slot" s = 4*b + 2*h + o names block b (0..7)
+// of the unit, half h (128 elements) and sixteen o (elements l = 16*o .. 16*o + 15 of each 32-element column).
+//   [   0,  512)  X: 16 bytes per lane slot; byte i = code(c=0, l) | (code(c=3, l) & 3) << 6        l = 16*o + i
+//   [ 512, 1024)  Y: byte i = code(c=1, l) | ((code(c=3, l) >> 2) & 3) << 6
+//   [1024, 1536)  Z: byte i = code(c=2, l) | ((code(c=3, l) >> 4) & 3) << 6
+//   [1536, 1664)  the sixteen int8 scales of each block, 16 bytes per block
+//   [1664, 1680)  the fp16 d of each block
+// code(c, l) is the six-bit value of element 128*h + 32*c + l of the block (VecDotQ6K_Scalar's q1..q4 for c = 0..3,
+// QuantizationKernels.Q6.cs:28-41).  Three of the four code words of a lane are one AND away; a quarter warp reads
+// 128 contiguous bytes of each of X, Y, Z, so shared-memory reads of a unit are free of bank conflicts.
+#define SMC_Q6U_BYTES 1680
+#define SMC_Q6U_Y 512
+#define SMC_Q6U_Z 1024
+#define SMC_Q6U_SC 1536
+#define SMC_Q6U_D 1664
+// byte offset of lane slot (blk & 7, h, o) inside the X plane of block blk's unit (add SMC_Q6U_Y / _Z for the others)
+__host__ __device__ inline size_t smc_q6u_slot(size_t blk, int h, int o)
+{
+    return (blk >> 3) * SMC_Q6U_BYTES + 16 * (4 * (blk & 7) + 2 * h + o);
+}
+__host__ __device__ inline size_t smc_q6u_scales(size_t blk) { return (blk >> 3) * SMC_Q6U_BYTES + SMC_Q6U_SC + 16 * (blk & 7); }
+__host__ __device__ inline size_t smc_q6u_d(size_t blk) { return (blk >> 3) * SMC_Q6U_BYTES + SMC_Q6U_D + 2 * (blk & 7); }
+__host__ __device__ inline size_t smc_q6u_bytes(size_t nblk) { return ((nblk + 7) >> 3) * SMC_Q6U_BYTES; }
 
 // Q8_0-quantised activations in structure-of-arrays form.
 struct smc_q8act {
@@ -50,6 +72,7 @@ struct smc_ctx {
     cudaStream_t stream = nullptr;  // used by the host-pointer entry points
     std::mutex mu;
     std::mutex mu_scratch;  // guards the kernels' own scratch buffers (taken with or without `mu` held)
+    std::mutex mu_error;    // guards last_error
     std::string last_error;
     std::unordered_map<const void *, smc_weight *> by_host;
     // staging for host-pointer calls (grown on demand)
@@ -60,10 +83,8 @@ struct smc_ctx {
     // scratch owned by the context
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
-    bool use_pdl = true;               // SMC_PDL=0 in the environment launches every kernel fully serialised
-    bool use_mma = true;               // SMC_GEMV=dp4a in the environment keeps batches on the dp4a kernels
-    bool use_tc = true;                // SMC_GEMV=notc keeps prefill-sized batches off the tcgen05 kernel
-    bool use_tma = true;               // SMC_GEMV=stream in the environment selects the register-prefetch kernels
+    bool use_pdl = true;               // programmatic dependent launch (smc_set_option "pdl")
+    int tma_slots = 0, tma_ss = 0, tma_ctas = 0;  // one-row GEMV ring geometry, 0 = built-in choice (smc_set_option)
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
     int argmax_rows = 0, argmax_chunks = 0;
     void *d_prefill = nullptr;         // activation image of the tensor-core matmul
@@ -95,7 +116,6 @@ int smc_launch_gemv_q8(smc_ctx *, const smc_q8act *, const smc_weight *, float *
 bool smc_tma_supported(const smc_weight *, int M);
 int smc_launch_gemv_tma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_tma_f32in(smc_ctx *, const float *x, const smc_weight *, float *out, cudaStream_t s);
-int smc_launch_gemv_tma_x(smc_ctx *, const smc_q8act *, const float *xf, const smc_weight *, float *out, cudaStream_t s);
 struct smc_gather_dev;
 struct smc_gather;
 int smc_launch_gemv_tma_xg(smc_ctx *, const smc_q8act *, const float *xf, const smc_weight *, float *out,
@@ -111,8 +131,6 @@ int smc_launch_gemv_tma_full(smc_ctx *, const smc_q8act *, const float *xf, cons
                              const smc_weight *, float *out, const smc_gather_dev *, cudaStream_t s);
 int smc_launch_gemv_tma_addnorm(smc_ctx *, const float *x, const smc_norm_prologue *, const smc_weight *, float *out,
                                 cudaStream_t s);
-int smc_launch_gemv_tma_xgu(smc_ctx *, const smc_q8act *, const float *xf, const float *xu, const smc_weight *, float *out,
-                            const smc_gather_dev *, cudaStream_t s);
 int smc_launch_gemv_tma_swiglu(smc_ctx *, const float *gate, const float *up, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_tma_gather(smc_ctx *, const float *x, const smc_weight *, float *out, const smc_gather_dev *,
                                cudaStream_t s);
@@ -122,8 +140,6 @@ bool smc_prefill_supported(const smc_weight *, int M);
 int smc_launch_prefill_q4k(smc_ctx *, const float *x, const smc_weight *, float *out, int M, cudaStream_t s);
 bool smc_mma_supported(const smc_weight *, int M);
 int smc_launch_gemv_mma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
-bool smc_stream_supported(const smc_weight *, int M);
-int smc_launch_gemv_stream(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,
                         cudaStream_t s);
 int smc_launch_swiglu_quantize_q8(smc_ctx *ctx, const float *gate, const float *up, int M, int K, int ld, smc_q8act *a,
@@ -242,6 +258,17 @@ __device__ __forceinline__ float smc_group_sum_rt(float v, int lanes)
 {
     for (int o = lanes / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+
+// The four code words of a lane slot's word j (bytes l = 16*o + 4*j .. + 3) from its X, Y, Z words: q[c] holds the
+// six-bit codes of column c, one per byte.
+__device__ __forceinline__ void smc_q6u_codes(uint32_t X, uint32_t Y, uint32_t Z, uint32_t (&q)[4])
+{
+    const uint32_t M6 = 0x3F3F3F3Fu;
+    q[0] = X & M6;
+    q[1] = Y & M6;
+    q[2] = Z & M6;
+    q[3] = ((X >> 6) & 0x03030303u) | ((Y >> 4) & 0x0C0C0C0Cu) | ((Z >> 2) & 0x30303030u);
 }
 
 // Q4_K / Q5_K 6-bit scale and min of sub-block j (0..7) from the 12 packed bytes held as three

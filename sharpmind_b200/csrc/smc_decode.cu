@@ -331,7 +331,7 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
     // per-head norm + RoPE + append, attention, Wo, gate||up, down (+ the next layer's QKV takes its residual).
     // (an FFN wider than 8192 keeps its SiLU-gate as a launch of its own: the down-projection's row is then too
     // long to be worth staging through the gate in every CTA)
-    bool one_row = mode == SMC_ACT_Q8 && B == 1 && H <= 8192 && ctx->use_tma && smc_tma_supported(d.lm_head, 1) &&
+    bool one_row = mode == SMC_ACT_Q8 && B == 1 && H <= 8192 && smc_tma_supported(d.lm_head, 1) &&
                    (F <= 8192 || m->qb);
     for (int l = 0; l < d.n_layers && one_row; ++l)
         one_row = m->wqkv[l] && smc_tma_supported(m->wqkv[l], 1) && smc_tma_supported(m->wgu[l], 1) && m->wdown[l]->fast &&
@@ -394,7 +394,7 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, B, H, d.eps, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
         SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, B, mode, reuse ? m->qa : nullptr, s));
-        if (mode == SMC_ACT_Q8 && B == 1 && F <= 8192 && ctx->use_tma && m->wdown[l]->fast && smc_tma_supported(m->wdown[l], 1)) {
+        if (mode == SMC_ACT_Q8 && B == 1 && F <= 8192 && m->wdown[l]->fast && smc_tma_supported(m->wdown[l], 1)) {
             // one row: SiLU(gate) * up is formed and quantised while the down-projection stages its activations
             SMC_TRY(smc_launch_gemv_tma_swiglu(ctx, m->gu, m->gu + F, m->wdown[l], m->tmp, s));
         } else {

@@ -15,8 +15,8 @@
 //   Q8_0  16 quants (half a block) from the repacked planes [N][K] int8 + [N][K/32] fp16
 //   Q4_K  16 bytes of qs = 16 low nibbles of sub-block a and 16 high nibbles of sub-block a+1,
 //         plus the 16-byte block header, straight from the GGUF layout (144 B = 9 x 16 B)
-//   Q6_K  a quarter block: 16 bytes of ql, 16 of ql+32, 16 of qh -> 64 six-bit values, from the
-//         repacked planes ql / qh / scales / d
+//   Q6_K  a quarter block: the 16-byte X, Y, Z entries of one lane slot of the unit layout
+//         (smc_common.cuh) -> 64 six-bit values, plus the block's scales and d
 //
 // References: VecDotQ8_0_* QuantizationKernels.Q8.cs:11-138, VecDotQ4K_* QuantizationKernels.Q4.cs:586-747,
 // VecDotQ6K_* QuantizationKernels.Q6.cs:12-235, QuantizedMatMul_*_Wrapper QuantizationKernels.cs:11-42
@@ -37,9 +37,7 @@ struct WPtrs {
     const uint8_t *raw;    // Q4_K blocks
     const int8_t *q8_qs;
     const __half *q8_d;
-    const uint8_t *q6_ql, *q6_qh;
-    const int8_t *q6_sc;
-    const __half *q6_d;
+    const uint8_t *q6u;    // Q6_K units (smc_common.cuh)
 };
 
 __device__ __forceinline__ float4 ldx4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
@@ -174,7 +172,7 @@ struct FmtQ4_K {
 // ------------------------------------------------------------------------------------------ Q6_K
 struct FmtQ6_K {
     struct Unit {
-        uint4 a, b, h;  // ql[l0..], ql[32 + l0..], qh[l0..] of one 128-half
+        uint4 a, b, h;  // the X, Y, Z entries of lane slot (block, half, sixteen)
         uint2 sc;       // the 8 int8 scales of that half
         float d;
     };
@@ -187,25 +185,22 @@ struct FmtQ6_K {
     static __device__ __forceinline__ Unit load(const WPtrs &p, int row, int u, int K)
     {
         size_t blk = (size_t)row * (K / 256) + (u >> 2);
-        int h = (u >> 1) & 1, l0 = 16 * (u & 1);
+        int h = (u >> 1) & 1;
+        const uint8_t *slot = p.q6u + smc_q6u_slot(blk, h, u & 1);
         Unit t;
-        t.a = smc_ldg_stream16(p.q6_ql + blk * 128 + 64 * h + l0);
-        t.b = smc_ldg_stream16(p.q6_ql + blk * 128 + 64 * h + 32 + l0);
-        t.h = smc_ldg_stream16(p.q6_qh + blk * 64 + 32 * h + l0);
-        t.sc = smc_ldg_stream8(p.q6_sc + blk * 16 + 8 * h);
-        t.d = smc_h2f(smc_ldg_stream2(p.q6_d + blk));
+        t.a = smc_ldg_stream16(slot);
+        t.b = smc_ldg_stream16(slot + SMC_Q6U_Y);
+        t.h = smc_ldg_stream16(slot + SMC_Q6U_Z);
+        t.sc = smc_ldg_stream8(p.q6u + smc_q6u_scales(blk) + 8 * h);
+        t.d = smc_h2f(smc_ldg_stream2(p.q6u + smc_q6u_d(blk)));
         return t;
     }
     // six-bit codes of column c (0..3) of the half, word j (0..3): elements 32c + l0 + 4j .. +3
     static __device__ __forceinline__ uint32_t codes(uint32_t a, uint32_t b, uint32_t h, int c)
     {
-        const uint32_t M4 = 0x0F0F0F0Fu, M2 = 0x30303030u;
-        switch (c) {
-        case 0: return (a & M4) | ((h << 4) & M2);
-        case 1: return (b & M4) | ((h << 2) & M2);
-        case 2: return ((a >> 4) & M4) | (h & M2);
-        default: return ((b >> 4) & M4) | ((h >> 2) & M2);
-        }
+        uint32_t q[4];
+        smc_q6u_codes(a, b, h, q);
+        return q[c];
     }
     static __device__ __forceinline__ int scale_of(const Unit &t, int u, int c)
     {
@@ -347,10 +342,7 @@ WPtrs wptrs(const smc_weight *w)
     p.raw = w->d_raw;
     p.q8_qs = w->q8_qs;
     p.q8_d = w->q8_d;
-    p.q6_ql = w->q6_ql;
-    p.q6_qh = w->q6_qh;
-    p.q6_sc = w->q6_sc;
-    p.q6_d = w->q6_d;
+    p.q6u = w->q6u;
     return p;
 }
 
@@ -531,9 +523,9 @@ int smc_launch_gemv_f32(smc_ctx *ctx, const float *x, const smc_weight *w, float
 int smc_launch_gemv_q8(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *out, cudaStream_t s)
 {
     // two or more rows: per-block integer sums on the int8 tensor-core path (Q8_0, Q4_K)
-    if (ctx->use_mma && smc_mma_supported(w, a->M)) return smc_launch_gemv_mma(ctx, a, w, out, s);
-    if (ctx->use_tma && smc_tma_supported(w, a->M)) return smc_launch_gemv_tma(ctx, a, w, out, s);
-    if (smc_stream_supported(w, a->M)) return smc_launch_gemv_stream(ctx, a, w, out, s);
+    if (smc_mma_supported(w, a->M)) return smc_launch_gemv_mma(ctx, a, w, out, s);
+    // one row: the bulk-copy kernel, fed the rows quantised beforehand
+    if (smc_tma_supported(w, a->M)) return smc_launch_gemv_tma(ctx, a, w, out, s);
     ActPtrs ap{};
     ap.q = a->q;
     ap.d = a->d;

@@ -237,10 +237,11 @@ gemv_mma_q4_K_kernel(const uint8_t *__restrict__ raw, const int8_t *__restrict__
 }
 
 // ------------------------------------------------------------------------------------------------ Q6_K
-// Planes per 256-element block: ql[128], qh[64], 16 int8 scales, fp16 d.  A scale covers 16 elements, so the unit
-// is mma.m16n8k16: for half h (128 elements) and sixteen `is` a lane reads four bytes of ql[l], ql[32 + l] and
-// qh[l] at l = 16*is + 4*tg of each of its four rows and forms from them the codes of columns c = 0..3 (elements
-// 32c + l .. l + 3 of the half), 32 subtracted bytewise; out += (d * sc[8h + is + 2c]) * dx[4h + c] * isum.
+// Weights in the unit layout of smc_common.cuh (X, Y, Z entries per lane slot, 16 int8 scales and fp16 d per block).
+// A scale covers 16 elements, so the unit is mma.m16n8k16: for half h (128 elements) and sixteen `is` a lane reads
+// four bytes of the X, Y and Z entries of slot (block, h, is) at byte 4*tg of each of its four rows and forms from
+// them the codes of columns c = 0..3 (elements 32c + l .. l + 3 of the half, l = 16*is + 4*tg), 32 subtracted
+// bytewise; out += (d * sc[8h + is + 2c]) * dx[4h + c] * isum.
 __device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0)
 {
     asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
@@ -256,21 +257,20 @@ __device__ __forceinline__ uint32_t ldg4(const void *p)
 }
 
 template <int C>
-__device__ __forceinline__ uint32_t q6_codes(uint32_t wa, uint32_t wb, uint32_t wh)
+__device__ __forceinline__ uint32_t q6_codes(uint32_t wx, uint32_t wy, uint32_t wz)
 {
-    const uint32_t M4 = 0x0F0F0F0Fu, M2 = 0x30303030u;
+    const uint32_t M6 = 0x3F3F3F3Fu;
     uint32_t q;
-    if (C == 0) q = (wa & M4) | ((wh << 4) & M2);
-    else if (C == 1) q = (wb & M4) | ((wh << 2) & M2);
-    else if (C == 2) q = ((wa >> 4) & M4) | (wh & M2);
-    else q = ((wb >> 4) & M4) | ((wh >> 2) & M2);
+    if (C == 0) q = wx & M6;
+    else if (C == 1) q = wy & M6;
+    else if (C == 2) q = wz & M6;
+    else q = ((wx >> 6) & 0x03030303u) | ((wy >> 4) & 0x0C0C0C0Cu) | ((wz >> 2) & 0x30303030u);
     return __vsub4(q, 0x20202020u);  // codes 0..63 -> -32..31, no byte borrows into its neighbour
 }
 
 template <int NT, int NW>
 __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1)
-gemv_mma_q6_K_kernel(const uint8_t *__restrict__ ql, const uint8_t *__restrict__ qh, const int8_t *__restrict__ scp,
-                     const __half *__restrict__ dp, const int8_t *__restrict__ xq, const float *__restrict__ xd,
+gemv_mma_q6_K_kernel(const uint8_t *__restrict__ q6u, const int8_t *__restrict__ xq, const float *__restrict__ xd,
                      float *__restrict__ out, int N, int K, int M)
 {
     // NW warps split K: 8 (two CTAs per SM), or 16 in one CTA per SM for rows of 8192 elements and more
@@ -298,8 +298,8 @@ gemv_mma_q6_K_kernel(const uint8_t *__restrict__ ql, const uint8_t *__restrict__
                 for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
         for (int sb = warp; sb < nsb; sb += NW) {
             // this lane's row: d * sc of the sixteen sub-blocks
-            const uint4 scw = *reinterpret_cast<const uint4 *>(scp + (size_t)(hblk + sb) * 16);
-            const float d = __half2float(dp[hblk + sb]);
+            const uint4 scw = *reinterpret_cast<const uint4 *>(q6u + smc_q6u_scales(hblk + sb));
+            const float d = __half2float(*reinterpret_cast<const __half *>(q6u + smc_q6u_d(hblk + sb)));
             // this lane's token: activation scales of the eight 32-element blocks
             const float4 dxa = *reinterpret_cast<const float4 *>(xrow + sb * 8), dxb = *reinterpret_cast<const float4 *>(xrow + sb * 8 + 4);
             // up to 16 tokens both halves are unrolled and their loads overlap; beyond, the accumulators need the registers
@@ -312,9 +312,8 @@ gemv_mma_q6_K_kernel(const uint8_t *__restrict__ ql, const uint8_t *__restrict__
                     uint32_t wa[4], wb[4], wh[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint8_t *pl = ql + (size_t)(rblk[j] + sb) * 128 + 64 * h + 16 * is + 4 * tg;
-                        wa[j] = ldg4(pl), wb[j] = ldg4(pl + 32);
-                        wh[j] = ldg4(qh + (size_t)(rblk[j] + sb) * 64 + 32 * h + 16 * is + 4 * tg);
+                        const uint8_t *pl = q6u + smc_q6u_slot(rblk[j] + sb, h, is) + 4 * tg;
+                        wa[j] = ldg4(pl), wb[j] = ldg4(pl + SMC_Q6U_Y), wh[j] = ldg4(pl + SMC_Q6U_Z);
                     }
                     auto column = [&](auto cc) {
                         constexpr int c = decltype(cc)::value;
@@ -364,7 +363,7 @@ bool smc_mma_supported(const smc_weight *w, int M)
     if (!w->fast || M < 2) return false;
     if (w->dtype == SMC_Q8_0) return w->K % 128 == 0 && w->q8_qs != nullptr;
     if (w->dtype == SMC_Q4_K) return w->K % 256 == 0 && w->d_raw != nullptr;
-    if (w->dtype == SMC_Q6_K) return w->K % 256 == 0 && w->q6_ql != nullptr;
+    if (w->dtype == SMC_Q6_K) return w->K % 256 == 0 && w->q6u != nullptr;
     return false;
 }
 
@@ -387,8 +386,8 @@ int smc_launch_gemv_mma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, f
         auto go = [&](auto kernel, int nw) {
             const size_t smem = (size_t)nw * 32 * 33 * sizeof(float);
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            smc_launch_dep(ctx->use_pdl, kernel, grid, dim3(nw * 32), smem, s, (const uint8_t *)w->q6_ql, (const uint8_t *)w->q6_qh,
-                           (const int8_t *)w->q6_sc, (const __half *)w->q6_d, (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
+            smc_launch_dep(ctx->use_pdl, kernel, grid, dim3(nw * 32), smem, s, (const uint8_t *)w->q6u, (const int8_t *)a->q,
+                           (const float *)a->d, out, N, K, M);
         };
         if (wide) {
             if (nt == 1) go(gemv_mma_q6_K_kernel<1, 16>, 16);

@@ -1,27 +1,38 @@
-// TMA-staged streaming GEMV for Q8_0-quantised activations, the decode hot kernel.
+// Bulk-copy (TMA) staged streaming GEMV for one activation row: the decode hot kernel.
 //
-// Each warp owns a contiguous range of weight rows, i.e. one contiguous byte stream per weight
-// array, and consumes it in "steps" of 32 lane-units (Q4_K / Q6_K: 8 blocks = 2048 elements,
-// Q8_0: 32 blocks = 1024 elements).  The bytes of a step are brought into a warp-private ring of
-// shared-memory slots by bulk asynchronous copies (cp.async.bulk global -> shared, completion on an
-// mbarrier) issued by one lane, up to `slots` steps ahead of the math:
-//   * memory-level parallelism is set by shared memory, not by registers (6-8 slots x 8 warps x
-//     2-3 CTAs keep more than 100 KB per SM in flight, against the ~45 KB Little's law asks for);
+// Work split.  The weight bytes of a matrix are a flat stream of "steps" of 32 lane-units (Q4_K / Q6_K: 8 blocks =
+// 2048 elements, Q8_0: 32 blocks = 1024 elements; a row is K / STEP_ELEMS steps).  A CTA owns a contiguous range
+// of whole rows (rows are dealt out evenly, the first N % grid CTAs take one more), and its warps cut the CTA's
+// steps into equal contiguous pieces WITHOUT regard to row boundaries, so every warp of the grid streams the same
+// number of bytes (+-1 step) whatever N and K are: a 4096 x 14336 matrix, 1.15 rows per resident warp, no longer
+// runs a second, nearly empty round of rows.  A row that straddles two warps is continued, not re-added: the warp
+// that holds its first steps hands its 32 lane accumulators to the next warp through shared memory (an mbarrier
+// says when), and that warp goes on accumulating from them.  The sum of a row is therefore formed in one fixed
+// order (per lane over the row's steps in order, then a butterfly over the lanes) however the rows are divided:
+// the bits of an output do not depend on the grid, on N, or on a split of the matrix across GPUs.  To keep the
+// hand-over off the critical path a warp works in the order [its unfinished last row][its whole rows][the
+// continuation of its predecessor's row]: what it hands over is produced first, what it receives is needed last.
+//
+// Data movement.  The bytes of a warp's next stages (1, 2 or 4 consecutive steps) are brought into a warp-private
+// ring of shared-memory slots by bulk asynchronous copies (cp.async.bulk global -> shared, completion on an
+// mbarrier) issued by one lane, up to `slots` stages ahead of the math:
+//   * memory-level parallelism is set by shared memory, not by registers;
 //   * HBM and L2 see whole contiguous ranges, never half-used sectors;
-//   * the lanes read their unit with conflict-free 128-bit shared loads, and for M = 1 the
-//     activation row is in shared memory too (16-byte chunks permuted per format so that the
-//     strided reads of eight lanes fall in eight different bank groups): the inner loop issues no
-//     global loads at all.
-// The kernels are bound by instruction issue before they are bound by HBM, so the inner loop is
-// written for a short instruction stream: 32-bit shared addresses and explicit ld.shared, every
-// lane-constant offset hoisted, Q4_K scale / min bytes unpacked with two PRMTs, high nibbles dotted
-// in place (dp4a on w & 0xF0F0F0F0, exact shift by 4 afterwards), independent dp4a chains.
-// A slot is re-armed only after __syncwarp(): every lane has passed its wait and read its data, so
-// no lane can be left waiting on a phase that has already been reused.  Every wait is bounded; on
-// expiry the warp raises a flag in device memory (read back by smc_device_status) and stops.
+//   * Q4_K streams the GGUF blocks as they are (144 B = 9 x 16 B) and Q6_K the 1680-byte units of smc_common.cuh,
+//     one copy per stage; Q8_0 streams its two planes (quants, scales), two copies per stage;
+//   * the lanes read their unit with conflict-free 128-bit shared loads, and the activation row is in shared
+//     memory too (16-byte chunks permuted per format so that the strided reads of eight lanes fall in eight
+//     different bank groups): the inner loop issues no global loads at all.
+// The activation row is quantised to Q8_0 inside the kernel while it is staged (rules of
+// QuantizedKVCache.QuantizeRowQ8_0, SharpMind.Model/QuantizedKVCache.cs:191-223), optionally after SiLU(gate) * up
+// or a residual add + RMSNorm, so a matmul is one launch with no scratch buffer; rows quantised beforehand
+// (smc_q8act) are staged as they are.
+// A slot is re-armed only after __syncwarp(): every lane has passed its wait and read its data, so no lane can be
+// left waiting on a phase that has already been reused.  Every wait is bounded; on expiry the warp raises a flag in
+// device memory (read back by smc_device_status), drains the copies it still has in flight and stops.
 //
-// Arithmetic is identical to the other SMC_ACT_Q8 kernels: exact int32 block dots (dp4a), one fp32
-// multiply-add per 32-element block.  Shapes: K % 2048 == 0 (K-quants) / K % 1024 == 0 (Q8_0).
+// Arithmetic is that of the other SMC_ACT_Q8 kernels: exact int32 block dots (dp4a), one fp32 multiply-add per
+// 16- or 32-element block.  Shapes: K % 2048 == 0 (K-quants) / K % 1024 == 0 (Q8_0).
 // References: VecDotQ4K_* SharpMind.Core/Quantization/QuantizationKernels.Q4.cs:586-747, GetScaleMinK4_*
 // QuantizationKernels.cs:177-189, VecDotQ6K_* QuantizationKernels.Q6.cs:12-235, VecDotQ8_0_*
 // QuantizationKernels.Q8.cs:11-138.
@@ -43,6 +54,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
 {
@@ -73,7 +88,7 @@ __device__ __forceinline__ void fence_barrier_init()
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// explicit shared-space loads on 32-bit addresses
+// explicit shared-space accesses on 32-bit addresses
 __device__ __forceinline__ uint4 lds128(uint32_t a)
 {
     uint4 v;
@@ -98,6 +113,7 @@ __device__ __forceinline__ uint32_t lds16u(uint32_t a)
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
     return v;
 }
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
 
 __device__ __forceinline__ float warp_sum32(float v)
 {
@@ -107,11 +123,11 @@ __device__ __forceinline__ float warp_sum32(float v)
 }
 
 struct XPtrs {
-    const int8_t *q;
+    const int8_t *q;    // rows quantised beforehand (smc_q8act), used when xf is null
     const float *d;
     const float *sd;
     const int16_t *s16;
-    const float *xf;  // when set (M = 1): fp32 activations, quantised to Q8_0 while they are staged
+    const float *xf;  // when set: fp32 activations, quantised to Q8_0 while they are staged
     const float *xu;  // when set too: the staged row is SiLU(xf[i]) * xu[i] (FfnKernels.Gated's activation)
     // when nw is set: the staged row is RMSNorm(xf + xadd) * nw (xadd may be null), and CTA 0 writes xf + xadd to
     // xsum: the residual add and the norm of a decoder block folded into the matmul that consumes them
@@ -120,24 +136,34 @@ struct XPtrs {
     float eps;
 };
 
-// Shared layout of the staged activation row: q | d | sd | s16.  The quants are stored in 16-byte
-// chunks permuted by Math::swz so that the 128-bit reads of a quarter warp (eight lanes, each format
-// with its own stride pattern) fall in eight different bank groups.
+// Shared layout of the staged activation row: q [K] int8 | d [K/32] float | aux.  The quants are stored in 16-byte
+// chunks permuted by Math::swz so that the 128-bit reads of a quarter warp (eight lanes, each format with its own
+// stride pattern) fall in eight different bank groups.  aux is, per format,
+//   Q4_K (Math::SD):  sd [K/32] float = d * sum(q) of the block (the min term's factor);
+//   Q6_K (Math::S16): m32 [K/16] int32 = -32 * sum(q) of each sixteen (the codes' offset), eight per 128 elements in
+//                     the order [sixteen o of a column][column c], so that a lane reads its four with one 16-byte load.
 template <class Math>
-__device__ __forceinline__ void stage_x(const XPtrs &g, int m, int K, uint8_t *sx)
+__host__ __device__ inline size_t x_bytes(int K)
+{
+    return (size_t)K + (size_t)(K / 32) * 4 + (Math::SD ? (size_t)(K / 32) * 4 : 0) + (Math::S16 ? (size_t)(K / 16) * 4 : 0);
+}
+__device__ __forceinline__ int m32_pos(int g16) { return (g16 >> 3) * 8 + (g16 & 1) * 4 + ((g16 >> 1) & 3); }
+
+template <class Math>
+__device__ __forceinline__ void stage_x(const XPtrs &g, int K, uint8_t *sx)
 {
     uint4 *sq = reinterpret_cast<uint4 *>(sx);
     float *sdx = reinterpret_cast<float *>(sx + K);
     float *ssd = sdx + K / 32;
-    int16_t *ss16 = reinterpret_cast<int16_t *>(ssd + K / 32);
-    const uint4 *gq = reinterpret_cast<const uint4 *>(g.q + (size_t)m * K);
+    int *sm32 = reinterpret_cast<int *>(sdx + K / 32);
+    const uint4 *gq = reinterpret_cast<const uint4 *>(g.q);
     for (int i = threadIdx.x; i < K / 16; i += blockDim.x) sq[Math::swz(i)] = __ldg(gq + i);
     for (int i = threadIdx.x; i < K / 32; i += blockDim.x) {
-        sdx[i] = __ldg(g.d + (size_t)m * (K / 32) + i);
-        if (Math::SD) ssd[i] = __ldg(g.sd + (size_t)m * (K / 32) + i);
+        sdx[i] = __ldg(g.d + i);
+        if (Math::SD) ssd[i] = __ldg(g.sd + i);
     }
     if (Math::S16)
-        for (int i = threadIdx.x; i < K / 16; i += blockDim.x) ss16[i] = __ldg(g.s16 + (size_t)m * (K / 16) + i);
+        for (int i = threadIdx.x; i < K / 16; i += blockDim.x) sm32[m32_pos(i)] = -32 * (int)__ldg(g.s16 + i);
 }
 // Quantises the eight values of chunk c (lanes 4b .. 4b+3 hold the four chunks of block b) and stores them, their
 // block scale and sums in the staged layout: the rules of QuantizedKVCache.QuantizeRowQ8_0 (d = amax/127, 1 for a
@@ -147,7 +173,7 @@ __device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, u
 {
     float *sdx = reinterpret_cast<float *>(sx + K);
     float *ssd = sdx + K / 32;
-    int16_t *ss16 = reinterpret_cast<int16_t *>(ssd + K / 32);
+    int *sm32 = reinterpret_cast<int *>(sdx + K / 32);
     float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
@@ -168,7 +194,7 @@ __device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, u
     const int s16v = s + __shfl_xor_sync(0xffffffffu, s, 1);
     const int total = s16v + __shfl_xor_sync(0xffffffffu, s16v, 2);
     const int blk = c >> 2;
-    if (Math::S16 && (c & 1) == 0) ss16[blk * 2 + ((c >> 1) & 1)] = (int16_t)s16v;
+    if (Math::S16 && (c & 1) == 0) sm32[m32_pos(c >> 1)] = -32 * s16v;
     if ((c & 3) == 0) {
         const float df = __half2float(__float2half_rn(scale));
         sdx[blk] = df;
@@ -220,7 +246,7 @@ template <class Math>
 __device__ __forceinline__ void stage_x_addnorm_quant(const float *x, const float *add, const float *w, float eps, float *xsum,
                                                       int K, uint8_t *sx)
 {
-    __shared__ float red[8];
+    __shared__ float red[WARPS];
     const int nchunks = K / 8;
     constexpr int UB = 4;
     float v[UB][8];
@@ -263,31 +289,24 @@ __device__ __forceinline__ void stage_x_addnorm_quant(const float *x, const floa
         }
     }
 }
-__host__ __device__ inline size_t x_bytes(int K) { return (size_t)K + (size_t)(K / 32) * 8 + (size_t)(K / 16) * 2; }
 
 // Where the weight arrays of a format start (piece sizes and slot offsets are Math constants).
 struct StepSrc {
-    const uint8_t *base[4];  // first step of row 0 in each weight array
+    const uint8_t *base[2];  // step 0 of the tensor in each weight array
 };
 
-// Fetches stage `g` (SS consecutive steps, contiguous in every weight array) into a slot.  PIECES and
-// the per-piece sizes are compile-time so that the elected lane spends a handful of instructions here.
+// Fetches `n` consecutive steps starting at global step `g` (contiguous in every weight array) into a slot sized
+// for SS steps.  PIECES and the per-piece sizes are compile-time so that the elected lane spends a handful of
+// instructions here.
 template <class Math, int SS>
-__device__ __forceinline__ void issue_stage(const StepSrc &s, long long g, uint32_t slot_addr, uint32_t bar)
+__device__ __forceinline__ void issue_stage(const StepSrc &s, long long g, int n, uint32_t slot_addr, uint32_t bar)
 {
-    mbar_expect_tx(bar, Math::STEP_BYTES * SS);
+    mbar_expect_tx(bar, Math::STEP_BYTES * (uint32_t)n);
 #pragma unroll
     for (int i = 0; i < Math::PIECES; ++i)
-        bulk_g2s(slot_addr + Math::piece_off(i) * SS, s.base[i] + (size_t)g * (Math::piece_bytes(i) * SS),
-                 Math::piece_bytes(i) * SS, bar);
+        bulk_g2s(slot_addr + Math::piece_off(i) * SS, s.base[i] + (size_t)g * Math::piece_bytes(i), Math::piece_bytes(i) * (uint32_t)n,
+                 bar);
 }
-
-// Context handed to the per-format math: where the activations are.
-struct XCtx {
-    uint32_t sx;   // shared address of the staged row (M = 1)
-    int K, m0, M;
-    XPtrs g;       // global buffers (M > 1)
-};
 
 // ------------------------------------------------------------------------------------------------ Q4_K
 struct MathQ4K {
@@ -300,12 +319,11 @@ struct MathQ4K {
     // a quarter warp reads chunks 16*b + 4*p + j (two blocks b, four p, fixed j)
     static __host__ __device__ __forceinline__ int swz(int c) { return c ^ ((c >> 3) & 7); }
 
-    uint32_t blk_off, q_off;   // lane's block and qs bytes inside a slot
+    uint32_t blk_off, q_off;   // lane's block and qs bytes inside a step
     uint32_t xo[4];            // swizzled byte offsets of the lane's four activation chunks inside a step
     uint32_t dx_off;           // byte offset of the lane's two block scales inside a step
     uint32_t selR, selT;       // PRMT selectors of the scale unpack
     bool low;
-    int k_lane;                // element offset of the lane's unit inside a step
 
     __device__ __forceinline__ void init(int lane)
     {
@@ -319,11 +337,11 @@ struct MathQ4K {
         selR = (2 * pp) | ((2 * pp + 1) << 4) | ((4 + 2 * pp) << 8) | ((5 + 2 * pp) << 12);
         selT = (2 * pp) | ((2 * pp + 1) << 4) | ((2 * pp) << 8) | ((2 * pp + 1) << 12);
         low = p < 2;
-        k_lane = b * 256 + 64 * p;
     }
 
-    template <int MT, bool XS, int SS>
-    __device__ __forceinline__ void step(uint32_t slot, int i, int part, const XCtx &xc, float *acc) const
+    // step i of the slot against part `part` of the staged row (sx = shared address of the row, K its length)
+    template <int SS>
+    __device__ __forceinline__ void step(uint32_t slot, int i, int part, uint32_t sx, int K, float &acc) const
     {
         slot += i * 1152;
         const uint4 hdr = lds128(slot + blk_off), q0 = lds128(slot + q_off), q1 = lds128(slot + q_off + 16);
@@ -338,134 +356,92 @@ struct MathQ4K {
         const float d = smc_h2f((uint16_t)(hdr.x & 0xFFFF));
         const float dmin = smc_h2f((uint16_t)(hdr.x >> 16));
         const uint32_t M4 = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u;
-        const uint32_t l0 = q0.x & M4, l1 = q0.y & M4, l2 = q0.z & M4, l3 = q0.w & M4;
-        const uint32_t l4 = q1.x & M4, l5 = q1.y & M4, l6 = q1.z & M4, l7 = q1.w & M4;
-        const uint32_t h0 = q0.x & MH, h1 = q0.y & MH, h2 = q0.z & MH, h3 = q0.w & MH;
-        const uint32_t h4 = q1.x & MH, h5 = q1.y & MH, h6 = q1.z & MH, h7 = q1.w & MH;
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            uint4 a0, a1, c0, c1;
-            float2 dx, sdx;
-            if (XS) {
-                const uint32_t xb = xc.sx + part * 2048;
-                a0 = lds128(xb + xo[0]), a1 = lds128(xb + xo[1]), c0 = lds128(xb + xo[2]), c1 = lds128(xb + xo[3]);
-                const uint32_t db = xc.sx + xc.K + part * 256 + dx_off;
-                const uint2 t0 = lds64(db), t1 = lds64(db + (xc.K >> 3));
-                dx = make_float2(__uint_as_float(t0.x), __uint_as_float(t0.y));
-                sdx = make_float2(__uint_as_float(t1.x), __uint_as_float(t1.y));
-            } else {
-                const int mm = min(xc.m0 + m, xc.M - 1);
-                const int k0 = part * 2048 + k_lane;
-                const uint4 *xq = reinterpret_cast<const uint4 *>(xc.g.q + (size_t)mm * xc.K + k0);
-                a0 = __ldg(xq), a1 = __ldg(xq + 1), c0 = __ldg(xq + 2), c1 = __ldg(xq + 3);
-                const size_t b32 = (size_t)mm * (xc.K / 32) + (k0 >> 5);
-                dx = __ldg(reinterpret_cast<const float2 *>(xc.g.d + b32));
-                sdx = __ldg(reinterpret_cast<const float2 *>(xc.g.sd + b32));
-            }
-            int lo = smc_dp4a(l0, a0.x, 0), lo2 = smc_dp4a(l1, a0.y, 0);
-            lo = smc_dp4a(l2, a0.z, lo), lo2 = smc_dp4a(l3, a0.w, lo2);
-            lo = smc_dp4a(l4, a1.x, lo), lo2 = smc_dp4a(l5, a1.y, lo2);
-            lo = smc_dp4a(l6, a1.z, lo), lo2 = smc_dp4a(l7, a1.w, lo2);
-            int hi = smc_dp4a_us(h0, c0.x, 0), hi2 = smc_dp4a_us(h1, c0.y, 0);
-            hi = smc_dp4a_us(h2, c0.z, hi), hi2 = smc_dp4a_us(h3, c0.w, hi2);
-            hi = smc_dp4a_us(h4, c1.x, hi), hi2 = smc_dp4a_us(h5, c1.y, hi2);
-            hi = smc_dp4a_us(h6, c1.z, hi), hi2 = smc_dp4a_us(h7, c1.w, hi2);
-            lo += lo2;
-            hi = (hi + hi2) >> 4;  // every term carried a factor 16: exact
-            const float tsum = fmaf((float)(sc_lo * lo), dx.x, (float)(sc_hi * hi) * dx.y);
-            const float msum = fmaf(mn_lo, sdx.x, mn_hi * sdx.y);
-            acc[m] = fmaf(d, tsum, acc[m]);
-            acc[m] = fmaf(-dmin, msum, acc[m]);
-        }
+        const uint32_t xb = sx + part * 2048;
+        const uint4 a0 = lds128(xb + xo[0]), a1 = lds128(xb + xo[1]), c0 = lds128(xb + xo[2]), c1 = lds128(xb + xo[3]);
+        const uint32_t db = sx + K + part * 256 + dx_off;
+        const uint2 t0 = lds64(db), t1 = lds64(db + (K >> 3));
+        const float2 dx = make_float2(__uint_as_float(t0.x), __uint_as_float(t0.y));
+        const float2 sdx = make_float2(__uint_as_float(t1.x), __uint_as_float(t1.y));
+        int lo = smc_dp4a(q0.x & M4, a0.x, 0), lo2 = smc_dp4a(q0.y & M4, a0.y, 0);
+        lo = smc_dp4a(q0.z & M4, a0.z, lo), lo2 = smc_dp4a(q0.w & M4, a0.w, lo2);
+        lo = smc_dp4a(q1.x & M4, a1.x, lo), lo2 = smc_dp4a(q1.y & M4, a1.y, lo2);
+        lo = smc_dp4a(q1.z & M4, a1.z, lo), lo2 = smc_dp4a(q1.w & M4, a1.w, lo2);
+        // high nibbles are dotted in place: every term carries a factor 16, taken out exactly afterwards
+        int hi = smc_dp4a_us(q0.x & MH, c0.x, 0), hi2 = smc_dp4a_us(q0.y & MH, c0.y, 0);
+        hi = smc_dp4a_us(q0.z & MH, c0.z, hi), hi2 = smc_dp4a_us(q0.w & MH, c0.w, hi2);
+        hi = smc_dp4a_us(q1.x & MH, c1.x, hi), hi2 = smc_dp4a_us(q1.y & MH, c1.y, hi2);
+        hi = smc_dp4a_us(q1.z & MH, c1.z, hi), hi2 = smc_dp4a_us(q1.w & MH, c1.w, hi2);
+        lo += lo2;
+        hi = (hi + hi2) >> 4;
+        const float tsum = fmaf((float)(sc_lo * lo), dx.x, (float)(sc_hi * hi) * dx.y);
+        const float msum = fmaf(mn_lo, sdx.x, mn_hi * sdx.y);
+        acc = fmaf(d, tsum, acc);
+        acc = fmaf(-dmin, msum, acc);
     }
 };
 
 // ------------------------------------------------------------------------------------------------ Q6_K
 struct MathQ6K {
     static constexpr int STEP_ELEMS = 2048;
-    static constexpr int PIECES = 4;  // ql, qh, scales, d of 8 blocks
-    static constexpr uint32_t STEP_BYTES = 1680;
-    static __host__ __device__ constexpr uint32_t piece_bytes(int i) { return i == 0 ? 1024 : (i == 1 ? 512 : (i == 2 ? 128 : 16)); }
-    static __host__ __device__ constexpr uint32_t piece_off(int i) { return i == 0 ? 0 : (i == 1 ? 1024 : (i == 2 ? 1536 : 1664)); }
+    static constexpr int PIECES = 1;  // one unit of the layout in smc_common.cuh
+    static constexpr uint32_t STEP_BYTES = SMC_Q6U_BYTES;
+    static __host__ __device__ constexpr uint32_t piece_bytes(int) { return SMC_Q6U_BYTES; }
+    static __host__ __device__ constexpr uint32_t piece_off(int) { return 0; }
     static constexpr bool SD = false, S16 = true;
-    // a quarter warp reads chunks 16*b + 8*h + e + 2*cc (two b, two h, two e, fixed cc)
+    // a quarter warp reads chunks 16*b + 8*h + o + 2*c (two b, two h, two o, fixed c)
     static __host__ __device__ __forceinline__ int swz(int c) { return c ^ (((c >> 3) & 3) << 1); }
 
-    uint32_t a_off, h_off, sc_off, d_off;
-    uint32_t xo[4], dx_off, s16_off;
-    int odd, ssel, k_half, l0;
+    uint32_t w_off, sc_off, d_off;
+    uint32_t xo[4], dx_off, m32_off;
+    int odd;
 
     __device__ __forceinline__ void init(int lane)
     {
         const int b = lane >> 2, r = lane & 3, h = r >> 1;
         odd = r & 1;
-        l0 = 16 * odd;
-        a_off = b * 128 + 64 * h + l0;   // offsets inside each piece of one step
-        h_off = b * 64 + 32 * h + l0;
-        sc_off = b * 16 + 8 * h;
-        d_off = 2 * b;
+        w_off = 16 * lane;  // lane slot 4b + 2h + o is the lane itself
+        sc_off = SMC_Q6U_SC + b * 16 + 8 * h;
+        d_off = SMC_Q6U_D + 2 * b;
         const int c = 16 * b + 8 * h + odd;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) xo[cc] = 16 * swz(c + 2 * cc);
         dx_off = (8 * b + 4 * h) * 4;
-        s16_off = (16 * b + 8 * h) * 2;
-        ssel = odd ? 0 : 16;  // left shift that brings the wanted int16 of a pair to the top
-        k_half = b * 256 + 128 * h;
+        m32_off = (2 * b + h) * 32 + odd * 16;
     }
 
-    template <int MT, bool XS, int SS>
-    __device__ __forceinline__ void step(uint32_t slot, int i, int part, const XCtx &xc, float *acc) const
+    template <int SS>
+    __device__ __forceinline__ void step(uint32_t slot, int i, int part, uint32_t sx, int K, float &acc) const
     {
-        const uint32_t pa = slot + i * 1024 + a_off;
-        const uint4 ua = lds128(pa), ub = lds128(pa + 32), uh = lds128(slot + SS * 1024 + i * 512 + h_off);
-        const uint2 usc = lds64(slot + SS * 1536 + i * 128 + sc_off);
-        const float d = smc_h2f((uint16_t)lds16u(slot + SS * 1664 + i * 16 + d_off));
-        const uint32_t M4 = 0x0F0F0F0Fu, M2 = 0x30303030u;
-        const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w}, wh[4] = {uh.x, uh.y, uh.z, uh.w};
-        uint32_t q[4][4];  // [column c][word j]: six-bit codes of elements 32c + l0 + 4j .. +3
+        slot += i * SMC_Q6U_BYTES;
+        const uint4 X = lds128(slot + w_off), Y = lds128(slot + SMC_Q6U_Y + w_off), Z = lds128(slot + SMC_Q6U_Z + w_off);
+        const uint2 usc = lds64(slot + sc_off);
+        const float d = smc_h2f((uint16_t)lds16u(slot + d_off));
+        const uint32_t wx[4] = {X.x, X.y, X.z, X.w}, wy[4] = {Y.x, Y.y, Y.z, Y.w}, wz[4] = {Z.x, Z.y, Z.z, Z.w};
+        uint32_t q[4][4];  // [word j][column c]
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            q[0][j] = (wa[j] & M4) | ((wh[j] << 4) & M2);
-            q[1][j] = (wb[j] & M4) | ((wh[j] << 2) & M2);
-            q[2][j] = ((wa[j] >> 4) & M4) | (wh[j] & M2);
-            q[3][j] = ((wb[j] >> 4) & M4) | ((wh[j] >> 2) & M2);
+        for (int j = 0; j < 4; ++j) smc_q6u_codes(wx[j], wy[j], wz[j], q[j]);
+        const uint32_t xb = sx + part * 2048;
+        // sum (q - 32) x = sum q x - 32 sum x: the second term is the chain's starting value
+        const uint4 mu = lds128(sx + K + (K >> 3) + part * 512 + m32_off);
+        int s[4] = {(int)mu.x, (int)mu.y, (int)mu.z, (int)mu.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint4 x = lds128(xb + xo[c]);
+            s[c] = smc_dp4a(q[0][c], x.x, s[c]);
+            s[c] = smc_dp4a(q[1][c], x.y, s[c]);
+            s[c] = smc_dp4a(q[2][c], x.z, s[c]);
+            s[c] = smc_dp4a(q[3][c], x.w, s[c]);
         }
-        // int8 scales is + {0, 2, 4, 6} with is = l0 / 16: bytes odd, odd+2, odd+4, odd+6 of the half's eight
+        const uint4 dxu = lds128(sx + K + part * 256 + dx_off);
+        // int8 scales is + {0, 2, 4, 6} with is = o: bytes o, o+2, o+4, o+6 of the half's eight
         const uint32_t sw0 = odd ? (usc.x >> 8) : usc.x, sw1 = odd ? (usc.y >> 8) : usc.y;
         const int scl[4] = {(int)(int8_t)(sw0 & 0xFF), (int)(int8_t)((sw0 >> 16) & 0xFF), (int)(int8_t)(sw1 & 0xFF),
                             (int)(int8_t)((sw1 >> 16) & 0xFF)};
+        const float dxs[4] = {__uint_as_float(dxu.x), __uint_as_float(dxu.y), __uint_as_float(dxu.z), __uint_as_float(dxu.w)};
+        float rsum = 0.f;
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            uint4 x[4], dxu, sw;
-            if (XS) {
-                const uint32_t xb = xc.sx + part * 2048;
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc) x[cc] = lds128(xb + xo[cc]);
-                dxu = lds128(xc.sx + xc.K + part * 256 + dx_off);
-                sw = lds128(xc.sx + xc.K + (xc.K >> 2) + part * 256 + s16_off);
-            } else {
-                const int mm = min(xc.m0 + m, xc.M - 1);
-                const int kb = part * 2048 + k_half;
-                const int8_t *xq = xc.g.q + (size_t)mm * xc.K + kb + l0;
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc) x[cc] = __ldg(reinterpret_cast<const uint4 *>(xq + 32 * cc));
-                dxu = __ldg(reinterpret_cast<const uint4 *>(xc.g.d + (size_t)mm * (xc.K / 32) + (kb >> 5)));
-                sw = __ldg(reinterpret_cast<const uint4 *>(xc.g.s16 + (size_t)mm * (xc.K / 16) + (kb >> 4)));
-            }
-            const uint32_t sws[4] = {sw.x, sw.y, sw.z, sw.w};
-            const float dxs[4] = {__uint_as_float(dxu.x), __uint_as_float(dxu.y), __uint_as_float(dxu.z),
-                                  __uint_as_float(dxu.w)};
-            float rsum = 0.f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                int s = smc_dp4a(q[c][0], x[c].x, 0), s2 = smc_dp4a(q[c][1], x[c].y, 0);
-                s = smc_dp4a(q[c][2], x[c].z, s), s2 = smc_dp4a(q[c][3], x[c].w, s2);
-                const int sxq = ((int)(sws[c] << ssel)) >> 16;  // sum of the 16 activation quants
-                s = s + s2 - 32 * sxq;                           // sum (q - 32) x = sum q x - 32 sum x
-                rsum = fmaf((float)(scl[c] * s), dxs[c], rsum);
-            }
-            acc[m] = fmaf(d, rsum, acc[m]);
-        }
+        for (int c = 0; c < 4; ++c) rsum = fmaf((float)(scl[c] * s[c]), dxs[c], rsum);
+        acc = fmaf(d, rsum, acc);
     }
 };
 
@@ -482,155 +458,174 @@ struct MathQ8_0 {
     static __host__ __device__ __forceinline__ int swz(int c) { return c; }
 
     uint32_t qa_off, qb_off, d_off, dx_off;
-    int sel, k_lane;
     __device__ __forceinline__ void init(int lane)
     {
-        sel = (lane >> 2) & 1;
+        const int sel = (lane >> 2) & 1;
         qa_off = 32 * lane + 16 * sel;
         qb_off = 32 * lane + 16 * (1 - sel);
         d_off = 2 * lane;
         dx_off = 4 * lane;
-        k_lane = 32 * lane;
     }
-    template <int MT, bool XS, int SS>
-    __device__ __forceinline__ void step(uint32_t slot, int i, int part, const XCtx &xc, float *acc) const
+    template <int SS>
+    __device__ __forceinline__ void step(uint32_t slot, int i, int part, uint32_t sx, int K, float &acc) const
     {
         const uint4 q0 = lds128(slot + i * 1024 + qa_off), q1 = lds128(slot + i * 1024 + qb_off);
         const float d = smc_h2f((uint16_t)lds16u(slot + SS * 1024 + i * 64 + d_off));
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            uint4 a0, a1;
-            float dx;
-            if (XS) {
-                const uint32_t xb = xc.sx + part * 1024;
-                a0 = lds128(xb + qa_off), a1 = lds128(xb + qb_off);
-                dx = __uint_as_float(lds32(xc.sx + xc.K + part * 128 + dx_off));
-            } else {
-                const int mm = min(xc.m0 + m, xc.M - 1);
-                const int k0 = part * 1024 + k_lane;
-                const uint4 *xq = reinterpret_cast<const uint4 *>(xc.g.q + (size_t)mm * xc.K + k0);
-                a0 = __ldg(xq + sel), a1 = __ldg(xq + 1 - sel);
-                dx = __ldg(xc.g.d + (size_t)mm * (xc.K / 32) + (k0 >> 5));
-            }
-            int s = smc_dp4a(q0.x, a0.x, 0), s2 = smc_dp4a(q0.y, a0.y, 0);
-            s = smc_dp4a(q0.z, a0.z, s), s2 = smc_dp4a(q0.w, a0.w, s2);
-            s = smc_dp4a(q1.x, a1.x, s), s2 = smc_dp4a(q1.y, a1.y, s2);
-            s = smc_dp4a(q1.z, a1.z, s), s2 = smc_dp4a(q1.w, a1.w, s2);
-            acc[m] = fmaf(d * dx, (float)(s + s2), acc[m]);
-        }
+        const uint32_t xb = sx + part * 1024;
+        const uint4 a0 = lds128(xb + qa_off), a1 = lds128(xb + qb_off);
+        const float dx = __uint_as_float(lds32(sx + K + part * 128 + dx_off));
+        int s = smc_dp4a(q0.x, a0.x, 0), s2 = smc_dp4a(q0.y, a0.y, 0);
+        s = smc_dp4a(q0.z, a0.z, s), s2 = smc_dp4a(q0.w, a0.w, s2);
+        s = smc_dp4a(q1.x, a1.x, s), s2 = smc_dp4a(q1.y, a1.y, s2);
+        s = smc_dp4a(q1.z, a1.z, s), s2 = smc_dp4a(q1.w, a1.w, s2);
+        acc = fmaf(d * dx, (float)(s + s2), acc);
     }
 };
 
 // ------------------------------------------------------------------------------------------------
-// Work is handed out in "groups" of whole rows so that a row's partial sums never leave its warp:
-// a stage is SS consecutive steps; when a row is shorter than a stage (spr <= SS) a group is SS/spr
-// rows = one stage, otherwise a group is one row = spr/SS stages.  Warp w of W takes groups
-// w, w + W, w + 2W, ...: at any moment the grid reads one dense window that slides through the matrix.
-template <class Math, int MT, int MINB, int SS, bool GATHER>
-__global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs xg, float *__restrict__ out, int N, int K,
-                                                             int M, int slots, int *__restrict__ status,
-                                                             const smc_gather_dev *gd)
+template <class Math, int MINB, int SS, bool GATHER>
+__global__ void __launch_bounds__(WARPS * 32, MINB) gemv_tma_kernel(StepSrc src, XPtrs xg, float *__restrict__ out, int N, int K,
+                                                                    int slots, int *__restrict__ status, const smc_gather_dev *gd)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     int sending = -1;      // whether packets go out, known after the first look at the peers' ready flags (warp uniform)
     unsigned gtag = 0;     // number of the running exchange
-    constexpr bool XS = (MT == 1);
     constexpr uint32_t SLOT = (Math::STEP_BYTES * SS + 127u) & ~127u;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int m0 = blockIdx.y * MT;
 
-    // shared layout: [x row (M = 1)] [8 warps x slots x SLOT bytes] [8 warps x slots barriers]
-    const uint32_t xb = XS ? (uint32_t)((x_bytes(K) + 127) & ~(size_t)127) : 0u;
+    // shared layout: [x row] [8 warps x slots x SLOT bytes] [8 warps x slots ring barriers] [8 x 32 floats handed
+    // from warp w-1 to warp w] [8 hand-over barriers]
+    const uint32_t xb = (uint32_t)((x_bytes<Math>(K) + 127) & ~(size_t)127);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t ring = sbase + xb + (uint32_t)(warp * slots) * SLOT;
     const uint32_t bars = sbase + xb + (uint32_t)(WARPS * slots) * SLOT + (uint32_t)(warp * slots) * 8u;
+    const uint32_t hand = sbase + xb + (uint32_t)(WARPS * slots) * (SLOT + 8u);  // + 128 * warp
+    const uint32_t hbar = hand + WARPS * 128u;                                     // + 8 * warp
 
-    const int spr = K / Math::STEP_ELEMS;            // steps per row
-    const int rg = SS >= spr ? SS / spr : 1;         // rows per group
-    const int spg = SS >= spr ? 1 : spr / SS;        // stages per group
-    const int W = gridDim.x * WARPS, w = blockIdx.x * WARPS + warp;
-    const int ngroups = N / rg;
-    const int mine = w < ngroups ? (ngroups - w + W - 1) / W : 0;
-    const int nstages = mine * spg;
+    // this CTA's rows, and this warp's piece [s0, s1) of their steps
+    const int spr = K / Math::STEP_ELEMS;  // steps per row
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int rbase = N / G, rrem = N - rbase * G;
+    const int R0 = cta * rbase + min(cta, rrem), nrows = rbase + (cta < rrem ? 1 : 0);
+    const int T = nrows * spr;
+    const int Wa = T < WARPS ? T : WARPS;  // warps that get work
+    int s0 = 0, s1 = 0;
+    if (warp < Wa) {
+        s0 = (int)((long long)T * warp / Wa);
+        s1 = (int)((long long)T * (warp + 1) / Wa);
+    }
+    // processing order: [tb, s1) the start of a row the next warp finishes, [hb, tb) whole rows, [s0, hb) the end of a
+    // row the previous warp started.  A piece that lies inside one row is all "end of row" and is handed on.
+    const int hb = (s0 % spr == 0) ? s0 : min(s1, (s0 / spr + 1) * spr);
+    const int tb = (s1 % spr == 0) ? s1 : max(hb, (s1 / spr) * spr);
+    const int segb[3] = {tb, hb, s0}, sege[3] = {s1, tb, hb};
+    const long long gstep0 = (long long)R0 * spr;
 
     if (lane == 0) {
         for (int s = 0; s < slots; ++s) mbar_init(bars + 8 * s, 1);
+        mbar_init(hbar + 8 * warp, 1);
         fence_barrier_init();
     }
     __syncwarp();
-    // producer cursor (lane 0): global index of the next stage to fetch
-    long long pstage = (long long)w * spg;
-    int pin = 0, issued = 0;
-    auto fetch_next = [&](uint32_t saddr, uint32_t bar) {
-        issue_stage<Math, SS>(src, pstage, saddr, bar);
-        ++issued;
-        ++pstage;
-        if (++pin == spg) {
-            pin = 0;
-            pstage += (long long)(W - 1) * spg;
+    // producer cursor (used by lane 0): segment and step of the next stage to fetch
+    int pseg = 0, ps = segb[0], issued = 0;
+    auto fetch_next = [&](uint32_t saddr, uint32_t bar) -> bool {
+        while (pseg < 3 && ps >= sege[pseg]) {
+            ++pseg;
+            if (pseg < 3) ps = segb[pseg];
         }
+        if (pseg >= 3) return false;
+        const int n = min(SS, sege[pseg] - ps);
+        issue_stage<Math, SS>(src, gstep0 + ps, n, saddr, bar);
+        ps += n;
+        ++issued;
+        return true;
     };
-    if (lane == 0) {
-        const int pre = nstages < slots ? nstages : slots;
-        for (int t = 0; t < pre; ++t) fetch_next(ring + (uint32_t)t * SLOT, bars + 8 * t);
-    }
+    if (lane == 0)
+        for (int t = 0; t < slots; ++t)
+            if (!fetch_next(ring + (uint32_t)t * SLOT, bars + 8 * t)) break;
     // The weight stages requested above do not depend on earlier launches; everything below does (activations,
     // the output buffer, the exchange counters), so this is where a dependent launch waits for its predecessor.
     smc_grid_dep_sync();
-    // row-split across GPUs (one row only): tell the peers that this rank's readers of the previous exchange are done
+    // row-split across GPUs: tell the peers that this rank's readers of the previous exchange are done
     if (GATHER && blockIdx.x == 0 && threadIdx.x == 32) smc_gather_post_ready(gd);
-    if (XS) {
-        if (xg.nw) stage_x_addnorm_quant<Math>(xg.xf, xg.xadd, xg.nw, xg.eps, blockIdx.x == 0 ? xg.xsum : nullptr, K, smem);
-        else if (xg.xf) stage_x_quant<Math>(xg.xf, xg.xu, K, smem);
-        else stage_x<Math>(xg, m0, K, smem);
-        __syncthreads();
-    }
+    if (xg.nw) stage_x_addnorm_quant<Math>(xg.xf, xg.xadd, xg.nw, xg.eps, blockIdx.x == 0 ? xg.xsum : nullptr, K, smem);
+    else if (xg.xf) stage_x_quant<Math>(xg.xf, xg.xu, K, smem);
+    else stage_x<Math>(xg, K, smem);
+    __syncthreads();  // the row is staged, and every warp's hand-over barrier is initialised
 
     Math math;
     math.init(lane);
-    XCtx xc{sbase, K, m0, M, xg};
-    float acc[MT];
-#pragma unroll
-    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
-
-    int slot = 0, part = 0, row = w * rg, cin = 0;
+    float acc = 0.f;
+    int slot = 0, consumed = 0;
     uint32_t phase = 0;
-    for (int t = 0; t < nstages; ++t) {
-        const uint32_t bar = bars + 8 * slot;
-        const uint32_t saddr = ring + (uint32_t)slot * SLOT;
-        if (!mbar_wait(bar, phase)) {
-            if (lane == 0) atomicExch(status, 1);
-            break;
-        }
-#pragma unroll
-        for (int i = 0; i < SS; ++i) {
-            math.template step<MT, XS, SS>(saddr, i, part, xc, acc);
-            if (++part == spr) {
-                if (XS && GATHER && sending < 0) {  // first finished row of this warp: the peers' ready flags, one lane each
-                    gtag = smc_gather_tag(gd);
-                    sending = smc_gather_wait_ready_warp(gd, gtag) ? 1 : 0;
-                }
-#pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    const float v = warp_sum32(acc[m]);  // every lane holds the sum
-                    if (lane == 0 && m0 + m < M) out[(size_t)(m0 + m) * N + row] = v;
-                    // this rank's chunk starts at rank * N in every peer's buffer; lane p sends to peer p
-                    if (XS && GATHER && sending) smc_gather_send_warp(gd, (size_t)N, (size_t)row, v, gtag);
-                    acc[m] = 0.f;
-                }
-                part = 0;
-                ++row;
+    bool dead = false;
+    for (int sg = 0; sg < 3 && !dead; ++sg) {
+        int s = segb[sg];
+        const int e = sege[sg];
+        if (s >= e) continue;
+        int part = s % spr, row = R0 + s / spr;
+        if (sg == 2) {  // the lane sums of the row's first steps, left by the previous warp
+            if (!__all_sync(0xffffffffu, mbar_wait(hbar + 8 * warp, 0))) {
+                if (lane == 0) atomicExch(status, 1);
+                dead = true;
+                break;
             }
+            acc = __uint_as_float(lds32(hand + 128 * warp + 4 * lane));
         }
-        __syncwarp();  // every lane has read the slot: it may be refilled
-        if (lane == 0 && issued < nstages) fetch_next(saddr, bar);
-        if (++slot == slots) {
-            slot = 0;
-            phase ^= 1;
+        while (s < e) {
+            const int n = min(SS, e - s);
+            const uint32_t bar = bars + 8 * slot;
+            const uint32_t saddr = ring + (uint32_t)slot * SLOT;
+            if (!__all_sync(0xffffffffu, mbar_wait(bar, phase))) {  // one decision for the warp
+                if (lane == 0) atomicExch(status, 1);
+                dead = true;
+                break;
+            }
+            ++consumed;
+#pragma unroll
+            for (int i = 0; i < SS; ++i) {
+                if (i < n) {
+                    math.template step<SS>(saddr, i, part, sbase, K, acc);
+                    if (++part == spr) {
+                        if (GATHER && sending < 0) {  // first finished row of this warp: the peers' ready flags, one lane each
+                            gtag = smc_gather_tag(gd);
+                            sending = smc_gather_wait_ready_warp(gd, gtag) ? 1 : 0;
+                        }
+                        const float v = warp_sum32(acc);  // every lane holds the sum
+                        if (lane == 0) out[row] = v;
+                        // this rank's chunk starts at rank * N in every peer's buffer; lane p sends to peer p
+                        if (GATHER && sending) smc_gather_send_warp(gd, (size_t)N, (size_t)row, v, gtag);
+                        acc = 0.f;
+                        part = 0;
+                        ++row;
+                    }
+                }
+            }
+            __syncwarp();  // every lane has read the slot: it may be refilled
+            if (lane == 0) fetch_next(saddr, bar);
+            if (++slot == slots) {
+                slot = 0;
+                phase ^= 1;
+            }
+            s += n;
         }
-        if (++cin == spg) {
-            cin = 0;
-            row += (W - 1) * rg;
+        if (!dead && part != 0) {  // an unfinished row: the next warp continues from these sums
+            sts32(hand + 128 * (warp + 1) + 4 * lane, __float_as_uint(acc));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(hbar + 8 * (warp + 1));
+            acc = 0.f;
+        }
+    }
+    if (dead) {
+        // copies already requested still target this CTA's shared memory: wait for them (bounded) before leaving
+        const int pending = __shfl_sync(0xffffffffu, issued, 0) - consumed;
+        for (int t = 0; t < pending; ++t) {
+            mbar_wait(bars + 8 * slot, phase);
+            if (++slot == slots) {
+                slot = 0;
+                phase ^= 1;
+            }
         }
     }
     // rows done: unpack this CTA's stripe of the peers' slices as they arrive
@@ -640,89 +635,54 @@ __global__ void __launch_bounds__(256, MINB) gemv_tma_kernel(StepSrc src, XPtrs 
     }
 }
 
-struct Tuning {
-    int slots = 2;        // ring depth per warp, in stages (measured best: 2 x 2 steps, 3 CTAs per SM)
-    int ctas_per_sm = 3;  // resident CTAs the grid is sized for (M = 1)
-    int ss = 2;           // steps per stage (M = 1): 1, 2 or 4
-};
-
-Tuning tuning()
-{
-    static Tuning t = [] {
-        Tuning v;
-        if (const char *e = getenv("SMC_TMA_SLOTS")) v.slots = atoi(e) > 1 ? atoi(e) : v.slots;
-        if (const char *e = getenv("SMC_TMA_CTAS")) v.ctas_per_sm = atoi(e) > 0 ? atoi(e) : v.ctas_per_sm;
-        if (const char *e = getenv("SMC_TMA_SS")) v.ss = atoi(e) > 0 ? atoi(e) : v.ss;
-        return v;
-    }();
-    return t;
-}
-
-template <class Math, int MT, int MINB, int SS>
+template <class Math, int MINB, int SS>
 void launch_one(smc_ctx *ctx, dim3 grid, size_t smem, cudaStream_t s, const StepSrc &src, const XPtrs &x, float *out, int N,
-                int K, int M, int slots, const smc_gather_dev *gd)
+                int K, int slots, const smc_gather_dev *gd)
 {
-    if (MT == 1 && gd) {
-        cudaFuncSetAttribute(gemv_tma_kernel<Math, MT, MINB, SS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, MT, MINB, SS, true>, grid, dim3(256), smem, s, src, x, out, N, K, M, slots,
+    if (gd) {
+        cudaFuncSetAttribute(gemv_tma_kernel<Math, MINB, SS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, MINB, SS, true>, grid, dim3(WARPS * 32), smem, s, src, x, out, N, K, slots,
                        ctx->d_status, gd);
         return;
     }
-    cudaFuncSetAttribute(gemv_tma_kernel<Math, MT, MINB, SS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, MT, MINB, SS, false>, grid, dim3(256), smem, s, src, x, out, N, K, M, slots,
+    cudaFuncSetAttribute(gemv_tma_kernel<Math, MINB, SS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, MINB, SS, false>, grid, dim3(WARPS * 32), smem, s, src, x, out, N, K, slots,
                    ctx->d_status, (const smc_gather_dev *)nullptr);
 }
 
 template <class Math>
-int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, int N, int K, int M, cudaStream_t s,
+int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, int N, int K, cudaStream_t s,
                 const smc_gather_dev *gd)
 {
-    const Tuning tn = tuning();
-    const int mt = M == 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8));
-    const int spr = K / Math::STEP_ELEMS;
-    // steps per stage: the largest of 4, 2, 1 allowed by the tuning that tiles rows exactly
-    int ss = 1;
-    if (mt == 1)
-        for (int c = 4; c >= 2; c >>= 1) {
-            if (c > tn.ss) continue;
-            const bool tiles = (c >= spr) ? (c % spr == 0 && N % (c / spr) == 0) : (spr % c == 0);
-            if (tiles) {
-                ss = c;
-                break;
-            }
-        }
-    const size_t xb = mt == 1 ? ((x_bytes(K) + 127) & ~(size_t)127) : 0;
-    const size_t slot_bytes = ((size_t)Math::STEP_BYTES * ss + 127) & ~(size_t)127;
-    int per_sm = mt == 1 ? tn.ctas_per_sm : 2;
-    int slots = tn.slots;
-    // `per_sm` CTAs must fit in the 227 KB of an SM (1 KB per CTA is reserved by the system)
-    auto need = [&](int sl) { return xb + (size_t)WARPS * sl * (slot_bytes + 8); };
-    while (per_sm > 1 && (need(slots) + 1024) * per_sm > 227 * 1024) {
-        if (slots > 3) --slots;
-        else --per_sm;
+    // ring geometry: `slots` stages of `ss` steps per warp, `per_sm` resident CTAs the grid is sized for
+    int slots = ctx->tma_slots ? ctx->tma_slots : 2;
+    int ss = ctx->tma_ss ? ctx->tma_ss : 2;
+    int per_sm = ctx->tma_ctas ? ctx->tma_ctas : 3;
+    const size_t xb = (x_bytes<Math>(K) + 127) & ~(size_t)127;
+    auto need = [&](int sl, int st) {
+        const size_t slot_bytes = ((size_t)Math::STEP_BYTES * st + 127) & ~(size_t)127;
+        return xb + (size_t)WARPS * sl * (slot_bytes + 8) + (size_t)WARPS * 136;
+    };
+    // `per_sm` CTAs must fit in the 227 KB of an SM (1 KB per CTA is reserved by the system): a long activation row
+    // first costs ring depth, then stage length, then resident CTAs
+    while ((need(slots, ss) + 1024) * per_sm > 227 * 1024) {
+        if (slots > 2) --slots;
+        else if (ss > 1) ss >>= 1;
+        else if (per_sm > 1) --per_sm;
+        else break;
     }
-    const size_t smem = need(slots);
+    const size_t smem = need(slots, ss);
     if (smem > 226 * 1024) return smc_fail(ctx, SMC_E_UNSUPPORTED, "K = %d needs %zu bytes of shared memory", K, smem);
-    const int rg = ss >= spr ? ss / spr : 1;
-    const int ngroups = N / rg;
-    int warps = ctx->sm_count * per_sm * WARPS;
-    if (warps > ngroups) warps = ngroups;
-    dim3 grid((warps + WARPS - 1) / WARPS, (M + mt - 1) / mt);
-    if (mt == 1) {
-        const bool three = per_sm >= 3;
-        if (ss == 4) three ? launch_one<Math, 1, 3, 4>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd)
-                           : launch_one<Math, 1, 2, 4>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
-        else if (ss == 2) three ? launch_one<Math, 1, 3, 2>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd)
-                                : launch_one<Math, 1, 2, 2>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
-        else three ? launch_one<Math, 1, 3, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd)
-                   : launch_one<Math, 1, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
-    } else if (mt == 2) {
-        launch_one<Math, 2, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
-    } else if (mt == 4) {
-        launch_one<Math, 4, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
-    } else {
-        launch_one<Math, 8, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, M, slots, gd);
-    }
+    int ctas = ctx->sm_count * per_sm;
+    if (ctas > N) ctas = N;
+    const dim3 grid(ctas);
+    const bool three = per_sm >= 3;
+    if (ss == 4) three ? launch_one<Math, 3, 4>(ctx, grid, smem, s, src, x, out, N, K, slots, gd)
+                       : launch_one<Math, 2, 4>(ctx, grid, smem, s, src, x, out, N, K, slots, gd);
+    else if (ss == 2) three ? launch_one<Math, 3, 2>(ctx, grid, smem, s, src, x, out, N, K, slots, gd)
+                            : launch_one<Math, 2, 2>(ctx, grid, smem, s, src, x, out, N, K, slots, gd);
+    else three ? launch_one<Math, 3, 1>(ctx, grid, smem, s, src, x, out, N, K, slots, gd)
+               : launch_one<Math, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, slots, gd);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
@@ -731,87 +691,70 @@ int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, in
 
 bool smc_tma_supported(const smc_weight *w, int M)
 {
-    if (!w->fast || M < 1) return false;
-    if (w->dtype == SMC_Q8_0) return w->K % 1024 == 0 && w->K <= 65536;
-    return w->K % 2048 == 0 && w->K <= 65536;
+    if (!w->fast || M != 1) return false;
+    if (w->dtype == SMC_Q8_0) return w->K % 1024 == 0 && w->K <= 65536 && w->q8_qs != nullptr;
+    if (w->dtype == SMC_Q6_K) return w->K % 2048 == 0 && w->K <= 65536 && w->q6u != nullptr;
+    return w->K % 2048 == 0 && w->K <= 65536 && w->d_raw != nullptr;
 }
 
-// M = 1 with fp32 input: the row is quantised inside the kernel, no scratch buffer is involved.
+// fp32 input: the row is quantised inside the kernel, no scratch buffer is involved.
 int smc_launch_gemv_tma_f32in(smc_ctx *ctx, const float *x, const smc_weight *w, float *out, cudaStream_t s)
 {
-    smc_q8act one{};
-    one.M = 1, one.K = w->K;
-    return smc_launch_gemv_tma_x(ctx, &one, x, w, out, s);
+    return smc_launch_gemv_tma_full(ctx, nullptr, x, nullptr, nullptr, w, out, nullptr, s);
 }
 
+// Row 0 of `a`, quantised beforehand.
 int smc_launch_gemv_tma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *out, cudaStream_t s)
 {
-    return smc_launch_gemv_tma_x(ctx, a, nullptr, w, out, s);
-}
-
-int smc_launch_gemv_tma_x(smc_ctx *ctx, const smc_q8act *a, const float *xf, const smc_weight *w, float *out,
-                          cudaStream_t s)
-{
-    return smc_launch_gemv_tma_xg(ctx, a, xf, w, out, nullptr, s);
+    return smc_launch_gemv_tma_full(ctx, a, nullptr, nullptr, nullptr, w, out, nullptr, s);
 }
 
 // One fp32 row, quantised in the kernel, whose output slice is exchanged with the peers in the kernel's tail.
 int smc_launch_gemv_tma_gather(smc_ctx *ctx, const float *x, const smc_weight *w, float *out, const smc_gather_dev *gd,
                                cudaStream_t s)
 {
-    smc_q8act one{};
-    one.M = 1, one.K = w->K;
-    return smc_launch_gemv_tma_xg(ctx, &one, x, w, out, gd, s);
+    return smc_launch_gemv_tma_full(ctx, nullptr, x, nullptr, nullptr, w, out, gd, s);
+}
+
+// The same exchange for a row quantised beforehand.
+int smc_launch_gemv_tma_xg(smc_ctx *ctx, const smc_q8act *a, const float *xf, const smc_weight *w, float *out,
+                           const smc_gather_dev *gd, cudaStream_t s)
+{
+    return smc_launch_gemv_tma_full(ctx, a, xf, nullptr, nullptr, w, out, gd, s);
 }
 
 // One row whose activation is SiLU(gate) * up, formed and quantised while the row is staged.
 int smc_launch_gemv_tma_swiglu(smc_ctx *ctx, const float *gate, const float *up, const smc_weight *w, float *out, cudaStream_t s)
 {
-    smc_q8act one{};
-    one.M = 1, one.K = w->K;
-    return smc_launch_gemv_tma_xgu(ctx, &one, gate, up, w, out, nullptr, s);
-}
-
-int smc_launch_gemv_tma_xg(smc_ctx *ctx, const smc_q8act *a, const float *xf, const smc_weight *w, float *out,
-                           const smc_gather_dev *gd, cudaStream_t s)
-{
-    return smc_launch_gemv_tma_xgu(ctx, a, xf, nullptr, w, out, gd, s);
+    return smc_launch_gemv_tma_full(ctx, nullptr, gate, up, nullptr, w, out, nullptr, s);
 }
 
 // One row that is RMSNorm(x + add) * w, formed and quantised while the row is staged; x + add goes to `sum`.
 int smc_launch_gemv_tma_addnorm(smc_ctx *ctx, const float *x, const smc_norm_prologue *pro, const smc_weight *w, float *out,
                                 cudaStream_t s)
 {
-    smc_q8act one{};
-    one.M = 1, one.K = w->K;
-    return smc_launch_gemv_tma_full(ctx, &one, x, nullptr, pro, w, out, nullptr, s);
-}
-
-int smc_launch_gemv_tma_xgu(smc_ctx *ctx, const smc_q8act *a, const float *xf, const float *xu, const smc_weight *w, float *out,
-                            const smc_gather_dev *gd, cudaStream_t s)
-{
-    return smc_launch_gemv_tma_full(ctx, a, xf, xu, nullptr, w, out, gd, s);
+    return smc_launch_gemv_tma_full(ctx, nullptr, x, nullptr, pro, w, out, nullptr, s);
 }
 
 int smc_launch_gemv_tma_full(smc_ctx *ctx, const smc_q8act *a, const float *xf, const float *xu, const smc_norm_prologue *pro,
                              const smc_weight *w, float *out, const smc_gather_dev *gd, cudaStream_t s)
 {
-    const int N = w->N, K = w->K, M = a->M;
-    XPtrs x{a->q, a->d, a->sd, a->s16, xf, xu, nullptr, nullptr, nullptr, 0.f};
+    const int N = w->N, K = w->K;
+    if (!xf && (!a || a->M != 1 || a->K != K)) return smc_fail(ctx, SMC_E_INVALID, "one-row matmul: the activation buffer must hold one row of %d", K);
+    XPtrs x{};
+    if (a) x.q = a->q, x.d = a->d, x.sd = a->sd, x.s16 = a->s16;
+    x.xf = xf, x.xu = xu;
     if (pro) x.xadd = pro->add, x.nw = pro->w, x.xsum = pro->sum, x.eps = pro->eps;
     StepSrc src{};
     if (w->dtype == SMC_Q4_K) {
         src.base[0] = w->d_raw;
-        return launch_math<MathQ4K>(ctx, src, x, out, N, K, M, s, gd);
+        return launch_math<MathQ4K>(ctx, src, x, out, N, K, s, gd);
     }
     if (w->dtype == SMC_Q6_K) {
-        src.base[0] = w->q6_ql;
-        src.base[1] = w->q6_qh;
-        src.base[2] = reinterpret_cast<const uint8_t *>(w->q6_sc);
-        src.base[3] = reinterpret_cast<const uint8_t *>(w->q6_d);
-        return launch_math<MathQ6K>(ctx, src, x, out, N, K, M, s, gd);
+        src.base[0] = w->q6u;
+        return launch_math<MathQ6K>(ctx, src, x, out, N, K, s, gd);
     }
     src.base[0] = reinterpret_cast<const uint8_t *>(w->q8_qs);
     src.base[1] = reinterpret_cast<const uint8_t *>(w->q8_d);
-    return launch_math<MathQ8_0>(ctx, src, x, out, N, K, M, s, gd);
+    return launch_math<MathQ8_0>(ctx, src, x, out, N, K, s, gd);
 }

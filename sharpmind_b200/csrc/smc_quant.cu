@@ -5,7 +5,7 @@
 //   * weight quantisers, bit-exact device forms of TensorQuantizer.WriteBlock (Q8_0,
 //     SharpMind.Core/Quantization/TensorQuantizer.cs:80-144), WriteKQ4 and WriteKQ6
 //     (TensorQuantizer.KQuant.cs:173-225, 303-376) -- they make the synthetic weights;
-//   * the upload-time repack of Q8_0 and Q6_K tensors into 16-byte-aligned planes.
+//   * the upload-time repack of Q8_0 tensors into 16-byte-aligned planes and of Q6_K tensors into 1680-byte units.
 // All arithmetic that decides a code or a scale uses explicit round-to-nearest intrinsics.
 #include "smc_common.cuh"
 
@@ -221,19 +221,28 @@ __global__ void repack_q8_0_kernel(const uint8_t *__restrict__ raw, int8_t *__re
     }
 }
 
-__global__ void repack_q6_K_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ ql, uint8_t *__restrict__ qh,
-                                   int8_t *__restrict__ sc, __half *__restrict__ d, long long nblocks)
+// GGUF Q6_K blocks -> the unit layout of smc_common.cuh.  One thread per (block, half h, byte l of the 32-element
+// columns): it forms the four six-bit codes of elements 128h + 32c + l (c = 0..3, as VecDotQ6K_Scalar reads them,
+// QuantizationKernels.Q6.cs:28-41) and stores the X, Y, Z bytes of its lane slot; the first threads of a block also
+// move its scales and d.
+__global__ void repack_q6_K_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ units, long long nblocks)
 {
     long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (; t < nblocks * 128; t += stride) {
-        long long blk = t >> 7;
-        int i = (int)(t & 127);
+    for (; t < nblocks * 64; t += stride) {
+        const long long blk = t >> 6;
+        const int h = (int)(t >> 5) & 1, l = (int)(t & 31);
         const uint8_t *b = raw + blk * 210;
-        ql[t] = b[i];
-        if (i < 64) qh[blk * 64 + i] = b[128 + i];
-        if (i < 16) sc[blk * 16 + i] = (int8_t)b[192 + i];
-        if (i == 0) d[blk] = __ushort_as_half((uint16_t)(b[208] | (b[209] << 8)));
+        const uint32_t la = b[64 * h + l], lb = b[64 * h + 32 + l], hh = b[128 + 32 * h + l];
+        const uint32_t c0 = (la & 0x0F) | ((hh & 3) << 4), c1 = (lb & 0x0F) | (((hh >> 2) & 3) << 4);
+        const uint32_t c2 = (la >> 4) | (((hh >> 4) & 3) << 4), c3 = (lb >> 4) | (((hh >> 6) & 3) << 4);
+        uint8_t *slot = units + smc_q6u_slot((size_t)blk, h, l >> 4) + (l & 15);
+        slot[0] = (uint8_t)(c0 | ((c3 & 3) << 6));
+        slot[SMC_Q6U_Y] = (uint8_t)(c1 | (((c3 >> 2) & 3) << 6));
+        slot[SMC_Q6U_Z] = (uint8_t)(c2 | (((c3 >> 4) & 3) << 6));
+        const int i = (int)(t & 63);
+        if (i < 16) units[smc_q6u_scales((size_t)blk) + i] = b[192 + i];
+        if (i == 16) *reinterpret_cast<uint16_t *>(units + smc_q6u_d((size_t)blk)) = (uint16_t)(b[208] | (b[209] << 8));
     }
 }
 
@@ -338,12 +347,10 @@ int smc_launch_repack(smc_ctx *ctx, smc_weight *w, cudaStream_t s)
         SMC_LAUNCH_CHECK(ctx);
     } else if (w->dtype == SMC_Q6_K) {
         long long nblocks = (long long)w->N * w->K / 256;
-        SMC_CUDA(ctx, cudaMalloc(&w->q6_ql, (size_t)nblocks * 128));
-        SMC_CUDA(ctx, cudaMalloc(&w->q6_qh, (size_t)nblocks * 64));
-        SMC_CUDA(ctx, cudaMalloc(&w->q6_sc, (size_t)nblocks * 16));
-        SMC_CUDA(ctx, cudaMalloc(&w->q6_d, (size_t)nblocks * sizeof(__half)));
-        repack_q6_K_kernel<<<grid_for(nblocks * 128, 256, ctx->sm_count * 16), 256, 0, s>>>(
-            w->d_raw, w->q6_ql, w->q6_qh, w->q6_sc, w->q6_d, nblocks);
+        SMC_CUDA(ctx, cudaMalloc(&w->q6u, smc_q6u_bytes((size_t)nblocks)));
+        if (nblocks % 8)  // the blocks missing from the last unit read as zero weights
+            SMC_CUDA(ctx, cudaMemsetAsync(w->q6u + smc_q6u_bytes((size_t)nblocks) - SMC_Q6U_BYTES, 0, SMC_Q6U_BYTES, s));
+        repack_q6_K_kernel<<<grid_for(nblocks * 64, 256, ctx->sm_count * 16), 256, 0, s>>>(w->d_raw, w->q6u, nblocks);
         SMC_LAUNCH_CHECK(ctx);
     }
     return SMC_OK;

@@ -111,6 +111,10 @@ class CudaContext:
     def synchronize(self):
         self.check(self.lib.smc_synchronize(self.h))
 
+    def set_option(self, name: str, value: int):
+        """smc_set_option: "pdl", "gemv_slots", "gemv_steps_per_stage", "gemv_ctas_per_sm"."""
+        self.check(self.lib.smc_set_option(self.h, name.encode(), int(value)))
+
     def device_status(self) -> int:
         """Waits for the device; raises if a kernel abandoned a bounded wait since the last call."""
         st = C.c_int(0)

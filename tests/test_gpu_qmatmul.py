@@ -133,6 +133,52 @@ def test_one_row_long_rows_against_oracle(oracle, cuda, dev, dtype, n, k):
     assert cuda.device_status() == 0
 
 
+# The one-row kernel cuts a CTA's rows into equal pieces per warp without regard to row boundaries and continues a
+# row from the lane sums its previous warp left: an output's bits must not depend on how the rows were divided.
+# The ring options change the grid (resident CTAs), the stage length and with them every piece boundary.
+PARTITION_SHAPES = [
+    (Q6_K, 4096, 14336), (Q6_K, 3, 14336), (Q6_K, 37, 6144), (Q4_K, 4096, 4096), (Q4_K, 1, 8192), (Q4_K, 445, 2048),
+    (Q8_0, 1500, 2048), (Q8_0, 7, 5120), (Q8_0, 3072, 1024),
+]
+
+
+@pytest.mark.parametrize("dtype,n,k", PARTITION_SHAPES)
+def test_one_row_bits_do_not_depend_on_the_partition(oracle, cuda, dev, dtype, n, k):
+    import torch
+
+    from sharpmind_b200.ops import Mode
+
+    g = torch.Generator(device="cuda").manual_seed(n * 31 + k)
+    raw_d = dev.quantize_weights(dtype, torch.randn((n, k), generator=g, device="cuda") * 0.02)
+    w = cuda.register_dev(raw_d, dtype, n, k, keep_raw=True)
+    x = to_dev(synth.normal("gpu", f"partx{dtype}_{n}_{k}", (1, k)))
+    try:
+        base = dev.qmatmul(x, w, Mode.ACT_Q8).cpu().numpy()
+        # the exact integer block sums and fp32 scaling of the reference-order-free generic kernel bound it
+        rows = sorted({0, n // 2, n - 1})
+        raw = raw_d.cpu().numpy()
+        xq = oracle.quantize_rows_q8_0(x.cpu().numpy(), 1, k)
+        xhat = oracle.dequantize(Q8_0, xq[0], k)[None, :]
+        per_row = len(raw) // n
+        for r in rows:
+            want = oracle.qmatmul(dtype, xhat, raw, 1, k, n, cols=(r, r + 1))[0, r]
+            wrow = oracle.dequantize(dtype, raw[r * per_row:(r + 1) * per_row], k)
+            assert abs(float(base[0, r]) - float(want)) <= 1e-5 * np.linalg.norm(wrow) * np.linalg.norm(xhat)
+        for opts in ({"gemv_ctas_per_sm": 1}, {"gemv_ctas_per_sm": 2, "gemv_steps_per_stage": 1},
+                     {"gemv_steps_per_stage": 4, "gemv_slots": 3}, {"gemv_ctas_per_sm": 1, "gemv_slots": 4, "pdl": 0}):
+            for name, v in opts.items():
+                cuda.set_option(name, v)
+            try:
+                got = dev.qmatmul(x, w, Mode.ACT_Q8).cpu().numpy()
+            finally:
+                for name in opts:
+                    cuda.set_option(name, 1 if name == "pdl" else 0)
+            assert np.array_equal(bits(got), bits(base)), opts
+    finally:
+        cuda.release(w)
+    assert cuda.device_status() == 0
+
+
 @pytest.mark.parametrize("k", [8, 15, 20, 32, 33, 40, 63, 64, 96, 137, 896])
 def test_q8_0_block_tails_with_poisoned_padding(oracle, cuda, dev, k):
     # Q8BlockTailTests.cs:25-97: partial last blocks; anything read past K would pick up 1e6

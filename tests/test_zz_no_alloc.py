@@ -36,17 +36,32 @@ def test_noalloc_matches_allocating_entry_point_twice(oracle, cuda, dev):
     assert cuda.device_status() == 0
 
 
-def test_noalloc_refuses_shapes_beyond_its_buffer(oracle, cuda, dev):
+def test_noalloc_at_its_limit_and_refusal_beyond(oracle, cuda, dev):
+    """M * K exactly at the limit with seeded random rows, for every format (Q4_K reads the block sums, Q6_K the
+    half-block sums, so every region of the fixed array is exercised at full size); a smaller shape straight
+    after shows that what the large call left behind does no harm; one row more is refused."""
     import torch
 
     from sharpmind_b200 import ops
 
-    k, n = 16384, 32
-    raw = oracle.quantize(Q8_0, synth.normal("noalloc", "wbig", (n, k), 0.02))
-    w = cuda.register(raw, Q8_0, n, k)
-    ok = torch.zeros((32, k), device="cuda")      # 32 * 16384 = the limit exactly
-    assert dev.qmatmul_q8_noalloc(ok, w).shape == (32, n)
-    too_big = torch.zeros((33, k), device="cuda")
-    with pytest.raises(ops.ArgumentOutOfRangeException):
-        dev.qmatmul_q8_noalloc(too_big, w)
-    cuda.release(w)
+    k, n = 16384, 32  # 32 * 16384 = SMC_NOALLOC_MAX_ELEMS exactly
+    for dtype in (Q8_0, Q4_K, Q6_K):
+        raw = oracle.quantize(dtype, synth.normal("noalloc", f"wbig{dtype}", (n, k), 0.02))
+        w = cuda.register(raw, dtype, n, k)
+        full = torch.from_numpy(synth.normal("noalloc", f"xbig{dtype}", (32, k))).cuda()
+        want = dev.qmatmul(full, w, ops.Mode.ACT_Q8).cpu().numpy()
+        got = dev.qmatmul_q8_noalloc(full, w).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), dtype
+        small = torch.from_numpy(synth.normal("noalloc", f"xsmall{dtype}", (3, k))).cuda()
+        want = dev.qmatmul(small, w, ops.Mode.ACT_Q8).cpu().numpy()
+        got = dev.qmatmul_q8_noalloc(small, w).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), dtype
+        one = small[1:2].contiguous()  # a single row takes the bulk-copy kernel on the rows quantised into the array
+        want = dev.qmatmul(one, w, ops.Mode.ACT_Q8).cpu().numpy()
+        got = dev.qmatmul_q8_noalloc(one, w).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), dtype
+        too_big = torch.zeros((33, k), device="cuda")
+        with pytest.raises(ops.ArgumentOutOfRangeException):
+            dev.qmatmul_q8_noalloc(too_big, w)
+        cuda.release(w)
+    assert cuda.device_status() == 0
