@@ -89,7 +89,8 @@ SMC_API const char *smc_last_error(smc_ctx *ctx);
  *                           weight prefetch overlaps its predecessor's tail, or fully serialised
  *   "gemv_slots"            ring depth per warp of the one-row matmul kernel, 2..8 (0 = built-in choice)
  *   "gemv_steps_per_stage"  steps per bulk copy of that kernel: 1, 2 or 4 (0 = built-in choice)
- *   "gemv_ctas_per_sm"      resident CTAs per SM its grid is sized for, 1..4 (0 = built-in choice)
+ *   "gemv_ctas"             CTAs in its grid (0 = built-in choice: one per SM)
+ *   "gemv_prefetch_first"   stages a warp requests before the activation loads are issued, 0..8 (default 1)
  * Results do not depend on any of them.  SMC_E_INVALID for an unknown name. */
 SMC_API int smc_set_option(smc_ctx *ctx, const char *name, int value);
 /* QuantizationOps.GetRawTensorByteCount for a [N, K] tensor (QuantizationOps.cs:15-72); -1 if dtype unknown. */

@@ -84,7 +84,8 @@ struct smc_ctx {
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
     bool use_pdl = true;               // programmatic dependent launch (smc_set_option "pdl")
-    int tma_slots = 0, tma_ss = 0, tma_ctas = 0;  // one-row GEMV ring geometry, 0 = built-in choice (smc_set_option)
+    int tma_slots = 0, tma_ss = 0, tma_ctas = 0;  // one-row GEMV ring geometry and grid, 0 = built-in choice (smc_set_option)
+    int tma_pre = 1;                              // stages requested before the activation loads are issued
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
     int argmax_rows = 0, argmax_chunks = 0;
     void *d_prefill = nullptr;         // activation image of the tensor-core matmul

@@ -43,7 +43,7 @@
 
 namespace {
 
-constexpr int WARPS = 8;
+constexpr int WARPS = 24;  // one CTA per SM
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -115,6 +115,16 @@ __device__ __forceinline__ uint32_t lds16u(uint32_t a)
 }
 __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
 
+// stores into the staged activation row (sx = its shared::cta address)
+__device__ __forceinline__ void xst64(uint32_t sx, uint32_t off, uint2 v)
+{
+    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sx + off), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void xst32(uint32_t sx, uint32_t off, uint32_t v)
+{
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(sx + off), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ float warp_sum32(float v)
 {
 #pragma unroll
@@ -149,31 +159,66 @@ __host__ __device__ inline size_t x_bytes(int K)
 }
 __device__ __forceinline__ int m32_pos(int g16) { return (g16 >> 3) * 8 + (g16 & 1) * 4 + ((g16 >> 1) & 3); }
 
-template <class Math>
-__device__ __forceinline__ void stage_x(const XPtrs &g, int K, uint8_t *sx)
+// `mid` is called once, after the first round of loads has been issued and before anything waits for it: the kernel
+// uses it to request the rest of its weight stages BEHIND the activation loads.  Requested the other way round, the
+// activation loads would queue behind every byte the rings have in flight, and the whole CTA would wait for them.
+template <class Math, class Mid>
+__device__ __forceinline__ void stage_x(const XPtrs &g, int K, uint8_t *sx, Mid mid)
 {
     uint4 *sq = reinterpret_cast<uint4 *>(sx);
     float *sdx = reinterpret_cast<float *>(sx + K);
     float *ssd = sdx + K / 32;
     int *sm32 = reinterpret_cast<int *>(sdx + K / 32);
     const uint4 *gq = reinterpret_cast<const uint4 *>(g.q);
-    for (int i = threadIdx.x; i < K / 16; i += blockDim.x) sq[Math::swz(i)] = __ldg(gq + i);
+    constexpr int R = 4;  // 16-byte chunks per thread and round
+    const int nq = K / 16;
+    bool first = true;
+    for (int i0 = threadIdx.x; i0 < nq || first; i0 += R * blockDim.x) {
+        uint4 v[R];
+        int16_t hs[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const int i = i0 + j * blockDim.x;
+            if (i < nq) {
+                v[j] = __ldg(gq + i);
+                if (Math::S16) hs[j] = __ldg(g.s16 + i);
+            }
+        }
+        if (first) mid();
+        first = false;
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const int i = i0 + j * blockDim.x;
+            if (i < nq) {
+                sq[Math::swz(i)] = v[j];
+                if (Math::S16) sm32[m32_pos(i)] = -32 * (int)hs[j];
+            }
+        }
+    }
     for (int i = threadIdx.x; i < K / 32; i += blockDim.x) {
         sdx[i] = __ldg(g.d + i);
         if (Math::SD) ssd[i] = __ldg(g.sd + i);
     }
-    if (Math::S16)
-        for (int i = threadIdx.x; i < K / 16; i += blockDim.x) sm32[m32_pos(i)] = -32 * (int)__ldg(g.s16 + i);
 }
+// round-half-even(x / scale), the quotient correctly rounded first (what QuantizeRowQ8_0's MathF.Round(x / d) does), at
+// the price of a multiplication in all but rare cases: x * (1/scale) with an approximate reciprocal is within 1e-4 of
+// the exact quotient for |quotient| <= 128, so both round to the same integer unless the product lies that close to a
+// half; only then (or when the product is not finite) the IEEE division decides.
+__device__ __forceinline__ int quant_div_rn(float x, float scale, float rcp)
+{
+    const float t = x * rcp;
+    const float f = fabsf(t - rintf(t));
+    if (!(fabsf(f - 0.5f) > 1e-3f) || !(fabsf(t) < 200.0f)) return __float2int_rn(__fdiv_rn(x, scale));
+    return __float2int_rn(t);
+}
+
 // Quantises the eight values of chunk c (lanes 4b .. 4b+3 hold the four chunks of block b) and stores them, their
 // block scale and sums in the staged layout: the rules of QuantizedKVCache.QuantizeRowQ8_0 (d = amax/127, 1 for a
 // zero block, stored through fp16; q = round-half-even(x/d)).
 template <class Math>
-__device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, uint8_t *sx)
+__device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, uint32_t dst)
 {
-    float *sdx = reinterpret_cast<float *>(sx + K);
-    float *ssd = sdx + K / 32;
-    int *sm32 = reinterpret_cast<int *>(sdx + K / 32);
+    const uint32_t o_d = (uint32_t)K, o_aux = (uint32_t)K + (uint32_t)(K / 32) * 4u;
     float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
@@ -181,84 +226,101 @@ __device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, u
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     float scale = __fdiv_rn(amax, 127.0f);
     if (amax == 0.0f) scale = 1.0f;
+    float rcp;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(scale));
     int q[8], s = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        q[i] = max(-128, min(127, __float2int_rn(__fdiv_rn(v[i], scale))));
+        q[i] = max(-128, min(127, quant_div_rn(v[i], scale, rcp)));
         s += q[i];
     }
     uint2 packed;
     packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
     packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
-    *reinterpret_cast<uint2 *>(sx + 16 * Math::swz(c >> 1) + 8 * (c & 1)) = packed;
+    xst64(dst, 16u * (uint32_t)Math::swz(c >> 1) + 8u * (c & 1), packed);
     const int s16v = s + __shfl_xor_sync(0xffffffffu, s, 1);
     const int total = s16v + __shfl_xor_sync(0xffffffffu, s16v, 2);
     const int blk = c >> 2;
-    if (Math::S16 && (c & 1) == 0) sm32[m32_pos(c >> 1)] = -32 * s16v;
+    if (Math::S16 && (c & 1) == 0) xst32(dst, o_aux + 4u * (uint32_t)m32_pos(c >> 1), (uint32_t)(-32 * s16v));
     if ((c & 3) == 0) {
         const float df = __half2float(__float2half_rn(scale));
-        sdx[blk] = df;
-        if (Math::SD) ssd[blk] = df * (float)total;
+        xst32(dst, o_d + 4u * blk, __float_as_uint(df));
+        if (Math::SD) xst32(dst, o_aux + 4u * blk, __float_as_uint(df * (float)total));
     }
 }
 
 // Same layout, filled by quantising an fp32 row on the fly.  Four consecutive lanes share a 32-element block,
-// eight elements each; all loads of a batch are issued before any arithmetic so the row costs one memory
-// latency, not one per block.  With `up` the row is SiLU(x) * up in the arithmetic of the stand-alone kernel.
-template <class Math>
-__device__ __forceinline__ void stage_x_quant(const float *x, const float *up, int K, uint8_t *sx)
+// eight elements each; all loads of a round (R chunks per thread) are issued before any arithmetic so a round costs
+// one memory latency, not one per block.  With `up` the row is SiLU(x) * up in the arithmetic of the stand-alone
+// kernel.  `mid` as for stage_x: called once, after the first round's loads are on their way.
+template <class Math, int R, bool GATE, class Mid>
+__device__ __forceinline__ void stage_x_quant(const float *x, const float *up, int K, uint32_t dst, Mid mid)
 {
-    const int nchunks = K / 8;  // K is a multiple of 1024, so whole warps stay converged
-    constexpr int UB = 4;
-    for (int c0 = threadIdx.x; c0 < nchunks; c0 += UB * blockDim.x) {
-        float4 va[UB], vb[UB];
+    const int cend = K / 8;  // K is a multiple of 1024, so whole warps stay converged
+    bool called = false;
+    for (int c0 = threadIdx.x; c0 < cend; c0 += R * blockDim.x) {
+        float4 va[R], vb[R], ua[GATE ? R : 1], ub[GATE ? R : 1];
 #pragma unroll
-        for (int j = 0; j < UB; ++j) {
+        for (int j = 0; j < R; ++j) {
             const int c = c0 + j * blockDim.x;
-            if (c < nchunks) {
+            if (c < cend) {
                 va[j] = __ldg(reinterpret_cast<const float4 *>(x) + 2 * c);
                 vb[j] = __ldg(reinterpret_cast<const float4 *>(x) + 2 * c + 1);
+                if (GATE) {
+                    ua[j] = __ldg(reinterpret_cast<const float4 *>(up) + 2 * c);
+                    ub[j] = __ldg(reinterpret_cast<const float4 *>(up) + 2 * c + 1);
+                }
             }
         }
+        if (!called) mid(), called = true;
 #pragma unroll
-        for (int j = 0; j < UB; ++j) {
+        for (int j = 0; j < R; ++j) {
             const int c = c0 + j * blockDim.x;
-            if (c < nchunks) {  // uniform per warp: nchunks is a multiple of 128
+            if (c < cend) {  // uniform per warp: the row is a multiple of 128 chunks
                 float v[8] = {va[j].x, va[j].y, va[j].z, va[j].w, vb[j].x, vb[j].y, vb[j].z, vb[j].w};
-                if (up) {  // g / (1 + exp(-g)) * u
-                    const float4 ua = __ldg(reinterpret_cast<const float4 *>(up) + 2 * c), ub = __ldg(reinterpret_cast<const float4 *>(up) + 2 * c + 1);
-                    const float u[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+                if (GATE) {  // g / (1 + exp(-g)) * u
+                    const float u[8] = {ua[j].x, ua[j].y, ua[j].z, ua[j].w, ub[j].x, ub[j].y, ub[j].z, ub[j].w};
 #pragma unroll
                     for (int i = 0; i < 8; ++i) v[i] = __fdiv_rn(v[i], 1.0f + expf(-v[i])) * u[i];
                 }
-                quant_chunk<Math>(v, c, K, sx);
+                quant_chunk<Math>(v, c, K, dst);
             }
         }
     }
+    if (!called) mid();
 }
 
 // The residual add and the RMSNorm that precede a matmul in a decoder block, done while its activation row is
 // staged: v = x + add (add may be null), xsum = v (written by the CTA that is given a pointer), row = v * rsqrt(mean
-// v^2 + eps) * w, quantised as above.  K <= 8192: a thread keeps its (at most four) chunks in registers between the
+// v^2 + eps) * w, quantised as above.  K <= 12288: a thread keeps its (at most two) chunks in registers between the
 // sum of squares and the scaling.  The sum of squares is taken in a fixed order (thread chunks in order, warp
 // butterfly, warps in order), which is not the order of the stand-alone norm kernel: results agree to rounding.
-template <class Math>
+template <class Math, class Mid>
 __device__ __forceinline__ void stage_x_addnorm_quant(const float *x, const float *add, const float *w, float eps, float *xsum,
-                                                      int K, uint8_t *sx)
+                                                      int K, uint32_t dst, Mid mid)
 {
     __shared__ float red[WARPS];
     const int nchunks = K / 8;
-    constexpr int UB = 4;
+    constexpr int UB = 2;  // chunks per thread: K <= 8 * 2 * 768
     float v[UB][8];
     float ss = 0.f;
+    float4 pa[UB], pb[UB];
 #pragma unroll
     for (int j = 0; j < UB; ++j) {
         const int c = threadIdx.x + j * blockDim.x;
         if (c < nchunks) {
             const float4 a = __ldg(reinterpret_cast<const float4 *>(x) + 2 * c), b = __ldg(reinterpret_cast<const float4 *>(x) + 2 * c + 1);
             v[j][0] = a.x, v[j][1] = a.y, v[j][2] = a.z, v[j][3] = a.w, v[j][4] = b.x, v[j][5] = b.y, v[j][6] = b.z, v[j][7] = b.w;
+            if (add) pa[j] = __ldg(reinterpret_cast<const float4 *>(add) + 2 * c), pb[j] = __ldg(reinterpret_cast<const float4 *>(add) + 2 * c + 1);
+        }
+    }
+    mid();
+#pragma unroll
+    for (int j = 0; j < UB; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < nchunks) {
             if (add) {
-                const float4 p = __ldg(reinterpret_cast<const float4 *>(add) + 2 * c), q = __ldg(reinterpret_cast<const float4 *>(add) + 2 * c + 1);
+                const float4 p = pa[j], q = pb[j];
                 v[j][0] += p.x, v[j][1] += p.y, v[j][2] += p.z, v[j][3] += p.w, v[j][4] += q.x, v[j][5] += q.y, v[j][6] += q.z, v[j][7] += q.w;
             }
             if (xsum) {
@@ -285,7 +347,7 @@ __device__ __forceinline__ void stage_x_addnorm_quant(const float *x, const floa
             float r[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) r[i] = (v[j][i] * inv) * g[i];
-            quant_chunk<Math>(r, c, K, sx);
+            quant_chunk<Math>(r, c, K, dst);
         }
     }
 }
@@ -483,9 +545,10 @@ struct MathQ8_0 {
 };
 
 // ------------------------------------------------------------------------------------------------
-template <class Math, int MINB, int SS, bool GATHER>
-__global__ void __launch_bounds__(WARPS * 32, MINB) gemv_tma_kernel(StepSrc src, XPtrs xg, float *__restrict__ out, int N, int K,
-                                                                    int slots, int *__restrict__ status, const smc_gather_dev *gd)
+template <class Math, int SS, bool GATHER>
+__global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XPtrs xg, float *__restrict__ out, int N, int K,
+                                                                    int slots, int tune, int *__restrict__ status,
+                                                                    const smc_gather_dev *gd)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     int sending = -1;      // whether packets go out, known after the first look at the peers' ready flags (warp uniform)
@@ -493,8 +556,8 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) gemv_tma_kernel(StepSrc src,
     constexpr uint32_t SLOT = (Math::STEP_BYTES * SS + 127u) & ~127u;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-    // shared layout: [x row] [8 warps x slots x SLOT bytes] [8 warps x slots ring barriers] [8 x 32 floats handed
-    // from warp w-1 to warp w] [8 hand-over barriers]
+    // shared layout: [x row] [WARPS x slots x SLOT bytes] [WARPS x slots ring barriers] [WARPS x 32 floats handed
+    // from warp w-1 to warp w] [WARPS hand-over barriers]
     const uint32_t xb = (uint32_t)((x_bytes<Math>(K) + 127) & ~(size_t)127);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t ring = sbase + xb + (uint32_t)(warp * slots) * SLOT;
@@ -541,19 +604,30 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) gemv_tma_kernel(StepSrc src,
         ++issued;
         return true;
     };
+    // One stage per warp is requested at once: weights depend on no earlier launch, so this part of the stream runs
+    // under the predecessor's tail.  The other slots are filled from `fill_rest`, behind the activation loads.
+    const int pre = tune & 0xFF;
     if (lane == 0)
-        for (int t = 0; t < slots; ++t)
+        for (int t = 0; t < pre && t < slots; ++t)
             if (!fetch_next(ring + (uint32_t)t * SLOT, bars + 8 * t)) break;
-    // The weight stages requested above do not depend on earlier launches; everything below does (activations,
-    // the output buffer, the exchange counters), so this is where a dependent launch waits for its predecessor.
+    auto fill_rest = [&]() {
+        if (lane == 0)
+            for (int t = pre; t < slots; ++t)
+                if (!fetch_next(ring + (uint32_t)t * SLOT, bars + 8 * t)) break;
+    };
+    // Everything below depends on earlier launches (activations, the output buffer, the exchange counters), so this
+    // is where a dependent launch waits for its predecessor.
     smc_grid_dep_sync();
     // row-split across GPUs: tell the peers that this rank's readers of the previous exchange are done
     if (GATHER && blockIdx.x == 0 && threadIdx.x == 32) smc_gather_post_ready(gd);
-    if (xg.nw) stage_x_addnorm_quant<Math>(xg.xf, xg.xadd, xg.nw, xg.eps, blockIdx.x == 0 ? xg.xsum : nullptr, K, smem);
-    else if (xg.xf) stage_x_quant<Math>(xg.xf, xg.xu, K, smem);
-    else stage_x<Math>(xg, K, smem);
+    if (xg.xf) {
+        if (xg.nw) stage_x_addnorm_quant<Math>(xg.xf, xg.xadd, xg.nw, xg.eps, blockIdx.x == 0 ? xg.xsum : nullptr, K, sbase, fill_rest);
+        else if (xg.xu) stage_x_quant<Math, 2, true>(xg.xf, xg.xu, K, sbase, fill_rest);
+        else stage_x_quant<Math, 4, false>(xg.xf, nullptr, K, sbase, fill_rest);
+    } else {
+        stage_x<Math>(xg, K, smem, fill_rest);  // rows quantised beforehand
+    }
     __syncthreads();  // the row is staged, and every warp's hand-over barrier is initialised
-
     Math math;
     math.init(lane);
     float acc = 0.f;
@@ -635,54 +709,50 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) gemv_tma_kernel(StepSrc src,
     }
 }
 
-template <class Math, int MINB, int SS>
+template <class Math, int SS>
 void launch_one(smc_ctx *ctx, dim3 grid, size_t smem, cudaStream_t s, const StepSrc &src, const XPtrs &x, float *out, int N,
                 int K, int slots, const smc_gather_dev *gd)
 {
+    const int tune = ctx->tma_pre & 0xFF;
     if (gd) {
-        cudaFuncSetAttribute(gemv_tma_kernel<Math, MINB, SS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, MINB, SS, true>, grid, dim3(WARPS * 32), smem, s, src, x, out, N, K, slots,
-                       ctx->d_status, gd);
+        cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, true>, grid, dim3(WARPS * 32), smem, s, src, x, out, N, K, slots,
+                       tune, ctx->d_status, gd);
         return;
     }
-    cudaFuncSetAttribute(gemv_tma_kernel<Math, MINB, SS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, MINB, SS, false>, grid, dim3(WARPS * 32), smem, s, src, x, out, N, K, slots,
-                   ctx->d_status, (const smc_gather_dev *)nullptr);
+    cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, false>, grid, dim3(WARPS * 32), smem, s, src, x, out, N, K, slots,
+                   tune, ctx->d_status, (const smc_gather_dev *)nullptr);
 }
 
 template <class Math>
 int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, int N, int K, cudaStream_t s,
                 const smc_gather_dev *gd)
 {
-    // ring geometry: `slots` stages of `ss` steps per warp, `per_sm` resident CTAs the grid is sized for
+    // One CTA of 24 warps per SM: the activation row is fetched and quantised once per SM (with three CTAs of eight
+    // warps each, 444 copies of a 14336-element fp32 row were half as many bytes into the SMs as the matrix itself).
+    // Ring geometry: `slots` stages of `ss` steps per warp.
     int slots = ctx->tma_slots ? ctx->tma_slots : 2;
     int ss = ctx->tma_ss ? ctx->tma_ss : 2;
-    int per_sm = ctx->tma_ctas ? ctx->tma_ctas : 3;
     const size_t xb = (x_bytes<Math>(K) + 127) & ~(size_t)127;
     auto need = [&](int sl, int st) {
         const size_t slot_bytes = ((size_t)Math::STEP_BYTES * st + 127) & ~(size_t)127;
         return xb + (size_t)WARPS * sl * (slot_bytes + 8) + (size_t)WARPS * 136;
     };
-    // `per_sm` CTAs must fit in the 227 KB of an SM (1 KB per CTA is reserved by the system): a long activation row
-    // first costs ring depth, then stage length, then resident CTAs
-    while ((need(slots, ss) + 1024) * per_sm > 227 * 1024) {
+    // a long activation row first costs ring depth, then stage length
+    while (need(slots, ss) > 226 * 1024) {
         if (slots > 2) --slots;
         else if (ss > 1) ss >>= 1;
-        else if (per_sm > 1) --per_sm;
         else break;
     }
     const size_t smem = need(slots, ss);
     if (smem > 226 * 1024) return smc_fail(ctx, SMC_E_UNSUPPORTED, "K = %d needs %zu bytes of shared memory", K, smem);
-    int ctas = ctx->sm_count * per_sm;
+    int ctas = ctx->tma_ctas ? ctx->tma_ctas : ctx->sm_count;
     if (ctas > N) ctas = N;
     const dim3 grid(ctas);
-    const bool three = per_sm >= 3;
-    if (ss == 4) three ? launch_one<Math, 3, 4>(ctx, grid, smem, s, src, x, out, N, K, slots, gd)
-                       : launch_one<Math, 2, 4>(ctx, grid, smem, s, src, x, out, N, K, slots, gd);
-    else if (ss == 2) three ? launch_one<Math, 3, 2>(ctx, grid, smem, s, src, x, out, N, K, slots, gd)
-                            : launch_one<Math, 2, 2>(ctx, grid, smem, s, src, x, out, N, K, slots, gd);
-    else three ? launch_one<Math, 3, 1>(ctx, grid, smem, s, src, x, out, N, K, slots, gd)
-               : launch_one<Math, 2, 1>(ctx, grid, smem, s, src, x, out, N, K, slots, gd);
+    if (ss == 4) launch_one<Math, 4>(ctx, grid, smem, s, src, x, out, N, K, slots, gd);
+    else if (ss == 2) launch_one<Math, 2>(ctx, grid, smem, s, src, x, out, N, K, slots, gd);
+    else launch_one<Math, 1>(ctx, grid, smem, s, src, x, out, N, K, slots, gd);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }

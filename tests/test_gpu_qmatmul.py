@@ -135,7 +135,7 @@ def test_one_row_long_rows_against_oracle(oracle, cuda, dev, dtype, n, k):
 
 # The one-row kernel cuts a CTA's rows into equal pieces per warp without regard to row boundaries and continues a
 # row from the lane sums its previous warp left: an output's bits must not depend on how the rows were divided.
-# The ring options change the grid (resident CTAs), the stage length and with them every piece boundary.
+# The options change the grid, the stage length and with them every piece boundary.
 PARTITION_SHAPES = [
     (Q6_K, 4096, 14336), (Q6_K, 3, 14336), (Q6_K, 37, 6144), (Q4_K, 4096, 4096), (Q4_K, 1, 8192), (Q4_K, 445, 2048),
     (Q8_0, 1500, 2048), (Q8_0, 7, 5120), (Q8_0, 3072, 1024),
@@ -164,15 +164,15 @@ def test_one_row_bits_do_not_depend_on_the_partition(oracle, cuda, dev, dtype, n
             want = oracle.qmatmul(dtype, xhat, raw, 1, k, n, cols=(r, r + 1))[0, r]
             wrow = oracle.dequantize(dtype, raw[r * per_row:(r + 1) * per_row], k)
             assert abs(float(base[0, r]) - float(want)) <= 1e-5 * np.linalg.norm(wrow) * np.linalg.norm(xhat)
-        for opts in ({"gemv_ctas_per_sm": 1}, {"gemv_ctas_per_sm": 2, "gemv_steps_per_stage": 1},
-                     {"gemv_steps_per_stage": 4, "gemv_slots": 3}, {"gemv_ctas_per_sm": 1, "gemv_slots": 4, "pdl": 0}):
+        for opts in ({"gemv_ctas": 37}, {"gemv_ctas": 296, "gemv_steps_per_stage": 1, "gemv_prefetch_first": 0},
+                     {"gemv_steps_per_stage": 4, "gemv_slots": 3}, {"gemv_ctas": 1, "gemv_slots": 4, "pdl": 0}):
             for name, v in opts.items():
                 cuda.set_option(name, v)
             try:
                 got = dev.qmatmul(x, w, Mode.ACT_Q8).cpu().numpy()
             finally:
                 for name in opts:
-                    cuda.set_option(name, 1 if name == "pdl" else 0)
+                    cuda.set_option(name, {"pdl": 1, "gemv_prefetch_first": 1}.get(name, 0))
             assert np.array_equal(bits(got), bits(base)), opts
     finally:
         cuda.release(w)
