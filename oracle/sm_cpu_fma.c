@@ -234,6 +234,8 @@ static inline float vecdot(int dtype, const float *in, const uint8_t *raw, int c
 }
 
 SMF_API int smf_num_threads(void) { return omp_get_max_threads(); }
+/* A launcher may have pinned OMP_NUM_THREADS to 1 in the environment: the caller states the thread count itself. */
+SMF_API void smf_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
 
 /* QuantizedMatMul*_Parallel_FMA (e.g. QuantizationKernels.Q8.cs:556-574) with
  * DecodeParallel's chunking rule (QuantizationKernels.cs:73-108): for M <= 1 split N into

@@ -307,9 +307,12 @@ SMO_API int smo_qmatmul(int dtype, const float *input, const uint8_t *raw, float
 {
     if (dtype != SMO_Q8_0 && dtype != SMO_Q4_K && dtype != SMO_Q6_K)
         return -1;
-    for (int r = 0; r < M; r++)
+    /* outputs are independent: spreading the columns over threads changes no bit of any of them */
+    for (int r = 0; r < M; r++) {
+#pragma omp parallel for schedule(static) if ((int64_t)N * K >= 262144)
         for (int c = 0; c < N; c++)
             output[(int64_t)r * N + c] = smo_vecdot(dtype, input + (int64_t)r * K, raw, c, K);
+    }
     return 0;
 }
 
@@ -858,6 +861,27 @@ typedef struct {
     int down_dtype, head_dtype;
 } smo_model;
 
+/* The matmul of the decode step.  act_q8 == 0: the reference's own arithmetic (fp32 activations into the scalar
+ * vec-dot).  act_q8 != 0: what the CUDA library's SMC_ACT_Q8 mode is specified to compute -- every activation row is
+ * first quantised to Q8_0 blocks by the rules of QuantizedKVCache.QuantizeRowQ8_0
+ * (SharpMind.Model/QuantizedKVCache.cs:191-223, restated in smo_quantize_row_q8_0) and the scalar vec-dot is fed the
+ * dequantised row -- so that a decode step in that mode can be held to the same bound as a single matmul. */
+static int step_matmul(int act_q8, int dtype, const float *in, const uint8_t *raw, float *out, int M, int K, int N)
+{
+    if (!act_q8) return smo_qmatmul(dtype, in, raw, out, M, K, N);
+    if (K % 32) return -5;
+    uint8_t *q = malloc((size_t)(K / 32) * 34);
+    float *hat = malloc(sizeof(float) * (size_t)M * K);
+    if (!q || !hat) { free(q); free(hat); return -2; }
+    for (int r = 0; r < M; r++) {
+        smo_quantize_row_q8_0(in + (size_t)r * K, q, K);
+        smo_dequant_row_q8_0(q, hat + (size_t)r * K, K);
+    }
+    int rc = smo_qmatmul(dtype, hat, raw, out, M, K, N);
+    free(q); free(hat);
+    return rc;
+}
+
 /* Follows Transformer.ForwardLastLogits (SharpMind.Model/Transformer.cs:417-463),
  * DecoderArch.Forward (SharpMind.Model/Arch/DecoderArch.cs:115-134),
  * UnhookedTransformerBlock.Forward (SharpMind.Model/Layers/UnhookedTransformerBlock.cs:12-47),
@@ -865,9 +889,10 @@ typedef struct {
  * FfnKernels.Gated (SharpMind.Model/Layers/Ffn/FfnKernels.cs:35-59),
  * KVCache.Update (SharpMind.Model/KVCache.cs:84-150) for seqLen == 1 and `batch`
  * lock-step sequences.  kcache / vcache are [layer][batch][kvHead][max_seq][head_dim]
- * fp32 and already hold positions [0, pos).  Writes logits [batch, vocab]. */
-SMO_API int smo_decode_step(const smo_model *m, const int *tokens, int batch, int pos, float *kcache,
-                            float *vcache, float *logits)
+ * fp32 and already hold positions [0, pos).  Writes logits [batch, vocab].
+ * act_q8: see step_matmul. */
+SMO_API int smo_decode_step_ex(const smo_model *m, const int *tokens, int batch, int pos, float *kcache,
+                               float *vcache, float *logits, int act_q8)
 {
     int H = m->hidden, nh = m->n_heads, nkv = m->n_kv_heads, hd = m->head_dim, F = m->ffn;
     int qDim = nh * hd, kvDim = nkv * hd;
@@ -888,9 +913,9 @@ SMO_API int smo_decode_step(const smo_model *m, const int *tokens, int batch, in
     size_t layerStride = B * nkv * (size_t)m->max_seq * hd;
     for (int L = 0; L < m->n_layers; L++) {
         smo_rmsnorm(x, m->norm1[L], xn, batch, H, m->eps);
-        smo_qmatmul(m->dtype, xn, m->wq[L], q, batch, H, qDim);
-        smo_qmatmul(m->dtype, xn, m->wk[L], k, batch, H, kvDim);
-        smo_qmatmul(m->dtype, xn, m->wv[L], v, batch, H, kvDim);
+        if ((rc = step_matmul(act_q8, m->dtype, xn, m->wq[L], q, batch, H, qDim))) goto done;
+        if ((rc = step_matmul(act_q8, m->dtype, xn, m->wk[L], k, batch, H, kvDim))) goto done;
+        if ((rc = step_matmul(act_q8, m->dtype, xn, m->wv[L], v, batch, H, kvDim))) goto done;
         if (m->qk_norm) {
             smo_rmsnorm(q, m->qnorm[L], q, batch * nh, hd, m->eps);
             smo_rmsnorm(k, m->knorm[L], k, batch * nkv, hd, m->eps);
@@ -915,18 +940,24 @@ SMO_API int smo_decode_step(const smo_model *m, const int *tokens, int batch, in
                 smo_sdpa_flash(q + (size_t)b * qDim + (size_t)h * hd, kc + base, vc + base,
                                att + (size_t)b * qDim + (size_t)h * hd, 1, kvLen, hd, scale, 1, qDim, qDim);
             }
-        smo_qmatmul(m->dtype, att, m->wo[L], tmp, batch, qDim, H);
+        if ((rc = step_matmul(act_q8, m->dtype, att, m->wo[L], tmp, batch, qDim, H))) goto done;
         smo_add_inplace(x, tmp, (int64_t)B * H);
         smo_rmsnorm(x, m->norm2[L], xn, batch, H, m->eps);
-        smo_qmatmul(m->dtype, xn, m->wgu[L], gu, batch, H, 2 * F);
+        if ((rc = step_matmul(act_q8, m->dtype, xn, m->wgu[L], gu, batch, H, 2 * F))) goto done;
         for (int b = 0; b < batch; b++)
             smo_swiglu(gu + (size_t)b * 2 * F, gu + (size_t)b * 2 * F + F, act + (size_t)b * F, F);
-        smo_qmatmul(m->down_dtype ? m->down_dtype : m->dtype, act, m->wdown[L], tmp, batch, F, H);
+        if ((rc = step_matmul(act_q8, m->down_dtype ? m->down_dtype : m->dtype, act, m->wdown[L], tmp, batch, F, H))) goto done;
         smo_add_inplace(x, tmp, (int64_t)B * H);
     }
     smo_rmsnorm(x, m->final_norm, x, batch, H, m->eps);
-    smo_qmatmul(m->head_dtype ? m->head_dtype : m->dtype, x, m->lm_head, logits, batch, H, m->vocab);
+    rc = step_matmul(act_q8, m->head_dtype ? m->head_dtype : m->dtype, x, m->lm_head, logits, batch, H, m->vocab);
 done:
     free(x); free(xn); free(q); free(k); free(v); free(att); free(tmp); free(gu); free(act);
     return rc;
+}
+
+SMO_API int smo_decode_step(const smo_model *m, const int *tokens, int batch, int pos, float *kcache,
+                            float *vcache, float *logits)
+{
+    return smo_decode_step_ex(m, tokens, batch, pos, kcache, vcache, logits, 0);
 }

@@ -106,6 +106,9 @@ def lib() -> C.CDLL:
         L.smo_decode_step.restype = C.c_int
         L.smo_decode_step.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                       C.c_void_p]
+        L.smo_decode_step_ex.restype = C.c_int
+        L.smo_decode_step_ex.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_int]
     return _lib
 
 
@@ -420,11 +423,13 @@ class Decoder:
         m.cosT, m.sinT = self.cos.ctypes.data, self.sin.ctypes.data
         self._m = m
 
-    def step(self, tokens, pos: int) -> np.ndarray:
+    def step(self, tokens, pos: int, act_q8: bool = False) -> np.ndarray:
+        """One decode step.  act_q8: every matmul input is quantised to Q8_0 and dequantised first (the arithmetic
+        the CUDA library's SMC_ACT_Q8 mode is specified to have)."""
         tok = np.ascontiguousarray(tokens, dtype=np.int32)
         logits = np.zeros((self.batch, self.cfg["vocab"]), dtype=np.float32)
-        rc = lib().smo_decode_step(C.byref(self._m), _p(tok), self.batch, pos, _p(self.kcache),
-                                   _p(self.vcache), _p(logits))
+        rc = lib().smo_decode_step_ex(C.byref(self._m), _p(tok), self.batch, pos, _p(self.kcache),
+                                      _p(self.vcache), _p(logits), int(act_q8))
         if rc:
             raise RuntimeError(f"oracle decode_step failed: {rc}")
         return logits

@@ -59,29 +59,158 @@ def test_decode_matches_oracle_tokens(oracle, cuda, cfg, name, mode, batch):
     assert worst <= 1e-4, worst
 
 
+# SMC_ACT_Q8 against the oracle run in the same arithmetic (every matmul input quantised to Q8_0 and dequantised,
+# oracle.Decoder.step(act_q8=True)).  The two sides differ by fp32 rounding only, and where no activation sits on a
+# rounding boundary their logits agree to 1e-7 of the logit scale (measured).  But rounding to int8 is not continuous:
+# an activation whose quotient x/d lies within that fp32 noise of a half is quantised one step apart on the two sides
+# ("a flip"), which moves the outputs of that matmul by about d * w.  Every later matmul re-quantises the perturbed
+# activations, where more of them now flip, so one early flip grows into a difference of the size of the Q8_0
+# quantisation noise itself: measured 3e-3 .. 9e-3 of the logit scale on the two- and three-layer models here, 1.6e-2 on
+# a two-layer model of the benchmark's widths (worst of 151 936 logits), 6e-2 .. 8e-2 after 28 layers.  No
+# implementation of this mode can be pinned tighter against another one; what can be pinned is that the arithmetic
+# model is right (flip-free steps agree to 1e-7) and that nothing exceeds the noise.  The bars therefore are
+#   * shallow models: every step within 3e-2, and at least three quarters of the steps of the small models flip-free
+#     (within 1e-5);
+#   * the 28-layer configuration: within 1.2e-1 in SMC_ACT_Q8, while the same model is held to 1e-4 (measured 6e-6)
+#     with an exact top-1 match in SMC_ACT_F32 and SMC_REF_ORDER;
+#   * in SMC_ACT_Q8 top-1 agrees wherever the oracle's margin between its two best tokens exceeds twice the bar (the
+#     bar itself for the deep model).
+Q8_SHALLOW_TOL, Q8_DEEP_TOL, Q8_EXACT = 3e-2, 1.2e-1, 1e-5
+
+
+def _q8_step_check(want, got, picked, worst, tol=Q8_SHALLOW_TOL, margin=2.0):
+    """Returns (worst error so far, the oracle's greedy tokens, rows whose top-1 was decidable, rows that were flip-free)."""
+    scale = np.abs(want).max(axis=1)
+    err = np.abs(got - want).max(axis=1) / scale
+    assert np.all(err <= tol), err
+    top2 = np.sort(want, axis=1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > margin * tol * scale
+    pick = want.argmax(axis=1).astype(np.int32)
+    assert np.array_equal(picked[clear], pick[clear])
+    return max(worst, float(err.max())), pick, int(clear.sum()), int((err <= Q8_EXACT).sum())
+
+
+@pytest.mark.parametrize("cfg,name", [(SMALL, "dec_small"), (LLAMA_LIKE, "dec_llama")])
 @pytest.mark.parametrize("batch", [1, 4])
-def test_decode_quantised_activations_track_oracle(oracle, cuda, batch):
-    """ACT_Q8 re-quantises every activation row to Q8_0, so logits move by ~1e-2 of their scale; the
-    greedy token still has to agree wherever the oracle's top-2 margin exceeds that noise."""
+def test_decode_quantised_activations_match_q8_oracle(oracle, cuda, cfg, name, batch):
     import torch
 
-    cfg, name, steps = SMALL, "dec_small", 16
+    steps = 16
     w = _weights(oracle, cfg, name)
     ref = oracle.Decoder(cfg, w, batch)
     dec = Decoder(cuda, cfg, w, max_batch=batch)
     tok = synth.token_ids(name, "prompt", (batch,), cfg["vocab"])
+    worst, decided, exact = 0.0, 0, 0
     for pos in range(steps):
-        want = ref.step(tok, pos)
+        want = ref.step(tok, pos, act_q8=True)
         logits, nxt = dec.step(torch.from_numpy(tok.copy()).cuda(), pos, ops.Mode.ACT_Q8)
-        got = logits.cpu().numpy()
-        scale = np.abs(want).max(axis=1)
-        assert np.all(np.abs(got - want).max(axis=1) <= 0.05 * scale)
-        top2 = np.sort(want, axis=1)[:, -2:]
-        clear = (top2[:, 1] - top2[:, 0]) > 0.1 * scale
-        pick = want.argmax(axis=1).astype(np.int32)
-        assert np.array_equal(nxt.cpu().numpy()[clear], pick[clear])
-        tok = pick
+        worst, tok, n, ex = _q8_step_check(want, logits.cpu().numpy(), nxt.cpu().numpy(), worst)
+        decided += n
+        exact += ex
     dec.close()
+    print(f"ACT_Q8 decode vs Q8 oracle, {name} batch {batch}: worst logit error {worst:.2e} of scale, "
+          f"{exact}/{steps * batch} flip-free, {decided} decidable")
+    assert exact >= steps * batch * 3 // 4, "too many steps differ by more than rounding"
+    assert decided >= steps * batch // 2, "too few steps had a decidable top-1"
+
+
+def _qwen3_device_weights(dev, cfg, seed):
+    import torch
+
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    L, H, hd = cfg["n_layers"], cfg["hidden"], cfg["head_dim"]
+    q_dim, kv_dim, F, V = cfg["n_heads"] * hd, cfg["n_kv_heads"] * hd, cfg["ffn"], cfg["vocab"]
+
+    def mat(n, k):
+        return dev.quantize_weights(cfg["dtype"], torch.randn((n, k), generator=g, device="cuda") * 0.02)
+
+    def vec(n):
+        return torch.randn(n, generator=g, device="cuda") * 0.1 + 1.0
+
+    wd = {k: [] for k in ("wq", "wk", "wv", "wo", "wgu", "wdown", "norm1", "norm2", "qnorm", "knorm")}
+    for _ in range(L):
+        wd["wq"].append(mat(q_dim, H)), wd["wk"].append(mat(kv_dim, H)), wd["wv"].append(mat(kv_dim, H))
+        wd["wo"].append(mat(H, q_dim)), wd["wgu"].append(mat(2 * F, H)), wd["wdown"].append(mat(H, F))
+        wd["norm1"].append(vec(H)), wd["norm2"].append(vec(H)), wd["qnorm"].append(vec(hd)), wd["knorm"].append(vec(hd))
+    wd["final_norm"] = vec(H)
+    wd["embedding"] = mat(V, H)
+    wh = {k: ([t.cpu().numpy() for t in v] if isinstance(v, list) else v.cpu().numpy()) for k, v in wd.items()}
+    return wd, wh, g
+
+
+@pytest.mark.parametrize("n_layers", [2, 28])
+def test_decode_full_qwen3_0_6b_shape_against_oracle(oracle, cuda, dev, n_layers):
+    """The benchmarked decode configuration itself: hidden 1024, 16 / 8 heads of 128, FFN 3072, vocabulary 151 936, all
+    matrices Q8_0 drawn on the device (the oracle gets the same bytes), a seeded 2048-position context installed on both
+    sides, then greedy steps with teacher forcing.  Batch 1 (the one-sequence path with its fused staging) in
+    SMC_ACT_Q8, SMC_ACT_F32 and SMC_REF_ORDER, and rows 0 and 21 of a batch of 32 (the small-batch kernels) in
+    SMC_ACT_Q8.  28 layers is the configuration; the two-layer cut keeps SMC_ACT_Q8 clear of the flip cascade
+    described above and is held to the shallow bar."""
+    import torch
+
+    cfg = dict(synth.QWEN3_0_6B)
+    cfg["n_layers"] = n_layers
+    deep = n_layers > 4
+    ctx_len, steps_q8, steps_f32 = 2048, (16 if deep else 6), (16 if deep else 3)
+    q8_tol, q8_margin = (Q8_DEEP_TOL, 1.0) if deep else (Q8_SHALLOW_TOL, 2.0)
+    wd, wh, g = _qwen3_device_weights(dev, cfg, 20240611)
+    L, hd, V = n_layers, cfg["head_dim"], cfg["vocab"]
+    # context: the same seeded K / V rows for the sequences that are compared (rows 0 and 21 of the batch of 32)
+    rows = (0, 21)
+    kv_shape = (L, 32, cfg["n_kv_heads"], ctx_len, hd)
+    kd, vd = torch.randn(kv_shape, generator=g, device="cuda"), torch.randn(kv_shape, generator=g, device="cuda")
+    tok32 = synth.token_ids("qwen3_full", "tok32", (32,), V)
+
+    def oracle_with_context(sel):
+        ref = oracle.Decoder(cfg, wh, len(sel))
+        for i, r in enumerate(sel):
+            ref.kcache[:, i, :, :ctx_len] = kd[:, r].cpu().numpy()
+            ref.vcache[:, i, :, :ctx_len] = vd[:, r].cpu().numpy()
+        return ref
+
+    # ---- batch 1, every mode
+    for mode, steps in ((ops.Mode.ACT_F32, steps_f32), (ops.Mode.REF_ORDER, steps_f32), (ops.Mode.ACT_Q8, steps_q8)):
+        ref = oracle_with_context((0,))
+        dec = Decoder(cuda, cfg, wd, max_batch=1, keep_raw=(mode == ops.Mode.REF_ORDER))
+        dec.load_kv(kd[:, 0:1].contiguous(), vd[:, 0:1].contiguous())
+        tok = tok32[0:1].copy()
+        worst = 0.0
+        for s in range(steps):
+            pos = ctx_len + s
+            want = ref.step(tok, pos, act_q8=(mode == ops.Mode.ACT_Q8))
+            logits, nxt = dec.step(to_dev(tok), pos, mode)
+            got, picked = logits.cpu().numpy(), nxt.cpu().numpy()
+            if mode == ops.Mode.ACT_Q8:
+                worst, tok, _, _ = _q8_step_check(want, got, picked, worst, q8_tol, q8_margin)
+            else:
+                scale = np.abs(want).max()
+                worst = max(worst, float(np.abs(got - want).max() / scale))
+                assert np.abs(got - want).max() <= 1e-4 * scale, (mode, worst)
+                top2 = np.sort(want[0])[-2:]
+                tok = want.argmax(axis=1).astype(np.int32)
+                if top2[1] - top2[0] > 2e-4 * scale:
+                    assert picked[0] == tok[0]
+        print(f"Qwen3-0.6B shape, {n_layers} layers, batch 1, mode {int(mode)}: worst logit error {worst:.2e} of scale over {steps} steps")
+        dec.close()
+        del ref
+    # ---- batch 32 (lock-step sequences, the small-batch kernels), two of its rows against the oracle
+    ref = oracle_with_context(rows)
+    dec = Decoder(cuda, cfg, wd, max_batch=32)
+    dec.load_kv(kd, vd)
+    del kd, vd
+    tok = tok32.copy()
+    worst = 0.0
+    for s in range(4):
+        pos = ctx_len + s
+        want = ref.step(tok[list(rows)], pos, act_q8=True)
+        logits, nxt = dec.step(to_dev(tok), pos, ops.Mode.ACT_Q8)
+        got, picked = logits.cpu().numpy(), nxt.cpu().numpy()
+        worst, pick, _, _ = _q8_step_check(want, got[list(rows)], picked[list(rows)], worst, q8_tol, q8_margin)
+        tok = picked.copy()          # the other sequences follow their own greedy tokens
+        tok[list(rows)] = pick       # the compared ones are teacher-forced on the oracle's
+    print(f"Qwen3-0.6B shape, {n_layers} layers, batch 32 rows {rows}: worst logit error {worst:.2e} of scale")
+    dec.close()
+    assert cuda.device_status() == 0
 
 
 def test_decode_batch_rows_are_independent(oracle, cuda):
@@ -149,20 +278,17 @@ def test_decode_one_sequence_fused_path(oracle, cuda):
     w2 = {k: ([a.copy() for a in v] if isinstance(v, list) else v.copy()) for k, v in w.items()}
     two = Decoder(cuda, cfg, w2, max_batch=2)
     tok = synth.token_ids(name, "prompt", (1,), cfg["vocab"])
+    worst = 0.0
     for pos in range(steps):
-        want = ref.step(tok, pos)
+        want = ref.step(tok, pos, act_q8=True)
         t1 = torch.from_numpy(tok.copy()).cuda()
         l1, n1 = one.step(t1, pos, ops.Mode.ACT_Q8)
         l2, _ = two.step(torch.cat([t1, t1]), pos, ops.Mode.ACT_Q8)
         got, pair = l1.cpu().numpy(), l2.cpu().numpy()
         scale = np.abs(want).max()
-        assert np.abs(got - want).max() <= 0.05 * scale
         assert np.abs(got[0] - pair[0]).max() <= 2e-3 * scale, float(np.abs(got[0] - pair[0]).max() / scale)
-        top2 = np.sort(want[0])[-2:]
-        pick = want.argmax(axis=1).astype(np.int32)
-        if top2[1] - top2[0] > 0.1 * scale:
-            assert n1.cpu().numpy()[0] == pick[0]
-        tok = pick
+        worst, tok, _, _ = _q8_step_check(want, got, n1.cpu().numpy(), worst)
+    print(f"fused one-sequence path vs Q8 oracle: worst logit error {worst:.2e} of scale")
     one.close()
     two.close()
     assert cuda.device_status() == 0
@@ -208,10 +334,10 @@ def test_prompt_pass_quantised_activations_and_guards(oracle, cuda):
     ref = oracle.Decoder(cfg, w, 1)
     toks = synth.token_ids(name, "prompt_q8", (12,), cfg["vocab"])
     for p in range(12):
-        want = ref.step(toks[p:p + 1], p)
+        want = ref.step(toks[p:p + 1], p, act_q8=True)
     dec = Decoder(cuda, cfg, w, max_batch=1)
     got = dec.forward_last_logits(to_dev(toks), 0, 0, ops.Mode.ACT_Q8)[0].cpu().numpy()
-    assert np.max(np.abs(got - want[0])) <= 0.05 * np.abs(want).max()
+    assert np.max(np.abs(got - want[0])) <= Q8_SHALLOW_TOL * np.abs(want).max(), float(np.max(np.abs(got - want[0])) / np.abs(want).max())
     with pytest.raises(ops.SharpMindCudaError):
         dec.forward_last_logits(to_dev(toks), cfg["max_seq"] - 5, 0)      # runs past the cache
     with pytest.raises(ops.SharpMindCudaError):
@@ -240,8 +366,8 @@ def test_mixed_format_decoder_prompt_and_decode(oracle, cuda):
     assert np.max(np.abs(got - want[0])) <= 2e-4 * scale, float(np.max(np.abs(got - want[0])) / scale)
     assert int(got.argmax()) == int(want[0].argmax())
     for p, mode, tol in ((n_prompt, ops.Mode.ACT_F32, 2e-4), (n_prompt + 1, ops.Mode.REF_ORDER, 2e-4),
-                         (n_prompt + 2, ops.Mode.ACT_Q8, 0.05)):
-        want = ref.step(toks[p:p + 1], p)
+                         (n_prompt + 2, ops.Mode.ACT_Q8, Q8_SHALLOW_TOL)):
+        want = ref.step(toks[p:p + 1], p, act_q8=(mode == ops.Mode.ACT_Q8))
         out = dec.step(to_dev(toks[p:p + 1]), p, mode)[0].cpu().numpy()
         assert np.max(np.abs(out[0] - want[0])) <= tol * np.abs(want).max(), (mode, float(np.max(np.abs(out[0] - want[0])) / np.abs(want).max()))
     dec.close()
@@ -265,12 +391,12 @@ def test_decode_one_sequence_wide_ffn(oracle, cuda):
     two = Decoder(cuda, cfg, w2, max_batch=2)
     tok = synth.token_ids(name, "prompt", (1,), cfg["vocab"])
     for pos in range(6):
-        want = ref.step(tok, pos)
+        want = ref.step(tok, pos, act_q8=True)
         t1 = torch.from_numpy(tok.copy()).cuda()
         got = one.step(t1, pos, ops.Mode.ACT_Q8)[0].cpu().numpy()
         pair = two.step(torch.cat([t1, t1]), pos, ops.Mode.ACT_Q8)[0].cpu().numpy()
         scale = np.abs(want).max()
-        assert np.abs(got - want).max() <= 0.05 * scale
+        assert np.abs(got - want).max() <= 2e-2 * scale, float(np.abs(got - want).max() / scale)
         # The two paths take the norm's sum of squares in different orders; a last-bit difference flips the Q8_0
         # rounding of the activations that sit next to a rounding boundary (a few per cent of 10240 elements), which
         # moves an output by a few 1e-3 of its scale per matmul: a looser bar than for the narrow FFN above.
