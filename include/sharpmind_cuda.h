@@ -123,6 +123,12 @@ SMC_API int smc_weight_shape(const smc_weight *w, int *dtype, int *N, int *K);
  * LogitOps.cs:143).  host_raw must have been registered. */
 SMC_API int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, float *output, int M,
                              int K, int N, int dtype, int mode);
+/* The same slot for a caller that kept the handle registration returned (an InferenceLinearLayer that registers in
+ * SetRawWeight, InferenceLinearLayer.cs:200-221, and stores the handle next to RawQuantizedData): no pointer lookup,
+ * and weights that never had a host copy (registered from device memory) can be used.  M, K, N as in
+ * QuantizedMatMulFn; K and N are checked against the handle (SMC_E_SIZE_MISMATCH). */
+SMC_API int smc_qmatmul_host_w(smc_ctx *ctx, const float *input, const smc_weight *w, float *output, int M, int K,
+                               int N, int mode);
 /* VecDotFn(float* input, byte* rawWeights, int col, int inFeatures) (QuantizationOps.cs:8,176-202). */
 SMC_API int smc_vecdot_host(smc_ctx *ctx, const float *input, const void *host_raw, int col, int K,
                             int dtype, float *result);

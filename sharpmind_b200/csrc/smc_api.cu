@@ -570,6 +570,24 @@ int smc_quantize_weights_dev(smc_ctx *ctx, int dtype, const float *d_values, int
 }
 
 // ------------------------------------------------------------------------------------------ host slots
+// Host activations in, host results out, on a weight the caller already holds a handle of.
+static int qmatmul_host_impl(smc_ctx *ctx, const float *input, const smc_weight *w, float *output, int M, int mode)
+{
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    int rc;
+    size_t in_bytes = (size_t)M * w->K * sizeof(float), out_bytes = (size_t)M * w->N * sizeof(float);
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_in, &ctx->stage_in_cap, in_bytes))) return rc;
+    if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, out_bytes))) return rc;
+    // one wait per call: input copy, kernels and result copy are ordered by the stream
+    if ((rc = h2d_queued(ctx, ctx->d_stage_in, input, in_bytes, out_bytes))) return rc;
+    if ((rc = qmatmul_impl(ctx, ctx->d_stage_in, w, ctx->d_stage_out, M, mode, ctx->stream))) {
+        cudaStreamSynchronize(ctx->stream);
+        return rc;
+    }
+    return d2h(ctx, output, ctx->d_stage_out, out_bytes);
+}
+
 int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, float *output, int M, int K, int N,
                      int dtype, int mode)
 {
@@ -582,18 +600,16 @@ int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, flo
         return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "qmatmul_host: weight was registered as dtype=%d N=%d K=%d, call says dtype=%d N=%d K=%d",
                         w->dtype, w->N, w->K, dtype, N, K);
     if (M == 0) return SMC_OK;
-    std::lock_guard<std::mutex> lock(ctx->mu);
-    cudaSetDevice(ctx->device);
-    size_t in_bytes = (size_t)M * K * sizeof(float), out_bytes = (size_t)M * N * sizeof(float);
-    if ((rc = ensure_dev(ctx, &ctx->d_stage_in, &ctx->stage_in_cap, in_bytes))) return rc;
-    if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, out_bytes))) return rc;
-    // one wait per call: input copy, kernels and result copy are ordered by the stream
-    if ((rc = h2d_queued(ctx, ctx->d_stage_in, input, in_bytes, out_bytes))) return rc;
-    if ((rc = qmatmul_impl(ctx, ctx->d_stage_in, w, ctx->d_stage_out, M, mode, ctx->stream))) {
-        cudaStreamSynchronize(ctx->stream);
-        return rc;
-    }
-    return d2h(ctx, output, ctx->d_stage_out, out_bytes);
+    return qmatmul_host_impl(ctx, input, w, output, M, mode);
+}
+
+int smc_qmatmul_host_w(smc_ctx *ctx, const float *input, const smc_weight *w, float *output, int M, int K, int N, int mode)
+{
+    if (!ctx || !input || !w || !output || M < 0) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_host_w: bad arguments");
+    if (w->K != K || w->N != N)
+        return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "qmatmul_host_w: weight is N=%d K=%d, call says N=%d K=%d", w->N, w->K, N, K);
+    if (M == 0) return SMC_OK;
+    return qmatmul_host_impl(ctx, input, w, output, M, mode);
 }
 
 int smc_vecdot_host(smc_ctx *ctx, const float *input, const void *host_raw, int col, int K, int dtype, float *result)

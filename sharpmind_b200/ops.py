@@ -197,6 +197,19 @@ class QuantizationOps:
                                                      self.mode if mode is None else int(mode)))
         return output
 
+    def QuantizedMatMulHandle(self, input, weight: "Weight", output, M, K, N, mode=None):
+        """The same slot for a layer that kept the `Weight` its registration returned (smc_qmatmul_host_w): host
+        activations in, host results out, no lookup by pointer; works for weights registered from device memory."""
+        x = _f32(input)
+        if x.size != M * K:
+            raise ArgumentException(f"input holds {x.size} values, expected M*K = {M * K}")
+        if not (isinstance(output, np.ndarray) and output.dtype == np.float32 and output.flags.c_contiguous
+                and output.size == M * N):
+            raise ArgumentException("output must be a C-contiguous float32 array of M*N values")
+        self.ctx.check(self.ctx.lib.smc_qmatmul_host_w(self.ctx.h, x.ctypes.data, weight.handle, output.ctypes.data,
+                                                       M, K, N, self.mode if mode is None else int(mode)))
+        return output
+
     def QuantizedMatMulQ8_0(self, input, rawWeights, output, M, K, N):
         return self.QuantizedMatMulFn(QuantDType.Q8_0, input, rawWeights, output, M, K, N)
 

@@ -121,7 +121,7 @@ class PeerGather:
 
         import torch
 
-        self.ctx, self.split, self.torch, self.C = ctx, split, torch, C
+        self.ctx, self.split, self.torch, self.C, self.dist = ctx, split, torch, C, dist
         self.capacity = int(capacity_floats)
         h = C.c_void_p()
         ctx.check(ctx.lib.smc_gather_create(ctx.h, split.rank, split.world, self.capacity, C.byref(h)))
@@ -166,6 +166,12 @@ class PeerGather:
         self.ctx.check(self.ctx.lib.smc_gather_exchange_dev(self.ctx.h, self.h, int(count), self._stream()))
 
     def close(self):
+        """Every rank must call this (it is collective when `dist` was given): a peer's kernel may still be storing
+        packets or ready flags into this rank's buffer, so each rank first finishes its own device work and then all
+        ranks meet before any of them unmaps or frees anything."""
         if self.h:
+            self.torch.cuda.synchronize()
+            if self.dist is not None and self.split.world > 1:
+                self.dist.barrier()
             self.ctx.lib.smc_gather_destroy(self.ctx.h, self.h)
             self.h = None

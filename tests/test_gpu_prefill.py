@@ -38,6 +38,37 @@ def test_tc_matmul_matches_oracle(oracle, cuda, dev, n, k, m):
     cuda.release(w)
 
 
+@pytest.mark.parametrize("n,k", [(28672, 8192), (8192, 28672)])
+def test_tc_matmul_llama70b_shapes_sampled_rows(oracle, cuda, dev, n, k):
+    """The benchmarked prefill shapes (Llama-3-70B FFN, 512 tokens): weights drawn and quantised on the device, sampled
+    weight rows (first, last, both sides of a 128-row tile edge, 16 random ones) against the oracle's scalar vec-dot
+    on every token, at the same per-output bound as the small shapes (the bound scales with ||w|| ||x||, hence with K)."""
+    import torch
+
+    m = 512
+    g = torch.Generator(device="cuda").manual_seed(n + 7 * k)
+    raw_d = dev.quantize_weights(Q4_K, torch.randn((n, k), generator=g, device="cuda") * 0.02)
+    w = cuda.register_dev(raw_d, Q4_K, n, k)
+    x = synth.normal("prefill", f"x70b_{k}", (m, k))
+    got = dev.qmatmul_tc(to_dev(x), w).cpu().numpy()
+    assert cuda.device_status() == 0
+    rs = np.random.default_rng(n)
+    rows = sorted({0, n - 1, 127, 128, n // 2 - 1, n // 2} | set(int(r) for r in rs.integers(0, n, 16)))
+    per_row = k // 256 * 144
+    xn = np.linalg.norm(x.astype(np.float64), axis=1)
+    worst = 0.0
+    for r in rows:
+        raw_row = raw_d[r * per_row:(r + 1) * per_row].cpu().numpy()
+        want = oracle.qmatmul(Q4_K, x, raw_row, m, k, 1)[:, 0]
+        wn = np.linalg.norm(oracle.dequantize(Q4_K, raw_row, k).astype(np.float64))
+        bound = 1e-5 * wn * xn
+        err = np.abs(got[:, r].astype(np.float64) - want)
+        worst = max(worst, float(np.max(err / bound)))
+        assert np.all(err <= bound), (r, worst)
+    print(f"tcgen05 matmul {n}x{k}, 512 tokens: worst error {worst:.3f} of the bound over {len(rows)} sampled rows")
+    cuda.release(w)
+
+
 def test_tc_matmul_scaling_and_zero_rows(oracle, cuda, dev):
     """Rows of very different magnitude (per-token power-of-two scale) and an all-zero row."""
     n, k, m = 128, 512, 16

@@ -137,6 +137,8 @@ def test_one_row_long_rows_against_oracle(oracle, cuda, dev, dtype, n, k):
 # row from the lane sums its previous warp left: an output's bits must not depend on how the rows were divided.
 # The options change the grid, the stage length and with them every piece boundary.
 PARTITION_SHAPES = [
+    (Q4_K, 28672, 4096),   # the Llama-3-8B gate||up launch of the benchmark
+    (Q4_K, 8192, 28672),   # Llama-3-70B down: the row takes two rounds of activation loads
     (Q6_K, 4096, 14336), (Q6_K, 3, 14336), (Q6_K, 37, 6144), (Q4_K, 4096, 4096), (Q4_K, 1, 8192), (Q4_K, 445, 2048),
     (Q8_0, 1500, 2048), (Q8_0, 7, 5120), (Q8_0, 3072, 1024),
 ]
