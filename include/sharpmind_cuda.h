@@ -152,6 +152,13 @@ SMC_API int smc_sdpa_host(smc_ctx *ctx, const float *q, const float *k, const fl
 SMC_API int smc_qmatmul_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, int mode,
                             void *stream);
 
+/* LinearLayer.AddBiasInPlace (SharpMind.Model/Layers/Linearlayer.cs:154-163): d_out[r, j] += d_bias[j] for every row. */
+SMC_API int smc_add_bias_dev(smc_ctx *ctx, float *d_out, const float *d_bias, int rows, int n, void *stream);
+/* InferenceLinearLayer.Forward (SharpMind.Model/Layers/InferenceLinearLayer.cs:148-190): the matmul of smc_qmatmul_dev
+ * followed, when d_bias is not null, by the bias add. */
+SMC_API int smc_linear_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, const float *d_bias, float *d_out, int M,
+                           int mode, void *stream);
+
 /* Q8_0 activation buffers: the device form of QuantizedKVCache.QuantizeRowQ8_0
  * (SharpMind.Model/QuantizedKVCache.cs:191-223): d = amax/127 (1 for an all-zero block), stored as
  * fp16 (round to nearest even), q = round-half-even(x/d). */
@@ -249,6 +256,10 @@ typedef struct smc_model_desc {
     const float *const *norm1, *const *norm2, *const *qnorm, *const *knorm;                        /* [n_layers] */
     const float *final_norm;
     const smc_weight *lm_head;
+    /* Bias vectors of the linear layers (LinearLayer._bias, added by AddBiasInPlace, Linearlayer.cs:154-163): each
+     * member is null (no such biases anywhere) or an array of n_layers device pointers whose entries may be null.
+     * bq [heads*headDim], bk / bv [kvHeads*headDim], bo [hidden], bgu [2*ffn], bdown [hidden]. */
+    const float *const *bq, *const *bk, *const *bv, *const *bo, *const *bgu, *const *bdown;
 } smc_model_desc;
 /* Allocates the fp32 KV cache [layer, max_batch, kvHeads, max_seq, headDim] (KVCache.cs:13-14), RoPE tables
  * and intermediates.  The description's arrays are copied; the weights stay owned by the context. */
@@ -306,12 +317,22 @@ SMC_API int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts,
  * itself moves no data through the host or a collective library: the producing kernel stores its slice
  * into every peer's buffer over NVLink and returns when every peer's slice has arrived here.
  * All ranks must issue the same sequence of exchanges on an object; calls on one object must not overlap
- * (one stream).  A peer that does not show up within 2 s raises smc_device_status (value 2). */
+ * (one stream).  A peer that does not show up within the wait limit (2 s unless smc_gather_set_wait_ns changed it)
+ * raises smc_device_status (value 2): the kernel still ends, the context stays usable, the data of that exchange is
+ * invalid.  Teardown: every rank finishes its device work and all ranks meet (a barrier of the host's choosing) BEFORE
+ * any of them calls smc_gather_destroy, and likewise after a status 2 before the objects are reused or destroyed: a
+ * peer's kernel may still be storing into this rank's buffer. */
 typedef struct smc_gather smc_gather;
 #define SMC_IPC_HANDLE_BYTES 64
 SMC_API int smc_gather_create(smc_ctx *ctx, int rank, int world, size_t capacity_floats, smc_gather **out);
 SMC_API int smc_gather_export(smc_ctx *ctx, smc_gather *g, unsigned char *handle /* [64] */);
 SMC_API int smc_gather_connect(smc_ctx *ctx, smc_gather *g, const unsigned char *handles /* [world][64] */);
+/* The same for ranks that live in ONE process (one host thread per GPU, or several objects on one GPU): `all` holds the
+ * `world` objects in rank order, all[rank] == g; the peers' buffers are addressed directly, no IPC handle is involved.
+ * Objects on different GPUs need peer access between them enabled by the caller. */
+SMC_API int smc_gather_connect_local(smc_ctx *ctx, smc_gather *g, smc_gather *const *all /* [world] */);
+/* Limit of every wait of an exchange on this object, in nanoseconds (default 2 000 000 000). */
+SMC_API int smc_gather_set_wait_ns(smc_ctx *ctx, smc_gather *g, unsigned long long ns);
 /* Device address of the receive buffer (chunk r at d_buf + r * count for an exchange of `count` floats). */
 SMC_API int smc_gather_buffer(smc_ctx *ctx, smc_gather *g, float **d_buf);
 /* y_local = x W_local^T written as this rank's chunk, then exchanged; on return of the launch's completion

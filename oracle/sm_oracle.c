@@ -859,7 +859,18 @@ typedef struct {
     /* formats of the down projection and of the LM head / embedding when they differ from `dtype`
      * (GGUF files mix formats per tensor); 0 = same as `dtype` */
     int down_dtype, head_dtype;
+    /* bias vectors of the linear layers (LinearLayer._bias): null, or n_layers pointers whose entries may be null */
+    const float **bq, **bk, **bv, **bo, **bgu, **bdown;
 } smo_model;
+
+/* LinearLayer.AddBiasInPlace (SharpMind.Model/Layers/Linearlayer.cs:154-163): row[j] += bias[j] for every row. */
+static void add_bias(float *out, const float **per_layer, int layer, int rows, int n)
+{
+    if (!per_layer || !per_layer[layer]) return;
+    const float *bias = per_layer[layer];
+    for (int i = 0; i < rows; i++)
+        for (int j = 0; j < n; j++) out[(size_t)i * n + j] += bias[j];
+}
 
 /* The matmul of the decode step.  act_q8 == 0: the reference's own arithmetic (fp32 activations into the scalar
  * vec-dot).  act_q8 != 0: what the CUDA library's SMC_ACT_Q8 mode is specified to compute -- every activation row is
@@ -916,6 +927,7 @@ SMO_API int smo_decode_step_ex(const smo_model *m, const int *tokens, int batch,
         if ((rc = step_matmul(act_q8, m->dtype, xn, m->wq[L], q, batch, H, qDim))) goto done;
         if ((rc = step_matmul(act_q8, m->dtype, xn, m->wk[L], k, batch, H, kvDim))) goto done;
         if ((rc = step_matmul(act_q8, m->dtype, xn, m->wv[L], v, batch, H, kvDim))) goto done;
+        add_bias(q, m->bq, L, batch, qDim), add_bias(k, m->bk, L, batch, kvDim), add_bias(v, m->bv, L, batch, kvDim);
         if (m->qk_norm) {
             smo_rmsnorm(q, m->qnorm[L], q, batch * nh, hd, m->eps);
             smo_rmsnorm(k, m->knorm[L], k, batch * nkv, hd, m->eps);
@@ -941,12 +953,15 @@ SMO_API int smo_decode_step_ex(const smo_model *m, const int *tokens, int batch,
                                att + (size_t)b * qDim + (size_t)h * hd, 1, kvLen, hd, scale, 1, qDim, qDim);
             }
         if ((rc = step_matmul(act_q8, m->dtype, att, m->wo[L], tmp, batch, qDim, H))) goto done;
+        add_bias(tmp, m->bo, L, batch, H);
         smo_add_inplace(x, tmp, (int64_t)B * H);
         smo_rmsnorm(x, m->norm2[L], xn, batch, H, m->eps);
         if ((rc = step_matmul(act_q8, m->dtype, xn, m->wgu[L], gu, batch, H, 2 * F))) goto done;
+        add_bias(gu, m->bgu, L, batch, 2 * F);
         for (int b = 0; b < batch; b++)
             smo_swiglu(gu + (size_t)b * 2 * F, gu + (size_t)b * 2 * F + F, act + (size_t)b * F, F);
         if ((rc = step_matmul(act_q8, m->down_dtype ? m->down_dtype : m->dtype, act, m->wdown[L], tmp, batch, F, H))) goto done;
+        add_bias(tmp, m->bdown, L, batch, H);
         smo_add_inplace(x, tmp, (int64_t)B * H);
     }
     smo_rmsnorm(x, m->final_norm, x, batch, H, m->eps);

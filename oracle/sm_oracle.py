@@ -379,6 +379,8 @@ class _Model(C.Structure):
         ("final_norm", C.c_void_p), ("lm_head", C.c_void_p), ("embedding", C.c_void_p),
         ("cosT", C.c_void_p), ("sinT", C.c_void_p),
         ("down_dtype", C.c_int), ("head_dtype", C.c_int),
+        ("bq", C.POINTER(C.c_void_p)), ("bk", C.POINTER(C.c_void_p)), ("bv", C.POINTER(C.c_void_p)),
+        ("bo", C.POINTER(C.c_void_p)), ("bgu", C.POINTER(C.c_void_p)), ("bdown", C.POINTER(C.c_void_p)),
     ]
 
 
@@ -417,6 +419,12 @@ class Decoder:
         m.wgu, m.wdown = arr("wgu"), arr("wdown")
         m.norm1, m.norm2 = arr("norm1"), arr("norm2")
         m.qnorm, m.knorm = arr("qnorm"), arr("knorm")
+        for name in ("bq", "bk", "bv", "bo", "bgu", "bdown"):  # optional bias vectors (entries may be None)
+            if weights.get(name) is None:
+                continue
+            a = (C.c_void_p * L)(*[None if b is None else b.ctypes.data for b in weights[name]])
+            self._keep.append(a)
+            setattr(m, name, C.cast(a, C.POINTER(C.c_void_p)))
         m.final_norm = weights["final_norm"].ctypes.data
         m.lm_head = weights["embedding"].ctypes.data
         m.embedding = self.embedding.ctypes.data

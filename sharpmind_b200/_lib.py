@@ -57,6 +57,8 @@ SIGNATURES = {
     "smc_rope_dev": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_void_p]),
     "smc_add_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "smc_add_bias_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "smc_linear_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "smc_argmax_dev": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "smc_embed_q8_0_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "smc_sdpa_decode_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -73,6 +75,8 @@ SIGNATURES = {
     "smc_gather_create": (c_int, [c_void_p, c_int, c_int, c_size_t, _pp]),
     "smc_gather_export": (c_int, [c_void_p, c_void_p, c_void_p]),
     "smc_gather_connect": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "smc_gather_connect_local": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "smc_gather_set_wait_ns": (c_int, [c_void_p, c_void_p, C.c_uint64]),
     "smc_gather_buffer": (c_int, [c_void_p, c_void_p, _pp]),
     "smc_qmatmul_gather_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "smc_gather_exchange_dev": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),

@@ -457,6 +457,49 @@ int smc_launch_sdpa_tile(smc_ctx *ctx, const float *q, const float *k, const flo
     return SMC_OK;
 }
 
+// Scratch of the split-KV decode attention: a fixed header of tickets (one per (sequence, virtual KV head), zeroed at
+// allocation and left at zero by every launch), then one record per (sequence, head, split).  It is sized for the most
+// splits the shape can ever use (the count grows with kvLen until the whole cache of maxSeq positions is in play), so
+// that decoding further into a sequence never reallocates: growth happens only for a larger batch, more heads or a
+// larger maxSeq, after a device-wide synchronisation (make the first call of such a shape outside stream capture;
+// smc_model_create reserves for the model's own shape).  Caller holds ctx->mu_scratch.
+constexpr size_t TICKET_BYTES = 65536 * sizeof(unsigned);
+static int reserve_split_scratch(smc_ctx *ctx, int batch, int heads, int kvHeadsVirtual, int headDim, int maxSeq)
+{
+    const int pairs = batch * kvHeadsVirtual;
+    if ((size_t)pairs > 65536) return smc_fail(ctx, SMC_E_RANGE, "sdpa_decode: more than 65536 (sequence, KV head) pairs");
+    int worst = (2 * ctx->sm_count + pairs - 1) / pairs;
+    if (worst > (maxSeq + 63) / 64) worst = (maxSeq + 63) / 64;
+    if (worst < 1) worst = 1;
+    if (worst > MERGE_MAX_SPLITS) worst = MERGE_MAX_SPLITS;
+    const size_t need = TICKET_BYTES + (size_t)batch * heads * head_record_floats(worst, headDim) * sizeof(float);
+    if (need <= ctx->attn_part_cap) return SMC_OK;
+    if (ctx->d_attn_part) {
+        cudaDeviceSynchronize();
+        cudaFree(ctx->d_attn_part);
+    }
+    ctx->d_attn_part = nullptr;
+    ctx->attn_part_cap = 0;
+    SMC_CUDA(ctx, cudaMalloc(&ctx->d_attn_part, need));
+    SMC_CUDA(ctx, cudaMemset(ctx->d_attn_part, 0, TICKET_BYTES));
+    ctx->attn_part_cap = need;
+    return SMC_OK;
+}
+
+// Reserves the decode attention's scratch for every batch size up to `max_batch` of a model shape.
+int smc_sdpa_decode_reserve(smc_ctx *ctx, int max_batch, int heads, int kvHeads, int headDim, int maxSeq)
+{
+    const int Gall = heads / kvHeads;
+    const int G = Gall > 2 ? (Gall % 2 == 0 ? 2 : 1) : Gall;
+    const int kvVirtual = kvHeads * (Gall / G);
+    std::lock_guard<std::mutex> lock(ctx->mu_scratch);
+    for (int b = 1; b <= max_batch; ++b) {  // the record count is not monotonic in the batch size (fewer splits per pair)
+        int rc = reserve_split_scratch(ctx, b, heads, kvVirtual, headDim, maxSeq);
+        if (rc) return rc;
+    }
+    return SMC_OK;
+}
+
 extern "C" {
 
 int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const float *d_v, float *d_out, int batch,
@@ -473,10 +516,8 @@ int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const 
     // spread over CTAs that read the same cached head (the second read comes from L2).  Measured on a Llama-3-8B
     // shape (4 per KV head, context 2048): 2.40 -> 2.16 ms per step at batch 1 together with the wide-FFN path,
     // 6.0 -> 5.2 ms at batch 8, 12.9 -> 11.8 ms at batch 32 against all four heads in one CTA.
-    // SMC_ATTN_WIDE_FROM=<batch> brings the four-head CTA back from that batch size on.
     int G = Gall;
-    static const int wide_from = getenv("SMC_ATTN_WIDE_FROM") ? atoi(getenv("SMC_ATTN_WIDE_FROM")) : (1 << 30);
-    if (Gall > 2) G = (Gall % 4 == 0 && batch >= wide_from) ? 4 : (Gall % 2 == 0 ? 2 : 1);
+    if (Gall > 2) G = Gall % 2 == 0 ? 2 : 1;
     const int hshare = Gall / G;
     const int kvReal = kvHeads;
     kvHeads *= hshare;  // virtual KV heads from here on
@@ -503,23 +544,10 @@ int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const 
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
     if (splits > MERGE_MAX_SPLITS) splits = MERGE_MAX_SPLITS;
-    // scratch: a fixed header of tickets (one per (sequence, KV head), zeroed at allocation and left at zero by
-    // every launch), then one record per (sequence, head, split); grown on demand (the first call of a larger
-    // shape allocates: make it outside stream capture)
-    constexpr size_t TICKET_BYTES = 65536 * sizeof(unsigned);
-    if ((size_t)batch * kvHeads > 65536) return smc_fail(ctx, SMC_E_RANGE, "sdpa_decode: more than 65536 (sequence, KV head) pairs");
-    const size_t need = TICKET_BYTES + (size_t)batch * heads * head_record_floats(splits, headDim) * sizeof(float);
-    if (need > ctx->attn_part_cap) {
-        std::lock_guard<std::mutex> lock(ctx->mu);
-        if (ctx->d_attn_part) {
-            cudaDeviceSynchronize();
-            cudaFree(ctx->d_attn_part);
-        }
-        ctx->d_attn_part = nullptr;
-        ctx->attn_part_cap = 0;
-        SMC_CUDA(ctx, cudaMalloc(&ctx->d_attn_part, need));
-        SMC_CUDA(ctx, cudaMemset(ctx->d_attn_part, 0, TICKET_BYTES));
-        ctx->attn_part_cap = need;
+    std::lock_guard<std::mutex> scratch_lock(ctx->mu_scratch);  // held until the launch is queued (one stream per context)
+    {
+        int rc = reserve_split_scratch(ctx, batch, heads, kvHeads, headDim, maxSeq);
+        if (rc) return rc;
     }
     unsigned *tickets = reinterpret_cast<unsigned *>(ctx->d_attn_part);
     float *records = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ctx->d_attn_part) + TICKET_BYTES);

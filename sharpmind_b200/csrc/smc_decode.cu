@@ -23,6 +23,10 @@ struct smc_model {
     float *qkv = nullptr;            // [batch][qDim + 2 kvDim]
     float *x2 = nullptr;             // second residual buffer of the one-sequence path (the stream ping-pongs)
     std::vector<const float *> norm1, norm2, qnorm, knorm;
+    // optional per-layer bias vectors of the linear layers (LinearLayer.AddBiasInPlace); bqkv = [bq | bk | bv] (owned)
+    std::vector<const float *> bq, bk, bv, bo, bgu, bdown;
+    std::vector<float *> bqkv;
+    bool has_bias = false;
     float *kcache = nullptr, *vcache = nullptr;  // [layer][batch][kvHeads][max_seq][head_dim]
     float *cosT = nullptr, *sinT = nullptr;
     float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *tmp = nullptr,
@@ -39,6 +43,7 @@ void free_model(smc_ctx *ctx, smc_model *m)
     for (float *p : bufs) cudaFree(p);
     for (smc_weight *w : m->wqkv)
         if (w) smc_weight_release(ctx, w);
+    for (float *b : m->bqkv) cudaFree(b);
     smc_q8act_free(m->qa);
     smc_q8act_free(m->qb);
     delete m;
@@ -76,10 +81,11 @@ int alloc_rows(smc_ctx *ctx, smc_model *m, int rows)
 // y[M, N] = x[M, K] W^T in the requested mode; for SMC_ACT_Q8 with several rows the quantised rows in
 // `pre` (made by the caller from the same x) are reused instead of quantising again.
 int linear(smc_ctx *ctx, const float *x, const smc_weight *w, float *y, int M, int mode, const smc_q8act *pre,
-           cudaStream_t s)
+           cudaStream_t s, const float *bias = nullptr)
 {
-    if (mode == SMC_ACT_Q8 && pre) return smc_qmatmul_q8_dev(ctx, pre, w, y, s);
-    return smc_qmatmul_dev(ctx, x, w, y, M, mode, s);
+    int rc = (mode == SMC_ACT_Q8 && pre) ? smc_qmatmul_q8_dev(ctx, pre, w, y, s) : smc_qmatmul_dev(ctx, x, w, y, M, mode, s);
+    if (rc || !bias) return rc;
+    return smc_add_bias_dev(ctx, y, bias, M, w->N, s);  // InferenceLinearLayer.Forward: matmul, then AddBiasInPlace
 }
 
 // src [layers][batch][kvHeads][len][headDim] dense  ->  cache [layers][max_batch][kvHeads][max_seq][headDim]
@@ -241,6 +247,15 @@ int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, sm
     copy_w(m->wq, d.wq), copy_w(m->wk, d.wk), copy_w(m->wv, d.wv), copy_w(m->wo, d.wo), copy_w(m->wgu, d.wgu),
         copy_w(m->wdown, d.wdown);
     copy_f(m->norm1, d.norm1), copy_f(m->norm2, d.norm2), copy_f(m->qnorm, d.qnorm), copy_f(m->knorm, d.knorm);
+    auto copy_b = [&](std::vector<const float *> &dst, const float *const *src) {
+        dst.assign(d.n_layers, nullptr);
+        if (!src) return;
+        for (int l = 0; l < d.n_layers; ++l) {
+            dst[l] = src[l];
+            m->has_bias = m->has_bias || src[l] != nullptr;
+        }
+    };
+    copy_b(m->bq, d.bq), copy_b(m->bk, d.bk), copy_b(m->bv, d.bv), copy_b(m->bo, d.bo), copy_b(m->bgu, d.bgu), copy_b(m->bdown, d.bdown);
     const size_t B = (size_t)max_batch;
     const size_t cache = (size_t)d.n_layers * B * d.n_kv_heads * d.max_seq * d.head_dim;
     const size_t half = (size_t)d.max_seq * (d.head_dim / 2);
@@ -271,12 +286,27 @@ int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, sm
               parts[0]->dtype == parts[2]->dtype))
             continue;
         rc = smc_weight_concat_rows(ctx, parts, 3, &m->wqkv[l]);
+        if (rc == SMC_E_UNSUPPORTED) rc = SMC_OK, m->wqkv[l] = nullptr;  // parts that cannot be joined stay three matmuls
+    }
+    // the joined matmul takes the three bias vectors joined the same way (zeros where a projection has none)
+    m->bqkv.assign(d.n_layers, nullptr);
+    for (int l = 0; l < d.n_layers && !rc; ++l) {
+        if (!m->wqkv[l] || !(m->bq[l] || m->bk[l] || m->bv[l])) continue;
+        cudaError_t ce = cudaMalloc(&m->bqkv[l], (size_t)(qDim + 2 * kvDim) * sizeof(float));
+        if (ce == cudaSuccess) ce = cudaMemset(m->bqkv[l], 0, (size_t)(qDim + 2 * kvDim) * sizeof(float));
+        const float *src[3] = {m->bq[l], m->bk[l], m->bv[l]};
+        const int off[3] = {0, qDim, qDim + kvDim}, len[3] = {qDim, kvDim, kvDim};
+        for (int i = 0; i < 3 && ce == cudaSuccess; ++i)
+            if (src[i]) ce = cudaMemcpy(m->bqkv[l] + off[i], src[i], (size_t)len[i] * sizeof(float), cudaMemcpyDeviceToDevice);
+        if (ce != cudaSuccess) rc = smc_fail(ctx, SMC_E_CUDA, "model_create: bias: %s", cudaGetErrorString(ce));
     }
     if (rc) {
         free_model(ctx, m);
         return rc;
     }
     rc = smc_rope_tables(ctx, d.rope_theta, d.head_dim, d.max_seq, m->cosT, m->sinT);
+    // the attention's scratch for every step this model can run: decoding never allocates
+    if (!rc && (d.head_dim == 64 || d.head_dim == 128)) rc = smc_sdpa_decode_reserve(ctx, max_batch, d.n_heads, d.n_kv_heads, d.head_dim, d.max_seq);
     if (rc) {
         free_model(ctx, m);
         return rc;
@@ -331,7 +361,7 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
     // per-head norm + RoPE + append, attention, Wo, gate||up, down (+ the next layer's QKV takes its residual).
     // (an FFN wider than 8192 keeps its SiLU-gate as a launch of its own: the down-projection's row is then too
     // long to be worth staging through the gate in every CTA)
-    bool one_row = mode == SMC_ACT_Q8 && B == 1 && H <= 8192 && smc_tma_supported(d.lm_head, 1) &&
+    bool one_row = mode == SMC_ACT_Q8 && B == 1 && H <= 8192 && !m->has_bias && smc_tma_supported(d.lm_head, 1) &&
                    (F <= 8192 || m->qb);
     for (int l = 0; l < d.n_layers && one_row; ++l)
         one_row = m->wqkv[l] && smc_tma_supported(m->wqkv[l], 1) && smc_tma_supported(m->wgu[l], 1) && m->wdown[l]->fast &&
@@ -373,12 +403,12 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
         // the joined matrix carries no GGUF-layout copy unless its parts kept theirs: reference order needs it
         const smc_weight *joined = m->wqkv[l];
         if (joined && (mode != SMC_REF_ORDER || joined->d_raw)) {
-            SMC_TRY(linear(ctx, m->xn, joined, m->qkv, B, mode, reuse ? m->qa : nullptr, s));
+            SMC_TRY(linear(ctx, m->xn, joined, m->qkv, B, mode, reuse ? m->qa : nullptr, s, m->bqkv[l]));
             SMC_TRY(launch_qkv_post(ctx, m, l, kc, vc, B, pos, s));
         } else {
-            SMC_TRY(linear(ctx, m->xn, m->wq[l], m->q, B, mode, reuse ? m->qa : nullptr, s));
-            SMC_TRY(linear(ctx, m->xn, m->wk[l], m->k, B, mode, reuse ? m->qa : nullptr, s));
-            SMC_TRY(linear(ctx, m->xn, m->wv[l], m->v, B, mode, reuse ? m->qa : nullptr, s));
+            SMC_TRY(linear(ctx, m->xn, m->wq[l], m->q, B, mode, reuse ? m->qa : nullptr, s, m->bq[l]));
+            SMC_TRY(linear(ctx, m->xn, m->wk[l], m->k, B, mode, reuse ? m->qa : nullptr, s, m->bk[l]));
+            SMC_TRY(linear(ctx, m->xn, m->wv[l], m->v, B, mode, reuse ? m->qa : nullptr, s, m->bv[l]));
             if (d.qk_norm) {
                 SMC_TRY(smc_rmsnorm_dev(ctx, m->q, m->qnorm[l], m->q, B * nh, hd, d.eps, s));
                 SMC_TRY(smc_rmsnorm_dev(ctx, m->k, m->knorm[l], m->k, B * nkv, hd, d.eps, s));
@@ -390,11 +420,11 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
         }
         SMC_TRY(smc_sdpa_decode_dev(ctx, m->q, kc, vc, m->att, B, nh, nkv, hd, pos + 1, d.max_seq, scale, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->att, B, qDim, m->qb, s));
-        SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s));
+        SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s, m->bo[l]));
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, B, H, d.eps, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
-        SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, B, mode, reuse ? m->qa : nullptr, s));
-        if (mode == SMC_ACT_Q8 && B == 1 && F <= 8192 && m->wdown[l]->fast && smc_tma_supported(m->wdown[l], 1)) {
+        SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, B, mode, reuse ? m->qa : nullptr, s, m->bgu[l]));
+        if (mode == SMC_ACT_Q8 && B == 1 && F <= 8192 && !m->bdown[l] && m->wdown[l]->fast && smc_tma_supported(m->wdown[l], 1)) {
             // one row: SiLU(gate) * up is formed and quantised while the down-projection stages its activations
             SMC_TRY(smc_launch_gemv_tma_swiglu(ctx, m->gu, m->gu + F, m->wdown[l], m->tmp, s));
         } else {
@@ -403,7 +433,7 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
             } else {
                 SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, B, F, 2 * F, s));
             }
-            SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s));
+            SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s, m->bdown[l]));
         }
         // residual add, then the next block's first norm (the final norm after the last block)
         const float *next_norm = l + 1 < d.n_layers ? m->norm1[l + 1] : d.final_norm;
@@ -445,21 +475,21 @@ int smc_forward_last_logits(smc_ctx *ctx, smc_model *m, const int *d_tokens, int
     for (int l = 0; l < d.n_layers; ++l) {
         float *kc = m->kcache + (size_t)l * layer_stride, *vc = m->vcache + (size_t)l * layer_stride;
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, T, H, m->qa, s));
-        SMC_TRY(linear(ctx, m->xn, m->wqkv[l], m->qkv, T, mode, reuse ? m->qa : nullptr, s));
+        SMC_TRY(linear(ctx, m->xn, m->wqkv[l], m->qkv, T, mode, reuse ? m->qa : nullptr, s, m->bqkv[l]));
         // row t: per-head norm, rotation by position pos + t, K and V appended to sequence `seq`
         SMC_TRY(launch_qkv_post(ctx, m, l, kc, vc, T, pos, s, seq));
         SMC_TRY(smc_launch_sdpa_prefill(ctx, m->q, kc + seq_off, vc + seq_off, m->att, T, nh, nkv, hd, pos, d.max_seq, scale, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->att, T, qDim, m->qb, s));
-        SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s));
+        SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s, m->bo[l]));
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, T, H, d.eps, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, T, H, m->qa, s));
-        SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, T, mode, reuse ? m->qa : nullptr, s));
+        SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, T, mode, reuse ? m->qa : nullptr, s, m->bgu[l]));
         if (reuse) {
             SMC_TRY(smc_launch_swiglu_quantize_q8(ctx, m->gu, m->gu + F, T, F, 2 * F, m->qb, s));
         } else {
             SMC_TRY(smc_swiglu_dev(ctx, m->gu, m->gu + F, m->act, T, F, 2 * F, s));
         }
-        SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s));
+        SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s, m->bdown[l]));
         const float *next_norm = l + 1 < d.n_layers ? m->norm1[l + 1] : d.final_norm;
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, T, H, d.eps, s));
     }

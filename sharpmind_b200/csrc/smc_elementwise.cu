@@ -274,6 +274,14 @@ __global__ void __launch_bounds__(256) rope_kernel(float *__restrict__ x, int se
 }
 
 // ---------------------------------------------------------------------------- add / argmax / embed
+// LinearLayer.AddBiasInPlace (SharpMind.Model/Layers/Linearlayer.cs:154-163): out[r, j] += bias[j].
+__global__ void __launch_bounds__(256) add_bias_kernel(float *__restrict__ out, const float *__restrict__ bias, long long total, int n)
+{
+    smc_grid_dep_sync();
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) out[t] = out[t] + __ldg(bias + t % n);
+}
+
 __global__ void __launch_bounds__(256) add_kernel(float *__restrict__ x, const float *__restrict__ y, long long n)
 {
     long long stride = (long long)gridDim.x * blockDim.x;
@@ -521,6 +529,25 @@ int smc_add_dev(smc_ctx *ctx, float *d_x, const float *d_y, int64_t n, void *str
     add_kernel<<<ew_grid(n / 4 + 1, ctx->sm_count * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(d_x, d_y, n);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
+}
+
+int smc_add_bias_dev(smc_ctx *ctx, float *d_out, const float *d_bias, int rows, int n, void *stream)
+{
+    if (!ctx || !d_out || !d_bias || rows < 0 || n <= 0) return smc_fail(ctx, SMC_E_INVALID, "add_bias: bad arguments");
+    if (rows == 0) return SMC_OK;
+    const long long total = (long long)rows * n;
+    smc_launch_dep(ctx->use_pdl, add_bias_kernel, dim3(ew_grid(total, ctx->sm_count * 8)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                   d_out, d_bias, total, n);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+int smc_linear_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, const float *d_bias, float *d_out, int M, int mode,
+                   void *stream)
+{
+    int rc = smc_qmatmul_dev(ctx, d_in, w, d_out, M, mode, stream);
+    if (rc || !d_bias || M == 0) return rc;
+    return smc_add_bias_dev(ctx, d_out, d_bias, M, w->N, stream);
 }
 
 int smc_argmax_dev(smc_ctx *ctx, const float *d_logits, int rows, int n, int *d_out, void *stream)

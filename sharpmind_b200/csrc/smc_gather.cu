@@ -99,6 +99,7 @@ int smc_gather_create(smc_ctx *ctx, int rank, int world, size_t capacity_floats,
         return smc_fail(ctx, SMC_E_CUDA, "gather_create: %s", cudaGetErrorString(e));
     }
     g->view.rank = rank, g->view.world = world, g->view.status = ctx->d_status;
+    g->view.wait_ns = SMC_GATHER_WAIT_NS;
     g->view.ctrl[rank] = reinterpret_cast<smc_gather_ctrl *>(g->base);
     g->view.data = reinterpret_cast<float *>(g->base + SMC_GATHER_CTRL_BYTES);
     g->view.peer_data[rank] = g->view.data;
@@ -146,6 +147,35 @@ int smc_gather_connect(smc_ctx *ctx, smc_gather *g, const unsigned char *handles
     if (rc) return rc;
     g->connected = true;
     return SMC_OK;
+}
+
+int smc_gather_connect_local(smc_ctx *ctx, smc_gather *g, smc_gather *const *all)
+{
+    if (!ctx || !g || !all) return smc_fail(ctx, SMC_E_INVALID, "gather_connect_local: bad arguments");
+    if (g->connected) return smc_fail(ctx, SMC_E_INVALID, "gather_connect_local: already connected");
+    for (int p = 0; p < g->world; ++p)
+        if (!all[p] || all[p]->world != g->world || all[p]->rank != p || all[p]->capacity != g->capacity || (p == g->rank && all[p] != g))
+            return smc_fail(ctx, SMC_E_INVALID, "gather_connect_local: entry %d is not rank %d of a world of %d with this capacity", p, p, g->world);
+    SMC_CUDA(ctx, cudaSetDevice(ctx->device));
+    for (int p = 0; p < g->world; ++p) {
+        if (p == g->rank) continue;
+        unsigned char *ptr = all[p]->base;  // same process: the peer's allocation is addressed directly
+        g->view.ctrl[p] = reinterpret_cast<smc_gather_ctrl *>(ptr);
+        g->view.pkt[p] = reinterpret_cast<unsigned long long *>(ptr + SMC_GATHER_CTRL_BYTES + g->capacity * sizeof(float));
+        g->view.peer_data[p] = reinterpret_cast<float *>(ptr + SMC_GATHER_CTRL_BYTES);
+    }
+    int rc = upload_view(ctx, g);
+    if (rc) return rc;
+    g->connected = true;
+    return SMC_OK;
+}
+
+int smc_gather_set_wait_ns(smc_ctx *ctx, smc_gather *g, unsigned long long ns)
+{
+    if (!ctx || !g || ns == 0) return smc_fail(ctx, SMC_E_INVALID, "gather_set_wait_ns: bad arguments");
+    SMC_CUDA(ctx, cudaSetDevice(ctx->device));
+    g->view.wait_ns = ns;
+    return upload_view(ctx, g);
 }
 
 int smc_gather_buffer(smc_ctx *ctx, smc_gather *g, float **d_buf)

@@ -25,7 +25,7 @@
 
 #define SMC_GATHER_MAX_RANKS 8
 #define SMC_GATHER_CTRL_BYTES 256
-#define SMC_GATHER_WAIT_NS 2000000000ull  // 2 s
+#define SMC_GATHER_WAIT_NS 2000000000ull  // default limit of every wait: 2 s (smc_gather_set_wait_ns changes it per object)
 
 // Control block at the start of each rank's allocation (what peers address).
 struct smc_gather_ctrl {
@@ -43,6 +43,7 @@ struct smc_gather_dev {
     float *data;                                     // this rank's dense data area
     int rank, world;
     int *status;  // the context's status word
+    unsigned long long wait_ns;  // limit of every wait of an exchange on this object
 };
 
 #ifdef __CUDACC__
@@ -98,7 +99,7 @@ __device__ __forceinline__ bool smc_gather_wait_ready(const smc_gather_dev *g, u
         while ((int)(smc_ld_relaxed_sys(&me->ready[p]) - tag) < 0) {
             if ((++polls & 63u) == 0) {
                 if (!t0) t0 = smc_globaltimer();
-                else if (smc_globaltimer() - t0 > SMC_GATHER_WAIT_NS) {
+                else if (smc_globaltimer() - t0 > g->wait_ns) {
                     atomicExch(g->status, 2);
                     return false;
                 }
@@ -120,7 +121,7 @@ __device__ __forceinline__ bool smc_gather_wait_ready_warp(const smc_gather_dev 
         while ((int)(smc_ld_relaxed_sys(&me->ready[lane]) - tag) < 0) {
             if ((++polls & 63u) == 0) {
                 if (!t0) t0 = smc_globaltimer();
-                else if (smc_globaltimer() - t0 > SMC_GATHER_WAIT_NS) {
+                else if (smc_globaltimer() - t0 > g->wait_ns) {
                     atomicExch(g->status, 2);
                     ok = false;
                     break;
@@ -167,7 +168,7 @@ __device__ __forceinline__ void smc_gather_collect(const smc_gather_dev *g, size
             const unsigned long long t0 = smc_globaltimer();
             unsigned polls = 0;
             while ((unsigned)((pk = smc_ld_relaxed_sys64(src)) >> 32) != tag) {
-                if ((++polls & 63u) == 0 && smc_globaltimer() - t0 > SMC_GATHER_WAIT_NS) {
+                if ((++polls & 63u) == 0 && smc_globaltimer() - t0 > g->wait_ns) {
                     dead = true;
                     atomicExch(g->status, 2);
                     break;
@@ -212,7 +213,7 @@ __device__ __forceinline__ void smc_gather_finish_bulk(const smc_gather_dev *g, 
         const unsigned long long t0 = smc_globaltimer();
         unsigned polls = 0;
         while ((int)(smc_ld_acquire_sys(&me->arrived[threadIdx.x]) - tag) < 0) {
-            if ((++polls & 63u) == 0 && smc_globaltimer() - t0 > SMC_GATHER_WAIT_NS) {
+            if ((++polls & 63u) == 0 && smc_globaltimer() - t0 > g->wait_ns) {
                 atomicExch(g->status, 2);
                 break;
             }

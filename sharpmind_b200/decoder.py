@@ -23,6 +23,8 @@ class _Desc(C.Structure):
         ("norm1", C.POINTER(C.c_void_p)), ("norm2", C.POINTER(C.c_void_p)),
         ("qnorm", C.POINTER(C.c_void_p)), ("knorm", C.POINTER(C.c_void_p)),
         ("final_norm", C.c_void_p), ("lm_head", C.c_void_p),
+        ("bq", C.POINTER(C.c_void_p)), ("bk", C.POINTER(C.c_void_p)), ("bv", C.POINTER(C.c_void_p)),
+        ("bo", C.POINTER(C.c_void_p)), ("bgu", C.POINTER(C.c_void_p)), ("bdown", C.POINTER(C.c_void_p)),
     ]
 
 
@@ -73,6 +75,16 @@ class Decoder:
         d.qnorm, d.knorm = ptrs(self.norms["qnorm"]), ptrs(self.norms["knorm"])
         d.final_norm = self.final_norm.data_ptr()
         d.lm_head = self.embedding.handle
+        # optional bias vectors of the linear layers: weights["bq"] ... ["bdown"], lists of n_layers arrays (or None)
+        self.biases = {}
+        for name in ("bq", "bk", "bv", "bo", "bgu", "bdown"):
+            if weights.get(name) is None:
+                continue
+            ts = [None if b is None else self._dev(b) for b in weights[name]]
+            self.biases[name] = ts
+            a = (C.c_void_p * L)(*[None if t_ is None else t_.data_ptr() for t_ in ts])
+            self._keep.append(a)
+            setattr(d, name, C.cast(a, C.POINTER(C.c_void_p)))
         self._desc = d
         h = C.c_void_p()
         ctx.check(ctx.lib.smc_model_create(ctx.h, C.byref(d), max_batch, C.byref(h)))

@@ -213,6 +213,43 @@ def test_decode_full_qwen3_0_6b_shape_against_oracle(oracle, cuda, dev, n_layers
     assert cuda.device_status() == 0
 
 
+@pytest.mark.parametrize("which", ["qkv", "all"])
+@pytest.mark.parametrize("mode", [ops.Mode.ACT_F32, ops.Mode.REF_ORDER, ops.Mode.ACT_Q8])
+def test_decode_with_linear_biases(oracle, cuda, which, mode):
+    """Linear layers with a bias (InferenceLinearLayer.Forward -> LinearLayer.AddBiasInPlace): the attention
+    projections only, as Qwen2-class checkpoints have them, or every linear layer; decode steps and a prompt pass."""
+    cfg, name, batch = SMALL, "dec_small", 2
+    w = dict(_weights(oracle, cfg, name))
+    L, H, hd = cfg["n_layers"], cfg["hidden"], cfg["head_dim"]
+    q_dim, kv_dim, F = cfg["n_heads"] * hd, cfg["n_kv_heads"] * hd, cfg["ffn"]
+    sizes = {"bq": q_dim, "bk": kv_dim, "bv": kv_dim, "bo": H, "bgu": 2 * F, "bdown": H}
+    for bname, n in sizes.items():
+        if which == "qkv" and bname not in ("bq", "bk", "bv"):
+            continue
+        # one layer keeps a missing vector: entries may be null
+        w[bname] = [None if (bname == "bo" and i == 1) else synth.normal(name, f"l{i}.{bname}", (n,), 0.05) for i in range(L)]
+    ref = oracle.Decoder(cfg, w, batch)
+    dec = Decoder(cuda, cfg, w, max_batch=batch, keep_raw=(mode == ops.Mode.REF_ORDER))
+    tok = synth.token_ids(name, "bias_prompt", (batch,), cfg["vocab"])
+    q8 = mode == ops.Mode.ACT_Q8
+    for pos in range(6):
+        want = ref.step(tok, pos, act_q8=q8)
+        logits, _ = dec.step(to_dev(tok), pos, mode)
+        got = logits.cpu().numpy()
+        scale = np.abs(want).max()
+        assert np.abs(got - want).max() <= (Q8_SHALLOW_TOL if q8 else 1e-4) * scale, float(np.abs(got - want).max() / scale)
+        tok = want.argmax(axis=1).astype(np.int32)
+    # a prompt pass of sequence 0 over its own six tokens lands on the oracle's next logits
+    if not q8:
+        ref1 = oracle.Decoder(cfg, w, 1)
+        toks = synth.token_ids(name, "bias_pass", (7,), cfg["vocab"])
+        for p in range(7):
+            want1 = ref1.step(toks[p:p + 1], p)
+        got1 = dec.forward_last_logits(to_dev(toks), 0, 1, mode)[0].cpu().numpy()
+        assert np.abs(got1 - want1[0]).max() <= 1e-4 * np.abs(want1).max()
+    dec.close()
+
+
 def test_decode_batch_rows_are_independent(oracle, cuda):
     """Lock-step sequences do not interact: row b of a batch of 4 equals the same sequence decoded alone."""
     import torch
