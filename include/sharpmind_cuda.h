@@ -89,7 +89,8 @@ SMC_API const char *smc_last_error(smc_ctx *ctx);
  *                           weight prefetch overlaps its predecessor's tail, or fully serialised
  *   "gemv_slots"            ring depth per warp of the one-row matmul kernel, 2..8 (0 = built-in choice)
  *   "gemv_steps_per_stage"  steps per bulk copy of that kernel: 1, 2 or 4 (0 = built-in choice)
- *   "gemv_ctas"             CTAs in its grid (0 = built-in choice: one per SM)
+ *   "gemv_ctas"             CTAs in its grid (0 = built-in choice: the SMs times the CTAs per SM)
+ *   "gemv_warps"            warps per CTA, 24 (one CTA per SM) or 12 (two); 0 = built-in choice by row length
  *   "gemv_prefetch_first"   stages a warp requests before the activation loads are issued, 0..8 (default 1)
  * Results do not depend on any of them.  SMC_E_INVALID for an unknown name. */
 SMC_API int smc_set_option(smc_ctx *ctx, const char *name, int value);
@@ -225,6 +226,27 @@ SMC_API int smc_add_rmsnorm_dev(smc_ctx *ctx, float *d_x, const float *d_y, cons
                                 int n, float eps, void *stream);
 /* Sampler.Argmax (SharpMind.Inference/Sampler.cs:50-58) per row: first maximum wins. */
 SMC_API int smc_argmax_dev(smc_ctx *ctx, const float *d_logits, int rows, int n, int *d_out, void *stream);
+/* Sampler.Sample (SharpMind.Inference/Sampler.cs:16-46) per row of d_logits [rows, n]: temperature, guarded softmax,
+ * min-p, top-k, top-p, normalise, one categorical draw; temperature <= 0 is the greedy shortcut (Sampler.Argmax).
+ * The fields are SamplingConfig's (SamplingConfig.cs: Temperature, TopK 0 = off, TopP 1 = off, MinP 0 = off).
+ * d_uniform [rows] holds the number rng.NextSingle() produced for each row (the host keeps its own generator, so a
+ * seeded run draws the same stream it would have drawn on the CPU); d_work [rows, n] is scratch for the
+ * probabilities.  The logits are not modified.  Probabilities bit-equal to a top-k / top-p cut value are all kept,
+ * and sums are formed by a fixed tree instead of the reference's sequential loops: a draw within rounding of a
+ * boundary between two tokens may pick the neighbour. */
+typedef struct smc_sampling {
+    float temperature;
+    int top_k;
+    float top_p;
+    float min_p;
+} smc_sampling;
+SMC_API int smc_sample_dev(smc_ctx *ctx, const float *d_logits, int rows, int n, const smc_sampling *cfg,
+                           const float *d_uniform, float *d_work, int *d_tokens, void *stream);
+/* RepetitionPenalty.Apply (SharpMind.Inference/RepetitionPenalty.cs:15-27) in place on d_logits [rows, n]: every
+ * DISTINCT id of row r's window d_ids[r, 0 .. window) scales its logit once (positive: divided by the penalty,
+ * negative: multiplied); ids outside [0, n) are skipped, so -1 pads a short window. */
+SMC_API int smc_repetition_penalty_dev(smc_ctx *ctx, float *d_logits, int rows, int n, const int *d_ids, int window,
+                                       float penalty, void *stream);
 /* EmbeddingTable.Forward (SharpMind.Core/Embeddings/EmbeddingTable.cs:87-116) gathering rows of a Q8_0
  * table dequantised as ReadQ8_0_Scalar does (QuantizationKernels.Q8.cs:412-433): out[i] = row tokens[i]. */
 SMC_API int smc_embed_q8_0_dev(smc_ctx *ctx, const smc_weight *table, const int *d_tokens, int count, float *d_out,

@@ -976,3 +976,147 @@ SMO_API int smo_decode_step(const smo_model *m, const int *tokens, int batch, in
 {
     return smo_decode_step_ex(m, tokens, batch, pos, kcache, vcache, logits, 0);
 }
+
+/* ------------------------------------------------------------------------- */
+/* sampler                                                                    */
+/* ------------------------------------------------------------------------- */
+
+/* RepetitionPenalty.Apply (SharpMind.Inference/RepetitionPenalty.cs:15-27): every DISTINCT id of the window
+ * scales its logit once: positive logits are divided by the penalty, negative ones multiplied. */
+SMO_API void smo_repetition_penalty(float *logits, int n, const int *ids, int count, float penalty)
+{
+    for (int i = 0; i < count; i++) {
+        int id = ids[i], seen = 0;
+        for (int j = 0; j < i; j++)
+            if (ids[j] == id) { seen = 1; break; }
+        if (seen || id < 0 || id >= n) continue;
+        logits[id] = logits[id] >= 0.f ? logits[id] / penalty : logits[id] * penalty;
+    }
+}
+
+static void sift_down(float *vals, int *idxs, int pos, int heap)
+{
+    for (;;) {
+        int smallest = pos, l = 2 * pos + 1, r = 2 * pos + 2;
+        if (l < heap && vals[l] < vals[smallest]) smallest = l;
+        if (r < heap && vals[r] < vals[smallest]) smallest = r;
+        if (smallest == pos) break;
+        float tv = vals[pos]; vals[pos] = vals[smallest]; vals[smallest] = tv;
+        int ti = idxs[pos]; idxs[pos] = idxs[smallest]; idxs[smallest] = ti;
+        pos = smallest;
+    }
+}
+
+typedef struct { float v; int i; } smo_vi;
+static int cmp_vi(const void *a, const void *b)
+{
+    const smo_vi *x = a, *y = b;
+    if (x->v < y->v) return -1;
+    if (x->v > y->v) return 1;
+    return x->i < y->i ? -1 : (x->i > y->i ? 1 : 0); /* the reference's sort leaves the order of equal values open */
+}
+
+/* Sampler.Sample (SharpMind.Inference/Sampler.cs:16-46) with the uniform number `r` that rng.NextSingle() would
+ * have produced handed in by the caller: temperature (:62-66), guarded softmax (:70-100), min-p (:222-229),
+ * top-k by heap select (:109-161), top-p over an ascending sort walked from the top (:189-225), normalise
+ * (:233-240), categorical draw (:244-257).  temperature <= 0 is the greedy shortcut (Argmax, :50-58). */
+SMO_API int smo_sample_ex(const float *logits, int n, float temperature, int topK, float topP, float minP, float r,
+                          float *probs_out);
+SMO_API int smo_sample(const float *logits, int n, float temperature, int topK, float topP, float minP, float r)
+{
+    return smo_sample_ex(logits, n, temperature, topK, topP, minP, r, NULL);
+}
+
+/* The same; probs_out (n floats, may be null) receives the normalised probabilities the draw was made from. */
+SMO_API int smo_sample_ex(const float *logits, int n, float temperature, int topK, float topP, float minP, float r,
+                          float *probs_out)
+{
+    if (temperature <= 0.f) return smo_argmax(logits, n);
+    float *p = malloc(sizeof(float) * (size_t)n);
+    float *vals = malloc(sizeof(float) * (size_t)n);
+    int *idxs = malloc(sizeof(int) * (size_t)n);
+    int result = 0;
+    if (!p || !vals || !idxs) { result = -1; goto done; }
+    float inv = 1.f / temperature;
+    for (int i = 0; i < n; i++) p[i] = logits[i] * inv;
+    /* softmax */
+    int bad = 0;
+    for (int i = 0; i < n; i++)
+        if (isinf(p[i]) || isnan(p[i])) { bad = 1; break; }
+    if (bad) {
+        memset(p, 0, sizeof(float) * (size_t)n);
+        p[0] = 1.f;
+    } else {
+        float mx = p[0];
+        for (int i = 0; i < n; i++) if (p[i] > mx) mx = p[i];
+        float sum = 0.f;
+        for (int i = 0; i < n; i++) {
+            float e = p[i] - mx;
+            if (e > 80.f) e = 80.f; else if (e < -80.f) e = -80.f;
+            p[i] = expf(e);
+            sum += p[i];
+        }
+        float is = 1.f / sum;
+        for (int i = 0; i < n; i++) p[i] *= is;
+    }
+    if (minP > 0.f) {
+        float mx = 0.f;
+        for (int i = 0; i < n; i++) if (p[i] > mx) mx = p[i];
+        float thr = minP * mx;
+        for (int i = 0; i < n; i++) if (p[i] < thr) p[i] = 0.f;
+    }
+    if (topK > 0 && topK < n) {
+        int count = 0;
+        for (int i = 0; i < n; i++) if (p[i] > 0.f) { vals[count] = p[i]; idxs[count] = i; count++; }
+        if (count > topK) {
+            for (int i = topK / 2 - 1; i >= 0; i--) sift_down(vals, idxs, i, topK);
+            for (int i = topK; i < count; i++)
+                if (vals[i] > vals[0]) {
+                    float tv = vals[0]; vals[0] = vals[i]; vals[i] = tv;
+                    int ti = idxs[0]; idxs[0] = idxs[i]; idxs[i] = ti;
+                    sift_down(vals, idxs, 0, topK);
+                }
+            for (int i = topK; i < count; i++) p[idxs[i]] = 0.f;
+        }
+    }
+    if (topP < 1.0f && topP > 0.f) {
+        smo_vi *s = malloc(sizeof(smo_vi) * (size_t)n);
+        if (!s) { result = -1; goto done; }
+        int count = 0;
+        for (int i = 0; i < n; i++) if (p[i] > 0.f) { s[count].v = p[i]; s[count].i = i; count++; }
+        qsort(s, (size_t)count, sizeof(smo_vi), cmp_vi);
+        float cum = 0.f;
+        for (int i = count - 1; i >= 0; i--) {
+            cum += s[i].v;
+            if (cum >= topP) {
+                for (int j = i - 1; j >= 0; j--) p[s[j].i] = 0.f;
+                break;
+            }
+        }
+        free(s);
+    }
+    {
+        float sum = 0.f;
+        for (int i = 0; i < n; i++) sum += p[i];
+        if (sum > 0.f) {
+            float is = 1.f / sum;
+            for (int i = 0; i < n; i++) p[i] *= is;
+        }
+    }
+    if (probs_out) memcpy(probs_out, p, sizeof(float) * (size_t)n);
+    {
+        float cum = 0.f;
+        result = -2;
+        for (int i = 0; i < n; i++) {
+            cum += p[i];
+            if (r <= cum) { result = i; break; }
+        }
+        if (result == -2) {
+            result = 0;
+            for (int i = n - 1; i >= 0; i--) if (p[i] > 0.f) { result = i; break; }
+        }
+    }
+done:
+    free(p); free(vals); free(idxs);
+    return result;
+}

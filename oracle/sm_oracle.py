@@ -103,6 +103,12 @@ def lib() -> C.CDLL:
         L.smo_sdpa_flash.restype = None
         L.smo_sdpa_flash.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                      C.c_float, C.c_int, C.c_int, C.c_int]
+        L.smo_sample.restype = C.c_int
+        L.smo_sample.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float, C.c_float]
+        L.smo_sample_ex.restype = C.c_int
+        L.smo_sample_ex.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float, C.c_float, C.c_void_p]
+        L.smo_repetition_penalty.restype = None
+        L.smo_repetition_penalty.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float]
         L.smo_decode_step.restype = C.c_int
         L.smo_decode_step.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                       C.c_void_p]
@@ -353,6 +359,28 @@ def add(x, y) -> np.ndarray:
 def argmax(logits) -> int:
     logits = _f32(logits)
     return int(lib().smo_argmax(_p(logits), logits.size))
+
+
+def sample(logits, temperature: float, top_k: int, top_p: float, min_p: float, r: float) -> int:
+    """Sampler.Sample on one row of logits with the uniform draw `r` supplied by the caller."""
+    x = _f32(logits)
+    return int(lib().smo_sample(_p(x), x.size, temperature, top_k, top_p, min_p, r))
+
+
+def sample_probs(logits, temperature: float, top_k: int, top_p: float, min_p: float, r: float):
+    """(token, probabilities the draw was made from) of Sampler.Sample; temperature must be > 0."""
+    x = _f32(logits)
+    probs = np.zeros(x.size, np.float32)
+    tok = int(lib().smo_sample_ex(_p(x), x.size, temperature, top_k, top_p, min_p, r, _p(probs)))
+    return tok, probs
+
+
+def repetition_penalty(logits, ids, penalty: float) -> np.ndarray:
+    """RepetitionPenalty.Apply on a copy of one row of logits."""
+    x = _f32(logits).copy()
+    i = np.ascontiguousarray(ids, dtype=np.int32)
+    lib().smo_repetition_penalty(_p(x), x.size, _p(i), i.size, penalty)
+    return x
 
 
 def sdpa_flash(q, k, v, scale: float, causal: bool = True) -> np.ndarray:

@@ -60,6 +60,8 @@ SIGNATURES = {
     "smc_add_bias_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "smc_linear_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "smc_argmax_dev": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "smc_sample_dev": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "smc_repetition_penalty_dev": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_void_p]),
     "smc_embed_q8_0_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "smc_sdpa_decode_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_float, c_void_p]),

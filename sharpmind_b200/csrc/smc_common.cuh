@@ -85,6 +85,7 @@ struct smc_ctx {
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
     bool use_pdl = true;               // programmatic dependent launch (smc_set_option "pdl")
     int tma_slots = 0, tma_ss = 0, tma_ctas = 0;  // one-row GEMV ring geometry and grid, 0 = built-in choice (smc_set_option)
+    int tma_warps = 0;                            // warps per CTA of the one-row GEMV: 24 (one CTA per SM, default) or 12 (two)
     int tma_pre = 1;                              // stages requested before the activation loads are issued
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
     int argmax_rows = 0, argmax_chunks = 0;

@@ -461,6 +461,33 @@ class DeviceOps:
         self.ctx.check(self.lib.smc_argmax_dev(self.ctx.h, self._chk(logits), rows, n, out.data_ptr(), self._stream()))
         return out
 
+    def sample(self, logits, temperature: float, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, uniform=None,
+               work=None):
+        """Sampler.Sample per row of `logits` [rows, n]; `uniform` [rows] holds the host generator's NextSingle() per row."""
+        t = self.torch
+
+        class _Cfg(C.Structure):
+            _fields_ = [("temperature", C.c_float), ("top_k", C.c_int), ("top_p", C.c_float), ("min_p", C.c_float)]
+
+        rows, n = logits.shape
+        cfg = _Cfg(temperature, top_k, top_p, min_p)
+        out = t.empty(rows, dtype=t.int32, device=logits.device)
+        if temperature > 0 and work is None:
+            work = t.empty_like(logits)
+        self.ctx.check(self.lib.smc_sample_dev(self.ctx.h, self._chk(logits, t.float32), rows, n, C.byref(cfg),
+                                               None if uniform is None else self._chk(uniform, t.float32),
+                                               None if work is None else self._chk(work, t.float32), out.data_ptr(),
+                                               self._stream()))
+        return out
+
+    def repetition_penalty_(self, logits, ids, penalty: float):
+        """RepetitionPenalty.Apply in place: `ids` [rows, window] int32 (pad with -1)."""
+        t = self.torch
+        rows, n = logits.shape
+        self.ctx.check(self.lib.smc_repetition_penalty_dev(self.ctx.h, self._chk(logits, t.float32), rows, n,
+                                                           self._chk(ids, t.int32), ids.shape[1], penalty, self._stream()))
+        return logits
+
     def embed(self, table: Weight, tokens, out=None):
         t = self.torch
         if out is None:

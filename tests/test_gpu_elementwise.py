@@ -288,3 +288,64 @@ def test_fused_one_row_matmuls(oracle, cuda, dev, dtype, n, k):
                                            got.data_ptr(), st))
     assert (got - want).abs().max().item() <= 2e-2 * want.abs().max().item()
     cuda.release(w)
+
+
+# ------------------------------------------------------------------------------------------ sampler
+@pytest.mark.parametrize("n", [1000, 151936])
+@pytest.mark.parametrize("cfg", [
+    dict(temperature=1.0, top_k=0, top_p=1.0, min_p=0.0),
+    dict(temperature=0.7, top_k=40, top_p=1.0, min_p=0.0),
+    dict(temperature=0.8, top_k=0, top_p=0.9, min_p=0.0),
+    dict(temperature=1.3, top_k=50, top_p=0.95, min_p=0.05),
+    dict(temperature=0.0, top_k=40, top_p=0.9, min_p=0.0),     # greedy shortcut
+    dict(temperature=1.0, top_k=1, top_p=1.0, min_p=0.0),      # top-1 = argmax whatever the draw
+])
+def test_sampler_matches_reference_given_the_same_uniform(oracle, cuda, dev, n, cfg):
+    """Sampler.Sample: with the host's uniform number r handed in, the device picks the token whose interval of the
+    cumulative distribution contains r.  The reference finds it with a sequential fp32 running sum, whose value after
+    i terms is off the exact sum by up to about i * 2^-24 relative (1e-5 at 152k tokens, several tokens wide where each
+    holds 1e-5 of the mass); the device's fixed summation tree rounds differently.  So the contract is stated on the
+    reference's own probabilities, summed exactly: cum(i - 1) - tol <= r <= cum(i) + tol with tol = 3e-5 (the fp32
+    uncertainty of either side), the picked token must have kept its mass, and the reference's own pick satisfies the
+    same inequality.  For short rows, and whenever top-k leaves few candidates, this means the same token."""
+    rows = 24
+    logits = synth.normal("sampler", f"l{n}", (rows, n), 2.0)
+    r = synth.uniform("sampler", f"r{n}", (rows,), 0.0, 1.0).astype(np.float32)
+    got = dev.sample(to_dev(logits), uniform=to_dev(r), **cfg).cpu().numpy()
+    args = (cfg["temperature"], cfg["top_k"], cfg["top_p"], cfg["min_p"])
+    same = 0
+    for i in range(rows):
+        if cfg["temperature"] <= 0:
+            assert int(got[i]) == oracle.sample(logits[i], *args, float(r[i]))
+            same += 1
+            continue
+        want, probs = oracle.sample_probs(logits[i], *args, float(r[i]))
+        cum = np.cumsum(probs.astype(np.float64))
+        tol = 3e-5
+        for tok in (int(got[i]), want):
+            assert probs[tok] > 0
+            lo = cum[tok - 1] if tok > 0 else 0.0
+            assert lo - tol <= float(r[i]) <= cum[tok] + tol, (i, tok, lo, float(r[i]), cum[tok])
+        same += int(got[i]) == want
+    if n <= 1000 or 0 < cfg["top_k"] <= 50:
+        assert same == rows, f"{same}/{rows} rows picked the reference's token"
+
+
+def test_sampler_guards_and_repetition_penalty(oracle, cuda, dev):
+    n = 4096
+    logits = synth.normal("sampler", "guard", (3, n), 2.0)
+    logits[1, 77] = np.inf          # the softmax guard: a point mass on token 0
+    logits[2, 5] = np.nan
+    r = np.array([0.3, 0.9, 0.1], np.float32)
+    got = dev.sample(to_dev(logits), 1.0, uniform=to_dev(r)).cpu().numpy()
+    assert got[1] == 0 and got[2] == 0
+    assert got[0] == oracle.sample(logits[0], 1.0, 0, 1.0, 0.0, 0.3)
+    # repetition penalty: distinct ids scale once, out-of-range ids and padding are skipped
+    ids = np.array([[5, 9, 5, 4095, -1, 7000, 9], [1, 1, 1, 2, -1, -1, -1], [0, 3, 3, 3, 3, 3, 3]], np.int32)
+    base = synth.normal("sampler", "rep", (3, n), 2.0)
+    x = to_dev(base.copy())
+    dev.repetition_penalty_(x, to_dev(ids), 1.3)
+    out = x.cpu().numpy()
+    for i in range(3):
+        want = oracle.repetition_penalty(base[i], ids[i], 1.3)
+        assert np.array_equal(out[i].view(np.uint32), want.view(np.uint32))
