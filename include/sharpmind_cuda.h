@@ -262,6 +262,39 @@ SMC_API int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k
 SMC_API int smc_kv_append_dev(smc_ctx *ctx, const float *d_k, const float *d_v, float *d_kcache, float *d_vcache,
                               int batch, int kvHeads, int headDim, int pos, int maxSeq, void *stream);
 
+/* ---- KV cache objects -----------------------------------------------------------------------
+ * IKVCache (SharpMind.Model/IKVCache.cs:7-18) on the device: KVCache (fp32, KVCache.cs) and QuantizedKVCache with Q8_0
+ * rows (QuantizedKVCache.cs).  One object holds the keys and values of one attention layer for `batch` lock-step
+ * sequences that share one position (CurrentPosition), as the reference's caches do.  Host-side state (the length)
+ * changes when the call returns; device work is queued on `stream`, so calls on one object go to one stream. */
+typedef struct smc_kv smc_kv;
+enum { SMC_KV_F32 = 0, SMC_KV_Q8_0 = 8 };
+SMC_API int smc_kv_create(smc_ctx *ctx, int batch, int kvHeads, int maxSeq, int headDim, int kind, smc_kv **out);
+SMC_API int smc_kv_destroy(smc_ctx *ctx, smc_kv *kv);
+SMC_API int smc_kv_length(const smc_kv *kv);   /* IKVCache.Length */
+SMC_API int smc_kv_max_seq(const smc_kv *kv);  /* IKVCache.MaxSeqLen */
+SMC_API int smc_kv_reset(smc_ctx *ctx, smc_kv *kv);                 /* Reset(): length = 0 */
+SMC_API int smc_kv_truncate(smc_ctx *ctx, smc_kv *kv, int length);  /* Truncate(length): length = min(length, current) */
+/* TrimToLast(keep) (KVCache.cs:44-82, QuantizedKVCache.cs:128-160): the last `keep` positions move to the front. */
+SMC_API int smc_kv_trim_to_last(smc_ctx *ctx, smc_kv *kv, int keep, void *stream);
+/* Update(k, v) (KVCache.cs:84-150, QuantizedKVCache.cs:84-126): d_k, d_v are [batch, seqLen, kvHeads, headDim] fp32 and
+ * are appended at the current length (quantised row by row for a Q8_0 cache); SMC_E_RANGE on overflow. */
+SMC_API int smc_kv_update_dev(smc_ctx *ctx, smc_kv *kv, const float *d_k, const float *d_v, int batch, int seqLen, void *stream);
+/* Snapshot / Restore (KVCache.cs:152-174, QuantizedKVCache.cs:162-189), synchronous, host buffers.  What is saved: the
+ * positions [0, length) of EVERY (sequence, head), densely packed [batch][kvHead][length][row], a row being headDim
+ * floats or headDim/32 Q8_0 blocks of 34 bytes in the reference's block layout.  (The reference copies the first
+ * batch*heads*length rows of its flat array instead, which are the active rows only for a single head; its restore
+ * onto the same object still works because nothing else was touched.) */
+SMC_API int64_t smc_kv_snapshot_bytes(const smc_kv *kv);  /* bytes per tensor (keys and values have the same size) */
+SMC_API int smc_kv_snapshot(smc_ctx *ctx, const smc_kv *kv, void *host_k, void *host_v, int64_t bytes_each, int *position);
+SMC_API int smc_kv_restore(smc_ctx *ctx, smc_kv *kv, const void *host_k, const void *host_v, int64_t bytes_each, int position);
+/* Causal attention of the LAST seqLen positions against the whole cache (AttentionLayer.Forward's per-(batch, head)
+ * loop, AttentionLayer.cs:326-413, with ScaledDotProductFlash* for an fp32 cache, AttentionKernels.cs:315-475, and
+ * ScaledDotProductFlashQ8_0* for a Q8_0 one, :489-813): d_q and d_out are [batch, seqLen, heads, headDim]; the keys and
+ * values of those positions must have been appended already. */
+SMC_API int smc_sdpa_kv_dev(smc_ctx *ctx, const smc_kv *kv, const float *d_q, float *d_out, int batch, int heads, int seqLen,
+                            float scale, void *stream);
+
 /* ---- one decode step of a Llama/Qwen-shaped decoder -------------------------------------------
  * What Transformer.ForwardLastLogits computes for [batch, 1] token ids (SharpMind.Model/Transformer.cs:417-463
  * -> DecoderArch.Forward Arch/DecoderArch.cs:115-134 -> UnhookedTransformerBlock.Forward
@@ -282,6 +315,9 @@ typedef struct smc_model_desc {
      * member is null (no such biases anywhere) or an array of n_layers device pointers whose entries may be null.
      * bq [heads*headDim], bk / bv [kvHeads*headDim], bo [hidden], bgu [2*ffn], bdown [hidden]. */
     const float *const *bq, *const *bk, *const *bv, *const *bo, *const *bgu, *const *bdown;
+    /* Format of the KV cache: SMC_KV_F32 (0, KVCache) or SMC_KV_Q8_0 (8, QuantizedKVCache with Q8_0 rows: a quarter of the
+     * bytes a decode step sweeps).  Needs the joined Q/K/V path and headDim 64 or 128. */
+    int kv_dtype;
 } smc_model_desc;
 /* Allocates the fp32 KV cache [layer, max_batch, kvHeads, max_seq, headDim] (KVCache.cs:13-14), RoPE tables
  * and intermediates.  The description's arrays are copied; the weights stay owned by the context. */
@@ -327,6 +363,30 @@ SMC_API int smc_qmatmul_addnorm_dev(smc_ctx *ctx, const float *d_x, const float 
 /* A new weight whose rows are the rows of parts[0], parts[1], ... in order (same dtype and K, all registered
  * with SMC_W_REPACK): how the decoder turns Wq / Wk / Wv into one matmul.  The parts stay valid. */
 SMC_API int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts, int count, smc_weight **out);
+
+/* ---- GGUF files to device weights -------------------------------------------------------------
+ * GgufLoader (SharpMind.Model/Format/GgufLoader.cs): LoadMeta's header parse (:124-176) and LoadSingleTensor's copy of
+ * a tensor's raw bytes (:512-672), with the device as the destination: the file is memory-mapped and a tensor goes
+ * from the mapping to the GPU in one registration.  dtype uses GGUF's numbering, which is QuantDType's (F32 = 0,
+ * F16 = 1, Q8_0 = 8, Q4_K = 12, Q6_K = 14); dims[0] is the innermost dimension (inFeatures). */
+typedef struct smc_gguf smc_gguf;
+SMC_API int smc_gguf_open(smc_ctx *ctx, const char *path, smc_gguf **out);
+SMC_API int smc_gguf_close(smc_ctx *ctx, smc_gguf *g);
+SMC_API int smc_gguf_tensor_count(const smc_gguf *g);
+/* Index of the tensor called `name`, or -1. */
+SMC_API int smc_gguf_find(const smc_gguf *g, const char *name);
+/* bytes = GetRawTensorByteCount(shape, dtype) (QuantizationOps.cs:15-72), -1 for a format this library does not size. */
+SMC_API int smc_gguf_tensor_info(const smc_gguf *g, int index, const char **name, int *dtype, int *n_dims, int64_t *dims4,
+                                 int64_t *bytes);
+/* Scalar metadata (ModelMetaData.GetLong / GetFloat / GetString); SMC_E_NOT_REGISTERED / null when the key is absent. */
+SMC_API int smc_gguf_meta_int(const smc_gguf *g, const char *key, int64_t *value);
+SMC_API int smc_gguf_meta_float(const smc_gguf *g, const char *key, double *value);
+SMC_API const char *smc_gguf_meta_string(const smc_gguf *g, const char *key);
+/* Registers a Q8_0 / Q4_K / Q6_K matrix (N = dims[1], K = dims[0]) straight from the mapping; flags as for
+ * smc_weight_register.  SMC_E_UNSUPPORTED for other formats. */
+SMC_API int smc_gguf_register(smc_ctx *ctx, const smc_gguf *g, int index, int flags, smc_weight **out);
+/* An F32 or F16 tensor (norm vectors, biases) as fp32 into device memory; `count` must be its element count. */
+SMC_API int smc_gguf_read_f32(smc_ctx *ctx, const smc_gguf *g, int index, float *d_dst, int64_t count);
 
 /* ---- row-split matmul across GPUs -----------------------------------------------------------
  * No reference counterpart: SharpMind runs one device per process (Accelerator selection in

@@ -861,6 +861,10 @@ typedef struct {
     int down_dtype, head_dtype;
     /* bias vectors of the linear layers (LinearLayer._bias): null, or n_layers pointers whose entries may be null */
     const float **bq, **bk, **bv, **bo, **bgu, **bdown;
+    /* != 0: the cache is a QuantizedKVCache with Q8_0 rows (SharpMind.Model/QuantizedKVCache.cs:84-126): every appended K
+     * and V head row is quantised by QuantizeRowQ8_0; the cache here keeps the values those blocks decode to (val * d),
+     * which is what ScaledDotProductFlashQ8_0* multiplies by. */
+    int kv_q8;
 } smo_model;
 
 /* LinearLayer.AddBiasInPlace (SharpMind.Model/Layers/Linearlayer.cs:154-163): row[j] += bias[j] for every row. */
@@ -940,8 +944,17 @@ SMO_API int smo_decode_step_ex(const smo_model *m, const int *tokens, int batch,
         for (int b = 0; b < batch; b++)
             for (int h = 0; h < nkv; h++) {
                 size_t dst = (((size_t)b * nkv + h) * m->max_seq + pos) * hd;
-                memcpy(kc + dst, k + (size_t)b * kvDim + (size_t)h * hd, sizeof(float) * hd);
-                memcpy(vc + dst, v + (size_t)b * kvDim + (size_t)h * hd, sizeof(float) * hd);
+                float *krow = k + (size_t)b * kvDim + (size_t)h * hd, *vrow = v + (size_t)b * kvDim + (size_t)h * hd;
+                if (m->kv_q8) {
+                    uint8_t blocks[8 * 34];
+                    if (hd > 256 || hd % 32) { rc = -6; goto done; }
+                    smo_quantize_row_q8_0(krow, blocks, hd);
+                    smo_dequant_row_q8_0(blocks, krow, hd);
+                    smo_quantize_row_q8_0(vrow, blocks, hd);
+                    smo_dequant_row_q8_0(blocks, vrow, hd);
+                }
+                memcpy(kc + dst, krow, sizeof(float) * hd);
+                memcpy(vc + dst, vrow, sizeof(float) * hd);
             }
         int kvLen = pos + 1;
         int group = nh / nkv;
@@ -1119,4 +1132,77 @@ SMO_API int smo_sample_ex(const float *logits, int n, float temperature, int top
 done:
     free(p); free(vals); free(idxs);
     return result;
+}
+
+/* SharpMind.Model/Layers/Attention/AttentionKernels.cs:724-813 (ScaledDotProductFlashQ8_0Scalar), alibiSlope = 0:
+ * keys and values are rows of Q8_0 blocks (fp16 d + 32 int8, headDim/32 blocks per row, colStride bytes apart);
+ * the key dot is summed in fp64 over (q * (val * d)) products formed in fp32, the rest is the fp32 flash recurrence. */
+SMO_API void smo_sdpa_flash_q8(const float *q, const uint8_t *kQuant, const uint8_t *vQuant, float *out, int seqLen,
+                               int kvLen, int headDim, float scale, int causal, int qStride, int oStride)
+{
+    float tile[64];
+    int nBlocks = (headDim + 31) / 32, colStride = nBlocks * 34;
+    int queryBase = causal ? kvLen - seqLen : 0;
+    for (int i = 0; i < seqLen; i++) {
+        const float *qi = q + (int64_t)i * qStride;
+        int absQ = queryBase + i;
+        int eff = causal ? (absQ + 1 < kvLen ? absQ + 1 : kvLen) : kvLen;
+        float mMax = -INFINITY, lSum = 0.f;
+        float *o = out + (int64_t)i * oStride;
+        for (int d = 0; d < headDim; d++) o[d] = 0.f;
+        for (int start = 0; start < eff; start += 64) {
+            int end = start + 64 < eff ? start + 64 : eff;
+            int len = end - start;
+            float tmax = -INFINITY;
+            for (int j = start; j < end; j++) {
+                const uint8_t *kj = kQuant + (int64_t)j * colStride;
+                double dot = 0;
+                for (int b = 0; b < nBlocks; b++) {
+                    const uint8_t *bp = kj + b * 34;
+                    float d = smo_half_to_float((uint16_t)(bp[0] | (bp[1] << 8)));
+                    const int8_t *vals = (const int8_t *)(bp + 2);
+                    int blockEnd = headDim - b * 32 < 32 ? headDim - b * 32 : 32;
+                    for (int k = 0; k < blockEnd; k++) {
+                        float w = (float)vals[k] * d;
+                        float p = qi[b * 32 + k] * w;
+                        dot += p;
+                    }
+                }
+                float score = (float)dot * scale;
+                tile[j - start] = score;
+                if (score > tmax) tmax = score;
+            }
+            float newMax = mMax > tmax ? mMax : tmax;
+            float scaleOld = expf(mMax - newMax);
+            float scaleNew = 0.f;
+            for (int t = 0; t < len; t++) {
+                tile[t] = expf(tile[t] - newMax);
+                scaleNew += tile[t];
+            }
+            float so = scaleOld * lSum;
+            float newL = so + scaleNew;
+            for (int d = 0; d < headDim; d++) o[d] *= scaleOld;
+            for (int t = 0; t < len; t++) {
+                const uint8_t *vj = vQuant + (int64_t)(start + t) * colStride;
+                float sm = tile[t];
+                for (int b = 0; b < nBlocks; b++) {
+                    const uint8_t *bp = vj + b * 34;
+                    float d = smo_half_to_float((uint16_t)(bp[0] | (bp[1] << 8)));
+                    const int8_t *vals = (const int8_t *)(bp + 2);
+                    int blockEnd = headDim - b * 32 < 32 ? headDim - b * 32 : 32;
+                    for (int k = 0; k < blockEnd; k++) {
+                        float w = (float)vals[k] * d;
+                        float p = sm * w;
+                        o[b * 32 + k] += p;
+                    }
+                }
+            }
+            mMax = newMax;
+            lSum = newL;
+        }
+        if (lSum > 0.f)
+            for (int d = 0; d < headDim; d++) o[d] /= lSum;
+        else
+            for (int d = 0; d < headDim; d++) o[d] = 0.f;
+    }
 }

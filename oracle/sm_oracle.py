@@ -103,6 +103,9 @@ def lib() -> C.CDLL:
         L.smo_sdpa_flash.restype = None
         L.smo_sdpa_flash.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                      C.c_float, C.c_int, C.c_int, C.c_int]
+        L.smo_sdpa_flash_q8.restype = None
+        L.smo_sdpa_flash_q8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                        C.c_float, C.c_int, C.c_int, C.c_int]
         L.smo_sample.restype = C.c_int
         L.smo_sample.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float, C.c_float]
         L.smo_sample_ex.restype = C.c_int
@@ -361,6 +364,17 @@ def argmax(logits) -> int:
     return int(lib().smo_argmax(_p(logits), logits.size))
 
 
+def sdpa_flash_q8(q, k_rows, v_rows, scale: float, causal: bool = True) -> np.ndarray:
+    """ScaledDotProductFlashQ8_0Scalar for one head: q [seqLen, headDim] fp32, k_rows / v_rows [kvLen, headDim/32 * 34]
+    uint8 (Q8_0 blocks as QuantizedKVCache stores them)."""
+    q = _f32(q)
+    seq, hd = q.shape
+    k, v = _u8(k_rows), _u8(v_rows)
+    out = np.zeros_like(q)
+    lib().smo_sdpa_flash_q8(_p(q), _p(k), _p(v), _p(out), seq, k.shape[0], hd, scale, int(causal), hd, hd)
+    return out
+
+
 def sample(logits, temperature: float, top_k: int, top_p: float, min_p: float, r: float) -> int:
     """Sampler.Sample on one row of logits with the uniform draw `r` supplied by the caller."""
     x = _f32(logits)
@@ -409,6 +423,7 @@ class _Model(C.Structure):
         ("down_dtype", C.c_int), ("head_dtype", C.c_int),
         ("bq", C.POINTER(C.c_void_p)), ("bk", C.POINTER(C.c_void_p)), ("bv", C.POINTER(C.c_void_p)),
         ("bo", C.POINTER(C.c_void_p)), ("bgu", C.POINTER(C.c_void_p)), ("bdown", C.POINTER(C.c_void_p)),
+        ("kv_q8", C.c_int),
     ]
 
 
@@ -453,6 +468,7 @@ class Decoder:
             a = (C.c_void_p * L)(*[None if b is None else b.ctypes.data for b in weights[name]])
             self._keep.append(a)
             setattr(m, name, C.cast(a, C.POINTER(C.c_void_p)))
+        m.kv_q8 = 1 if cfg.get("kv_dtype", 0) == 8 else 0  # QuantizedKVCache with Q8_0 rows
         m.final_norm = weights["final_norm"].ctypes.data
         m.lm_head = weights["embedding"].ctypes.data
         m.embedding = self.embedding.ctypes.data

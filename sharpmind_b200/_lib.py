@@ -65,6 +65,18 @@ SIGNATURES = {
     "smc_embed_q8_0_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "smc_sdpa_decode_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_float, c_void_p]),
+    "smc_kv_create": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, _pp]),
+    "smc_kv_destroy": (c_int, [c_void_p, c_void_p]),
+    "smc_kv_length": (c_int, [c_void_p]),
+    "smc_kv_max_seq": (c_int, [c_void_p]),
+    "smc_kv_reset": (c_int, [c_void_p, c_void_p]),
+    "smc_kv_truncate": (c_int, [c_void_p, c_void_p, c_int]),
+    "smc_kv_trim_to_last": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
+    "smc_kv_update_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "smc_kv_snapshot_bytes": (c_int64, [c_void_p]),
+    "smc_kv_snapshot": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, C.POINTER(c_int)]),
+    "smc_kv_restore": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int]),
+    "smc_sdpa_kv_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
     "smc_model_create": (c_int, [c_void_p, c_void_p, c_int, _pp]),
     "smc_model_destroy": (c_int, [c_void_p, c_void_p]),
     "smc_model_kv": (c_int, [c_void_p, c_void_p, _pp, _pp]),
@@ -74,6 +86,17 @@ SIGNATURES = {
     "smc_qmatmul_swiglu_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "smc_qmatmul_addnorm_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "smc_weight_concat_rows": (c_int, [c_void_p, c_void_p, c_int, _pp]),
+    "smc_gguf_open": (c_int, [c_void_p, C.c_char_p, _pp]),
+    "smc_gguf_close": (c_int, [c_void_p, c_void_p]),
+    "smc_gguf_tensor_count": (c_int, [c_void_p]),
+    "smc_gguf_find": (c_int, [c_void_p, C.c_char_p]),
+    "smc_gguf_tensor_info": (c_int, [c_void_p, c_int, C.POINTER(C.c_char_p), C.POINTER(c_int), C.POINTER(c_int),
+                                     C.POINTER(c_int64), C.POINTER(c_int64)]),
+    "smc_gguf_meta_int": (c_int, [c_void_p, C.c_char_p, C.POINTER(c_int64)]),
+    "smc_gguf_meta_float": (c_int, [c_void_p, C.c_char_p, C.POINTER(C.c_double)]),
+    "smc_gguf_meta_string": (C.c_char_p, [c_void_p, C.c_char_p]),
+    "smc_gguf_register": (c_int, [c_void_p, c_void_p, c_int, c_int, _pp]),
+    "smc_gguf_read_f32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64]),
     "smc_gather_create": (c_int, [c_void_p, c_int, c_int, c_size_t, _pp]),
     "smc_gather_export": (c_int, [c_void_p, c_void_p, c_void_p]),
     "smc_gather_connect": (c_int, [c_void_p, c_void_p, c_void_p]),

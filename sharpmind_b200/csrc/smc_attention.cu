@@ -107,11 +107,16 @@ __device__ __forceinline__ void merge_heads(const float *rec0, float *out0, int 
 }
 
 // partial results per (batch, head): see head_record_floats
-template <int DPL, int G>  // DPL = dims per lane = headDim / 8, G = query heads per KV head
+// Q8: the cache holds Q8_0 rows (QuantizedKVCache, SharpMind.Model/QuantizedKVCache.cs) as two planes per tensor: int8
+// quants [.., maxSeq, HD] in kc / vc and fp16 block scales [.., maxSeq, HD/32] in kd / vd.  A lane's dims lie inside one
+// 32-element block; bytes become floats through a PRMT + FADD pair, and the block scale multiplies the lane's partial
+// dot (keys) or the softmax weight (values) once instead of every element: what ScaledDotProductFlashQ8_0*
+// (AttentionKernels.cs:489-813) computes, at a quarter of the fp32 cache's bytes.
+template <int DPL, int G, bool Q8>  // DPL = dims per lane = headDim / 8, G = query heads per KV head
 __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
-    const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc, float *part,
-    int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits, float *__restrict__ out, unsigned *tickets,
-    int hshare)
+    const float *__restrict__ q, const void *__restrict__ kc_, const void *__restrict__ vc_, const __half *__restrict__ kd,
+    const __half *__restrict__ vd, float *part, int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits,
+    float *__restrict__ out, unsigned *tickets, int hshare)
 {
     // kvHeads counts virtual KV heads: `hshare` consecutive ones read the same cached head, each for its own G
     // query heads (a group of 8 query heads runs as 4 x 2, so that the per-thread state of G heads stays in registers)
@@ -126,8 +131,13 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
     const int chunk = (kvLen + splits - 1) / splits;
     const int k0 = split * chunk, k1 = min(kvLen, k0 + chunk);
 
-    const float *kbase = kc + ((size_t)b * (kvHeads / hshare) + kvh / hshare) * (size_t)maxSeq * HD;
-    const float *vbase = vc + ((size_t)b * (kvHeads / hshare) + kvh / hshare) * (size_t)maxSeq * HD;
+    const size_t cached_head = (size_t)b * (kvHeads / hshare) + kvh / hshare;
+    const float *kbase = static_cast<const float *>(kc_) + cached_head * (size_t)maxSeq * HD;
+    const float *vbase = static_cast<const float *>(vc_) + cached_head * (size_t)maxSeq * HD;
+    const int8_t *kq = static_cast<const int8_t *>(kc_) + cached_head * (size_t)maxSeq * HD + sub * DPL;
+    const int8_t *vq = static_cast<const int8_t *>(vc_) + cached_head * (size_t)maxSeq * HD + sub * DPL;
+    const __half *kdb = Q8 ? kd + cached_head * (size_t)maxSeq * (HD / 32) + (sub * DPL) / 32 : nullptr;
+    const __half *vdb = Q8 ? vd + cached_head * (size_t)maxSeq * (HD / 32) + (sub * DPL) / 32 : nullptr;
 
     float qr[G][DPL];
 #pragma unroll
@@ -155,18 +165,39 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
         const bool live = j < k1;
         const int jj = live ? j : k0;
         float kr[DPL], vr[DPL];
+        float dk = 1.f, dv = 1.f;  // block scales of the lane's dims (Q8)
+        if (Q8) {
+            uint32_t kw[DPL / 4], vw[DPL / 4];
+            if (DPL == 16) {
+                const uint4 a = smc_ldg_stream16(kq + (size_t)jj * HD), c = smc_ldg_stream16(vq + (size_t)jj * HD);
+                kw[0] = a.x, kw[1] = a.y, kw[DPL / 4 - 2] = a.z, kw[DPL / 4 - 1] = a.w;
+                vw[0] = c.x, vw[1] = c.y, vw[DPL / 4 - 2] = c.z, vw[DPL / 4 - 1] = c.w;
+            } else {
+                const uint2 a = smc_ldg_stream8(kq + (size_t)jj * HD), c = smc_ldg_stream8(vq + (size_t)jj * HD);
+                kw[0] = a.x, kw[1] = a.y, vw[0] = c.x, vw[1] = c.y;
+            }
+            dk = __half2float(__ldg(kdb + (size_t)jj * (HD / 32)));
+            dv = __half2float(__ldg(vdb + (size_t)jj * (HD / 32)));
 #pragma unroll
-        for (int d = 0; d < DPL; d += 4) {
-            float4 t = smc_ldg_stream16f(kbase + (size_t)jj * HD + sub * DPL + d);
-            kr[d] = t.x, kr[d + 1] = t.y, kr[d + 2] = t.z, kr[d + 3] = t.w;
-            float4 u = smc_ldg_stream16f(vbase + (size_t)jj * HD + sub * DPL + d);
-            vr[d] = u.x, vr[d + 1] = u.y, vr[d + 2] = u.z, vr[d + 3] = u.w;
+            for (int d = 0; d < DPL; ++d) {  // signed byte -> float: flip to unsigned, magic-number convert, take 128 off
+                kr[d] = __uint_as_float(__byte_perm(kw[d >> 2] ^ 0x80808080u, 0x4B000000u, 0x7540u | (d & 3))) - 8388736.0f;
+                vr[d] = __uint_as_float(__byte_perm(vw[d >> 2] ^ 0x80808080u, 0x4B000000u, 0x7540u | (d & 3))) - 8388736.0f;
+            }
+        } else {
+#pragma unroll
+            for (int d = 0; d < DPL; d += 4) {
+                float4 t = smc_ldg_stream16f(kbase + (size_t)jj * HD + sub * DPL + d);
+                kr[d] = t.x, kr[d + 1] = t.y, kr[d + 2] = t.z, kr[d + 3] = t.w;
+                float4 u = smc_ldg_stream16f(vbase + (size_t)jj * HD + sub * DPL + d);
+                vr[d] = u.x, vr[d + 1] = u.y, vr[d + 2] = u.z, vr[d + 3] = u.w;
+            }
         }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             float dot = 0.f;
 #pragma unroll
             for (int d = 0; d < DPL; ++d) dot = fmaf(qr[g][d], kr[d], dot);
+            if (Q8) dot *= dk;
             dot = smc_group_sum<LPK>(dot);
             if (live) {
                 float s = dot * scale;
@@ -174,8 +205,9 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sdpa_decode_split_kernel(
                 float alpha = expf(m[g] - mn);  // exp(-inf) = 0 on the first key
                 float p = expf(s - mn);
                 l[g] = fmaf(l[g], alpha, p);
+                const float pv = Q8 ? p * dv : p;
 #pragma unroll
-                for (int d = 0; d < DPL; ++d) o[g][d] = fmaf(p, vr[d], o[g][d] * alpha);
+                for (int d = 0; d < DPL; ++d) o[g][d] = fmaf(pv, vr[d], o[g][d] * alpha);
                 m[g] = mn;
             }
         }
@@ -292,17 +324,17 @@ __global__ void kv_append_kernel(const float *__restrict__ k, const float *__res
     vc[dst] = v[t];
 }
 
-template <int DPL>
-int launch_split_g(smc_ctx *ctx, int G, dim3 grid, size_t smem, cudaStream_t s, const float *q, const float *k,
-                   const float *v, float *part, int heads, int kvHeads, int kvLen, int maxSeq, float scale, int splits, float *out,
-                   unsigned *tickets, int hshare)
+template <int DPL, bool Q8>
+int launch_split_g(smc_ctx *ctx, int G, dim3 grid, size_t smem, cudaStream_t s, const float *q, const void *k,
+                   const void *v, const __half *kd, const __half *vd, float *part, int heads, int kvHeads, int kvLen, int maxSeq,
+                   float scale, int splits, float *out, unsigned *tickets, int hshare)
 {
 #define SMC_SPLIT_CASE(GV)                                                                                         \
     case GV:                                                                                                       \
         if (smem > 48 * 1024)                                                                                      \
-            cudaFuncSetAttribute(sdpa_decode_split_kernel<DPL, GV>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+            cudaFuncSetAttribute(sdpa_decode_split_kernel<DPL, GV, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                  (int)smem);                                                                       \
-        smc_launch_dep(ctx->use_pdl, sdpa_decode_split_kernel<DPL, GV>, grid, dim3(SPLIT_THREADS), smem, s, q, k, v, part, heads, \
+        smc_launch_dep(ctx->use_pdl, sdpa_decode_split_kernel<DPL, GV, Q8>, grid, dim3(SPLIT_THREADS), smem, s, q, k, v, kd, vd, part, heads, \
                        kvHeads, kvLen, maxSeq, scale, splits, out, tickets, hshare);        \
         break;
     switch (G) {
@@ -505,12 +537,25 @@ extern "C" {
 int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const float *d_v, float *d_out, int batch,
                         int heads, int kvHeads, int headDim, int kvLen, int maxSeq, float scale, void *stream)
 {
+    return smc_sdpa_decode_any(ctx, d_q, d_k, d_v, nullptr, nullptr, d_out, batch, heads, kvHeads, headDim, kvLen, maxSeq, scale,
+                               static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+// fp32 cache (d_kd == null: d_k / d_v are fp32 [batch, kvHeads, maxSeq, headDim]) or Q8_0 cache (d_k / d_v are the int8
+// planes of that shape, d_kd / d_vd the fp16 block scales [batch, kvHeads, maxSeq, headDim / 32]).
+int smc_sdpa_decode_any(smc_ctx *ctx, const float *d_q, const void *d_k, const void *d_v, const __half *d_kd, const __half *d_vd,
+                        float *d_out, int batch, int heads, int kvHeads, int headDim, int kvLen, int maxSeq, float scale,
+                        cudaStream_t stream)
+{
+    const bool q8 = d_kd != nullptr;
     if (!ctx || !d_q || !d_k || !d_v || !d_out || batch < 0 || heads <= 0 || kvHeads <= 0 || heads % kvHeads ||
-        headDim <= 0 || kvLen <= 0 || kvLen > maxSeq)
+        headDim <= 0 || kvLen <= 0 || kvLen > maxSeq || (q8 && !d_vd))
         return smc_fail(ctx, SMC_E_INVALID, "sdpa_decode: bad arguments");
     if (headDim > 256) return smc_fail(ctx, SMC_E_RANGE, "sdpa_decode: headDim %d exceeds 256", headDim);
     if (batch == 0) return SMC_OK;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaStream_t s = stream;
     const int Gall = heads / kvHeads;
     // query heads per CTA: at most two, so that the running state of its heads stays in registers; a larger group is
     // spread over CTAs that read the same cached head (the second read comes from L2).  Measured on a Llama-3-8B
@@ -525,12 +570,13 @@ int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const 
                           ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_k) |
                             reinterpret_cast<uintptr_t>(d_v)) & 15) == 0;
     if (!split_ok) {
+        if (q8) return smc_fail(ctx, SMC_E_UNSUPPORTED, "sdpa_decode: a Q8_0 cache needs headDim 64 or 128 and 16-byte aligned buffers");
         // reference-order kernel, one launch per (batch, head) group is avoided by treating each
         // (batch, head) as its own single-query problem through grid.y
         for (int b = 0; b < batch; ++b)
             for (int h = 0; h < heads; ++h) {
-                const float *kp = d_k + ((size_t)b * kvReal + h / Gall) * (size_t)maxSeq * headDim;
-                const float *vp = d_v + ((size_t)b * kvReal + h / Gall) * (size_t)maxSeq * headDim;
+                const float *kp = static_cast<const float *>(d_k) + ((size_t)b * kvReal + h / Gall) * (size_t)maxSeq * headDim;
+                const float *vp = static_cast<const float *>(d_v) + ((size_t)b * kvReal + h / Gall) * (size_t)maxSeq * headDim;
                 int rc = smc_launch_sdpa_tile(ctx, d_q + ((size_t)b * heads + h) * headDim, kp, vp,
                                               d_out + ((size_t)b * heads + h) * headDim, 1, kvLen, headDim, scale, 1,
                                               headDim, headDim, 0.f, s);
@@ -556,14 +602,20 @@ int smc_sdpa_decode_dev(smc_ctx *ctx, const float *d_q, const float *d_k, const 
     dim3 grid(splits, kvHeads, batch);
     int rc;
     if (headDim == 128)
-        rc = launch_split_g<16>(ctx, G, grid, smem, s, d_q, d_k, d_v, records, heads, kvHeads, kvLen, maxSeq,
-                                scale, splits, d_out, tickets, hshare);
+        rc = q8 ? launch_split_g<16, true>(ctx, G, grid, smem, s, d_q, d_k, d_v, d_kd, d_vd, records, heads, kvHeads, kvLen, maxSeq,
+                                           scale, splits, d_out, tickets, hshare)
+                : launch_split_g<16, false>(ctx, G, grid, smem, s, d_q, d_k, d_v, d_kd, d_vd, records, heads, kvHeads, kvLen, maxSeq,
+                                            scale, splits, d_out, tickets, hshare);
     else
-        rc = launch_split_g<8>(ctx, G, grid, smem, s, d_q, d_k, d_v, records, heads, kvHeads, kvLen, maxSeq,
-                               scale, splits, d_out, tickets, hshare);
+        rc = q8 ? launch_split_g<8, true>(ctx, G, grid, smem, s, d_q, d_k, d_v, d_kd, d_vd, records, heads, kvHeads, kvLen, maxSeq,
+                                          scale, splits, d_out, tickets, hshare)
+                : launch_split_g<8, false>(ctx, G, grid, smem, s, d_q, d_k, d_v, d_kd, d_vd, records, heads, kvHeads, kvLen, maxSeq,
+                                           scale, splits, d_out, tickets, hshare);
     if (rc) return rc;
     return SMC_OK;
 }
+
+extern "C" {
 
 int smc_kv_append_dev(smc_ctx *ctx, const float *d_k, const float *d_v, float *d_kcache, float *d_vcache, int batch,
                       int kvHeads, int headDim, int pos, int maxSeq, void *stream)

@@ -151,6 +151,11 @@ int smc_launch_block_isums(smc_ctx *, const smc_q8act *, int m, const smc_weight
                            int32_t *sums, cudaStream_t s);
 int smc_launch_quantize_weights(smc_ctx *, int dtype, const float *v, int64_t n, void *raw, cudaStream_t s);
 int smc_launch_repack(smc_ctx *, smc_weight *, cudaStream_t s);
+int smc_sdpa_decode_any(smc_ctx *, const float *d_q, const void *d_k, const void *d_v, const __half *d_kd, const __half *d_vd,
+                        float *d_out, int batch, int heads, int kvHeads, int headDim, int kvLen, int maxSeq, float scale,
+                        cudaStream_t stream);
+int smc_launch_sdpa_q8_rows(smc_ctx *ctx, const float *q, const int8_t *kq, const __half *kd, const int8_t *vq, const __half *vd, float *out,
+                            int batch, int seqLen, int heads, int kvHeads, int hd, int kvLen, int maxSeq, float scale, cudaStream_t s);
 int smc_sdpa_decode_reserve(smc_ctx *, int max_batch, int heads, int kvHeads, int headDim, int maxSeq);
 int smc_launch_sdpa_prefill(smc_ctx *ctx, const float *q, const float *kc, const float *vc, float *out, int T, int nh, int nkv,
                             int hd, int pos0, int maxSeq, float scale, cudaStream_t s);

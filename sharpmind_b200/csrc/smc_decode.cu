@@ -28,6 +28,11 @@ struct smc_model {
     std::vector<float *> bqkv;
     bool has_bias = false;
     float *kcache = nullptr, *vcache = nullptr;  // [layer][batch][kvHeads][max_seq][head_dim]
+    // kv_dtype == SMC_KV_Q8_0: the caches are Q8_0 rows instead (QuantizedKVCache), as int8 planes of the same shape and
+    // fp16 block scales [layer][batch][kvHeads][max_seq][head_dim / 32]
+    bool kv_q8 = false;
+    int8_t *kq8 = nullptr, *vq8 = nullptr;
+    __half *kd8 = nullptr, *vd8 = nullptr;
     float *cosT = nullptr, *sinT = nullptr;
     float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *tmp = nullptr,
           *gu = nullptr, *act = nullptr;
@@ -41,6 +46,7 @@ void free_model(smc_ctx *ctx, smc_model *m)
     if (!m) return;
     float *bufs[] = {m->kcache, m->vcache, m->cosT, m->sinT, m->x, m->xn, m->q, m->k, m->v, m->att, m->tmp, m->gu, m->act, m->qkv, m->x2};
     for (float *p : bufs) cudaFree(p);
+    cudaFree(m->kq8), cudaFree(m->vq8), cudaFree(m->kd8), cudaFree(m->vd8);
     for (smc_weight *w : m->wqkv)
         if (w) smc_weight_release(ctx, w);
     for (float *b : m->bqkv) cudaFree(b);
@@ -112,9 +118,31 @@ __global__ void kv_load_kernel(const float *__restrict__ src, float *__restrict_
 // attention kernel.  Lane l holds elements l, l + 32, ...: the norm sums in the order of the stand-alone norm
 // kernel and the rotation uses the same unfused products, so the results are the same bits as the separate
 // launches.  headDim % 64 == 0, headDim <= 256.
+// A head row held as elements lane + 32 j -> Q8_0: block j is element j of every lane (QuantizeRowQ8_0,
+// QuantizedKVCache.cs:191-223: d = amax / 127, 1 for a zero block, stored as fp16; q = round-half-even(x / d)).
+template <int EPL>
+__device__ __forceinline__ void store_row_q8(const float (&v)[EPL], int8_t *qrow, __half *drow, int lane)
+{
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        float amax = fabsf(v[j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        float d = __fdiv_rn(amax, 127.0f);
+        if (amax == 0.0f) d = 1.0f;
+        qrow[lane + 32 * j] = (int8_t)max(-128, min(127, __float2int_rn(__fdiv_rn(v[j], d))));
+        if (lane == 0) drow[j] = __float2half_rn(d);
+    }
+}
+
+struct Q8Planes {
+    int8_t *kq, *vq;   // null: the cache is fp32
+    __half *kd, *vd;
+};
+
 template <int EPL>  // elements per lane = headDim / 32
 __global__ void __launch_bounds__(256) qkv_post_kernel(const float *__restrict__ qkv, float *__restrict__ q_out,
-                                                       float *__restrict__ kc, float *__restrict__ vc,
+                                                       float *__restrict__ kc, float *__restrict__ vc, Q8Planes q8,
                                                        const float *__restrict__ qnorm, const float *__restrict__ knorm,
                                                        const float *__restrict__ cosT, const float *__restrict__ sinT, int batch,
                                                        int nh, int nkv, int pos, int maxSeq, float eps, int neox, int seq0)
@@ -134,7 +162,12 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(const float *__restrict__
 #pragma unroll
     for (int j = 0; j < EPL; ++j) v[j] = src[lane + 32 * j];
     if (slot >= nh + nkv) {  // V: straight into the cache
-        float *dst = vc + (((size_t)b * nkv + (slot - nh - nkv)) * maxSeq + pos) * HD;
+        const size_t crow = ((size_t)b * nkv + (slot - nh - nkv)) * maxSeq + pos;
+        if (q8.vq) {
+            store_row_q8<EPL>(v, q8.vq + crow * HD, q8.vd + crow * EPL, lane);
+            return;
+        }
+        float *dst = vc + crow * HD;
 #pragma unroll
         for (int j = 0; j < EPL; ++j) dst[lane + 32 * j] = v[j];
         return;
@@ -171,19 +204,32 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(const float *__restrict__
                               : __fsub_rn(__fmul_rn(v[j], c), __fmul_rn(other, sn));
         }
     }
+    if (!is_q && q8.kq) {
+        const size_t crow = ((size_t)b * nkv + (slot - nh)) * maxSeq + pos;
+        store_row_q8<EPL>(v, q8.kq + crow * HD, q8.kd + crow * EPL, lane);
+        return;
+    }
     float *dst = is_q ? q_out + ((size_t)row * nh + slot) * HD : kc + (((size_t)b * nkv + (slot - nh)) * maxSeq + pos) * HD;
 #pragma unroll
     for (int j = 0; j < EPL; ++j) dst[lane + 32 * j] = v[j];
 }
 
+// per-layer strides of the caches (elements of the fp32 cache = bytes of the int8 planes; block scales are 1/32 of that)
+size_t layer_elems(const smc_model *m) { return (size_t)m->max_batch * m->d.n_kv_heads * m->d.max_seq * m->d.head_dim; }
+
 int launch_qkv_post(smc_ctx *ctx, const smc_model *m, int l, float *kc, float *vc, int B, int pos, cudaStream_t s, int seq0 = -1)
 {
     const smc_model_desc &d = m->d;
+    Q8Planes q8{nullptr, nullptr, nullptr, nullptr};
+    if (m->kv_q8) {
+        const size_t le = layer_elems(m);
+        q8 = Q8Planes{m->kq8 + l * le, m->vq8 + l * le, m->kd8 + l * (le / 32), m->vd8 + l * (le / 32)};
+    }
     const int warps = B * (d.n_heads + 2 * d.n_kv_heads);
     const dim3 grid((warps + 7) / 8);
     const float *qn = d.qk_norm ? m->qnorm[l] : nullptr, *kn = d.qk_norm ? m->knorm[l] : nullptr;
 #define SMC_QKV_POST(E)                                                                                              \
-    smc_launch_dep(ctx->use_pdl, qkv_post_kernel<E>, grid, dim3(256), 0, s, (const float *)m->qkv, m->q, kc, vc, qn, kn, \
+    smc_launch_dep(ctx->use_pdl, qkv_post_kernel<E>, grid, dim3(256), 0, s, (const float *)m->qkv, m->q, kc, vc, q8, qn, kn, \
                    (const float *)m->cosT, (const float *)m->sinT, B, d.n_heads, d.n_kv_heads, pos, d.max_seq, d.eps,    \
                    d.neox, seq0)
     switch (d.head_dim) {
@@ -198,6 +244,45 @@ int launch_qkv_post(smc_ctx *ctx, const smc_model *m, int l, float *kc, float *v
     return SMC_OK;
 }
 
+// one decode step of attention for layer l over the model's cache (fp32 or Q8_0)
+int attend_decode(smc_ctx *ctx, const smc_model *m, int l, int B, int pos, float scale, cudaStream_t s)
+{
+    const smc_model_desc &d = m->d;
+    const size_t le = layer_elems(m);
+    if (m->kv_q8)
+        return smc_sdpa_decode_any(ctx, m->q, m->kq8 + l * le, m->vq8 + l * le, m->kd8 + l * (le / 32), m->vd8 + l * (le / 32), m->att, B,
+                                   d.n_heads, d.n_kv_heads, d.head_dim, pos + 1, d.max_seq, scale, s);
+    return smc_sdpa_decode_any(ctx, m->q, m->kcache + l * le, m->vcache + l * le, nullptr, nullptr, m->att, B, d.n_heads, d.n_kv_heads,
+                               d.head_dim, pos + 1, d.max_seq, scale, s);
+}
+
+// dense fp32 context rows -> Q8_0 planes of the cache: one warp per 32-element block
+__global__ void __launch_bounds__(256) kv_load_q8_kernel(const float *__restrict__ src, int8_t *__restrict__ q, __half *__restrict__ dsc,
+                                                         long long nblocks, int batch, int max_batch, int kvh, int len, int max_seq, int hd)
+{
+    const int lane = threadIdx.x & 31, bpr = hd / 32;
+    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long blk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); blk < nblocks; blk += stride) {
+        const int bi = (int)(blk % bpr);
+        long long r = blk / bpr;
+        const int p = (int)(r % len);
+        r /= len;
+        const int h = (int)(r % kvh);
+        r /= kvh;
+        const int b = (int)(r % batch);
+        const long long l = r / batch;
+        const float x = src[blk * 32 + lane];
+        float amax = fabsf(x);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        float dd = __fdiv_rn(amax, 127.0f);
+        if (amax == 0.0f) dd = 1.0f;
+        const size_t row = (((size_t)l * max_batch + b) * kvh + h) * max_seq + p;
+        q[row * hd + 32 * bi + lane] = (int8_t)max(-128, min(127, __float2int_rn(__fdiv_rn(x, dd))));
+        if (lane == 0) dsc[row * bpr + bi] = __float2half_rn(dd);
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -210,6 +295,12 @@ int smc_model_kv_load(smc_ctx *ctx, smc_model *m, const float *d_k, const float 
     if (total == 0) return SMC_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int grid = (int)((total + 255) / 256 > ctx->sm_count * 16 ? ctx->sm_count * 16 : (total + 255) / 256);
+    if (m->kv_q8) {  // the context rows are quantised as QuantizedKVCache.Update would have quantised them
+        kv_load_q8_kernel<<<grid, 256, 0, s>>>(d_k, m->kq8, m->kd8, total / 32, batch, m->max_batch, m->d.n_kv_heads, len, m->d.max_seq, m->d.head_dim);
+        kv_load_q8_kernel<<<grid, 256, 0, s>>>(d_v, m->vq8, m->vd8, total / 32, batch, m->max_batch, m->d.n_kv_heads, len, m->d.max_seq, m->d.head_dim);
+        SMC_LAUNCH_CHECK(ctx);
+        return SMC_OK;
+    }
     kv_load_kernel<<<grid, 256, 0, s>>>(d_k, m->kcache, total, batch, m->max_batch, m->d.n_kv_heads, len, m->d.max_seq, m->d.head_dim);
     kv_load_kernel<<<grid, 256, 0, s>>>(d_v, m->vcache, total, batch, m->max_batch, m->d.n_kv_heads, len, m->d.max_seq, m->d.head_dim);
     SMC_LAUNCH_CHECK(ctx);
@@ -226,6 +317,10 @@ int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, sm
         (d.qk_norm && (!d.qnorm || !d.knorm)))
         return smc_fail(ctx, SMC_E_INVALID, "model_create: incomplete description");
     if (d.head_dim > 256) return smc_fail(ctx, SMC_E_RANGE, "headDim %d exceeds FlashMaxHeadDim 256", d.head_dim);
+    if (d.kv_dtype != SMC_KV_F32 && d.kv_dtype != SMC_KV_Q8_0)
+        return smc_fail(ctx, SMC_E_UNSUPPORTED, "model_create: kv_dtype %d (fp32 = 0 and Q8_0 = 8 are built)", d.kv_dtype);
+    if (d.kv_dtype == SMC_KV_Q8_0 && d.head_dim != 64 && d.head_dim != 128)
+        return smc_fail(ctx, SMC_E_UNSUPPORTED, "model_create: a Q8_0 KV cache needs headDim 64 or 128");
     const int H = d.hidden, qDim = d.n_heads * d.head_dim, kvDim = d.n_kv_heads * d.head_dim, F = d.ffn;
     auto shape_ok = [&](const smc_weight *w, int n, int k) { return w && w->N == n && w->K == k; };
     for (int l = 0; l < d.n_layers; ++l) {
@@ -263,10 +358,23 @@ int smc_model_create(smc_ctx *ctx, const smc_model_desc *desc, int max_batch, sm
     auto alloc = [&](float **p, size_t n) {
         if (e == cudaSuccess) e = cudaMalloc(p, n * sizeof(float));
     };
-    alloc(&m->kcache, cache), alloc(&m->vcache, cache), alloc(&m->cosT, half), alloc(&m->sinT, half);
+    m->kv_q8 = d.kv_dtype == SMC_KV_Q8_0;
+    if (m->kv_q8) {
+        if (e == cudaSuccess) e = cudaMalloc(&m->kq8, cache);
+        if (e == cudaSuccess) e = cudaMalloc(&m->vq8, cache);
+        if (e == cudaSuccess) e = cudaMalloc(&m->kd8, cache / 32 * sizeof(__half));
+        if (e == cudaSuccess) e = cudaMalloc(&m->vd8, cache / 32 * sizeof(__half));
+        if (e == cudaSuccess) e = cudaMemset(m->kq8, 0, cache);
+        if (e == cudaSuccess) e = cudaMemset(m->vq8, 0, cache);
+        if (e == cudaSuccess) e = cudaMemset(m->kd8, 0, cache / 32 * sizeof(__half));
+        if (e == cudaSuccess) e = cudaMemset(m->vd8, 0, cache / 32 * sizeof(__half));
+    } else {
+        alloc(&m->kcache, cache), alloc(&m->vcache, cache);
+        if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache * sizeof(float));
+        if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache * sizeof(float));
+    }
+    alloc(&m->cosT, half), alloc(&m->sinT, half);
     alloc(&m->x2, (size_t)H);
-    if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache * sizeof(float));
-    if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache * sizeof(float));
     if (e != cudaSuccess) {
         free_model(ctx, m);
         return smc_fail(ctx, SMC_E_CUDA, "model_create: allocation failed: %s", cudaGetErrorString(e));
@@ -327,6 +435,7 @@ int smc_model_destroy(smc_ctx *ctx, smc_model *m)
 int smc_model_kv(smc_ctx *ctx, smc_model *m, float **d_k, float **d_v)
 {
     if (!ctx || !m || !d_k || !d_v) return smc_fail(ctx, SMC_E_INVALID, "model_kv: bad arguments");
+    if (m->kv_q8) return smc_fail(ctx, SMC_E_UNSUPPORTED, "model_kv: the model's cache holds Q8_0 rows, not floats");
     *d_k = m->kcache;
     *d_v = m->vcache;
     return SMC_OK;
@@ -376,7 +485,7 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
             SMC_TRY(smc_launch_gemv_tma_addnorm(ctx, cur, &p1, m->wqkv[l], m->qkv, s));
             if (pending) std::swap(cur, other);
             SMC_TRY(launch_qkv_post(ctx, m, l, kc, vc, 1, pos, s));
-            SMC_TRY(smc_sdpa_decode_dev(ctx, m->q, kc, vc, m->att, 1, nh, nkv, hd, pos + 1, d.max_seq, scale, s));
+            SMC_TRY(attend_decode(ctx, m, l, 1, pos, scale, s));
             SMC_TRY(smc_qmatmul_dev(ctx, m->att, m->wo[l], m->tmp, 1, mode, s));
             smc_norm_prologue p2{m->tmp, m->norm2[l], other, d.eps};
             SMC_TRY(smc_launch_gemv_tma_addnorm(ctx, cur, &p2, m->wgu[l], m->gu, s));
@@ -406,6 +515,7 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
             SMC_TRY(linear(ctx, m->xn, joined, m->qkv, B, mode, reuse ? m->qa : nullptr, s, m->bqkv[l]));
             SMC_TRY(launch_qkv_post(ctx, m, l, kc, vc, B, pos, s));
         } else {
+            if (m->kv_q8) return smc_fail(ctx, SMC_E_UNSUPPORTED, "decode_step: a Q8_0 KV cache needs the joined Q/K/V path (layer %d has none usable in mode %d)", l, mode);
             SMC_TRY(linear(ctx, m->xn, m->wq[l], m->q, B, mode, reuse ? m->qa : nullptr, s, m->bq[l]));
             SMC_TRY(linear(ctx, m->xn, m->wk[l], m->k, B, mode, reuse ? m->qa : nullptr, s, m->bk[l]));
             SMC_TRY(linear(ctx, m->xn, m->wv[l], m->v, B, mode, reuse ? m->qa : nullptr, s, m->bv[l]));
@@ -418,7 +528,7 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
             SMC_TRY(smc_rope_dev(ctx, m->k, 1, B * nkv, hd, hd, pos, m->cosT, m->sinT, d.neox, s));
             SMC_TRY(smc_kv_append_dev(ctx, m->k, m->v, kc, vc, B, nkv, hd, pos, d.max_seq, s));
         }
-        SMC_TRY(smc_sdpa_decode_dev(ctx, m->q, kc, vc, m->att, B, nh, nkv, hd, pos + 1, d.max_seq, scale, s));
+        SMC_TRY(attend_decode(ctx, m, l, B, pos, scale, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->att, B, qDim, m->qb, s));
         SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s, m->bo[l]));
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, B, H, d.eps, s));
@@ -478,7 +588,13 @@ int smc_forward_last_logits(smc_ctx *ctx, smc_model *m, const int *d_tokens, int
         SMC_TRY(linear(ctx, m->xn, m->wqkv[l], m->qkv, T, mode, reuse ? m->qa : nullptr, s, m->bqkv[l]));
         // row t: per-head norm, rotation by position pos + t, K and V appended to sequence `seq`
         SMC_TRY(launch_qkv_post(ctx, m, l, kc, vc, T, pos, s, seq));
-        SMC_TRY(smc_launch_sdpa_prefill(ctx, m->q, kc + seq_off, vc + seq_off, m->att, T, nh, nkv, hd, pos, d.max_seq, scale, s));
+        if (m->kv_q8) {
+            const size_t le = layer_elems(m);
+            SMC_TRY(smc_launch_sdpa_q8_rows(ctx, m->q, m->kq8 + l * le + seq_off, m->kd8 + (l * le + seq_off) / 32, m->vq8 + l * le + seq_off,
+                                            m->vd8 + (l * le + seq_off) / 32, m->att, 1, T, nh, nkv, hd, pos + T, d.max_seq, scale, s));
+        } else {
+            SMC_TRY(smc_launch_sdpa_prefill(ctx, m->q, kc + seq_off, vc + seq_off, m->att, T, nh, nkv, hd, pos, d.max_seq, scale, s));
+        }
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->att, T, qDim, m->qb, s));
         SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s, m->bo[l]));
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, T, H, d.eps, s));

@@ -25,6 +25,7 @@ class _Desc(C.Structure):
         ("final_norm", C.c_void_p), ("lm_head", C.c_void_p),
         ("bq", C.POINTER(C.c_void_p)), ("bk", C.POINTER(C.c_void_p)), ("bv", C.POINTER(C.c_void_p)),
         ("bo", C.POINTER(C.c_void_p)), ("bgu", C.POINTER(C.c_void_p)), ("bdown", C.POINTER(C.c_void_p)),
+        ("kv_dtype", C.c_int),
     ]
 
 
@@ -41,6 +42,10 @@ class Decoder:
         self._keep = []
 
         def reg(raw, n, k, fmt=dt):
+            if isinstance(raw, ops.Weight):  # registered already (e.g. straight from a GGUF file)
+                if (raw.N, raw.K) != (n, k):
+                    raise ops.InvalidOperationException(f"weight is [{raw.N}, {raw.K}], the model needs [{n}, {k}]")
+                return raw
             if isinstance(raw, np.ndarray):
                 return ctx.register(raw, fmt, n, k, repack=True, keep_raw=keep_raw)
             return ctx.register_dev(raw, fmt, n, k, repack=True, keep_raw=keep_raw)
@@ -75,6 +80,7 @@ class Decoder:
         d.qnorm, d.knorm = ptrs(self.norms["qnorm"]), ptrs(self.norms["knorm"])
         d.final_norm = self.final_norm.data_ptr()
         d.lm_head = self.embedding.handle
+        d.kv_dtype = int(cfg.get("kv_dtype", 0))  # 0 = fp32 cache, 8 = Q8_0 rows (QuantizedKVCache)
         # optional bias vectors of the linear layers: weights["bq"] ... ["bdown"], lists of n_layers arrays (or None)
         self.biases = {}
         for name in ("bq", "bk", "bv", "bo", "bgu", "bdown"):

@@ -511,3 +511,77 @@ class DeviceOps:
         batch, kvh, max_seq, hd = kcache.shape
         self.ctx.check(self.lib.smc_kv_append_dev(self.ctx.h, self._chk(k), self._chk(v), self._chk(kcache),
                                                   self._chk(vcache), batch, kvh, hd, pos, max_seq, self._stream()))
+
+
+class KVCache:
+    """IKVCache on the device (SharpMind.Model/IKVCache.cs): an fp32 cache (KVCache) or a Q8_0 one (QuantizedKVCache),
+    holding one attention layer's keys and values for `batch` lock-step sequences."""
+
+    F32, Q8_0 = 0, 8
+
+    def __init__(self, ctx: CudaContext, batch: int, kv_heads: int, max_seq: int, head_dim: int, kind: int = 0):
+        import torch
+
+        self.ctx, self.torch, self.kind = ctx, torch, kind
+        self.batch, self.kv_heads, self.head_dim = batch, kv_heads, head_dim
+        h = C.c_void_p()
+        ctx.check(ctx.lib.smc_kv_create(ctx.h, batch, kv_heads, max_seq, head_dim, kind, C.byref(h)))
+        self.h = h
+
+    def _stream(self):
+        return C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+
+    @property
+    def Length(self) -> int:
+        return self.ctx.lib.smc_kv_length(self.h)
+
+    @property
+    def MaxSeqLen(self) -> int:
+        return self.ctx.lib.smc_kv_max_seq(self.h)
+
+    @property
+    def IsFull(self) -> bool:
+        return self.Length >= self.MaxSeqLen
+
+    def Reset(self):
+        self.ctx.check(self.ctx.lib.smc_kv_reset(self.ctx.h, self.h))
+
+    def Truncate(self, length: int):
+        self.ctx.check(self.ctx.lib.smc_kv_truncate(self.ctx.h, self.h, length))
+
+    def TrimToLast(self, keep: int):
+        self.ctx.check(self.ctx.lib.smc_kv_trim_to_last(self.ctx.h, self.h, keep, self._stream()))
+
+    def Update(self, k, v):
+        """k, v: CUDA fp32 [batch, seqLen, kvHeads, headDim]."""
+        b, s = k.shape[0], k.shape[1]
+        self.ctx.check(self.ctx.lib.smc_kv_update_dev(self.ctx.h, self.h, k.contiguous().data_ptr(), v.contiguous().data_ptr(),
+                                                      b, s, self._stream()))
+
+    def Snapshot(self):
+        """(position, keys, values) as host arrays ([batch, kvHeads, position, row] bytes or floats), or None when empty."""
+        n = self.ctx.lib.smc_kv_snapshot_bytes(self.h)
+        if n == 0:
+            return None
+        k, v, pos = np.empty(n, np.uint8), np.empty(n, np.uint8), C.c_int()
+        self.ctx.check(self.ctx.lib.smc_kv_snapshot(self.ctx.h, self.h, k.ctypes.data, v.ctypes.data, n, C.byref(pos)))
+        return pos.value, k, v
+
+    def Restore(self, snapshot):
+        if snapshot is None:
+            return
+        pos, k, v = snapshot
+        self.ctx.check(self.ctx.lib.smc_kv_restore(self.ctx.h, self.h, k.ctypes.data, v.ctypes.data, k.size, pos))
+
+    def attention(self, q, scale: float):
+        """q: CUDA fp32 [batch, seqLen, heads, headDim], the queries of the last seqLen positions; returns the same shape."""
+        b, s, heads, hd = q.shape
+        out = self.torch.empty_like(q)
+        self.ctx.check(self.ctx.lib.smc_sdpa_kv_dev(self.ctx.h, self.h, q.contiguous().data_ptr(), out.data_ptr(), b, heads, s, scale,
+                                                    self._stream()))
+        return out
+
+    def Dispose(self):
+        if self.h:
+            self.ctx.lib.smc_kv_destroy(self.ctx.h, self.h)
+            self.h = None

@@ -250,6 +250,42 @@ def test_decode_with_linear_biases(oracle, cuda, which, mode):
     dec.close()
 
 
+@pytest.mark.parametrize("cfg0,name", [(SMALL, "dec_small"), (LLAMA_LIKE, "dec_llama")])
+@pytest.mark.parametrize("mode", [ops.Mode.ACT_F32, ops.Mode.REF_ORDER])
+def test_decode_with_q8_0_kv_cache(oracle, cuda, cfg0, name, mode):
+    """kv_dtype = Q8_0 (QuantizedKVCache): a prompt pass writes quantised K / V rows, decode steps (one sequence and
+    two) append to them and attend over them; against the oracle whose cache holds what those rows decode to.  A K or V
+    element whose quotient sits on a rounding boundary may quantise one step apart on the two sides (one element of one
+    cached row: a few 1e-5 of the attention output), hence 1e-3 rather than the 1e-4 of the fp32 cache."""
+    cfg = dict(cfg0, kv_dtype=8)
+    w = _weights(oracle, cfg, name)
+    n_prompt = 9
+    toks = synth.token_ids(name, "q8kv", (n_prompt + 5, 2), cfg["vocab"])
+    ref = oracle.Decoder(cfg, w, 2)
+    for p in range(n_prompt):
+        want = ref.step(toks[p], p)
+    dec = Decoder(cuda, cfg, w, max_batch=2, keep_raw=(mode == ops.Mode.REF_ORDER))
+    for seq in range(2):
+        got = dec.forward_last_logits(to_dev(np.ascontiguousarray(toks[:n_prompt, seq])), 0, seq, mode)[0].cpu().numpy()
+        assert np.abs(got - want[seq]).max() <= 1e-3 * np.abs(want).max(), float(np.abs(got - want[seq]).max() / np.abs(want).max())
+    for p in range(n_prompt, n_prompt + 5):
+        want = ref.step(toks[p], p)
+        got = dec.step(to_dev(toks[p]), p, mode)[0].cpu().numpy()
+        assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max(), (p, float(np.abs(got - want).max() / np.abs(want).max()))
+    dec.close()
+    # one sequence with quantised activations takes the fused one-row path over the same cache format
+    ref1 = oracle.Decoder(cfg, w, 1)
+    dec1 = Decoder(cuda, cfg, w, max_batch=1)
+    tok = toks[0, :1].copy()
+    for p in range(6):
+        want = ref1.step(tok, p, act_q8=True)
+        got = dec1.step(to_dev(tok), p, ops.Mode.ACT_Q8)[0].cpu().numpy()
+        assert np.abs(got - want).max() <= Q8_SHALLOW_TOL * np.abs(want).max()
+        tok = want.argmax(axis=1).astype(np.int32)
+    dec1.close()
+    assert cuda.device_status() == 0
+
+
 def test_decode_batch_rows_are_independent(oracle, cuda):
     """Lock-step sequences do not interact: row b of a batch of 4 equals the same sequence decoded alone."""
     import torch
