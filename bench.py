@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload llama70b|llama8b] [--batch M] [--mode q8|f32] [--layers L]
-                    [--only gemv:<shape>[:<M>[:q8|q8pre|f32]] | decode[:qwen3|llama8b] | prompt | elementwise | prefill]
+                    [--only gemv:<shape>[:<M>[:q8|q8pre|f32]] | decode[:qwen3|llama8b][:q8kv] | prompt | elementwise | prefill]
 
 Workload (default `llama70b`, BASELINE configs[4], the largest configuration that fits one GPU and the one the
 multi-GPU target is stated on): the Llama-3-70B-shaped FFN GEMV stack -- per layer the fused gate||up projection
@@ -305,7 +305,8 @@ def decode_step_bytes(cfg: dict, batch: int, ctx_len: int) -> dict:
     dt = cfg["dtype"]
     per_layer = (q_dim * H + 2 * kv_dim * H + H * q_dim + 2 * F * H) * bpe[dt] + H * F * bpe[cfg.get("down_dtype") or dt]
     weights = int(L * per_layer + V * H * bpe[cfg.get("head_dtype") or dt])
-    kv = L * batch * 2 * cfg["n_kv_heads"] * (ctx_len + 1) * hd * 4
+    kv_bpe = 34 / 32 if cfg.get("kv_dtype") == 8 else 4  # QuantizedKVCache rows are Q8_0 blocks
+    kv = int(L * batch * 2 * cfg["n_kv_heads"] * (ctx_len + 1) * hd * kv_bpe)
     return {"weights": weights, "kv": kv}
 
 
@@ -501,6 +502,8 @@ def run_only(args):
         res = time_gemv_shape(torch, ctx, dev, ops, parts[1], M, parts[3] if len(parts) > 3 else "q8", peak)
     elif parts[0] == "decode":
         cfg = dict(synth.LLAMA3_8B if len(parts) > 1 and parts[1] == "llama8b" else synth.QWEN3_0_6B)
+        if parts[-1] == "q8kv":
+            cfg["kv_dtype"] = 8
         if args.layers:
             cfg["n_layers"] = args.layers
         res = {"decode": time_decode(torch, ctx, dev, cfg, [args.batch], 2048, max(args.steps, 4), mode, once=args.no_graph)}
@@ -897,6 +900,10 @@ def run_ours(args):
                  "tokens_per_s_batch1": rows[0]["tokens_per_s"], "ms_per_step_batch1": rows[0]["ms_per_step"],
                  "tokens_per_s_batch32": rows[1]["tokens_per_s"], "ms_per_step_batch32": rows[1]["ms_per_step"],
                  "GBps_batch1": rows[0]["GBps"], "GBps_batch32": rows[1]["GBps"]}
+            q8kv = time_decode(torch, ctx, dev, dict(synth.QWEN3_0_6B, kv_dtype=8), [1, 32], 2048, 16, ops.Mode.ACT_Q8)
+            d["q8_0_kv"] = {"what": "the same steps over a Q8_0 KV cache (QuantizedKVCache rows)",
+                            "tokens_per_s_batch1": q8kv[0]["tokens_per_s"], "tokens_per_s_batch32": q8kv[1]["tokens_per_s"],
+                            "kv_MB_batch32": q8kv[1]["kv_MB"], "GBps_batch32": q8kv[1]["GBps"]}
             pr = time_prompt(torch, ctx, dev, dict(synth.QWEN3_0_6B), 2048, 1024, ops.Mode.ACT_Q8, 2)
             d["prompt_pass"] = {"what": "ForwardLastLogits over a 2048-token seeded prompt in chunks of 1024, one sequence",
                                 "ms": pr["ms"], "tokens_per_s": pr["tokens_per_s"]}

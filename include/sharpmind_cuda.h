@@ -347,6 +347,25 @@ SMC_API int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int
 SMC_API int smc_forward_last_logits(smc_ctx *ctx, smc_model *model, const int *d_tokens, int seqLen, int seq, int pos,
                                     int mode, float *d_logits, int *d_argmax, void *stream);
 
+/* Transformer.Forward over `seqLen` tokens of one sequence (the K + 1 draft tokens of a verification round,
+ * MedusaGenerator.cs:247-260): as smc_forward_last_logits, but d_logits is [seqLen, vocab] (row i predicts the token
+ * after token i), d_argmax [seqLen] the greedy pick per row, and d_hidden (may be null) [seqLen, hidden] receives the
+ * final-normed hidden states.  The model's cache keeps no length of its own: IKVCache.Truncate(n) after a rejected draft
+ * (MedusaGenerator.cs:394-398, SpeculativeGenerator's Restore) is the caller passing pos = n on its next call; rows past
+ * it are never read and are overwritten by the next append. */
+SMC_API int smc_forward_logits(smc_ctx *ctx, smc_model *model, const int *d_tokens, int seqLen, int seq, int pos, int mode,
+                               float *d_logits, int *d_argmax, float *d_hidden, void *stream);
+/* The acceptance rule of a verification round (MedusaGenerator.cs:262-283): d_draft [heads + 1] holds the model's own
+ * greedy token followed by the heads' guesses, d_argmax [heads + 1] the greedy pick after each of them;
+ * *d_accepted = 1 + the longest prefix i < heads with d_argmax[i] == d_draft[i + 1]. */
+SMC_API int smc_verify_greedy_dev(smc_ctx *ctx, const int *d_argmax, const int *d_draft, int heads, int *d_accepted, void *stream);
+/* MedusaHeads.Predict on a Q8_0 head (MedusaHeads.cs:64-130): head h maps the normed hidden state through
+ * h' = SiLU(hidden W_h + b_h) (d_head_w [k][hidden][hidden] fp32 with W[j * hidden + i], d_head_b [k][hidden]) and the
+ * shared LM head picks its token: d_tokens [k].  d_work holds k * (hidden + vocab) floats.  The head transform is summed
+ * in the reference's order; the LM head runs in SMC_REF_ORDER when the weight kept its GGUF copy, else SMC_ACT_F32. */
+SMC_API int smc_medusa_predict_dev(smc_ctx *ctx, const float *d_hidden, const float *d_head_w, const float *d_head_b, int k,
+                                   int hidden, const smc_weight *lm_head, float *d_work, int *d_tokens, void *stream);
+
 /* One activation row whose elementwise producer rides in the matmul's staging (SMC_ACT_Q8 arithmetic, weights that
  * the one-row bulk-copy kernel takes: registered with SMC_W_REPACK, K % 1024 == 0 for Q8_0 / K % 2048 == 0 for the
  * K-quants, K <= 8192; SMC_E_UNSUPPORTED otherwise):

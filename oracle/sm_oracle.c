@@ -784,6 +784,37 @@ SMO_API int smo_argmax(const float *logits, int n)
     return best;
 }
 
+/* SharpMind.Model/Layers/MedusaHeads.cs:80-101 (PredictQuantized, the head transform): head h maps the normed hidden
+ * state to SiLU(b_h + hidden W_h), W_h stored [j * H + i], the sum taken over j in order from the bias.
+ * w [k][H][H], b [k][H], out [k][H]. */
+SMO_API void smo_medusa_heads(const float *hidden, const float *w, const float *b, float *out, int k, int H)
+{
+    for (int h = 0; h < k; h++) {
+        const float *wh = w + (int64_t)h * H * H;
+        float *o = out + (int64_t)h * H;
+        for (int i = 0; i < H; i++) {
+            float sum = b[(int64_t)h * H + i];
+            for (int j = 0; j < H; j++)
+                sum += hidden[j] * wh[(int64_t)j * H + i];
+            o[i] = sum;
+        }
+        for (int i = 0; i < H; i++)
+            o[i] = o[i] / (1.0f + expf(-o[i]));
+    }
+}
+
+/* SharpMind.Inference/MedusaGenerator.cs:269-283: token 0 of the draft is the model's own greedy choice and always
+ * accepted; head guess i + 1 is accepted while the verification pass's greedy pick after token i equals it. */
+SMO_API int smo_verify_greedy(const int *argmax, const int *draft, int heads)
+{
+    int accepted = 1;
+    for (int i = 0; i < heads; i++) {
+        if (argmax[i] != draft[i + 1]) break;
+        accepted++;
+    }
+    return accepted;
+}
+
 /* SharpMind.Model/Layers/Attention/AttentionKernels.cs:409-475 (ScaledDotProductFlashScalar),
  * alibiSlope = 0. Tiles of 64 keys, running max / sum, O rescaled per tile. */
 SMO_API void smo_sdpa_flash(const float *q, const float *k, const float *v, float *out, int seqLen,

@@ -100,6 +100,10 @@ def lib() -> C.CDLL:
         L.smo_add_inplace.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
         L.smo_argmax.restype = C.c_int
         L.smo_argmax.argtypes = [C.c_void_p, C.c_int]
+        L.smo_medusa_heads.restype = None
+        L.smo_medusa_heads.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        L.smo_verify_greedy.restype = C.c_int
+        L.smo_verify_greedy.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.smo_sdpa_flash.restype = None
         L.smo_sdpa_flash.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                      C.c_float, C.c_int, C.c_int, C.c_int]
@@ -362,6 +366,29 @@ def add(x, y) -> np.ndarray:
 def argmax(logits) -> int:
     logits = _f32(logits)
     return int(lib().smo_argmax(_p(logits), logits.size))
+
+
+def medusa_heads(hidden, w, b) -> np.ndarray:
+    """MedusaHeads.PredictQuantized's head transform: hidden [H], w [k, H, H], b [k, H] -> SiLU(b + hidden W) [k, H]."""
+    hidden, w, b = _f32(hidden), _f32(w), _f32(b)
+    k, H = b.shape
+    out = np.empty((k, H), dtype=np.float32)
+    lib().smo_medusa_heads(_p(hidden), _p(w), _p(b), _p(out), k, H)
+    return out
+
+
+def medusa_predict(hidden, w, b, lm_head_raw, vocab: int) -> tuple[np.ndarray, np.ndarray]:
+    """MedusaHeads.Predict on a Q8_0 LM head: the tokens the k heads pick and their logits [k, vocab]."""
+    h = medusa_heads(hidden, w, b)
+    k, H = h.shape
+    logits = qmatmul(8, h, lm_head_raw, k, H, vocab)
+    return np.array([argmax(logits[i]) for i in range(k)], dtype=np.int32), logits
+
+
+def verify_greedy(argmax_rows, draft) -> int:
+    a = np.ascontiguousarray(argmax_rows, dtype=np.int32)
+    d = np.ascontiguousarray(draft, dtype=np.int32)
+    return int(lib().smo_verify_greedy(_p(a), _p(d), d.size - 1))
 
 
 def sdpa_flash_q8(q, k_rows, v_rows, scale: float, causal: bool = True) -> np.ndarray:

@@ -555,8 +555,25 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
     return SMC_OK;
 }
 
+// all_rows == 0: Transformer.ForwardLastLogits (logits of the last position); != 0: Transformer.Forward (logits of every
+// position, [seqLen, vocab]), with the final-normed hidden states copied to d_hidden [seqLen, hidden] when given.
+static int forward_tokens(smc_ctx *ctx, smc_model *m, const int *d_tokens, int seqLen, int seq, int pos, int mode, float *d_logits,
+                          int *d_argmax, int all_rows, float *d_hidden, void *stream);
+
 int smc_forward_last_logits(smc_ctx *ctx, smc_model *m, const int *d_tokens, int seqLen, int seq, int pos, int mode,
                             float *d_logits, int *d_argmax, void *stream)
+{
+    return forward_tokens(ctx, m, d_tokens, seqLen, seq, pos, mode, d_logits, d_argmax, 0, nullptr, stream);
+}
+
+int smc_forward_logits(smc_ctx *ctx, smc_model *m, const int *d_tokens, int seqLen, int seq, int pos, int mode, float *d_logits,
+                       int *d_argmax, float *d_hidden, void *stream)
+{
+    return forward_tokens(ctx, m, d_tokens, seqLen, seq, pos, mode, d_logits, d_argmax, 1, d_hidden, stream);
+}
+
+static int forward_tokens(smc_ctx *ctx, smc_model *m, const int *d_tokens, int seqLen, int seq, int pos, int mode, float *d_logits,
+                          int *d_argmax, int all_rows, float *d_hidden, void *stream)
 {
     if (!ctx || !m || !d_tokens || !d_logits || seqLen <= 0) return smc_fail(ctx, SMC_E_INVALID, "forward_last_logits: bad arguments");
     if (seq < 0 || seq >= m->max_batch) return smc_fail(ctx, SMC_E_RANGE, "forward_last_logits: sequence %d outside [0, %d)", seq, m->max_batch);
@@ -609,11 +626,76 @@ int smc_forward_last_logits(smc_ctx *ctx, smc_model *m, const int *d_tokens, int
         const float *next_norm = l + 1 < d.n_layers ? m->norm1[l + 1] : d.final_norm;
         SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, T, H, d.eps, s));
     }
+    if (all_rows) {  // Transformer.Forward: the LM head meets every position (draft verification reads all of them)
+        if (d_hidden) SMC_CUDA(ctx, cudaMemcpyAsync(d_hidden, m->xn, (size_t)T * H * sizeof(float), cudaMemcpyDeviceToDevice, s));
+        SMC_TRY(smc_qmatmul_dev(ctx, m->xn, d.lm_head, d_logits, T, mode, s));
+        if (d_argmax) SMC_TRY(smc_argmax_dev(ctx, d_logits, T, d.vocab, d_argmax, s));
+        return SMC_OK;
+    }
     // only the last position's logits are formed (Transformer.ForwardLastLogits)
     SMC_TRY(smc_qmatmul_dev(ctx, m->xn + (size_t)(T - 1) * H, d.lm_head, d_logits, 1, mode, s));
     if (d_argmax) SMC_TRY(smc_argmax_dev(ctx, d_logits, 1, d.vocab, d_argmax, s));
 #undef SMC_TRY
     return SMC_OK;
+}
+
+// ---- draft verification (MedusaGenerator.cs:262-283) and the Medusa heads (MedusaHeads.PredictQuantized, MedusaHeads.cs:80-130) ----
+namespace {
+
+// accepted = 1 + the longest prefix i with argmax[i] == draft[i + 1]  (token 0 was the model's own greedy choice)
+__global__ void verify_greedy_kernel(const int *__restrict__ argmax, const int *__restrict__ draft, int heads, int *__restrict__ accepted)
+{
+    smc_grid_dep_sync();
+    if (threadIdx.x || blockIdx.x) return;
+    int a = 1;
+    for (int i = 0; i < heads; ++i) {
+        if (argmax[i] != draft[i + 1]) break;
+        ++a;
+    }
+    *accepted = a;
+}
+
+// h'[head][i] = SiLU(b[i] + sum_j hidden[j] * W[j * H + i]), the sum taken sequentially in fp32 with unfused products as
+// the reference's loop does; one thread per (head, i), consecutive threads read consecutive i of a weight row.
+__global__ void __launch_bounds__(256) medusa_heads_kernel(const float *__restrict__ hidden, const float *__restrict__ w,
+                                                          const float *__restrict__ b, float *__restrict__ out, int k, int H)
+{
+    smc_grid_dep_sync();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= k * H) return;
+    const int head = t / H, i = t - head * H;
+    const float *wh = w + (size_t)head * H * H;
+    float sum = b[(size_t)head * H + i];
+    for (int j = 0; j < H; ++j) sum = __fadd_rn(sum, __fmul_rn(hidden[j], wh[(size_t)j * H + i]));
+    out[t] = __fdiv_rn(sum, 1.0f + expf(-sum));
+}
+
+}  // namespace
+
+int smc_verify_greedy_dev(smc_ctx *ctx, const int *d_argmax, const int *d_draft, int heads, int *d_accepted, void *stream)
+{
+    if (!ctx || !d_argmax || !d_draft || !d_accepted || heads < 0) return smc_fail(ctx, SMC_E_INVALID, "verify_greedy: bad arguments");
+    smc_launch_dep(ctx->use_pdl, verify_greedy_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), d_argmax, d_draft, heads, d_accepted);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+int smc_medusa_predict_dev(smc_ctx *ctx, const float *d_hidden, const float *d_head_w, const float *d_head_b, int k, int hidden,
+                           const smc_weight *lm_head, float *d_work, int *d_tokens, void *stream)
+{
+    if (!ctx || !d_hidden || !d_head_w || !d_head_b || !lm_head || !d_work || !d_tokens || k < 0 || hidden <= 0)
+        return smc_fail(ctx, SMC_E_INVALID, "medusa_predict: bad arguments");
+    if (lm_head->K != hidden) return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "medusa_predict: lm_head has K = %d, hidden is %d", lm_head->K, hidden);
+    if (k == 0) return SMC_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float *heads_out = d_work, *logits = d_work + (size_t)k * hidden;  // d_work holds k * (hidden + vocab) floats
+    smc_launch_dep(ctx->use_pdl, medusa_heads_kernel, dim3((k * hidden + 255) / 256), dim3(256), 0, s, d_hidden, d_head_w, d_head_b, heads_out, k,
+                   hidden);
+    SMC_LAUNCH_CHECK(ctx);
+    // QuantizedMatMulQ8_0(headsInput, rawEmbedding, logits, k, hidden, vocab) in the scalar tier's order, then Argmax per head
+    int rc = smc_qmatmul_dev(ctx, heads_out, lm_head, logits, k, lm_head->d_raw ? SMC_REF_ORDER : SMC_ACT_F32, stream);
+    if (rc) return rc;
+    return smc_argmax_dev(ctx, logits, k, lm_head->N, d_tokens, stream);
 }
 
 }  // extern "C"

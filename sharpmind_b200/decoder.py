@@ -139,6 +139,39 @@ class Decoder:
                                                                 C.c_void_p(t.cuda.current_stream().cuda_stream)))
         return logits, argmax
 
+    def forward_logits(self, tokens, pos: int, seq: int = 0, mode: int = ops.Mode.ACT_Q8, want_hidden: bool = False):
+        """Transformer.Forward over the tokens of one sequence (a verification round's K + 1 draft tokens): returns
+        (logits [seqLen, vocab], greedy pick per row [seqLen], final-normed hidden states [seqLen, hidden] or None)."""
+        t = self.torch
+        n = tokens.numel()
+        logits = t.empty((n, self.cfg["vocab"]), dtype=t.float32, device="cuda")
+        argmax = t.empty(n, dtype=t.int32, device="cuda")
+        hidden = t.empty((n, self.cfg["hidden"]), dtype=t.float32, device="cuda") if want_hidden else None
+        self.ctx.check(self.ctx.lib.smc_forward_logits(self.ctx.h, self.h, tokens.contiguous().data_ptr(), n, seq, pos, int(mode),
+                                                       logits.data_ptr(), argmax.data_ptr(),
+                                                       None if hidden is None else hidden.data_ptr(),
+                                                       C.c_void_p(t.cuda.current_stream().cuda_stream)))
+        return logits, argmax, hidden
+
+    def verify_greedy(self, argmax, draft):
+        """1 + the number of leading head guesses the model agrees with (MedusaGenerator's acceptance rule)."""
+        t = self.torch
+        acc = t.zeros(1, dtype=t.int32, device="cuda")
+        self.ctx.check(self.ctx.lib.smc_verify_greedy_dev(self.ctx.h, argmax.data_ptr(), draft.contiguous().data_ptr(), draft.numel() - 1,
+                                                          acc.data_ptr(), C.c_void_p(t.cuda.current_stream().cuda_stream)))
+        return int(acc.item())
+
+    def medusa_predict(self, hidden, head_w, head_b):
+        """MedusaHeads.Predict: hidden [hidden] (final-normed), head_w [k, hidden, hidden], head_b [k, hidden] -> tokens [k]."""
+        t = self.torch
+        k, H = head_w.shape[0], self.cfg["hidden"]
+        work = t.empty(k * (H + self.cfg["vocab"]), dtype=t.float32, device="cuda")
+        out = t.empty(k, dtype=t.int32, device="cuda")
+        self.ctx.check(self.ctx.lib.smc_medusa_predict_dev(self.ctx.h, hidden.contiguous().data_ptr(), head_w.contiguous().data_ptr(),
+                                                           head_b.contiguous().data_ptr(), k, H, self.embedding.handle, work.data_ptr(),
+                                                           out.data_ptr(), C.c_void_p(t.cuda.current_stream().cuda_stream)))
+        return out
+
     def close(self):
         if self.h:
             self.ctx.lib.smc_model_destroy(self.ctx.h, self.h)

@@ -343,3 +343,25 @@ def test_sdpa_flash_matches_plain_softmax_attention(oracle):
     p = np.exp(s - s.max())
     want = (p / p.sum()) @ v.astype(np.float64)
     assert np.allclose(got[0], want, rtol=1e-5, atol=1e-6)
+
+
+def test_medusa_head_transform_and_acceptance_rule(oracle):
+    """The oracle's Medusa restatement against a literal Python loop of MedusaHeads.PredictQuantized's head transform
+    (small case), and the acceptance rule on hand-written cases."""
+    rng = np.random.default_rng(7)
+    k, H = 2, 12
+    hidden = rng.standard_normal(H).astype(np.float32)
+    w = rng.standard_normal((k, H, H)).astype(np.float32)
+    b = rng.standard_normal((k, H)).astype(np.float32)
+    got = oracle.medusa_heads(hidden, w, b)
+    for h in range(k):
+        for i in range(H):
+            s = np.float32(b[h, i])
+            for j in range(H):
+                s = np.float32(s + np.float32(hidden[j] * w[h, j, i]))
+            want = np.float32(s / np.float32(np.float32(1.0) + np.exp(np.float32(-s), dtype=np.float32)))
+            assert abs(got[h, i] - want) <= 2e-7 * max(1.0, abs(want))
+    assert oracle.verify_greedy([5, 6, 7, 8], [1, 5, 6, 7]) == 4          # every guess right (the 4th pick is the bonus)
+    assert oracle.verify_greedy([5, 9, 7, 8], [1, 5, 6, 7]) == 2          # second guess wrong: later matches do not count
+    assert oracle.verify_greedy([4, 6, 7, 8], [1, 5, 6, 7]) == 1          # token 0 alone
+    assert oracle.verify_greedy([4], [1]) == 1                            # no heads
