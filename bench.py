@@ -370,7 +370,7 @@ def time_prompt(torch, ctx, dev, cfg: dict, n_tokens: int, chunk: int, mode, rep
     return row
 
 
-def time_gemv_shape(torch, ctx, dev, ops, which: str, M: int, mode: str, peak: float) -> dict:
+def time_gemv_shape(torch, ctx, dev, ops, which: str, M: int, mode: str, peak: float, once: bool = False) -> dict:
     """One matrix shape alone: `copies` distinct matrices (more than the L2 in total) cycled inside a CUDA graph."""
     dt, n, k, L = GEMV_SHAPES[which]
     ws = [device_matrix(torch, dev, ctx, dt, n, k, layer + 1) for layer in range(L)]
@@ -388,6 +388,10 @@ def time_gemv_shape(torch, ctx, dev, ops, which: str, M: int, mode: str, peak: f
             else:
                 dev.qmatmul(x, w, ops.Mode.ACT_F32, out=out)
 
+    if once:  # one pass over the copies, no graph: the form a counter capture wants
+        body()
+        torch.cuda.synchronize()
+        return {"shape": which, "M": M, "mode": mode, "launches": L, "device_status": ctx.device_status()}
     us = time_graph_us(torch, body, L, reps=5)
     nbytes = raw_bytes(dt, n, k) + 4 * M * k + 4 * M * n
     for w in ws:
@@ -499,7 +503,7 @@ def run_only(args):
     mode = ops.Mode.ACT_Q8 if args.mode == "q8" else ops.Mode.ACT_F32
     if parts[0] == "gemv":
         M = int(parts[2]) if len(parts) > 2 else 1
-        res = time_gemv_shape(torch, ctx, dev, ops, parts[1], M, parts[3] if len(parts) > 3 else "q8", peak)
+        res = time_gemv_shape(torch, ctx, dev, ops, parts[1], M, parts[3] if len(parts) > 3 else "q8", peak, once=args.no_graph)
     elif parts[0] == "decode":
         cfg = dict(synth.LLAMA3_8B if len(parts) > 1 and parts[1] == "llama8b" else synth.QWEN3_0_6B)
         if parts[-1] == "q8kv":
