@@ -102,6 +102,13 @@ SMC_API int64_t smc_raw_tensor_bytes(int dtype, int64_t N, int64_t K);
 SMC_API int smc_device_status(smc_ctx *ctx, int *status);
 /* Blocks until everything queued on the context's own stream has finished. */
 SMC_API int smc_synchronize(smc_ctx *ctx);
+/* Device memory for hosts without a CUDA runtime binding of their own (the C# backend assembly; SharpMind.GPU gets its
+ * buffers from ILGPU's Accelerator.Allocate1D, GPUActivationKernels.cs:10-20): allocations on the context's device,
+ * and copies ordered on `stream` (null = the context's stream) that have completed when the call returns. */
+SMC_API int smc_dev_alloc(smc_ctx *ctx, size_t bytes, void **d_out);
+SMC_API int smc_dev_free(smc_ctx *ctx, void *d_ptr);
+SMC_API int smc_copy_to_device(smc_ctx *ctx, void *d_dst, const void *host_src, size_t bytes, void *stream);
+SMC_API int smc_copy_to_host(smc_ctx *ctx, void *host_dst, const void *d_src, size_t bytes, void *stream);
 
 /* ---- weights: uploaded once ---------------------------------------------------------------
  * InferenceLinearLayer.SetRawWeight (SharpMind.Model/Layers/InferenceLinearLayer.cs:200-221)

@@ -246,6 +246,45 @@ int smc_synchronize(smc_ctx *ctx)
     return SMC_OK;
 }
 
+// Device memory for hosts that bring no CUDA runtime binding of their own (the C# assembly): plain allocations on the
+// context's device; copies are ordered on `stream` (null: the context's own stream) and have completed on return.
+int smc_dev_alloc(smc_ctx *ctx, size_t bytes, void **out)
+{
+    if (!ctx || !out || bytes == 0) return smc_fail(ctx, SMC_E_INVALID, "dev_alloc: bad arguments");
+    SMC_CUDA(ctx, cudaSetDevice(ctx->device));
+    SMC_CUDA(ctx, cudaMalloc(out, bytes));
+    return SMC_OK;
+}
+
+int smc_dev_free(smc_ctx *ctx, void *d_ptr)
+{
+    if (!ctx) return SMC_E_INVALID;
+    if (!d_ptr) return SMC_OK;
+    SMC_CUDA(ctx, cudaSetDevice(ctx->device));
+    SMC_CUDA(ctx, cudaFree(d_ptr));
+    return SMC_OK;
+}
+
+int smc_copy_to_device(smc_ctx *ctx, void *d_dst, const void *host_src, size_t bytes, void *stream)
+{
+    if (!ctx || (bytes && (!d_dst || !host_src))) return smc_fail(ctx, SMC_E_INVALID, "copy_to_device: bad arguments");
+    cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+    SMC_CUDA(ctx, cudaSetDevice(ctx->device));
+    SMC_CUDA(ctx, cudaMemcpyAsync(d_dst, host_src, bytes, cudaMemcpyHostToDevice, s));
+    SMC_CUDA(ctx, cudaStreamSynchronize(s));
+    return SMC_OK;
+}
+
+int smc_copy_to_host(smc_ctx *ctx, void *host_dst, const void *d_src, size_t bytes, void *stream)
+{
+    if (!ctx || (bytes && (!host_dst || !d_src))) return smc_fail(ctx, SMC_E_INVALID, "copy_to_host: bad arguments");
+    cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : ctx->stream;
+    SMC_CUDA(ctx, cudaSetDevice(ctx->device));
+    SMC_CUDA(ctx, cudaMemcpyAsync(host_dst, d_src, bytes, cudaMemcpyDeviceToHost, s));
+    SMC_CUDA(ctx, cudaStreamSynchronize(s));
+    return SMC_OK;
+}
+
 // ------------------------------------------------------------------------------------------ weights
 int smc_weight_register(smc_ctx *ctx, const void *host_raw, size_t bytes, int dtype, int N, int K, int flags,
                         smc_weight **out)
