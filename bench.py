@@ -17,17 +17,19 @@ One JSON line is printed by rank 0:
             in HBM, steps replayed from a CUDA graph, timed with CUDA events, max over ranks;
   e2e       the same metric through the host-facing call: host fp32 activations in, host fp32 outputs back, H2D / D2H
             inside the timed region.  One GPU: smc_qmatmul_host_w (the C-ABI slot a SharpMind linear layer binds);
-            N GPUs: pinned host row -> device, smc_qmatmul_gather_dev, gathered row -> pinned host, per matmul;
+            N GPUs: pinned host row -> device, the layer's two kernels, summed row -> pinned host, per layer;
   roofline  the kernel with the largest share of the step, timed alone over all layers against the measured HBM copy
             bandwidth in MEASURED_PEAKS.json; `kernels` carries every matrix of the workload the same way;
-  parity    N > 1: before anything is timed rank 0 regenerates every rank's slice of layer 0, computes it locally and
-            compares the gathered buffer bit for bit;
+  parity    N > 1: before anything is timed rank 0 regenerates every rank's slices of layer 0, computes them locally and
+            compares the exchanged result bit for bit;
   cpu_baseline  the reference's AVX2/FMA tier (C port, oracle/sm_cpu_fma.c) on the host cores, on a bounded sample;
   extras at N = 1: the configs[1] stack with its batch sweep, configs[0] (Q8_0 3072 x 1024 and the LM-head GEMV),
             configs[2] (the fp32 elementwise chain), the tcgen05 prefill matmul, decode tokens/s (configs[3]).
-With --gpus N > 1 (launched under torchrun) every matrix is row-split across the ranks and the output slices are
-exchanged inside the GEMV kernel over NVLink peer memory (`--gather nccl`: a library all-gather per matmul
-instead); total work is fixed ("strong" scaling).
+With --gpus N > 1 (launched under torchrun) the layer runs tensor-parallel with ONE exchange (`--tp ffn`, the default for
+one activation row): gate||up split by rows, its output and the SiLU-gate stay on the rank, the down projection is split
+along K and its partial sums are exchanged and added in rank order inside the GEMV kernel over NVLink peer memory.
+`--tp rows` splits every matrix by rows and exchanges the output slices of every matmul inside the kernel;
+`--gather nccl` uses a library all-gather per matmul instead.  Total work is fixed ("strong" scaling).
 `--impl reference` times the CPU port alone on a bounded sample per step (rank 0 only, all host threads).
 `--only ...` runs one kernel or section by itself and prints its own JSON line: the commands behind profiles/.
 """
@@ -81,6 +83,10 @@ def parse():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="N > 1: exchange inside the GEMV kernel over peer memory, or a library all-gather per matmul")
+    ap.add_argument("--tp", default="ffn", choices=["ffn", "rows"],
+                    help="N > 1, one row: 'ffn' = gate||up by rows, SwiGLU local, down split along K with the partial sums "
+                         "exchanged and added inside the kernel (one exchange per layer); 'rows' = every matrix by rows, "
+                         "one exchange per matmul")
     ap.add_argument("--no-extras", action="store_true", help="skip everything but the headline line (and e2e)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--only", default="", help="run one kernel / section alone (see the module docstring)")
@@ -544,7 +550,7 @@ def run_ours(args):
         dist = None
         torch.cuda.set_device(local)
     from sharpmind_b200 import ops, synth
-    from sharpmind_b200.sharded import PeerGather, RowSplit
+    from sharpmind_b200.sharded import KSplit, PeerGather, RowSplit
 
     ctx = ops.CudaContext(local)
     dev = ops.DeviceOps(ctx)
@@ -564,17 +570,30 @@ def run_ours(args):
         parts = 2 if name == "gate_up" else 1  # gate and up are split separately
         return split.rows(n // parts) * parts
 
+    # N > 1 with one activation row: the feed-forward dataflow with ONE exchange per layer.  gate||up is split by rows
+    # along whole K-steps of the down projection (its output stays on the rank, SiLU-gate included), down along K.
+    tp_ffn = world > 1 and args.gather == "peer" and args.tp == "ffn" and args.batch == 1 and mode == ops.Mode.ACT_Q8
+    ksplit = KSplit(world, rank, 2048)
+
+    def local_shapes(r):
+        """[(name, dtype, rows, K)] of rank r's slices."""
+        if tp_ffn:
+            f0, f1 = ksplit.k_range(F, r)
+            return [("gate_up", mats[0][1], 2 * (f1 - f0), H), ("down", mats[1][1], H, f1 - f0)]
+        return [(name, dt, rows_local_of(name, n), k) for (name, dt, n, k) in mats]
+
+    lmats = local_shapes(rank)
+
     # ---- weights: generated and quantised on the device, one slice per rank
     weights = []
     for layer in range(L):
-        weights.append([device_matrix(torch, dev, ctx, dt, rows_local_of(name, n), k, seed_of(layer, mi, rank))
-                        for mi, (name, dt, n, k) in enumerate(mats)])
+        weights.append([device_matrix(torch, dev, ctx, dt, n, k, seed_of(layer, mi, rank)) for mi, (name, dt, n, k) in enumerate(lmats)])
     torch.cuda.synchronize()
 
     def make_state(M):
         xs = [torch.from_numpy(np.random.default_rng(17 + i).standard_normal((M, k), dtype=np.float32)).cuda()
-              for i, (_, _, _, k) in enumerate(mats)]
-        acts = [ops.Q8Act(ctx, M, k) for (_, _, _, k) in mats]
+              for i, (_, _, _, k) in enumerate(lmats)]
+        acts = [ops.Q8Act(ctx, M, k) for (_, _, _, k) in lmats]
         outs = [torch.empty((M, w.N), device="cuda", dtype=torch.float32) for w in weights[0]]
         gathered = [torch.empty((world, M, w.N), device="cuda", dtype=torch.float32) for w in weights[0]] if world > 1 else None
         return xs, acts, outs, gathered
@@ -614,12 +633,25 @@ def run_ours(args):
             return gathered[mi]
         return outs[mi]
 
+    def ffn_layer(state, layer, md, x=None):
+        """gate||up on this rank's rows, then the K-split down projection whose staging applies the SiLU-gate and whose
+        tail exchanges and adds the partial sums: two launches, one exchange.  Returns the [1, H] sums."""
+        xs, _, outs, _ = state
+        fl = weights[layer][1].K
+        dev.qmatmul(xs[0] if x is None else x, weights[layer][0], md, out=outs[0])
+        return gather_for(1, 1).matmul_reduce(outs[0][0, :fl], weights[layer][1], md, up=outs[0][0, fl:])
+
     def step(state, M, md):
         for layer in range(L):
+            if tp_ffn:
+                ffn_layer(state, layer, md)
+                continue
             for mi in range(len(mats)):
                 one_matmul(state, M, layer, mi, md)
 
     def launches_per_step(M, md):
+        if tp_ffn:
+            return 2 * L
         # a single row is quantised inside the GEMV kernel; otherwise a quantiser launch precedes it
         per = sum(2 if (md == ops.Mode.ACT_Q8 and M > 1) else 1 for _ in mats)
         if peer and not (md == ops.Mode.ACT_Q8 and M == 1):
@@ -679,7 +711,37 @@ def run_ours(args):
     # its seed, computes it locally with the same kernel and compares the gathered buffer bit for bit (the one-row
     # kernel's sums do not depend on how rows are divided); every rank also checks its own chunk.
     parity = {"checked": False, "note": "single GPU: results are covered by the -m gpu parity tests"}
-    if world > 1:
+    if world > 1 and tp_ffn:
+        # layer 0 on every rank; rank 0 then regenerates EVERY rank's two slices from their seeds, forms each rank's
+        # partial sums with the same kernels and adds them in rank order: the exchanged sums must equal that bit for
+        # bit, and all ranks must hold the same bits
+        state = make_state(1)
+        got = ffn_layer(state, 0, mode).clone()
+        torch.cuda.synchronize()
+        ok = True
+        if rank == 0:
+            want = None
+            for r in range(world):
+                (_, dt_g, n_g, k_g), (_, dt_d, n_d, k_d) = local_shapes(r)
+                wg = weights[0][0] if r == 0 else device_matrix(torch, dev, ctx, dt_g, n_g, k_g, seed_of(0, 0, r))
+                wd = weights[0][1] if r == 0 else device_matrix(torch, dev, ctx, dt_d, n_d, k_d, seed_of(0, 1, r))
+                gu = dev.qmatmul(state[0][0], wg, mode)
+                part = dev.qmatmul(dev.swiglu(gu[:, :k_d].contiguous(), gu[:, k_d:].contiguous()), wd, mode)
+                want = part.clone() if want is None else want + part
+                if r:
+                    ctx.release(wg), ctx.release(wd)
+            ok = bool(torch.equal(got, want))
+        digest = got.view(torch.int32).to(torch.int64).sum()
+        lo, hi = digest.clone(), digest.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN), dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        same = bool(lo.item() == hi.item())
+        flag = torch.tensor([1 if (ok and same) else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity = {"checked": True, "ok": bool(flag.item()), "what": "layer 0 of the one-exchange feed-forward block: rank 0 recomputes "
+                  "every rank's partial sums from the seeds of their slices and adds them in rank order; the exchanged sums "
+                  "equal that bit for bit and every rank holds the same bits", "all_ranks_identical": same}
+        del state
+    elif world > 1:
         state = make_state(M)
         ok_all, detail = True, []
         for mi, (name, dt, n, k) in enumerate(mats):
@@ -724,6 +786,9 @@ def run_ours(args):
                    "l2": f"{L} distinct layers ({step_bytes / 1e9:.2f} GB per step) >> 126 MB L2",
                    "cuda_graph": graphed,
                    "parallelism": "single GPU" if world == 1 else (
+                       f"tp{world}: gate||up by rows (whole K-steps of down: {[b // 2048 for b in ksplit.bounds(F)]}), SiLU-gate "
+                       f"local, down split along K, partial sums exchanged and added in rank order inside the GEMV kernel over "
+                       f"NVLink peer memory: one exchange per layer" if tp_ffn else
                        f"row-split x{world}, slices exchanged by the GEMV kernel over NVLink peer memory" if peer
                        else f"row-split x{world} + NCCL all-gather")},
         "pct_of_8TBs_nominal": value / 8000.0 * 100.0 / world,
@@ -746,6 +811,22 @@ def run_ours(args):
                     q.QuantizedMatMulHandle(xs_h[mi], weights[layer][mi], outs_h[mi], M, k_, n_)
 
         api = "smc_qmatmul_host_w: one synchronous C-ABI call per matmul, host fp32 in / out"
+    elif tp_ffn:
+        pin_x = torch.from_numpy(xs_h[0]).pin_memory()
+        dev_x0 = torch.empty((1, H), device="cuda")
+        pin_y = torch.empty((1, H), dtype=torch.float32).pin_memory()
+        st_e = make_state(1)
+        gather_for(1, 1)
+
+        def e2e_step():
+            for layer in range(L):
+                dev_x0.copy_(pin_x, non_blocking=True)
+                pin_y.copy_(ffn_layer(st_e, layer, mode, dev_x0), non_blocking=True)
+                torch.cuda.current_stream().synchronize()  # the caller reads the block's output before its next call
+
+        api = ("per layer: pinned host row -> device, gate||up on the rank's rows, smc_qmatmul_reduce_dev (SiLU-gate in the "
+               "staging, K-split down, partial sums exchanged and added in the kernel), summed row -> pinned host, stream "
+               "synchronised")
     else:
         pin_x = [torch.from_numpy(x).pin_memory() for x in xs_h]
         dev_x = [torch.empty((M, k), device="cuda") for (_, _, _, k) in mats]
@@ -783,14 +864,14 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         el = float(t.item())
     result["e2e"] = {"value": step_bytes / el / 1e9, "unit": "GB/s", "ms_per_step": el * 1e3,
-                     "h2d_bytes_per_step": sum(4 * M * k for _, _, _, k in mats) * L,
-                     "d2h_bytes_per_step": sum(4 * M * n for _, _, n, _ in mats) * L, "api": api}
+                     "h2d_bytes_per_step": (4 * H if tp_ffn else sum(4 * M * k for _, _, _, k in mats)) * L,
+                     "d2h_bytes_per_step": (4 * H if tp_ffn else sum(4 * M * n for _, _, n, _ in mats)) * L, "api": api}
 
     if rank == 0 and not args.no_extras:
         # ---- every matrix of the workload alone over all layers; the roofline names the one with the largest share
         state = make_state(M)
         kern = {}
-        for mi, (name, dt, n, k) in enumerate(mats):
+        for mi, (name, dt, n, k) in enumerate(lmats):
             if mode == ops.Mode.ACT_Q8 and M > 1:
                 dev.quantize_q8(state[0][mi], state[1][mi], k)
 

@@ -447,6 +447,17 @@ SMC_API int smc_gather_buffer(smc_ctx *ctx, smc_gather *g, float **d_buf);
  * the buffer holds [world][M][N_local].  Same modes and errors as smc_qmatmul_dev. */
 SMC_API int smc_qmatmul_gather_dev(smc_ctx *ctx, smc_gather *g, const float *d_in, const smc_weight *w_local, int M,
                                    int mode, void *stream);
+/* A matmul split along K (tensor-parallel "down" projection: rank g holds columns [k0_g, k1_g) of every row, as a
+ * registered weight [N, k1_g - k0_g], and the matching slice of the activation row): every rank computes partial sums
+ * of all N outputs, the partials are exchanged, and every rank ends with dense[0 .. M*N) = sum over ranks IN RANK ORDER
+ * (fp32, the same additions on every rank: all ranks hold bit-identical results; they differ from the unsplit matmul by
+ * summation order only, within the mode's parity bound).  One row in SMC_ACT_Q8 runs as ONE kernel: partial sums leave
+ * as packets from the lanes that finish them and the kernel's tail adds them.  d_up != null: the activation is
+ * SiLU(d_in) * d_up, formed while the row is staged (the SwiGLU of a row-split gate||up stays local, so a whole FFN
+ * costs one exchange).  Other shapes: matmul, gather of the partials, a small adding kernel.  The buffer needs
+ * world * M * N floats.  The result is read from smc_gather_buffer. */
+SMC_API int smc_qmatmul_reduce_dev(smc_ctx *ctx, smc_gather *g, const float *d_in, const float *d_up, const smc_weight *w_local,
+                                   int M, int mode, void *stream);
 /* Exchange alone: this rank's chunk (count floats at d_buf + rank * count) was written by earlier work on
  * `stream`. */
 SMC_API int smc_gather_exchange_dev(smc_ctx *ctx, smc_gather *g, size_t count, void *stream);

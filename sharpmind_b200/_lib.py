@@ -108,6 +108,7 @@ SIGNATURES = {
     "smc_gather_destroy": (c_int, [c_void_p, c_void_p]),
     "smc_decode_step": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "smc_forward_last_logits": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "smc_qmatmul_reduce_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "smc_dev_alloc": (c_int, [c_void_p, C.c_size_t, C.POINTER(c_void_p)]),
     "smc_dev_free": (c_int, [c_void_p, c_void_p]),
     "smc_copy_to_device": (c_int, [c_void_p, c_void_p, c_void_p, C.c_size_t, c_void_p]),

@@ -498,9 +498,9 @@ int smc_qmatmul_dev_gather(smc_ctx *ctx, const float *d_in, const smc_weight *w,
 
 extern "C" {
 
-static int one_row_fusable(smc_ctx *ctx, const smc_weight *w, const char *what)
+static int one_row_fusable(smc_ctx *ctx, const smc_weight *w, const char *what, int max_k)
 {
-    if (!w->fast || w->K > 8192 || !smc_tma_supported(w, 1))
+    if (!w->fast || w->K > max_k || !smc_tma_supported(w, 1))
         return smc_fail(ctx, SMC_E_UNSUPPORTED, "%s: the weight is not one the one-row bulk-copy kernel takes (K = %d)", what, w->K);
     return SMC_OK;
 }
@@ -510,7 +510,7 @@ int smc_qmatmul_swiglu_dev(smc_ctx *ctx, const float *d_gate, const float *d_up,
     if (!ctx || !d_gate || !d_up || !w || !d_out) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_swiglu: bad arguments");
     if ((reinterpret_cast<uintptr_t>(d_gate) | reinterpret_cast<uintptr_t>(d_up)) & 15)
         return smc_fail(ctx, SMC_E_INVALID, "qmatmul_swiglu: gate and up must be 16-byte aligned");
-    int rc = one_row_fusable(ctx, w, "qmatmul_swiglu");
+    int rc = one_row_fusable(ctx, w, "qmatmul_swiglu", 65536);
     if (rc) return rc;
     return smc_launch_gemv_tma_swiglu(ctx, d_gate, d_up, w, d_out, static_cast<cudaStream_t>(stream));
 }
@@ -522,7 +522,7 @@ int smc_qmatmul_addnorm_dev(smc_ctx *ctx, const float *d_x, const float *d_add, 
     if ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_add) | reinterpret_cast<uintptr_t>(d_norm_w) |
          reinterpret_cast<uintptr_t>(d_sum)) & 15)
         return smc_fail(ctx, SMC_E_INVALID, "qmatmul_addnorm: operands must be 16-byte aligned");
-    int rc = one_row_fusable(ctx, w, "qmatmul_addnorm");
+    int rc = one_row_fusable(ctx, w, "qmatmul_addnorm", 9216);  // a thread keeps its chunks in registers across the norm
     if (rc) return rc;
     smc_norm_prologue pro{d_add, d_norm_w, d_sum, eps};
     return smc_launch_gemv_tma_addnorm(ctx, d_x, &pro, w, d_out, static_cast<cudaStream_t>(stream));

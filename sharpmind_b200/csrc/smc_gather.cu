@@ -8,8 +8,8 @@
 
 struct smc_gather {
     int rank = 0, world = 1;
-    size_t capacity = 0;           // floats in the dense data area (and packets in the packet area)
-    unsigned char *base = nullptr;  // own allocation: [control block | dense data | packets]
+    size_t capacity = 0;           // floats in the dense data area (and packets in each of the two packet areas)
+    unsigned char *base = nullptr;  // own allocation: [control block | dense data | packet area 0 | packet area 1]
     void *peer_base[SMC_GATHER_MAX_RANKS] = {};
     bool connected = false;
     smc_gather_dev view{};          // host copy of the device-resident view
@@ -25,21 +25,23 @@ namespace {
 // unpack the stripes of the peers' packets.
 __global__ void __launch_bounds__(512) gather_exchange_kernel(const smc_gather_dev *g, size_t count)
 {
-    __shared__ int s_ok;
     const unsigned tag = smc_gather_tag(g);
-    if (threadIdx.x == 0) {
-        if (blockIdx.x == 0) smc_gather_post_ready(g);
-        s_ok = smc_gather_wait_ready(g, tag) ? 1 : 0;
-    }
-    __syncthreads();
-    if (s_ok) {
-        const float *src = g->data + (size_t)g->rank * count;
-        const size_t nth = (size_t)gridDim.x * blockDim.x;
-        for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < count; t += nth)
-            smc_gather_send(g, count, t, __ldcg(src + t), tag);
-    }
+    const float *src = g->data + (size_t)g->rank * count;
+    const size_t nth = (size_t)gridDim.x * blockDim.x;
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < count; t += nth)
+        smc_gather_send(g, count, t, __ldcg(src + t), tag);
     smc_gather_collect(g, count, blockIdx.x, gridDim.x, tag);
     smc_gather_done(g, gridDim.x);
+}
+
+// Partial sums gathered as [world][count]: dense[i] = their sum in rank order (the order the fused one-row kernel uses).
+__global__ void __launch_bounds__(256) reduce_chunks_kernel(float *data, size_t count, int world)
+{
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float sum = 0.f;
+    for (int p = 0; p < world; ++p) sum += data[(size_t)p * count + i];
+    data[i] = sum;
 }
 
 // Exchange of a large chunk: stripes of 16-byte stores straight into every peer's dense area.
@@ -89,7 +91,7 @@ int smc_gather_create(smc_ctx *ctx, int rank, int world, size_t capacity_floats,
     smc_gather *g = new smc_gather();
     g->rank = rank, g->world = world;
     g->capacity = (capacity_floats + 3) & ~(size_t)3;
-    const size_t bytes = SMC_GATHER_CTRL_BYTES + g->capacity * (sizeof(float) + sizeof(unsigned long long));
+    const size_t bytes = SMC_GATHER_CTRL_BYTES + g->capacity * (sizeof(float) + 2 * sizeof(unsigned long long));
     cudaError_t e = cudaMalloc(&g->base, bytes);
     if (e == cudaSuccess) e = cudaMemset(g->base, 0, bytes);
     if (e == cudaSuccess) e = cudaMalloc(&g->d_view, sizeof(smc_gather_dev));
@@ -100,6 +102,7 @@ int smc_gather_create(smc_ctx *ctx, int rank, int world, size_t capacity_floats,
     }
     g->view.rank = rank, g->view.world = world, g->view.status = ctx->d_status;
     g->view.wait_ns = SMC_GATHER_WAIT_NS;
+    g->view.capacity = g->capacity;
     g->view.ctrl[rank] = reinterpret_cast<smc_gather_ctrl *>(g->base);
     g->view.data = reinterpret_cast<float *>(g->base + SMC_GATHER_CTRL_BYTES);
     g->view.peer_data[rank] = g->view.data;
@@ -224,6 +227,40 @@ int smc_qmatmul_gather_dev(smc_ctx *ctx, smc_gather *g, const float *d_in, const
     int rc = smc_qmatmul_dev_gather(ctx, d_in, w, chunk, M, mode, s, g->d_view, &fused);
     if (rc || fused) return rc;
     return smc_gather_exchange_dev(ctx, g, count, stream);
+}
+
+int smc_qmatmul_reduce_dev(smc_ctx *ctx, smc_gather *g, const float *d_in, const float *d_up, const smc_weight *w, int M, int mode,
+                           void *stream)
+{
+    if (!ctx || !g || !d_in || !w || M < 0) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_reduce: bad arguments");
+    if (!g->connected) return smc_fail(ctx, SMC_E_NOT_REGISTERED, "qmatmul_reduce: peers are not connected");
+    const size_t count = (size_t)M * (size_t)w->N;
+    if (count * (size_t)g->world > g->capacity)
+        return smc_fail(ctx, SMC_E_RANGE, "qmatmul_reduce: %d x %d partial sums x %d ranks exceed the buffer of %zu floats", M, w->N,
+                        g->world, g->capacity);
+    if (d_up && (M != 1 || mode != SMC_ACT_Q8 || !smc_tma_supported(w, 1)))
+        return smc_fail(ctx, SMC_E_UNSUPPORTED, "qmatmul_reduce: the SiLU-gate input needs one row, SMC_ACT_Q8 and a K the one-row kernel takes");
+    if (d_up && ((reinterpret_cast<uintptr_t>(d_in) | reinterpret_cast<uintptr_t>(d_up)) & 15))
+        return smc_fail(ctx, SMC_E_INVALID, "qmatmul_reduce: gate and up must be 16-byte aligned");
+    if (M == 0) return SMC_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float *dense = reinterpret_cast<float *>(g->base + SMC_GATHER_CTRL_BYTES);
+    if (g->world == 1) {  // nothing to add
+        if (d_up) return smc_launch_gemv_tma_swiglu(ctx, d_in, d_up, w, dense, s);
+        return smc_qmatmul_dev(ctx, d_in, w, dense, M, mode, stream);
+    }
+    // one row through the bulk-copy kernel: partial sums leave as packets from the lanes that finish them, and the
+    // kernel's tail adds the packets of all ranks
+    if (M == 1 && mode == SMC_ACT_Q8 && smc_tma_supported(w, 1) && !((reinterpret_cast<uintptr_t>(d_in)) & 15))
+        return smc_launch_gemv_tma_any(ctx, nullptr, d_in, d_up, nullptr, w, nullptr, g->d_view, true, s);
+    // any other shape: partial sums into this rank's chunk, all chunks gathered, then added in the same order
+    int rc = smc_qmatmul_dev(ctx, d_in, w, smc_gather_local_chunk(g, count), M, mode, stream);
+    if (rc) return rc;
+    rc = smc_gather_exchange_dev(ctx, g, count, stream);
+    if (rc) return rc;
+    reduce_chunks_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(dense, count, g->world);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
 }
 
 int smc_gather_destroy(smc_ctx *ctx, smc_gather *g)

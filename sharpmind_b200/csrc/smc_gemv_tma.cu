@@ -551,8 +551,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
                                                                     const smc_gather_dev *gd)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    int sending = -1;      // whether packets go out, known after the first look at the peers' ready flags (warp uniform)
-    unsigned gtag = 0;     // number of the running exchange
     constexpr uint32_t SLOT = (Math::STEP_BYTES * SS + 127u) & ~127u;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nw = blockDim.x >> 5;  // warps of this CTA
@@ -619,8 +617,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
     // Everything below depends on earlier launches (activations, the output buffer, the exchange counters), so this
     // is where a dependent launch waits for its predecessor.
     smc_grid_dep_sync();
-    // row-split across GPUs: tell the peers that this rank's readers of the previous exchange are done
-    if (GATHER && blockIdx.x == 0 && threadIdx.x == 32) smc_gather_post_ready(gd);
+    // split across GPUs: the number of this exchange (the counter is advanced by the previous exchange's last CTA, which
+    // the dependency wait above has seen complete)
+    const unsigned gtag = GATHER ? smc_gather_tag(gd) : 0u;
+    const bool greduce = GATHER && (tune & 0x100);  // partial sums of a K-split: every rank gets every output, summed
     if (xg.xf) {
         if (xg.nw) stage_x_addnorm_quant<Math>(xg.xf, xg.xadd, xg.nw, xg.eps, blockIdx.x == 0 ? xg.xsum : nullptr, K, sbase, fill_rest);
         else if (xg.xu) stage_x_quant<Math, 2, true>(xg.xf, xg.xu, K, sbase, fill_rest);
@@ -663,14 +663,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
                 if (i < n) {
                     math.template step<SS>(saddr, i, part, sbase, K, acc);
                     if (++part == spr) {
-                        if (GATHER && sending < 0) {  // first finished row of this warp: the peers' ready flags, one lane each
-                            gtag = smc_gather_tag(gd);
-                            sending = smc_gather_wait_ready_warp(gd, gtag) ? 1 : 0;
-                        }
                         const float v = warp_sum32(acc);  // every lane holds the sum
-                        if (lane == 0) out[row] = v;
-                        // this rank's chunk starts at rank * N in every peer's buffer; lane p sends to peer p
-                        if (GATHER && sending) smc_gather_send_warp(gd, (size_t)N, (size_t)row, v, gtag);
+                        if (lane == 0 && !greduce) out[row] = v;
+                        // this rank's chunk starts at rank * N in every peer's packet area; lane p sends to peer p
+                        if (GATHER) smc_gather_send_warp(gd, (size_t)N, (size_t)row, v, gtag, greduce);
                         acc = 0.f;
                         part = 0;
                         ++row;
@@ -705,16 +701,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
     }
     // rows done: unpack this CTA's stripe of the peers' slices as they arrive
     if (GATHER) {
-        smc_gather_collect(gd, (size_t)N, blockIdx.x, gridDim.x, smc_gather_tag(gd));
+        if (greduce) smc_gather_collect_reduce(gd, (size_t)N, blockIdx.x, gridDim.x, gtag);
+        else smc_gather_collect(gd, (size_t)N, blockIdx.x, gridDim.x, gtag);
         smc_gather_done(gd, gridDim.x);
     }
 }
 
 template <class Math, int SS>
 void launch_one(smc_ctx *ctx, dim3 grid, int nw, size_t smem, cudaStream_t s, const StepSrc &src, const XPtrs &x, float *out, int N,
-                int K, int slots, const smc_gather_dev *gd)
+                int K, int slots, const smc_gather_dev *gd, bool reduce)
 {
-    const int tune = ctx->tma_pre & 0xFF;
+    const int tune = (ctx->tma_pre & 0xFF) | (reduce ? 0x100 : 0);
     if (gd) {
         cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, true>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
@@ -728,7 +725,7 @@ void launch_one(smc_ctx *ctx, dim3 grid, int nw, size_t smem, cudaStream_t s, co
 
 template <class Math>
 int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, int N, int K, cudaStream_t s,
-                const smc_gather_dev *gd)
+                const smc_gather_dev *gd, bool reduce)
 {
     // One CTA of 24 warps per SM: the activation row is fetched and quantised once per SM (with three CTAs of eight
     // warps each, 444 copies of a 14336-element fp32 row were half as many bytes into the SMs as the matrix itself).
@@ -754,9 +751,9 @@ int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, in
     int ctas = ctx->tma_ctas ? ctx->tma_ctas : ctx->sm_count * per_sm;
     if (ctas > N) ctas = N;
     const dim3 grid(ctas);
-    if (ss == 4) launch_one<Math, 4>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd);
-    else if (ss == 2) launch_one<Math, 2>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd);
-    else launch_one<Math, 1>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd);
+    if (ss == 4) launch_one<Math, 4>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce);
+    else if (ss == 2) launch_one<Math, 2>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce);
+    else launch_one<Math, 1>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
@@ -813,6 +810,14 @@ int smc_launch_gemv_tma_addnorm(smc_ctx *ctx, const float *x, const smc_norm_pro
 int smc_launch_gemv_tma_full(smc_ctx *ctx, const smc_q8act *a, const float *xf, const float *xu, const smc_norm_prologue *pro,
                              const smc_weight *w, float *out, const smc_gather_dev *gd, cudaStream_t s)
 {
+    return smc_launch_gemv_tma_any(ctx, a, xf, xu, pro, w, out, gd, false, s);
+}
+
+// `reduce`: the matrix is a K-slice; the partial sums of all ranks are exchanged and added in rank order into the
+// dense buffer of `gd` (out is not written).
+int smc_launch_gemv_tma_any(smc_ctx *ctx, const smc_q8act *a, const float *xf, const float *xu, const smc_norm_prologue *pro,
+                            const smc_weight *w, float *out, const smc_gather_dev *gd, bool reduce, cudaStream_t s)
+{
     const int N = w->N, K = w->K;
     if (!xf && (!a || a->M != 1 || a->K != K)) return smc_fail(ctx, SMC_E_INVALID, "one-row matmul: the activation buffer must hold one row of %d", K);
     XPtrs x{};
@@ -822,13 +827,13 @@ int smc_launch_gemv_tma_full(smc_ctx *ctx, const smc_q8act *a, const float *xf, 
     StepSrc src{};
     if (w->dtype == SMC_Q4_K) {
         src.base[0] = w->d_raw;
-        return launch_math<MathQ4K>(ctx, src, x, out, N, K, s, gd);
+        return launch_math<MathQ4K>(ctx, src, x, out, N, K, s, gd, reduce);
     }
     if (w->dtype == SMC_Q6_K) {
         src.base[0] = w->q6u;
-        return launch_math<MathQ6K>(ctx, src, x, out, N, K, s, gd);
+        return launch_math<MathQ6K>(ctx, src, x, out, N, K, s, gd, reduce);
     }
     src.base[0] = reinterpret_cast<const uint8_t *>(w->q8_qs);
     src.base[1] = reinterpret_cast<const uint8_t *>(w->q8_d);
-    return launch_math<MathQ8_0>(ctx, src, x, out, N, K, s, gd);
+    return launch_math<MathQ8_0>(ctx, src, x, out, N, K, s, gd, reduce);
 }

@@ -174,6 +174,7 @@ internal static unsafe partial class Native
     [LibraryImport(Lib)] internal static partial int smc_gather_set_wait_ns(nint ctx, nint gather, ulong ns);
     [LibraryImport(Lib)] internal static partial int smc_gather_buffer(nint ctx, nint gather, out nint dBuf);
     [LibraryImport(Lib)] internal static partial int smc_qmatmul_gather_dev(nint ctx, nint gather, nint dIn, nint weightLocal, int m, int mode, nint stream);
+    [LibraryImport(Lib)] internal static partial int smc_qmatmul_reduce_dev(nint ctx, nint gather, nint dIn, nint dUp, nint weightLocal, int m, int mode, nint stream);
     [LibraryImport(Lib)] internal static partial int smc_gather_exchange_dev(nint ctx, nint gather, nuint count, nint stream);
     [LibraryImport(Lib)] internal static partial int smc_gather_destroy(nint ctx, nint gather);
 

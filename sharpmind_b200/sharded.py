@@ -9,8 +9,13 @@ multiple of the format's block size, otherwise the slice would start inside a bl
 The fused gate||up matrix is split per half (each rank holds its gate rows followed by its up rows)
 so that SwiGLU can run on local data; `gather_fused` restores the [gate | up] column order.
 
-The reference has no multi-device path (single process, single accelerator); this is the exchange
-step the row-split adds, and the only collective on the path.
+A feed-forward block needs only ONE exchange when its second matrix is split along K instead (`KSplit`):
+gate||up by rows with a split that follows whole K-steps of the down projection, SwiGLU on local data, then
+rank g multiplies its slice of the activation row by columns [k0_g, k1_g) of every row of `down` and the
+partial sums of all ranks are added in rank order (`PeerGather.matmul_reduce`, inside the producing kernel).
+
+The reference has no multi-device path (single process, single accelerator); these are the exchange
+steps the split adds, and the only collectives on the path.
 """
 from __future__ import annotations
 
@@ -64,6 +69,96 @@ class RowSplit:
         import torch
 
         return torch.cat([gate, up])
+
+
+# elements one step of the one-row kernel covers: K-slices are whole steps so that every rank's slice runs on it
+KSTEP_ELEMS = {8: 1024, 12: 2048, 14: 2048}
+
+
+@dataclass(frozen=True)
+class KSplit:
+    """Split of an inner dimension of `k` elements into whole steps of `step` elements, as even as whole steps allow:
+    with s = k / step steps over G ranks the first s % G ranks take one step more.  (28672 columns of a Q4_K / Q6_K
+    matrix are 14 steps: 7 + 7 over two ranks, 4 + 4 + 3 + 3 over four, 2 x 6 + 1 x 2 over eight.)"""
+    world: int
+    rank: int
+    step: int = 2048
+
+    def bounds(self, k: int) -> list[int]:
+        if k % self.step:
+            raise ValueError(f"K = {k} is not a whole number of {self.step}-element steps")
+        steps = k // self.step
+        if steps < self.world:
+            raise ValueError(f"{steps} steps cannot be split over {self.world} ranks")
+        base, extra = divmod(steps, self.world)
+        b = [0]
+        for r in range(self.world):
+            b.append(b[-1] + (base + (1 if r < extra else 0)) * self.step)
+        return b
+
+    def k_range(self, k: int, rank: int | None = None) -> tuple[int, int]:
+        b = self.bounds(k)
+        r = self.rank if rank is None else rank
+        return b[r], b[r + 1]
+
+    def slice_columns_raw(self, raw, dtype: int, n: int, k: int, rank: int | None = None):
+        """Columns [k0, k1) of every row of a GGUF-layout [n, k] tensor as a contiguous [n, k1 - k0] tensor."""
+        be = BLOCK_ELEMS[int(dtype)]
+        k0, k1 = self.k_range(k, rank)
+        per_row = raw.shape[0] // n
+        bb = per_row * be // k  # bytes per block
+        if per_row * n != raw.shape[0] or bb * (k // be) != per_row:
+            raise ValueError("tensor bytes are not whole rows of whole blocks")
+        rows = raw.reshape(n, per_row)[:, k0 // be * bb:k1 // be * bb]
+        import numpy as np
+
+        if isinstance(raw, np.ndarray):
+            return np.ascontiguousarray(rows).reshape(-1)
+        return rows.contiguous().reshape(-1)
+
+    def slice_fused_rows_raw(self, raw, dtype: int, n_half: int, k: int, rank: int | None = None):
+        """gate||up [2 * n_half, k] split by ROWS the way this split cuts the `n_half` inner elements of the down
+        projection: this rank's gate rows followed by its up rows."""
+        f0, f1 = self.k_range(n_half, rank)
+        per_row = raw.shape[0] // (2 * n_half)
+        gate = raw[f0 * per_row:f1 * per_row]
+        up = raw[(n_half + f0) * per_row:(n_half + f1) * per_row]
+        import numpy as np
+
+        if isinstance(raw, np.ndarray):
+            return np.concatenate([gate, up])
+        import torch
+
+        return torch.cat([gate, up])
+
+
+class ShardedFfn:
+    """One gated feed-forward block over G ranks with a single exchange: y = down(SiLU(gate(x)) * up(x)).
+
+    `gate_up(x) -> [M, 2 * F_local]` and `down_partial(act) -> [M, H]` are the local matmuls on this rank's slices
+    (injected, as for ShardedLinear); `dist.all_reduce` stands in for the in-kernel exchange on backends without peer
+    memory (gloo on CPU).  The product path is PeerGather.matmul_reduce."""
+
+    def __init__(self, split: KSplit, gate_up, down_partial, dist=None):
+        self.split, self.gate_up, self.down_partial, self.dist = split, gate_up, down_partial, dist
+
+    def forward(self, x):
+        import torch
+
+        gu = self.gate_up(x)
+        f = gu.shape[-1] // 2
+        g, u = gu[..., :f], gu[..., f:]
+        act = g / (1.0 + torch.exp(-g)) * u
+        part = self.down_partial(act)
+        if self.split.world == 1:
+            return part
+        # rank-ordered sum: gather the partials and add them 0, 1, ..., G - 1 (what the kernel's tail does)
+        parts = [torch.empty_like(part) for _ in range(self.split.world)]
+        self.dist.all_gather(parts, part.contiguous())
+        out = parts[0].clone()
+        for p in parts[1:]:
+            out += p
+        return out
 
 
 class ShardedLinear:
@@ -161,6 +256,15 @@ class PeerGather:
         self.ctx.check(self.ctx.lib.smc_qmatmul_gather_dev(self.ctx.h, self.h, x.data_ptr(), w_local.handle, m,
                                                            int(mode), self._stream()))
         return self.buffer()[: self.split.world * m * w_local.N].view(self.split.world, m, w_local.N)
+
+    def matmul_reduce(self, x, w_local, mode: int, up=None):
+        """K-split matmul: `w_local` holds this rank's columns of every row, `x` the matching slice of the activation
+        row(s) (or, with `up`, the local gate slice: the activation is SiLU(x) * up).  Returns a [M, N] view of the
+        receive buffer holding the sum of all ranks' partial products in rank order, identical on every rank."""
+        m = x.shape[0] if x.dim() > 1 else 1
+        self.ctx.check(self.ctx.lib.smc_qmatmul_reduce_dev(self.ctx.h, self.h, x.data_ptr(), None if up is None else up.data_ptr(),
+                                                           w_local.handle, m, int(mode), self._stream()))
+        return self.buffer()[: m * w_local.N].view(m, w_local.N)
 
     def exchange(self, count: int):
         self.ctx.check(self.ctx.lib.smc_gather_exchange_dev(self.ctx.h, self.h, int(count), self._stream()))

@@ -4,6 +4,11 @@ Every rank quantises the same seeded matrix on its own GPU, keeps its row slice,
 matmul with the in-kernel peer exchange reproduces the unsplit matmul of the same library bit for bit (each
 output row is computed by the same kernel arithmetic whichever rank owns it), for the fused one-row path, the
 several-row path, repeated exchanges, two objects in alternation, and a replayed CUDA graph.
+
+Then the one-exchange feed-forward block: gate||up split by rows, SwiGLU local, down split along K with the partial
+sums exchanged and added in rank order inside the producing kernel.  Every rank can form every rank's partial on its
+own GPU with the same kernel (a row's bits do not depend on the grid), so the sum is checked bit for bit against the
+rank-ordered sum of those, and within the parity bound against the unsplit block (summation order is all that differs).
 """
 import os
 import sys
@@ -16,7 +21,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 from sharpmind_b200 import ops, synth  # noqa: E402
-from sharpmind_b200.sharded import PeerGather, RowSplit, ShardedLinear  # noqa: E402
+from sharpmind_b200.sharded import KSplit, PeerGather, RowSplit, ShardedLinear  # noqa: E402
 
 
 def main():
@@ -79,6 +84,51 @@ def main():
             failures.append(f"dtype {dtype}: graph replay differs")
         dist.barrier()
         ga.close(), gb.close()
+    # ---- feed-forward block with one exchange (K-split down projection)
+    for down_dt, H, F in ((12, 2048, 16384), (14, 1024, 16384)):
+        ks = KSplit(world, rank)
+        wgu = dev.quantize_weights(12, torch.from_numpy(synth.normal("multi", f"ffn_gu{H}", (2 * F, H), 0.03)).cuda())
+        wdn = dev.quantize_weights(down_dt, torch.from_numpy(synth.normal("multi", f"ffn_dn{H}", (H, F), 0.03)).cuda())
+        full_gu, full_dn = ctx.register_dev(wgu, 12, 2 * F, H), ctx.register_dev(wdn, down_dt, H, F)
+        gu_parts, dn_parts = [], []
+        for r in range(world):
+            f0, f1 = ks.k_range(F, r)
+            gu_parts.append(ctx.register_dev(ks.slice_fused_rows_raw(wgu, 12, F, H, r).contiguous(), 12, 2 * (f1 - f0), H))
+            dn_parts.append(ctx.register_dev(ks.slice_columns_raw(wdn, down_dt, H, F, r), down_dt, H, f1 - f0))
+        red = PeerGather(ctx, split, world * 4 * H, dist)
+        for m in (1, 1, 1, 4):
+            x = torch.from_numpy(synth.normal("multi", f"ffn_x{H}_{m}", (m, H))).cuda()
+            # what every rank's partial is, formed locally, and their sum in rank order
+            want = None
+            for r in range(world):
+                fl = dn_parts[r].K
+                gu = dev.qmatmul(x, gu_parts[r], ops.Mode.ACT_Q8)
+                act = dev.swiglu(gu[:, :fl].contiguous(), gu[:, fl:].contiguous())
+                p = dev.qmatmul(act, dn_parts[r], ops.Mode.ACT_Q8)
+                want = p.clone() if want is None else want + p
+            fl = dn_parts[rank].K
+            gu = dev.qmatmul(x, gu_parts[rank], ops.Mode.ACT_Q8)
+            if m == 1:  # the SiLU-gate rides in the staging of the K-split matmul: one kernel per projection
+                got = red.matmul_reduce(gu[0, :fl], dn_parts[rank], ops.Mode.ACT_Q8, up=gu[0, fl:]).clone()
+            else:
+                act = dev.swiglu(gu[:, :fl].contiguous(), gu[:, fl:].contiguous())
+                got = red.matmul_reduce(act, dn_parts[rank], ops.Mode.ACT_Q8).clone()
+            if not torch.equal(got, want):
+                failures.append(f"ffn H {H} M {m}: differs from the rank-ordered sum by {(got - want).abs().max().item()}")
+            gu_f = dev.qmatmul(x, full_gu, ops.Mode.ACT_Q8)
+            unsplit = dev.qmatmul(dev.swiglu(gu_f[:, :F].contiguous(), gu_f[:, F:].contiguous()), full_dn, ops.Mode.ACT_Q8)
+            # each rank quantises its slice of the activation row with per-block scales, as the unsplit row does: the
+            # integer sums are the same, only the fp32 additions are grouped per rank
+            if (got - unsplit).abs().max().item() > 1e-5 * unsplit.abs().max().item():
+                failures.append(f"ffn H {H} M {m}: {((got - unsplit).abs().max() / unsplit.abs().max()).item():.2e} from the unsplit block")
+            # every rank must hold the same bits
+            mine = got.view(torch.int32).sum(dtype=torch.int64)
+            lo, hi = mine.clone(), mine.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN), dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            if lo.item() != hi.item():
+                failures.append(f"ffn H {H} M {m}: ranks hold different sums")
+        dist.barrier()
+        red.close()
     status = ctx.device_status()
     if status:
         failures.append(f"device status {status}")

@@ -55,7 +55,40 @@ def _worker(rank, world, port, results):
                             fused_halves=2)
         got = lin.forward(torch.from_numpy(x)).numpy()
         out["fused"] = bool(np.array_equal(got.view(np.uint32), full.view(np.uint32)))
-        # a rank that passes a wrong-sized slice is caught by the collective's shape check
+        # one exchange per feed-forward block: gate||up by rows, down split along K, partial sums added in rank order
+        from sharpmind_b200.sharded import KSplit, ShardedFfn
+
+        H, F, m = 256, 1024, 2
+        ks = KSplit(world, rank, step=256)
+        raw_gu = oracle.quantize(Q4_K, synth.normal("shard", "ffn_gu", (2 * F, H), 0.05))
+        raw_dn = oracle.quantize(Q6_K, synth.normal("shard", "ffn_dn", (H, F), 0.05))
+        x = synth.normal("shard", "ffn_x", (m, H))
+
+        def ffn_parts(r):
+            f0, f1 = ks.k_range(F, r)
+            gu_l = ks.slice_fused_rows_raw(raw_gu, Q4_K, F, H, r)
+            dn_l = ks.slice_columns_raw(raw_dn, Q6_K, H, F, r)
+            gu = oracle.qmatmul(Q4_K, x, gu_l, m, H, 2 * (f1 - f0))
+            act = oracle.swiglu(np.ascontiguousarray(gu[:, :f1 - f0]), np.ascontiguousarray(gu[:, f1 - f0:]))
+            return oracle.qmatmul(Q6_K, act, dn_l, m, f1 - f0, H)
+
+        f0, f1 = ks.k_range(F)
+        gu_local = ks.slice_fused_rows_raw(raw_gu, Q4_K, F, H)
+        dn_local = ks.slice_columns_raw(raw_dn, Q6_K, H, F)
+        ffn = ShardedFfn(ks,
+                         lambda xt: torch.from_numpy(oracle.qmatmul(Q4_K, xt.numpy(), gu_local, m, H, 2 * (f1 - f0))),
+                         lambda at: torch.from_numpy(oracle.qmatmul(Q6_K, np.ascontiguousarray(at.numpy()), dn_local, m, f1 - f0, H)),
+                         dist)
+        got = ffn.forward(torch.from_numpy(x)).numpy()
+        want_sum = ffn_parts(0)
+        for r in range(1, world):
+            want_sum = want_sum + ffn_parts(r)
+        gu = oracle.qmatmul(Q4_K, x, raw_gu, m, H, 2 * F)
+        full = oracle.qmatmul(Q6_K, oracle.swiglu(np.ascontiguousarray(gu[:, :F]), np.ascontiguousarray(gu[:, F:])), raw_dn, m, F, H)
+        # torch's SiLU-gate differs from the oracle's in the last place, so the sum is held to the parity bound, and
+        # the K-split differs from the unsplit product by summation order only
+        out["ffn_rank_order"] = bool(np.max(np.abs(got - want_sum)) <= 1e-5 * np.max(np.abs(full)))
+        out["ffn_vs_unsplit"] = bool(np.max(np.abs(got - full)) <= 1e-5 * np.max(np.abs(full)))
         results[rank] = out
     finally:
         dist.destroy_process_group()
@@ -84,6 +117,25 @@ def test_split_refuses_unaligned_slices():
     with pytest.raises(ValueError):
         s.check_block_aligned(Q8_0, 4, 48)
     assert RowSplit(4, 3).row_range(16) == (12, 16)
+
+
+def test_k_split_follows_whole_steps():
+    from sharpmind_b200.sharded import KSplit
+
+    assert KSplit(2, 0).bounds(28672) == [0, 14336, 28672]
+    assert KSplit(4, 0).bounds(28672) == [0, 8192, 16384, 22528, 28672]                   # 4 + 4 + 3 + 3 steps
+    assert [b // 2048 for b in KSplit(8, 0).bounds(28672)] == [0, 2, 4, 6, 8, 10, 12, 13, 14]
+    assert KSplit(8, 7).k_range(28672) == (26624, 28672)
+    with pytest.raises(ValueError):
+        KSplit(2, 0).bounds(3000)          # not whole steps
+    with pytest.raises(ValueError):
+        KSplit(8, 0).bounds(4 * 2048)      # fewer steps than ranks
+    # column slices of a GGUF tensor: rows keep their order, blocks [k0/256, k1/256) of each row
+    raw = np.arange(4 * 16 * 144, dtype=np.uint32).astype(np.uint8)  # 4 rows x 16 Q4_K blocks
+    ks = KSplit(2, 1, step=2048)
+    sl = ks.slice_columns_raw(raw, Q4_K, 4, 4096)
+    assert sl.shape[0] == 4 * 8 * 144
+    assert np.array_equal(sl.reshape(4, 8 * 144), raw.reshape(4, 16 * 144)[:, 8 * 144:])
 
 
 def test_assemble_single_rank_is_identity():
