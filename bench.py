@@ -87,6 +87,8 @@ def parse():
                     help="N > 1, one row: 'ffn' = gate||up by rows, SwiGLU local, down split along K with the partial sums "
                          "exchanged and added inside the kernel (one exchange per layer); 'rows' = every matrix by rows, "
                          "one exchange per matmul")
+    ap.add_argument("--no-exchange", action="store_true",
+                    help="diagnosis only (the line is marked invalid): N > 1 with --tp ffn, but the partial sums are not exchanged")
     ap.add_argument("--no-extras", action="store_true", help="skip everything but the headline line (and e2e)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--only", default="", help="run one kernel / section alone (see the module docstring)")
@@ -605,7 +607,10 @@ def run_ours(args):
     def gather_for(M, mi):
         # one receive buffer per (batch, matrix): the exchange runs inside the GEMV kernel over peer memory
         if (M, mi) not in gathers:
-            gathers[(M, mi)] = PeerGather(ctx, split, world * M * weights[0][mi].N, dist)
+            if args.no_exchange:
+                gathers[(M, mi)] = PeerGather(ctx, RowSplit(1, 0), world * M * weights[0][mi].N, None)
+            else:
+                gathers[(M, mi)] = PeerGather(ctx, split, world * M * weights[0][mi].N, dist)
         return gathers[(M, mi)]
 
     def one_matmul(state, M, layer, mi, md):
@@ -663,7 +668,7 @@ def run_ours(args):
         runner = lambda: step(state, M, md)  # noqa: E731
         graphed = False
         if peer:
-            for mi in range(len(mats)):
+            for mi in ([1] if tp_ffn else range(len(mats))):
                 gather_for(M, mi)  # created (and peers mapped) on every rank before anything is timed or captured
         if use_graph and (world == 1 or peer):
             runner = graph_of(torch, lambda: step(state, M, md)).replay
@@ -711,7 +716,7 @@ def run_ours(args):
     # its seed, computes it locally with the same kernel and compares the gathered buffer bit for bit (the one-row
     # kernel's sums do not depend on how rows are divided); every rank also checks its own chunk.
     parity = {"checked": False, "note": "single GPU: results are covered by the -m gpu parity tests"}
-    if world > 1 and tp_ffn:
+    if world > 1 and tp_ffn and not args.no_exchange:
         # layer 0 on every rank; rank 0 then regenerates EVERY rank's two slices from their seeds, forms each rank's
         # partial sums with the same kernels and adds them in rank order: the exchanged sums must equal that bit for
         # bit, and all ranks must hold the same bits
@@ -741,7 +746,7 @@ def run_ours(args):
                   "every rank's partial sums from the seeds of their slices and adds them in rank order; the exchanged sums "
                   "equal that bit for bit and every rank holds the same bits", "all_ranks_identical": same}
         del state
-    elif world > 1:
+    elif world > 1 and not args.no_exchange:
         state = make_state(M)
         ok_all, detail = True, []
         for mi, (name, dt, n, k) in enumerate(mats):
@@ -797,6 +802,8 @@ def run_ours(args):
         "clocks": clocks,
         "parity": parity,
     }
+    if args.no_exchange:
+        result["invalid"] = "diagnosis run: partial sums were not exchanged"
 
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region
     xs_h = [np.random.default_rng(17 + i).standard_normal((M, k), dtype=np.float32) for i, (_, _, _, k) in enumerate(mats)]

@@ -429,7 +429,9 @@ SMC_API int smc_gguf_read_f32(smc_ctx *ctx, const smc_gguf *g, int index, float 
  * raises smc_device_status (value 2): the kernel still ends, the context stays usable, the data of that exchange is
  * invalid.  Teardown: every rank finishes its device work and all ranks meet (a barrier of the host's choosing) BEFORE
  * any of them calls smc_gather_destroy, and likewise after a status 2 before the objects are reused or destroyed: a
- * peer's kernel may still be storing into this rank's buffer. */
+ * peer's kernel may still be storing into this rank's buffer. 
+ * Every rank of a world must create its object with the SAME capacity: a peer's buffer is addressed through this
+ * rank's own layout. */
 typedef struct smc_gather smc_gather;
 #define SMC_IPC_HANDLE_BYTES 64
 SMC_API int smc_gather_create(smc_ctx *ctx, int rank, int world, size_t capacity_floats, smc_gather **out);

@@ -225,8 +225,13 @@ class PeerGather:
             mine = (C.c_ubyte * 64)()
             ctx.check(ctx.lib.smc_gather_export(ctx.h, self.h, mine))
             handles = [None] * split.world
-            dist.all_gather_object(handles, bytes(mine))
-            blob = (C.c_ubyte * (64 * split.world)).from_buffer_copy(b"".join(handles))
+            dist.all_gather_object(handles, (self.capacity, bytes(mine)))
+            if any(cap != self.capacity for cap, _ in handles):
+                # a peer's packet areas are addressed through this rank's own capacity: all buffers must be laid out alike
+                ctx.lib.smc_gather_destroy(ctx.h, self.h)
+                self.h = None
+                raise ValueError(f"PeerGather: ranks asked for different capacities {[cap for cap, _ in handles]}")
+            blob = (C.c_ubyte * (64 * split.world)).from_buffer_copy(b"".join(h_ for _, h_ in handles))
             ctx.check(ctx.lib.smc_gather_connect(ctx.h, self.h, blob))
             dist.barrier()  # nobody starts an exchange before every rank has mapped its peers
         p = C.c_void_p()
