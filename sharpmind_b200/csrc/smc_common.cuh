@@ -87,6 +87,7 @@ struct smc_ctx {
     int tma_slots = 0, tma_ss = 0, tma_ctas = 0;  // one-row GEMV ring geometry and grid, 0 = built-in choice (smc_set_option)
     int tma_warps = 0;                            // warps per CTA of the one-row GEMV: 24 (one CTA per SM, default) or 12 (two)
     int tma_pre = 1;                              // stages requested before the activation loads are issued
+    int mt_ring = 1;                              // 2..32 rows, weights through the bulk-copy ring: 0 never, 1 Q4_K, 2 every format
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
     int argmax_rows = 0, argmax_chunks = 0;
     void *d_prefill = nullptr;         // activation image of the tensor-core matmul
@@ -143,6 +144,8 @@ int smc_qmatmul_dev_gather(smc_ctx *, const float *d_in, const smc_weight *, flo
 bool smc_prefill_supported(const smc_weight *, int M);
 int smc_launch_prefill_q4k(smc_ctx *, const float *x, const smc_weight *, float *out, int M, cudaStream_t s);
 bool smc_mma_supported(const smc_weight *, int M);
+bool smc_mt_supported(const smc_weight *, int M);
+int smc_launch_gemv_mt(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_mma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,
                         cudaStream_t s);

@@ -98,6 +98,55 @@ def test_results_do_not_depend_on_batch_size(oracle, cuda, dev):
         cuda.release(w)
 
 
+RING_SHAPES = [
+    (Q4_K, 304, 4096), (Q4_K, 48, 14336), (Q4_K, 16, 2048), (Q6_K, 64, 14336), (Q6_K, 160, 4096), (Q6_K, 2384, 2048),
+    (Q8_0, 272, 5120), (Q8_0, 64, 1024), (Q8_0, 4752, 1024),
+]
+
+
+@pytest.mark.parametrize("dtype,n,k", RING_SHAPES)
+def test_small_batch_ring_kernel(oracle, cuda, dev, dtype, n, k):
+    """2..32 rows with the weights streamed through the bulk-copy ring: every output within the SMC_ACT_Q8 bound of the
+    oracle fed the dequantised activations; the same bits whatever the grid (1, 5, 37 CTAs, one per SM), whatever the
+    batch size a row travels in, and with dependent launch off; within the bound of the kernel that fetches its
+    fragments from global memory (the two add a row's blocks in different orders)."""
+    from sharpmind_b200.ops import Mode
+
+    raw = make_weight(oracle, dtype, n, k, f"ring{dtype}_{n}_{k}")
+    w = cuda.register(raw, dtype, n, k)
+    xh = synth.normal("gpu", f"ringx{dtype}_{n}_{k}", (32, k))
+    x = to_dev(xh)
+    cuda.set_option("small_batch_ring", 2)  # every format through the ring (by default only Q4_K takes it)
+    try:
+        full = dev.qmatmul(x, w, Mode.ACT_Q8).cpu().numpy()
+        xq = oracle.quantize_rows_q8_0(xh, 32, k)
+        xhat = np.stack([oracle.dequantize(Q8_0, xq[r], k) for r in range(32)])
+        cols = sorted({c for c in (0, 15, 16, n // 2, n - 17, n - 1) if 0 <= c < n})
+        bound = row_norm_bound(oracle, dtype, raw, n, k, xhat)
+        for c in cols:
+            want = oracle.qmatmul(dtype, xhat, raw, 32, k, n, cols=(c, c + 1))[:, c]
+            assert np.all(np.abs(full[:, c].astype(np.float64) - want) <= bound[:, c]), (c, float(np.max(np.abs(full[:, c] - want) / bound[:, c])))
+        for m in (2, 7, 8, 9, 16, 17, 31):
+            part = dev.qmatmul(x[:m].contiguous(), w, Mode.ACT_Q8).cpu().numpy()
+            assert np.array_equal(bits(part), bits(full[:m])), m
+        for opts in ({"gemv_ctas": 1}, {"gemv_ctas": 5, "pdl": 0}, {"gemv_ctas": 37}):
+            for name, v in opts.items():
+                cuda.set_option(name, v)
+            try:
+                got = dev.qmatmul(x[:9].contiguous(), w, Mode.ACT_Q8).cpu().numpy()
+            finally:
+                for name in opts:
+                    cuda.set_option(name, {"pdl": 1}.get(name, 0))
+            assert np.array_equal(bits(got), bits(full[:9])), opts
+        cuda.set_option("small_batch_ring", 0)
+        other = dev.qmatmul(x, w, Mode.ACT_Q8).cpu().numpy()
+        assert np.all(np.abs(other.astype(np.float64) - full) <= 2 * bound), float(np.max(np.abs(other - full) / bound))
+    finally:
+        cuda.set_option("small_batch_ring", 1)
+        cuda.release(w)
+    assert cuda.device_status() == 0
+
+
 # One row against few long rows: row counts near the number of resident warps (some warps take one row, some two),
 # rows of many steps, and row counts that the warps do not divide.
 LONG_ROW_SHAPES = [
