@@ -80,4 +80,5 @@ __device__ __forceinline__ void smc_sts64(uint32_t a, uint2 v)
 {
     asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(v.x), "r"(v.y) : "memory");
 }
+
 #endif

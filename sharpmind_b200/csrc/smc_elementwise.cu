@@ -273,6 +273,41 @@ __global__ void __launch_bounds__(256) rope_kernel(float *__restrict__ x, int se
     }
 }
 
+// Four pairs per thread with 16-byte accesses (ropeDim % 8 == 0, 16-byte aligned rows): NEOX pairing rotates
+// (d .. d+3) against (d+half .. d+half+3), adjacent pairing the two float4 that hold pairs 4q .. 4q+3.  The arithmetic
+// per pair is that of rope_kernel (unfused products, one add), so both give the same bits.
+__global__ void __launch_bounds__(256) rope_vec_kernel(float *__restrict__ x, int seq, int heads, int headDim, int ropeDim,
+                                                       int posOffset, const float *__restrict__ cosT,
+                                                       const float *__restrict__ sinT, int neox)
+{
+    const int pairs = ropeDim / 2, quads = pairs / 4;
+    const long long total = (long long)seq * heads * quads;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+        const int q = (int)(t % quads);
+        const long long sh = t / quads;  // s * heads + h
+        const int s = (int)(sh / heads);
+        const float4 c = __ldg(reinterpret_cast<const float4 *>(cosT + (size_t)(posOffset + s) * pairs) + q);
+        const float4 sn = __ldg(reinterpret_cast<const float4 *>(sinT + (size_t)(posOffset + s) * pairs) + q);
+        float *p = x + sh * headDim;
+        if (neox) {
+            float4 *pa = reinterpret_cast<float4 *>(p) + q, *pb = reinterpret_cast<float4 *>(p + pairs) + q;
+            const float4 a = *pa, b = *pb;
+            *pa = make_float4(__fsub_rn(__fmul_rn(a.x, c.x), __fmul_rn(b.x, sn.x)), __fsub_rn(__fmul_rn(a.y, c.y), __fmul_rn(b.y, sn.y)),
+                              __fsub_rn(__fmul_rn(a.z, c.z), __fmul_rn(b.z, sn.z)), __fsub_rn(__fmul_rn(a.w, c.w), __fmul_rn(b.w, sn.w)));
+            *pb = make_float4(__fadd_rn(__fmul_rn(b.x, c.x), __fmul_rn(a.x, sn.x)), __fadd_rn(__fmul_rn(b.y, c.y), __fmul_rn(a.y, sn.y)),
+                              __fadd_rn(__fmul_rn(b.z, c.z), __fmul_rn(a.z, sn.z)), __fadd_rn(__fmul_rn(b.w, c.w), __fmul_rn(a.w, sn.w)));
+        } else {
+            float4 *pv = reinterpret_cast<float4 *>(p) + 2 * q;
+            const float4 u = pv[0], v = pv[1];  // pairs (u.x, u.y), (u.z, u.w), (v.x, v.y), (v.z, v.w)
+            pv[0] = make_float4(__fsub_rn(__fmul_rn(u.x, c.x), __fmul_rn(u.y, sn.x)), __fadd_rn(__fmul_rn(u.y, c.x), __fmul_rn(u.x, sn.x)),
+                                __fsub_rn(__fmul_rn(u.z, c.y), __fmul_rn(u.w, sn.y)), __fadd_rn(__fmul_rn(u.w, c.y), __fmul_rn(u.z, sn.y)));
+            pv[1] = make_float4(__fsub_rn(__fmul_rn(v.x, c.z), __fmul_rn(v.y, sn.z)), __fadd_rn(__fmul_rn(v.y, c.z), __fmul_rn(v.x, sn.z)),
+                                __fsub_rn(__fmul_rn(v.z, c.w), __fmul_rn(v.w, sn.w)), __fadd_rn(__fmul_rn(v.w, c.w), __fmul_rn(v.z, sn.w)));
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------- add / argmax / embed
 // LinearLayer.AddBiasInPlace (SharpMind.Model/Layers/Linearlayer.cs:154-163): out[r, j] += bias[j].
 __global__ void __launch_bounds__(256) add_bias_kernel(float *__restrict__ out, const float *__restrict__ bias, long long total, int n)
@@ -516,8 +551,14 @@ int smc_rope_dev(smc_ctx *ctx, float *d_x, int seq, int heads, int headDim, int 
         return smc_fail(ctx, SMC_E_INVALID, "rope: bad arguments");
     if (seq == 0) return SMC_OK;
     long long total = (long long)seq * heads * (ropeDim / 2);
-    rope_kernel<<<ew_grid(total, ctx->sm_count * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        d_x, seq, heads, headDim, ropeDim, posOffset, d_cos, d_sin, neox);
+    const bool vec = (ropeDim % 8) == 0 && (headDim % 4) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_cos) | reinterpret_cast<uintptr_t>(d_sin)) & 15) == 0;
+    if (vec)
+        rope_vec_kernel<<<ew_grid(total / 4, ctx->sm_count * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            d_x, seq, heads, headDim, ropeDim, posOffset, d_cos, d_sin, neox);
+    else
+        rope_kernel<<<ew_grid(total, ctx->sm_count * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            d_x, seq, heads, headDim, ropeDim, posOffset, d_cos, d_sin, neox);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
