@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload llama70b|llama8b] [--batch M] [--mode q8|f32] [--layers L]
-                    [--only gemv:<shape>[:<M>[:q8|q8pre|f32]] | decode[:qwen3|llama8b][:q8kv] | prompt | elementwise | prefill]
+                    [--only gemv:<shape>[:<M>[:q8|q8pre|f32[:ring]]] | decode[:qwen3|llama8b][:q8kv] | prompt | elementwise | prefill]
 
 Workload (default `llama70b`, BASELINE configs[4], the largest configuration that fits one GPU and the one the
 multi-GPU target is stated on): the Llama-3-70B-shaped FFN GEMV stack -- per layer the fused gate||up projection
@@ -513,6 +513,8 @@ def run_only(args):
     mode = ops.Mode.ACT_Q8 if args.mode == "q8" else ops.Mode.ACT_F32
     if parts[0] == "gemv":
         M = int(parts[2]) if len(parts) > 2 else 1
+        if len(parts) > 4 and parts[4] == "ring":  # 2..32 rows: weights through the bulk-copy ring (off by default)
+            ctx.set_option("small_batch_ring", 2)
         res = time_gemv_shape(torch, ctx, dev, ops, parts[1], M, parts[3] if len(parts) > 3 else "q8", peak, once=args.no_graph)
     elif parts[0] == "decode":
         cfg = dict(synth.LLAMA3_8B if len(parts) > 1 and parts[1] == "llama8b" else synth.QWEN3_0_6B)

@@ -80,7 +80,8 @@ gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ w
 #pragma unroll
     for (int j = 0; j < 4; ++j) arow[j] = wq + (size_t)min(r0 + (j >> 1) * 16 + g + (j & 1) * 8, N - 1) * K + 8 * tg;
     const __half *drow = wd + (size_t)min(r0 + lane, N - 1) * nb;
-    for (int t0 = 0; t0 < M; t0 += 8 * NT) {
+    {  // one pass of 8 * NT tokens per CTA: blockIdx.y picks the pass (a batch of more than 32 rows fills the grid with passes)
+        const int t0 = blockIdx.y * 8 * NT;
         const int8_t *brow[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) brow[t] = xq + (size_t)min(t0 + 8 * t + g, M - 1) * K + 8 * tg;
@@ -155,7 +156,8 @@ gemv_mma_q4_K_kernel(const uint8_t *__restrict__ raw, const int8_t *__restrict__
 #pragma unroll
     for (int j = 0; j < 4; ++j) arow[j] = raw + (size_t)min(r0 + (j >> 1) * 16 + g + (j & 1) * 8, N - 1) * row_bytes + 16 + 8 * tg;
     const uint8_t *hrow = raw + (size_t)min(r0 + lane, N - 1) * row_bytes;
-    for (int t0 = 0; t0 < M; t0 += 8 * NT) {
+    {  // one pass of 8 * NT tokens per CTA: blockIdx.y picks the pass (a batch of more than 32 rows fills the grid with passes)
+        const int t0 = blockIdx.y * 8 * NT;
         const int8_t *brow[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) brow[t] = xq + (size_t)min(t0 + 8 * t + g, M - 1) * K + 8 * tg;
@@ -284,7 +286,8 @@ gemv_mma_q6_K_kernel(const uint8_t *__restrict__ q6u, const int8_t *__restrict__
 #pragma unroll
     for (int j = 0; j < 4; ++j) rblk[j] = (uint32_t)min(r0 + (j >> 1) * 16 + g + (j & 1) * 8, N - 1) * (uint32_t)nsb;
     const uint32_t hblk = (uint32_t)min(r0 + lane, N - 1) * (uint32_t)nsb;
-    for (int t0 = 0; t0 < M; t0 += 8 * NT) {
+    {  // one pass of 8 * NT tokens per CTA: blockIdx.y picks the pass (a batch of more than 32 rows fills the grid with passes)
+        const int t0 = blockIdx.y * 8 * NT;
         const int8_t *brow[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) brow[t] = xq + (size_t)min(t0 + 8 * t + g, M - 1) * K + 4 * tg;
@@ -370,8 +373,8 @@ bool smc_mma_supported(const smc_weight *w, int M)
 int smc_launch_gemv_mma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *out, cudaStream_t s)
 {
     const int N = w->N, K = w->K, M = a->M;
-    const dim3 grid((N + MMA_ROWS - 1) / MMA_ROWS);
     const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+    const dim3 grid((N + MMA_ROWS - 1) / MMA_ROWS, (M + 8 * nt - 1) / (8 * nt));
     if (w->dtype == SMC_Q8_0) {
         if (nt == 1) smc_launch_dep(ctx->use_pdl, gemv_mma_q8_0_kernel<1>, grid, dim3(256), 0, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
                            (const int8_t *)a->q, (const float *)a->d, out, N, K, M);

@@ -116,7 +116,7 @@ def test_small_batch_ring_kernel(oracle, cuda, dev, dtype, n, k):
     w = cuda.register(raw, dtype, n, k)
     xh = synth.normal("gpu", f"ringx{dtype}_{n}_{k}", (32, k))
     x = to_dev(xh)
-    cuda.set_option("small_batch_ring", 2)  # every format through the ring (by default only Q4_K takes it)
+    cuda.set_option("small_batch_ring", 2)  # every format through the ring (off by default)
     try:
         full = dev.qmatmul(x, w, Mode.ACT_Q8).cpu().numpy()
         xq = oracle.quantize_rows_q8_0(xh, 32, k)
@@ -142,7 +142,7 @@ def test_small_batch_ring_kernel(oracle, cuda, dev, dtype, n, k):
         other = dev.qmatmul(x, w, Mode.ACT_Q8).cpu().numpy()
         assert np.all(np.abs(other.astype(np.float64) - full) <= 2 * bound), float(np.max(np.abs(other - full) / bound))
     finally:
-        cuda.set_option("small_batch_ring", 1)
+        cuda.set_option("small_batch_ring", 0)
         cuda.release(w)
     assert cuda.device_status() == 0
 
