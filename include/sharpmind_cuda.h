@@ -393,6 +393,17 @@ SMC_API int smc_qmatmul_addnorm_dev(smc_ctx *ctx, const float *d_x, const float 
 /* A new weight whose rows are the rows of parts[0], parts[1], ... in order (same dtype and K, all registered
  * with SMC_W_REPACK): how the decoder turns Wq / Wk / Wv into one matmul.  The parts stay valid. */
 SMC_API int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts, int count, smc_weight **out);
+/* The gate and up projections of a gated feed-forward block (FfnKernels.Gated, Layers/Ffn/FfnKernels.cs:35-59) woven
+ * into one matrix [2 * ffn, hidden] with row 2i = gate row i and row 2i + 1 = up row i, for smc_qmatmul_swiglu_pairs_dev.
+ * Both weights registered with SMC_W_REPACK, same format and shape; Q6_K rows must be whole 2048-element units. */
+SMC_API int smc_weight_interleave_rows(smc_ctx *ctx, const smc_weight *gate, const smc_weight *up, smc_weight **out);
+/* One activation row through an interleaved gate / up matrix with the activation in the matmul's epilogue:
+ * d_act[i] = SiLU(w[2i] . x) * (w[2i + 1] . x), i < N / 2, in the arithmetic of smc_qmatmul_dev(SMC_ACT_Q8) followed by
+ * smc_swiglu_dev (same bits).  The block's second matmul then stages a plain row: with the SiLU-gate in ITS staging
+ * (smc_qmatmul_swiglu_dev) every SM recomputes SiLU over the whole row, which costs more than the memory it saves once
+ * the row is long (6.4 us for 14 336 elements, measured).  Shapes the one-row bulk-copy kernel takes; else
+ * SMC_E_UNSUPPORTED. */
+SMC_API int smc_qmatmul_swiglu_pairs_dev(smc_ctx *ctx, const float *d_x, const smc_weight *w_interleaved, float *d_act, void *stream);
 
 /* ---- GGUF files to device weights -------------------------------------------------------------
  * GgufLoader (SharpMind.Model/Format/GgufLoader.cs): LoadMeta's header parse (:124-176) and LoadSingleTensor's copy of

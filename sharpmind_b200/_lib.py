@@ -109,6 +109,8 @@ SIGNATURES = {
     "smc_decode_step": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "smc_forward_last_logits": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "smc_qmatmul_reduce_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "smc_weight_interleave_rows": (c_int, [c_void_p, c_void_p, c_void_p, _pp]),
+    "smc_qmatmul_swiglu_pairs_dev": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "smc_dev_alloc": (c_int, [c_void_p, C.c_size_t, C.POINTER(c_void_p)]),
     "smc_dev_free": (c_int, [c_void_p, c_void_p]),
     "smc_copy_to_device": (c_int, [c_void_p, c_void_p, c_void_p, C.c_size_t, c_void_p]),

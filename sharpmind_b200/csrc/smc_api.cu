@@ -587,6 +587,66 @@ int smc_weight_concat_rows(smc_ctx *ctx, const smc_weight *const *parts, int cou
     return SMC_OK;
 }
 
+int smc_weight_interleave_rows(smc_ctx *ctx, const smc_weight *a, const smc_weight *b, smc_weight **out)
+{
+    if (!ctx || !a || !b || !out) return smc_fail(ctx, SMC_E_INVALID, "weight_interleave: bad arguments");
+    if (a->dtype != b->dtype || a->K != b->K || a->N != b->N)
+        return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "weight_interleave: the two weights differ in dtype or shape");
+    if (!a->fast || !b->fast) return smc_fail(ctx, SMC_E_UNSUPPORTED, "weight_interleave: weights must be registered with SMC_W_REPACK");
+    const int dtype = a->dtype, K = a->K, N = a->N;
+    if (dtype == SMC_Q6_K && K % 2048) return smc_fail(ctx, SMC_E_UNSUPPORTED, "weight_interleave: Q6_K rows must be whole 2048-element units");
+    if (dtype != SMC_Q8_0 && K % 256) return smc_fail(ctx, SMC_E_UNSUPPORTED, "weight_interleave: rows must be whole blocks");
+    if (2LL * N > INT32_MAX) return smc_fail(ctx, SMC_E_RANGE, "weight_interleave: too many rows");
+    const bool raw = a->d_raw && b->d_raw;
+    SMC_CUDA(ctx, cudaSetDevice(ctx->device));
+    smc_weight *w = new smc_weight();
+    w->dtype = dtype, w->N = 2 * N, w->K = K, w->flags = SMC_W_REPACK | (raw ? SMC_W_KEEP_RAW : 0), w->fast = true;
+    w->raw_bytes = (size_t)smc_raw_tensor_bytes(dtype, 2 * N, K);
+    cudaError_t e = cudaSuccess;
+    // row 2i of the result = row i of a, row 2i + 1 = row i of b, for every array of the compute layout
+    auto weave = [&](auto smc_weight::*field, size_t per_row) {
+        using T = std::remove_reference_t<decltype(w->*field)>;
+        if (e != cudaSuccess || per_row == 0) return;
+        uint8_t *dst = nullptr;
+        e = cudaMalloc(&dst, per_row * 2 * (size_t)N);
+        if (e != cudaSuccess) return;
+        w->*field = reinterpret_cast<T>(dst);
+        e = cudaMemcpy2DAsync(dst, 2 * per_row, reinterpret_cast<const uint8_t *>(a->*field), per_row, per_row, (size_t)N,
+                              cudaMemcpyDeviceToDevice, ctx->stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(dst + per_row, 2 * per_row, reinterpret_cast<const uint8_t *>(b->*field), per_row, per_row, (size_t)N,
+                                  cudaMemcpyDeviceToDevice, ctx->stream);
+    };
+    if (raw) weave(&smc_weight::d_raw, (size_t)smc_raw_tensor_bytes(dtype, 1, K));
+    if (dtype == SMC_Q8_0) {
+        weave(&smc_weight::q8_qs, (size_t)K);
+        weave(&smc_weight::q8_d, (size_t)K / 32 * 2);
+    } else if (dtype == SMC_Q6_K) {
+        weave(&smc_weight::q6u, (size_t)K / 2048 * SMC_Q6U_BYTES);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        free_weight(w);
+        return smc_fail(ctx, SMC_E_CUDA, "weight_interleave: %s", cudaGetErrorString(e));
+    }
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        ctx->by_host[static_cast<const void *>(w)] = w;  // no host bytes: the handle is its own key
+    }
+    *out = w;
+    return SMC_OK;
+}
+
+int smc_qmatmul_swiglu_pairs_dev(smc_ctx *ctx, const float *d_x, const smc_weight *w, float *d_act, void *stream)
+{
+    if (!ctx || !d_x || !w || !d_act) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_swiglu_pairs: bad arguments");
+    if (reinterpret_cast<uintptr_t>(d_x) & 15) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_swiglu_pairs: the activation row must be 16-byte aligned");
+    if (w->N & 1) return smc_fail(ctx, SMC_E_SIZE_MISMATCH, "qmatmul_swiglu_pairs: the interleaved matrix has an odd row count");
+    int rc = one_row_fusable(ctx, w, "qmatmul_swiglu_pairs", 65536);
+    if (rc) return rc;
+    return smc_launch_gemv_tma_any(ctx, nullptr, d_x, nullptr, nullptr, w, d_act, nullptr, false, true, static_cast<cudaStream_t>(stream));
+}
+
 int smc_qmatmul_tc_dev(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, void *stream)
 {
     if (!ctx || !d_in || !w || !d_out || M < 0) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_tc: bad arguments");

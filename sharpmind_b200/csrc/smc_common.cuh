@@ -133,7 +133,7 @@ struct smc_norm_prologue {
 int smc_launch_gemv_tma_full(smc_ctx *, const smc_q8act *, const float *xf, const float *xu, const smc_norm_prologue *,
                              const smc_weight *, float *out, const smc_gather_dev *, cudaStream_t s);
 int smc_launch_gemv_tma_any(smc_ctx *, const smc_q8act *, const float *xf, const float *xu, const smc_norm_prologue *,
-                            const smc_weight *, float *out, const smc_gather_dev *, bool reduce, cudaStream_t);
+                            const smc_weight *, float *out, const smc_gather_dev *, bool reduce, bool pairs, cudaStream_t);
 int smc_launch_gemv_tma_addnorm(smc_ctx *, const float *x, const smc_norm_prologue *, const smc_weight *, float *out,
                                 cudaStream_t s);
 int smc_launch_gemv_tma_swiglu(smc_ctx *, const float *gate, const float *up, const smc_weight *, float *out, cudaStream_t s);

@@ -252,7 +252,7 @@ int smc_qmatmul_reduce_dev(smc_ctx *ctx, smc_gather *g, const float *d_in, const
     // one row through the bulk-copy kernel: partial sums leave as packets from the lanes that finish them, and the
     // kernel's tail adds the packets of all ranks
     if (M == 1 && mode == SMC_ACT_Q8 && smc_tma_supported(w, 1) && !((reinterpret_cast<uintptr_t>(d_in)) & 15))
-        return smc_launch_gemv_tma_any(ctx, nullptr, d_in, d_up, nullptr, w, nullptr, g->d_view, true, s);
+        return smc_launch_gemv_tma_any(ctx, nullptr, d_in, d_up, nullptr, w, nullptr, g->d_view, true, false, s);
     // any other shape: partial sums into this rank's chunk, all chunks gathered, then added in the same order
     int rc = smc_qmatmul_dev(ctx, d_in, w, smc_gather_local_chunk(g, count), M, mode, stream);
     if (rc) return rc;

@@ -545,13 +545,19 @@ struct MathQ8_0 {
 };
 
 // ------------------------------------------------------------------------------------------------
-template <class Math, int SS, bool GATHER>
+// MODE 0: out[row] = sum.  MODE 1: the same, and the slice is exchanged with the peers (gather, or partial sums added in
+// rank order).  MODE 2: the matrix holds gate and up rows interleaved (row 2i = gate i, row 2i + 1 = up i) and the
+// kernel writes out[i] = SiLU(sum(2i)) * sum(2i + 1) (FfnKernels.Gated's activation, Layers/Ffn/FfnKernels.cs:35-59):
+// a CTA owns whole pairs, parks its row sums in shared memory and forms the products when its rows are done, so the
+// down projection stages a plain row instead of every SM recomputing SiLU over the whole row.
+template <class Math, int SS, int MODE>
 __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XPtrs xg, float *__restrict__ out, int N, int K,
                                                                     int slots, int tune, int *__restrict__ status,
                                                                     const smc_gather_dev *gd)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t SLOT = (Math::STEP_BYTES * SS + 127u) & ~127u;
+    constexpr bool GATHER = MODE == 1, PAIRS = MODE == 2;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nw = blockDim.x >> 5;  // warps of this CTA
 
@@ -567,8 +573,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
     // this CTA's rows, and this warp's piece [s0, s1) of their steps
     const int spr = K / Math::STEP_ELEMS;  // steps per row
     const int G = gridDim.x, cta = blockIdx.x;
-    const int rbase = N / G, rrem = N - rbase * G;
-    const int R0 = cta * rbase + min(cta, rrem), nrows = rbase + (cta < rrem ? 1 : 0);
+    constexpr int RU = PAIRS ? 2 : 1;  // rows are dealt out in units of one row, or of one (gate, up) pair
+    const int rbase = (N / RU) / G, rrem = N / RU - rbase * G;
+    const int R0 = RU * (cta * rbase + min(cta, rrem)), nrows = RU * (rbase + (cta < rrem ? 1 : 0));
+    const uint32_t srow = hbar + nw * 8u;  // PAIRS: this CTA's row sums, RU * (rbase + 1) floats
     const int T = nrows * spr;
     const int Wa = T < nw ? T : nw;  // warps that get work
     int s0 = 0, s1 = 0;
@@ -664,7 +672,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
                     math.template step<SS>(saddr, i, part, sbase, K, acc);
                     if (++part == spr) {
                         const float v = warp_sum32(acc);  // every lane holds the sum
-                        if (lane == 0 && !greduce) out[row] = v;
+                        if (lane == 0) {
+                            if (PAIRS) sts32(srow + 4u * (uint32_t)(row - R0), __float_as_uint(v));
+                            else if (!greduce) out[row] = v;
+                        }
                         // this rank's chunk starts at rank * N in every peer's packet area; lane p sends to peer p
                         if (GATHER) smc_gather_send_warp(gd, (size_t)N, (size_t)row, v, gtag, greduce);
                         acc = 0.f;
@@ -699,6 +710,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
             }
         }
     }
+    if (PAIRS) {  // every row sum of this CTA is in shared memory: out[i] = SiLU(gate i) * up i, the stand-alone kernel's arithmetic
+        __syncthreads();
+        for (int i = threadIdx.x; i < nrows / 2; i += blockDim.x) {
+            const float g = __uint_as_float(lds32(srow + 8u * i)), u = __uint_as_float(lds32(srow + 8u * i + 4u));
+            out[R0 / 2 + i] = __fdiv_rn(g, 1.0f + expf(-g)) * u;
+        }
+    }
     // rows done: unpack this CTA's stripe of the peers' slices as they arrive
     if (GATHER) {
         if (greduce) smc_gather_collect_reduce(gd, (size_t)N, blockIdx.x, gridDim.x, gtag);
@@ -709,23 +727,29 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
 
 template <class Math, int SS>
 void launch_one(smc_ctx *ctx, dim3 grid, int nw, size_t smem, cudaStream_t s, const StepSrc &src, const XPtrs &x, float *out, int N,
-                int K, int slots, const smc_gather_dev *gd, bool reduce)
+                int K, int slots, const smc_gather_dev *gd, bool reduce, bool pairs)
 {
     const int tune = (ctx->tma_pre & 0xFF) | (reduce ? 0x100 : 0);
     if (gd) {
-        cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, true>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
+        cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, 1>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
                        tune, ctx->d_status, gd);
         return;
     }
-    cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, false>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
+    if (pairs) {
+        cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, 2>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
+                       tune, ctx->d_status, (const smc_gather_dev *)nullptr);
+        return;
+    }
+    cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, 0>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
                    tune, ctx->d_status, (const smc_gather_dev *)nullptr);
 }
 
 template <class Math>
 int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, int N, int K, cudaStream_t s,
-                const smc_gather_dev *gd, bool reduce)
+                const smc_gather_dev *gd, bool reduce, bool pairs)
 {
     // One CTA of 24 warps per SM: the activation row is fetched and quantised once per SM (with three CTAs of eight
     // warps each, 444 copies of a 14336-element fp32 row were half as many bytes into the SMs as the matrix itself).
@@ -746,14 +770,16 @@ int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, in
         else if (ss > 1) ss >>= 1;
         else break;
     }
-    const size_t smem = need(slots, ss);
-    if ((smem + 1024) * per_sm > 227 * 1024) return smc_fail(ctx, SMC_E_UNSUPPORTED, "K = %d needs %zu bytes of shared memory", K, smem);
     int ctas = ctx->tma_ctas ? ctx->tma_ctas : ctx->sm_count * per_sm;
-    if (ctas > N) ctas = N;
+    const int units = pairs ? N / 2 : N;  // what is dealt out to the CTAs: rows, or (gate, up) pairs
+    if (ctas > units) ctas = units;
+    // the pair form parks a CTA's row sums in shared memory behind the hand-over barriers
+    const size_t smem = need(slots, ss) + (pairs ? (size_t)8 * (units / ctas + 1) + 16 : 0);
+    if ((smem + 1024) * per_sm > 227 * 1024) return smc_fail(ctx, SMC_E_UNSUPPORTED, "K = %d needs %zu bytes of shared memory", K, smem);
     const dim3 grid(ctas);
-    if (ss == 4) launch_one<Math, 4>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce);
-    else if (ss == 2) launch_one<Math, 2>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce);
-    else launch_one<Math, 1>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce);
+    if (ss == 4) launch_one<Math, 4>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce, pairs);
+    else if (ss == 2) launch_one<Math, 2>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce, pairs);
+    else launch_one<Math, 1>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce, pairs);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
@@ -810,14 +836,16 @@ int smc_launch_gemv_tma_addnorm(smc_ctx *ctx, const float *x, const smc_norm_pro
 int smc_launch_gemv_tma_full(smc_ctx *ctx, const smc_q8act *a, const float *xf, const float *xu, const smc_norm_prologue *pro,
                              const smc_weight *w, float *out, const smc_gather_dev *gd, cudaStream_t s)
 {
-    return smc_launch_gemv_tma_any(ctx, a, xf, xu, pro, w, out, gd, false, s);
+    return smc_launch_gemv_tma_any(ctx, a, xf, xu, pro, w, out, gd, false, false, s);
 }
 
 // `reduce`: the matrix is a K-slice; the partial sums of all ranks are exchanged and added in rank order into the
 // dense buffer of `gd` (out is not written).
+// `pairs`: the matrix is gate / up rows interleaved and out [N / 2] receives SiLU(gate) * up (no exchange in this form).
 int smc_launch_gemv_tma_any(smc_ctx *ctx, const smc_q8act *a, const float *xf, const float *xu, const smc_norm_prologue *pro,
-                            const smc_weight *w, float *out, const smc_gather_dev *gd, bool reduce, cudaStream_t s)
+                            const smc_weight *w, float *out, const smc_gather_dev *gd, bool reduce, bool pairs, cudaStream_t s)
 {
+    if (pairs && (gd || (w->N & 1))) return smc_fail(ctx, SMC_E_INVALID, "one-row matmul: the pair form takes an even row count and no exchange");
     const int N = w->N, K = w->K;
     if (!xf && (!a || a->M != 1 || a->K != K)) return smc_fail(ctx, SMC_E_INVALID, "one-row matmul: the activation buffer must hold one row of %d", K);
     XPtrs x{};
@@ -827,13 +855,13 @@ int smc_launch_gemv_tma_any(smc_ctx *ctx, const smc_q8act *a, const float *xf, c
     StepSrc src{};
     if (w->dtype == SMC_Q4_K) {
         src.base[0] = w->d_raw;
-        return launch_math<MathQ4K>(ctx, src, x, out, N, K, s, gd, reduce);
+        return launch_math<MathQ4K>(ctx, src, x, out, N, K, s, gd, reduce, pairs);
     }
     if (w->dtype == SMC_Q6_K) {
         src.base[0] = w->q6u;
-        return launch_math<MathQ6K>(ctx, src, x, out, N, K, s, gd, reduce);
+        return launch_math<MathQ6K>(ctx, src, x, out, N, K, s, gd, reduce, pairs);
     }
     src.base[0] = reinterpret_cast<const uint8_t *>(w->q8_qs);
     src.base[1] = reinterpret_cast<const uint8_t *>(w->q8_d);
-    return launch_math<MathQ8_0>(ctx, src, x, out, N, K, s, gd, reduce);
+    return launch_math<MathQ8_0>(ctx, src, x, out, N, K, s, gd, reduce, pairs);
 }

@@ -66,6 +66,7 @@ internal static unsafe partial class Native
     [LibraryImport(Lib)] internal static partial int smc_weight_release(nint ctx, nint weight);
     [LibraryImport(Lib)] internal static partial int smc_weight_shape(nint weight, out int dtype, out int n, out int k);
     [LibraryImport(Lib)] internal static partial int smc_weight_concat_rows(nint ctx, nint* parts, int count, out nint joined);
+    [LibraryImport(Lib)] internal static partial int smc_weight_interleave_rows(nint ctx, nint gate, nint up, out nint woven);
 
     // ---- host-pointer slots (the reference's delegate signatures)
     [LibraryImport(Lib)] internal static partial int smc_qmatmul_host(nint ctx, float* input, byte* hostRaw, float* output,
@@ -115,6 +116,7 @@ internal static unsafe partial class Native
     [LibraryImport(Lib)] internal static partial int smc_kv_append_dev(nint ctx, nint dK, nint dV, nint dKCache, nint dVCache, int batch,
         int kvHeads, int headDim, int pos, int maxSeq, nint stream);
     [LibraryImport(Lib)] internal static partial int smc_qmatmul_swiglu_dev(nint ctx, nint dGate, nint dUp, nint weight, nint dOut, nint stream);
+    [LibraryImport(Lib)] internal static partial int smc_qmatmul_swiglu_pairs_dev(nint ctx, nint dX, nint weightInterleaved, nint dAct, nint stream);
     [LibraryImport(Lib)] internal static partial int smc_qmatmul_addnorm_dev(nint ctx, nint dX, nint dAdd, nint dNormW, float eps,
         nint dSum, nint weight, nint dOut, nint stream);
 

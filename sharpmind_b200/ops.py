@@ -329,6 +329,21 @@ class DeviceOps:
                                                 M, int(mode), self._stream()))
         return out
 
+    def interleave_rows(self, gate: Weight, up: Weight) -> Weight:
+        """gate and up [ffn, hidden] woven into one matrix [2 * ffn, hidden]: row 2i = gate i, row 2i + 1 = up i."""
+        h = C.c_void_p()
+        self.ctx.check(self.lib.smc_weight_interleave_rows(self.ctx.h, gate.handle, up.handle, C.byref(h)))
+        return Weight(h, gate.dtype, 2 * gate.N, gate.K)
+
+    def qmatmul_swiglu_pairs(self, x, w: Weight, out=None):
+        """One activation row through an interleaved gate / up matrix; returns SiLU(gate . x) * (up . x), [1, N / 2]."""
+        t = self.torch
+        if out is None:
+            out = t.empty((1, w.N // 2), dtype=t.float32, device=x.device)
+        self.ctx.check(self.lib.smc_qmatmul_swiglu_pairs_dev(self.ctx.h, self._chk(x, t.float32), w.handle, self._chk(out, t.float32),
+                                                            self._stream()))
+        return out
+
     def qmatmul_tc(self, x, w: Weight, out=None):
         """Prefill-sized matmul on the tensor cores (Q4_K, N % 128 == 0, K % 256 == 0)."""
         t = self.torch

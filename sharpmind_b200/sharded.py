@@ -116,14 +116,22 @@ class KSplit:
             return np.ascontiguousarray(rows).reshape(-1)
         return rows.contiguous().reshape(-1)
 
-    def slice_fused_rows_raw(self, raw, dtype: int, n_half: int, k: int, rank: int | None = None):
+    def slice_fused_rows_raw(self, raw, dtype: int, n_half: int, k: int, rank: int | None = None, interleave: bool = False):
         """gate||up [2 * n_half, k] split by ROWS the way this split cuts the `n_half` inner elements of the down
-        projection: this rank's gate rows followed by its up rows."""
+        projection: this rank's gate rows followed by its up rows, or (`interleave`) woven gate 0, up 0, gate 1, ...
+        for the matmul that applies the SiLU-gate in its epilogue."""
         f0, f1 = self.k_range(n_half, rank)
         per_row = raw.shape[0] // (2 * n_half)
         gate = raw[f0 * per_row:f1 * per_row]
         up = raw[(n_half + f0) * per_row:(n_half + f1) * per_row]
         import numpy as np
+
+        if interleave:
+            if isinstance(raw, np.ndarray):
+                return np.stack([gate.reshape(f1 - f0, per_row), up.reshape(f1 - f0, per_row)], axis=1).reshape(-1)
+            import torch
+
+            return torch.stack([gate.reshape(f1 - f0, per_row), up.reshape(f1 - f0, per_row)], dim=1).reshape(-1)
 
         if isinstance(raw, np.ndarray):
             return np.concatenate([gate, up])

@@ -94,6 +94,8 @@ def main():
         for r in range(world):
             f0, f1 = ks.k_range(F, r)
             gu_parts.append(ctx.register_dev(ks.slice_fused_rows_raw(wgu, 12, F, H, r).contiguous(), 12, 2 * (f1 - f0), H))
+            if r == rank:  # the same rows woven (gate i, up i) for the matmul with the SiLU-gate in its epilogue
+                gu_woven = ctx.register_dev(ks.slice_fused_rows_raw(wgu, 12, F, H, r, interleave=True).contiguous(), 12, 2 * (f1 - f0), H)
             dn_parts.append(ctx.register_dev(ks.slice_columns_raw(wdn, down_dt, H, F, r), down_dt, H, f1 - f0))
         red = PeerGather(ctx, split, world * 4 * H, dist)
         for m in (1, 1, 1, 4):
@@ -115,6 +117,11 @@ def main():
                 got = red.matmul_reduce(act, dn_parts[rank], ops.Mode.ACT_Q8).clone()
             if not torch.equal(got, want):
                 failures.append(f"ffn H {H} M {m}: differs from the rank-ordered sum by {(got - want).abs().max().item()}")
+            if m == 1:  # the other one-row form: SiLU-gate in the first matmul's epilogue, a plain row into the K-split matmul
+                act = dev.qmatmul_swiglu_pairs(x, gu_woven)
+                got2 = red.matmul_reduce(act, dn_parts[rank], ops.Mode.ACT_Q8).clone()
+                if not torch.equal(got2, want):
+                    failures.append(f"ffn H {H}: woven gate/up form differs by {(got2 - want).abs().max().item()}")
             gu_f = dev.qmatmul(x, full_gu, ops.Mode.ACT_Q8)
             unsplit = dev.qmatmul(dev.swiglu(gu_f[:, :F].contiguous(), gu_f[:, F:].contiguous()), full_dn, ops.Mode.ACT_Q8)
             # each rank quantises its slice of the activation row with per-block scales, as the unsplit row does: the

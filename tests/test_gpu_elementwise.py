@@ -349,3 +349,39 @@ def test_sampler_guards_and_repetition_penalty(oracle, cuda, dev):
     for i in range(3):
         want = oracle.repetition_penalty(base[i], ids[i], 1.3)
         assert np.array_equal(out[i].view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("dtype,ffn,k", [(Q4_K, 1184, 2048), (Q4_K, 7168, 4096), (Q6_K, 333, 2048), (Q8_0, 1536, 1024), (Q8_0, 5, 3072)])
+def test_gate_up_interleaved_with_the_activation_in_the_epilogue(oracle, cuda, dev, dtype, ffn, k):
+    """gate and up woven row by row, one launch gives SiLU(gate . x) * (up . x): the bits of the two matmuls followed by
+    the SwiGLU kernel, whatever the grid; the woven matrix itself is rows 2i = gate i, 2i + 1 = up i of every layout."""
+    import torch
+
+    from sharpmind_b200.ops import Mode
+
+    g_raw = oracle.quantize(dtype, synth.normal("gpue", f"pg{dtype}_{ffn}_{k}", (ffn, k), 0.02))
+    u_raw = oracle.quantize(dtype, synth.normal("gpue", f"pu{dtype}_{ffn}_{k}", (ffn, k), 0.02))
+    wg, wu = cuda.register(g_raw, dtype, ffn, k, keep_raw=True), cuda.register(u_raw, dtype, ffn, k, keep_raw=True)
+    woven = dev.interleave_rows(wg, wu)
+    x = to_dev(synth.normal("gpue", f"px{k}", (1, k)))
+    want = dev.swiglu(dev.qmatmul(x, wg, Mode.ACT_Q8), dev.qmatmul(x, wu, Mode.ACT_Q8))
+    got = dev.qmatmul_swiglu_pairs(x, woven)
+    assert torch.equal(got, want)
+    for ctas in (1 if ffn <= 2048 else 5, 7, 148):  # (one CTA parks all row sums in shared memory: small matrices only)
+        cuda.set_option("gemv_ctas", ctas)
+        try:
+            again = dev.qmatmul_swiglu_pairs(x, woven)
+        finally:
+            cuda.set_option("gemv_ctas", 0)
+        assert torch.equal(again, want), ctas
+    # the woven matrix as a plain matmul (reference order reads its GGUF copy): outputs alternate gate, up
+    both = dev.qmatmul(x, woven, Mode.REF_ORDER)
+    assert torch.equal(both[0, 0::2], dev.qmatmul(x, wg, Mode.REF_ORDER)[0]) and torch.equal(both[0, 1::2], dev.qmatmul(x, wu, Mode.REF_ORDER)[0])
+    # against the oracle: matmuls on the dequantised activation row, then the scalar SwiGLU
+    xq = oracle.quantize_rows_q8_0(x.cpu().numpy(), 1, k)
+    xhat = oracle.dequantize(Q8_0, xq[0], k)[None, :]
+    ref = oracle.swiglu(oracle.qmatmul(dtype, xhat, g_raw, 1, k, ffn), oracle.qmatmul(dtype, xhat, u_raw, 1, k, ffn))
+    assert np.max(np.abs(got.cpu().numpy() - ref)) <= 2e-5 * max(1.0, float(np.max(np.abs(ref))))
+    for w_ in (wg, wu, woven):
+        cuda.release(w_)
+    assert cuda.device_status() == 0
