@@ -466,6 +466,9 @@ int smc_launch_sdpa_prefill(smc_ctx *ctx, const float *q, const float *kc, const
 {
     if (hd != 64 && hd != 128) return smc_fail(ctx, SMC_E_UNSUPPORTED, "prefill attention needs headDim 64 or 128, got %d", hd);
     if (nh % nkv) return smc_fail(ctx, SMC_E_INVALID, "prefill attention: heads %d not a multiple of KV heads %d", nh, nkv);
+    // the contractions on the tensor cores (bf16 MMAs on three-way split operands: fp32-grade accuracy) unless switched off
+    if (ctx->attn_mma && smc_sdpa_prefill_mma_supported(nh, nkv, hd))
+        return smc_launch_sdpa_prefill_mma(ctx, q, kc, vc, out, T, nh, nkv, hd, pos0, maxSeq, scale, s);
     // query rows per warp: four, or two while that leaves fewer than three CTAs per SM (a CTA waits on its K/V
     // tile loads with nothing else to do, so the SM needs other CTAs to run meanwhile)
     auto go = [&](auto kernel, int R) {

@@ -87,6 +87,7 @@ struct smc_ctx {
     int tma_slots = 0, tma_ss = 0, tma_ctas = 0;  // one-row GEMV ring geometry and grid, 0 = built-in choice (smc_set_option)
     int tma_warps = 0;                            // warps per CTA of the one-row GEMV: 24 (one CTA per SM, default) or 12 (two)
     int tma_pre = 1;                              // stages requested before the activation loads are issued
+    int attn_mma = 1;                             // prompt attention on the tensor cores (0: the fp32 CUDA-core kernel)
     int mt_ring = 0;                              // 2..32 rows, weights through the bulk-copy ring: 0 never, 1 Q4_K, 2 every format
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
     int argmax_rows = 0, argmax_chunks = 0;
@@ -145,6 +146,9 @@ bool smc_prefill_supported(const smc_weight *, int M);
 int smc_launch_prefill_q4k(smc_ctx *, const float *x, const smc_weight *, float *out, int M, cudaStream_t s);
 bool smc_mma_supported(const smc_weight *, int M);
 bool smc_mt_supported(const smc_weight *, int M);
+bool smc_sdpa_prefill_mma_supported(int nh, int nkv, int hd);
+int smc_launch_sdpa_prefill_mma(smc_ctx *, const float *q, const float *kc, const float *vc, float *out, int T, int nh, int nkv, int hd,
+                                int pos0, int maxSeq, float scale, cudaStream_t s);
 int smc_launch_gemv_mt(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_mma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,

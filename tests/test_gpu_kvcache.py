@@ -133,3 +133,40 @@ def test_q8_cache_long_context_decode(oracle, cuda):
     want = _oracle_attention(oracle, ops.KVCache.Q8_0, q, np.ascontiguousarray(kc), np.ascontiguousarray(vc), n, scale)
     assert np.max(np.abs(got - want)) <= 1e-5 * np.max(np.abs(want))
     kv.Dispose()
+
+
+@pytest.mark.parametrize("hd,heads,kvh", [(128, 8, 4), (128, 6, 2), (64, 4, 4), (64, 8, 1)])
+def test_prompt_attention_on_tensor_cores(oracle, cuda, hd, heads, kvh):
+    """Causal attention of a chunk of query rows over an fp32 cache with both contractions as bf16 MMAs on operands split
+    three ways: within 1e-5 of the oracle's scalar flash attention (the bound of the fp32 kernel), for chunks that end
+    inside a 64-row tile, start after an earlier chunk, and for query-head groups of 1, 2, 3 and 8; and the fp32
+    CUDA-core kernel it replaces gives the same result to that bound."""
+    B, max_seq = 2, 320
+    kv = ops.KVCache(cuda, B, kvh, max_seq, hd, ops.KVCache.F32)
+    scale = 1.0 / np.sqrt(hd)
+    kc = np.zeros((B, kvh, max_seq, hd), np.float32)
+    vc = np.zeros_like(kc)
+    length = 0
+    for tag, s in (("p", 150), ("q", 77), ("r", 1), ("s", 64)):
+        k = synth.normal("kvmma", f"k{tag}{hd}", (B, s, kvh, hd))
+        v = synth.normal("kvmma", f"v{tag}{hd}", (B, s, kvh, hd))
+        if tag == "p":
+            k *= 4.0  # sharper softmax: scores of a few units
+        kv.Update(to_dev(k), to_dev(v))
+        kc[:, :, length:length + s] = k.transpose(0, 2, 1, 3)
+        vc[:, :, length:length + s] = v.transpose(0, 2, 1, 3)
+        length += s
+        q = synth.normal("kvmma", f"q{tag}{hd}", (B, s, heads, hd))
+        got = kv.attention(to_dev(q), scale).cpu().numpy()
+        want = _oracle_attention(oracle, ops.KVCache.F32, q, kc, vc, length, scale)
+        err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
+        assert err <= 1e-5, (tag, err)
+        if s > 1:
+            cuda.set_option("prompt_attention_mma", 0)
+            try:
+                old = kv.attention(to_dev(q), scale).cpu().numpy()
+            finally:
+                cuda.set_option("prompt_attention_mma", 1)
+            assert np.max(np.abs(old - got)) <= 2e-5 * np.max(np.abs(want))
+    kv.Dispose()
+    assert cuda.device_status() == 0
