@@ -81,6 +81,7 @@ def parse():
     ap.add_argument("--mode", default="q8", choices=["q8", "f32"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--chunk", type=int, default=1024, help="--only prompt: tokens per ForwardLastLogits call")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="N > 1: exchange inside the GEMV kernel over peer memory, or a library all-gather per matmul")
     ap.add_argument("--tp", default="ffn", choices=["ffn", "rows"],
@@ -527,7 +528,7 @@ def run_only(args):
         cfg = dict(synth.QWEN3_0_6B)
         if args.layers:
             cfg["n_layers"] = args.layers
-        res = {"prompt": time_prompt(torch, ctx, dev, cfg, 2048, 1024, mode)}
+        res = {"prompt": time_prompt(torch, ctx, dev, cfg, 2048, args.chunk, mode)}
     elif parts[0] == "elementwise":
         res = {"elementwise": elementwise_chain(torch, ctx, dev, peak, once=args.no_graph)}
     elif parts[0] == "prefill":

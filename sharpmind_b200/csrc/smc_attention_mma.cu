@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
     const int hl = warp >> 2, wq = warp & 3;          // head of the CTA's group, 16-row slice of the 64 rows
     const int h = blockIdx.y * HPC + hl, kvh = (blockIdx.y * HPC) / (nh / nkv);
-    const int t0 = blockIdx.x * QROWS;
+    const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * QROWS;  // later rows see more keys: they start first
     const int cta_len = pos0 + min(T, t0 + QROWS);    // keys any row of this CTA sees
     const float *kbase = kc + (size_t)kvh * maxSeq * HD, *vbase = vc + (size_t)kvh * maxSeq * HD;
 
@@ -106,34 +106,50 @@ __global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float
     const uint32_t bk_off = (uint32_t)(((lane & 7) + 8 * (lane >> 4)) * LDB + 16 * ((lane >> 3) & 1));   // K: [key][dim], two key tiles
     const uint32_t bv_off = (uint32_t)(((lane & 7) + 8 * ((lane >> 3) & 1)) * LDB + 16 * (lane >> 4));   // V: transposed, two dim tiles
 
-    for (int start = 0; start < cta_len; start += KT) {
-        __syncthreads();  // the previous tile has been consumed (and Q is in place before its first use)
-        for (int e = threadIdx.x; e < KT * (HD / 4); e += NTH) {
-            const int r = e / (HD / 4), c = e % (HD / 4);
-            float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+    // A tile's K and V rows are requested one iteration ahead into registers (the loads fly while the previous tile is
+    // multiplied), then split into their planes and stored once everybody has finished reading that previous tile.
+    constexpr int PF = KT * (HD / 4) / NTH;  // float4 pieces of K (and of V) per thread and tile
+    float4 pk[PF], pv[PF];
+    auto fetch = [&](int start) {
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+            const int e = threadIdx.x + i * NTH, r = e / (HD / 4), c = e % (HD / 4);
+            pk[i] = pv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (start + r < cta_len) {
-                kk = *reinterpret_cast<const float4 *>(kbase + (size_t)(start + r) * HD + 4 * c);
-                vv = *reinterpret_cast<const float4 *>(vbase + (size_t)(start + r) * HD + 4 * c);
+                pk[i] = *reinterpret_cast<const float4 *>(kbase + (size_t)(start + r) * HD + 4 * c);
+                pv[i] = *reinterpret_cast<const float4 *>(vbase + (size_t)(start + r) * HD + 4 * c);
             }
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+            const int e = threadIdx.x + i * NTH, r = e / (HD / 4), c = e % (HD / 4);
             __nv_bfloat16 p[3][4];
-            split3(kk.x, p[0][0], p[1][0], p[2][0]), split3(kk.y, p[0][1], p[1][1], p[2][1]);
-            split3(kk.z, p[0][2], p[1][2], p[2][2]), split3(kk.w, p[0][3], p[1][3], p[2][3]);
+            split3(pk[i].x, p[0][0], p[1][0], p[2][0]), split3(pk[i].y, p[0][1], p[1][1], p[2][1]);
+            split3(pk[i].z, p[0][2], p[1][2], p[2][2]), split3(pk[i].w, p[0][3], p[1][3], p[2][3]);
 #pragma unroll
             for (int pl = 0; pl < 3; ++pl)
                 *reinterpret_cast<uint2 *>(sk + pl * KPLANE + r * LDB + 8 * c) = make_uint2(pack2(p[pl][0], p[pl][1]), pack2(p[pl][2], p[pl][3]));
-            split3(vv.x, p[0][0], p[1][0], p[2][0]), split3(vv.y, p[0][1], p[1][1], p[2][1]);
-            split3(vv.z, p[0][2], p[1][2], p[2][2]), split3(vv.w, p[0][3], p[1][3], p[2][3]);
+            split3(pv[i].x, p[0][0], p[1][0], p[2][0]), split3(pv[i].y, p[0][1], p[1][1], p[2][1]);
+            split3(pv[i].z, p[0][2], p[1][2], p[2][2]), split3(pv[i].w, p[0][3], p[1][3], p[2][3]);
 #pragma unroll
             for (int pl = 0; pl < 3; ++pl)
                 *reinterpret_cast<uint2 *>(sv + pl * KPLANE + r * LDB + 8 * c) = make_uint2(pack2(p[pl][0], p[pl][1]), pack2(p[pl][2], p[pl][3]));
         }
+    };
+    fetch(0);
+    for (int start = 0; start < cta_len; start += KT) {
+        __syncthreads();  // the previous tile has been consumed (and Q is in place before its first use)
+        stash();
         __syncthreads();
+        if (start + KT < cta_len) fetch(start + KT);  // in flight under this tile's MMAs
         if (start >= warp_len) continue;  // warp uniform: every row's causal bound lies before the tile
 
         // ---- S = Q K^T for 16 rows x 32 keys
-        float s[KT / 8][4];
+        float s[KT / 8][4], s2[KT / 8][4];  // even and odd k-steps: two independent chains of dependent MMAs per key tile
 #pragma unroll
-        for (int n = 0; n < KT / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        for (int n = 0; n < KT / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = s2[n][0] = s2[n][1] = s2[n][2] = s2[n][3] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
             uint32_t ah[4], am[4], al[4];
@@ -147,10 +163,17 @@ __global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float
                 for (int pl = 0; pl < 3; ++pl) ldsm4(sk_a + pl * KPLANE + bk_off + np * 16 * LDB + 32 * ks, b[pl]);
                 const uint32_t b0a[3] = {b[0][0], b[1][0], b[2][0]}, b1a[3] = {b[0][1], b[1][1], b[2][1]};
                 const uint32_t b0b[3] = {b[0][2], b[1][2], b[2][2]}, b1b[3] = {b[0][3], b[1][3], b[2][3]};
-                mma6(s[2 * np], ah, am, al, b0a, b1a);
-                mma6(s[2 * np + 1], ah, am, al, b0b, b1b);
+                if (ks & 1) {
+                    mma6(s2[2 * np], ah, am, al, b0a, b1a);
+                    mma6(s2[2 * np + 1], ah, am, al, b0b, b1b);
+                } else {
+                    mma6(s[2 * np], ah, am, al, b0a, b1a);
+                    mma6(s[2 * np + 1], ah, am, al, b0b, b1b);
+                }
             }
         }
+#pragma unroll
+        for (int n = 0; n < KT / 8; ++n) s[n][0] += s2[n][0], s[n][1] += s2[n][1], s[n][2] += s2[n][2], s[n][3] += s2[n][3];
         // ---- online softmax: lane holds keys start + 8n + 2tg, + 1 of rows g (s[n][0..1]) and g + 8 (s[n][2..3])
         float tm0 = -INFINITY, tm1 = -INFINITY;
 #pragma unroll
