@@ -40,9 +40,9 @@ __device__ __forceinline__ uint2 ldg8(const void *p)
     return v;
 }
 
-// Adds the warps' partial tiles in warp order and stores out[t, r]; red is [NW warps][32 tokens][33].
-template <int NT, int NW = MMA_WARPS>
-__device__ __forceinline__ void reduce_and_store(float (*red)[32][33], const float (&acc)[2][NT][4], float *out, int N, int M,
+// Adds the warps' partial tiles in warp order and stores out[t, r]; red is [NW warps][TOK tokens][33], TOK >= 8 * NT.
+template <int NT, int NW = MMA_WARPS, int TOK = 32>
+__device__ __forceinline__ void reduce_and_store(float (*red)[TOK][33], const float (&acc)[2][NT][4], float *out, int N, int M,
                                                  int r0, int t0)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
@@ -66,11 +66,15 @@ __device__ __forceinline__ void reduce_and_store(float (*red)[32][33], const flo
 // ------------------------------------------------------------------------------------------ Q8_0
 // Planes: quants [N][K] int8, scales [N][K/32] fp16.  K % 128 == 0; a warp works on groups of four blocks.
 template <int NT>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, NT > 4 ? 1 : 2)
 gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ wd, const int8_t *__restrict__ xq,
                      const float *__restrict__ xd, float *__restrict__ out, int N, int K, int M)
 {
-    __shared__ float red[MMA_WARPS][32][33];
+    // NT token tiles of 8 per pass: 1, 2, 4 for up to 32 rows; 8 for prompt-sized batches (64 tokens share every weight
+    // fragment and scale, which halves the passes over the matrix)
+    constexpr int TOK = NT > 4 ? 64 : 32, XR = TOK / 32;
+    extern __shared__ __align__(16) float red_q8[];
+    float (*red)[TOK][33] = reinterpret_cast<float (*)[TOK][33]>(red_q8);
     smc_grid_dep_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
     const int r0 = blockIdx.x * MMA_ROWS;
@@ -85,7 +89,9 @@ gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ w
         const int8_t *brow[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) brow[t] = xq + (size_t)min(t0 + 8 * t + g, M - 1) * K + 8 * tg;
-        const float *xrow = xd + (size_t)min(t0 + lane, M - 1) * nb;
+        const float *xrow[XR];  // this lane's tokens: lane, and lane + 32 in a 64-token pass
+#pragma unroll
+        for (int x = 0; x < XR; ++x) xrow[x] = xd + (size_t)min(t0 + 32 * x + lane, M - 1) * nb;
         float acc[2][NT][4];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)
@@ -101,7 +107,9 @@ gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ w
 #pragma unroll
                 for (int j = 0; j < 4; ++j) aq[kb][j] = ldg8(arow[j] + (gi * 4 + kb) * 32);
             const uint2 dwp = *reinterpret_cast<const uint2 *>(drow + gi * 4);   // this lane's row, 4 blocks
-            const float4 dxp = *reinterpret_cast<const float4 *>(xrow + gi * 4);  // this lane's token, 4 blocks
+            float4 dxp[XR];                                                      // this lane's tokens, 4 blocks
+#pragma unroll
+            for (int x = 0; x < XR; ++x) dxp[x] = *reinterpret_cast<const float4 *>(xrow[x] + gi * 4);
 #pragma unroll
             for (int kb = 0; kb < 4; ++kb) {
                 const int koff = (gi * 4 + kb) * 32;
@@ -110,7 +118,9 @@ gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ w
 #pragma unroll
                 for (int t = 0; t < NT; ++t) b[t] = ldg8(brow[t] + koff);
                 const uint32_t dword = (kb & 2) ? dwp.y : dwp.x;
-                const float dxl = kb == 0 ? dxp.x : kb == 1 ? dxp.y : kb == 2 ? dxp.z : dxp.w;
+                float dxl[XR];
+#pragma unroll
+                for (int x = 0; x < XR; ++x) dxl[x] = kb == 0 ? dxp[x].x : kb == 1 ? dxp[x].y : kb == 2 ? dxp[x].z : dxp[x].w;
                 float dw[2][2];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -119,8 +129,8 @@ gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ w
                 }
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
-                    const float dx0 = __shfl_sync(0xffffffffu, dxl, 8 * t + 2 * tg);
-                    const float dx1 = __shfl_sync(0xffffffffu, dxl, 8 * t + 2 * tg + 1);
+                    const float dx0 = __shfl_sync(0xffffffffu, dxl[t >> 2], 8 * (t & 3) + 2 * tg);
+                    const float dx1 = __shfl_sync(0xffffffffu, dxl[t >> 2], 8 * (t & 3) + 2 * tg + 1);
 #pragma unroll
                     for (int mt = 0; mt < 2; ++mt) {
                         int c[4];
@@ -133,7 +143,7 @@ gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ w
                 }
             }
         }
-        reduce_and_store<NT>(red, acc, out, N, M, r0, t0);
+        reduce_and_store<NT, MMA_WARPS, TOK>(red, acc, out, N, M, r0, t0);
     }
 }
 
@@ -376,12 +386,19 @@ int smc_launch_gemv_mma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, f
     const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
     const dim3 grid((N + MMA_ROWS - 1) / MMA_ROWS, (M + 8 * nt - 1) / (8 * nt));
     if (w->dtype == SMC_Q8_0) {
-        if (nt == 1) smc_launch_dep(ctx->use_pdl, gemv_mma_q8_0_kernel<1>, grid, dim3(256), 0, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
+        // prompt-sized batches: passes of 64 tokens
+        const int nt8 = M >= 64 ? 8 : nt;
+        const dim3 g8((N + MMA_ROWS - 1) / MMA_ROWS, (M + 8 * nt8 - 1) / (8 * nt8));
+        auto go8 = [&](auto kernel, int tok) {
+            const size_t smem = (size_t)MMA_WARPS * tok * 33 * sizeof(float);
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            smc_launch_dep(ctx->use_pdl, kernel, g8, dim3(256), smem, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
                            (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
-        else if (nt == 2) smc_launch_dep(ctx->use_pdl, gemv_mma_q8_0_kernel<2>, grid, dim3(256), 0, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
-                           (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
-        else smc_launch_dep(ctx->use_pdl, gemv_mma_q8_0_kernel<4>, grid, dim3(256), 0, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
-                           (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
+        };
+        if (nt8 == 1) go8(gemv_mma_q8_0_kernel<1>, 32);
+        else if (nt8 == 2) go8(gemv_mma_q8_0_kernel<2>, 32);
+        else if (nt8 == 4) go8(gemv_mma_q8_0_kernel<4>, 32);
+        else go8(gemv_mma_q8_0_kernel<8>, 64);
     } else if (w->dtype == SMC_Q6_K) {
         // the warp count follows from K alone, so a row's bits depend neither on the batch nor on how the rows are
         // split across GPUs; long rows are where matrices of few rows (FFN down) need the extra warps per SM
