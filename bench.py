@@ -88,6 +88,9 @@ def parse():
                     help="N > 1, one row: 'ffn' = gate||up by rows, SwiGLU local, down split along K with the partial sums "
                          "exchanged and added inside the kernel (one exchange per layer); 'rows' = every matrix by rows, "
                          "one exchange per matmul")
+    ap.add_argument("--tp-pairs", action="store_true",
+                    help="--tp ffn: gate / up rows woven and the SiLU-gate in the first matmul's epilogue instead of the second's staging "
+                         "(pays only while the rank's slice of the row is long: 14 336 elements at N = 2)")
     ap.add_argument("--no-exchange", action="store_true",
                     help="diagnosis only (the line is marked invalid): N > 1 with --tp ffn, but the partial sums are not exchanged")
     ap.add_argument("--no-extras", action="store_true", help="skip everything but the headline line (and e2e)")
@@ -642,13 +645,17 @@ def run_ours(args):
         return outs[mi]
 
     def ffn_layer(state, layer, md, x=None):
-        """gate||up on this rank's rows with the SiLU-gate in its epilogue, then the K-split down projection whose tail
-        exchanges and adds the partial sums: two launches, one exchange.  Returns the [1, H] sums."""
+        """gate||up on this rank's rows, then the K-split down projection (the SiLU-gate in its staging, or with
+        --tp-pairs in the first matmul's epilogue) whose tail exchanges and adds the partial sums: two launches, one
+        exchange.  Returns the [1, H] sums."""
         xs, _, outs, _ = state
         fl = weights[layer][1].K
-        act = outs[0][:, :fl]  # gate||up rows are woven (gate i, up i): the SiLU-gate is the first matmul's epilogue
-        dev.qmatmul_swiglu_pairs(xs[0] if x is None else x, weights[layer][0], out=act)
-        return gather_for(1, 1).matmul_reduce(act, weights[layer][1], md)
+        if args.tp_pairs:  # gate||up rows woven (gate i, up i), the SiLU-gate in the first matmul's epilogue
+            act = outs[0][:, :fl]
+            dev.qmatmul_swiglu_pairs(xs[0] if x is None else x, weights[layer][0], out=act)
+            return gather_for(1, 1).matmul_reduce(act, weights[layer][1], md)
+        dev.qmatmul(xs[0] if x is None else x, weights[layer][0], md, out=outs[0])  # [gate rows | up rows]
+        return gather_for(1, 1).matmul_reduce(outs[0][0, :fl], weights[layer][1], md, up=outs[0][0, fl:])
 
     def step(state, M, md):
         for layer in range(L):
@@ -734,8 +741,11 @@ def run_ours(args):
                 (_, dt_g, n_g, k_g), (_, dt_d, n_d, k_d) = local_shapes(r)
                 wg = weights[0][0] if r == 0 else device_matrix(torch, dev, ctx, dt_g, n_g, k_g, seed_of(0, 0, r))
                 wd = weights[0][1] if r == 0 else device_matrix(torch, dev, ctx, dt_d, n_d, k_d, seed_of(0, 1, r))
-                gu = dev.qmatmul(state[0][0], wg, mode)  # rows woven: gate i, up i
-                part = dev.qmatmul(dev.swiglu(gu[:, 0::2].contiguous(), gu[:, 1::2].contiguous()), wd, mode)
+                gu = dev.qmatmul(state[0][0], wg, mode)
+                if args.tp_pairs:  # rows woven: gate i, up i
+                    part = dev.qmatmul(dev.swiglu(gu[:, 0::2].contiguous(), gu[:, 1::2].contiguous()), wd, mode)
+                else:
+                    part = dev.qmatmul(dev.swiglu(gu[:, :k_d].contiguous(), gu[:, k_d:].contiguous()), wd, mode)
                 want = part.clone() if want is None else want + part
                 if r:
                     ctx.release(wg), ctx.release(wd)
@@ -796,7 +806,7 @@ def run_ours(args):
                    "cuda_graph": graphed,
                    "parallelism": "single GPU" if world == 1 else (
                        f"tp{world}: gate||up by rows (whole K-steps of down: {[b // 2048 for b in ksplit.bounds(F)]}), SiLU-gate "
-                       f"in its epilogue, down split along K, partial sums exchanged and added in rank order inside the GEMV kernel over "
+                       f"local, down split along K, partial sums exchanged and added in rank order inside the GEMV kernel over "
                        f"NVLink peer memory: one exchange per layer" if tp_ffn else
                        f"row-split x{world}, slices exchanged by the GEMV kernel over NVLink peer memory" if peer
                        else f"row-split x{world} + NCCL all-gather")},
@@ -835,9 +845,9 @@ def run_ours(args):
                 pin_y.copy_(ffn_layer(st_e, layer, mode, dev_x0), non_blocking=True)
                 torch.cuda.current_stream().synchronize()  # the caller reads the block's output before its next call
 
-        api = ("per layer: pinned host row -> device, smc_qmatmul_swiglu_pairs_dev on the rank's woven gate / up rows, "
-               "smc_qmatmul_reduce_dev (K-split down, partial sums exchanged and added in the kernel), summed row -> pinned "
-               "host, stream synchronised")
+        api = ("per layer: pinned host row -> device, gate||up on the rank's rows, smc_qmatmul_reduce_dev (SiLU-gate in the "
+               "staging, K-split down, partial sums exchanged and added in the kernel), summed row -> pinned host, stream "
+               "synchronised")
     else:
         pin_x = [torch.from_numpy(x).pin_memory() for x in xs_h]
         dev_x = [torch.empty((M, k), device="cuda") for (_, _, _, k) in mats]

@@ -9,9 +9,8 @@
 // number of the running exchange is complete.  System-scope fences cost several microseconds each on this
 // platform (measured: a fence + flag protocol took 12 us per exchange, a plain peer copy 2 us), which is why
 // none is used.  Protocol for exchange number t = epoch + 1 (a counter in device memory, so a captured graph replays):
-//   1. output values are stored into the local dense chunk and, as packets tagged t, into packet area (t & 1) of
-//      every peer, in runs of consecutive packets per warp store (the memory system merges them into 128-byte
-//      writes: one 8-byte store per value and peer was tens of thousands of NVLink write packets per exchange);
+//   1. a thread that has produced an output value stores it into the local dense chunk and as a packet tagged t
+//      into packet area (t & 1) of every peer;
 //   2. when a CTA has finished its own rows it turns a stripe of the incoming packets of every peer into
 //      dense floats, polling each packet until its tag is t.  The kernel therefore completes when the whole
 //      gathered row is in local memory, and later launches on the stream just read it;
@@ -124,6 +123,17 @@ __device__ __forceinline__ bool smc_gather_wait_ready(const smc_gather_dev *g, u
 __device__ __forceinline__ unsigned long long *smc_gather_area(const smc_gather_dev *g, int r, unsigned tag)
 {
     return g->pkt[r] + (size_t)(tag & 1u) * g->capacity;
+}
+
+// Step 1 for a whole warp that holds `v` in every lane: lane p sends to peer p (`self`: to this rank as well, the
+// reduce form).
+__device__ __forceinline__ void smc_gather_send_warp(const smc_gather_dev *g, size_t count, size_t idx, float v, unsigned tag,
+                                                     bool self = false)
+{
+    const int lane = threadIdx.x & 31;
+    if (lane < g->world && (self || lane != g->rank))
+        smc_st_relaxed_sys64(smc_gather_area(g, lane, tag) + (size_t)g->rank * count + idx,
+                             ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v));
 }
 
 // Step 1: element `idx` of this rank's chunk of `count` floats.

@@ -576,7 +576,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
     constexpr int RU = PAIRS ? 2 : 1;  // rows are dealt out in units of one row, or of one (gate, up) pair
     const int rbase = (N / RU) / G, rrem = N / RU - rbase * G;
     const int R0 = RU * (cta * rbase + min(cta, rrem)), nrows = RU * (rbase + (cta < rrem ? 1 : 0));
-    const uint32_t srow = hbar + nw * 8u;  // MODE 1, 2: this CTA's row sums, RU * (rbase + 1) floats
+    const uint32_t srow = hbar + nw * 8u;  // PAIRS: this CTA's row sums, RU * (rbase + 1) floats
     const int T = nrows * spr;
     const int Wa = T < nw ? T : nw;  // warps that get work
     int s0 = 0, s1 = 0;
@@ -673,9 +673,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
                     if (++part == spr) {
                         const float v = warp_sum32(acc);  // every lane holds the sum
                         if (lane == 0) {
-                            if (MODE != 0) sts32(srow + 4u * (uint32_t)(row - R0), __float_as_uint(v));  // sent / combined below
-                            else out[row] = v;
+                            if (PAIRS) sts32(srow + 4u * (uint32_t)(row - R0), __float_as_uint(v));
+                            else if (!greduce) out[row] = v;
                         }
+                        // this rank's chunk starts at rank * N in every peer's packet area; lane p sends to peer p
+                        if (GATHER) smc_gather_send_warp(gd, (size_t)N, (size_t)row, v, gtag, greduce);
                         acc = 0.f;
                         part = 0;
                         ++row;
@@ -715,23 +717,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
             out[R0 / 2 + i] = __fdiv_rn(g, 1.0f + expf(-g)) * u;
         }
     }
-    // rows done.  This CTA's row sums leave as RUNS of packets: warp w takes peer w, w + warps, ... and its lanes store
-    // consecutive 8-byte packets, which the memory system merges into 128-byte writes.  (One 8-byte store per row and peer,
-    // issued as each row finished, was 57 k NVLink write packets per matmul and rank at eight ranks, and the exchange grew
-    // from 7 us at two ranks to 12 us at eight; the slice is a few hundred bytes per CTA and peer, so sending it at the
-    // end costs no overlap worth having.)
-    if (GATHER) {
-        __syncthreads();
-        if (!greduce)
-            for (int i = threadIdx.x; i < nrows; i += blockDim.x) out[R0 + i] = __uint_as_float(lds32(srow + 4u * i));
-        for (int p = warp; p < gd->world; p += nw) {
-            if (p == gd->rank && !greduce) continue;  // the reduce form posts to itself as well
-            unsigned long long *dst = smc_gather_area(gd, p, gtag) + (size_t)gd->rank * (size_t)N + (size_t)R0;
-            for (int i = lane; i < nrows; i += 32)
-                smc_st_relaxed_sys64(dst + i, ((unsigned long long)gtag << 32) | (unsigned long long)lds32(srow + 4u * i));
-        }
-    }
-    // unpack this CTA's stripe of the peers' slices as they arrive
+    // rows done: unpack this CTA's stripe of the peers' slices as they arrive
     if (GATHER) {
         if (greduce) smc_gather_collect_reduce(gd, (size_t)N, blockIdx.x, gridDim.x, gtag);
         else smc_gather_collect(gd, (size_t)N, blockIdx.x, gridDim.x, gtag);
@@ -787,8 +773,8 @@ int launch_math(smc_ctx *ctx, const StepSrc &src, const XPtrs &x, float *out, in
     int ctas = ctx->tma_ctas ? ctx->tma_ctas : ctx->sm_count * per_sm;
     const int units = pairs ? N / 2 : N;  // what is dealt out to the CTAs: rows, or (gate, up) pairs
     if (ctas > units) ctas = units;
-    // the pair and exchange forms park a CTA's row sums in shared memory behind the hand-over barriers
-    const size_t smem = need(slots, ss) + ((pairs || gd) ? (size_t)(pairs ? 8 : 4) * (units / ctas + 1) + 16 : 0);
+    // the pair form parks a CTA's row sums in shared memory behind the hand-over barriers
+    const size_t smem = need(slots, ss) + (pairs ? (size_t)8 * (units / ctas + 1) + 16 : 0);
     if ((smem + 1024) * per_sm > 227 * 1024) return smc_fail(ctx, SMC_E_UNSUPPORTED, "K = %d needs %zu bytes of shared memory", K, smem);
     const dim3 grid(ctas);
     if (ss == 4) launch_one<Math, 4>(ctx, grid, nw, smem, s, src, x, out, N, K, slots, gd, reduce, pairs);
