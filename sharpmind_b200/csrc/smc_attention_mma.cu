@@ -74,8 +74,9 @@ __global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float
     smc_grid_dep_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
     const int hl = warp >> 2, wq = warp & 3;          // head of the CTA's group, 16-row slice of the 64 rows
-    const int h = blockIdx.y * HPC + hl, kvh = (blockIdx.y * HPC) / (nh / nkv);
-    const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * QROWS;  // later rows see more keys: they start first
+    const int hg = blockIdx.x;                          // head group; the grid's fast index, so CTAs start heaviest tile first
+    const int h = hg * HPC + hl, kvh = (hg * HPC) / (nh / nkv);
+    const int t0 = (int)(gridDim.y - 1 - blockIdx.y) * QROWS;  // later rows see more keys: they start first
     const int cta_len = pos0 + min(T, t0 + QROWS);    // keys any row of this CTA sees
     const float *kbase = kc + (size_t)kvh * maxSeq * HD, *vbase = vc + (size_t)kvh * maxSeq * HD;
 
@@ -83,7 +84,7 @@ __global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float
     for (int e = threadIdx.x; e < HPC * QROWS * (HD / 4); e += NTH) {
         const int c = e % (HD / 4), r = (e / (HD / 4)) % QROWS, hh = e / (QROWS * (HD / 4));
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (t0 + r < T) v = *reinterpret_cast<const float4 *>(q + ((size_t)(t0 + r) * nh + blockIdx.y * HPC + hh) * HD + 4 * c);
+        if (t0 + r < T) v = *reinterpret_cast<const float4 *>(q + ((size_t)(t0 + r) * nh + hg * HPC + hh) * HD + 4 * c);
         __nv_bfloat16 p[3][4];
         split3(v.x, p[0][0], p[1][0], p[2][0]), split3(v.y, p[0][1], p[1][1], p[2][1]);
         split3(v.z, p[0][2], p[1][2], p[2][2]), split3(v.w, p[0][3], p[1][3], p[2][3]);
@@ -244,14 +245,15 @@ int smc_launch_sdpa_prefill_mma(smc_ctx *ctx, const float *q, const float *kc, c
 {
     const int G = nh / nkv;
     auto go = [&](auto kernel, int hpc) {
-        const dim3 grid((T + QROWS - 1) / QROWS, nh / hpc);
+        const dim3 grid(nh / hpc, (T + QROWS - 1) / QROWS);
         const size_t ldb = (size_t)hd * 2 + 16;
         const size_t smem = 3 * ((size_t)hpc * QROWS + 2 * KT) * ldb;
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         smc_launch_dep(ctx->use_pdl, kernel, grid, dim3(128 * hpc), smem, s, q, kc, vc, out, T, nh, nkv, pos0, maxSeq, scale);
     };
-    if (hd == 128) (G % 2 == 0) ? go(sdpa_prefill_mma_kernel<128, 2>, 2) : go(sdpa_prefill_mma_kernel<128, 1>, 1);
-    else (G % 2 == 0) ? go(sdpa_prefill_mma_kernel<64, 2>, 2) : go(sdpa_prefill_mma_kernel<64, 1>, 1);
+    const bool two = G % 2 == 0 && ctx->attn_hpc != 1;
+    if (hd == 128) two ? go(sdpa_prefill_mma_kernel<128, 2>, 2) : go(sdpa_prefill_mma_kernel<128, 1>, 1);
+    else two ? go(sdpa_prefill_mma_kernel<64, 2>, 2) : go(sdpa_prefill_mma_kernel<64, 1>, 1);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }

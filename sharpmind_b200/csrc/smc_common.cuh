@@ -88,6 +88,7 @@ struct smc_ctx {
     int tma_warps = 0;                            // warps per CTA of the one-row GEMV: 24 (one CTA per SM, default) or 12 (two)
     int tma_pre = 1;                              // stages requested before the activation loads are issued
     int attn_mma = 1;                             // prompt attention on the tensor cores (0: the fp32 CUDA-core kernel)
+    int attn_hpc = 0;                             // query heads per CTA of that kernel: 0 = two where heads share a KV head, 1 = always one
     int mt_ring = 0;                              // 2..32 rows, weights through the bulk-copy ring: 0 never, 1 Q4_K, 2 every format
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
     int argmax_rows = 0, argmax_chunks = 0;

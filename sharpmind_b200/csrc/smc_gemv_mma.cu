@@ -24,6 +24,9 @@ namespace {
 
 constexpr int MMA_ROWS = 32;   // weight rows per CTA
 constexpr int MMA_WARPS = 8;
+// floats per token of the warps' partial tiles in shared memory: a lane (g, tg) of an accumulator fragment writes token
+// 2 * tg (+ 1), row g (+ 8), so 2 * RED_LD = 8 (mod 32) puts the 32 lanes of a store on 32 banks (33 left them 4 deep)
+constexpr int RED_LD = 36;
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
 {
@@ -40,9 +43,9 @@ __device__ __forceinline__ uint2 ldg8(const void *p)
     return v;
 }
 
-// Adds the warps' partial tiles in warp order and stores out[t, r]; red is [NW warps][TOK tokens][33], TOK >= 8 * NT.
+// Adds the warps' partial tiles in warp order and stores out[t, r]; red is [NW warps][TOK tokens][RED_LD], TOK >= 8 * NT.
 template <int NT, int NW = MMA_WARPS, int TOK = 32>
-__device__ __forceinline__ void reduce_and_store(float (*red)[TOK][33], const float (&acc)[2][NT][4], float *out, int N, int M,
+__device__ __forceinline__ void reduce_and_store(float (*red)[TOK][RED_LD], const float (&acc)[2][NT][4], float *out, int N, int M,
                                                  int r0, int t0)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
@@ -74,7 +77,7 @@ gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ w
     // fragment and scale, which halves the passes over the matrix)
     constexpr int TOK = NT > 4 ? 64 : 32, XR = TOK / 32;
     extern __shared__ __align__(16) float red_q8[];
-    float (*red)[TOK][33] = reinterpret_cast<float (*)[TOK][33]>(red_q8);
+    float (*red)[TOK][RED_LD] = reinterpret_cast<float (*)[TOK][RED_LD]>(red_q8);
     smc_grid_dep_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
     const int r0 = blockIdx.x * MMA_ROWS;
@@ -156,7 +159,7 @@ __global__ void __launch_bounds__(256, 2)
 gemv_mma_q4_K_kernel(const uint8_t *__restrict__ raw, const int8_t *__restrict__ xq, const float *__restrict__ xd,
                      const float *__restrict__ xsd, float *__restrict__ out, int N, int K, int M)
 {
-    __shared__ float red[MMA_WARPS][32][33];
+    __shared__ float red[MMA_WARPS][32][RED_LD];
     smc_grid_dep_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
     const int r0 = blockIdx.x * MMA_ROWS;
@@ -287,7 +290,7 @@ gemv_mma_q6_K_kernel(const uint8_t *__restrict__ q6u, const int8_t *__restrict__
 {
     // NW warps split K: 8 (two CTAs per SM), or 16 in one CTA per SM for rows of 8192 elements and more
     extern __shared__ __align__(16) float red_dyn[];
-    float (*red)[32][33] = reinterpret_cast<float (*)[32][33]>(red_dyn);
+    float (*red)[32][RED_LD] = reinterpret_cast<float (*)[32][RED_LD]>(red_dyn);
     smc_grid_dep_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
     const int r0 = blockIdx.x * MMA_ROWS;
@@ -390,7 +393,7 @@ int smc_launch_gemv_mma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, f
         const int nt8 = M >= 64 ? 8 : nt;
         const dim3 g8((N + MMA_ROWS - 1) / MMA_ROWS, (M + 8 * nt8 - 1) / (8 * nt8));
         auto go8 = [&](auto kernel, int tok) {
-            const size_t smem = (size_t)MMA_WARPS * tok * 33 * sizeof(float);
+            const size_t smem = (size_t)MMA_WARPS * tok * RED_LD * sizeof(float);
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             smc_launch_dep(ctx->use_pdl, kernel, g8, dim3(256), smem, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
                            (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
@@ -404,7 +407,7 @@ int smc_launch_gemv_mma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, f
         // split across GPUs; long rows are where matrices of few rows (FFN down) need the extra warps per SM
         const bool wide = K >= 8192;
         auto go = [&](auto kernel, int nw) {
-            const size_t smem = (size_t)nw * 32 * 33 * sizeof(float);
+            const size_t smem = (size_t)nw * 32 * RED_LD * sizeof(float);
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             smc_launch_dep(ctx->use_pdl, kernel, grid, dim3(nw * 32), smem, s, (const uint8_t *)w->q6u, (const int8_t *)a->q,
                            (const float *)a->d, out, N, K, M);

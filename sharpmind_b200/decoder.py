@@ -122,7 +122,7 @@ class Decoder:
                                                     C.c_void_p(t.cuda.current_stream().cuda_stream)))
         return logits, argmax
 
-    def forward_last_logits(self, tokens, pos: int = 0, seq: int = 0, mode: int = ops.Mode.ACT_Q8, chunk: int = 1024):
+    def forward_last_logits(self, tokens, pos: int = 0, seq: int = 0, mode: int = ops.Mode.ACT_Q8, chunk: int = 2048):
         """Prompt processing (Transformer.ForwardLastLogits with seqLen > 1): tokens is CUDA int32 [seqLen], one
         sequence, placed at positions pos .. pos + seqLen - 1 of cache slot `seq`, fed in chunks of `chunk` tokens.
         Returns (logits [vocab] of the last token, its greedy pick [1])."""
