@@ -237,6 +237,13 @@ SMC_API int smc_add_dev(smc_ctx *ctx, float *d_x, const float *d_y, int64_t n, v
  * Same bits as smc_add_dev followed by smc_rmsnorm_dev. */
 SMC_API int smc_add_rmsnorm_dev(smc_ctx *ctx, float *d_x, const float *d_y, const float *d_w, float *d_out, int rows,
                                 int n, float eps, void *stream);
+/* The same pass with the normalised rows leaving as Q8_0 activations in `a` (QuantizedKVCache.QuantizeRowQ8_0's rules,
+ * QuantizedKVCache.cs:191-223), ready for smc_qmatmul_q8_dev: x += y (d_y may be null: no add), a = Q8_0(RMSNorm(x) * w),
+ * and d_out = the fp32 rows too when it is not null.  Between two matmuls of a block that runs several rows with
+ * quantised activations the fp32 rows are read by nothing else.  Same bits as smc_add_rmsnorm_dev (or smc_rmsnorm_dev)
+ * followed by smc_quantize_q8_dev.  n % 32 == 0, n > 256 and 16-byte aligned pointers, else SMC_E_UNSUPPORTED. */
+SMC_API int smc_add_rmsnorm_q8_dev(smc_ctx *ctx, float *d_x, const float *d_y, const float *d_w, float *d_out, int rows,
+                                   int n, float eps, smc_q8act *a, void *stream);
 /* Sampler.Argmax (SharpMind.Inference/Sampler.cs:50-58) per row: first maximum wins. */
 SMC_API int smc_argmax_dev(smc_ctx *ctx, const float *d_logits, int rows, int n, int *d_out, void *stream);
 /* Sampler.Sample (SharpMind.Inference/Sampler.cs:16-46) per row of d_logits [rows, n]: temperature, guarded softmax,

@@ -154,6 +154,8 @@ int smc_launch_gemv_mt(smc_ctx *, const smc_q8act *, const smc_weight *, float *
 int smc_launch_gemv_mma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,
                         cudaStream_t s);
+int smc_launch_add_rmsnorm_q8(smc_ctx *ctx, float *d_x, const float *d_y, const float *d_w, float *d_out, int rows, int n, float eps,
+                              smc_q8act *a, cudaStream_t s);
 int smc_launch_swiglu_quantize_q8(smc_ctx *ctx, const float *gate, const float *up, int M, int K, int ld, smc_q8act *a,
                                   cudaStream_t s);
 int smc_launch_quantize_q8(smc_ctx *, const float *x, int M, int K, smc_q8act *, cudaStream_t s);

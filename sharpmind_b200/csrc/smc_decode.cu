@@ -86,6 +86,17 @@ int alloc_rows(smc_ctx *ctx, smc_model *m, int rows)
 
 // y[M, N] = x[M, K] W^T in the requested mode; for SMC_ACT_Q8 with several rows the quantised rows in
 // `pre` (made by the caller from the same x) are reused instead of quantising again.
+// RMSNorm of x (after x += add when `add` is given) for matmuls that read quantised activations: one pass that leaves
+// the Q8_0 rows in m->qa, or the separate kernels through m->xn where the shape needs them.  Same bits either way.
+int norm_into_q8(smc_ctx *ctx, smc_model *m, float *x, const float *add, const float *w, int rows, int H, float eps, cudaStream_t s)
+{
+    int rc = smc_launch_add_rmsnorm_q8(ctx, x, add, w, nullptr, rows, H, eps, m->qa, s);
+    if (rc != SMC_E_UNSUPPORTED) return rc;
+    rc = add ? smc_add_rmsnorm_dev(ctx, x, add, w, m->xn, rows, H, eps, s) : smc_rmsnorm_dev(ctx, x, w, m->xn, rows, H, eps, s);
+    if (rc) return rc;
+    return smc_quantize_q8_dev(ctx, m->xn, rows, H, m->qa, s);
+}
+
 int linear(smc_ctx *ctx, const float *x, const smc_weight *w, float *y, int M, int mode, const smc_q8act *pre,
            cudaStream_t s, const float *bias = nullptr)
 {
@@ -504,11 +515,11 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
         return SMC_OK;
     }
     SMC_TRY(smc_embed_q8_0_dev(ctx, d.lm_head, d_tokens, B, m->x, s));
-    SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm1[0], m->xn, B, H, d.eps, s));
+    if (reuse) SMC_TRY(norm_into_q8(ctx, m, m->x, nullptr, m->norm1[0], B, H, d.eps, s));
+    else SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm1[0], m->xn, B, H, d.eps, s));
     for (int l = 0; l < d.n_layers; ++l) {
-        // m->xn holds RMSNorm(x) with this layer's first norm (made by the previous layer's tail)
+        // m->xn (m->qa with quantised activations) holds RMSNorm(x) with this layer's first norm, made by the previous layer's tail
         float *kc = m->kcache + (size_t)l * layer_stride, *vc = m->vcache + (size_t)l * layer_stride;
-        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
         // the joined matrix carries no GGUF-layout copy unless its parts kept theirs: reference order needs it
         const smc_weight *joined = m->wqkv[l];
         if (joined && (mode != SMC_REF_ORDER || joined->d_raw)) {
@@ -531,8 +542,8 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
         SMC_TRY(attend_decode(ctx, m, l, B, pos, scale, s));
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->att, B, qDim, m->qb, s));
         SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, B, mode, reuse ? m->qb : nullptr, s, m->bo[l]));
-        SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, B, H, d.eps, s));
-        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
+        if (reuse) SMC_TRY(norm_into_q8(ctx, m, m->x, m->tmp, m->norm2[l], B, H, d.eps, s));
+        else SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, B, H, d.eps, s));
         SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, B, mode, reuse ? m->qa : nullptr, s, m->bgu[l]));
         if (mode == SMC_ACT_Q8 && B == 1 && F <= 8192 && !m->bdown[l] && m->wdown[l]->fast && smc_tma_supported(m->wdown[l], 1)) {
             // one row: SiLU(gate) * up is formed and quantised while the down-projection stages its activations
@@ -547,9 +558,9 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
         }
         // residual add, then the next block's first norm (the final norm after the last block)
         const float *next_norm = l + 1 < d.n_layers ? m->norm1[l + 1] : d.final_norm;
-        SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, B, H, d.eps, s));
+        if (reuse) SMC_TRY(norm_into_q8(ctx, m, m->x, m->tmp, next_norm, B, H, d.eps, s));
+        else SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, B, H, d.eps, s));
     }
-    if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, B, H, m->qa, s));
     SMC_TRY(linear(ctx, m->xn, d.lm_head, d_logits, B, mode, reuse ? m->qa : nullptr, s));
     if (d_argmax) SMC_TRY(smc_argmax_dev(ctx, d_logits, B, d.vocab, d_argmax, s));
     return SMC_OK;
@@ -598,10 +609,10 @@ static int forward_tokens(smc_ctx *ctx, smc_model *m, const int *d_tokens, int s
     const size_t layer_stride = (size_t)m->max_batch * nkv * d.max_seq * hd, seq_off = (size_t)seq * nkv * d.max_seq * hd;
     const bool reuse = mode == SMC_ACT_Q8 && T > 1 && m->qa && m->qb;
     SMC_TRY(smc_embed_q8_0_dev(ctx, d.lm_head, d_tokens, T, m->x, s));
-    SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm1[0], m->xn, T, H, d.eps, s));
+    if (reuse) SMC_TRY(norm_into_q8(ctx, m, m->x, nullptr, m->norm1[0], T, H, d.eps, s));
+    else SMC_TRY(smc_rmsnorm_dev(ctx, m->x, m->norm1[0], m->xn, T, H, d.eps, s));
     for (int l = 0; l < d.n_layers; ++l) {
         float *kc = m->kcache + (size_t)l * layer_stride, *vc = m->vcache + (size_t)l * layer_stride;
-        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, T, H, m->qa, s));
         SMC_TRY(linear(ctx, m->xn, m->wqkv[l], m->qkv, T, mode, reuse ? m->qa : nullptr, s, m->bqkv[l]));
         // row t: per-head norm, rotation by position pos + t, K and V appended to sequence `seq`
         SMC_TRY(launch_qkv_post(ctx, m, l, kc, vc, T, pos, s, seq));
@@ -614,8 +625,8 @@ static int forward_tokens(smc_ctx *ctx, smc_model *m, const int *d_tokens, int s
         }
         if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->att, T, qDim, m->qb, s));
         SMC_TRY(linear(ctx, m->att, m->wo[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s, m->bo[l]));
-        SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, T, H, d.eps, s));
-        if (reuse) SMC_TRY(smc_quantize_q8_dev(ctx, m->xn, T, H, m->qa, s));
+        if (reuse) SMC_TRY(norm_into_q8(ctx, m, m->x, m->tmp, m->norm2[l], T, H, d.eps, s));
+        else SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, m->norm2[l], m->xn, T, H, d.eps, s));
         SMC_TRY(linear(ctx, m->xn, m->wgu[l], m->gu, T, mode, reuse ? m->qa : nullptr, s, m->bgu[l]));
         if (reuse) {
             SMC_TRY(smc_launch_swiglu_quantize_q8(ctx, m->gu, m->gu + F, T, F, 2 * F, m->qb, s));
@@ -624,7 +635,9 @@ static int forward_tokens(smc_ctx *ctx, smc_model *m, const int *d_tokens, int s
         }
         SMC_TRY(linear(ctx, m->act, m->wdown[l], m->tmp, T, mode, reuse ? m->qb : nullptr, s, m->bdown[l]));
         const float *next_norm = l + 1 < d.n_layers ? m->norm1[l + 1] : d.final_norm;
-        SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, T, H, d.eps, s));
+        // the last block's output meets the LM head as fp32 rows; the others are only ever read quantised
+        if (reuse && l + 1 < d.n_layers) SMC_TRY(norm_into_q8(ctx, m, m->x, m->tmp, next_norm, T, H, d.eps, s));
+        else SMC_TRY(smc_add_rmsnorm_dev(ctx, m->x, m->tmp, next_norm, m->xn, T, H, d.eps, s));
     }
     if (all_rows) {  // Transformer.Forward: the LM head meets every position (draft verification reads all of them)
         if (d_hidden) SMC_CUDA(ctx, cudaMemcpyAsync(d_hidden, m->xn, (size_t)T * H * sizeof(float), cudaMemcpyDeviceToDevice, s));

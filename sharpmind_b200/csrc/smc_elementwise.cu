@@ -162,6 +162,84 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float *x, const float 
     }
 }
 
+// The same pass with the normalised row leaving as Q8_0 activations (QuantizeRowQ8_0's rules, the structure-of-arrays
+// form the integer matmuls read) instead of, or besides, fp32: in a block of several rows with quantised activations
+// the norm's output is only ever read by the quantiser, so the fp32 row need not go through memory.  n % 32 == 0 and
+// 16-byte aligned rows; eight consecutive threads hold one 32-element block (four values each).  Values, scales and
+// sums are bit for bit those of add_rmsnorm_kernel followed by the row quantiser.
+__global__ void __launch_bounds__(256) add_rmsnorm_q8_kernel(float *x, const float *__restrict__ y, const float *__restrict__ w,
+                                                             float *out, int n, float eps, int8_t *__restrict__ q,
+                                                             float *__restrict__ d, uint16_t *__restrict__ dbits,
+                                                             float *__restrict__ sd, int16_t *__restrict__ s16)
+{
+    __shared__ float red[32];
+    smc_grid_dep_sync();
+    float4 *p4 = reinterpret_cast<float4 *>(x + (size_t)blockIdx.x * n);
+    const int n4 = n / 4;
+    float ss = 0.f;
+    if (y) {
+        const float4 *q4 = reinterpret_cast<const float4 *>(y + (size_t)blockIdx.x * n);
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 a = p4[i], b = q4[i];
+            const float4 v = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+            p4[i] = v;
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 v = p4[i];
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = __fdiv_rn(1.0f, sqrtf(__fdiv_rn(ss, (float)n) + eps));
+    const float4 *w4 = reinterpret_cast<const float4 *>(w);
+    const size_t blk0 = (size_t)blockIdx.x * (n / 32);
+    for (int i0 = 0; i0 < n4; i0 += blockDim.x) {  // whole warps stay in the loop: the shuffles below name all lanes
+        const int i = i0 + threadIdx.x;
+        const bool live = i < n4;                   // uniform over each group of eight threads (n4 % 8 == 0)
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) {
+            const float4 a = p4[i], g = __ldg(w4 + i);
+            v = make_float4((a.x * inv) * g.x, (a.y * inv) * g.y, (a.z * inv) * g.z, (a.w * inv) * g.w);
+            if (out) reinterpret_cast<float4 *>(out + (size_t)blockIdx.x * n)[i] = v;
+        }
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        float scale = __fdiv_rn(amax, 127.0f);
+        if (amax == 0.0f) scale = 1.0f;
+        const int q0 = max(-128, min(127, __float2int_rn(__fdiv_rn(v.x, scale))));
+        const int q1 = max(-128, min(127, __float2int_rn(__fdiv_rn(v.y, scale))));
+        const int q2 = max(-128, min(127, __float2int_rn(__fdiv_rn(v.z, scale))));
+        const int q3 = max(-128, min(127, __float2int_rn(__fdiv_rn(v.w, scale))));
+        int sum = q0 + q1 + q2 + q3;
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);                 // half block (16 values)
+        const int total = sum + __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (live) {
+            const size_t blk = blk0 + (size_t)(i >> 3);
+            reinterpret_cast<uint32_t *>(q + (size_t)blockIdx.x * n)[i] =
+                (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+            if ((i & 3) == 0) s16[blk * 2 + ((i >> 2) & 1)] = (int16_t)sum;
+            if ((i & 7) == 0) {
+                const __half h = __float2half_rn(scale);
+                const float df = __half2float(h);
+                d[blk] = df;
+                dbits[blk] = __half_as_ushort(h);
+                sd[blk] = df * (float)total;
+            }
+        }
+    }
+}
+
 __global__ void rmsnorm_row_kernel(const float *__restrict__ src, const float *__restrict__ w, float *__restrict__ dst,
                                    int n, float rms_inv)
 {
@@ -438,6 +516,24 @@ int ew_grid(long long items, int cap)
 
 }  // namespace
 
+// Residual add (d_y may be null: none) + RMSNorm with the row leaving as Q8_0 activations in `a`, and as fp32 too when
+// d_out is given.  Returns SMC_E_UNSUPPORTED without launching when the shape or alignment needs the separate kernels.
+int smc_launch_add_rmsnorm_q8(smc_ctx *ctx, float *d_x, const float *d_y, const float *d_w, float *d_out, int rows, int n, float eps,
+                              smc_q8act *a, cudaStream_t s)
+{
+    const bool aligned = ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_y) | reinterpret_cast<uintptr_t>(d_out) |
+                           reinterpret_cast<uintptr_t>(d_w)) & 15) == 0;
+    if (!aligned || n % 32 || n <= 256) return SMC_E_UNSUPPORTED;
+    if (rows > a->max_rows || n > a->max_k || (size_t)rows * n > (size_t)a->max_rows * a->max_k)
+        return smc_fail(ctx, SMC_E_INVALID, "q8act buffer %d x %d too small for %d x %d", a->max_rows, a->max_k, rows, n);
+    a->M = rows;
+    a->K = n;
+    smc_launch_dep(ctx->use_pdl, add_rmsnorm_q8_kernel, dim3(rows), dim3(256), 0, s, d_x, d_y, d_w, d_out, n, eps, a->q, a->d, a->dbits,
+                   a->sd, a->s16);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
 // ------------------------------------------------------------------------------------------ C ABI
 extern "C" {
 
@@ -478,6 +574,16 @@ int smc_add_rmsnorm_dev(smc_ctx *ctx, float *d_x, const float *d_y, const float 
                    n, eps, (aligned && (n & 3) == 0) ? 1 : 0);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
+}
+
+int smc_add_rmsnorm_q8_dev(smc_ctx *ctx, float *d_x, const float *d_y, const float *d_w, float *d_out, int rows, int n, float eps,
+                           smc_q8act *a, void *stream)
+{
+    if (!ctx || !d_x || !d_w || !a || rows <= 0 || n <= 0) return smc_fail(ctx, SMC_E_INVALID, "add_rmsnorm_q8: bad arguments");
+    const int rc = smc_launch_add_rmsnorm_q8(ctx, d_x, d_y, d_w, d_out, rows, n, eps, a, static_cast<cudaStream_t>(stream));
+    if (rc == SMC_E_UNSUPPORTED)
+        return smc_fail(ctx, rc, "add_rmsnorm_q8: rows of %d floats (needs a multiple of 32 above 256 and 16-byte aligned pointers)", n);
+    return rc;
 }
 
 int smc_swiglu_dev(smc_ctx *ctx, const float *d_gate, const float *d_up, float *d_dst, int rows, int F, int ld,

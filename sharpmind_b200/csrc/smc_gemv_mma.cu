@@ -150,6 +150,105 @@ gemv_mma_q8_0_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ w
     }
 }
 
+// Prompt-sized batches (hundreds of rows): the same sums with no shared-memory reduction.  The kernel above splits K
+// over the eight warps of a CTA (warp w takes the groups w, w + 8, ...) and adds the eight partial tiles in warp order;
+// with this many tokens there is parallelism enough without that split, so here one warp owns a 32 x 64 output tile and
+// walks the eight group classes one after the other, adding each finished class to its running total: the same
+// partial sums added in the same order, hence the same bits, without the barriers, the 64 KB of partial tiles and the
+// 8-way re-read that cost the split kernel a quarter of its instructions on K = 1024.  A CTA = eight token tiles of
+// one 32-row strip, which share the weight fragments through L1.
+__global__ void __launch_bounds__(256, 1)
+gemv_mma_q8_0_tile_kernel(const int8_t *__restrict__ wq, const __half *__restrict__ wd, const int8_t *__restrict__ xq,
+                          const float *__restrict__ xd, float *__restrict__ out, int N, int K, int M)
+{
+    constexpr int NT = 8;
+    smc_grid_dep_sync();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
+    const int r0 = blockIdx.x * MMA_ROWS;
+    const int t0 = (blockIdx.y * (blockDim.x >> 5) + warp) * 8 * NT;  // the launcher picks 1..8 warps (token tiles) per CTA
+    if (t0 >= M) return;  // no barrier below
+    const int nb = K / 32, ngroups = nb / 4;
+    const int8_t *abase = wq + 8 * tg;
+    uint32_t aoff[4];  // 32-bit offsets (the launcher keeps N * K and M * K below 2^32): pointers would not fit the register file
+#pragma unroll
+    for (int j = 0; j < 4; ++j) aoff[j] = (uint32_t)min(r0 + (j >> 1) * 16 + g + (j & 1) * 8, N - 1) * (uint32_t)K;
+    const __half *drow = wd + (size_t)min(r0 + lane, N - 1) * nb;
+    const int8_t *bbase = xq + 8 * tg;
+    uint32_t boff[NT];  // rows past the end are clamped for loads and masked at the store
+#pragma unroll
+    for (int t = 0; t < NT; ++t) boff[t] = (uint32_t)min(t0 + 8 * t + g, M - 1) * (uint32_t)K;
+    const float *xrow[2] = {xd + (size_t)min(t0 + lane, M - 1) * nb, xd + (size_t)min(t0 + 32 + lane, M - 1) * nb};
+    float total[2][NT][4];
+#pragma unroll 1
+    for (int cls = 0; cls < MMA_WARPS; ++cls) {
+        float acc[2][NT][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
+#pragma unroll 1
+        for (int gi = cls; gi < ngroups; gi += MMA_WARPS) {
+            uint2 aq[4][4];
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) aq[kb][j] = ldg8(abase + aoff[j] + (uint32_t)(gi * 4 + kb) * 32u);
+            const uint2 dwp = *reinterpret_cast<const uint2 *>(drow + gi * 4);
+            const float4 dxp[2] = {*reinterpret_cast<const float4 *>(xrow[0] + gi * 4), *reinterpret_cast<const float4 *>(xrow[1] + gi * 4)};
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                const uint32_t koff = (uint32_t)(gi * 4 + kb) * 32u;
+                uint2 b[NT];
+                const uint2 (&a)[4] = aq[kb];
+#pragma unroll
+                for (int t = 0; t < NT; ++t) b[t] = ldg8(bbase + boff[t] + koff);
+                const uint32_t dword = (kb & 2) ? dwp.y : dwp.x;
+                float dxl[2];
+#pragma unroll
+                for (int x = 0; x < 2; ++x) dxl[x] = kb == 0 ? dxp[x].x : kb == 1 ? dxp[x].y : kb == 2 ? dxp[x].z : dxp[x].w;
+                float dw[2][2];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t wv = __shfl_sync(0xffffffffu, dword, (j >> 1) * 16 + g + (j & 1) * 8);
+                    dw[j >> 1][j & 1] = smc_h2f((uint16_t)((kb & 1) ? (wv >> 16) : (wv & 0xFFFFu)));
+                }
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    const float dx0 = __shfl_sync(0xffffffffu, dxl[t >> 2], 8 * (t & 3) + 2 * tg);
+                    const float dx1 = __shfl_sync(0xffffffffu, dxl[t >> 2], 8 * (t & 3) + 2 * tg + 1);
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        int c[4];
+                        mma_s8(c, a[2 * mt].x, a[2 * mt + 1].x, a[2 * mt].y, a[2 * mt + 1].y, b[t].x, b[t].y);
+                        acc[mt][t][0] = fmaf((float)c[0], dw[mt][0] * dx0, acc[mt][t][0]);
+                        acc[mt][t][1] = fmaf((float)c[1], dw[mt][0] * dx1, acc[mt][t][1]);
+                        acc[mt][t][2] = fmaf((float)c[2], dw[mt][1] * dx0, acc[mt][t][2]);
+                        acc[mt][t][3] = fmaf((float)c[3], dw[mt][1] * dx1, acc[mt][t][3]);
+                    }
+                }
+            }
+        }
+        // the split kernel's fold: s = partial of warp 0; s += partial of warp 1; ...
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) total[mt][t][i] = cls == 0 ? acc[mt][t][i] : total[mt][t][i] + acc[mt][t][i];
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int tok = t0 + 8 * t + 2 * tg + (i & 1), row = r0 + mt * 16 + g + ((i >> 1) << 3);
+                if (row < N && tok < M) out[(size_t)tok * N + row] = total[mt][t][i];
+            }
+}
+
 // ------------------------------------------------------------------------------------------ Q4_K
 // GGUF blocks of 144 bytes: d, dmin (fp16), 12 packed scale / min bytes, 128 nibble bytes; the 32 bytes of
 // group gq hold sub-block 2*gq in the low nibbles and 2*gq + 1 in the high ones.  K % 256 == 0; a warp works
@@ -398,7 +497,15 @@ int smc_launch_gemv_mma(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, f
             smc_launch_dep(ctx->use_pdl, kernel, g8, dim3(256), smem, s, (const int8_t *)w->q8_qs, (const __half *)w->q8_d,
                            (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
         };
-        if (nt8 == 1) go8(gemv_mma_q8_0_kernel<1>, 32);
+        if (M >= 256 && (size_t)N * K < (1ull << 32) && (size_t)M * K < (1ull << 32)) {  // enough token tiles for a warp to own one: no K split, no shared memory
+            // eight token tiles of a 32-row strip per CTA share its weight fragments through L1; matrices of few rows
+            // take fewer per CTA so that the grid still covers the SMs twice (a warp's bits do not depend on this)
+            const int strips = (N + MMA_ROWS - 1) / MMA_ROWS, tiles = (M + 63) / 64;
+            int wpc = 8;
+            while (wpc > 1 && strips * ((tiles + wpc - 1) / wpc) < 2 * ctx->sm_count) wpc >>= 1;
+            smc_launch_dep(ctx->use_pdl, gemv_mma_q8_0_tile_kernel, dim3(strips, (tiles + wpc - 1) / wpc), dim3(32 * wpc), 0, s,
+                           (const int8_t *)w->q8_qs, (const __half *)w->q8_d, (const int8_t *)a->q, (const float *)a->d, out, N, K, M);
+        } else if (nt8 == 1) go8(gemv_mma_q8_0_kernel<1>, 32);
         else if (nt8 == 2) go8(gemv_mma_q8_0_kernel<2>, 32);
         else if (nt8 == 4) go8(gemv_mma_q8_0_kernel<4>, 32);
         else go8(gemv_mma_q8_0_kernel<8>, 64);

@@ -365,6 +365,15 @@ class DeviceOps:
         act.M, act.K = M, K
         return act
 
+    def add_rmsnorm_q8(self, x, y, w, eps: float, act: Q8Act, out=None):
+        """x += y (y may be None), act = Q8_0(RMSNorm(x) * w) row by row; `out` also receives the fp32 rows."""
+        rows, n = x.shape
+        self.ctx.check(self.lib.smc_add_rmsnorm_q8_dev(self.ctx.h, self._chk(x, self.torch.float32), None if y is None else self._chk(y),
+                                                       self._chk(w), None if out is None else self._chk(out), rows, n, eps, act.h,
+                                                       self._stream()))
+        act.M, act.K = rows, n
+        return act
+
     def qmatmul_q8(self, act: Q8Act, w: Weight, out=None):
         t = self.torch
         if out is None:

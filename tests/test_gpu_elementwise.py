@@ -232,6 +232,41 @@ def test_add_rmsnorm_equals_separate_launches(dev, rows, n):
     assert torch.equal(out, want)
 
 
+@pytest.mark.parametrize("rows,n,with_add", [(1, 1024, True), (7, 4096, True), (33, 2560, True), (5, 1024, False), (300, 8192, True)])
+def test_add_rmsnorm_q8_equals_separate_launches(dev, rows, n, with_add):
+    """Residual add + RMSNorm + Q8_0 row quantiser in one pass: the quants and fp16 scales are those of the separate
+    kernels, and so are the per-block sums the Q4_K / Q6_K matmuls read (checked through a matmul of each format)."""
+    import ctypes as C
+
+    import torch
+
+    from sharpmind_b200 import ops
+
+    ctx = dev.ctx
+    x = to_dev(synth.normal("gpue", f"aqx{rows}_{n}", (rows, n)))
+    y = to_dev(synth.normal("gpue", f"aqy{rows}_{n}", (rows, n))) if with_add else None
+    w = to_dev(synth.normal("gpue", f"aqw{n}", (n,), 0.1, 1.0))
+    x1 = x.clone()
+    if with_add:
+        dev.add_(x1, y)
+    normed = dev.rmsnorm(x1, w, 1e-6)
+    want = ops.Q8Act(ctx, rows, n)
+    dev.quantize_q8(normed, want, n)
+    x2, out = x.clone(), torch.empty_like(x)
+    got = dev.add_rmsnorm_q8(x2, y, w, 1e-6, ops.Q8Act(ctx, rows, n), out=out)
+    assert torch.equal(x1, x2) and torch.equal(out, normed)
+    (wq, wd), (gq, gd) = want.read(), got.read()
+    assert np.array_equal(wq, gq) and np.array_equal(wd, gd)
+    got2 = dev.add_rmsnorm_q8(x.clone(), y, w, 1e-6, ops.Q8Act(ctx, rows, n))  # without the fp32 copy
+    assert np.array_equal(got2.read()[0], wq)
+    for dtype in (8, 12, 14):
+        mat = ctx.register_dev(dev.quantize_weights(dtype, to_dev(synth.normal("gpue", f"aqm{dtype}_{n}", (64, n), 0.05))), dtype, 64, n)
+        assert torch.equal(dev.qmatmul_q8(got2, mat), dev.qmatmul_q8(want, mat)), dtype
+        ctx.release(mat)
+    with pytest.raises(Exception):  # rows that are not whole 32-element blocks keep to the separate kernels
+        dev.add_rmsnorm_q8(to_dev(np.zeros((2, 1000), np.float32)), None, to_dev(np.ones(1000, np.float32)), 1e-6, ops.Q8Act(ctx, 2, 1024))
+
+
 def test_argmax_first_maximum_over_chunks(dev):
     import torch
 

@@ -98,6 +98,33 @@ def test_results_do_not_depend_on_batch_size(oracle, cuda, dev):
         cuda.release(w)
 
 
+@pytest.mark.parametrize("n,k", [(100, 1024), (96, 3072), (40, 640), (64, 2048)])
+def test_q8_0_prompt_sized_batches_keep_the_small_batch_bits(oracle, cuda, dev, n, k):
+    """Q8_0 at 256 rows and more runs a kernel in which a warp owns a whole output tile (no K split across warps): it
+    must give each row the bits the 32-row kernel gives it (ragged last tiles, rows past N, group counts that do not fill
+    the eight classes), and sampled rows must meet the oracle."""
+    from sharpmind_b200.ops import Mode
+
+    raw = make_weight(oracle, Q8_0, n, k, f"pq{n}_{k}")
+    w = cuda.register(raw, Q8_0, n, k)
+    for m in (256, 300, 577):
+        xh = synth.normal("gpu", f"pqx{k}_{m}", (m, k))
+        x = to_dev(xh)
+        full = dev.qmatmul(x, w, Mode.ACT_Q8).cpu().numpy()
+        for lo in (0, 32, m - 32):  # the same rows as batches of 32: the K-split kernel
+            part = dev.qmatmul(x[lo:lo + 32].contiguous(), w, Mode.ACT_Q8).cpu().numpy()
+            assert np.array_equal(bits(part), bits(full[lo:lo + 32])), (m, lo)
+        mid = dev.qmatmul(x[:128].contiguous(), w, Mode.ACT_Q8).cpu().numpy()  # 64-token passes of the K-split kernel
+        assert np.array_equal(bits(mid), bits(full[:128]))
+        rows = [0, m // 2, m - 1]
+        xq = oracle.quantize_rows_q8_0(xh[rows], len(rows), k)
+        xhat = np.stack([oracle.dequantize(Q8_0, xq[r], k) for r in range(len(rows))])
+        want = oracle.qmatmul(Q8_0, xhat, raw, len(rows), k, n)
+        bound = row_norm_bound(oracle, Q8_0, raw, n, k, xhat)
+        assert np.all(np.abs(full[rows].astype(np.float64) - want) <= bound)
+    cuda.release(w)
+
+
 RING_SHAPES = [
     (Q4_K, 304, 4096), (Q4_K, 48, 14336), (Q4_K, 16, 2048), (Q6_K, 64, 14336), (Q6_K, 160, 4096), (Q6_K, 2384, 2048),
     (Q8_0, 272, 5120), (Q8_0, 64, 1024), (Q8_0, 4752, 1024),
