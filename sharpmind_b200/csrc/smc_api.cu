@@ -194,6 +194,7 @@ int smc_set_option(smc_ctx *ctx, const char *name, int value)
     else if (!strcmp(name, "gemv_warps")) ctx->tma_warps = (value == 12 || value == 24) ? value : 0;
     else if (!strcmp(name, "gemv_prefetch_first")) ctx->tma_pre = value >= 0 && value <= 8 ? value : 1;
     else if (!strcmp(name, "prompt_attention_mma")) ctx->attn_mma = value ? 1 : 0;
+    else if (!strcmp(name, "gemv_pair_staging")) ctx->tma_cluster = value ? 1 : 0;
     else if (!strcmp(name, "prompt_attention_heads_per_cta")) ctx->attn_hpc = value == 1 ? 1 : 0;
     else if (!strcmp(name, "small_batch_ring")) ctx->mt_ring = value >= 0 && value <= 2 ? value : 0;
     else return smc_fail(ctx, SMC_E_INVALID, "set_option: unknown option '%s'", name);

@@ -88,6 +88,7 @@ struct smc_ctx {
     int tma_warps = 0;                            // warps per CTA of the one-row GEMV: 24 (one CTA per SM, default) or 12 (two)
     int tma_pre = 1;                              // stages requested before the activation loads are issued
     int attn_mma = 1;                             // prompt attention on the tensor cores (0: the fp32 CUDA-core kernel)
+    int tma_cluster = 1;                          // one-row kernel: SM pairs share the quantisation of a long fp32 row
     int attn_hpc = 0;                             // query heads per CTA of that kernel: 0 = two where heads share a KV head, 1 = always one
     int mt_ring = 0;                              // 2..32 rows, weights through the bulk-copy ring: 0 never, 1 Q4_K, 2 every format
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
@@ -205,6 +206,22 @@ inline void smc_launch_dep(bool allow_overlap, void (*kernel)(KArgs...), dim3 gr
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at, cfg.numAttrs = allow_overlap ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// The same with the grid's CTAs paired into thread-block clusters of `cluster_x` (the grid must be a multiple of it).
+template <class... KArgs, class... Args>
+inline void smc_launch_dep_cluster(bool allow_overlap, int cluster_x, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                   cudaStream_t s, Args... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)cluster_x, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = allow_overlap ? 2 : 1;
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

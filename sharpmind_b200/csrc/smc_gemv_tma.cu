@@ -124,6 +124,38 @@ __device__ __forceinline__ void xst32(uint32_t sx, uint32_t off, uint32_t v)
 {
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(sx + off), "r"(v) : "memory");
 }
+// Thread-block clusters: the CTAs of a pair each quantise half of the activation row and store it into both shared
+// memories (sx2 = the partner's row as a shared::cluster address; 0 = no partner).
+__device__ __forceinline__ uint32_t cluster_ncta()
+{
+    uint32_t v;
+    asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(v));
+    return v;
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank()
+{
+    uint32_t v;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(v));
+    return v;
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t cta_addr, uint32_t rank)
+{
+    uint32_t v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(v) : "r"(cta_addr), "r"(rank));
+    return v;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void xst64r(uint32_t sx2, uint32_t off, uint2 v)
+{
+    asm volatile("st.shared::cluster.v2.u32 [%0], {%1,%2};" ::"r"(sx2 + off), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void xst32r(uint32_t sx2, uint32_t off, uint32_t v)
+{
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(sx2 + off), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ float warp_sum32(float v)
 {
@@ -216,7 +248,7 @@ __device__ __forceinline__ int quant_div_rn(float x, float scale, float rcp)
 // block scale and sums in the staged layout: the rules of QuantizedKVCache.QuantizeRowQ8_0 (d = amax/127, 1 for a
 // zero block, stored through fp16; q = round-half-even(x/d)).
 template <class Math>
-__device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, uint32_t dst)
+__device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, uint32_t dst, uint32_t dst2 = 0)
 {
     const uint32_t o_d = (uint32_t)K, o_aux = (uint32_t)K + (uint32_t)(K / 32) * 4u;
     float amax = 0.f;
@@ -237,15 +269,24 @@ __device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, u
     uint2 packed;
     packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
     packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
-    xst64(dst, 16u * (uint32_t)Math::swz(c >> 1) + 8u * (c & 1), packed);
+    const uint32_t o_q = 16u * (uint32_t)Math::swz(c >> 1) + 8u * (c & 1);
+    xst64(dst, o_q, packed);
+    if (dst2) xst64r(dst2, o_q, packed);
     const int s16v = s + __shfl_xor_sync(0xffffffffu, s, 1);
     const int total = s16v + __shfl_xor_sync(0xffffffffu, s16v, 2);
     const int blk = c >> 2;
-    if (Math::S16 && (c & 1) == 0) xst32(dst, o_aux + 4u * (uint32_t)m32_pos(c >> 1), (uint32_t)(-32 * s16v));
+    if (Math::S16 && (c & 1) == 0) {
+        xst32(dst, o_aux + 4u * (uint32_t)m32_pos(c >> 1), (uint32_t)(-32 * s16v));
+        if (dst2) xst32r(dst2, o_aux + 4u * (uint32_t)m32_pos(c >> 1), (uint32_t)(-32 * s16v));
+    }
     if ((c & 3) == 0) {
         const float df = __half2float(__float2half_rn(scale));
         xst32(dst, o_d + 4u * blk, __float_as_uint(df));
         if (Math::SD) xst32(dst, o_aux + 4u * blk, __float_as_uint(df * (float)total));
+        if (dst2) {
+            xst32r(dst2, o_d + 4u * blk, __float_as_uint(df));
+            if (Math::SD) xst32r(dst2, o_aux + 4u * blk, __float_as_uint(df * (float)total));
+        }
     }
 }
 
@@ -253,12 +294,16 @@ __device__ __forceinline__ void quant_chunk(const float (&v)[8], int c, int K, u
 // eight elements each; all loads of a round (R chunks per thread) are issued before any arithmetic so a round costs
 // one memory latency, not one per block.  With `up` the row is SiLU(x) * up in the arithmetic of the stand-alone
 // kernel.  `mid` as for stage_x: called once, after the first round's loads are on their way.
+// In a cluster of two, CTA `part` of `parts` quantises that share of the row and stores it into both shared memories
+// (dst2 = the partner's copy); the caller then meets the partner at a cluster barrier.
 template <class Math, int R, bool GATE, class Mid>
-__device__ __forceinline__ void stage_x_quant(const float *x, const float *up, int K, uint32_t dst, Mid mid)
+__device__ __forceinline__ void stage_x_quant(const float *x, const float *up, int K, uint32_t dst, Mid mid, int part = 0, int parts = 1,
+                                              uint32_t dst2 = 0)
 {
-    const int cend = K / 8;  // K is a multiple of 1024, so whole warps stay converged
+    // K is a multiple of 1024, so whole warps stay converged, also in a half of the row
+    const int cbeg = (K / 8 / parts) * part, cend = cbeg + K / 8 / parts;
     bool called = false;
-    for (int c0 = threadIdx.x; c0 < cend; c0 += R * blockDim.x) {
+    for (int c0 = cbeg + threadIdx.x; c0 < cend; c0 += R * blockDim.x) {
         float4 va[R], vb[R], ua[GATE ? R : 1], ub[GATE ? R : 1];
 #pragma unroll
         for (int j = 0; j < R; ++j) {
@@ -283,7 +328,7 @@ __device__ __forceinline__ void stage_x_quant(const float *x, const float *up, i
 #pragma unroll
                     for (int i = 0; i < 8; ++i) v[i] = __fdiv_rn(v[i], 1.0f + expf(-v[i])) * u[i];
                 }
-                quant_chunk<Math>(v, c, K, dst);
+                quant_chunk<Math>(v, c, K, dst, dst2);
             }
         }
     }
@@ -629,14 +674,21 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
     // the dependency wait above has seen complete)
     const unsigned gtag = GATHER ? smc_gather_tag(gd) : 0u;
     const bool greduce = GATHER && (tune & 0x100);  // partial sums of a K-split: every rank gets every output, summed
+    // launched as clusters of two (long fp32 rows): each CTA of a pair quantises half of the row for both
+    const uint32_t cn = cluster_ncta();
+    const int cpart = cn > 1 ? (int)cluster_cta_rank() : 0;
+    const uint32_t peer_x = cn > 1 ? cluster_map(sbase, (uint32_t)cpart ^ 1u) : 0u;
     if (xg.xf) {
         if (xg.nw) stage_x_addnorm_quant<Math>(xg.xf, xg.xadd, xg.nw, xg.eps, blockIdx.x == 0 ? xg.xsum : nullptr, K, sbase, fill_rest);
-        else if (xg.xu) stage_x_quant<Math, 2, true>(xg.xf, xg.xu, K, sbase, fill_rest);
-        else stage_x_quant<Math, 4, false>(xg.xf, nullptr, K, sbase, fill_rest);
+        else if (xg.xu) stage_x_quant<Math, 2, true>(xg.xf, xg.xu, K, sbase, fill_rest, cpart, (int)cn, peer_x);
+        else stage_x_quant<Math, 4, false>(xg.xf, nullptr, K, sbase, fill_rest, cpart, (int)cn, peer_x);
     } else {
         stage_x<Math>(xg, K, smem, fill_rest);  // rows quantised beforehand
     }
-    __syncthreads();  // the row is staged, and every warp's hand-over barrier is initialised
+    // the row is staged, and every warp's hand-over barrier is initialised; nothing touches the partner's shared
+    // memory after this barrier, so either CTA of a pair may finish first
+    if (cn > 1) cluster_sync_all();
+    else __syncthreads();
     Math math;
     math.init(lane);
     float acc = 0.f;
@@ -730,10 +782,17 @@ void launch_one(smc_ctx *ctx, dim3 grid, int nw, size_t smem, cudaStream_t s, co
                 int K, int slots, const smc_gather_dev *gd, bool reduce, bool pairs)
 {
     const int tune = (ctx->tma_pre & 0xFF) | (reduce ? 0x100 : 0);
+    // A long fp32 row (quantised, perhaps SiLU-gated, by every CTA while HBM waits) is shared by the two SMs of a pair:
+    // each quantises half.  Only the plain and the gated staging split (K % 1024 == 0 keeps whole warps in each half).
+    const bool pair_sms = ctx->tma_cluster && x.xf && !x.nw && K >= (x.xu ? 6144 : 8192) && grid.x % 2 == 0 && nw == WARPS;
     if (gd) {
         cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, 1>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
-                       tune, ctx->d_status, gd);
+        if (pair_sms)
+            smc_launch_dep_cluster(ctx->use_pdl, 2, gemv_tma_kernel<Math, SS, 1>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
+                                   tune, ctx->d_status, gd);
+        else
+            smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, 1>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
+                           tune, ctx->d_status, gd);
         return;
     }
     if (pairs) {
@@ -743,6 +802,11 @@ void launch_one(smc_ctx *ctx, dim3 grid, int nw, size_t smem, cudaStream_t s, co
         return;
     }
     cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (pair_sms) {
+        smc_launch_dep_cluster(ctx->use_pdl, 2, gemv_tma_kernel<Math, SS, 0>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
+                               tune, ctx->d_status, (const smc_gather_dev *)nullptr);
+        return;
+    }
     smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, 0>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
                    tune, ctx->d_status, (const smc_gather_dev *)nullptr);
 }

@@ -284,7 +284,7 @@ def test_argmax_first_maximum_over_chunks(dev):
     assert dev.argmax(small).cpu().numpy().tolist() == small.cpu().numpy().argmax(axis=1).tolist()
 
 
-@pytest.mark.parametrize("dtype,n,k", [(Q8_0, 1024, 2048), (Q8_0, 256, 3072), (Q4_K, 512, 2048), (Q6_K, 600, 8192)])
+@pytest.mark.parametrize("dtype,n,k", [(Q8_0, 1024, 2048), (Q8_0, 256, 3072), (Q4_K, 512, 2048), (Q6_K, 600, 8192), (Q4_K, 300, 14336), (Q8_0, 200, 9216)])
 def test_fused_one_row_matmuls(oracle, cuda, dev, dtype, n, k):
     """SiLU-gate and residual add + RMSNorm folded into the staging of a one-row matmul, against the separate kernels."""
     import ctypes as C
@@ -304,6 +304,9 @@ def test_fused_one_row_matmuls(oracle, cuda, dev, dtype, n, k):
     got = torch.empty_like(want)
     cuda.check(lib.smc_qmatmul_swiglu_dev(h, gu.data_ptr(), gu.data_ptr() + 4 * k, w.handle, got.data_ptr(), st))
     assert torch.equal(got, want)
+    if k > 9216:  # the norm prologue keeps a thread's chunks in registers: rows up to 9216
+        cuda.release(w)
+        return
     # add + norm prologue: the stream sum has the bits of the add kernel; the matmul agrees to rounding
     x = to_dev(synth.normal("gpue", f"fx{k}", (1, k)))
     y = to_dev(synth.normal("gpue", f"fy{k}", (1, k)))

@@ -216,7 +216,7 @@ PARTITION_SHAPES = [
     (Q4_K, 28672, 4096),   # the Llama-3-8B gate||up launch of the benchmark
     (Q4_K, 8192, 28672),   # Llama-3-70B down: the row takes two rounds of activation loads
     (Q6_K, 4096, 14336), (Q6_K, 3, 14336), (Q6_K, 37, 6144), (Q4_K, 4096, 4096), (Q4_K, 1, 8192), (Q4_K, 445, 2048),
-    (Q8_0, 1500, 2048), (Q8_0, 7, 5120), (Q8_0, 3072, 1024),
+    (Q8_0, 1500, 2048), (Q8_0, 7, 5120), (Q8_0, 3072, 1024), (Q8_0, 300, 8192),
 ]
 
 
@@ -243,14 +243,16 @@ def test_one_row_bits_do_not_depend_on_the_partition(oracle, cuda, dev, dtype, n
             wrow = oracle.dequantize(dtype, raw[r * per_row:(r + 1) * per_row], k)
             assert abs(float(base[0, r]) - float(want)) <= 1e-5 * np.linalg.norm(wrow) * np.linalg.norm(xhat)
         for opts in ({"gemv_ctas": 37}, {"gemv_ctas": 296, "gemv_steps_per_stage": 1, "gemv_prefetch_first": 0},
-                     {"gemv_steps_per_stage": 4, "gemv_slots": 3}, {"gemv_ctas": 1, "gemv_slots": 4, "pdl": 0}):
+                     {"gemv_steps_per_stage": 4, "gemv_slots": 3}, {"gemv_ctas": 1, "gemv_slots": 4, "pdl": 0},
+                     {"gemv_pair_staging": 0}, {"gemv_pair_staging": 0, "gemv_ctas": 74}, {"gemv_ctas": 74}):
+            # (gemv_pair_staging: rows of 8192 elements and more are quantised half each by the two SMs of a pair)
             for name, v in opts.items():
                 cuda.set_option(name, v)
             try:
                 got = dev.qmatmul(x, w, Mode.ACT_Q8).cpu().numpy()
             finally:
                 for name in opts:
-                    cuda.set_option(name, {"pdl": 1, "gemv_prefetch_first": 1}.get(name, 0))
+                    cuda.set_option(name, {"pdl": 1, "gemv_prefetch_first": 1, "gemv_pair_staging": 1}.get(name, 0))
             assert np.array_equal(bits(got), bits(base)), opts
     finally:
         cuda.release(w)
