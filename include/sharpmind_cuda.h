@@ -92,8 +92,13 @@ SMC_API const char *smc_last_error(smc_ctx *ctx);
  *   "gemv_ctas"             CTAs in its grid (0 = built-in choice: the SMs times the CTAs per SM)
  *   "gemv_warps"            warps per CTA, 24 (one CTA per SM) or 12 (two); 0 = built-in choice by row length
  *   "gemv_prefetch_first"   stages a warp requests before the activation loads are issued, 0..8 (default 1)
+ *   "gemv_pair_staging"     1 (default): for fp32 rows of 8192 elements and more the two SMs of a pair (a thread-block
+ *                           cluster of two) each quantise half of the row into both shared memories; 0: every CTA
+ *                           quantises the whole row
  *   "prompt_attention_mma"  causal attention of a prompt chunk: 1 (default) bf16 tensor-core MMAs on operands split three
  *                           ways (fp32-grade accuracy), 0 the fp32 CUDA-core kernel
+ *   "prompt_attention_heads_per_cta"  0 (default): a CTA of that kernel takes two query heads that share a KV head where
+ *                           the model has them; 1: always one
  *   "small_batch_ring"      2..32 rows in SMC_ACT_Q8: weights through the bulk-copy ring for 1 Q4_K, 2 every format,
  *                           0 (default) never (then the kernel that fetches its fragments from global memory runs; the
  *                           two add a row's blocks in different orders: results agree within the mode's bound, not
