@@ -826,14 +826,18 @@ def run_ours(args):
     e2e_steps = max(2, args.steps // 4)
     if world == 1:
         q = ops.QuantizationOps(ctx, mode)
-        outs_h = [np.empty((M, n), np.float32) for (_, _, n, _) in mats]
+        # the caller's rows live in page-locked host memory (numpy views of pinned tensors): the call copies from and to
+        # them directly
+        pins = [torch.from_numpy(x).pin_memory() for x in xs_h] + [torch.empty((M, n), dtype=torch.float32).pin_memory() for (_, _, n, _) in mats]
+        xs_h = [t.numpy() for t in pins[:len(mats)]]
+        outs_h = [t.numpy() for t in pins[len(mats):]]
 
         def e2e_step():
             for layer in range(L):
                 for mi, (_, _, n_, k_) in enumerate(mats):
                     q.QuantizedMatMulHandle(xs_h[mi], weights[layer][mi], outs_h[mi], M, k_, n_)
 
-        api = "smc_qmatmul_host_w: one synchronous C-ABI call per matmul, host fp32 in / out"
+        api = "smc_qmatmul_host_w: one synchronous C-ABI call per matmul, page-locked host fp32 rows in / out"
     elif tp_ffn:
         pin_x = torch.from_numpy(xs_h[0]).pin_memory()
         dev_x0 = torch.empty((1, H), device="cuda")

@@ -145,7 +145,10 @@ SMC_API int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_
 /* The same slot for a caller that kept the handle registration returned (an InferenceLinearLayer that registers in
  * SetRawWeight, InferenceLinearLayer.cs:200-221, and stores the handle next to RawQuantizedData): no pointer lookup,
  * and weights that never had a host copy (registered from device memory) can be used.  M, K, N as in
- * QuantizedMatMulFn; K and N are checked against the handle (SMC_E_SIZE_MISMATCH). */
+ * QuantizedMatMulFn; K and N are checked against the handle (SMC_E_SIZE_MISMATCH).
+ * Both host entry points copy from and to page-locked caller memory (cudaHostAlloc / cudaHostRegister; in .NET a
+ * pinned, registered array) directly; pageable buffers go through the context's own pinned bounce buffer, which
+ * costs a host memcpy each way. */
 SMC_API int smc_qmatmul_host_w(smc_ctx *ctx, const float *input, const smc_weight *w, float *output, int M, int K,
                                int N, int mode);
 /* VecDotFn(float* input, byte* rawWeights, int col, int inFeatures) (QuantizationOps.cs:8,176-202). */

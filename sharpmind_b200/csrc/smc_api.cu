@@ -90,6 +90,18 @@ int d2h(smc_ctx *ctx, void *dst, const void *src, size_t bytes)
     return SMC_OK;
 }
 
+// Page-locked host memory (cudaHostAlloc / cudaHostRegister by the caller) is copied from and to directly: no bounce
+// buffer, no host memcpy.  Anything else (ordinary pageable memory, or a pointer the runtime cannot classify) is not.
+bool host_is_pinned(const void *p)
+{
+    cudaPointerAttributes at{};
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();  // an unknown pointer is not an error of this call
+        return false;
+    }
+    return at.type == cudaMemoryTypeHost;
+}
+
 bool known_dtype(int dtype) { return dtype == SMC_Q8_0 || dtype == SMC_Q4_K || dtype == SMC_Q6_K; }
 
 void free_weight(smc_weight *w)
@@ -194,7 +206,7 @@ int smc_set_option(smc_ctx *ctx, const char *name, int value)
     else if (!strcmp(name, "gemv_warps")) ctx->tma_warps = (value == 12 || value == 24) ? value : 0;
     else if (!strcmp(name, "gemv_prefetch_first")) ctx->tma_pre = value >= 0 && value <= 8 ? value : 1;
     else if (!strcmp(name, "prompt_attention_mma")) ctx->attn_mma = value ? 1 : 0;
-    else if (!strcmp(name, "gemv_pair_staging")) ctx->tma_cluster = value ? 1 : 0;
+    else if (!strcmp(name, "gemv_pair_staging")) ctx->tma_cluster = value < 0 ? 0 : value;
     else if (!strcmp(name, "prompt_attention_heads_per_cta")) ctx->attn_hpc = value == 1 ? 1 : 0;
     else if (!strcmp(name, "small_batch_ring")) ctx->mt_ring = value >= 0 && value <= 2 ? value : 0;
     else return smc_fail(ctx, SMC_E_INVALID, "set_option: unknown option '%s'", name);
@@ -683,13 +695,19 @@ static int qmatmul_host_impl(smc_ctx *ctx, const float *input, const smc_weight 
     size_t in_bytes = (size_t)M * w->K * sizeof(float), out_bytes = (size_t)M * w->N * sizeof(float);
     if ((rc = ensure_dev(ctx, &ctx->d_stage_in, &ctx->stage_in_cap, in_bytes))) return rc;
     if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, out_bytes))) return rc;
-    // one wait per call: input copy, kernels and result copy are ordered by the stream
-    if ((rc = h2d_queued(ctx, ctx->d_stage_in, input, in_bytes, out_bytes))) return rc;
+    // one wait per call: input copy, kernels and result copy are ordered by the stream.  Page-locked caller buffers
+    // are the source and the target of the copies themselves; pageable ones go through the context's bounce buffer.
+    const bool pin_in = host_is_pinned(input), pin_out = host_is_pinned(output);
+    if (pin_in) SMC_CUDA(ctx, cudaMemcpyAsync(ctx->d_stage_in, input, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
+    else if ((rc = h2d_queued(ctx, ctx->d_stage_in, input, in_bytes, pin_out ? in_bytes : out_bytes))) return rc;
     if ((rc = qmatmul_impl(ctx, ctx->d_stage_in, w, ctx->d_stage_out, M, mode, ctx->stream))) {
         cudaStreamSynchronize(ctx->stream);
         return rc;
     }
-    return d2h(ctx, output, ctx->d_stage_out, out_bytes);
+    if (!pin_out) return d2h(ctx, output, ctx->d_stage_out, out_bytes);
+    SMC_CUDA(ctx, cudaMemcpyAsync(output, ctx->d_stage_out, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    SMC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return SMC_OK;
 }
 
 int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, float *output, int M, int K, int N,

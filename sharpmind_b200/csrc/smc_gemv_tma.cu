@@ -784,7 +784,8 @@ void launch_one(smc_ctx *ctx, dim3 grid, int nw, size_t smem, cudaStream_t s, co
     const int tune = (ctx->tma_pre & 0xFF) | (reduce ? 0x100 : 0);
     // A long fp32 row (quantised, perhaps SiLU-gated, by every CTA while HBM waits) is shared by the two SMs of a pair:
     // each quantises half.  Only the plain and the gated staging split (K % 1024 == 0 keeps whole warps in each half).
-    const bool pair_sms = ctx->tma_cluster && x.xf && !x.nw && K >= (x.xu ? 6144 : 8192) && grid.x % 2 == 0 && nw == WARPS;
+    const int pair_min_k = ctx->tma_cluster > 1 ? ctx->tma_cluster : (x.xu ? 6144 : 8192);  // an option value above 1 is the row length to pair from
+    const bool pair_sms = ctx->tma_cluster && x.xf && !x.nw && K >= pair_min_k && grid.x % 2 == 0 && (nw == WARPS || ctx->tma_cluster > 1);
     if (gd) {
         cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (pair_sms)

@@ -353,6 +353,17 @@ def test_host_slot_equals_device_path_and_guards(oracle, cuda, dev):
         q.QuantizedMatMulQ8_0(x, raw, out, m, k, n)
         ref = dev.qmatmul(to_dev(x), w, mode).cpu().numpy()
         assert np.array_equal(bits(out), bits(ref))
+    # page-locked caller buffers are copied from / to directly, pageable ones through the bounce buffer: same bits
+    import torch
+
+    q = ops.QuantizationOps(cuda, ops.Mode.ACT_Q8)
+    ref = dev.qmatmul(to_dev(x), w, ops.Mode.ACT_Q8).cpu().numpy()
+    for pin_in in (False, True):
+        for pin_out in (False, True):
+            xi = torch.from_numpy(x).pin_memory().numpy() if pin_in else x.copy()
+            oo = torch.zeros((m, n), dtype=torch.float32).pin_memory().numpy() if pin_out else np.zeros((m, n), np.float32)
+            q.QuantizedMatMulQ8_0(xi, raw, oo, m, k, n)
+            assert np.array_equal(bits(oo), bits(ref)), (pin_in, pin_out)
     q = ops.QuantizationOps(cuda)
     out = np.zeros((m, n), np.float32)
     with pytest.raises(ops.InvalidOperationException):  # shape does not match the registration
