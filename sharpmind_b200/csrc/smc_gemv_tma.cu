@@ -126,12 +126,6 @@ __device__ __forceinline__ void xst32(uint32_t sx, uint32_t off, uint32_t v)
 }
 // Thread-block clusters: the CTAs of a pair each quantise half of the activation row and store it into both shared
 // memories (sx2 = the partner's row as a shared::cluster address; 0 = no partner).
-__device__ __forceinline__ uint32_t cluster_ncta()
-{
-    uint32_t v;
-    asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(v));
-    return v;
-}
 __device__ __forceinline__ uint32_t cluster_cta_rank()
 {
     uint32_t v;
@@ -595,7 +589,7 @@ struct MathQ8_0 {
 // kernel writes out[i] = SiLU(sum(2i)) * sum(2i + 1) (FfnKernels.Gated's activation, Layers/Ffn/FfnKernels.cs:35-59):
 // a CTA owns whole pairs, parks its row sums in shared memory and forms the products when its rows are done, so the
 // down projection stages a plain row instead of every SM recomputing SiLU over the whole row.
-template <class Math, int SS, int MODE>
+template <class Math, int SS, int MODE, bool PAIR = false>
 __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XPtrs xg, float *__restrict__ out, int N, int K,
                                                                     int slots, int tune, int *__restrict__ status,
                                                                     const smc_gather_dev *gd)
@@ -674,10 +668,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
     // the dependency wait above has seen complete)
     const unsigned gtag = GATHER ? smc_gather_tag(gd) : 0u;
     const bool greduce = GATHER && (tune & 0x100);  // partial sums of a K-split: every rank gets every output, summed
-    // launched as clusters of two (long fp32 rows): each CTA of a pair quantises half of the row for both
-    const uint32_t cn = cluster_ncta();
-    const int cpart = cn > 1 ? (int)cluster_cta_rank() : 0;
-    const uint32_t peer_x = cn > 1 ? cluster_map(sbase, (uint32_t)cpart ^ 1u) : 0u;
+    // PAIR: launched as clusters of two (long fp32 rows), each CTA of a pair quantises half of the row for both.  A
+    // template parameter, so that the kernels of short rows (a decode step's) carry none of this code.
+    constexpr uint32_t cn = PAIR ? 2u : 1u;
+    const int cpart = PAIR ? (int)cluster_cta_rank() : 0;
+    const uint32_t peer_x = PAIR ? cluster_map(sbase, (uint32_t)cpart ^ 1u) : 0u;
     if (xg.xf) {
         if (xg.nw) stage_x_addnorm_quant<Math>(xg.xf, xg.xadd, xg.nw, xg.eps, blockIdx.x == 0 ? xg.xsum : nullptr, K, sbase, fill_rest);
         else if (xg.xu) stage_x_quant<Math, 2, true>(xg.xf, xg.xu, K, sbase, fill_rest, cpart, (int)cn, peer_x);
@@ -687,7 +682,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_tma_kernel(StepSrc src, XP
     }
     // the row is staged, and every warp's hand-over barrier is initialised; nothing touches the partner's shared
     // memory after this barrier, so either CTA of a pair may finish first
-    if (cn > 1) cluster_sync_all();
+    if (PAIR) cluster_sync_all();
     else __syncthreads();
     Math math;
     math.init(lane);
@@ -788,10 +783,11 @@ void launch_one(smc_ctx *ctx, dim3 grid, int nw, size_t smem, cudaStream_t s, co
     const bool pair_sms = ctx->tma_cluster && x.xf && !x.nw && K >= pair_min_k && grid.x % 2 == 0 && (nw == WARPS || ctx->tma_cluster > 1);
     if (gd) {
         cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (pair_sms)
-            smc_launch_dep_cluster(ctx->use_pdl, 2, gemv_tma_kernel<Math, SS, 1>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
+        if (pair_sms) {
+            cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            smc_launch_dep_cluster(ctx->use_pdl, 2, gemv_tma_kernel<Math, SS, 1, true>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
                                    tune, ctx->d_status, gd);
-        else
+        } else
             smc_launch_dep(ctx->use_pdl, gemv_tma_kernel<Math, SS, 1>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
                            tune, ctx->d_status, gd);
         return;
@@ -804,7 +800,8 @@ void launch_one(smc_ctx *ctx, dim3 grid, int nw, size_t smem, cudaStream_t s, co
     }
     cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (pair_sms) {
-        smc_launch_dep_cluster(ctx->use_pdl, 2, gemv_tma_kernel<Math, SS, 0>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
+        cudaFuncSetAttribute(gemv_tma_kernel<Math, SS, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        smc_launch_dep_cluster(ctx->use_pdl, 2, gemv_tma_kernel<Math, SS, 0, true>, grid, dim3(nw * 32), smem, s, src, x, out, N, K, slots,
                                tune, ctx->d_status, (const smc_gather_dev *)nullptr);
         return;
     }
