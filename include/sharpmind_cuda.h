@@ -188,6 +188,11 @@ SMC_API int smc_q8act_create(smc_ctx *ctx, int max_rows, int max_k, smc_q8act **
 SMC_API int smc_q8act_destroy(smc_ctx *ctx, smc_q8act *a);
 SMC_API int smc_quantize_q8_dev(smc_ctx *ctx, const float *d_x, int M, int K, smc_q8act *a, void *stream);
 /* Copies the quantised rows back to the host: q [M, K] int8, d_bits [M, K/32] fp16 bit patterns. */
+/* FfnKernels.Gated's activation and the row quantiser in one pass: a = Q8_0(SiLU(gate) * up), gate and up being `rows`
+ * rows of `ld` floats of which the first F are used (ld = 2 F for a joined gate||up output); the fp32 product is not
+ * written.  Same bits as smc_swiglu_dev followed by smc_quantize_q8_dev.  F % 32 == 0. */
+SMC_API int smc_swiglu_quantize_q8_dev(smc_ctx *ctx, const float *d_gate, const float *d_up, int rows, int F, int ld, smc_q8act *a,
+                                       void *stream);
 SMC_API int smc_q8act_read(smc_ctx *ctx, const smc_q8act *a, int8_t *q, uint16_t *d_bits);
 /* The same product for prefill-sized M on the tensor cores (tcgen05 MMA, accumulators in tensor memory):
  * Q4_K weights with N % 128 == 0 and K % 256 == 0; the integer part of each weight is exact in fp16 and the

@@ -420,6 +420,12 @@ int smc_quantize_q8_dev(smc_ctx *ctx, const float *d_x, int M, int K, smc_q8act 
     return smc_launch_quantize_q8(ctx, d_x, M, K, a, static_cast<cudaStream_t>(stream));
 }
 
+int smc_swiglu_quantize_q8_dev(smc_ctx *ctx, const float *d_gate, const float *d_up, int rows, int F, int ld, smc_q8act *a, void *stream)
+{
+    if (!ctx || !d_gate || !d_up || !a || rows <= 0 || F <= 0 || ld < F) return smc_fail(ctx, SMC_E_INVALID, "swiglu_quantize_q8: bad arguments");
+    return smc_launch_swiglu_quantize_q8(ctx, d_gate, d_up, rows, F, ld, a, static_cast<cudaStream_t>(stream));
+}
+
 int smc_q8act_read(smc_ctx *ctx, const smc_q8act *a, int8_t *q, uint16_t *d_bits)
 {
     if (!ctx || !a || a->M <= 0) return smc_fail(ctx, SMC_E_INVALID, "q8act_read: buffer holds no rows");

@@ -365,6 +365,14 @@ class DeviceOps:
         act.M, act.K = M, K
         return act
 
+    def swiglu_quantize_q8(self, gu, F: int, act: Q8Act):
+        """act = Q8_0(SiLU(gate) * up) for a joined gate||up output gu [rows, 2 F]."""
+        rows = gu.numel() // (2 * F)
+        p = self._chk(gu, self.torch.float32)
+        self.ctx.check(self.lib.smc_swiglu_quantize_q8_dev(self.ctx.h, p, p + 4 * F, rows, F, 2 * F, act.h, self._stream()))
+        act.M, act.K = rows, F
+        return act
+
     def add_rmsnorm_q8(self, x, y, w, eps: float, act: Q8Act, out=None):
         """x += y (y may be None), act = Q8_0(RMSNorm(x) * w) row by row; `out` also receives the fp32 rows."""
         rows, n = x.shape

@@ -267,6 +267,28 @@ def test_add_rmsnorm_q8_equals_separate_launches(dev, rows, n, with_add):
         dev.add_rmsnorm_q8(to_dev(np.zeros((2, 1000), np.float32)), None, to_dev(np.ones(1000, np.float32)), 1e-6, ops.Q8Act(ctx, 2, 1024))
 
 
+@pytest.mark.parametrize("rows,F", [(1, 3072), (5, 1024), (33, 14336), (300, 3072), (2, 32)])
+def test_swiglu_quantize_q8_equals_separate_launches(dev, rows, F):
+    """SiLU(gate) * up and the Q8_0 row quantiser in one pass (16-byte accesses for batches, one lane per value for a
+    block or two): quants and scales of the separate kernels, and their block sums through a matmul of each format."""
+    import torch
+
+    from sharpmind_b200 import ops
+
+    ctx = dev.ctx
+    gu = to_dev(synth.normal("gpue", f"sq{rows}_{F}", (rows, 2 * F), 1.5))
+    want = ops.Q8Act(ctx, rows, F)
+    dev.quantize_q8(dev.swiglu_fused(gu, F), want, F)
+    got = dev.swiglu_quantize_q8(gu, F, ops.Q8Act(ctx, rows, F))
+    (wq, wd), (gq, gd) = want.read(), got.read()
+    assert np.array_equal(wq, gq) and np.array_equal(wd, gd)
+    if F % 256 == 0:
+        for dtype in (8, 12, 14):
+            mat = ctx.register_dev(dev.quantize_weights(dtype, to_dev(synth.normal("gpue", f"sqm{dtype}_{F}", (32, F), 0.05))), dtype, 32, F)
+            assert torch.equal(dev.qmatmul_q8(got, mat), dev.qmatmul_q8(want, mat)), dtype
+            ctx.release(mat)
+
+
 def test_argmax_first_maximum_over_chunks(dev):
     import torch
 
