@@ -168,5 +168,12 @@ def test_prompt_attention_on_tensor_cores(oracle, cuda, hd, heads, kvh):
             finally:
                 cuda.set_option("prompt_attention_mma", 1)
             assert np.max(np.abs(old - got)) <= 2e-5 * np.max(np.abs(want))
+            # one query head per CTA instead of two that share a KV head: every head's arithmetic is the same
+            cuda.set_option("prompt_attention_heads_per_cta", 1)
+            try:
+                single = kv.attention(to_dev(q), scale).cpu().numpy()
+            finally:
+                cuda.set_option("prompt_attention_heads_per_cta", 0)
+            assert np.array_equal(single.view(np.uint32), got.view(np.uint32))
     kv.Dispose()
     assert cuda.device_status() == 0
