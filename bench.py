@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload llama70b|llama8b] [--batch M] [--mode q8|f32] [--layers L]
-                    [--only gemv:<shape>[:<M>[:q8|q8pre|f32[:ring]]] | decode[:qwen3|llama8b][:q8kv] | prompt | elementwise | prefill]
+                    [--only gemv:<shape>[:<M>[:q8|q8pre|f32[:ring]]] | decode[:qwen3|llama8b][:q8kv] | prompt[:llama8b] | elementwise | prefill]
 
 Workload (default `llama70b`, BASELINE configs[4], the largest configuration that fits one GPU and the one the
 multi-GPU target is stated on): the Llama-3-70B-shaped FFN GEMV stack -- per layer the fused gate||up projection
@@ -530,7 +530,7 @@ def run_only(args):
             cfg["n_layers"] = args.layers
         res = {"decode": time_decode(torch, ctx, dev, cfg, [args.batch], 2048, max(args.steps, 4), mode, once=args.no_graph)}
     elif parts[0] == "prompt":
-        cfg = dict(synth.QWEN3_0_6B)
+        cfg = dict(synth.LLAMA3_8B if len(parts) > 1 and parts[1] == "llama8b" else synth.QWEN3_0_6B)
         if args.layers:
             cfg["n_layers"] = args.layers
         res = {"prompt": time_prompt(torch, ctx, dev, cfg, 2048, args.chunk, mode)}
@@ -1029,7 +1029,11 @@ def run_ours(args):
 
         def decode8b():
             rows8 = time_decode(torch, ctx, dev, dict(synth.LLAMA3_8B), [1, 32], 2048, 8, ops.Mode.ACT_Q8)
-            return {"workload": "Llama-3-8B-shaped decoder: Q4_K attention and gate||up, Q6_K down, Q8_0 tied embedding, fp32 KV, "
+            pr8 = time_prompt(torch, ctx, dev, dict(synth.LLAMA3_8B), 2048, 2048, ops.Mode.ACT_Q8, 2)
+            return {"prompt_pass": {"what": "ForwardLastLogits over a 2048-token seeded prompt in one call (Q4_K matmuls on tcgen05 over "
+                                            "the Q8_0 activation rows, Q6_K down on int8 mma.sync)",
+                                    "ms": pr8["ms"], "tokens_per_s": pr8["tokens_per_s"]},
+                    "workload": "Llama-3-8B-shaped decoder: Q4_K attention and gate||up, Q6_K down, Q8_0 tied embedding, fp32 KV, "
                                 "2048-position seeded random context, q8_0 activations, CUDA graph",
                     "tokens_per_s_batch1": rows8[0]["tokens_per_s"], "ms_per_step_batch1": rows8[0]["ms_per_step"],
                     "tokens_per_s_batch32": rows8[1]["tokens_per_s"], "ms_per_step_batch32": rows8[1]["ms_per_step"],

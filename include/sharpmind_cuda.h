@@ -94,7 +94,10 @@ SMC_API const char *smc_last_error(smc_ctx *ctx);
  *   "gemv_prefetch_first"   stages a warp requests before the activation loads are issued, 0..8 (default 1)
  *   "gemv_pair_staging"     1 (default): for fp32 rows of 8192 elements and more the two SMs of a pair (a thread-block
  *                           cluster of two) each quantise half of the row into both shared memories; 0: every CTA
- *                           quantises the whole row
+ *                           quantises the whole row; a value above 1 is the row length from which rows are shared
+ *   "q8_prefill_tensor_cores"  1 (default): SMC_ACT_Q8 over Q4_K at 64 rows and more runs the tcgen05 kernel on the Q8_0
+ *                           activation rows (d * q is exact in its fp16 pairs; same parity bound as the int8 kernels, other
+ *                           summation order); 0: the int8 mma.sync kernels at every batch size
  *   "prompt_attention_mma"  causal attention of a prompt chunk: 1 (default) bf16 tensor-core MMAs on operands split three
  *                           ways (fp32-grade accuracy), 0 the fp32 CUDA-core kernel
  *   "prompt_attention_heads_per_cta"  0 (default): a CTA of that kernel takes two query heads that share a KV head where

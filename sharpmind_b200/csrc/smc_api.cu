@@ -207,6 +207,7 @@ int smc_set_option(smc_ctx *ctx, const char *name, int value)
     else if (!strcmp(name, "gemv_prefetch_first")) ctx->tma_pre = value >= 0 && value <= 8 ? value : 1;
     else if (!strcmp(name, "prompt_attention_mma")) ctx->attn_mma = value ? 1 : 0;
     else if (!strcmp(name, "gemv_pair_staging")) ctx->tma_cluster = value < 0 ? 0 : value;
+    else if (!strcmp(name, "q8_prefill_tensor_cores")) ctx->q8_prefill_tc = value ? 1 : 0;
     else if (!strcmp(name, "prompt_attention_heads_per_cta")) ctx->attn_hpc = value == 1 ? 1 : 0;
     else if (!strcmp(name, "small_batch_ring")) ctx->mt_ring = value >= 0 && value <= 2 ? value : 0;
     else return smc_fail(ctx, SMC_E_INVALID, "set_option: unknown option '%s'", name);
@@ -444,6 +445,11 @@ int smc_qmatmul_q8_dev(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, fl
         return smc_fail(ctx, SMC_E_UNSUPPORTED,
                         "quantised-activation matmul needs a weight registered with SMC_W_REPACK and K %% %d == 0",
                         w->dtype == SMC_Q8_0 ? 32 : 256);
+    // prefill-sized batches over Q4_K: the quantised rows go through the tcgen05 kernel (their values d * q are exact in
+    // its fp16 pairs), three times the rate of the int8 mma.sync kernels; same parity bound, not the same bits as a
+    // small batch (the products are the same, their fp32 summation is not)
+    if (ctx->q8_prefill_tc && a->M >= 64 && smc_prefill_supported(w, a->M))
+        return smc_launch_prefill_q4k_q8(ctx, a, w, d_out, static_cast<cudaStream_t>(stream));
     return smc_launch_gemv_q8(ctx, a, w, d_out, static_cast<cudaStream_t>(stream));
 }
 
@@ -496,6 +502,7 @@ static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, fl
             *fused = true;
             return smc_launch_gemv_tma_xg(ctx, ctx->act, nullptr, w, d_out, gd, s);
         }
+        if (ctx->q8_prefill_tc && M >= 64 && smc_prefill_supported(w, M)) return smc_launch_prefill_q4k_q8(ctx, ctx->act, w, d_out, s, true);
         return smc_launch_gemv_q8(ctx, ctx->act, w, d_out, s);
     }
     default: return smc_fail(ctx, SMC_E_INVALID, "qmatmul: unknown mode %d", mode);

@@ -89,6 +89,7 @@ struct smc_ctx {
     int tma_pre = 1;                              // stages requested before the activation loads are issued
     int attn_mma = 1;                             // prompt attention on the tensor cores (0: the fp32 CUDA-core kernel)
     int tma_cluster = 1;                          // one-row kernel: SM pairs share the quantisation of a long fp32 row
+    int q8_prefill_tc = 1;                        // SMC_ACT_Q8, Q4_K, 64 rows and more: contraction on the tcgen05 kernel
     int attn_hpc = 0;                             // query heads per CTA of that kernel: 0 = two where heads share a KV head, 1 = always one
     int mt_ring = 0;                              // 2..32 rows, weights through the bulk-copy ring: 0 never, 1 Q4_K, 2 every format
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax
@@ -146,6 +147,7 @@ int smc_qmatmul_dev_gather(smc_ctx *, const float *d_in, const smc_weight *, flo
                            const smc_gather_dev *, bool *fused);
 bool smc_prefill_supported(const smc_weight *, int M);
 int smc_launch_prefill_q4k(smc_ctx *, const float *x, const smc_weight *, float *out, int M, cudaStream_t s);
+int smc_launch_prefill_q4k_q8(smc_ctx *, const smc_q8act *a, const smc_weight *, float *out, cudaStream_t s, bool scratch_locked = false);
 bool smc_mma_supported(const smc_weight *, int M);
 bool smc_mt_supported(const smc_weight *, int M);
 bool smc_sdpa_prefill_mma_supported(int nh, int nkv, int hd);

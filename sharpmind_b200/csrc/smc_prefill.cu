@@ -548,15 +548,34 @@ static int ensure_scratch(smc_ctx *ctx, size_t bytes)
     return SMC_OK;
 }
 
-int smc_launch_prefill_q4k(smc_ctx *ctx, const float *x, const smc_weight *w, float *out, int M, cudaStream_t s)
+// Q8_0 activation rows back to fp32 (x^ = d * q, exact: an 11-bit scale times an 8-bit code), four values per thread.
+__global__ void __launch_bounds__(256) dequant_q8_rows_kernel(const int8_t *__restrict__ q, const float *__restrict__ d,
+                                                              float *__restrict__ out, long long nquads)
+{
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= nquads) return;
+    const char4 c = reinterpret_cast<const char4 *>(q)[t];
+    const float dd = d[t >> 3];
+    reinterpret_cast<float4 *>(out)[t] = make_float4(dd * (float)c.x, dd * (float)c.y, dd * (float)c.z, dd * (float)c.w);
+}
+
+// x: fp32 activations [M, K]; or, when `a` is given, the rows it holds: they are expanded to fp32 in the scratch first
+// (their values d * q are exact in the fp16 pairs of the activation image, so the contraction sees exactly the
+// quantised activations).
+static int launch_prefill(smc_ctx *ctx, const float *x, const smc_q8act *a, const smc_weight *w, float *out, int M, cudaStream_t s,
+                          bool scratch_locked = false)
 {
     if (!smc_prefill_supported(w, M)) return smc_fail(ctx, SMC_E_UNSUPPORTED, "tensor-core matmul needs Q4_K, N %% 128 == 0, K %% 256 == 0");
     if (reinterpret_cast<uintptr_t>(x) & 15) return smc_fail(ctx, SMC_E_INVALID, "tensor-core matmul needs 16-byte aligned activations");
     const int N = w->N, K = w->K, ntt = (M + TN - 1) / TN, nsb = K / 256;
     const size_t img_halves = (size_t)ntt * TN * K * 2, mimg_halves = (size_t)ntt * nsb * 2 * TN * 16;
     const size_t scale_off = (img_halves + mimg_halves) * sizeof(__half);
-    const size_t bytes = scale_off + (size_t)ntt * TN * sizeof(float);
-    {
+    const size_t x_off = (scale_off + (size_t)ntt * TN * sizeof(float) + 255) & ~(size_t)255;
+    const size_t bytes = x_off + (a ? (size_t)M * K * sizeof(float) : 0);
+    if (scratch_locked) {  // the caller holds mu_scratch (its own scratch rows are the input)
+        int rc = ensure_scratch(ctx, bytes);
+        if (rc) return rc;
+    } else {
         std::lock_guard<std::mutex> lock(ctx->mu_scratch);
         int rc = ensure_scratch(ctx, bytes);
         if (rc) return rc;
@@ -564,6 +583,12 @@ int smc_launch_prefill_q4k(smc_ctx *ctx, const float *x, const smc_weight *w, fl
     __half *img = reinterpret_cast<__half *>(ctx->d_prefill);
     __half *mimg = img + img_halves;
     float *scale = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ctx->d_prefill) + scale_off);
+    if (a) {
+        float *xd = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ctx->d_prefill) + x_off);
+        const long long nquads = (long long)M * K / 4;
+        dequant_q8_rows_kernel<<<(unsigned)((nquads + 255) / 256), 256, 0, s>>>(a->q, a->d, xd, nquads);
+        x = xd;
+    }
     prefill_scale_kernel<<<M, 256, 0, s>>>(x, M, K, scale);
     prefill_image_kernel<<<ntt * nsb, 256, 0, s>>>(x, M, K, scale, img, mimg);
     static bool attr_set = false;
@@ -574,4 +599,16 @@ int smc_launch_prefill_q4k(smc_ctx *ctx, const float *x, const smc_weight *w, fl
     prefill_q4k_kernel<<<(N / TM) * ntt, THREADS, SMEM_BYTES, s>>>(w->d_raw, img, mimg, scale, out, N, K, M, ntt, ctx->d_status);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
+}
+
+int smc_launch_prefill_q4k(smc_ctx *ctx, const float *x, const smc_weight *w, float *out, int M, cudaStream_t s)
+{
+    return launch_prefill(ctx, x, nullptr, w, out, M, s);
+}
+
+// The same contraction over quantised activation rows (SMC_ACT_Q8 at prefill sizes): out = W . (d * q).
+int smc_launch_prefill_q4k_q8(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, float *out, cudaStream_t s, bool scratch_locked)
+{
+    if (a->K != w->K) return smc_fail(ctx, SMC_E_INVALID, "tensor-core matmul: activations have K=%d, weight has K=%d", a->K, w->K);
+    return launch_prefill(ctx, nullptr, a, w, out, a->M, s, scratch_locked);
 }

@@ -102,3 +102,33 @@ def test_tc_matmul_rejects_other_shapes(oracle, cuda, dev):
     with pytest.raises(ops.NotSupportedException):
         dev.qmatmul_tc(to_dev(synth.normal("prefill", "xr", (4, 256))), w)
     cuda.release(w)
+
+
+@pytest.mark.parametrize("n,k,m", [(256, 2048, 64), (128, 4096, 300), (384, 1024, 129)])
+def test_quantised_activations_at_prefill_sizes_run_on_the_tensor_cores(oracle, cuda, dev, n, k, m):
+    """SMC_ACT_Q8 over Q4_K at 64 rows and more: the Q8_0 activation rows go through the tcgen05 kernel (d * q is exact in
+    its fp16 pairs).  Against the oracle on the dequantised rows at the mode's bound; against the int8 kernels of the same
+    library (option off) to a few ulps of the row scale; and the two entry points (fp32 rows in, Q8 rows in) bit for bit."""
+    raw = oracle.quantize(Q4_K, synth.normal("prefill", f"wq{n}x{k}", (n, k), 0.02))
+    x = synth.normal("prefill", f"xq{m}x{k}", (m, k))
+    w = cuda.register(raw, Q4_K, n, k)
+    xd = to_dev(x)
+    got = dev.qmatmul(xd, w, ops.Mode.ACT_Q8).cpu().numpy()
+    xq = oracle.quantize_rows_q8_0(x, m, k)
+    from tests.gpu_util import Q8_0
+    xhat = np.stack([oracle.dequantize(Q8_0, xq[r], k) for r in range(m)])
+    want = oracle.qmatmul(Q4_K, xhat, raw, m, k, n)
+    bound = row_norm_bound(oracle, Q4_K, raw, n, k, xhat)
+    assert np.all(np.abs(got - want) <= bound), float(np.max(np.abs(got - want) / bound))
+    act = ops.Q8Act(cuda, m, k)
+    dev.quantize_q8(xd, act, k)
+    assert np.array_equal(dev.qmatmul_q8(act, w).cpu().numpy().view(np.uint32), got.view(np.uint32))
+    cuda.set_option("q8_prefill_tensor_cores", 0)
+    try:
+        ints = dev.qmatmul_q8(act, w).cpu().numpy()
+    finally:
+        cuda.set_option("q8_prefill_tensor_cores", 1)
+    assert np.all(np.abs(ints - got) <= bound)
+    act.close()
+    cuda.release(w)
+    assert cuda.device_status() == 0
