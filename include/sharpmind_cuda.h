@@ -98,6 +98,9 @@ SMC_API const char *smc_last_error(smc_ctx *ctx);
  *   "q8_prefill_tensor_cores"  1 (default): SMC_ACT_Q8 over Q4_K at 64 rows and more runs the tcgen05 kernel on the Q8_0
  *                           activation rows (d * q is exact in its fp16 pairs; same parity bound as the int8 kernels, other
  *                           summation order); 0: the int8 mma.sync kernels at every batch size
+ *   "f32_prefill_int8_digits"  1 (default): SMC_ACT_F32 at 64 rows and more, where no tcgen05 kernel takes the format or
+ *                           shape, splits the fp32 rows into three int8 digit planes (fp32 accuracy) and runs the int8
+ *                           tensor-core kernels once per plane; 0: the CUDA-core kernel at every batch size
  *   "prompt_attention_mma"  causal attention of a prompt chunk: 1 (default) bf16 tensor-core MMAs on operands split three
  *                           ways (fp32-grade accuracy), 0 the fp32 CUDA-core kernel
  *   "prompt_attention_heads_per_cta"  0 (default): a CTA of that kernel takes two query heads that share a KV head where

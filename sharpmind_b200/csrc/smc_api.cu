@@ -208,6 +208,7 @@ int smc_set_option(smc_ctx *ctx, const char *name, int value)
     else if (!strcmp(name, "prompt_attention_mma")) ctx->attn_mma = value ? 1 : 0;
     else if (!strcmp(name, "gemv_pair_staging")) ctx->tma_cluster = value < 0 ? 0 : value;
     else if (!strcmp(name, "q8_prefill_tensor_cores")) ctx->q8_prefill_tc = value ? 1 : 0;
+    else if (!strcmp(name, "f32_prefill_int8_digits")) ctx->f32_digits = value ? 1 : 0;
     else if (!strcmp(name, "prompt_attention_heads_per_cta")) ctx->attn_hpc = value == 1 ? 1 : 0;
     else if (!strcmp(name, "small_batch_ring")) ctx->mt_ring = value >= 0 && value <= 2 ? value : 0;
     else return smc_fail(ctx, SMC_E_INVALID, "set_option: unknown option '%s'", name);
@@ -230,6 +231,8 @@ void smc_destroy(smc_ctx *ctx)
     cudaFree(ctx->d_status);
     if (ctx->h_pin) cudaFreeHost(ctx->h_pin);
     smc_q8act_free(ctx->act);
+    for (smc_q8act *a : ctx->digits) smc_q8act_free(a);
+    cudaFree(ctx->d_digit_out);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -453,6 +456,44 @@ int smc_qmatmul_q8_dev(smc_ctx *ctx, const smc_q8act *a, const smc_weight *w, fl
     return smc_launch_gemv_q8(ctx, a, w, d_out, static_cast<cudaStream_t>(stream));
 }
 
+// SMC_ACT_F32 at prefill sizes over a format without a tcgen05 kernel: the fp32 rows become three int8 digit planes
+// (x = d1 q1 + d2 q2 + d3 q3 to 6e-8 of a block's largest value), each plane goes through the integer tensor-core
+// kernels and the three products are added, smallest last.  Three passes of the int8 kernels instead of M / 8 passes
+// of the CUDA-core kernel over the weights; same parity bound as that kernel (tested), other bits.
+static int qmatmul_f32_digits(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, cudaStream_t s)
+{
+    std::lock_guard<std::mutex> lock(ctx->mu_scratch);  // held until everything is queued, like the Q8 scratch
+    int rc;
+    for (int i = 0; i < 3; ++i) {
+        smc_q8act *&a = ctx->digits[i];
+        if (a && a->max_rows >= M && a->max_k >= w->K) continue;
+        const int rows = a && a->max_rows > M ? a->max_rows : M, k = a && a->max_k > w->K ? a->max_k : w->K;
+        if (a) {  // growing allocates: make the first call of a new size outside stream capture
+            cudaDeviceSynchronize();
+            smc_q8act_free(a);
+            a = nullptr;
+        }
+        if ((rc = smc_q8act_alloc(ctx, rows, k, &a))) return rc;
+    }
+    const size_t out_bytes = (size_t)M * w->N * sizeof(float);
+    if (ctx->digit_out_cap < out_bytes) {
+        if (ctx->d_digit_out) {
+            cudaDeviceSynchronize();
+            cudaFree(ctx->d_digit_out);
+            ctx->d_digit_out = nullptr, ctx->digit_out_cap = 0;
+        }
+        SMC_CUDA(ctx, cudaMalloc(&ctx->d_digit_out, out_bytes));
+        ctx->digit_out_cap = out_bytes;
+    }
+    if ((rc = smc_launch_quantize_q8_digits(ctx, d_in, M, w->K, ctx->digits, s))) return rc;
+    if ((rc = smc_launch_gemv_q8(ctx, ctx->digits[0], w, d_out, s))) return rc;
+    for (int i = 1; i < 3; ++i) {
+        if ((rc = smc_launch_gemv_q8(ctx, ctx->digits[i], w, ctx->d_digit_out, s))) return rc;
+        if ((rc = smc_add_dev(ctx, d_out, ctx->d_digit_out, (int64_t)M * w->N, s))) return rc;
+    }
+    return SMC_OK;
+}
+
 // `gd` (row-split across GPUs): when the one-row TMA kernel runs, it also exchanges the output slice with the
 // peers and *fused is set; otherwise the caller launches the exchange after this returns.
 static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, float *d_out, int M, int mode,
@@ -464,6 +505,7 @@ static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, fl
         // prefill-sized batches of Q4_K run on the tcgen05 tensor cores (same parity bound, see smc_prefill.cu)
         if (M >= 64 && smc_prefill_supported(w, M) && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
             return smc_launch_prefill_q4k(ctx, d_in, w, d_out, M, s);
+        if (M >= 64 && ctx->f32_digits && w->fast && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) return qmatmul_f32_digits(ctx, d_in, w, d_out, M, s);
         if (w->fast && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) return smc_launch_gemv_f32(ctx, d_in, w, d_out, M, s);
         // shapes the vector kernels do not take (ragged K, rows that start inside a block) run in the
         // reference's own order instead

@@ -82,6 +82,10 @@ struct smc_ctx {
     size_t h_pin_cap = 0;
     // scratch owned by the context
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
+    smc_q8act *digits[3] = {nullptr, nullptr, nullptr};  // int8 digit planes of fp32 activations (SMC_ACT_F32 at prefill sizes)
+    float *d_digit_out = nullptr;      // one plane's product [M, N]
+    size_t digit_out_cap = 0;
+    int f32_digits = 1;                // that path on (0: the CUDA-core kernel at every batch size)
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
     bool use_pdl = true;               // programmatic dependent launch (smc_set_option "pdl")
     int tma_slots = 0, tma_ss = 0, tma_ctas = 0;  // one-row GEMV ring geometry and grid, 0 = built-in choice (smc_set_option)
@@ -159,6 +163,7 @@ int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *ou
                         cudaStream_t s);
 int smc_launch_add_rmsnorm_q8(smc_ctx *ctx, float *d_x, const float *d_y, const float *d_w, float *d_out, int rows, int n, float eps,
                               smc_q8act *a, cudaStream_t s);
+int smc_launch_quantize_q8_digits(smc_ctx *ctx, const float *x, int M, int K, smc_q8act *const a[3], cudaStream_t s);
 int smc_launch_swiglu_quantize_q8(smc_ctx *ctx, const float *gate, const float *up, int M, int K, int ld, smc_q8act *a,
                                   cudaStream_t s);
 int smc_launch_quantize_q8(smc_ctx *, const float *x, int M, int K, smc_q8act *, cudaStream_t s);

@@ -114,6 +114,62 @@ __global__ void __launch_bounds__(256) quantize_q8_vec_kernel(const float *__res
     }
 }
 
+// fp32 rows as three Q8_0-shaped "digit" planes: per 32-element block x = d1 q1 + d2 q2 + d3 q3 + r with d1 = amax / 127,
+// d2 = d1 / 254, d3 = d2 / 254 and |r| <= d3 / 2 = amax / 1.6e7, i.e. the activations to fp32 accuracy as int8 operands.
+// The integer kernels run once per plane and the three results add up to the fp32-activation product (SMC_ACT_F32 at
+// prefill sizes over formats without a tcgen05 kernel).  Eight threads per block, four values each.
+struct DigitPlane {
+    int8_t *q;
+    float *d, *sd;
+    int16_t *s16;
+};
+__global__ void __launch_bounds__(256) quantize_q8_digits_kernel(const float *__restrict__ x, DigitPlane p0, DigitPlane p1, DigitPlane p2,
+                                                                 long long nquads)
+{
+    smc_grid_dep_sync();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long base = (long long)blockIdx.x * blockDim.x; base < nquads; base += stride) {
+        const long long t = base + threadIdx.x;
+        const bool live = t < nquads;  // uniform over each group of eight threads
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {
+            const float4 f = *reinterpret_cast<const float4 *>(x + t * 4);
+            v[0] = f.x, v[1] = f.y, v[2] = f.z, v[3] = f.w;
+        }
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        float d = __fdiv_rn(amax, 127.0f);
+        if (!(amax > 0.0f) || !(amax < INFINITY)) d = 1.0f;
+        const DigitPlane planes[3] = {p0, p1, p2};
+#pragma unroll
+        for (int pl = 0; pl < 3; ++pl) {
+            int q[4], sum = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                q[i] = max(-127, min(127, __float2int_rn(__fdiv_rn(v[i], d))));
+                v[i] = fmaf(-d, (float)q[i], v[i]);  // what this digit leaves
+                sum += q[i];
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);  // half block
+            const int total = sum + __shfl_xor_sync(0xffffffffu, sum, 4);
+            if (live) {
+                const long long blk = t >> 3;
+                reinterpret_cast<uint32_t *>(planes[pl].q)[t] =
+                    (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+                if ((t & 3) == 0) planes[pl].s16[blk * 2 + ((t >> 2) & 1)] = (int16_t)sum;
+                if ((t & 7) == 0) {
+                    planes[pl].d[blk] = d;
+                    planes[pl].sd[blk] = d * (float)total;
+                }
+            }
+            d = __fdiv_rn(d, 254.0f);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------- weights -> Q8_0
 __global__ void __launch_bounds__(256) wq_q8_0_kernel(const float *__restrict__ v, uint8_t *__restrict__ out,
                                                       long long nblocks)
@@ -356,6 +412,25 @@ int smc_launch_quantize_q8(smc_ctx *ctx, const float *x, int M, int K, smc_q8act
     else
         smc_launch_dep(ctx->use_pdl, quantize_q8_kernel, dim3(grid_for(nblocks, 8, ctx->sm_count * 8)), dim3(256), 0, s, x,
                        (const float *)nullptr, K, K, a->q, a->d, a->dbits, a->sd, a->s16, nblocks);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+// x [M, K] fp32 -> the three digit planes a[0..2] (each a q8act of at least M x K; their fp16 scale bits are not
+// written: only the several-row integer kernels, which read the fp32 scales, may consume them).
+int smc_launch_quantize_q8_digits(smc_ctx *ctx, const float *x, int M, int K, smc_q8act *const a[3], cudaStream_t s)
+{
+    if (K % 32) return smc_fail(ctx, SMC_E_UNSUPPORTED, "Q8 activations need K %% 32 == 0 (K = %d)", K);
+    DigitPlane p[3];
+    for (int i = 0; i < 3; ++i) {
+        if (M > a[i]->max_rows || K > a[i]->max_k || (size_t)M * K > (size_t)a[i]->max_rows * a[i]->max_k)
+            return smc_fail(ctx, SMC_E_INVALID, "q8act buffer %d x %d too small for %d x %d", a[i]->max_rows, a[i]->max_k, M, K);
+        a[i]->M = M, a[i]->K = K;
+        p[i] = DigitPlane{a[i]->q, a[i]->d, a[i]->sd, a[i]->s16};
+    }
+    const long long nquads = (long long)M * K / 4;
+    smc_launch_dep(ctx->use_pdl, quantize_q8_digits_kernel, dim3(grid_for(nquads, 256, ctx->sm_count * 8)), dim3(256), 0, s, x, p[0], p[1],
+                   p[2], nquads);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
