@@ -20,7 +20,8 @@
  * Threads and streams.  A context may be used from several host threads.  The host-pointer entry points
  * (smc_*_host), registration and lookup are serialised by the context.  The device entry points (*_dev) only
  * queue work on the caller's stream; those that keep intermediate data in buffers owned by the context
- * (smc_qmatmul_dev with SMC_ACT_Q8 for M > 1 or shapes the one-row kernel does not take, smc_qmatmul_tc_dev,
+ * (smc_qmatmul_dev with SMC_ACT_Q8 or SMC_ACT_F32 for M > 1 or shapes the one-row kernel does not take, smc_qmatmul_q8_dev
+ * over Q4_K at 64 rows and more, smc_qmatmul_tc_dev,
  * smc_sdpa_decode_dev, smc_argmax_dev, smc_decode_step, smc_forward_last_logits) reuse those buffers in stream
  * order: all such calls on one context must go to ONE stream (or be ordered by events).  Work that is to run
  * concurrently on several streams takes one context per stream.
@@ -98,9 +99,11 @@ SMC_API const char *smc_last_error(smc_ctx *ctx);
  *   "q8_prefill_tensor_cores"  1 (default): SMC_ACT_Q8 over Q4_K at 64 rows and more runs the tcgen05 kernel on the Q8_0
  *                           activation rows (d * q is exact in its fp16 pairs; same parity bound as the int8 kernels, other
  *                           summation order); 0: the int8 mma.sync kernels at every batch size
- *   "f32_prefill_int8_digits"  1 (default): SMC_ACT_F32 at 64 rows and more, where no tcgen05 kernel takes the format or
- *                           shape, splits the fp32 rows into three int8 digit planes (fp32 accuracy) and runs the int8
- *                           tensor-core kernels once per plane; 0: the CUDA-core kernel at every batch size
+ *   "f32_prefill_int8_digits"  1 (default): SMC_ACT_F32 with two rows and more, where no tcgen05 kernel takes the format
+ *                           or shape, splits the fp32 rows into three int8 digit planes (fp32 accuracy) and runs the int8
+ *                           tensor-core kernels once per plane (the planes live in the context's scratch, like the
+ *                           SMC_ACT_Q8 activations of a several-row call); 0: the CUDA-core kernel at every batch size;
+ *                           a value above 1: the row count to start from
  *   "prompt_attention_mma"  causal attention of a prompt chunk: 1 (default) bf16 tensor-core MMAs on operands split three
  *                           ways (fp32-grade accuracy), 0 the fp32 CUDA-core kernel
  *   "prompt_attention_heads_per_cta"  0 (default): a CTA of that kernel takes two query heads that share a KV head where

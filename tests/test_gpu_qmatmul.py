@@ -126,9 +126,9 @@ def test_q8_0_prompt_sized_batches_keep_the_small_batch_bits(oracle, cuda, dev, 
 
 
 @pytest.mark.parametrize("dtype,n,k", [(Q6_K, 64, 2048), (Q8_0, 96, 1024), (Q4_K, 96, 4096), (Q6_K, 40, 14336)])
-@pytest.mark.parametrize("m", [64, 100])
-def test_fp32_activations_at_prefill_sizes_as_int8_digit_planes(oracle, cuda, dev, dtype, n, k, m):
-    """SMC_ACT_F32 at 64 rows and more, where no tcgen05 kernel takes the format or shape: the fp32 rows go through the
+@pytest.mark.parametrize("m", [2, 7, 64, 100])
+def test_fp32_activations_as_int8_digit_planes(oracle, cuda, dev, dtype, n, k, m):
+    """SMC_ACT_F32 with two rows and more, where no tcgen05 kernel takes the format or shape: the fp32 rows go through the
     int8 tensor-core kernels as three digit planes.  Same per-output bound against the oracle as the CUDA-core kernel it
     replaces, and agreement with that kernel (option off) inside twice the bound; rows with a zero block, a huge value
     and tiny values included."""
@@ -138,8 +138,8 @@ def test_fp32_activations_at_prefill_sizes_as_int8_digit_planes(oracle, cuda, de
     w = cuda.register(raw, dtype, n, k)
     x = synth.normal("gpu", f"dgx{dtype}_{k}_{m}", (m, k))
     x[1, :32] = 0.0
-    x[2, 5] = 3.0e4
-    x[3] *= 1.0e-6
+    x[0, 5] = 3.0e4
+    x[m - 1] *= 1.0e-6
     xd = to_dev(x)
     got = dev.qmatmul(xd, w, Mode.ACT_F32).cpu().numpy()
     want = oracle.qmatmul(dtype, x, raw, m, k, n)
@@ -151,7 +151,7 @@ def test_fp32_activations_at_prefill_sizes_as_int8_digit_planes(oracle, cuda, de
     finally:
         cuda.set_option("f32_prefill_int8_digits", 1)
     assert np.all(np.abs(old.astype(np.float64) - got) <= 2 * bound)
-    assert not np.array_equal(bits(old), bits(got)) or m < 64  # the option really switches kernels
+    assert not np.array_equal(bits(old), bits(got))  # the option really switches kernels
     cuda.release(w)
     assert cuda.device_status() == 0
 
