@@ -112,7 +112,8 @@ class CudaContext:
         self.check(self.lib.smc_synchronize(self.h))
 
     def set_option(self, name: str, value: int):
-        """smc_set_option: "pdl", "gemv_slots", "gemv_steps_per_stage", "gemv_ctas_per_sm"."""
+        """smc_set_option: per-context tuning and kernel-selection switches (the names and their meaning are listed
+        with the entry point in the C header); none of them changes a result beyond its mode's bound."""
         self.check(self.lib.smc_set_option(self.h, name.encode(), int(value)))
 
     def device_status(self) -> int:
@@ -200,14 +201,18 @@ class QuantizationOps:
     def QuantizedMatMulHandle(self, input, weight: "Weight", output, M, K, N, mode=None):
         """The same slot for a layer that kept the `Weight` its registration returned (smc_qmatmul_host_w): host
         activations in, host results out, no lookup by pointer; works for weights registered from device memory."""
-        x = _f32(input)
+        # (a linear layer calls this once per matmul: the checks are kept to attribute reads, and the addresses come from
+        # the array interface rather than from a ctypes view object)
+        x = input if (type(input) is np.ndarray and input.dtype == np.float32 and input.flags.c_contiguous) else _f32(input)
         if x.size != M * K:
             raise ArgumentException(f"input holds {x.size} values, expected M*K = {M * K}")
-        if not (isinstance(output, np.ndarray) and output.dtype == np.float32 and output.flags.c_contiguous
+        if not (type(output) is np.ndarray and output.dtype == np.float32 and output.flags.c_contiguous
                 and output.size == M * N):
             raise ArgumentException("output must be a C-contiguous float32 array of M*N values")
-        self.ctx.check(self.ctx.lib.smc_qmatmul_host_w(self.ctx.h, x.ctypes.data, weight.handle, output.ctypes.data,
-                                                       M, K, N, self.mode if mode is None else int(mode)))
+        rc = self.ctx.lib.smc_qmatmul_host_w(self.ctx.h, x.__array_interface__["data"][0], weight.handle,
+                                             output.__array_interface__["data"][0], M, K, N, self.mode if mode is None else int(mode))
+        if rc:
+            self.ctx.check(rc)
         return output
 
     def QuantizedMatMulQ8_0(self, input, rawWeights, output, M, K, N):
