@@ -92,14 +92,19 @@ int d2h(smc_ctx *ctx, void *dst, const void *src, size_t bytes)
 
 // Page-locked host memory (cudaHostAlloc / cudaHostRegister by the caller) is copied from and to directly: no bounce
 // buffer, no host memcpy.  Anything else (ordinary pageable memory, or a pointer the runtime cannot classify) is not.
-bool host_is_pinned(const void *p)
+// The answer for the caller's last few buffers is remembered (a layer calls with the same rows again and again, and the
+// query costs about a microsecond): a stale answer only chooses the other, equally correct, way of copying.
+bool host_is_pinned(smc_ctx *ctx, const void *p)
 {
+    for (int i = 0; i < 4; ++i)
+        if (ctx->pin_seen[i] == p) return ctx->pin_is[i];
     cudaPointerAttributes at{};
-    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
-        cudaGetLastError();  // an unknown pointer is not an error of this call
-        return false;
-    }
-    return at.type == cudaMemoryTypeHost;
+    bool pinned = false;
+    if (cudaPointerGetAttributes(&at, p) == cudaSuccess) pinned = at.type == cudaMemoryTypeHost;
+    else cudaGetLastError();  // an unknown pointer is not an error of this call
+    const int slot = ctx->pin_next++ & 3;
+    ctx->pin_seen[slot] = p, ctx->pin_is[slot] = pinned;
+    return pinned;
 }
 
 bool known_dtype(int dtype) { return dtype == SMC_Q8_0 || dtype == SMC_Q4_K || dtype == SMC_Q6_K; }
@@ -753,7 +758,7 @@ static int qmatmul_host_impl(smc_ctx *ctx, const float *input, const smc_weight 
     if ((rc = ensure_dev(ctx, &ctx->d_stage_out, &ctx->stage_out_cap, out_bytes))) return rc;
     // one wait per call: input copy, kernels and result copy are ordered by the stream.  Page-locked caller buffers
     // are the source and the target of the copies themselves; pageable ones go through the context's bounce buffer.
-    const bool pin_in = host_is_pinned(input), pin_out = host_is_pinned(output);
+    const bool pin_in = host_is_pinned(ctx, input), pin_out = host_is_pinned(ctx, output);  // under ctx->mu
     if (pin_in) SMC_CUDA(ctx, cudaMemcpyAsync(ctx->d_stage_in, input, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
     else if ((rc = h2d_queued(ctx, ctx->d_stage_in, input, in_bytes, pin_out ? in_bytes : out_bytes))) return rc;
     if ((rc = qmatmul_impl(ctx, ctx->d_stage_in, w, ctx->d_stage_out, M, mode, ctx->stream))) {

@@ -82,6 +82,9 @@ struct smc_ctx {
     size_t h_pin_cap = 0;
     // scratch owned by the context
     smc_q8act *act = nullptr;          // activations of smc_qmatmul_dev(SMC_ACT_Q8)
+    const void *pin_seen[4] = {nullptr, nullptr, nullptr, nullptr};  // host buffers lately classified as page-locked or not (under mu)
+    bool pin_is[4] = {false, false, false, false};
+    unsigned pin_next = 0;
     smc_q8act *digits[3] = {nullptr, nullptr, nullptr};  // int8 digit planes of fp32 activations (SMC_ACT_F32 at prefill sizes)
     float *d_digit_out = nullptr;      // one plane's product [M, N]
     size_t digit_out_cap = 0;
