@@ -214,6 +214,7 @@ int smc_set_option(smc_ctx *ctx, const char *name, int value)
     else if (!strcmp(name, "gemv_pair_staging")) ctx->tma_cluster = value < 0 ? 0 : value;
     else if (!strcmp(name, "q8_prefill_tensor_cores")) ctx->q8_prefill_tc = value ? 1 : 0;
     else if (!strcmp(name, "f32_prefill_int8_digits")) ctx->f32_digits = value < 0 ? 0 : value;
+    else if (!strcmp(name, "f32_one_row_digits_min_mb")) ctx->f32_digits_row_mb = value < 0 ? 0 : value;
     else if (!strcmp(name, "prompt_attention_heads_per_cta")) ctx->attn_hpc = value == 1 ? 1 : 0;
     else if (!strcmp(name, "small_batch_ring")) ctx->mt_ring = value >= 0 && value <= 2 ? value : 0;
     else return smc_fail(ctx, SMC_E_INVALID, "set_option: unknown option '%s'", name);
@@ -511,6 +512,12 @@ static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, fl
         if (M >= 64 && smc_prefill_supported(w, M) && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
             return smc_launch_prefill_q4k(ctx, d_in, w, d_out, M, s);
         if (ctx->f32_digits && M >= (ctx->f32_digits > 1 ? ctx->f32_digits : 2) && w->fast && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
+            return qmatmul_f32_digits(ctx, d_in, w, d_out, M, s);
+        // one row over a large matrix: three passes of the quantised one-row kernel beat one pass of the fp32 one
+        // (from about 32 MB on for the K-quants: 28672 x 4096 Q4_K 66 -> 47 us, 57344 x 8192 249 -> 140 us; small matrices are
+        // launch-bound and Q8_0 gains nothing)
+        if (M == 1 && ctx->f32_digits && ctx->f32_digits_row_mb > 0 && w->dtype != SMC_Q8_0 && w->fast && smc_tma_supported(w, 1) &&
+            smc_raw_tensor_bytes(w->dtype, w->N, w->K) >= (int64_t)ctx->f32_digits_row_mb << 20 && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
             return qmatmul_f32_digits(ctx, d_in, w, d_out, M, s);
         if (w->fast && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) return smc_launch_gemv_f32(ctx, d_in, w, d_out, M, s);
         // shapes the vector kernels do not take (ragged K, rows that start inside a block) run in the

@@ -89,6 +89,7 @@ struct smc_ctx {
     float *d_digit_out = nullptr;      // one plane's product [M, N]
     size_t digit_out_cap = 0;
     int f32_digits = 1;                // that path on (0: the CUDA-core kernel at every batch size)
+    int f32_digits_row_mb = 32;        // one row: K-quant matrices of at least this many MB take that path too (0: never)
     int *d_status = nullptr;           // raised by a kernel whose bounded wait ran out
     bool use_pdl = true;               // programmatic dependent launch (smc_set_option "pdl")
     int tma_slots = 0, tma_ss = 0, tma_ctas = 0;  // one-row GEMV ring geometry and grid, 0 = built-in choice (smc_set_option)

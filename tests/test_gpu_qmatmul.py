@@ -453,6 +453,19 @@ def test_llama8b_ffn_shapes_sampled_rows_and_linearity(oracle, cuda, dev):
                 wrow = oracle.dequantize(dtype, raw[r * (len(raw) // n):(r + 1) * (len(raw) // n)], k)
                 tol = 1e-5 * np.linalg.norm(wrow) * np.linalg.norm(x, axis=1)
                 assert np.all(np.abs(got[:, r] - want) <= tol)
+        # one row over a matrix this large also goes through the digit planes; the fp32 one-row kernel is the option-off form
+        one = dev.qmatmul(to_dev(x[:1]), w, Mode.ACT_F32).cpu().numpy()
+        cuda.set_option("f32_one_row_digits_min_mb", 0)
+        try:
+            plain = dev.qmatmul(to_dev(x[:1]), w, Mode.ACT_F32).cpu().numpy()
+        finally:
+            cuda.set_option("f32_one_row_digits_min_mb", 32)
+        assert np.array_equal(bits(one), bits(plain)) == (len(raw) < (32 << 20))  # the 33.0 MB Q4_K matrix is just below the limit
+        for r in rows:
+            want = oracle.qmatmul(dtype, x[:1], raw, 1, k, n, cols=(r, r + 1))[0, r]
+            wrow = oracle.dequantize(dtype, raw[r * (len(raw) // n):(r + 1) * (len(raw) // n)], k)
+            tol = 1e-5 * np.linalg.norm(wrow) * np.linalg.norm(x[0])
+            assert abs(one[0, r] - want) <= tol and abs(plain[0, r] - want) <= tol
         a = np.float32(0.5)
         xs = to_dev(np.stack([x[0], x[1], a * x[0] + x[1]]))
         y = dev.qmatmul(xs, w, Mode.ACT_F32).cpu().numpy().astype(np.float64)
