@@ -105,8 +105,8 @@ SMC_API const char *smc_last_error(smc_ctx *ctx);
  *                           SMC_ACT_Q8 activations of a several-row call); 0: the CUDA-core kernel at every batch size;
  *                           a value above 1: the row count to start from
  *   "f32_one_row_digits_min_mb"  one row in SMC_ACT_F32 takes the same path when the K-quant matrix holds at least this many
- *                           MB (default 32: three passes of the quantised one-row kernel then beat one pass of the fp32
- *                           one); 0: never
+ *                           MB (default 32: its three digit rows as one small batch then beat the fp32 one-row kernel);
+ *                           0: never
  *   "prompt_attention_mma"  causal attention of a prompt chunk: 1 (default) bf16 tensor-core MMAs on operands split three
  *                           ways (fp32-grade accuracy), 0 the fp32 CUDA-core kernel
  *   "prompt_attention_heads_per_cta"  0 (default): a CTA of that kernel takes two query heads that share a KV head where

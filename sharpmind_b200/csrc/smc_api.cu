@@ -237,7 +237,7 @@ void smc_destroy(smc_ctx *ctx)
     cudaFree(ctx->d_status);
     if (ctx->h_pin) cudaFreeHost(ctx->h_pin);
     smc_q8act_free(ctx->act);
-    for (smc_q8act *a : ctx->digits) smc_q8act_free(a);
+    smc_q8act_free(ctx->digits);
     cudaFree(ctx->d_digit_out);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -470,18 +470,17 @@ static int qmatmul_f32_digits(smc_ctx *ctx, const float *d_in, const smc_weight 
 {
     std::lock_guard<std::mutex> lock(ctx->mu_scratch);  // held until everything is queued, like the Q8 scratch
     int rc;
-    for (int i = 0; i < 3; ++i) {
-        smc_q8act *&a = ctx->digits[i];
-        if (a && a->max_rows >= M && a->max_k >= w->K) continue;
-        const int rows = a && a->max_rows > M ? a->max_rows : M, k = a && a->max_k > w->K ? a->max_k : w->K;
+    smc_q8act *&a = ctx->digits;
+    if (!a || (size_t)a->max_rows * a->max_k < (size_t)3 * M * w->K) {
         if (a) {  // growing allocates: make the first call of a new size outside stream capture
             cudaDeviceSynchronize();
             smc_q8act_free(a);
             a = nullptr;
         }
-        if ((rc = smc_q8act_alloc(ctx, rows, k, &a))) return rc;
+        if ((rc = smc_q8act_alloc(ctx, 3 * M, w->K, &a))) return rc;
     }
-    const size_t out_bytes = (size_t)M * w->N * sizeof(float);
+    a->max_rows = (int)(((size_t)a->max_rows * a->max_k) / w->K), a->max_k = w->K;  // the same bytes, seen with this K
+    const size_t out_bytes = (size_t)3 * M * w->N * sizeof(float);
     if (ctx->digit_out_cap < out_bytes) {
         if (ctx->d_digit_out) {
             cudaDeviceSynchronize();
@@ -491,13 +490,10 @@ static int qmatmul_f32_digits(smc_ctx *ctx, const float *d_in, const smc_weight 
         SMC_CUDA(ctx, cudaMalloc(&ctx->d_digit_out, out_bytes));
         ctx->digit_out_cap = out_bytes;
     }
-    if ((rc = smc_launch_quantize_q8_digits(ctx, d_in, M, w->K, ctx->digits, s))) return rc;
-    if ((rc = smc_launch_gemv_q8(ctx, ctx->digits[0], w, d_out, s))) return rc;
-    for (int i = 1; i < 3; ++i) {
-        if ((rc = smc_launch_gemv_q8(ctx, ctx->digits[i], w, ctx->d_digit_out, s))) return rc;
-        if ((rc = smc_add_dev(ctx, d_out, ctx->d_digit_out, (int64_t)M * w->N, s))) return rc;
-    }
-    return SMC_OK;
+    // the planes are 3 M rows of one batch: the weights are read once for all three
+    if ((rc = smc_launch_quantize_q8_digits(ctx, d_in, M, w->K, a, s))) return rc;
+    if ((rc = smc_launch_gemv_q8(ctx, a, w, ctx->d_digit_out, s))) return rc;
+    return smc_launch_sum3(ctx, ctx->d_digit_out, d_out, (long long)M * w->N, s);
 }
 
 // `gd` (row-split across GPUs): when the one-row TMA kernel runs, it also exchanges the output slice with the
@@ -513,9 +509,9 @@ static int qmatmul_impl(smc_ctx *ctx, const float *d_in, const smc_weight *w, fl
             return smc_launch_prefill_q4k(ctx, d_in, w, d_out, M, s);
         if (ctx->f32_digits && M >= (ctx->f32_digits > 1 ? ctx->f32_digits : 2) && w->fast && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
             return qmatmul_f32_digits(ctx, d_in, w, d_out, M, s);
-        // one row over a large matrix: three passes of the quantised one-row kernel beat one pass of the fp32 one
-        // (from about 32 MB on for the K-quants: 28672 x 4096 Q4_K 66 -> 47 us, 57344 x 8192 249 -> 140 us; small matrices are
-        // launch-bound and Q8_0 gains nothing)
+        // one row over a large matrix: its three digit rows through the several-row integer kernel beat the fp32 one-row kernel
+        // (from about 32 MB on for the K-quants: 28672 x 4096 Q4_K 66 -> 32 us, 57344 x 8192 249 -> 98 us; small matrices are
+        // launch-bound)
         if (M == 1 && ctx->f32_digits && ctx->f32_digits_row_mb > 0 && w->dtype != SMC_Q8_0 && w->fast && smc_tma_supported(w, 1) &&
             smc_raw_tensor_bytes(w->dtype, w->N, w->K) >= (int64_t)ctx->f32_digits_row_mb << 20 && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0)
             return qmatmul_f32_digits(ctx, d_in, w, d_out, M, s);

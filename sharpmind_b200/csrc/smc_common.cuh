@@ -85,8 +85,8 @@ struct smc_ctx {
     const void *pin_seen[4] = {nullptr, nullptr, nullptr, nullptr};  // host buffers lately classified as page-locked or not (under mu)
     bool pin_is[4] = {false, false, false, false};
     unsigned pin_next = 0;
-    smc_q8act *digits[3] = {nullptr, nullptr, nullptr};  // int8 digit planes of fp32 activations (SMC_ACT_F32 at prefill sizes)
-    float *d_digit_out = nullptr;      // one plane's product [M, N]
+    smc_q8act *digits = nullptr;       // the three int8 digit planes of fp32 activations, stacked as 3 M rows (SMC_ACT_F32)
+    float *d_digit_out = nullptr;      // their products [3 M, N]
     size_t digit_out_cap = 0;
     int f32_digits = 1;                // that path on (0: the CUDA-core kernel at every batch size)
     int f32_digits_row_mb = 32;        // one row: K-quant matrices of at least this many MB take that path too (0: never)
@@ -167,7 +167,8 @@ int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *ou
                         cudaStream_t s);
 int smc_launch_add_rmsnorm_q8(smc_ctx *ctx, float *d_x, const float *d_y, const float *d_w, float *d_out, int rows, int n, float eps,
                               smc_q8act *a, cudaStream_t s);
-int smc_launch_quantize_q8_digits(smc_ctx *ctx, const float *x, int M, int K, smc_q8act *const a[3], cudaStream_t s);
+int smc_launch_quantize_q8_digits(smc_ctx *ctx, const float *x, int M, int K, smc_q8act *a, cudaStream_t s);
+int smc_launch_sum3(smc_ctx *ctx, const float *y, float *out, long long n, cudaStream_t s);
 int smc_launch_swiglu_quantize_q8(smc_ctx *ctx, const float *gate, const float *up, int M, int K, int ld, smc_q8act *a,
                                   cudaStream_t s);
 int smc_launch_quantize_q8(smc_ctx *, const float *x, int M, int K, smc_q8act *, cudaStream_t s);

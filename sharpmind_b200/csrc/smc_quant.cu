@@ -416,21 +416,35 @@ int smc_launch_quantize_q8(smc_ctx *ctx, const float *x, int M, int K, smc_q8act
     return SMC_OK;
 }
 
-// x [M, K] fp32 -> the three digit planes a[0..2] (each a q8act of at least M x K; their fp16 scale bits are not
-// written: only the several-row integer kernels, which read the fp32 scales, may consume them).
-int smc_launch_quantize_q8_digits(smc_ctx *ctx, const float *x, int M, int K, smc_q8act *const a[3], cudaStream_t s)
+// x [M, K] fp32 -> three digit planes stacked as 3 M rows of `a` (plane p in rows p M .. p M + M - 1), so that one
+// several-row matmul over `a` reads the weights once for all three; their fp16 scale bits are not written (the
+// integer kernels read the fp32 scales).
+int smc_launch_quantize_q8_digits(smc_ctx *ctx, const float *x, int M, int K, smc_q8act *a, cudaStream_t s)
 {
     if (K % 32) return smc_fail(ctx, SMC_E_UNSUPPORTED, "Q8 activations need K %% 32 == 0 (K = %d)", K);
+    if ((size_t)3 * M * K > (size_t)a->max_rows * a->max_k)
+        return smc_fail(ctx, SMC_E_INVALID, "q8act buffer %d x %d too small for %d x %d", a->max_rows, a->max_k, 3 * M, K);
+    a->M = 3 * M, a->K = K;
+    const size_t n = (size_t)M * K, nb = n / 32;
     DigitPlane p[3];
-    for (int i = 0; i < 3; ++i) {
-        if (M > a[i]->max_rows || K > a[i]->max_k || (size_t)M * K > (size_t)a[i]->max_rows * a[i]->max_k)
-            return smc_fail(ctx, SMC_E_INVALID, "q8act buffer %d x %d too small for %d x %d", a[i]->max_rows, a[i]->max_k, M, K);
-        a[i]->M = M, a[i]->K = K;
-        p[i] = DigitPlane{a[i]->q, a[i]->d, a[i]->sd, a[i]->s16};
-    }
-    const long long nquads = (long long)M * K / 4;
+    for (size_t i = 0; i < 3; ++i) p[i] = DigitPlane{a->q + i * n, a->d + i * nb, a->sd + i * nb, a->s16 + i * nb * 2};
+    const long long nquads = (long long)n / 4;
     smc_launch_dep(ctx->use_pdl, quantize_q8_digits_kernel, dim3(grid_for(nquads, 256, ctx->sm_count * 8)), dim3(256), 0, s, x, p[0], p[1],
                    p[2], nquads);
+    SMC_LAUNCH_CHECK(ctx);
+    return SMC_OK;
+}
+
+// out = (y[0] + y[1]) + y[2] over three stacked [n] results
+__global__ void __launch_bounds__(256) sum3_kernel(const float *__restrict__ y, float *__restrict__ out, long long n)
+{
+    smc_grid_dep_sync();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = (y[i] + y[n + i]) + y[2 * n + i];
+}
+int smc_launch_sum3(smc_ctx *ctx, const float *y, float *out, long long n, cudaStream_t s)
+{
+    smc_launch_dep(ctx->use_pdl, sum3_kernel, dim3(grid_for(n, 256, ctx->sm_count * 8)), dim3(256), 0, s, y, out, n);
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
 }
