@@ -107,6 +107,9 @@ SMC_API const char *smc_last_error(smc_ctx *ctx);
  *   "f32_one_row_digits_min_mb"  one row in SMC_ACT_F32 takes the same path when the K-quant matrix holds at least this many
  *                           MB (default 32: its three digit rows as one small batch then beat the fp32 one-row kernel);
  *                           0: never
+ *   "decode_gate_in_staging_max_ffn"  one sequence per step with quantised activations: the widest FFN whose SiLU-gate is
+ *                           formed while the down projection stages its activation row (default 16384); a wider one
+ *                           runs the gate as a launch of its own.  Same bits either way
  *   "prompt_attention_mma"  causal attention of a prompt chunk: 1 (default) bf16 tensor-core MMAs on operands split three
  *                           ways (fp32-grade accuracy), 0 the fp32 CUDA-core kernel
  *   "prompt_attention_heads_per_cta"  0 (default): a CTA of that kernel takes two query heads that share a KV head where

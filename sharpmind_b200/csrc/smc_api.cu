@@ -215,6 +215,7 @@ int smc_set_option(smc_ctx *ctx, const char *name, int value)
     else if (!strcmp(name, "q8_prefill_tensor_cores")) ctx->q8_prefill_tc = value ? 1 : 0;
     else if (!strcmp(name, "f32_prefill_int8_digits")) ctx->f32_digits = value < 0 ? 0 : value;
     else if (!strcmp(name, "f32_one_row_digits_min_mb")) ctx->f32_digits_row_mb = value < 0 ? 0 : value;
+    else if (!strcmp(name, "decode_gate_in_staging_max_ffn")) ctx->ffn_fuse_max = value < 0 ? 0 : value;
     else if (!strcmp(name, "prompt_attention_heads_per_cta")) ctx->attn_hpc = value == 1 ? 1 : 0;
     else if (!strcmp(name, "small_batch_ring")) ctx->mt_ring = value >= 0 && value <= 2 ? value : 0;
     else return smc_fail(ctx, SMC_E_INVALID, "set_option: unknown option '%s'", name);

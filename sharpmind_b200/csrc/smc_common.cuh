@@ -98,6 +98,7 @@ struct smc_ctx {
     int attn_mma = 1;                             // prompt attention on the tensor cores (0: the fp32 CUDA-core kernel)
     int tma_cluster = 1;                          // one-row kernel: SM pairs share the quantisation of a long fp32 row
     int q8_prefill_tc = 1;                        // SMC_ACT_Q8, Q4_K, 64 rows and more: contraction on the tcgen05 kernel
+    int ffn_fuse_max = 16384;                     // one-row decode: widest FFN whose SiLU-gate rides in the down projection's staging
     int attn_hpc = 0;                             // query heads per CTA of that kernel: 0 = two where heads share a KV head, 1 = always one
     int mt_ring = 0;                              // 2..32 rows, weights through the bulk-copy ring: 0 never, 1 Q4_K, 2 every format
     void *d_argmax = nullptr;          // chunk results and tickets of the argmax

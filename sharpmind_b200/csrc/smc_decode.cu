@@ -479,13 +479,13 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
     // One sequence with quantised activations: every elementwise step between two matmuls rides in the staging of
     // the matmul that consumes it (residual add + RMSNorm, SiLU-gate), so a layer is eight launches: joined QKV,
     // per-head norm + RoPE + append, attention, Wo, gate||up, down (+ the next layer's QKV takes its residual).
-    // (an FFN wider than 8192 keeps its SiLU-gate as a launch of its own: the down-projection's row is then too
-    // long to be worth staging through the gate in every CTA)
+    // (an FFN wider than ctx->ffn_fuse_max, 16384 by default, keeps its SiLU-gate as a launch of its own: the
+    // down-projection's row is then too long to be worth staging through the gate on every SM pair)
     bool one_row = mode == SMC_ACT_Q8 && B == 1 && H <= 8192 && !m->has_bias && smc_tma_supported(d.lm_head, 1) &&
-                   (F <= 8192 || m->qb);
+                   (F <= ctx->ffn_fuse_max || m->qb);
     for (int l = 0; l < d.n_layers && one_row; ++l)
         one_row = m->wqkv[l] && smc_tma_supported(m->wqkv[l], 1) && smc_tma_supported(m->wgu[l], 1) && m->wdown[l]->fast &&
-                  (F > 8192 || smc_tma_supported(m->wdown[l], 1));
+                  (F > ctx->ffn_fuse_max || smc_tma_supported(m->wdown[l], 1));
     if (one_row) {
         float *cur = m->x, *other = m->x2;
         const float *pending = nullptr;  // output of the previous block's down-projection, not yet added to the stream
@@ -501,7 +501,7 @@ int smc_decode_step(smc_ctx *ctx, smc_model *m, const int *d_tokens, int batch, 
             smc_norm_prologue p2{m->tmp, m->norm2[l], other, d.eps};
             SMC_TRY(smc_launch_gemv_tma_addnorm(ctx, cur, &p2, m->wgu[l], m->gu, s));
             std::swap(cur, other);
-            if (F <= 8192) {
+            if (F <= ctx->ffn_fuse_max) {
                 SMC_TRY(smc_launch_gemv_tma_swiglu(ctx, m->gu, m->gu + F, m->wdown[l], m->tmp, s));
             } else {
                 SMC_TRY(smc_launch_swiglu_quantize_q8(ctx, m->gu, m->gu + F, 1, F, 2 * F, m->qb, s));

@@ -452,12 +452,31 @@ WIDE_FFN = dict(n_layers=2, hidden=1024, n_heads=8, n_kv_heads=2, head_dim=128, 
 
 
 def test_decode_one_sequence_wide_ffn(oracle, cuda):
-    """An FFN wider than 8192 (Llama-3-8B has 14336): the one-sequence path keeps the norms in the matmul staging but
-    runs the SiLU-gate as its own launch; same bars as the fused path, four query heads per KV head."""
+    """An FFN wider than 8192 (Llama-3-8B has 14336): the one-sequence path keeps the norms in the matmul staging and,
+    up to `decode_gate_in_staging_max_ffn` (default 16384), the SiLU-gate in the down projection's staging too (the two
+    SMs of a pair share that work); above it the gate is a launch of its own.  Both forms give the same bits (the
+    staged row is quantised by the same code), same bars as the narrow FFN, four query heads per KV head."""
     import torch
 
     cfg, name = WIDE_FFN, "dec_wideffn"
     w = _weights(oracle, cfg, name)
+    # the two forms of the gate, bit for bit
+    runs = []
+    for limit in (16384, 8192):
+        cuda.set_option("decode_gate_in_staging_max_ffn", limit)
+        try:
+            d = Decoder(cuda, cfg, {k: ([a.copy() for a in v] if isinstance(v, list) else v.copy()) for k, v in w.items()}, max_batch=1)
+            tk = torch.from_numpy(synth.token_ids(name, "prompt", (1,), cfg["vocab"]).copy()).cuda()
+            outs = []
+            for pos in range(5):
+                lg, tk = d.step(tk, pos, ops.Mode.ACT_Q8)
+                outs.append(lg.clone())
+                tk = tk.clone()
+            d.close()
+            runs.append(torch.stack(outs))
+        finally:
+            cuda.set_option("decode_gate_in_staging_max_ffn", 16384)
+    assert torch.equal(runs[0], runs[1])
     ref = oracle.Decoder(cfg, w, 1)
     one = Decoder(cuda, cfg, w, max_batch=1)
     w2 = {k: ([a.copy() for a in v] if isinstance(v, list) else v.copy()) for k, v in w.items()}
