@@ -105,6 +105,8 @@ internal static unsafe partial class Native
         int posOffset, nint dCos, nint dSin, int neox, nint stream);
     [LibraryImport(Lib)] internal static partial int smc_add_dev(nint ctx, nint dX, nint dY, long n, nint stream);
     [LibraryImport(Lib)] internal static partial int smc_add_rmsnorm_dev(nint ctx, nint dX, nint dY, nint dW, nint dOut, int rows, int n, float eps, nint stream);
+    [LibraryImport(Lib)] internal static partial int smc_add_rmsnorm_q8_dev(nint ctx, nint dX, nint dY, nint dW, nint dOut, int rows, int n, float eps, nint act, nint stream);
+    [LibraryImport(Lib)] internal static partial int smc_swiglu_quantize_q8_dev(nint ctx, nint dGate, nint dUp, int rows, int f, int ld, nint act, nint stream);
     [LibraryImport(Lib)] internal static partial int smc_argmax_dev(nint ctx, nint dLogits, int rows, int n, nint dOut, nint stream);
     [LibraryImport(Lib)] internal static partial int smc_sample_dev(nint ctx, nint dLogits, int rows, int n, in SmcSampling cfg,
         nint dUniform, nint dWork, nint dTokens, nint stream);
