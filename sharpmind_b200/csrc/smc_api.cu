@@ -472,15 +472,18 @@ static int qmatmul_f32_digits(smc_ctx *ctx, const float *d_in, const smc_weight 
     std::lock_guard<std::mutex> lock(ctx->mu_scratch);  // held until everything is queued, like the Q8 scratch
     int rc;
     smc_q8act *&a = ctx->digits;
-    if (!a || (size_t)a->max_rows * a->max_k < (size_t)3 * M * w->K) {
+    const size_t need = (size_t)3 * M * w->K;
+    if (!a || ctx->digits_cap < need) {
         if (a) {  // growing allocates: make the first call of a new size outside stream capture
             cudaDeviceSynchronize();
             smc_q8act_free(a);
             a = nullptr;
+            ctx->digits_cap = 0;
         }
         if ((rc = smc_q8act_alloc(ctx, 3 * M, w->K, &a))) return rc;
+        ctx->digits_cap = need;
     }
-    a->max_rows = (int)(((size_t)a->max_rows * a->max_k) / w->K), a->max_k = w->K;  // the same bytes, seen with this K
+    a->max_rows = (int)(ctx->digits_cap / w->K), a->max_k = w->K;  // the same allocation (digits_cap values), seen with this K
     const size_t out_bytes = (size_t)3 * M * w->N * sizeof(float);
     if (ctx->digit_out_cap < out_bytes) {
         if (ctx->d_digit_out) {

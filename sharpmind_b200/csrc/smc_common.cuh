@@ -86,6 +86,7 @@ struct smc_ctx {
     bool pin_is[4] = {false, false, false, false};
     unsigned pin_next = 0;
     smc_q8act *digits = nullptr;       // the three int8 digit planes of fp32 activations, stacked as 3 M rows (SMC_ACT_F32)
+    size_t digits_cap = 0;             // values it holds
     float *d_digit_out = nullptr;      // their products [3 M, N]
     size_t digit_out_cap = 0;
     int f32_digits = 1;                // that path on (0: the CUDA-core kernel at every batch size)

@@ -156,6 +156,44 @@ def test_fp32_activations_as_int8_digit_planes(oracle, cuda, dev, dtype, n, k, m
     assert cuda.device_status() == 0
 
 
+def test_fp32_digit_scratch_is_stable_across_shapes_under_capture(oracle, cuda, dev):
+    """The digit planes live in one scratch allocation sized by the largest call so far: alternating between matrices of
+    different K after a warm-up must not allocate again, or a stream capture of the same calls would be invalidated."""
+    import torch
+
+    from sharpmind_b200.ops import Mode
+
+    ws, xs = [], []
+    for n, k in ((64, 14336), (96, 4096), (32, 2048)):
+        ws.append(cuda.register(make_weight(oracle, Q6_K, n, k, f"cap{n}_{k}"), Q6_K, n, k))
+        xs.append(to_dev(synth.normal("gpu", f"capx{k}", (3, k))))
+    outs = [torch.empty((3, w.N), device="cuda") for w in ws]
+    want = [dev.qmatmul(x, w, Mode.ACT_F32).clone() for x, w in zip(xs, ws)]  # warm-up: the scratch reaches its size
+
+    def body():
+        for i in (0, 1, 2, 0, 1):
+            dev.qmatmul(xs[i], ws[i], Mode.ACT_F32, out=outs[i])
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        body()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        body()
+    for o in outs:
+        o.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    for o, w_ in zip(outs, want):
+        assert torch.equal(o, w_)
+    for w in ws:
+        cuda.release(w)
+    assert cuda.device_status() == 0
+
+
 RING_SHAPES = [
     (Q4_K, 304, 4096), (Q4_K, 48, 14336), (Q4_K, 16, 2048), (Q6_K, 64, 14336), (Q6_K, 160, 4096), (Q6_K, 2384, 2048),
     (Q8_0, 272, 5120), (Q8_0, 64, 1024), (Q8_0, 4752, 1024),
