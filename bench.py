@@ -69,7 +69,7 @@ GEMV_SHAPES = {
 # largest captured shape of each format (profiles/gemv_tma_one_row_all_formats.md: reads are 0.998-1.009 of the
 # algorithmic bytes, the rest are dirty lines of earlier kernels leaving the L2 during the capture); traffic grows with
 # the rows a launch covers, so other shapes scale it.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {Q4_K: 1.025, Q6_K: 1.044, Q8_0: 1.040}
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {Q4_K: 1.022, Q6_K: 1.044, Q8_0: 1.040}
 
 
 def parse():
