@@ -262,7 +262,7 @@ gemv_mma_q8_0_tile_kernel(const int8_t *__restrict__ wq, const __half *__restric
 // group gq hold sub-block 2*gq in the low nibbles and 2*gq + 1 in the high ones.  K % 256 == 0; a warp works
 // on whole 256-element blocks.  out += d*sc_j * dx * isum  -  dmin*m_j * (dx * sum(xq))  per sub-block.
 template <int NT>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, NT > 2 ? 1 : 2)
 gemv_mma_q4_K_kernel(const uint8_t *__restrict__ raw, const int8_t *__restrict__ xq, const float *__restrict__ xd,
                      const float *__restrict__ xsd, float *__restrict__ out, int N, int K, int M)
 {
