@@ -59,9 +59,13 @@ __device__ __forceinline__ void mma6(float (&c)[4], const uint32_t (&ah)[4], con
 }
 
 // Shared memory (bf16 planes, plane p of a tile at p * rows * LDB bytes): Q [3][HPC * 64][LD], K [3][32][LD], V [3][32][LD]
-template <int HD, int HPC>
-__global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float *__restrict__ q, const float *__restrict__ kc,
-                                                                     const float *__restrict__ vc, float *__restrict__ out, int T,
+// Q8: the cache holds Q8_0 rows as int8 planes kc / vc [.., maxSeq, HD] with fp16 block scales kd / vd [.., maxSeq, HD / 32]
+// (QuantizedKVCache); a staged value is d * q, a 19-bit number that its three bf16 parts hold exactly, so the contraction
+// sees exactly what ScaledDotProductFlashQ8_0* reads from the cache (AttentionKernels.cs:489-813).
+template <int HD, int HPC, bool Q8>
+__global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float *__restrict__ q, const void *__restrict__ kc,
+                                                                     const void *__restrict__ vc, const __half *__restrict__ kd,
+                                                                     const __half *__restrict__ vd, float *__restrict__ out, int T,
                                                                      int nh, int nkv, int pos0, int maxSeq, float scale)
 {
     constexpr int LDB = HD * 2 + 16;                 // bytes per row of a plane
@@ -78,7 +82,9 @@ __global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float
     const int h = hg * HPC + hl, kvh = (hg * HPC) / (nh / nkv);
     const int t0 = (int)(gridDim.y - 1 - blockIdx.y) * QROWS;  // later rows see more keys: they start first
     const int cta_len = pos0 + min(T, t0 + QROWS);    // keys any row of this CTA sees
-    const float *kbase = kc + (size_t)kvh * maxSeq * HD, *vbase = vc + (size_t)kvh * maxSeq * HD;
+    const float *kbase = static_cast<const float *>(kc) + (size_t)kvh * maxSeq * HD, *vbase = static_cast<const float *>(vc) + (size_t)kvh * maxSeq * HD;
+    const int8_t *kqb = static_cast<const int8_t *>(kc) + (size_t)kvh * maxSeq * HD, *vqb = static_cast<const int8_t *>(vc) + (size_t)kvh * maxSeq * HD;
+    const __half *kdb = Q8 ? kd + (size_t)kvh * maxSeq * (HD / 32) : nullptr, *vdb = Q8 ? vd + (size_t)kvh * maxSeq * (HD / 32) : nullptr;
 
     // ---- Q: split once
     for (int e = threadIdx.x; e < HPC * QROWS * (HD / 4); e += NTH) {
@@ -117,8 +123,16 @@ __global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float
             const int e = threadIdx.x + i * NTH, r = e / (HD / 4), c = e % (HD / 4);
             pk[i] = pv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (start + r < cta_len) {
-                pk[i] = *reinterpret_cast<const float4 *>(kbase + (size_t)(start + r) * HD + 4 * c);
-                pv[i] = *reinterpret_cast<const float4 *>(vbase + (size_t)(start + r) * HD + 4 * c);
+                if (Q8) {  // four codes and their block's scale: the piece is d * q
+                    const size_t row = (size_t)(start + r);
+                    const char4 ck = *reinterpret_cast<const char4 *>(kqb + row * HD + 4 * c), cv = *reinterpret_cast<const char4 *>(vqb + row * HD + 4 * c);
+                    const float dk = __half2float(kdb[row * (HD / 32) + c / 8]), dv = __half2float(vdb[row * (HD / 32) + c / 8]);
+                    pk[i] = make_float4(dk * (float)ck.x, dk * (float)ck.y, dk * (float)ck.z, dk * (float)ck.w);
+                    pv[i] = make_float4(dv * (float)cv.x, dv * (float)cv.y, dv * (float)cv.z, dv * (float)cv.w);
+                } else {
+                    pk[i] = *reinterpret_cast<const float4 *>(kbase + (size_t)(start + r) * HD + 4 * c);
+                    pv[i] = *reinterpret_cast<const float4 *>(vbase + (size_t)(start + r) * HD + 4 * c);
+                }
             }
         }
     };
@@ -240,8 +254,9 @@ __global__ void __launch_bounds__(128 * HPC) sdpa_prefill_mma_kernel(const float
 
 bool smc_sdpa_prefill_mma_supported(int nh, int nkv, int hd) { return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0; }
 
-int smc_launch_sdpa_prefill_mma(smc_ctx *ctx, const float *q, const float *kc, const float *vc, float *out, int T, int nh, int nkv,
-                                int hd, int pos0, int maxSeq, float scale, cudaStream_t s)
+// kd == null: kc / vc are fp32 rows; else the int8 planes and fp16 block scales of a Q8_0 cache
+static int launch_prefill_mma(smc_ctx *ctx, const float *q, const void *kc, const void *vc, const __half *kd, const __half *vd, float *out,
+                              int T, int nh, int nkv, int hd, int pos0, int maxSeq, float scale, cudaStream_t s)
 {
     const int G = nh / nkv;
     auto go = [&](auto kernel, int hpc) {
@@ -249,11 +264,29 @@ int smc_launch_sdpa_prefill_mma(smc_ctx *ctx, const float *q, const float *kc, c
         const size_t ldb = (size_t)hd * 2 + 16;
         const size_t smem = 3 * ((size_t)hpc * QROWS + 2 * KT) * ldb;
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        smc_launch_dep(ctx->use_pdl, kernel, grid, dim3(128 * hpc), smem, s, q, kc, vc, out, T, nh, nkv, pos0, maxSeq, scale);
+        smc_launch_dep(ctx->use_pdl, kernel, grid, dim3(128 * hpc), smem, s, q, kc, vc, kd, vd, out, T, nh, nkv, pos0, maxSeq, scale);
     };
     const bool two = G % 2 == 0 && ctx->attn_hpc != 1;
-    if (hd == 128) two ? go(sdpa_prefill_mma_kernel<128, 2>, 2) : go(sdpa_prefill_mma_kernel<128, 1>, 1);
-    else two ? go(sdpa_prefill_mma_kernel<64, 2>, 2) : go(sdpa_prefill_mma_kernel<64, 1>, 1);
+    if (kd) {
+        if (hd == 128) two ? go(sdpa_prefill_mma_kernel<128, 2, true>, 2) : go(sdpa_prefill_mma_kernel<128, 1, true>, 1);
+        else two ? go(sdpa_prefill_mma_kernel<64, 2, true>, 2) : go(sdpa_prefill_mma_kernel<64, 1, true>, 1);
+    } else {
+        if (hd == 128) two ? go(sdpa_prefill_mma_kernel<128, 2, false>, 2) : go(sdpa_prefill_mma_kernel<128, 1, false>, 1);
+        else two ? go(sdpa_prefill_mma_kernel<64, 2, false>, 2) : go(sdpa_prefill_mma_kernel<64, 1, false>, 1);
+    }
     SMC_LAUNCH_CHECK(ctx);
     return SMC_OK;
+}
+
+int smc_launch_sdpa_prefill_mma(smc_ctx *ctx, const float *q, const float *kc, const float *vc, float *out, int T, int nh, int nkv,
+                                int hd, int pos0, int maxSeq, float scale, cudaStream_t s)
+{
+    return launch_prefill_mma(ctx, q, kc, vc, nullptr, nullptr, out, T, nh, nkv, hd, pos0, maxSeq, scale, s);
+}
+
+// one sequence's Q8_0 cache planes (rows pos0 .. pos0 + T - 1 are the queries' own positions)
+int smc_launch_sdpa_prefill_mma_q8(smc_ctx *ctx, const float *q, const int8_t *kq, const __half *kd, const int8_t *vq, const __half *vd,
+                                   float *out, int T, int nh, int nkv, int hd, int pos0, int maxSeq, float scale, cudaStream_t s)
+{
+    return launch_prefill_mma(ctx, q, kq, vq, kd, vd, out, T, nh, nkv, hd, pos0, maxSeq, scale, s);
 }

@@ -163,6 +163,8 @@ bool smc_mt_supported(const smc_weight *, int M);
 bool smc_sdpa_prefill_mma_supported(int nh, int nkv, int hd);
 int smc_launch_sdpa_prefill_mma(smc_ctx *, const float *q, const float *kc, const float *vc, float *out, int T, int nh, int nkv, int hd,
                                 int pos0, int maxSeq, float scale, cudaStream_t s);
+int smc_launch_sdpa_prefill_mma_q8(smc_ctx *ctx, const float *q, const int8_t *kq, const __half *kd, const int8_t *vq, const __half *vd,
+                                   float *out, int T, int nh, int nkv, int hd, int pos0, int maxSeq, float scale, cudaStream_t s);
 int smc_launch_gemv_mt(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_mma(smc_ctx *, const smc_q8act *, const smc_weight *, float *out, cudaStream_t s);
 int smc_launch_gemv_ref(smc_ctx *, const float *x, const smc_weight *, float *out, int M, int col0, int col1,

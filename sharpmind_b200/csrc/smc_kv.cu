@@ -256,6 +256,17 @@ int smc_launch_sdpa_q8_rows(smc_ctx *ctx, const float *q, const int8_t *kq, cons
                             int batch, int seqLen, int heads, int kvHeads, int hd, int kvLen, int maxSeq, float scale, cudaStream_t s)
 {
     if (hd != 64 && hd != 128) return smc_fail(ctx, SMC_E_UNSUPPORTED, "a Q8_0 cache with headDim %d (64 and 128 are built)", hd);
+    // a chunk of a prompt (16 rows and more): the tensor-core kernel, one sequence at a time, its K / V tiles staged as d * q
+    if (ctx->attn_mma && seqLen >= 16 && smc_sdpa_prefill_mma_supported(heads, kvHeads, hd)) {
+        const size_t per_seq = (size_t)kvHeads * maxSeq * hd;
+        for (int b = 0; b < batch; ++b) {
+            const int rc = smc_launch_sdpa_prefill_mma_q8(ctx, q + (size_t)b * seqLen * heads * hd, kq + b * per_seq, kd + b * (per_seq / 32),
+                                                          vq + b * per_seq, vd + b * (per_seq / 32), out + (size_t)b * seqLen * heads * hd,
+                                                          seqLen, heads, kvHeads, hd, kvLen - seqLen, maxSeq, scale, s);
+            if (rc) return rc;
+        }
+        return SMC_OK;
+    }
     const dim3 grid(seqLen, heads, batch);
     if (hd == 128)
         smc_launch_dep(ctx->use_pdl, sdpa_q8_rows_kernel<128>, grid, dim3(128), 0, s, q, kq, kd, vq, vd, out, seqLen, heads, kvHeads, kvLen, maxSeq, scale);

@@ -177,3 +177,40 @@ def test_prompt_attention_on_tensor_cores(oracle, cuda, hd, heads, kvh):
             assert np.array_equal(single.view(np.uint32), got.view(np.uint32))
     kv.Dispose()
     assert cuda.device_status() == 0
+
+
+@pytest.mark.parametrize("hd,heads,kvh", [(128, 8, 4), (64, 6, 2)])
+def test_prompt_attention_on_tensor_cores_over_a_q8_0_cache(oracle, cuda, hd, heads, kvh):
+    """Chunks of 16 query rows and more over a Q8_0 cache take the tensor-core kernel with its K / V tiles staged as d * q
+    (exact in the three bf16 parts): within 1e-5 of the oracle's ScaledDotProductFlashQ8_0 on the same quantised rows,
+    and of the CUDA-core kernel it replaces; shorter chunks keep that kernel."""
+    B, max_seq = 2, 320
+    kv = ops.KVCache(cuda, B, kvh, max_seq, hd, ops.KVCache.Q8_0)
+    scale = 1.0 / np.sqrt(hd)
+    row = hd // 32 * 34
+    kc = np.zeros((B, kvh, max_seq, row), np.uint8)
+    vc = np.zeros_like(kc)
+    length = 0
+    for tag, s in (("p", 150), ("q", 77), ("r", 5), ("s", 64)):
+        k = synth.normal("kvmmaq8", f"k{tag}{hd}", (B, s, kvh, hd))
+        v = synth.normal("kvmmaq8", f"v{tag}{hd}", (B, s, kvh, hd))
+        if tag == "p":
+            k *= 4.0
+        kv.Update(to_dev(k), to_dev(v))
+        kc[:, :, length:length + s] = _rows_q8(oracle, k).transpose(0, 2, 1, 3)
+        vc[:, :, length:length + s] = _rows_q8(oracle, v).transpose(0, 2, 1, 3)
+        length += s
+        q = synth.normal("kvmmaq8", f"q{tag}{hd}", (B, s, heads, hd))
+        got = kv.attention(to_dev(q), scale).cpu().numpy()
+        want = _oracle_attention(oracle, ops.KVCache.Q8_0, q, kc, vc, length, scale)
+        err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
+        assert err <= 1e-5, (tag, err)
+        cuda.set_option("prompt_attention_mma", 0)
+        try:
+            old = kv.attention(to_dev(q), scale).cpu().numpy()
+        finally:
+            cuda.set_option("prompt_attention_mma", 1)
+        assert np.max(np.abs(old - got)) <= 2e-5 * np.max(np.abs(want))
+        assert np.array_equal(old.view(np.uint32), got.view(np.uint32)) == (s < 16)  # which kernel ran
+    kv.Dispose()
+    assert cuda.device_status() == 0
