@@ -157,6 +157,12 @@ SMC_API int smc_weight_shape(const smc_weight *w, int *dtype, int *N, int *K);
  * LogitOps.cs:143).  host_raw must have been registered. */
 SMC_API int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, float *output, int M,
                              int K, int N, int dtype, int mode);
+/* Page-locks `bytes` of host memory at `ptr` (cudaHostRegister) so that the host entry points copy from / to it directly,
+ * and releases it again: for hosts that do not link the CUDA runtime themselves (a .NET host pins its float[] with a
+ * GCHandle and registers the address once; unregister before the handle is freed).  The memory must stay allocated
+ * and must not move while registered. */
+SMC_API int smc_host_register(smc_ctx *ctx, void *ptr, size_t bytes);
+SMC_API int smc_host_unregister(smc_ctx *ctx, void *ptr);
 /* The same slot for a caller that kept the handle registration returned (an InferenceLinearLayer that registers in
  * SetRawWeight, InferenceLinearLayer.cs:200-221, and stores the handle next to RawQuantizedData): no pointer lookup,
  * and weights that never had a host copy (registered from device memory) can be used.  M, K, N as in

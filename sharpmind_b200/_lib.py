@@ -32,6 +32,8 @@ SIGNATURES = {
     "smc_weight_release": (c_int, [c_void_p, c_void_p]),
     "smc_weight_shape": (c_int, [c_void_p, C.POINTER(c_int), C.POINTER(c_int), C.POINTER(c_int)]),
     "smc_qmatmul_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
+    "smc_host_register": (c_int, [c_void_p, c_void_p, C.c_size_t]),
+    "smc_host_unregister": (c_int, [c_void_p, c_void_p]),
     "smc_qmatmul_host_w": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int]),
     "smc_vecdot_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, C.POINTER(c_float)]),
     "smc_swiglu_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int]),

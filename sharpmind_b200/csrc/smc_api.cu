@@ -793,6 +793,29 @@ int smc_qmatmul_host(smc_ctx *ctx, const float *input, const void *host_raw, flo
     return qmatmul_host_impl(ctx, input, w, output, M, mode);
 }
 
+int smc_host_register(smc_ctx *ctx, void *ptr, size_t bytes)
+{
+    if (!ctx || !ptr || bytes == 0) return smc_fail(ctx, SMC_E_INVALID, "host_register: bad arguments");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    SMC_CUDA(ctx, cudaHostRegister(ptr, bytes, cudaHostRegisterPortable));
+    for (int i = 0; i < 4; ++i)
+        if (ctx->pin_seen[i] == ptr) ctx->pin_seen[i] = nullptr;  // a remembered "pageable" answer for this address is stale
+    return SMC_OK;
+}
+
+int smc_host_unregister(smc_ctx *ctx, void *ptr)
+{
+    if (!ctx || !ptr) return smc_fail(ctx, SMC_E_INVALID, "host_unregister: bad arguments");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    SMC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // no copy of this context may still be reading it
+    SMC_CUDA(ctx, cudaHostUnregister(ptr));
+    for (int i = 0; i < 4; ++i)
+        if (ctx->pin_seen[i] == ptr) ctx->pin_seen[i] = nullptr;
+    return SMC_OK;
+}
+
 int smc_qmatmul_host_w(smc_ctx *ctx, const float *input, const smc_weight *w, float *output, int M, int K, int N, int mode)
 {
     if (!ctx || !input || !w || !output || M < 0) return smc_fail(ctx, SMC_E_INVALID, "qmatmul_host_w: bad arguments");

@@ -49,6 +49,8 @@ internal static unsafe partial class Native
     [LibraryImport(Lib)] internal static partial nint smc_last_error(nint ctx);
     [LibraryImport(Lib, StringMarshalling = StringMarshalling.Utf8)]
     internal static partial int smc_set_option(nint ctx, string name, int value);
+    [LibraryImport(Lib)] internal static partial int smc_host_register(nint ctx, void* ptr, nuint bytes);
+    [LibraryImport(Lib)] internal static partial int smc_host_unregister(nint ctx, void* ptr);
     [LibraryImport(Lib)] internal static partial long smc_raw_tensor_bytes(int dtype, long n, long k);
     [LibraryImport(Lib)] internal static partial int smc_device_status(nint ctx, out int status);
     [LibraryImport(Lib)] internal static partial int smc_synchronize(nint ctx);

@@ -111,6 +111,13 @@ class CudaContext:
     def synchronize(self):
         self.check(self.lib.smc_synchronize(self.h))
 
+    def host_register(self, a: np.ndarray):
+        """Page-locks a host array in place (smc_host_register): the host slots then copy from / to it directly."""
+        self.check(self.lib.smc_host_register(self.h, a.ctypes.data, a.nbytes))
+
+    def host_unregister(self, a: np.ndarray):
+        self.check(self.lib.smc_host_unregister(self.h, a.ctypes.data))
+
     def set_option(self, name: str, value: int):
         """smc_set_option: per-context tuning and kernel-selection switches (the names and their meaning are listed
         with the entry point in the C header); none of them changes a result beyond its mode's bound."""

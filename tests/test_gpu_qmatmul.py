@@ -433,6 +433,17 @@ def test_host_slot_equals_device_path_and_guards(oracle, cuda, dev):
             oo = torch.zeros((m, n), dtype=torch.float32).pin_memory().numpy() if pin_out else np.zeros((m, n), np.float32)
             q.QuantizedMatMulQ8_0(xi, raw, oo, m, k, n)
             assert np.array_equal(bits(oo), bits(ref)), (pin_in, pin_out)
+    # an ordinary array page-locked in place through the library (what a host without the CUDA runtime does)
+    xi, oo = x.copy(), np.zeros((m, n), np.float32)
+    q.QuantizedMatMulQ8_0(xi, raw, oo, m, k, n)   # seen as pageable first: the remembered answer must not stick
+    cuda.host_register(xi), cuda.host_register(oo)
+    oo[:] = 0
+    q.QuantizedMatMulQ8_0(xi, raw, oo, m, k, n)
+    assert np.array_equal(bits(oo), bits(ref))
+    cuda.host_unregister(xi), cuda.host_unregister(oo)
+    oo[:] = 0
+    q.QuantizedMatMulQ8_0(xi, raw, oo, m, k, n)
+    assert np.array_equal(bits(oo), bits(ref))
     q = ops.QuantizationOps(cuda)
     out = np.zeros((m, n), np.float32)
     with pytest.raises(ops.InvalidOperationException):  # shape does not match the registration
