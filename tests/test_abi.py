@@ -68,3 +68,21 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "sm_oracle" not in src and "oracle/" not in src and "import oracle" not in src, f
+
+
+def test_every_option_is_documented_where_it_is_declared():
+    """smc_set_option's names: each one the library accepts is described in the header and in the integration notes,
+    and the header describes none the library does not know; the C# source binds every declared entry point."""
+    api = open(os.path.join(ROOT, "sharpmind_b200", "csrc", "smc_api.cu")).read()
+    accepted = set(re.findall(r'strcmp\(name, "([a-z0-9_]+)"\)', api))
+    assert len(accepted) >= 10
+    header = open(HEADER).read()
+    block = header[header.index("smc_set_option") - 6000:header.index("SMC_API int smc_set_option")]
+    documented = set(re.findall(r'^ \*\s+"([a-z0-9_]+)"', block, flags=re.M))
+    assert accepted == documented, (sorted(accepted - documented), sorted(documented - accepted))
+    notes = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    for name in accepted:
+        assert f"`{name}`" in notes, name
+    native = open(os.path.join(ROOT, "sharpmind_b200", "dotnet", "SharpMind.Cuda", "Native.cs")).read()
+    for sym in declared_symbols():
+        assert re.search(rf"\b{sym}\(", native), f"{sym} has no P/Invoke declaration"
